@@ -1,0 +1,114 @@
+/* C ABI of the B200 interpreter backend (libtpucb.so).
+ *
+ * The reference exposes this path as C++ classes, not as a C ABI:
+ *   class MlirModuleInterpreter   include/tpuc/MlirModuleInterpreter.h:32-83
+ *   class CPUOpKernel::invoke()   include/tpuc/Interpreter/cpukernel.h:87-159
+ *   pymlir.module (pybind11)      bindings/python/pymlir.cpp:289-311
+ *   kl_diversity_hist (extern C)  bindings/python/kld/calibration_math.cpp:342-344
+ * Each entry point below names the member it stands in for. Host tensors cross
+ * this boundary exactly as they do in the reference: float32 NCHW "containers"
+ * (cpukernel.h:15-78) holding int8 / bf16 / fp32 values. Host memory passed in
+ * is borrowed for the duration of the call only.
+ *
+ * Every function returns 0 on success and a non-zero status otherwise;
+ * tpucb_last_error() returns the message of the calling thread's last failure.
+ * There is no CPU fallback: without a CUDA device every compute call fails.
+ */
+#ifndef TPUCB_H_
+#define TPUCB_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct tpucb_interp tpucb_interp;
+
+const char *tpucb_last_error(void);
+/* Library/ABI version, for the binding to check. */
+int tpucb_version(void);
+
+/* ---- MlirModuleInterpreter ------------------------------------------------- */
+
+/* MlirModuleInterpreter::MlirModuleInterpreter(max_batch_size)
+ * (MlirModuleInterpreter.h:35). `device` is the CUDA ordinal; the interpreter owns
+ * one stream and every device tensor of the module. */
+int tpucb_interp_create(int device, tpucb_interp **out);
+int tpucb_interp_destroy(tpucb_interp *it);
+
+/* MlirModuleInterpreter::updateWeightMap (MlirModuleInterpreter.cpp:352-369): register
+ * one tpu.load_weight tensor by name as fp32 values, before tpucb_interp_load_module. */
+int tpucb_interp_set_weight(tpucb_interp *it, const char *name, const float *data,
+                            const int64_t *shape, int rank);
+
+/* MlirModuleInterpreter::loadModule (MlirModuleInterpreter.cpp:73-83, 118-350). The module
+ * is given as text, one op per line:
+ *     <op_type> name=<result> in=<operand>,<operand>,... shape=<d0>,<d1>,.. dtype=INT8|BF16|FP32 key=value ...
+ * with the operand order of the TPU dialect op ("-" for an absent operand) and the
+ * attribute names of the dialect's param structs. An op the backend does not implement
+ * is an error here, not at run time. */
+int tpucb_interp_load_module(tpucb_interp *it, const char *module_text);
+
+/* MlirModuleInterpreter::setTensor (MlirModuleInterpreter.cpp:407-417). */
+int tpucb_interp_set_tensor(tpucb_interp *it, const char *name, const float *data, size_t numel);
+/* MlirModuleInterpreter::invoke / invokeTo (MlirModuleInterpreter.cpp:371-381); an empty or
+ * NULL name runs the whole module. Synchronous, like the reference. */
+int tpucb_interp_invoke(tpucb_interp *it);
+int tpucb_interp_invoke_to(tpucb_interp *it, const char *name);
+/* Asynchronous halves of invoke: enqueue on the interpreter's stream / wait and check the
+ * device error word. (No reference counterpart: the CPU interpreter is synchronous.) */
+int tpucb_interp_launch(tpucb_interp *it);
+int tpucb_interp_sync(tpucb_interp *it);
+/* MlirModuleInterpreter::getTensor (deep copy, MlirModuleInterpreter.cpp:419-427). */
+int tpucb_interp_get_tensor(tpucb_interp *it, const char *name, float *out, size_t numel);
+/* getTensorShape / getDataType / getAllTensorName (MlirModuleInterpreter.h:52-60). */
+int tpucb_interp_get_tensor_shape(tpucb_interp *it, const char *name, int64_t *shape, int *rank);
+/* writes "INT8", "BF16" or "FP32" */
+int tpucb_interp_get_data_type(tpucb_interp *it, const char *name, char *out, size_t cap);
+/* names separated by '\n'; *needed receives the required capacity */
+int tpucb_interp_get_all_tensor_names(tpucb_interp *it, char *out, size_t cap, size_t *needed);
+/* input_details / output_details (MlirModuleInterpreter.h:79-80): "name:numel" lines */
+int tpucb_interp_get_details(tpucb_interp *it, int outputs, char *out, size_t cap, size_t *needed);
+/* op_info of pymlir (bindings/python/pymlir.cpp:62-97): "name\ttype\tdtype\tshape" lines */
+int tpucb_interp_get_op_info(tpucb_interp *it, char *out, size_t cap, size_t *needed);
+
+/* Options: "cuda_graph" (0/1, default 1): replay the op list as one CUDA graph. */
+int tpucb_interp_set_option(tpucb_interp *it, const char *key, int value);
+/* Per-op device time of one eager pass (CUDA events on the interpreter's stream);
+ * ms[i] belongs to the i-th line of tpucb_interp_get_op_info. Returns the op count. */
+int tpucb_interp_profile(tpucb_interp *it, float *ms, int cap, int *count);
+/* Device time in milliseconds of `iters` back-to-back whole-module launches. */
+int tpucb_interp_time_launches(tpucb_interp *it, int iters, float *ms_total);
+/* Number of this library's kernels one whole-module invoke launches. */
+int tpucb_interp_kernel_count(tpucb_interp *it, int *count);
+
+/* Device pointer, byte size and channel pitch of a tensor's NHWC storage (for the
+ * calibration statistics entry points below and for torch.distributed collectives). */
+int tpucb_interp_tensor_device(tpucb_interp *it, const char *name, void **dev, size_t *bytes,
+                               int *channels, int *channel_pitch, int *dtype);
+
+/* Pinned host buffers for the e2e path. */
+int tpucb_host_alloc(void **ptr, size_t bytes);
+int tpucb_host_free(void *ptr);
+
+/* ---- calibration statistics (python/cvi_toolkit/calibration/kld_calibrator.py) --------- */
+
+/* find_min_max_abs (kld_calibrator.py:269-296): running min / max over the fp32 tensor's
+ * real channels, folded into stats[0]=min, stats[1]=max (device floats, caller-initialised
+ * to +inf / -inf). */
+int tpucb_calib_minmax(tpucb_interp *it, const char *name, float *d_stats);
+/* histogram (kld_calibrator.py:31-43): adds the tensor's |x| != 0 values to a device
+ * histogram of `bins` int64 counts with width abs_max / (bins - 1). */
+int tpucb_calib_hist(tpucb_interp *it, const char *name, float abs_max, int bins, int64_t *d_hist);
+/* kl_diversity_hist (calibration_math.cpp:283-344) for `count` histograms at once:
+ * d_hist [count][bins] int64 device counts, widths [count] host floats, thresholds
+ * [count] host floats out. */
+int tpucb_calib_kld(tpucb_interp *it, const int64_t *d_hist, const float *widths, int count,
+                    int bins, float *thresholds);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TPUCB_H_ */

@@ -1,0 +1,8 @@
+"""B200-native execution backend for the tpu_compiler interpreter path.
+
+``module`` mirrors ``pymlir.module`` (bindings/python/pymlir.cpp:289-311) over the
+C ABI of ``libtpucb.so``; ``graphs`` builds the module text and synthetic weights
+of the benchmark networks; ``calibration`` mirrors ``ActivationCalibrator``.
+"""
+from ._lib import TpucbError, lib  # noqa: F401
+from .interpreter import module  # noqa: F401

@@ -1,0 +1,153 @@
+// Calibration statistics on device.
+//   minmax_f32_kernel  find_min_max_abs          python/cvi_toolkit/calibration/kld_calibrator.py:269-296
+//   hist_f32_kernel    BaseKldCalibrator.histogram                       kld_calibrator.py:31-43
+//   kld_kernel         kl_diversity_hist / kl_calc_thread   bindings/python/kld/calibration_math.cpp:169-223, 283-344
+// Tensors are fp32 NHWC with channel pitch cp; padded lanes are skipped.
+#pragma once
+#include "common.cuh"
+
+namespace tpucb {
+
+__device__ __forceinline__ void atomic_max_f32(float *addr, float v) {
+  if (v >= 0) atomicMax(reinterpret_cast<int *>(addr), __float_as_int(v));
+  else atomicMin(reinterpret_cast<unsigned int *>(addr), __float_as_uint(v));
+}
+__device__ __forceinline__ void atomic_min_f32(float *addr, float v) {
+  if (v >= 0) atomicMin(reinterpret_cast<int *>(addr), __float_as_int(v));
+  else atomicMax(reinterpret_cast<unsigned int *>(addr), __float_as_uint(v));
+}
+
+// stats[0] = running min, stats[1] = running max.
+__global__ void minmax_f32_kernel(const float *__restrict__ x, size_t pixels, int c, int cp, float *stats) {
+  float mn = INFINITY, mx = -INFINITY;
+  const size_t total = pixels * (size_t)cp;
+  if ((cp & 3) == 0 && (c & 3) == 0) {
+    const size_t nvec = total / 4;
+    const int vpp = cp / 4, vreal = c / 4;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) {
+      if ((int)(i % vpp) >= vreal) continue;
+      float4 v = reinterpret_cast<const float4 *>(x)[i];
+      mn = fminf(fminf(mn, v.x), fminf(fminf(v.y, v.z), v.w));
+      mx = fmaxf(fmaxf(mx, v.x), fmaxf(fmaxf(v.y, v.z), v.w));
+    }
+  } else {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+      if ((int)(i % cp) >= c) continue;
+      float v = x[i];
+      mn = fminf(mn, v);
+      mx = fmaxf(mx, v);
+    }
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  }
+  __shared__ float smn[32], smx[32];
+  if ((threadIdx.x & 31) == 0) {
+    smn[threadIdx.x >> 5] = mn;
+    smx[threadIdx.x >> 5] = mx;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int i = 1; i < (int)(blockDim.x >> 5); ++i) {
+      mn = fminf(mn, smn[i]);
+      mx = fmaxf(mx, smx[i]);
+    }
+    if (mn <= mx) {
+      atomic_min_f32(stats, mn);
+      atomic_max_f32(stats + 1, mx);
+    }
+  }
+}
+
+// bins <= 4096. idx = floor(|x| / width + 0.5) in fp32 for x != 0; CTA-private shared histogram with
+// warp-aggregated atomics (lanes that hit the same bin elect one adder), flushed with 64-bit atomics.
+__global__ void hist_f32_kernel(const float *__restrict__ x, size_t pixels, int c, int cp, float width, int bins,
+                                unsigned long long *__restrict__ hist) {
+  extern __shared__ unsigned int s_h[];
+  for (int i = threadIdx.x; i < bins; i += blockDim.x) s_h[i] = 0;
+  __syncthreads();
+  const size_t total = pixels * (size_t)cp;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  const size_t rounds = (total + stride - 1) / stride;
+  size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+  for (size_t rd = 0; rd < rounds; ++rd, i += stride) {
+    int b = -1;
+    if (i < total && (int)(i % cp) < c) {
+      float t = fabsf(x[i]);
+      if (t != 0.0f) {
+        float f = floorf(__fadd_rn(__fdiv_rn(t, width), 0.5f));
+        if (f <= (float)(bins - 1)) b = (int)f;
+      }
+    }
+    unsigned active = __ballot_sync(0xffffffffu, b >= 0);
+    if (b >= 0) {
+      unsigned peers = __match_any_sync(active, b);
+      int leader = __ffs(peers) - 1;
+      if ((int)(threadIdx.x & 31) == leader) atomicAdd(&s_h[b], (unsigned)__popc(peers));
+    }
+  }
+  __syncthreads();
+  for (int j = threadIdx.x; j < bins; j += blockDim.x)
+    if (s_h[j]) atomicAdd(&hist[j], (unsigned long long)s_h[j]);
+}
+
+// One CTA per (histogram, candidate). N <= 4096 bins, 128-bin target. The float / double mix and
+// the accumulation order of kl_calc_thread are kept: P and the running sums are sequential fp32
+// additions of the converted counts; each KL term is formed in double and added into an fp32
+// accumulator in index order.
+__global__ void kld_kernel(const long long *__restrict__ hists, int N, float *__restrict__ kl_out) {
+  extern __shared__ unsigned char kld_smem[];
+  float *P = reinterpret_cast<float *>(kld_smem);
+  float *Q = P + N;
+  double *term = reinterpret_cast<double *>(Q + N);
+  __shared__ float s_sum, s_tail;
+  __shared__ long long s_count;
+  const int BINS = 128;
+  const int KL_NUM = N / BINS;
+  const long long *hist = hists + (size_t)(blockIdx.x / KL_NUM) * N;
+  const int i = (blockIdx.x % KL_NUM + 1) * BINS;
+  const int tid = threadIdx.x;
+  if (tid == 0) {
+    long long cnt = 0;
+    for (int j = 0; j < N; ++j) cnt += hist[j];
+    s_count = cnt;
+  } else if (tid == 32) {
+    float tail = 0.0f;
+    for (int j = i - 1; j < N; ++j) tail += (float)hist[j];
+    s_tail = tail;
+  } else if (tid == 64) {
+    float sum = 0.0f;
+    for (int j = 0; j < i; ++j) sum += (float)hist[j];
+    s_sum = sum;
+  }
+  __syncthreads();
+  const float fcount = (float)s_count;
+  for (int j = tid; j < i; j += blockDim.x) {
+    float p = j == i - 1 ? s_tail : (float)hist[j];
+    P[j] = p / fcount;
+  }
+  const int expand = i / BINS;
+  for (int j = tid; j < BINS; j += blockDim.x) {
+    float sum_bin = 0.0f, pos = 0.0f;
+    for (int k = 0; k < expand; ++k) {
+      long long h = hist[j * expand + k];
+      sum_bin += (float)h;
+      pos += h > 0 ? 1.0f : 0.0f;
+    }
+    pos = pos == 0.0f ? 1.0f : pos;
+    float q_base = sum_bin / pos / s_sum;
+    for (int k = 0; k < expand; ++k) Q[j * expand + k] = hist[j * expand + k] ? q_base : 0.0f;
+  }
+  __syncthreads();
+  for (int j = tid; j < i; j += blockDim.x)
+    term[j] = (double)P[j] * (log10((double)P[j] + 1e-30) - log10((double)Q[j] + 1e-30));
+  __syncthreads();
+  if (tid == 0) {
+    float kl = 0.0f;
+    for (int j = 0; j < i; ++j) kl = (float)((double)kl + term[j]);
+    kl_out[blockIdx.x] = kl;
+  }
+}
+
+} // namespace tpucb

@@ -1,0 +1,107 @@
+// Shared device/host helpers for the B200 interpreter backend.
+//
+// The requantisation and rounding primitives restate, for the device, the
+// reference's QuantizationArithmetic.cpp free functions
+// (lib/Dialect/TPU/Quantization/QuantizationArithmetic.cpp):
+//   qdm_requant      <- applyMultiplierAndRShiftAndSaturateInt8(.., qdm=true)  :518-539
+//                       (SaturatingRoundingDoublingHighMul :501-509,
+//                        RoundingDivideByPOT :487-499, saturateInt8 :301-334)
+//   mul_rshift_sat8  <- the same function with qdm=false                      :526
+//   rshift_sat8      <- applyRShiftAndSaturateInt8                            :481-483
+//   f32_to_bf16_bits <- F32ToBF16                                             :873-910
+//   f32_to_int8_rne  <- F32ToInt8(v, 0) / F32ToInt (round half to even on |v|) :918-947
+#pragma once
+#include <cstdint>
+#include <cuda_runtime.h>
+
+#define TPUCB_HD __host__ __device__ __forceinline__
+
+namespace tpucb {
+
+TPUCB_HD int clamp_i8(int q) { return q > 127 ? 127 : (q < -128 ? -128 : q); }
+
+// gemmlowp-style rounding doubling high multiply followed by a rounding right
+// shift and int8 saturation. v: int32 accumulator (bias already added),
+// M: multiplier as int32, r: right shift in [0,31].
+TPUCB_HD int qdm_requant(int32_t v, int32_t M, int r) {
+  long long ab = (long long)v * (long long)M;
+  long long x = ab + (ab >= 0 ? (1ll << 30) : (1ll - (1ll << 30)));
+  // C++ division by 2^31 truncates toward zero.
+  long long fl = x >> 31;
+  if (x < 0 && (x & 0x7fffffffll) != 0) fl += 1;
+  int32_t hi = (int32_t)fl;
+  int32_t q;
+  if (hi == 0 || r == 0) {
+    q = hi;
+  } else {
+    int32_t mask = (int32_t)((1ll << r) - 1);
+    int32_t rem = hi & mask;
+    int32_t thr = (mask >> 1) + (hi < 0 ? 1 : 0);
+    q = (hi >> r) + (rem > thr ? 1 : 0);
+  }
+  return clamp_i8(q);
+}
+
+// saturateInt8(floor(v * M / 2^r + 0.5)) for small integer v (|v*M| < 2^24 in the
+// reference's float; here integer, exact for |v*M| < 2^31): (v*M + 2^(r-1)) >> r.
+TPUCB_HD int mul_rshift_sat8(int32_t v, int32_t M, int r) {
+  int32_t t = v * M;
+  int32_t q = r == 0 ? t : ((t + (1 << (r - 1))) >> r);
+  return clamp_i8(q);
+}
+
+TPUCB_HD int rshift_sat8(int32_t v, int r) {
+  int32_t q = r == 0 ? v : ((v + (1 << (r - 1))) >> r);
+  return clamp_i8(q);
+}
+
+TPUCB_HD uint32_t f32_bits(float f) {
+#ifdef __CUDA_ARCH__
+  return __float_as_uint(f);
+#else
+  union { float f; uint32_t u; } c;
+  c.f = f;
+  return c.u;
+#endif
+}
+TPUCB_HD float bits_f32(uint32_t u) {
+#ifdef __CUDA_ARCH__
+  return __uint_as_float(u);
+#else
+  union { float f; uint32_t u; } c;
+  c.u = u;
+  return c.f;
+#endif
+}
+
+// Round-to-nearest-even BF16 with the hardware quirk that any exponent-all-ones
+// result (inf/NaN, either sign) becomes +max-finite 0x7f7f.
+TPUCB_HD uint16_t f32_to_bf16_bits(float f, bool rounding = true) {
+  uint32_t u = f32_bits(f);
+  if (!rounding) return (uint16_t)(u >> 16);
+  u += 0x7fffu + ((u >> 16) & 1u);
+  uint16_t h = (uint16_t)(u >> 16);
+  if ((h & 0x7f80) == 0x7f80) h = 0x7f7f;
+  return h;
+}
+TPUCB_HD float bf16_bits_to_f32(uint16_t h) { return bits_f32((uint32_t)h << 16); }
+TPUCB_HD float bf16_round(float f, bool rounding = true) {
+  return bf16_bits_to_f32(f32_to_bf16_bits(f, rounding));
+}
+
+// F32ToInt8(v, 0): round half to even on the magnitude, then saturate.
+__device__ __forceinline__ int f32_to_int8_rne(float v) {
+  // rintf is round-half-even and symmetric in sign, identical to the reference's
+  // modf-based rule for every finite v; clamp before the int conversion.
+  float r = rintf(v);
+  r = fminf(fmaxf(r, -128.0f), 127.0f);
+  return (int)r;
+}
+// F32ToInt8(v, 1): C cast (truncate) then saturate.
+__device__ __forceinline__ int f32_to_int8_rz(float v) {
+  float r = truncf(v);
+  r = fminf(fmaxf(r, -128.0f), 127.0f);
+  return (int)r;
+}
+
+} // namespace tpucb

@@ -1,0 +1,212 @@
+// Host planner for the INT8 implicit-GEMM kernel: weight packing, TMA tensor
+// maps, tile-shape heuristics and the launch. The geometry follows parseConvParam
+// (lib/Dialect/TPU/IR/TPUOperationSupport.cpp:366-428): four independent pads, the
+// output size taken from the result type, dilation, optional input zero-insertion.
+#pragma once
+#include "conv_gemm_i8.cuh"
+#include "host_common.h"
+#include "mem_kernels.cuh"
+
+#include <cudaTypedefs.h>
+
+namespace tpucb {
+
+struct ConvGeom {
+  int n, ic, ih, iw, oc, oh, ow, g, kh, kw, sh, sw, pt, pb, pl, pr, dh, dw, ins_h, ins_w;
+};
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                  const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+typedef CUresult (*EncodeIm2colFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                   const cuuint64_t *, const cuuint64_t *, const int *, const int *,
+                                   cuuint32_t, cuuint32_t, const cuuint32_t *, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                   CUtensorMapFloatOOBfill);
+
+struct TmaApi {
+  EncodeTiledFn tiled = nullptr;
+  EncodeIm2colFn im2col = nullptr;
+  int driver_version = 0;
+};
+
+// The driver entry points are fetched through the runtime so that the library carries no
+// link-time dependency on the driver library (it must load on machines without a GPU).
+inline const TmaApi &tma_api() {
+  static TmaApi api = [] {
+    TmaApi a;
+    void *fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    TPUCB_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
+    TPUCB_CHECK(fn && q == cudaDriverEntryPointSuccess, "cuTensorMapEncodeTiled not available");
+    a.tiled = (EncodeTiledFn)fn;
+    fn = nullptr;
+    TPUCB_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeIm2col", &fn, cudaEnableDefault, &q));
+    TPUCB_CHECK(fn && q == cudaDriverEntryPointSuccess, "cuTensorMapEncodeIm2col not available");
+    a.im2col = (EncodeIm2colFn)fn;
+    TPUCB_CUDA(cudaDriverGetVersion(&a.driver_version));
+    return a;
+  }();
+  return api;
+}
+
+inline CUtensorMapSwizzle swizzle_for(int BK) {
+  return BK == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                   : (BK == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
+}
+
+// tcgen05 instruction descriptor for kind::i8: D = s32 (bits 4-5 = 2), A and B signed
+// 8-bit (bits 7-9 and 10-12 = 1), both K-major, N >> 3 at bit 17, M >> 4 at bit 24.
+inline uint32_t make_idesc_i8(int M, int N) {
+  return (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) |
+         ((uint32_t)(M >> 4) << 24);
+}
+
+struct ConvPlan {
+  CUtensorMap tmA, tmB;
+  ConvGemmParams p;
+  dim3 grid;
+  size_t smem = 0;
+  bool use_patch = false;
+  PatchArgs patch;
+  int8_t *patch_buf = nullptr; // scratch: expanded patch matrix [M][kp]
+  size_t patch_bytes = 0;
+  const int8_t *in = nullptr;
+  double ops = 0, bytes = 0; // algorithmic work of one launch
+};
+
+inline int pick_bk(int k_bytes) {
+  int best = 128, best_cost = 1 << 30;
+  for (int bk : {128, 64, 32}) {
+    int cost = round_up(k_bytes, bk);
+    if (cost < best_cost) {
+      best_cost = cost;
+      best = bk;
+    }
+  }
+  return best;
+}
+
+// Pack OIHW fp32 weights (integer-valued) to int8 [oc_pad][taps][cin_pad] for the im2col
+// path, or [oc_pad][1][kp] with K order (r, s, c) for the patch path. For grouped
+// convolution the caller passes one group's slice.
+inline std::vector<int8_t> pack_conv_weights(const float *w, int oc, int icg, int kh, int kw,
+                                             int oc_pad, int cin_pad, bool patch, int kp) {
+  const int taps = kh * kw;
+  std::vector<int8_t> out((size_t)oc_pad * (patch ? kp : taps * cin_pad), 0);
+  for (int o = 0; o < oc; ++o)
+    for (int c = 0; c < icg; ++c)
+      for (int r = 0; r < kh; ++r)
+        for (int s = 0; s < kw; ++s) {
+          int8_t v = (int8_t)(int)w[(((size_t)o * icg + c) * kh + r) * kw + s];
+          if (patch) out[(size_t)o * kp + (size_t)(r * kw + s) * icg + c] = v;
+          else out[((size_t)o * taps + (r * kw + s)) * cin_pad + c] = v;
+        }
+  return out;
+}
+
+inline void encode_weight_map(CUtensorMap *tm, const int8_t *d_w, int oc_pad, int taps, int k_inner,
+                              int BK, int BN) {
+  cuuint64_t dims[3] = {(cuuint64_t)k_inner, (cuuint64_t)taps, (cuuint64_t)oc_pad};
+  cuuint64_t strides[2] = {(cuuint64_t)k_inner, (cuuint64_t)k_inner * taps};
+  cuuint32_t box[3] = {(cuuint32_t)BK, 1, (cuuint32_t)BN};
+  cuuint32_t es[3] = {1, 1, 1};
+  CUresult r = tma_api().tiled(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, (void *)d_w, dims, strides, box,
+                               es, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_for(BK),
+                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  TPUCB_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled(weights) failed: %d", (int)r);
+}
+
+inline void encode_matrix_map(CUtensorMap *tm, const int8_t *d_a, int rows, int k_inner, int ld,
+                              int BK) {
+  cuuint64_t dims[2] = {(cuuint64_t)k_inner, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld};
+  cuuint32_t box[2] = {(cuuint32_t)BK, 128};
+  cuuint32_t es[2] = {1, 1};
+  CUresult r = tma_api().tiled(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void *)d_a, dims, strides, box,
+                               es, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_for(BK),
+                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  TPUCB_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled(matrix) failed: %d", (int)r);
+}
+
+inline void encode_im2col_map(CUtensorMap *tm, const int8_t *d_in, const ConvGeom &g, int cp,
+                              int BK) {
+  cuuint64_t dims[4] = {(cuuint64_t)cp, (cuuint64_t)g.iw, (cuuint64_t)g.ih, (cuuint64_t)g.n};
+  cuuint64_t strides[3] = {(cuuint64_t)cp, (cuuint64_t)cp * g.iw, (cuuint64_t)cp * g.iw * g.ih};
+  // Base-pixel bounding box: lower corner = -pad_lo, upper corner chosen so that the number
+  // of base positions along each axis equals the op's output extent:
+  //   (extent + upper - lower - 1) / stride + 1 == out
+  int lower[2] = {-g.pl, -g.pt};
+  // Textbook value: pad_hi - (k - 1) * dilation. When the op's output extent does not follow
+  // from its pads by the usual formula (the result type rules), use the tight value instead.
+  int upper[2] = {g.pr - (g.kw - 1) * g.dw, g.pb - (g.kh - 1) * g.dh};
+  if ((g.iw + upper[0] - lower[0] - 1) / g.sw + 1 != g.ow)
+    upper[0] = (g.ow - 1) * g.sw + 1 - g.iw - g.pl;
+  if ((g.ih + upper[1] - lower[1] - 1) / g.sh + 1 != g.oh)
+    upper[1] = (g.oh - 1) * g.sh + 1 - g.ih - g.pt;
+  cuuint32_t es[4] = {1, (cuuint32_t)g.sw, (cuuint32_t)g.sh, 1};
+  CUresult r = tma_api().im2col(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, (void *)d_in, dims, strides,
+                                lower, upper, (cuuint32_t)BK, 128, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                swizzle_for(BK), CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  TPUCB_CHECK(r == CUDA_SUCCESS,
+              "cuTensorMapEncodeIm2col failed: %d (iw=%d ih=%d lower=%d,%d upper=%d,%d)", (int)r,
+              g.iw, g.ih, lower[0], lower[1], upper[0], upper[1]);
+  // Drivers up to CUDA 13.1 encode im2col maps of tensors smaller than 128 KiB with a flag
+  // (bit 21 of the second 64-bit word) that makes the load misbehave; the same correction
+  // is applied by NVIDIA's open-source CUTLASS when it builds these maps.
+  size_t tensor_bytes = (size_t)cp * g.iw * g.ih * g.n;
+  if (tma_api().driver_version <= 13010 && tensor_bytes < 131072)
+    reinterpret_cast<uint64_t *>(tm)[1] &= ~(1ull << 21);
+}
+
+// Build the launch plan for one GEMM-shaped problem.
+//   rows       implicit-GEMM M
+//   k_inner    K bytes per tap (padded input channels, or the whole K in matrix mode)
+//   oc_pad     padded output channels (multiple of 16)
+inline void finish_plan(ConvPlan &pl, int rows, int taps, int k_inner, int oc_pad, int sm_count) {
+  ConvGemmParams &p = pl.p;
+  p.M_total = rows;
+  p.BK = pick_bk(k_inner);
+  p.c_chunks = (k_inner + p.BK - 1) / p.BK;
+  const int m_tiles = (rows + 127) / 128;
+  int bn = oc_pad < 256 ? oc_pad : 256;
+  // Prefer enough CTAs to cover the SMs before making tiles wide.
+  while (bn > 32 && (bn / 2) % 16 == 0 && m_tiles * ((oc_pad + bn - 1) / bn) < sm_count) bn /= 2;
+  p.BN = bn;
+  p.n_valid = oc_pad;
+  int cols = 32;
+  while (cols < bn) cols *= 2;
+  p.tmem_cols = cols;
+  p.idesc = make_idesc_i8(128, bn);
+  const int k_iters = taps * p.c_chunks;
+  const size_t stage_bytes = (size_t)(128 + bn) * p.BK;
+  int stages = (int)((200 * 1024) / stage_bytes);
+  if (stages > kMaxStages) stages = kMaxStages;
+  if (stages > k_iters) stages = k_iters;
+  if (stages < 1) stages = 1;
+  p.stages = stages;
+  pl.smem = kSmemHeader + 1024 + stages * stage_bytes;
+  pl.grid = dim3(m_tiles, (oc_pad + bn - 1) / bn, 1);
+}
+
+inline void launch_conv_plan(const ConvPlan &pl, cudaStream_t stream, int sm_count) {
+  if (pl.use_patch) {
+    size_t total = (size_t)pl.p.M_total * pl.patch.kp;
+    patch_expand_i8_kernel<<<grid_for(total, 256, sm_count), 256, 0, stream>>>(pl.in, pl.patch_buf,
+                                                                              pl.patch);
+  }
+  conv_gemm_i8_kernel<<<pl.grid, kConvThreads, pl.smem, stream>>>(pl.tmA, pl.tmB, pl.p);
+}
+
+inline void conv_kernel_setup_once() {
+  static bool done = [] {
+    TPUCB_CUDA(cudaFuncSetAttribute(conv_gemm_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    227 * 1024));
+    return true;
+  }();
+  (void)done;
+}
+
+} // namespace tpucb

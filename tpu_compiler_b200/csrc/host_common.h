@@ -1,0 +1,76 @@
+// Host-side plumbing shared by the interpreter translation units: error type,
+// CUDA call checking, the device tensor record and launch sizing.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <map>
+#include <memory>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+namespace tpucb {
+
+struct Error : std::runtime_error {
+  using std::runtime_error::runtime_error;
+};
+
+inline std::string strfmt(const char *fmt, ...) {
+  char buf[1024];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  return buf;
+}
+
+#define TPUCB_CUDA(call)                                                                       \
+  do {                                                                                         \
+    cudaError_t e__ = (call);                                                                  \
+    if (e__ != cudaSuccess)                                                                    \
+      throw ::tpucb::Error(::tpucb::strfmt("%s failed: %s (%s:%d)", #call,                     \
+                                           cudaGetErrorString(e__), __FILE__, __LINE__));      \
+  } while (0)
+
+#define TPUCB_CHECK(cond, ...)                                            \
+  do {                                                                    \
+    if (!(cond)) throw ::tpucb::Error(::tpucb::strfmt(__VA_ARGS__));      \
+  } while (0)
+
+inline int round_up(int v, int m) { return (v + m - 1) / m * m; }
+
+// Device tensor. Mirrors the role of TensorData (include/tpuc/Interpreter/cpukernel.h:15-78):
+// one per op result, owned by the interpreter, shared by producer and consumers.
+// Storage is NHWC with channel pitch cp; logical shape is what the module text gave.
+struct DevTensor {
+  std::string name;
+  int dtype = 2; // DType
+  std::vector<int64_t> shape;
+  int n = 1, c = 1, h = 1, w = 1, cp = 1;
+  void *dev = nullptr;
+  bool owns = true;
+  size_t elsize() const { return dtype == 0 ? 1 : (dtype == 1 ? 2 : 4); }
+  size_t pixels() const { return (size_t)n * h * w; }
+  size_t bytes() const { return pixels() * cp * elsize(); }
+  size_t numel() const { return (size_t)n * c * h * w; }
+};
+using TensorPtr = std::shared_ptr<DevTensor>;
+
+struct HostWeight {
+  std::vector<float> data;
+  std::vector<int64_t> shape;
+};
+
+// Grid for a grid-stride kernel: a multiple of the SM count, capped by the work.
+inline int grid_for(size_t work_items, int block, int sm_count) {
+  size_t blocks = (work_items + block - 1) / block;
+  size_t cap = (size_t)sm_count * 16;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  return (int)blocks;
+}
+
+} // namespace tpucb

@@ -1,0 +1,984 @@
+// Host-side interpreter: the device counterpart of MlirModuleInterpreter
+// (include/tpuc/MlirModuleInterpreter.h:32-83, lib/Dialect/TPU/Interpreter/
+// MlirModuleInterpreter.cpp) and of the CPUOpKernel hierarchy
+// (include/tpuc/Interpreter/cpukernel.h:87-159). One OpKernel object per op, built at
+// loadModule time from the op's attributes and operands; invoke() enqueues the op's
+// CUDA kernel(s) on the interpreter's stream. All activations stay resident so that
+// get_tensor / get_all_tensor work as in the reference.
+#pragma once
+#include "conv_plan.cuh"
+#include "f32_kernels.cuh"
+#include "calib_kernels.cuh"
+
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <sstream>
+
+namespace tpucb {
+
+using Attrs = std::map<std::string, std::string>;
+
+struct ParsedOp {
+  std::string type, name;
+  std::vector<std::string> in;
+  std::vector<int64_t> shape;
+  std::string dtype = "FP32";
+  Attrs attrs;
+  int geti(const char *k, int def = 0) const {
+    auto it = attrs.find(k);
+    return it == attrs.end() ? def : atoi(it->second.c_str());
+  }
+  double getf(const char *k, double def = 0) const {
+    auto it = attrs.find(k);
+    return it == attrs.end() ? def : atof(it->second.c_str());
+  }
+  std::string gets(const char *k, const char *def = "") const {
+    auto it = attrs.find(k);
+    return it == attrs.end() ? std::string(def) : it->second;
+  }
+};
+
+class Interpreter;
+
+// Device counterpart of CPUOpKernel: shape / name / op_type / datatype are public as in
+// cpukernel.h:144-149; invoke() is the one virtual the driver loop calls (cpukernel.h:101).
+class OpKernel {
+public:
+  virtual ~OpKernel() {}
+  virtual void invoke(cudaStream_t s) = 0;
+  virtual int kernel_launches() const { return 1; }
+  std::string name, op_type;
+  std::vector<int64_t> shape;
+  int datatype = DT_F32;
+  TensorPtr result;
+  double alg_ops = 0, alg_bytes = 0; // algorithmic work of one invoke (for roofline reports)
+};
+
+inline int dtype_from_string(const std::string &s) {
+  if (s == "INT8" || s == "UINT8") return DT_I8;
+  if (s == "BF16") return DT_BF16;
+  return DT_F32;
+}
+inline const char *dtype_to_string(int dt) { return dt == DT_I8 ? "INT8" : (dt == DT_BF16 ? "BF16" : "FP32"); }
+
+class Interpreter {
+public:
+  explicit Interpreter(int device) : device_(device) {
+    TPUCB_CUDA(cudaSetDevice(device));
+    cudaDeviceProp prop;
+    TPUCB_CUDA(cudaGetDeviceProperties(&prop, device));
+    TPUCB_CHECK(prop.major == 10, "this backend is written for sm_100a (B200); device %d is sm_%d%d",
+                device, prop.major, prop.minor);
+    sm_count = prop.multiProcessorCount;
+    TPUCB_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
+    TPUCB_CUDA(cudaMalloc(&d_err, sizeof(int)));
+    TPUCB_CUDA(cudaMemset(d_err, 0, sizeof(int)));
+  }
+  ~Interpreter() {
+    cudaSetDevice(device_);
+    cudaStreamSynchronize(stream);
+    if (graph_exec) cudaGraphExecDestroy(graph_exec);
+    kernels.clear();
+    for (auto &kv : tensors)
+      if (kv.second->owns && kv.second->dev) cudaFree(kv.second->dev);
+    for (void *p : allocations) cudaFree(p);
+    if (staging) cudaFree(staging);
+    cudaFree(d_err);
+    cudaStreamDestroy(stream);
+  }
+
+  void bind() { TPUCB_CUDA(cudaSetDevice(device_)); }
+
+  // ---- device memory owned by the interpreter
+  void *dalloc(size_t bytes) {
+    void *p = nullptr;
+    TPUCB_CUDA(cudaMalloc(&p, bytes ? bytes : 16));
+    allocations.push_back(p);
+    return p;
+  }
+  template <class T> T *upload(const std::vector<T> &v) {
+    T *p = (T *)dalloc(v.size() * sizeof(T));
+    if (!v.empty()) TPUCB_CUDA(cudaMemcpy(p, v.data(), v.size() * sizeof(T), cudaMemcpyHostToDevice));
+    return p;
+  }
+  float *ensure_staging(size_t bytes) {
+    if (bytes > staging_bytes) {
+      TPUCB_CUDA(cudaStreamSynchronize(stream));
+      if (staging) cudaFree(staging);
+      TPUCB_CUDA(cudaMalloc(&staging, bytes));
+      staging_bytes = bytes;
+    }
+    return (float *)staging;
+  }
+
+  TensorPtr make_tensor(const std::string &name, const std::vector<int64_t> &shape, int dtype) {
+    auto t = std::make_shared<DevTensor>();
+    t->name = name;
+    t->dtype = dtype;
+    t->shape = shape;
+    TPUCB_CHECK(shape.size() >= 1 && shape.size() <= 4, "tensor %s: rank %zu not supported", name.c_str(),
+                shape.size());
+    int64_t d[4] = {1, 1, 1, 1};
+    for (size_t i = 0; i < shape.size(); ++i) d[i] = shape[i];
+    t->n = (int)d[0];
+    t->c = (int)d[1];
+    t->h = (int)d[2];
+    t->w = (int)d[3];
+    int lanes = 16 / (int)t->elsize();
+    t->cp = round_up(t->c, lanes);
+    TPUCB_CUDA(cudaMalloc(&t->dev, t->bytes()));
+    TPUCB_CUDA(cudaMemset(t->dev, 0, t->bytes()));
+    return t;
+  }
+
+  const HostWeight &weight(const std::string &name) const {
+    auto it = weights.find(name);
+    TPUCB_CHECK(it != weights.end(), "weight '%s' was not registered", name.c_str());
+    return it->second;
+  }
+  bool has_weight(const std::string &name) const {
+    return !name.empty() && name != "-" && weights.count(name);
+  }
+  TensorPtr tensor(const std::string &name) const {
+    auto it = tensors.find(name);
+    TPUCB_CHECK(it != tensors.end(), "tensor '%s' not found", name.c_str());
+    return it->second;
+  }
+
+  void load_module(const std::string &text);
+  void set_tensor(const std::string &name, const float *data, size_t numel);
+  void get_tensor(const std::string &name, float *out, size_t numel);
+  void launch_all();
+  void launch_to(const std::string &name);
+  void sync_and_check();
+  void invalidate_graph() {
+    if (graph_exec) {
+      cudaGraphExecDestroy(graph_exec);
+      graph_exec = nullptr;
+    }
+  }
+
+  int device_;
+  int sm_count = 148;
+  cudaStream_t stream = nullptr;
+  int *d_err = nullptr;
+  bool use_graph = true;
+  cudaGraphExec_t graph_exec = nullptr;
+  std::map<std::string, HostWeight> weights;
+  std::map<std::string, TensorPtr> tensors;
+  std::vector<std::string> tensor_order;
+  std::vector<std::unique_ptr<OpKernel>> kernels;
+  std::vector<std::pair<std::string, size_t>> input_details, output_details;
+  std::vector<void *> allocations;
+  void *staging = nullptr;
+  size_t staging_bytes = 0;
+};
+
+// =========================================================================== op kernels
+
+inline std::vector<int32_t> to_i32(const std::vector<float> &v, int pad_to, bool as_u32 = false) {
+  std::vector<int32_t> o(std::max<size_t>(pad_to, v.size()), 0);
+  for (size_t i = 0; i < v.size(); ++i)
+    o[i] = as_u32 ? (int32_t)(uint32_t)v[i] : (int32_t)v[i];
+  return o;
+}
+
+// ---------------------------------------------------------------------------- Input
+// InputOpKernel (core/input.cpp:7-24): holds the tensor set_tensor writes; no device work.
+class InputOp : public OpKernel {
+public:
+  void invoke(cudaStream_t) override {}
+  int kernel_launches() const override { return 0; }
+};
+
+// ---------------------------------------------------------------------------- Quant
+// QuantOpKernel (core/quant.cpp:113-166).
+class QuantOp : public OpKernel {
+public:
+  QuantOp(Interpreter &I, const ParsedOp &op, TensorPtr in, TensorPtr out, bool prev_is_input)
+      : I_(I), in_(in), out_(out) {
+    std::string from = op.gets("from", "NONE"), to = op.gets("to", "NONE");
+    scale_ = (float)op.getf("scale", 1.0);
+    TPUCB_CHECK(op.geti("zero_point", 0) == 0, "quant %s: zero_point != 0 is not supported",
+                op.name.c_str());
+    if (from == "NONE" && to == "INT8") kind_ = prev_is_input ? 0 : 1;
+    else if ((from == "INT8" || from == "UINT8") && to == "NONE") kind_ = 2;
+    else if ((from == "INT8" || from == "UINT8") && to == "BF16") kind_ = 3;
+    else if (from == "BF16" && to == "INT8") kind_ = 4;
+    else if (from == "NONE" && to == "BF16") kind_ = 5;
+    else if (from == "BF16" && to == "NONE") kind_ = 6;
+    else throw Error(strfmt("quant %s: %s -> %s is not supported", op.name.c_str(), from.c_str(), to.c_str()));
+    alg_bytes = (double)in->numel() * in->elsize() + (double)out->numel() * out->elsize();
+  }
+  void invoke(cudaStream_t s) override {
+    size_t total = out_->pixels() * out_->cp;
+    quant_kernel<<<grid_for(total, 256, I_.sm_count), 256, 0, s>>>(
+        in_->dev, out_->dev, out_->pixels(), out_->c, in_->cp, out_->cp, in_->dtype, out_->dtype,
+        kind_ == 6 ? 5 : kind_, scale_);
+  }
+
+private:
+  Interpreter &I_;
+  TensorPtr in_, out_;
+  int kind_ = 0;
+  float scale_ = 1;
+};
+
+// --------------------------------------------------------------------------- Conv2D
+// Conv2DOpKernel (core/conv.cpp:11-104). INT8: dense -> tcgen05 implicit GEMM; depthwise ->
+// the HBM-bound kernel. FP32: direct fp32 kernel (calibration forward).
+class Conv2DOp : public OpKernel {
+public:
+  Conv2DOp(Interpreter &I, const ParsedOp &op, TensorPtr in, TensorPtr out) : I_(I), in_(in), out_(out) {
+    ConvGeom g;
+    g.n = in->n; g.ic = in->c; g.ih = in->h; g.iw = in->w;
+    g.oc = out->c; g.oh = out->h; g.ow = out->w;
+    g.g = op.geti("g", 1);
+    g.kh = op.geti("kh", 1); g.kw = op.geti("kw", 1);
+    g.sh = op.geti("sh", 1); g.sw = op.geti("sw", 1);
+    g.pt = op.geti("pt", 0); g.pb = op.geti("pb", 0); g.pl = op.geti("pl", 0); g.pr = op.geti("pr", 0);
+    g.dh = op.geti("dh", 1); g.dw = op.geti("dw", 1);
+    g.ins_h = op.geti("ins_h", 0); g.ins_w = op.geti("ins_w", 0);
+    g_ = g;
+    do_relu_ = op.geti("do_relu", 0);
+    TPUCB_CHECK(op.in.size() >= 3, "conv %s: expects input, filter, bias[, scale, zeropoint, rshift, multiplier]",
+                op.name.c_str());
+    const HostWeight &filt = I.weight(op.in[1]);
+    const int icg = g.ic / g.g, ocg = g.oc / g.g;
+    TPUCB_CHECK((size_t)g.oc * icg * g.kh * g.kw == filt.data.size(), "conv %s: filter has %zu values, expected %zu",
+                op.name.c_str(), filt.data.size(), (size_t)g.oc * icg * g.kh * g.kw);
+    const bool with_bias = I.has_weight(op.in[2]);
+    std::vector<float> bias(g.oc, 0.0f);
+    if (with_bias) bias = I.weight(op.in[2]).data;
+    alg_ops = 2.0 * g.n * g.oc * g.oh * g.ow * icg * g.kh * g.kw;
+    if (out->dtype == DT_F32 || out->dtype == DT_BF16) {
+      TPUCB_CHECK(in->dtype == DT_F32 && out->dtype == DT_F32, "conv %s: BF16 convolution is not implemented",
+                  op.name.c_str());
+      f32_ = true;
+      f32_w_ = I.upload(pack_conv_weights_f32(filt.data.data(), g.oc, icg, g.kh, g.kw, g.g));
+      f32_b_ = I.upload(bias);
+      alg_bytes = 4.0 * ((double)in->numel() + out->numel() + filt.data.size() + g.oc);
+      return;
+    }
+    TPUCB_CHECK(in->dtype == DT_I8, "conv %s: INT8 convolution needs an INT8 input", op.name.c_str());
+    TPUCB_CHECK(op.in.size() >= 7 && I.has_weight(op.in[5]) && I.has_weight(op.in[6]),
+                "conv %s: INT8 convolution needs rshift and multiplier operands (RSHIFT_AND_M_I32)", op.name.c_str());
+    const int oc_pad = out->cp;
+    d_bias_ = I.upload(to_i32(bias, oc_pad));
+    d_mult_ = I.upload(to_i32(I.weight(op.in[6]).data, oc_pad, true));
+    d_rsh_ = I.upload(to_i32(I.weight(op.in[5]).data, oc_pad, true));
+    alg_bytes = (double)in->numel() + out->numel() + filt.data.size() + 12.0 * g.oc;
+    act_ = do_relu_ ? 1 : 0;
+
+    if (g.g == g.ic && g.g == g.oc && g.g > 1 && g.ins_h == 0 && g.ins_w == 0) {
+      // depthwise
+      dw_ = true;
+      std::vector<int8_t> w((size_t)g.kh * g.kw * in->cp, 0);
+      for (int c = 0; c < g.ic; ++c)
+        for (int t = 0; t < g.kh * g.kw; ++t) w[(size_t)t * in->cp + c] = (int8_t)(int)filt.data[(size_t)c * g.kh * g.kw + t];
+      DwArgs a;
+      a.n = g.n; a.c = g.ic; a.cp = in->cp; a.ih = g.ih; a.iw = g.iw; a.oh = g.oh; a.ow = g.ow;
+      a.kh = g.kh; a.kw = g.kw; a.sh = g.sh; a.sw = g.sw; a.pt = g.pt; a.pl = g.pl; a.dh = g.dh; a.dw = g.dw;
+      a.do_relu = do_relu_;
+      a.wgt = I.upload(w);
+      a.bias = d_bias_; a.mult = d_mult_; a.rshift = d_rsh_;
+      dwargs_ = a;
+      return;
+    }
+
+    conv_kernel_setup_once();
+    const bool one_by_one = g.kh == 1 && g.kw == 1 && g.sh == 1 && g.sw == 1 && g.pt == 0 && g.pl == 0 &&
+                            g.oh == g.ih && g.ow == g.iw;
+    const bool small_c = g.ic < 16;
+    const bool need_patch = g.g > 1 || g.ins_h || g.ins_w || (small_c && !one_by_one) ||
+                            g.pl > 127 || g.pt > 127 || (g.kw - 1) * g.dw > 255 || (g.kh - 1) * g.dh > 255;
+    const int groups = g.g;
+    for (int grp = 0; grp < groups; ++grp) {
+      ConvPlan pl;
+      std::memset(&pl.p, 0, sizeof(pl.p));
+      pl.in = (const int8_t *)in->dev;
+      ConvGemmParams &p = pl.p;
+      p.OH = g.oh; p.OW = g.ow; p.sh = g.sh; p.sw = g.sw; p.pt = g.pt; p.pl = g.pl; p.dh = g.dh; p.dw = g.dw;
+      p.act = act_;
+      p.bias = d_bias_ + grp * ocg; p.mult = d_mult_ + grp * ocg; p.rshift = d_rsh_ + grp * ocg;
+      p.out = (int8_t *)out->dev;
+      p.ldc = out->cp;
+      p.c_off = grp * ocg;
+      p.err = I.d_err;
+      const int rows = g.n * g.oh * g.ow;
+      const float *wsrc = filt.data.data() + (size_t)grp * ocg * icg * g.kh * g.kw;
+      int ocg_pad = groups == 1 ? oc_pad : ocg;
+      TPUCB_CHECK(groups == 1 || ocg % 16 == 0, "conv %s: grouped convolution needs oc/g to be a multiple of 16",
+                  op.name.c_str());
+      if (need_patch) {
+        pl.use_patch = true;
+        PatchArgs &a = pl.patch;
+        a.n = g.n; a.c = g.ic; a.cp = in->cp; a.ih = g.ih; a.iw = g.iw; a.oh = g.oh; a.ow = g.ow;
+        a.kh = g.kh; a.kw = g.kw; a.sh = g.sh; a.sw = g.sw; a.pt = g.pt; a.pl = g.pl; a.dh = g.dh; a.dw = g.dw;
+        a.ins_h = g.ins_h; a.ins_w = g.ins_w;
+        a.c_first = grp * icg; a.c_count = icg;
+        a.kp = round_up(g.kh * g.kw * icg, 16);
+        pl.patch_bytes = (size_t)rows * a.kp;
+        pl.patch_buf = (int8_t *)I.dalloc(pl.patch_bytes);
+        auto w = pack_conv_weights(wsrc, ocg, icg, g.kh, g.kw, ocg_pad, 0, true, a.kp);
+        const int8_t *d_w = I.upload(w);
+        p.kh = p.kw = 1;
+        p.a_im2col = 0;
+        finish_plan(pl, rows, 1, a.kp, ocg_pad, I.sm_count);
+        encode_matrix_map(&pl.tmA, pl.patch_buf, rows, a.kp, a.kp, p.BK);
+        encode_weight_map(&pl.tmB, d_w, ocg_pad, 1, a.kp, p.BK, p.BN);
+      } else if (one_by_one) {
+        auto w = pack_conv_weights(wsrc, ocg, icg, 1, 1, ocg_pad, in->cp, false, 0);
+        const int8_t *d_w = I.upload(w);
+        p.kh = p.kw = 1;
+        p.a_im2col = 0;
+        finish_plan(pl, rows, 1, in->cp, ocg_pad, I.sm_count);
+        encode_matrix_map(&pl.tmA, (const int8_t *)in->dev, rows, in->cp, in->cp, p.BK);
+        encode_weight_map(&pl.tmB, d_w, ocg_pad, 1, in->cp, p.BK, p.BN);
+      } else {
+        auto w = pack_conv_weights(wsrc, ocg, icg, g.kh, g.kw, ocg_pad, in->cp, false, 0);
+        const int8_t *d_w = I.upload(w);
+        p.kh = g.kh; p.kw = g.kw;
+        p.a_im2col = 1;
+        finish_plan(pl, rows, g.kh * g.kw, in->cp, ocg_pad, I.sm_count);
+        encode_im2col_map(&pl.tmA, (const int8_t *)in->dev, g, in->cp, p.BK);
+        encode_weight_map(&pl.tmB, d_w, ocg_pad, g.kh * g.kw, in->cp, p.BK, p.BN);
+      }
+      plans_.push_back(pl);
+    }
+  }
+  void set_leaky(int mp, int rp, int mn, int rn) {
+    for (auto &pl : plans_) {
+      pl.p.act = 2;
+      pl.p.leaky_mp = mp; pl.p.leaky_rp = rp; pl.p.leaky_mn = mn; pl.p.leaky_rn = rn;
+    }
+  }
+  void invoke(cudaStream_t s) override {
+    if (f32_) {
+      launch_conv2d_f32((const float *)in_->dev, f32_w_, f32_b_, (float *)out_->dev, g_, in_->cp, out_->cp, do_relu_,
+                        s, I_.sm_count);
+    } else if (dw_) {
+      size_t total = out_->pixels() * (out_->cp / 16);
+      dwconv_i8_kernel<<<grid_for(total, 128, I_.sm_count), 128, 0, s>>>((const int8_t *)in_->dev,
+                                                                          (int8_t *)out_->dev, dwargs_);
+    } else {
+      for (auto &pl : plans_) launch_conv_plan(pl, s, I_.sm_count);
+    }
+  }
+  int kernel_launches() const override {
+    if (f32_ || dw_) return 1;
+    int k = 0;
+    for (auto &pl : plans_) k += pl.use_patch ? 2 : 1;
+    return k;
+  }
+  bool is_tensor_core() const { return !f32_ && !dw_; }
+  std::vector<ConvPlan> plans_;
+
+private:
+  Interpreter &I_;
+  TensorPtr in_, out_;
+  ConvGeom g_;
+  int do_relu_ = 0, act_ = 0;
+  bool dw_ = false, f32_ = false;
+  DwArgs dwargs_;
+  const int32_t *d_bias_ = nullptr, *d_mult_ = nullptr, *d_rsh_ = nullptr;
+  const float *f32_w_ = nullptr, *f32_b_ = nullptr;
+};
+
+// ------------------------------------------------------------------- FullyConnected
+// FullyConnectedOpKernel (core/fullyconnected.cpp:7-91), batch == 1, no transposes.
+class FullyConnectedOp : public OpKernel {
+public:
+  FullyConnectedOp(Interpreter &I, const ParsedOp &op, TensorPtr in, TensorPtr out) : I_(I), in_(in), out_(out) {
+    do_relu_ = op.geti("do_relu", 0);
+    m_ = in->n;
+    const int hw = in->h * in->w;
+    k_ = in->c * hw;
+    n_ = out->c;
+    TPUCB_CHECK(out->n == m_ && out->h * out->w == 1, "fc %s: output must be [m, n]", op.name.c_str());
+    const HostWeight &filt = I.weight(op.in[1]);
+    TPUCB_CHECK(filt.data.size() == (size_t)n_ * k_, "fc %s: filter has %zu values, expected n*k = %zu",
+                op.name.c_str(), filt.data.size(), (size_t)n_ * k_);
+    std::vector<float> bias(n_, 0.0f);
+    if (op.in.size() > 2 && I.has_weight(op.in[2])) bias = I.weight(op.in[2]).data;
+    alg_ops = 2.0 * m_ * k_ * n_;
+    if (out->dtype != DT_I8) {
+      TPUCB_CHECK(in->dtype == DT_F32 && out->dtype == DT_F32, "fc %s: BF16 is not implemented", op.name.c_str());
+      f32_ = true;
+      // weights in device K order: (y, x, c) with pitch in->cp
+      kdev_ = hw * in->cp;
+      std::vector<float> w((size_t)n_ * kdev_, 0.0f);
+      for (int j = 0; j < n_; ++j)
+        for (int c = 0; c < in->c; ++c)
+          for (int p = 0; p < hw; ++p) w[(size_t)j * kdev_ + (size_t)p * in->cp + c] = filt.data[(size_t)j * k_ + (size_t)c * hw + p];
+      f32_w_ = I.upload(w);
+      f32_b_ = I.upload(bias);
+      alg_bytes = 4.0 * ((double)m_ * k_ + (double)n_ * k_ + (double)m_ * n_ + n_);
+      return;
+    }
+    TPUCB_CHECK(in->dtype == DT_I8, "fc %s: INT8 needs an INT8 input", op.name.c_str());
+    TPUCB_CHECK(op.in.size() >= 7 && I.has_weight(op.in[5]) && I.has_weight(op.in[6]),
+                "fc %s: INT8 needs rshift and multiplier operands", op.name.c_str());
+    conv_kernel_setup_once();
+    const int n_pad = out->cp;
+    kdev_ = hw * in->cp;
+    std::vector<int8_t> w((size_t)n_pad * kdev_, 0);
+    for (int j = 0; j < n_; ++j)
+      for (int c = 0; c < in->c; ++c)
+        for (int p = 0; p < hw; ++p)
+          w[(size_t)j * kdev_ + (size_t)p * in->cp + c] = (int8_t)(int)filt.data[(size_t)j * k_ + (size_t)c * hw + p];
+    const int8_t *d_w = I.upload(w);
+    // one (rshift, multiplier) pair per batch slice (fullyconnected.cpp:78-88) -> broadcast per column
+    std::vector<float> rs(n_, I.weight(op.in[5]).data.at(0)), mu(n_, I.weight(op.in[6]).data.at(0));
+    ConvPlan pl;
+    std::memset(&pl.p, 0, sizeof(pl.p));
+    ConvGemmParams &p = pl.p;
+    p.bias = I.upload(to_i32(bias, n_pad));
+    p.mult = I.upload(to_i32(mu, n_pad, true));
+    p.rshift = I.upload(to_i32(rs, n_pad, true));
+    p.out = (int8_t *)out->dev;
+    p.ldc = out->cp;
+    p.c_off = 0;
+    p.err = I.d_err;
+    p.OH = p.OW = 1; p.sh = p.sw = p.dh = p.dw = 1; p.kh = p.kw = 1;
+    // The reference applies ReLU to the float before the QDM requant; with a positive
+    // multiplier the two orders give the same int8 result.
+    p.act = do_relu_ ? 1 : 0;
+    p.a_im2col = 0;
+    finish_plan(pl, m_, 1, kdev_, n_pad, I.sm_count);
+    encode_matrix_map(&pl.tmA, (const int8_t *)in->dev, m_, kdev_, kdev_, p.BK);
+    encode_weight_map(&pl.tmB, d_w, n_pad, 1, kdev_, p.BK, p.BN);
+    plan_ = pl;
+    alg_bytes = (double)m_ * k_ + (double)n_ * k_ + (double)m_ * n_ + 4.0 * n_ + 8;
+  }
+  void invoke(cudaStream_t s) override {
+    if (f32_) launch_fc_f32((const float *)in_->dev, f32_w_, f32_b_, (float *)out_->dev, m_, kdev_, n_, out_->cp, do_relu_, s);
+    else launch_conv_plan(plan_, s, I_.sm_count);
+  }
+  ConvPlan plan_;
+
+private:
+  Interpreter &I_;
+  TensorPtr in_, out_;
+  int m_ = 1, k_ = 1, n_ = 1, kdev_ = 1, do_relu_ = 0;
+  bool f32_ = false;
+  const float *f32_w_ = nullptr, *f32_b_ = nullptr;
+};
+
+// -------------------------------------------------------------------------- Pooling
+// PoolingOpKernel (core/pooling.cpp:33-160).
+class PoolOp : public OpKernel {
+public:
+  PoolOp(Interpreter &I, const ParsedOp &op, TensorPtr in, TensorPtr out, bool is_avg) : I_(I), in_(in), out_(out) {
+    PoolArgs a;
+    a.n = in->n; a.c = in->c; a.cp = in->cp; a.ih = in->h; a.iw = in->w; a.oh = out->h; a.ow = out->w;
+    a.kh = op.geti("kh", 1); a.kw = op.geti("kw", 1); a.sh = op.geti("sh", 1); a.sw = op.geti("sw", 1);
+    a.pt = op.geti("pt", 0); a.pl = op.geti("pl", 0);
+    a.method = is_avg ? 1 : 0;
+    a.mult = 0; a.rshift = 0;
+    count_include_pad_ = op.geti("count_include_pad", 0);
+    TPUCB_CHECK(!op.geti("do_relu", 0), "pool %s: do_relu is not supported (the reference asserts it off)", op.name.c_str());
+    if (in->dtype == DT_I8 && is_avg) {
+      TPUCB_CHECK(op.in.size() >= 5 && I.has_weight(op.in[3]) && I.has_weight(op.in[4]),
+                  "pool_avg %s: INT8 needs rshift and multiplier operands", op.name.c_str());
+      a.rshift = (int)(uint32_t)I.weight(op.in[3]).data.at(0);
+      a.mult = (int)(uint32_t)I.weight(op.in[4]).data.at(0);
+    }
+    TPUCB_CHECK(in->dtype != DT_BF16, "pool %s: BF16 pooling is not implemented", op.name.c_str());
+    a_ = a;
+    alg_bytes = ((double)in->numel() + out->numel()) * in->elsize();
+  }
+  void invoke(cudaStream_t s) override {
+    if (in_->dtype == DT_I8) {
+      size_t total = out_->pixels() * (out_->cp / 16);
+      pool_i8_kernel<<<grid_for(total, 128, I_.sm_count), 128, 0, s>>>((const int8_t *)in_->dev, (int8_t *)out_->dev, a_);
+    } else {
+      launch_pool_f32((const float *)in_->dev, (float *)out_->dev, a_, count_include_pad_, s, I_.sm_count);
+    }
+  }
+
+private:
+  Interpreter &I_;
+  TensorPtr in_, out_;
+  PoolArgs a_;
+  int count_include_pad_ = 0;
+};
+
+// -------------------------------------------------------------------------- Eltwise
+// EltwiseAddOpKernel / EltwiseMulOpKernel (core/eltwise.cpp:7-107, 318-357).
+class EltwiseOp : public OpKernel {
+public:
+  EltwiseOp(Interpreter &I, const ParsedOp &op, std::vector<TensorPtr> ins, TensorPtr out, bool is_mul)
+      : I_(I), ins_(ins), out_(out), is_mul_(is_mul) {
+    const int nin = (int)ins.size();
+    TPUCB_CHECK(nin >= 1 && nin <= 4, "eltwise %s: %d inputs not supported (max 4)", op.name.c_str(), nin);
+    for (auto &t : ins)
+      TPUCB_CHECK(t->bytes() == out->bytes() && t->dtype == out->dtype, "eltwise %s: operand %s differs in shape or type",
+                  op.name.c_str(), t->name.c_str());
+    do_relu_ = op.geti("do_relu", 0);
+    alg_bytes = (double)(nin + 1) * out->numel() * out->elsize();
+    if (out->dtype == DT_I8) {
+      // operands: inputs..., quant_scale, quant_zeropoint, quant_rshift, quant_multiplier
+      TPUCB_CHECK((int)op.in.size() >= nin + 4 && I.has_weight(op.in[nin + 2]) && I.has_weight(op.in[nin + 3]),
+                  "eltwise %s: INT8 needs rshift and multiplier operands", op.name.c_str());
+      const auto &rs = I.weight(op.in[nin + 2]).data;
+      const auto &mu = I.weight(op.in[nin + 3]).data;
+      a_.nin = nin;
+      a_.do_relu = do_relu_;
+      a_.rshift = (int)(uint32_t)rs.at(0);
+      a_.qdm_mult = 0;
+      for (int i = 0; i < nin; ++i) a_.in[i] = (const int8_t *)ins[i]->dev;
+      if (is_mul) a_.qdm_mult = (int)(uint32_t)mu.at(0);
+      else
+        for (int i = 0; i < nin; ++i) a_.mult[i] = (int)(int8_t)mu.at(i);
+    } else {
+      TPUCB_CHECK(out->dtype == DT_F32 && !is_mul, "eltwise %s: only fp32 add is implemented outside INT8", op.name.c_str());
+      f_.nin = nin;
+      f_.do_relu = do_relu_;
+      for (int i = 0; i < nin; ++i) {
+        f_.in[i] = (const float *)ins[i]->dev;
+        f_.coeff[i] = 1.0f;
+      }
+      std::string co = op.gets("coeff", "");
+      if (!co.empty()) {
+        std::stringstream ss(co);
+        std::string tok;
+        int i = 0;
+        while (std::getline(ss, tok, ',') && i < nin) f_.coeff[i++] = (float)atof(tok.c_str());
+      }
+    }
+  }
+  void invoke(cudaStream_t s) override {
+    if (out_->dtype == DT_I8) {
+      size_t nvec = out_->bytes() / 16;
+      if (is_mul_) eltwise_mul_i8_kernel<<<grid_for(nvec, 256, I_.sm_count), 256, 0, s>>>(a_, (int8_t *)out_->dev, nvec);
+      else eltwise_add_i8_kernel<<<grid_for(nvec, 256, I_.sm_count), 256, 0, s>>>(a_, (int8_t *)out_->dev, nvec);
+    } else {
+      size_t n = out_->bytes() / 4;
+      eltwise_add_f32_kernel<<<grid_for(n, 256, I_.sm_count), 256, 0, s>>>(f_, (float *)out_->dev, n);
+    }
+  }
+
+private:
+  Interpreter &I_;
+  std::vector<TensorPtr> ins_;
+  TensorPtr out_;
+  bool is_mul_;
+  int do_relu_ = 0;
+  EltwiseArgs a_;
+  EltwiseF32Args f_;
+};
+
+// --------------------------------------------------------------------------- Concat
+// ConcatOpKernel (core/concat.cpp:7-90), channel axis, INT8 with per-input rescale.
+class ConcatOp : public OpKernel {
+public:
+  ConcatOp(Interpreter &I, const ParsedOp &op, std::vector<TensorPtr> ins, TensorPtr out) : I_(I), ins_(ins), out_(out) {
+    TPUCB_CHECK(op.geti("axis", 1) == 1, "concat %s: only the channel axis is supported", op.name.c_str());
+    TPUCB_CHECK(out->dtype == DT_I8, "concat %s: only INT8 is implemented", op.name.c_str());
+    const int nin = (int)ins.size();
+    do_relu_ = op.geti("do_relu", 0);
+    mult_.assign(nin, 1);
+    rsh_.assign(nin, 0);
+    if ((int)op.in.size() >= nin + 4 && I.has_weight(op.in[nin + 2]) && I.has_weight(op.in[nin + 3])) {
+      need_quant_ = true;
+      const auto &rs = I.weight(op.in[nin + 2]).data;
+      const auto &mu = I.weight(op.in[nin + 3]).data;
+      for (int i = 0; i < nin; ++i) {
+        rsh_[i] = (int)(uint32_t)rs.at(i);
+        mult_[i] = (int)(uint32_t)mu.at(i);
+      }
+    }
+    int c = 0;
+    for (auto &t : ins) c += t->c;
+    TPUCB_CHECK(c == out->c, "concat %s: channel counts do not add up", op.name.c_str());
+    alg_bytes = 2.0 * out->numel();
+  }
+  void invoke(cudaStream_t s) override {
+    int off = 0;
+    for (size_t i = 0; i < ins_.size(); ++i) {
+      auto &t = ins_[i];
+      size_t total = t->pixels() * t->c;
+      int requant = need_quant_ && !(mult_[i] == 1 && rsh_[i] == 0);
+      concat_slice_i8_kernel<<<grid_for(total, 256, I_.sm_count), 256, 0, s>>>(
+          (const int8_t *)t->dev, (int8_t *)out_->dev, t->pixels(), t->c, t->cp, out_->cp, off, mult_[i], rsh_[i],
+          requant, do_relu_);
+      off += t->c;
+    }
+  }
+  int kernel_launches() const override { return (int)ins_.size(); }
+
+private:
+  Interpreter &I_;
+  std::vector<TensorPtr> ins_;
+  TensorPtr out_;
+  std::vector<int> mult_, rsh_;
+  bool need_quant_ = false;
+  int do_relu_ = 0;
+};
+
+// ------------------------------------------------------------ Upsample / PixelShuffle
+// UpsampleOpKernel (core/upsample.cpp:20-41), DepthToSpaceOpKernel (core/depthtospace.cpp:50-80).
+class MoveOp : public OpKernel {
+public:
+  MoveOp(Interpreter &I, const ParsedOp &op, TensorPtr in, TensorPtr out, int mode) : I_(I), in_(in), out_(out) {
+    MoveArgs a;
+    a.n = in->n; a.ic = in->c; a.ih = in->h; a.iw = in->w; a.icp = in->cp;
+    a.oc = out->c; a.oh = out->h; a.ow = out->w; a.ocp = out->cp;
+    a.es = (int)in->elsize();
+    a.scale_h = op.geti("scale_h", 1); a.scale_w = op.geti("scale_w", 1);
+    a.r = op.geti("upscale_factor", 1);
+    a.mode = mode == 0 ? 0 : (op.gets("mode", "CRD") == "DCR" ? 2 : 1);
+    TPUCB_CHECK(in->dtype == out->dtype, "%s: input and output types differ", op.name.c_str());
+    a_ = a;
+    alg_bytes = ((double)in->numel() + out->numel()) * in->elsize();
+  }
+  void invoke(cudaStream_t s) override {
+    size_t total = out_->pixels() * out_->cp;
+    move_kernel<<<grid_for(total, 256, I_.sm_count), 256, 0, s>>>((const uint8_t *)in_->dev, (uint8_t *)out_->dev, a_);
+  }
+
+private:
+  Interpreter &I_;
+  TensorPtr in_, out_;
+  MoveArgs a_;
+};
+
+// ------------------------------------------------------------------- ReLU / LeakyReLU
+// ReluOpKernel, LeakyReluOpKernel (core/activation.cpp:104-180).
+class LeakyReluOp : public OpKernel {
+public:
+  LeakyReluOp(Interpreter &I, const ParsedOp &op, TensorPtr in, TensorPtr out, bool plain) : I_(I), in_(in), out_(out), plain_(plain) {
+    TPUCB_CHECK(in->dtype == DT_I8 && out->dtype == DT_I8, "%s: only INT8 is implemented", op.name.c_str());
+    if (!plain) {
+      // operands 5..8: rshift_pos, multiplier_pos, rshift_neg, multiplier_neg (activation.cpp:113-124)
+      TPUCB_CHECK(op.in.size() >= 9, "leaky_relu %s: INT8 needs 4 rescale operands", op.name.c_str());
+      rp = (int)(uint32_t)I.weight(op.in[5]).data.at(0);
+      mp = (int)I.weight(op.in[6]).data.at(0);
+      rn = (int)(uint32_t)I.weight(op.in[7]).data.at(0);
+      mn = (int)I.weight(op.in[8]).data.at(0);
+    }
+    alg_bytes = 2.0 * out->numel();
+  }
+  void invoke(cudaStream_t s) override {
+    size_t nvec = out_->bytes() / 16;
+    leaky_relu_i8_kernel<<<grid_for(nvec, 256, I_.sm_count), 256, 0, s>>>((const int8_t *)in_->dev, (int8_t *)out_->dev,
+                                                                          nvec, mp, rp, mn, rn, plain_ ? 1 : 0);
+  }
+  int mp = 0, rp = 0, mn = 0, rn = 0;
+
+private:
+  Interpreter &I_;
+  TensorPtr in_, out_;
+  bool plain_;
+};
+
+// ---------------------------------------------------------------------- LUT activations
+// SigmoidOpKernel / MishOpKernel / ExpOpKernel (core/activation.cpp:47-102, 251-268): INT8 mode is a
+// 256-entry table gather, BF16 mode the slope-interpolated table of bf16_lut_slope.
+// ReciprocalOpKernel BF16: bf16_lut_mantissa with the pow(-1) tables.
+class LutOp : public OpKernel {
+public:
+  LutOp(Interpreter &I, const ParsedOp &op, TensorPtr in, TensorPtr out) : I_(I), in_(in), out_(out) {
+    TPUCB_CHECK(in->dtype == out->dtype, "%s: input and output types differ", op.name.c_str());
+    TPUCB_CHECK(op.in.size() >= 3, "%s: expects input and two table operands", op.name.c_str());
+    const auto &t0 = I.weight(op.in[1]).data;
+    const auto &t1 = I.weight(op.in[2]).data;
+    TPUCB_CHECK(t0.size() >= 256, "%s: table operand needs at least 256 entries", op.name.c_str());
+    if (in->dtype == DT_I8) {
+      std::vector<int8_t> t(256);
+      for (int i = 0; i < 256; ++i) t[i] = (int8_t)(int)t0[i];
+      tab_i8_ = I.upload(t);
+      alg_bytes = 2.0 * out->numel();
+    } else {
+      TPUCB_CHECK(in->dtype == DT_BF16, "%s: lookup tables run in INT8 or BF16", op.name.c_str());
+      TPUCB_CHECK(t1.size() >= 256, "%s: second table needs at least 256 entries", op.name.c_str());
+      t0_ = I.upload(std::vector<float>(t0.begin(), t0.begin() + 256));
+      t1_ = I.upload(std::vector<float>(t1.begin(), t1.begin() + 256));
+      mantissa_ = op.type == "reciprocal";
+      double range = op.type == "sigmoid" ? 12 : (op.type == "mish" ? 8 : 15); // lut_func.hpp:8-15
+      scale_ = bf16_round((float)(256.0 / (2 * range)));
+      alg_bytes = 4.0 * out->numel();
+    }
+  }
+  void invoke(cudaStream_t s) override {
+    if (in_->dtype == DT_I8) {
+      size_t nvec = out_->bytes() / 16;
+      lut_i8_kernel<<<grid_for(nvec, 256, I_.sm_count), 256, 0, s>>>((const int8_t *)in_->dev, (int8_t *)out_->dev, nvec, tab_i8_);
+    } else if (mantissa_) {
+      size_t n = out_->bytes() / 2;
+      lut_bf16_mantissa_kernel<<<grid_for(n, 256, I_.sm_count), 256, 0, s>>>((const uint16_t *)in_->dev, (uint16_t *)out_->dev, n, t0_, t1_);
+    } else {
+      size_t n = out_->bytes() / 2;
+      lut_bf16_slope_kernel<<<grid_for(n / 8, 256, I_.sm_count), 256, 0, s>>>((const uint16_t *)in_->dev, (uint16_t *)out_->dev, n, t0_, t1_, scale_);
+    }
+  }
+
+private:
+  Interpreter &I_;
+  TensorPtr in_, out_;
+  const int8_t *tab_i8_ = nullptr;
+  const float *t0_ = nullptr, *t1_ = nullptr;
+  bool mantissa_ = false;
+  float scale_ = 1;
+};
+
+// ------------------------------------------------------------ fp32 Scale / Softmax
+// ScaleOpKernel (core/scale.cpp:15-37), SoftmaxOpKernel::invoke_fp32 (core/softmax.cpp:49-86).
+class ScaleOp : public OpKernel {
+public:
+  ScaleOp(Interpreter &I, const ParsedOp &op, TensorPtr in, TensorPtr out) : I_(I), in_(in), out_(out) {
+    TPUCB_CHECK(in->dtype == DT_F32 && out->dtype == DT_F32, "scale %s: fp32 only (as the reference)", op.name.c_str());
+    std::vector<float> sc = I.weight(op.in[1]).data, bi(in->c, 0.0f);
+    if (op.in.size() > 2 && I.has_weight(op.in[2])) bi = I.weight(op.in[2]).data;
+    sc.resize(in->cp, 0.0f);
+    bi.resize(in->cp, 0.0f);
+    d_s_ = I.upload(sc);
+    d_b_ = I.upload(bi);
+    alg_bytes = 8.0 * out->numel();
+  }
+  void invoke(cudaStream_t s) override {
+    size_t n = out_->bytes() / 4;
+    scale_f32_kernel<<<grid_for(n, 256, I_.sm_count), 256, 0, s>>>((const float *)in_->dev, d_s_, d_b_, (float *)out_->dev, n, out_->cp);
+  }
+
+private:
+  Interpreter &I_;
+  TensorPtr in_, out_;
+  const float *d_s_ = nullptr, *d_b_ = nullptr;
+};
+
+class SoftmaxOp : public OpKernel {
+public:
+  SoftmaxOp(Interpreter &I, const ParsedOp &op, TensorPtr in, TensorPtr out) : I_(I), in_(in), out_(out) {
+    TPUCB_CHECK(in->dtype == DT_F32 && out->dtype == DT_F32, "softmax %s: fp32 only", op.name.c_str());
+    TPUCB_CHECK(op.geti("axis", 1) == 1, "softmax %s: channel axis only", op.name.c_str());
+    alg_bytes = 8.0 * out->numel();
+  }
+  void invoke(cudaStream_t s) override {
+    softmax_f32_kernel<<<(unsigned)out_->pixels(), 128, 0, s>>>((const float *)in_->dev, (float *)out_->dev, out_->c, out_->cp);
+  }
+
+private:
+  Interpreter &I_;
+  TensorPtr in_, out_;
+};
+
+// ====================================================================== Interpreter bodies
+
+inline std::vector<std::string> split(const std::string &s, char sep) {
+  std::vector<std::string> out;
+  std::stringstream ss(s);
+  std::string tok;
+  while (std::getline(ss, tok, sep)) out.push_back(tok);
+  return out;
+}
+
+inline ParsedOp parse_line(const std::string &line) {
+  ParsedOp op;
+  std::stringstream ss(line);
+  std::string tok;
+  ss >> op.type;
+  while (ss >> tok) {
+    auto eq = tok.find('=');
+    TPUCB_CHECK(eq != std::string::npos, "module text: token '%s' is not key=value", tok.c_str());
+    std::string k = tok.substr(0, eq), v = tok.substr(eq + 1);
+    if (k == "name") op.name = v;
+    else if (k == "in") op.in = split(v, ',');
+    else if (k == "shape") {
+      for (auto &d : split(v, ',')) op.shape.push_back(atoll(d.c_str()));
+    } else if (k == "dtype") op.dtype = v;
+    else op.attrs[k] = v;
+  }
+  TPUCB_CHECK(!op.name.empty(), "module text: op '%s' has no name", op.type.c_str());
+  return op;
+}
+
+// loadModule / updateKernelList (MlirModuleInterpreter.cpp:73-83, 118-350).
+inline void Interpreter::load_module(const std::string &text) {
+  bind();
+  invalidate_graph();
+  kernels.clear();
+  for (auto &kv : tensors)
+    if (kv.second->owns && kv.second->dev) cudaFree(kv.second->dev);
+  tensors.clear();
+  tensor_order.clear();
+  input_details.clear();
+  output_details.clear();
+  std::map<std::string, std::string> producer_type;
+  std::map<std::string, int> uses;
+  std::stringstream ss(text);
+  std::string line;
+  while (std::getline(ss, line)) {
+    size_t b = line.find_first_not_of(" \t\r");
+    if (b == std::string::npos || line[b] == '#') continue;
+    ParsedOp op = parse_line(line.substr(b));
+    TPUCB_CHECK(!tensors.count(op.name), "module text: duplicate result name '%s'", op.name.c_str());
+    const int dt = dtype_from_string(op.dtype);
+    auto opd = [&](size_t i) -> TensorPtr {
+      TPUCB_CHECK(i < op.in.size(), "%s %s: operand %zu missing", op.type.c_str(), op.name.c_str(), i);
+      return tensor(op.in[i]);
+    };
+    for (auto &nm : op.in)
+      if (tensors.count(nm)) uses[nm]++;
+    std::unique_ptr<OpKernel> k;
+    TensorPtr out;
+    if (op.type == "reshape") {
+      // tpu.reshape is a pure alias of its operand's storage (MlirModuleInterpreter.cpp:331-338);
+      // valid on NHWC storage only when the element order is unchanged.
+      TensorPtr in = opd(0);
+      out = std::make_shared<DevTensor>(*in);
+      out->name = op.name;
+      out->shape = op.shape;
+      out->owns = false;
+      int64_t d[4] = {1, 1, 1, 1};
+      for (size_t i = 0; i < op.shape.size() && i < 4; ++i) d[i] = op.shape[i];
+      TPUCB_CHECK(in->h * in->w == 1 || (d[0] == in->n && d[1] == in->c && d[2] == in->h && d[3] == in->w),
+                  "reshape %s: only reshapes of [n,c,1,1] tensors (or identity) are supported", op.name.c_str());
+      if (in->h * in->w == 1) {
+        TPUCB_CHECK(d[0] == in->n && d[1] * d[2] * d[3] == in->c && (d[2] * d[3] == 1),
+                    "reshape %s: unsupported target shape", op.name.c_str());
+      }
+      tensors[op.name] = out;
+      tensor_order.push_back(op.name);
+      producer_type[op.name] = "reshape";
+      continue;
+    }
+    out = make_tensor(op.name, op.shape, dt);
+    if (op.type == "input") {
+      k.reset(new InputOp());
+      input_details.push_back({op.name, out->numel()});
+    } else if (op.type == "quant") {
+      std::string pt = producer_type[op.in.at(0)];
+      k.reset(new QuantOp(*this, op, opd(0), out, pt == "input"));
+    } else if (op.type == "conv_2d") {
+      k.reset(new Conv2DOp(*this, op, opd(0), out));
+    } else if (op.type == "fully_connected") {
+      k.reset(new FullyConnectedOp(*this, op, opd(0), out));
+    } else if (op.type == "pool_max_2d" || op.type == "pool_avg_2d") {
+      k.reset(new PoolOp(*this, op, opd(0), out, op.type == "pool_avg_2d"));
+    } else if (op.type == "eltwise_add" || op.type == "eltwise_mul") {
+      std::vector<TensorPtr> ins;
+      for (auto &nm : op.in)
+        if (tensors.count(nm)) ins.push_back(tensors[nm]);
+      k.reset(new EltwiseOp(*this, op, ins, out, op.type == "eltwise_mul"));
+    } else if (op.type == "concat") {
+      std::vector<TensorPtr> ins;
+      for (auto &nm : op.in)
+        if (tensors.count(nm)) ins.push_back(tensors[nm]);
+      k.reset(new ConcatOp(*this, op, ins, out));
+    } else if (op.type == "upsample") {
+      k.reset(new MoveOp(*this, op, opd(0), out, 0));
+    } else if (op.type == "pixelshuffle") {
+      k.reset(new MoveOp(*this, op, opd(0), out, 1));
+    } else if (op.type == "relu" || op.type == "leaky_relu") {
+      k.reset(new LeakyReluOp(*this, op, opd(0), out, op.type == "relu"));
+    } else if (op.type == "sigmoid" || op.type == "mish" || op.type == "exp" || op.type == "tanh" ||
+               op.type == "reciprocal") {
+      k.reset(new LutOp(*this, op, opd(0), out));
+    } else if (op.type == "scale") {
+      k.reset(new ScaleOp(*this, op, opd(0), out));
+    } else if (op.type == "softmax") {
+      k.reset(new SoftmaxOp(*this, op, opd(0), out));
+    } else {
+      cudaFree(out->dev);
+      throw Error(strfmt("op type '%s' (%s) is not implemented by the B200 backend", op.type.c_str(), op.name.c_str()));
+    }
+    k->name = op.name;
+    k->op_type = op.type;
+    k->shape = op.shape;
+    k->datatype = dt;
+    k->result = out;
+    tensors[op.name] = out;
+    tensor_order.push_back(op.name);
+    producer_type[op.name] = op.type;
+    kernels.push_back(std::move(k));
+  }
+  for (auto &k : kernels)
+    if (!uses.count(k->name) && k->op_type != "input") output_details.push_back({k->name, k->result->numel()});
+  TPUCB_CUDA(cudaDeviceSynchronize());
+}
+
+// setTensor (MlirModuleInterpreter.cpp:407-417): fp32 NCHW host values -> device storage.
+inline void Interpreter::set_tensor(const std::string &name, const float *data, size_t numel) {
+  bind();
+  TensorPtr t = tensor(name);
+  TPUCB_CHECK(numel == t->numel(), "set_tensor %s: got %zu values, tensor has %zu", name.c_str(), numel, t->numel());
+  float *stg = ensure_staging(numel * sizeof(float));
+  TPUCB_CUDA(cudaMemcpyAsync(stg, data, numel * sizeof(float), cudaMemcpyHostToDevice, stream));
+  TensorGeom g{t->n, t->c, t->h, t->w, t->cp};
+  size_t total = t->pixels() * t->cp;
+  int grid = grid_for(total, 256, sm_count);
+  if (t->dtype == DT_I8) nchw_f32_to_dev_kernel<DT_I8><<<grid, 256, 0, stream>>>(stg, t->dev, g);
+  else if (t->dtype == DT_BF16) nchw_f32_to_dev_kernel<DT_BF16><<<grid, 256, 0, stream>>>(stg, t->dev, g);
+  else nchw_f32_to_dev_kernel<DT_F32><<<grid, 256, 0, stream>>>(stg, t->dev, g);
+  TPUCB_CUDA(cudaGetLastError());
+}
+
+// getTensor (MlirModuleInterpreter.cpp:419-427): deep copy out as fp32 NCHW.
+inline void Interpreter::get_tensor(const std::string &name, float *out, size_t numel) {
+  bind();
+  TensorPtr t = tensor(name);
+  TPUCB_CHECK(numel == t->numel(), "get_tensor %s: buffer has %zu values, tensor has %zu", name.c_str(), numel, t->numel());
+  float *stg = ensure_staging(numel * sizeof(float));
+  TensorGeom g{t->n, t->c, t->h, t->w, t->cp};
+  int grid = grid_for(numel, 256, sm_count);
+  if (t->dtype == DT_I8) dev_to_nchw_f32_kernel<DT_I8><<<grid, 256, 0, stream>>>(t->dev, stg, g);
+  else if (t->dtype == DT_BF16) dev_to_nchw_f32_kernel<DT_BF16><<<grid, 256, 0, stream>>>(t->dev, stg, g);
+  else dev_to_nchw_f32_kernel<DT_F32><<<grid, 256, 0, stream>>>(t->dev, stg, g);
+  TPUCB_CUDA(cudaGetLastError());
+  TPUCB_CUDA(cudaMemcpyAsync(out, stg, numel * sizeof(float), cudaMemcpyDeviceToHost, stream));
+  TPUCB_CUDA(cudaStreamSynchronize(stream));
+}
+
+// invoke (MlirModuleInterpreter.cpp:371-381): the op loop; replayed as one CUDA graph.
+inline void Interpreter::launch_all() {
+  bind();
+  if (use_graph) {
+    if (!graph_exec) {
+      cudaGraph_t graph = nullptr;
+      TPUCB_CUDA(cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal));
+      try {
+        for (auto &k : kernels) k->invoke(stream);
+      } catch (...) {
+        cudaStreamEndCapture(stream, &graph);
+        if (graph) cudaGraphDestroy(graph);
+        throw;
+      }
+      TPUCB_CUDA(cudaStreamEndCapture(stream, &graph));
+      cudaError_t e = cudaGraphInstantiate(&graph_exec, graph, 0);
+      cudaGraphDestroy(graph);
+      TPUCB_CUDA(e);
+    }
+    TPUCB_CUDA(cudaGraphLaunch(graph_exec, stream));
+  } else {
+    for (auto &k : kernels) k->invoke(stream);
+    TPUCB_CUDA(cudaGetLastError());
+  }
+}
+
+inline void Interpreter::launch_to(const std::string &name) {
+  bind();
+  if (name.empty()) return launch_all();
+  tensor(name);
+  for (auto &k : kernels) {
+    k->invoke(stream);
+    if (k->name == name) break;
+  }
+  TPUCB_CUDA(cudaGetLastError());
+}
+
+inline void Interpreter::sync_and_check() {
+  bind();
+  TPUCB_CUDA(cudaStreamSynchronize(stream));
+  int err = 0;
+  TPUCB_CUDA(cudaMemcpy(&err, d_err, sizeof(int), cudaMemcpyDeviceToHost));
+  if (err != 0) {
+    TPUCB_CUDA(cudaMemset(d_err, 0, sizeof(int)));
+    throw Error(strfmt("a convolution kernel gave up on a bounded wait (code %d: 1 = tile load never arrived, "
+                       "2 = stage never freed, 3 = accumulator never completed)", err));
+  }
+}
+
+} // namespace tpucb

@@ -1,0 +1,488 @@
+// HBM-bound kernels of the interpreter backend: layout conversion at the host
+// boundary, quant/dequant, eltwise, pooling, depthwise convolution, patch
+// expansion, concat / upsample / pixel-shuffle, activations and lookup tables.
+//
+// Device tensors are NHWC with the channel pitch `cp` padded to 16 bytes
+// (int8: 16 channels, bf16: 8, fp32: 4); one thread handles one 16-byte vector
+// so that a warp moves 512 contiguous bytes. Grids are sized by the callers as
+// a multiple of the SM count with a grid-stride loop.
+//
+// Reference bodies restated here (lib/Dialect/TPU/Interpreter/core/):
+//   quant.cpp:9-166, eltwise.cpp:52-85,335-357, pooling.cpp:33-160, conv.cpp (depthwise),
+//   concat.cpp:34-90, upsample.cpp:20-41, depthtospace.cpp:6-48, activation.cpp:49-153,
+//   lut_func.cpp:136-187,306-333.
+#pragma once
+#include "common.cuh"
+
+namespace tpucb {
+
+enum DType { DT_I8 = 0, DT_BF16 = 1, DT_F32 = 2 };
+
+struct TensorGeom {
+  int n, c, h, w, cp; // logical NCHW extents and the padded channel pitch (elements)
+};
+
+// ------------------------------------------------------------------ host boundary
+// Host tensors are fp32 NCHW "containers" (include/tpuc/Interpreter/cpukernel.h:15-78).
+// upload: staging fp32 NCHW -> device NHWC of dtype; padded lanes are written as zero.
+template <int DT>
+__global__ void nchw_f32_to_dev_kernel(const float *__restrict__ src, void *__restrict__ dst,
+                                       TensorGeom g) {
+  const size_t total = (size_t)g.n * g.h * g.w * g.cp;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
+       i += (size_t)gridDim.x * blockDim.x) {
+    int c = (int)(i % g.cp);
+    size_t pix = i / g.cp;
+    int x = (int)(pix % g.w);
+    size_t t = pix / g.w;
+    int y = (int)(t % g.h);
+    int b = (int)(t / g.h);
+    float v = c < g.c ? src[(((size_t)b * g.c + c) * g.h + y) * g.w + x] : 0.0f;
+    if (DT == DT_I8) reinterpret_cast<int8_t *>(dst)[i] = (int8_t)(int)v;
+    else if (DT == DT_BF16) reinterpret_cast<uint16_t *>(dst)[i] = (uint16_t)(f32_bits(v) >> 16);
+    else reinterpret_cast<float *>(dst)[i] = v;
+  }
+}
+
+// download: device NHWC -> fp32 NCHW. One thread per NCHW element; reads of a warp
+// stride by cp but stay inside L2-resident rows for the sizes that are fetched.
+template <int DT>
+__global__ void dev_to_nchw_f32_kernel(const void *__restrict__ src, float *__restrict__ dst,
+                                       TensorGeom g) {
+  const size_t total = (size_t)g.n * g.c * g.h * g.w;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
+       i += (size_t)gridDim.x * blockDim.x) {
+    int x = (int)(i % g.w);
+    size_t t = i / g.w;
+    int y = (int)(t % g.h);
+    t /= g.h;
+    int c = (int)(t % g.c);
+    int b = (int)(t / g.c);
+    size_t s = (((size_t)b * g.h + y) * g.w + x) * g.cp + c;
+    float v;
+    if (DT == DT_I8) v = (float)reinterpret_cast<const int8_t *>(src)[s];
+    else if (DT == DT_BF16) v = bits_f32((uint32_t)reinterpret_cast<const uint16_t *>(src)[s] << 16);
+    else v = reinterpret_cast<const float *>(src)[s];
+    dst[i] = v;
+  }
+}
+
+// ------------------------------------------------------------------------- quant
+// kind: 0 fp32->int8 host rounding (std::round, half away from zero)  quant.cpp:22-30
+//       1 fp32->int8 TPU mode                                         quant.cpp:11-20
+//       2 int8->fp32   3 int8->bf16                                   quant.cpp:78-85,97-104
+//       4 bf16->int8                                                  quant.cpp:87-94
+//       5 fp32->bf16 (truncate)                                       quant.cpp:41-52
+// Source and destination may have different channel pitches (cps / cpd).
+__device__ __forceinline__ float load_as_f32(const void *p, int dt, size_t i) {
+  if (dt == DT_I8) return (float)reinterpret_cast<const int8_t *>(p)[i];
+  if (dt == DT_BF16) return bits_f32((uint32_t)reinterpret_cast<const uint16_t *>(p)[i] << 16);
+  return reinterpret_cast<const float *>(p)[i];
+}
+__device__ __forceinline__ void store_from_f32(void *p, int dt, size_t i, float v) {
+  if (dt == DT_I8) reinterpret_cast<int8_t *>(p)[i] = (int8_t)(int)v;
+  else if (dt == DT_BF16) reinterpret_cast<uint16_t *>(p)[i] = (uint16_t)(f32_bits(v) >> 16);
+  else reinterpret_cast<float *>(p)[i] = v;
+}
+
+__global__ void quant_kernel(const void *__restrict__ src, void *__restrict__ dst, size_t pixels,
+                             int c, int cps, int cpd, int sdt, int ddt, int kind, float scale) {
+  const size_t total = pixels * (size_t)cpd;
+  const float sb = bf16_round(scale);
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
+       i += (size_t)gridDim.x * blockDim.x) {
+    int ch = (int)(i % cpd);
+    size_t pix = i / cpd;
+    float out = 0.0f;
+    if (ch < c) {
+      float x = load_as_f32(src, sdt, pix * cps + ch);
+      switch (kind) {
+      case 0: {
+        float r = roundf(__fmul_rn(x, scale));
+        out = fminf(fmaxf(r, -128.0f), 127.0f);
+        break;
+      }
+      case 1:
+        out = (float)f32_to_int8_rne(bf16_round(__fmul_rn(bf16_round(x, false), sb)));
+        break;
+      case 2:
+      case 3:
+        out = bf16_round(__fmul_rn(x, sb));
+        break;
+      case 4:
+        out = (float)f32_to_int8_rne(bf16_round(__fmul_rn(x, sb)));
+        break;
+      default:
+        out = bf16_round(x, false);
+      }
+    }
+    store_from_f32(dst, ddt, i, out);
+  }
+}
+
+// ----------------------------------------------------------------------- eltwise
+// INT8 add: sum_i x_i * (int8)M_i, ReLU, (v + 2^(r-1)) >> r, saturate. eltwise.cpp:52-85.
+struct EltwiseArgs {
+  const int8_t *in[4];
+  int mult[4];
+  int nin;
+  int rshift;
+  int do_relu;
+  int qdm_mult; // eltwise mul: QDM multiplier (0 with rshift 0 = no requant)
+};
+
+__device__ __forceinline__ int sx8(uint32_t w, int j) { return (int)(int8_t)(w >> (8 * j)); }
+
+__global__ void eltwise_add_i8_kernel(EltwiseArgs a, int8_t *__restrict__ out, size_t nvec) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nvec;
+       i += (size_t)gridDim.x * blockDim.x) {
+    int acc[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) acc[j] = 0;
+    for (int k = 0; k < a.nin; ++k) {
+      uint4 v = reinterpret_cast<const uint4 *>(a.in[k])[i];
+      uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 16; ++j) acc[j] += sx8(w[j >> 2], j & 3) * a.mult[k];
+    }
+    uint32_t o[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      int v = acc[j];
+      if (a.do_relu && v < 0) v = 0;
+      int q = rshift_sat8(v, a.rshift);
+      o[j >> 2] |= ((uint32_t)(q & 0xff)) << (8 * (j & 3));
+    }
+    reinterpret_cast<uint4 *>(out)[i] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+// INT8 mul: product, ReLU, QDM requant with a scalar (M, r). eltwise.cpp:335-357.
+__global__ void eltwise_mul_i8_kernel(EltwiseArgs a, int8_t *__restrict__ out, size_t nvec) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nvec;
+       i += (size_t)gridDim.x * blockDim.x) {
+    int acc[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) acc[j] = 1;
+    for (int k = 0; k < a.nin; ++k) {
+      uint4 v = reinterpret_cast<const uint4 *>(a.in[k])[i];
+      uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 16; ++j) acc[j] *= sx8(w[j >> 2], j & 3);
+    }
+    uint32_t o[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      int v = acc[j];
+      if (a.do_relu && v < 0) v = 0;
+      int q = (a.rshift != 0 || a.qdm_mult != 0) ? qdm_requant(v, a.qdm_mult, a.rshift) : v;
+      o[j >> 2] |= ((uint32_t)(q & 0xff)) << (8 * (j & 3));
+    }
+    reinterpret_cast<uint4 *>(out)[i] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+// fp32 add with coefficients (eltwise.cpp:39-50); optional BF16 rounding of the result.
+struct EltwiseF32Args {
+  const float *in[4];
+  float coeff[4];
+  int nin;
+  int do_relu;
+};
+__global__ void eltwise_add_f32_kernel(EltwiseF32Args a, float *__restrict__ out, size_t n) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n;
+       i += (size_t)gridDim.x * blockDim.x) {
+    float acc = 0.0f;
+    for (int k = 0; k < a.nin; ++k) acc = __fadd_rn(acc, __fmul_rn(a.coeff[k], a.in[k][i]));
+    if (a.do_relu && acc < 0) acc = 0;
+    out[i] = acc;
+  }
+}
+
+// ----------------------------------------------------------------------- pooling
+// One thread per (output pixel, 16-channel vector). method 0 max, 1 avg (window sum,
+// then (sum*M + 2^(r-1)) >> r, saturate). pooling.cpp:65-82,146-155.
+struct PoolArgs {
+  int n, c, cp, ih, iw, oh, ow, kh, kw, sh, sw, pt, pl;
+  int method, mult, rshift;
+};
+__global__ void pool_i8_kernel(const int8_t *__restrict__ in, int8_t *__restrict__ out, PoolArgs a) {
+  const int vecs = a.cp / 16;
+  const size_t total = (size_t)a.n * a.oh * a.ow * vecs;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
+       i += (size_t)gridDim.x * blockDim.x) {
+    int v = (int)(i % vecs);
+    size_t pix = i / vecs;
+    int x = (int)(pix % a.ow);
+    size_t t = pix / a.ow;
+    int y = (int)(t % a.oh);
+    int b = (int)(t / a.oh);
+    int acc[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) acc[j] = a.method == 0 ? -128 : 0;
+    for (int r = 0; r < a.kh; ++r) {
+      int yy = y * a.sh - a.pt + r;
+      if (yy < 0 || yy >= a.ih) continue;
+      for (int s = 0; s < a.kw; ++s) {
+        int xx = x * a.sw - a.pl + s;
+        if (xx < 0 || xx >= a.iw) continue;
+        uint4 q = *reinterpret_cast<const uint4 *>(in + (((size_t)b * a.ih + yy) * a.iw + xx) * a.cp + v * 16);
+        uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          int e = sx8(w[j >> 2], j & 3);
+          acc[j] = a.method == 0 ? max(acc[j], e) : acc[j] + e;
+        }
+      }
+    }
+    uint32_t o[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      int q = a.method == 0 ? acc[j] : mul_rshift_sat8(acc[j], a.mult, a.rshift);
+      o[j >> 2] |= ((uint32_t)(q & 0xff)) << (8 * (j & 3));
+    }
+    *reinterpret_cast<uint4 *>(out + pix * a.cp + v * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+// ------------------------------------------------------------- depthwise 3x3 etc.
+// Depthwise convolution (groups == channels), any kh/kw/stride/dilation, zero padding.
+// Weights are packed tap-major [kh*kw][cp] so that a thread reads 16 consecutive
+// channels per tap; the epilogue is the conv epilogue (bias + QDM + saturate + ReLU).
+struct DwArgs {
+  int n, c, cp, ih, iw, oh, ow, kh, kw, sh, sw, pt, pl, dh, dw, do_relu;
+  const int8_t *wgt;  // [kh*kw][cp]
+  const int32_t *bias, *mult, *rshift; // [cp]
+};
+__global__ void dwconv_i8_kernel(const int8_t *__restrict__ in, int8_t *__restrict__ out, DwArgs a) {
+  const int vecs = a.cp / 16;
+  const size_t total = (size_t)a.n * a.oh * a.ow * vecs;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
+       i += (size_t)gridDim.x * blockDim.x) {
+    int v = (int)(i % vecs);
+    size_t pix = i / vecs;
+    int x = (int)(pix % a.ow);
+    size_t t = pix / a.ow;
+    int y = (int)(t % a.oh);
+    int b = (int)(t / a.oh);
+    int acc[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) acc[j] = 0;
+    for (int r = 0; r < a.kh; ++r) {
+      int yy = y * a.sh - a.pt + r * a.dh;
+      if (yy < 0 || yy >= a.ih) continue;
+      for (int s = 0; s < a.kw; ++s) {
+        int xx = x * a.sw - a.pl + s * a.dw;
+        if (xx < 0 || xx >= a.iw) continue;
+        uint4 q = *reinterpret_cast<const uint4 *>(in + (((size_t)b * a.ih + yy) * a.iw + xx) * a.cp + v * 16);
+        uint4 f = *reinterpret_cast<const uint4 *>(a.wgt + (size_t)(r * a.kw + s) * a.cp + v * 16);
+        uint32_t w[4] = {q.x, q.y, q.z, q.w};
+        uint32_t g[4] = {f.x, f.y, f.z, f.w};
+#pragma unroll
+        for (int j = 0; j < 16; ++j) acc[j] += sx8(w[j >> 2], j & 3) * sx8(g[j >> 2], j & 3);
+      }
+    }
+    uint32_t o[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      int ch = v * 16 + j;
+      int q = qdm_requant(acc[j] + a.bias[ch], a.mult[ch], a.rshift[ch]);
+      if (a.do_relu && q < 0) q = 0;
+      o[j >> 2] |= ((uint32_t)(q & 0xff)) << (8 * (j & 3));
+    }
+    *reinterpret_cast<uint4 *>(out + pix * a.cp + v * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+// ---------------------------------------------------------------- patch expansion
+// Writes the patch matrix A[M = n*oh*ow][kp] (kp = padded kh*kw*c, K order (r, s, c) over
+// the REAL channels) for convolutions the im2col TMA path does not take: very few
+// input channels (the 3-channel stems), input zero-insertion, grouped convolution.
+struct PatchArgs {
+  int n, c, cp, ih, iw, oh, ow, kh, kw, sh, sw, pt, pl, dh, dw, ins_h, ins_w;
+  int c_first, c_count; // channel slice (grouped convolution)
+  int kp;
+};
+__global__ void patch_expand_i8_kernel(const int8_t *__restrict__ in, int8_t *__restrict__ out,
+                                       PatchArgs a) {
+  const size_t total = (size_t)a.n * a.oh * a.ow * a.kp;
+  const int ihd = (a.ih - 1) * (a.ins_h + 1) + 1, iwd = (a.iw - 1) * (a.ins_w + 1) + 1;
+  const int kreal = a.kh * a.kw * a.c_count;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
+       i += (size_t)gridDim.x * blockDim.x) {
+    int k = (int)(i % a.kp);
+    size_t pix = i / a.kp;
+    int8_t v = 0;
+    if (k < kreal) {
+      int c = k % a.c_count;
+      int tap = k / a.c_count;
+      int s = tap % a.kw, r = tap / a.kw;
+      int x = (int)(pix % a.ow);
+      size_t t = pix / a.ow;
+      int y = (int)(t % a.oh);
+      int b = (int)(t / a.oh);
+      int yy = y * a.sh - a.pt + r * a.dh, xx = x * a.sw - a.pl + s * a.dw;
+      if (yy >= 0 && yy < ihd && xx >= 0 && xx < iwd && (yy % (a.ins_h + 1)) == 0 &&
+          (xx % (a.ins_w + 1)) == 0) {
+        v = in[(((size_t)b * a.ih + yy / (a.ins_h + 1)) * a.iw + xx / (a.ins_w + 1)) * a.cp + a.c_first + c];
+      }
+    }
+    out[i] = v;
+  }
+}
+
+// ------------------------------------------------------------------ data movement
+// Channel concat of one input into a slice of the output, with the optional non-QDM
+// rescale and ReLU of concat.cpp:70-85. Byte granular so that unaligned slices
+// (e.g. 255-channel heads) work; the 16-byte fast path is taken when everything aligns.
+__global__ void concat_slice_i8_kernel(const int8_t *__restrict__ in, int8_t *__restrict__ out,
+                                       size_t pixels, int c, int cps, int cpd, int c_off, int mult,
+                                       int rshift, int requant, int do_relu) {
+  const size_t total = pixels * (size_t)c;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
+       i += (size_t)gridDim.x * blockDim.x) {
+    int ch = (int)(i % c);
+    size_t pix = i / c;
+    int v = in[pix * cps + ch];
+    if (requant) v = mul_rshift_sat8(v, mult, rshift);
+    if (do_relu && v < 0) v = 0;
+    out[pix * cpd + c_off + ch] = (int8_t)v;
+  }
+}
+
+// Generic element copy with an index map; element size es bytes (1, 2 or 4).
+// mode 0: nearest upsample (upsample.cpp:20-41); mode 1/2: pixel shuffle CRD / DCR
+// (depthtospace.cpp:6-48), expressed as a gather over the OUTPUT index.
+struct MoveArgs {
+  int n, ic, ih, iw, icp, oc, oh, ow, ocp, es, mode, r, scale_h, scale_w;
+};
+__global__ void move_kernel(const uint8_t *__restrict__ in, uint8_t *__restrict__ out, MoveArgs a) {
+  const size_t total = (size_t)a.n * a.oh * a.ow * a.ocp;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
+       i += (size_t)gridDim.x * blockDim.x) {
+    int c = (int)(i % a.ocp);
+    size_t pix = i / a.ocp;
+    int x = (int)(pix % a.ow);
+    size_t t = pix / a.ow;
+    int y = (int)(t % a.oh);
+    int b = (int)(t / a.oh);
+    bool valid = c < a.oc;
+    int sc = c, sy = y, sx = x;
+    if (a.mode == 0) {
+      sy = y / a.scale_h;
+      sx = x / a.scale_w;
+    } else {
+      int r = a.r;
+      sy = y / r;
+      sx = x / r;
+      int dy = y % r, dx = x % r;
+      sc = a.mode == 1 ? (c * r * r + dy * r + dx) : ((dy * r + dx) * a.oc + c);
+    }
+    size_t s = (((size_t)b * a.ih + sy) * a.iw + sx) * a.icp + sc;
+    for (int e = 0; e < a.es; ++e) out[i * a.es + e] = valid ? in[s * a.es + e] : 0;
+  }
+}
+
+// ------------------------------------------------------------------- activations
+// INT8 leaky ReLU (activation.cpp:126-153) and plain ReLU (internal.cpp:13-18).
+__global__ void leaky_relu_i8_kernel(const int8_t *__restrict__ in, int8_t *__restrict__ out,
+                                     size_t nvec, int mp, int rp, int mn, int rn, int plain_relu) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nvec;
+       i += (size_t)gridDim.x * blockDim.x) {
+    uint4 v = reinterpret_cast<const uint4 *>(in)[i];
+    uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    uint32_t o[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      int x = sx8(w[j >> 2], j & 3);
+      int q;
+      if (plain_relu) q = x > 0 ? x : 0;
+      else if (x > 0) q = mp != 0 ? mul_rshift_sat8(x, mp, rp) : x;
+      else q = mul_rshift_sat8(x, mn, rn);
+      o[j >> 2] |= ((uint32_t)(q & 0xff)) << (8 * (j & 3));
+    }
+    reinterpret_cast<uint4 *>(out)[i] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+// INT8 256-entry table (activation.cpp:49-53): out = table[(uint8)x]; table staged in smem.
+__global__ void lut_i8_kernel(const int8_t *__restrict__ in, int8_t *__restrict__ out, size_t nvec,
+                              const int8_t *__restrict__ table) {
+  __shared__ int8_t s_t[256];
+  for (int i = threadIdx.x; i < 256; i += blockDim.x) s_t[i] = table[i];
+  __syncthreads();
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nvec;
+       i += (size_t)gridDim.x * blockDim.x) {
+    uint4 v = reinterpret_cast<const uint4 *>(in)[i];
+    uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    uint32_t o[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      uint32_t idx = (w[j >> 2] >> (8 * (j & 3))) & 0xff;
+      o[j >> 2] |= ((uint32_t)(uint8_t)s_t[idx]) << (8 * (j & 3));
+    }
+    reinterpret_cast<uint4 *>(out)[i] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+// BF16 slope-interpolated table (lut_func.cpp:169-186). Tables are 256 fp32 values holding
+// bf16-representable numbers; `scale` is BF16(256 / (2 * range)). Multiply and add are kept
+// separate (no FMA contraction), as the x86 reference computes them.
+__global__ void lut_bf16_slope_kernel(const uint16_t *__restrict__ in, uint16_t *__restrict__ out,
+                                      size_t n, const float *__restrict__ base,
+                                      const float *__restrict__ slope, float scale) {
+  __shared__ float s_b[256], s_s[256];
+  for (int i = threadIdx.x; i < 256; i += blockDim.x) {
+    s_b[i] = base[i];
+    s_s[i] = slope[i];
+  }
+  __syncthreads();
+  const size_t nvec = n / 8;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nvec;
+       i += (size_t)gridDim.x * blockDim.x) {
+    uint4 v = reinterpret_cast<const uint4 *>(in)[i];
+    uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float x = bits_f32(((w[j >> 1] >> (16 * (j & 1))) & 0xffffu) << 16);
+      float r = bf16_round(__fmul_rn(x, scale));
+      int idx = f32_to_int8_rz(r);
+      float dx = bf16_round(__fsub_rn(r, (float)idx));
+      float y = bf16_round(__fadd_rn(s_b[idx & 0xff], __fmul_rn(dx, s_s[idx & 0xff])));
+      uint32_t h = f32_bits(y) >> 16;
+      if ((j & 1) == 0) o[j >> 1] = h;
+      else o[j >> 1] |= h << 16;
+    }
+    reinterpret_cast<uint4 *>(out)[i] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+// BF16 exponent x mantissa table (lut_func.cpp:306-333, "mantissa" method; reciprocal is the
+// pow table with coefficient -1). floor(log2|x|) is the unbiased exponent field for normal x.
+__global__ void lut_bf16_mantissa_kernel(const uint16_t *__restrict__ in, uint16_t *__restrict__ out,
+                                         size_t n, const float *__restrict__ exp_table,
+                                         const float *__restrict__ mant_table) {
+  __shared__ float s_e[256], s_m[256];
+  for (int i = threadIdx.x; i < 256; i += blockDim.x) {
+    s_e[i] = exp_table[i];
+    s_m[i] = mant_table[i];
+  }
+  __syncthreads();
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n;
+       i += (size_t)gridDim.x * blockDim.x) {
+    uint32_t h = in[i];
+    float x = bits_f32(h << 16);
+    int e;
+    if (x == 0.0f) e = 0;
+    else {
+      int ex = (int)((h >> 7) & 0xff) - 127; // floor(log2 |x|) for normal bf16 values
+      e = ex + 63 + ((h & 0x8000u) ? 128 : 0);
+      e = min(max(e, 0), 255);
+    }
+    float y = bf16_round(__fmul_rn(s_e[e], s_m[h & 0xff]));
+    out[i] = (uint16_t)(f32_bits(y) >> 16);
+  }
+}
+
+} // namespace tpucb

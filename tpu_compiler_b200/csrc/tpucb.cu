@@ -1,0 +1,341 @@
+// C ABI of libtpucb.so: a thin extern "C" layer over tpucb::Interpreter. See include/tpucb.h
+// for the reference interface each entry point stands in for.
+#include "../../include/tpucb.h"
+#include "interpreter.cuh"
+
+#include <cmath>
+#include <string>
+
+using namespace tpucb;
+
+struct tpucb_interp {
+  Interpreter impl;
+  explicit tpucb_interp(int device) : impl(device) {}
+};
+
+static thread_local std::string g_last_error;
+
+#define TPUCB_API_BEGIN try {
+#define TPUCB_API_END                                  \
+  }                                                    \
+  catch (const std::exception &e) {                    \
+    g_last_error = e.what();                           \
+    return 1;                                          \
+  }                                                    \
+  catch (...) {                                        \
+    g_last_error = "unknown error";                    \
+    return 1;                                          \
+  }                                                    \
+  return 0;
+
+static int copy_out(const std::string &s, char *out, size_t cap, size_t *needed) {
+  if (needed) *needed = s.size() + 1;
+  if (out && cap > 0) {
+    size_t n = s.size() < cap - 1 ? s.size() : cap - 1;
+    memcpy(out, s.data(), n);
+    out[n] = 0;
+  }
+  return 0;
+}
+
+extern "C" {
+
+const char *tpucb_last_error(void) { return g_last_error.c_str(); }
+int tpucb_version(void) { return 1; }
+
+int tpucb_interp_create(int device, tpucb_interp **out) {
+  TPUCB_API_BEGIN
+  TPUCB_CHECK(out != nullptr, "tpucb_interp_create: out is NULL");
+  int count = 0;
+  cudaError_t e = cudaGetDeviceCount(&count);
+  TPUCB_CHECK(e == cudaSuccess && count > 0,
+              "no CUDA device is available (%s); this backend has no CPU fallback",
+              e == cudaSuccess ? "device count is 0" : cudaGetErrorString(e));
+  TPUCB_CHECK(device >= 0 && device < count, "device %d out of range (have %d)", device, count);
+  *out = new tpucb_interp(device);
+  TPUCB_API_END
+}
+
+int tpucb_interp_destroy(tpucb_interp *it) {
+  TPUCB_API_BEGIN
+  delete it;
+  TPUCB_API_END
+}
+
+int tpucb_interp_set_weight(tpucb_interp *it, const char *name, const float *data, const int64_t *shape, int rank) {
+  TPUCB_API_BEGIN
+  TPUCB_CHECK(it && name && data && rank >= 0, "tpucb_interp_set_weight: bad argument");
+  HostWeight w;
+  size_t n = 1;
+  for (int i = 0; i < rank; ++i) {
+    w.shape.push_back(shape[i]);
+    n *= (size_t)shape[i];
+  }
+  w.data.assign(data, data + n);
+  it->impl.weights[name] = std::move(w);
+  TPUCB_API_END
+}
+
+int tpucb_interp_load_module(tpucb_interp *it, const char *module_text) {
+  TPUCB_API_BEGIN
+  TPUCB_CHECK(it && module_text, "tpucb_interp_load_module: bad argument");
+  it->impl.load_module(module_text);
+  TPUCB_API_END
+}
+
+int tpucb_interp_set_tensor(tpucb_interp *it, const char *name, const float *data, size_t numel) {
+  TPUCB_API_BEGIN
+  TPUCB_CHECK(it && name && data, "tpucb_interp_set_tensor: bad argument");
+  it->impl.set_tensor(name, data, numel);
+  TPUCB_API_END
+}
+
+int tpucb_interp_invoke(tpucb_interp *it) {
+  TPUCB_API_BEGIN
+  TPUCB_CHECK(it, "tpucb_interp_invoke: bad argument");
+  it->impl.launch_all();
+  it->impl.sync_and_check();
+  TPUCB_API_END
+}
+
+int tpucb_interp_invoke_to(tpucb_interp *it, const char *name) {
+  TPUCB_API_BEGIN
+  TPUCB_CHECK(it, "tpucb_interp_invoke_to: bad argument");
+  it->impl.launch_to(name ? name : "");
+  it->impl.sync_and_check();
+  TPUCB_API_END
+}
+
+int tpucb_interp_launch(tpucb_interp *it) {
+  TPUCB_API_BEGIN
+  TPUCB_CHECK(it, "tpucb_interp_launch: bad argument");
+  it->impl.launch_all();
+  TPUCB_API_END
+}
+
+int tpucb_interp_sync(tpucb_interp *it) {
+  TPUCB_API_BEGIN
+  TPUCB_CHECK(it, "tpucb_interp_sync: bad argument");
+  it->impl.sync_and_check();
+  TPUCB_API_END
+}
+
+int tpucb_interp_get_tensor(tpucb_interp *it, const char *name, float *out, size_t numel) {
+  TPUCB_API_BEGIN
+  TPUCB_CHECK(it && name && out, "tpucb_interp_get_tensor: bad argument");
+  it->impl.get_tensor(name, out, numel);
+  TPUCB_API_END
+}
+
+int tpucb_interp_get_tensor_shape(tpucb_interp *it, const char *name, int64_t *shape, int *rank) {
+  TPUCB_API_BEGIN
+  TPUCB_CHECK(it && name && shape && rank, "tpucb_interp_get_tensor_shape: bad argument");
+  auto t = it->impl.tensor(name);
+  *rank = (int)t->shape.size();
+  for (size_t i = 0; i < t->shape.size(); ++i) shape[i] = t->shape[i];
+  TPUCB_API_END
+}
+
+int tpucb_interp_get_data_type(tpucb_interp *it, const char *name, char *out, size_t cap) {
+  TPUCB_API_BEGIN
+  TPUCB_CHECK(it && name && out, "tpucb_interp_get_data_type: bad argument");
+  copy_out(dtype_to_string(it->impl.tensor(name)->dtype), out, cap, nullptr);
+  TPUCB_API_END
+}
+
+int tpucb_interp_get_all_tensor_names(tpucb_interp *it, char *out, size_t cap, size_t *needed) {
+  TPUCB_API_BEGIN
+  TPUCB_CHECK(it, "tpucb_interp_get_all_tensor_names: bad argument");
+  std::string s;
+  for (auto &n : it->impl.tensor_order) s += n + "\n";
+  copy_out(s, out, cap, needed);
+  TPUCB_API_END
+}
+
+int tpucb_interp_get_details(tpucb_interp *it, int outputs, char *out, size_t cap, size_t *needed) {
+  TPUCB_API_BEGIN
+  TPUCB_CHECK(it, "tpucb_interp_get_details: bad argument");
+  std::string s;
+  for (auto &d : outputs ? it->impl.output_details : it->impl.input_details)
+    s += d.first + ":" + std::to_string(d.second) + "\n";
+  copy_out(s, out, cap, needed);
+  TPUCB_API_END
+}
+
+int tpucb_interp_get_op_info(tpucb_interp *it, char *out, size_t cap, size_t *needed) {
+  TPUCB_API_BEGIN
+  TPUCB_CHECK(it, "tpucb_interp_get_op_info: bad argument");
+  std::string s;
+  for (auto &k : it->impl.kernels) {
+    s += k->name + "\t" + k->op_type + "\t" + dtype_to_string(k->datatype) + "\t";
+    for (size_t i = 0; i < k->shape.size(); ++i) s += (i ? "," : "") + std::to_string(k->shape[i]);
+    s += "\t" + std::to_string(k->alg_ops) + "\t" + std::to_string(k->alg_bytes);
+    auto *cv = dynamic_cast<Conv2DOp *>(k.get());
+    auto *fc = dynamic_cast<FullyConnectedOp *>(k.get());
+    s += std::string("\t") + ((cv && cv->is_tensor_core()) || fc ? "tensor" : "hbm") + "\n";
+  }
+  copy_out(s, out, cap, needed);
+  TPUCB_API_END
+}
+
+int tpucb_interp_set_option(tpucb_interp *it, const char *key, int value) {
+  TPUCB_API_BEGIN
+  TPUCB_CHECK(it && key, "tpucb_interp_set_option: bad argument");
+  std::string k = key;
+  if (k == "cuda_graph") {
+    it->impl.use_graph = value != 0;
+    it->impl.invalidate_graph();
+  } else {
+    throw Error("unknown option '" + k + "'");
+  }
+  TPUCB_API_END
+}
+
+int tpucb_interp_profile(tpucb_interp *it, float *ms, int cap, int *count) {
+  TPUCB_API_BEGIN
+  TPUCB_CHECK(it && ms && count, "tpucb_interp_profile: bad argument");
+  Interpreter &I = it->impl;
+  I.bind();
+  const int n = (int)I.kernels.size();
+  *count = n;
+  TPUCB_CHECK(cap >= n, "tpucb_interp_profile: buffer holds %d entries, need %d", cap, n);
+  std::vector<cudaEvent_t> ev(n + 1);
+  for (auto &e : ev) TPUCB_CUDA(cudaEventCreate(&e));
+  TPUCB_CUDA(cudaEventRecord(ev[0], I.stream));
+  for (int i = 0; i < n; ++i) {
+    I.kernels[i]->invoke(I.stream);
+    TPUCB_CUDA(cudaEventRecord(ev[i + 1], I.stream));
+  }
+  I.sync_and_check();
+  for (int i = 0; i < n; ++i) TPUCB_CUDA(cudaEventElapsedTime(&ms[i], ev[i], ev[i + 1]));
+  for (auto &e : ev) cudaEventDestroy(e);
+  TPUCB_API_END
+}
+
+int tpucb_interp_time_launches(tpucb_interp *it, int iters, float *ms_total) {
+  TPUCB_API_BEGIN
+  TPUCB_CHECK(it && ms_total && iters > 0, "tpucb_interp_time_launches: bad argument");
+  Interpreter &I = it->impl;
+  I.bind();
+  cudaEvent_t a, b;
+  TPUCB_CUDA(cudaEventCreate(&a));
+  TPUCB_CUDA(cudaEventCreate(&b));
+  TPUCB_CUDA(cudaStreamSynchronize(I.stream));
+  TPUCB_CUDA(cudaEventRecord(a, I.stream));
+  for (int i = 0; i < iters; ++i) I.launch_all();
+  TPUCB_CUDA(cudaEventRecord(b, I.stream));
+  I.sync_and_check();
+  TPUCB_CUDA(cudaEventElapsedTime(ms_total, a, b));
+  cudaEventDestroy(a);
+  cudaEventDestroy(b);
+  TPUCB_API_END
+}
+
+int tpucb_interp_kernel_count(tpucb_interp *it, int *count) {
+  TPUCB_API_BEGIN
+  TPUCB_CHECK(it && count, "tpucb_interp_kernel_count: bad argument");
+  int c = 0;
+  for (auto &k : it->impl.kernels) c += k->kernel_launches();
+  *count = c;
+  TPUCB_API_END
+}
+
+int tpucb_interp_tensor_device(tpucb_interp *it, const char *name, void **dev, size_t *bytes, int *channels,
+                               int *channel_pitch, int *dtype) {
+  TPUCB_API_BEGIN
+  TPUCB_CHECK(it && name, "tpucb_interp_tensor_device: bad argument");
+  auto t = it->impl.tensor(name);
+  if (dev) *dev = t->dev;
+  if (bytes) *bytes = t->bytes();
+  if (channels) *channels = t->c;
+  if (channel_pitch) *channel_pitch = t->cp;
+  if (dtype) *dtype = t->dtype;
+  TPUCB_API_END
+}
+
+int tpucb_host_alloc(void **ptr, size_t bytes) {
+  TPUCB_API_BEGIN
+  TPUCB_CHECK(ptr, "tpucb_host_alloc: bad argument");
+  TPUCB_CUDA(cudaHostAlloc(ptr, bytes, cudaHostAllocDefault));
+  TPUCB_API_END
+}
+
+int tpucb_host_free(void *ptr) {
+  TPUCB_API_BEGIN
+  TPUCB_CUDA(cudaFreeHost(ptr));
+  TPUCB_API_END
+}
+
+// ---------------------------------------------------------------- calibration statistics
+
+int tpucb_calib_minmax(tpucb_interp *it, const char *name, float *d_stats) {
+  TPUCB_API_BEGIN
+  TPUCB_CHECK(it && name && d_stats, "tpucb_calib_minmax: bad argument");
+  Interpreter &I = it->impl;
+  I.bind();
+  auto t = I.tensor(name);
+  TPUCB_CHECK(t->dtype == DT_F32, "tpucb_calib_minmax: tensor %s is not fp32", name);
+  size_t total = t->pixels() * t->cp;
+  minmax_f32_kernel<<<grid_for(total / 4 + 1, 256, I.sm_count), 256, 0, I.stream>>>((const float *)t->dev, t->pixels(),
+                                                                                    t->c, t->cp, d_stats);
+  TPUCB_CUDA(cudaGetLastError());
+  TPUCB_API_END
+}
+
+int tpucb_calib_hist(tpucb_interp *it, const char *name, float abs_max, int bins, int64_t *d_hist) {
+  TPUCB_API_BEGIN
+  TPUCB_CHECK(it && name && d_hist, "tpucb_calib_hist: bad argument");
+  TPUCB_CHECK(bins >= 128 && bins <= 4096, "tpucb_calib_hist: bins must be in [128, 4096]");
+  Interpreter &I = it->impl;
+  I.bind();
+  auto t = I.tensor(name);
+  TPUCB_CHECK(t->dtype == DT_F32, "tpucb_calib_hist: tensor %s is not fp32", name);
+  // width = abs_max / (bin_num - 1), in fp32 as numpy computes it (kld_calibrator.py:34)
+  float width = abs_max / (float)(bins - 1);
+  size_t total = t->pixels() * t->cp;
+  int grid = grid_for(total, 256, I.sm_count);
+  if (grid > I.sm_count * 4) grid = I.sm_count * 4;
+  hist_f32_kernel<<<grid, 256, bins * sizeof(unsigned), I.stream>>>((const float *)t->dev, t->pixels(), t->c, t->cp,
+                                                                    width, bins, (unsigned long long *)d_hist);
+  TPUCB_CUDA(cudaGetLastError());
+  TPUCB_API_END
+}
+
+int tpucb_calib_kld(tpucb_interp *it, const int64_t *d_hist, const float *widths, int count, int bins,
+                    float *thresholds) {
+  TPUCB_API_BEGIN
+  TPUCB_CHECK(it && d_hist && widths && thresholds && count > 0, "tpucb_calib_kld: bad argument");
+  TPUCB_CHECK(bins % 128 == 0 && bins >= 128 && bins <= 4096, "tpucb_calib_kld: bins must be a multiple of 128 up to 4096");
+  Interpreter &I = it->impl;
+  I.bind();
+  const int kl_num = bins / 128;
+  float *d_kl = nullptr;
+  TPUCB_CUDA(cudaMalloc(&d_kl, sizeof(float) * count * kl_num));
+  size_t smem = (size_t)bins * (2 * sizeof(float) + sizeof(double));
+  cudaError_t e = cudaFuncSetAttribute(kld_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) {
+    cudaFree(d_kl);
+    TPUCB_CUDA(e);
+  }
+  kld_kernel<<<count * kl_num, 256, smem, I.stream>>>((const long long *)d_hist, bins, d_kl);
+  std::vector<float> kl((size_t)count * kl_num);
+  e = cudaMemcpyAsync(kl.data(), d_kl, kl.size() * sizeof(float), cudaMemcpyDeviceToHost, I.stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(I.stream);
+  cudaFree(d_kl);
+  TPUCB_CUDA(e);
+  // the_min_index + threshold (calibration_math.cpp:85-98, 321-322): first strict minimum.
+  for (int t = 0; t < count; ++t) {
+    const float *k = kl.data() + (size_t)t * kl_num;
+    int m_min = 0;
+    float best = k[0];
+    for (int i = 1; i < kl_num; ++i)
+      if (best > k[i]) {
+        best = k[i];
+        m_min = i;
+      }
+    thresholds[t] = widths[t] * (m_min + 1) * 128;
+  }
+  TPUCB_API_END
+}
+
+} // extern "C"

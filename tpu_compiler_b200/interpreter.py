@@ -1,0 +1,170 @@
+"""``module``: the pymlir.module method set (bindings/python/pymlir.cpp:289-311) over the
+C ABI of libtpucb.so. Tensors cross as float32 numpy arrays in the logical (NCHW) shape,
+exactly as they do with the reference binding."""
+import ctypes as C
+import os
+
+import numpy as np
+
+from ._lib import check, lib
+
+_f = C.POINTER(C.c_float)
+
+
+def _text(fn, *prefix):
+    need = C.c_size_t(0)
+    check(fn(*prefix, None, 0, C.byref(need)))
+    buf = C.create_string_buffer(need.value + 1)
+    check(fn(*prefix, buf, need.value + 1, C.byref(need)))
+    return buf.value.decode()
+
+
+class module:
+    def __init__(self, device=0):
+        self._h = C.c_void_p()
+        self._device = device
+        self._lib = lib()
+        check(self._lib.tpucb_interp_create(int(device), C.byref(self._h)))
+        self._weight_file = None
+        self.op_info = []
+
+    def __del__(self):
+        try:
+            if self._h:
+                self._lib.tpucb_interp_destroy(self._h)
+                self._h = C.c_void_p()
+        except Exception:
+            pass
+
+    close = __del__
+
+    # ---- loading ---------------------------------------------------------------
+    def load(self, mlir_file, weights=None):
+        """pymlir.module.load: ``mlir_file`` is a module text file; its weights come from the
+        ``.npz`` written next to it (``<file>.npz``, or the path on a ``# weight_file:`` line)."""
+        with open(mlir_file) as f:
+            text = f.read()
+        if weights is None:
+            wf = mlir_file + ".npz"
+            for line in text.splitlines():
+                if line.startswith("# weight_file:"):
+                    wf = os.path.join(os.path.dirname(mlir_file), line.split(":", 1)[1].strip())
+            self._weight_file = wf
+            weights = dict(np.load(wf))
+        self.load_text(text, weights)
+
+    def load_text(self, text, weights):
+        for name, arr in weights.items():
+            a = np.ascontiguousarray(arr, dtype=np.float32)
+            shape = (C.c_int64 * max(a.ndim, 1))(*(a.shape if a.ndim else (1,)))
+            check(self._lib.tpucb_interp_set_weight(self._h, name.encode(), a.ctypes.data_as(_f), shape,
+                                                    max(a.ndim, 1)))
+        check(self._lib.tpucb_interp_load_module(self._h, text.encode()))
+        self.op_info = []
+        for line in _text(self._lib.tpucb_interp_get_op_info, self._h).splitlines():
+            name, typ, dt, shape, ops, nbytes, bound = line.split("\t")
+            self.op_info.append({"name": name, "type": typ, "dtype": dt,
+                                 "shape": [int(s) for s in shape.split(",") if s],
+                                 "ops": float(ops), "bytes": float(nbytes), "bound": bound})
+
+    def get_weight_file_path(self):
+        return self._weight_file
+
+    # ---- tensors ---------------------------------------------------------------
+    def set_tensor(self, name, array):
+        a = np.ascontiguousarray(array, dtype=np.float32)
+        check(self._lib.tpucb_interp_set_tensor(self._h, name.encode(), a.ctypes.data_as(_f), a.size))
+
+    def set_tensor_ptr(self, name, host_ptr, numel):
+        """Same as set_tensor, from a raw (e.g. pinned) host pointer."""
+        check(self._lib.tpucb_interp_set_tensor(self._h, name.encode(), C.cast(host_ptr, _f), numel))
+
+    def get_tensor_shape(self, name):
+        shape = (C.c_int64 * 8)()
+        rank = C.c_int(0)
+        check(self._lib.tpucb_interp_get_tensor_shape(self._h, name.encode(), shape, C.byref(rank)))
+        return [int(shape[i]) for i in range(rank.value)]
+
+    def get_tensor(self, name):
+        shape = self.get_tensor_shape(name)
+        out = np.empty(shape, np.float32)
+        check(self._lib.tpucb_interp_get_tensor(self._h, name.encode(), out.ctypes.data_as(_f), out.size))
+        return out
+
+    def get_tensor_into(self, name, host_ptr, numel):
+        check(self._lib.tpucb_interp_get_tensor(self._h, name.encode(), C.cast(host_ptr, _f), numel))
+
+    def get_data_type(self, name):
+        buf = C.create_string_buffer(16)
+        check(self._lib.tpucb_interp_get_data_type(self._h, name.encode(), buf, 16))
+        return buf.value.decode()
+
+    def get_all_tensor_names(self):
+        return [n for n in _text(self._lib.tpucb_interp_get_all_tensor_names, self._h).splitlines() if n]
+
+    def get_all_tensor(self):
+        return {n: self.get_tensor(n) for n in self.get_all_tensor_names()}
+
+    def _details(self, outputs):
+        out = []
+        for line in _text(self._lib.tpucb_interp_get_details, self._h, int(outputs)).splitlines():
+            if line:
+                n, sz = line.rsplit(":", 1)
+                out.append(n)
+        return out
+
+    def get_input_details(self):
+        return self._details(False)
+
+    def get_output_details(self):
+        return self._details(True)
+
+    # ---- execution -------------------------------------------------------------
+    def invoke(self):
+        check(self._lib.tpucb_interp_invoke(self._h))
+
+    def invoke_to(self, name):
+        check(self._lib.tpucb_interp_invoke_to(self._h, name.encode()))
+
+    def launch(self):
+        check(self._lib.tpucb_interp_launch(self._h))
+
+    def sync(self):
+        check(self._lib.tpucb_interp_sync(self._h))
+
+    def run(self, input):
+        """pymlir.module.run: set the (single) input, invoke, return the outputs."""
+        ins = self.get_input_details()
+        if len(ins) != 1:
+            raise RuntimeError("run() needs a module with exactly one input")
+        self.set_tensor(ins[0], input)
+        self.invoke()
+        return {n: self.get_tensor(n) for n in self.get_output_details()}
+
+    # ---- measurement helpers ------------------------------------------------------
+    def set_option(self, key, value):
+        check(self._lib.tpucb_interp_set_option(self._h, key.encode(), int(value)))
+
+    def profile(self):
+        n = len(self.op_info)
+        ms = (C.c_float * max(n, 1))()
+        cnt = C.c_int(0)
+        check(self._lib.tpucb_interp_profile(self._h, ms, n, C.byref(cnt)))
+        return [float(ms[i]) for i in range(cnt.value)]
+
+    def time_launches(self, iters):
+        ms = C.c_float(0)
+        check(self._lib.tpucb_interp_time_launches(self._h, int(iters), C.byref(ms)))
+        return float(ms.value)
+
+    def kernel_count(self):
+        c = C.c_int(0)
+        check(self._lib.tpucb_interp_kernel_count(self._h, C.byref(c)))
+        return int(c.value)
+
+    def tensor_device(self, name):
+        dev, nbytes = C.c_void_p(), C.c_size_t()
+        c, cp, dt = C.c_int(), C.c_int(), C.c_int()
+        check(self._lib.tpucb_interp_tensor_device(self._h, name.encode(), C.byref(dev), C.byref(nbytes), C.byref(c),
+                                                   C.byref(cp), C.byref(dt)))
+        return {"ptr": dev.value, "bytes": nbytes.value, "channels": c.value, "pitch": cp.value, "dtype": dt.value}

@@ -1,0 +1,78 @@
+"""GPU parity of the whole INT8 ResNet-50 module (the benchmark workload): every tensor of a
+batch-1 run equals the CPU oracle bit for bit; larger batches are checked through the
+size-independent property that images do not interact (a batch equals its images run alone)."""
+import numpy as np
+import pytest
+
+from oracle import graph_runner
+from tpu_compiler_b200 import graphs
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def model_b1():
+    return graphs.resnet50_int8(batch=1, seed=1001)
+
+
+def test_resnet50_b1_every_tensor(model_b1):
+    from tpu_compiler_b200 import module
+    img = np.random.default_rng(123).uniform(-1, 1, (1, 3, 224, 224)).astype(np.float32)
+    ref = graph_runner.run(model_b1.text, model_b1.weights, {"data": img})
+    m = module(0)
+    m.load_text(model_b1.text, model_b1.weights)
+    m.set_tensor("data", img)
+    m.invoke()
+    first_bad = None
+    for name in m.get_all_tensor_names():
+        got = m.get_tensor(name)
+        if not np.array_equal(got.reshape(-1), ref[name].reshape(-1)):
+            first_bad = (name, int((got.reshape(-1) != ref[name].reshape(-1)).sum()), got.size)
+            break
+    assert first_bad is None, "first mismatching op: %s (%d of %d values)" % first_bad
+    assert m.get_data_type("res2a") == "INT8" and m.get_data_type("fc1000_dequant") == "FP32"
+    assert m.get_output_details() == ["fc1000_dequant"] and m.get_input_details() == ["data"]
+    m.close()
+
+
+def test_resnet50_batch_equals_single_images_and_graph_equals_eager(model_b1):
+    from tpu_compiler_b200 import module
+    B = 5
+    imgs = np.random.default_rng(321).uniform(-1, 1, (B, 3, 224, 224)).astype(np.float32)
+    mb = graphs.resnet50_int8(batch=B, seed=1001)
+    m = module(0)
+    m.load_text(mb.text, mb.weights)
+    m.set_tensor("data", imgs)
+    m.invoke()          # first invoke captures the CUDA graph
+    m.invoke()          # replay
+    names = ["conv1", "pool1", "res2c", "res3a_branch1", "res4f", "res5c", "pool5", "fc1000", "fc1000_dequant"]
+    batch = {n: m.get_tensor(n) for n in names}
+    m.set_option("cuda_graph", 0)
+    m.invoke()
+    for n in names:
+        assert np.array_equal(batch[n], m.get_tensor(n)), "graph replay differs from eager at " + n
+    m.close()
+    s = module(0)
+    s.load_text(model_b1.text, model_b1.weights)
+    for i in (0, B - 1):
+        s.set_tensor("data", imgs[i:i + 1])
+        s.invoke()
+        for n in names:
+            assert np.array_equal(batch[n][i:i + 1], s.get_tensor(n)), "image %d differs at %s" % (i, n)
+    s.close()
+
+
+def test_run_api_and_errors():
+    from tpu_compiler_b200 import TpucbError, module
+    model = graphs.single_conv_i8(1, 32, 32, 8, 3, 1, 1, seed=5)
+    m = module(0)
+    m.load_text(model.text, model.weights)
+    out = m.run(model.meta["x"])
+    assert list(out) == ["conv"] and out["conv"].shape == (1, 32, 8, 8)
+    with pytest.raises(TpucbError):
+        m.set_tensor("x", np.zeros(7, np.float32))
+    with pytest.raises(TpucbError):
+        m.get_tensor("nope")
+    with pytest.raises(TpucbError):
+        m.load_text("frobnicate name=a shape=1,1,1,1 dtype=INT8\n", {})
+    m.close()

@@ -1,0 +1,95 @@
+"""GPU parity of the calibration path: fp32 forward statistics (min / max / abs-max, 2048-bin
+histograms) and the KLD threshold search against the reference rule run on the CPU (numpy as
+in kld_calibrator.py, the oracle's restatement of calibration_math.cpp)."""
+import numpy as np
+import pytest
+
+import oracle
+from oracle import graph_runner
+from tpu_compiler_b200 import graphs
+
+pytestmark = pytest.mark.gpu
+
+
+def small_fp32_model(batch):
+    rng = np.random.default_rng(9)
+    b = graphs.GraphBuilder(9, simulate=False)
+    b.op("input", "data", [], (batch, 3, 24, 24), "FP32")
+    b.weight("w1", rng.normal(0, 0.3, (20, 3, 3, 3))), b.weight("b1", rng.normal(0, 0.1, 20))
+    b.op("conv_2d", "c1", ["data", "w1", "b1"], (batch, 20, 24, 24), "FP32", kh=3, kw=3, pt=1, pb=1, pl=1, pr=1,
+         do_relu=1, with_bias=1)
+    b.op("pool_max_2d", "p1", ["c1"], (batch, 20, 12, 12), "FP32", kh=2, kw=2, sh=2, sw=2)
+    b.weight("w2", rng.normal(0, 0.2, (33, 20, 1, 1))), b.weight("b2", rng.normal(0, 0.1, 33))
+    b.op("conv_2d", "c2", ["p1", "w2", "b2"], (batch, 33, 12, 12), "FP32", kh=1, kw=1, do_relu=0, with_bias=1)
+    b.op("conv_2d", "dead", ["p1", "wz", None], (batch, 4, 12, 12), "FP32", kh=1, kw=1, do_relu=1, with_bias=0)
+    b.weight("wz", np.zeros((4, 20, 1, 1)))
+    return graphs.Model(b.text(), b.weights, ["data"], ["c2"])
+
+
+def test_statistics_and_thresholds_match_cpu_rule():
+    from tpu_compiler_b200 import module
+    from tpu_compiler_b200.calibration import ActivationCalibrator
+    B, nb = 4, 3
+    model = small_fp32_model(B)
+    rng = np.random.default_rng(77)
+    data = [np.clip(rng.normal(0, 1, (B, 3, 24, 24)), -3, 3).astype(np.float32) for _ in range(nb)]
+    m = module(0)
+    m.load_text(model.text, model.weights)
+    cal = ActivationCalibrator(m, lambda: iter(data))
+    thr, stats = cal.run()
+    hist_gpu = cal.histograms.cpu().numpy()
+
+    # CPU: activations from the oracle forward, statistics exactly as kld_calibrator.py computes them.
+    acts = [graph_runner.run(model.text, model.weights, {"data": d}) for d in data]
+    # the GPU forward differs from the CPU forward in the last bits of fp32 (accumulation order), so
+    # statistics are compared on the GPU's own activations as well: fetch them once more
+    for t, name in enumerate(cal.names):
+        ref_all = np.concatenate([a[name].reshape(-1) for a in acts])
+        mn, mx, ab = stats[name]
+        if name == "dead":
+            assert (mn, mx, ab) == (np.float32(-1e-5), np.float32(1e-5), np.float32(1e-5))
+            continue
+        assert abs(mn - ref_all.min()) <= 1e-4 * max(1, abs(ref_all.min()))
+        assert abs(mx - ref_all.max()) <= 1e-4 * max(1, abs(ref_all.max()))
+    # exact check of the statistics kernels: recompute from the activations the GPU itself produced
+    got_acts = {n: [] for n in cal.names}
+    for d in data:
+        m.set_tensor("data", d)
+        m.invoke()
+        for n in cal.names:
+            got_acts[n].append(m.get_tensor(n).reshape(-1))
+    for t, name in enumerate(cal.names):
+        x = np.concatenate(got_acts[name])
+        mn, mx, ab = stats[name]
+        if name == "dead":
+            continue
+        assert mn == x.min() and mx == x.max() and ab == max(abs(x.min()), abs(x.max()))
+        tt = np.abs(x)
+        tt = tt[tt != 0]
+        width = ab / (2048 - 1)
+        ref_hist, _ = np.histogram(np.floor(tt / width + 0.5), bins=2048, range=(0, 2047))
+        assert np.array_equal(hist_gpu[t], ref_hist.astype(np.int64)), name
+        assert thr[name] == oracle.kld_threshold(ref_hist.astype(np.int32), float(width)), name
+    m.close()
+
+
+def test_kld_kernel_matches_golden(golden_dir):
+    """The device KLD search reproduces the reference's own kl_diversity_hist on the golden histograms."""
+    import ctypes as C
+    import os
+    import torch
+    from tpu_compiler_b200 import module
+    from tpu_compiler_b200._lib import check, lib
+    g = np.load(os.path.join(golden_dir, "kld.npz"))
+    model = graphs.single_conv_i8(1, 16, 16, 4, 1, 1, 0, seed=1)
+    m = module(0)
+    m.load_text(model.text, model.weights)
+    hist = torch.tensor(g["hist"].astype(np.int64), device="cuda")
+    widths = np.ascontiguousarray(g["width"], np.float32)
+    thr = np.zeros(len(widths), np.float32)
+    torch.cuda.synchronize()
+    fp = C.POINTER(C.c_float)
+    check(lib().tpucb_calib_kld(m._h, C.c_void_p(hist.data_ptr()), widths.ctypes.data_as(fp), len(widths), 2048,
+                                thr.ctypes.data_as(fp)))
+    assert np.array_equal(thr, g["threshold"])
+    m.close()

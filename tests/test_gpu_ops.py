@@ -50,7 +50,11 @@ CONV_CASES = [
     (1, 256, 64, 14, 1, 2, 0, 1),     # 1x1 stride 2
     (3, 32, 48, 13, 3, 2, 1, 1),      # odd size, stride 2, ragged tiles, Cout not a multiple of 32
     (1, 16, 255, 13, 1, 1, 0, 1),     # 255-channel head
-    (1, 3, 64, 32, 7, 2, 3, 1),       # 3-channel stem: patch-expansion path
+    (1, 3, 64, 32, 7, 2, 3, 1),       # 3-channel 7x7/2 stem: row-window path
+    (2, 3, 32, 32, 3, 1, 1, 1),       # 3-channel 3x3/1 stem: row-window path, 16-byte pixels
+    (2, 3, 32, 48, 3, 2, 1, 1),       # 3-channel 3x3/2 stem (OW = 24: 8-pixel copies)
+    (1, 3, 16, 13, 3, 2, 1, 1),       # stem whose width does not suit the window copies: patch path
+    (1, 4, 32, 32, 5, 4, 2, 1),       # stride 4, 4 channels
     (1, 96, 24, 9, 3, 1, 2, 2),       # dilation 2
     (2, 144, 40, 10, 5, 1, 2, 1),     # 5x5, channels not a multiple of 64
 ]

@@ -1,0 +1,112 @@
+"""Activation calibration on device: the statistics half of the reference's
+``ActivationCalibrator`` (python/cvi_toolkit/calibration/kld_calibrator.py:204-382).
+
+Two dependent passes over the calibration images, as in the reference: (1) running min / max /
+abs-max of every op result; (2) 2048-bin |x| histograms with width abs_max / 2047; then the
+KLD threshold search (bindings/python/kld/calibration_math.cpp) per tensor. The fp32 forward
+and all three statistics run as CUDA kernels; the tensors never leave the device. With
+``torch.distributed`` initialised, every rank calibrates on its own shard of the images and
+the statistics are combined with one all-reduce(MAX) after pass 1 (abs-max, max and -min packed
+into one buffer) and one all-reduce(SUM) of the int64 histograms after pass 2.
+"""
+import ctypes as C
+import datetime
+
+import numpy as np
+import torch
+
+from ._lib import check, lib
+
+
+class ActivationCalibrator:
+    def __init__(self, model, batches, histogram_bin_num=2048, input_name=None, dist=None):
+        """model: a loaded ``tpu_compiler_b200.module`` of an fp32 graph; batches: a callable
+        returning an iterator over this rank's input batches (float32 arrays of the input's
+        shape) -- it is called twice, once per pass."""
+        self.model = model
+        self.batches = batches
+        self.bin_num = int(histogram_bin_num)
+        self.dist = dist
+        self.input_name = input_name or model.get_input_details()[0]
+        self.names = [o["name"] for o in model.op_info if o["dtype"] == "FP32"]
+        self.device = torch.device("cuda", model._device)
+        self._lib = lib()
+        self.num_samples = 0
+
+    # -- pass 1 ------------------------------------------------------------------
+    def find_min_max_abs(self):
+        T = len(self.names)
+        stats = torch.empty((T, 2), dtype=torch.float32, device=self.device)
+        stats[:, 0] = float("inf")
+        stats[:, 1] = float("-inf")
+        torch.cuda.synchronize(self.device)
+        n_img = 0
+        for batch in self.batches():
+            self.model.set_tensor(self.input_name, batch)
+            self.model.launch()
+            for t, name in enumerate(self.names):
+                check(self._lib.tpucb_calib_minmax(self.model._h, name.encode(),
+                                                   C.c_void_p(stats.data_ptr() + t * 8)))
+            n_img += batch.shape[0]
+        self.model.sync()
+        if self.dist is not None:
+            packed = torch.stack([-stats[:, 0], stats[:, 1]], dim=1).contiguous()
+            self.dist.all_reduce(packed, op=self.dist.ReduceOp.MAX)
+            stats = torch.stack([-packed[:, 0], packed[:, 1]], dim=1)
+            cnt = torch.tensor([n_img], dtype=torch.int64, device=self.device)
+            self.dist.all_reduce(cnt, op=self.dist.ReduceOp.SUM)
+            n_img = int(cnt.item())
+        self.num_samples = n_img
+        host = stats.cpu().numpy()
+        out = {}
+        for t, name in enumerate(self.names):
+            mn, mx = np.float32(host[t, 0]), np.float32(host[t, 1])
+            ab = max(abs(mn), abs(mx))
+            if ab == 0:
+                mn, mx, ab = np.float32(-1e-5), np.float32(1e-5), np.float32(1e-5)
+            out[name] = (mn, mx, np.float32(ab))
+        return out
+
+    # -- pass 2 ------------------------------------------------------------------
+    def calc_histograms(self, activations_statistics):
+        T = len(self.names)
+        hist = torch.zeros((T, self.bin_num), dtype=torch.int64, device=self.device)
+        torch.cuda.synchronize(self.device)
+        for batch in self.batches():
+            self.model.set_tensor(self.input_name, batch)
+            self.model.launch()
+            for t, name in enumerate(self.names):
+                ab = float(activations_statistics[name][2])
+                check(self._lib.tpucb_calib_hist(self.model._h, name.encode(), C.c_float(ab), self.bin_num,
+                                                 C.c_void_p(hist.data_ptr() + t * self.bin_num * 8)))
+        self.model.sync()
+        if self.dist is not None:
+            self.dist.all_reduce(hist, op=self.dist.ReduceOp.SUM)
+        return hist
+
+    def find_threshold(self, hist, activations_statistics):
+        T = len(self.names)
+        widths = np.array([np.float32(activations_statistics[n][2]) / np.float32(self.bin_num - 1) for n in self.names],
+                          np.float32)
+        thr = np.zeros(T, np.float32)
+        torch.cuda.synchronize(self.device)
+        fp = C.POINTER(C.c_float)
+        check(self._lib.tpucb_calib_kld(self.model._h, C.c_void_p(hist.data_ptr()), widths.ctypes.data_as(fp), T,
+                                        self.bin_num, thr.ctypes.data_as(fp)))
+        return {n: thr[t] for t, n in enumerate(self.names)}
+
+    def run(self, output_calibration_table=None):
+        stats = self.find_min_max_abs()
+        hist = self.calc_histograms(stats)
+        thresholds = self.find_threshold(hist, stats)
+        self.histograms = hist
+        if output_calibration_table and (self.dist is None or self.dist.get_rank() == 0):
+            with open(output_calibration_table, "w") as f:
+                f.write("# genetated time: {}\n".format(datetime.datetime.now()))
+                f.write("# histogram number: {}\n".format(self.bin_num))
+                f.write("# sample number: {}\n###\n".format(self.num_samples))
+                f.write("# op_name    threshold    min    max\n")
+                for name in self.names:
+                    mn, mx, _ = stats[name]
+                    f.write("{} {:.7f} {:.7f} {:.7f}\n".format(name, thresholds[name], mn, mx))
+        return thresholds, stats

@@ -16,8 +16,9 @@
 // reads. The epilogue adds the int32 bias, applies the per-channel
 // multiplier/rshift requantisation, saturates, applies ReLU and stores int8 NHWC.
 //
-// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA
-// issuer, warps 2..5 = epilogue (each reads the 32 TMEM lanes it may access).
+// Warp roles (320 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA
+// issuer, warps 2..9 = epilogue (two warps per TMEM lane quarter, alternating
+// 32-column groups).
 // Every wait is bounded: on expiry the CTA records an error code in p.err and
 // leaves through the common tear-down (TMEM freed, in-flight copies drained).
 #pragma once
@@ -40,7 +41,8 @@ struct ConvGemmParams {
   int ldc;        // output row pitch in bytes
   int c_off;      // first output channel written inside a row
   int stages;     // pipeline depth
-  int a_im2col;   // 1: A through im2col TMA, 0: A is a 2-D [M][K] matrix
+  int a_mode;     // 0: A is a 2-D [M][K] matrix, 1: im2col TMA, 2: row windows (stem)
+  int win_g;      // mode 2: output pixels per copy
   int act;        // 0 none, 1 ReLU, 2 leaky (non-QDM pos/neg rescale of the int8 result)
   int tmem_cols;  // power of two >= max(32, BN)
   int leaky_mp, leaky_rp, leaky_mn, leaky_rn;
@@ -98,6 +100,14 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const void *tmap, uint
       "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
       " [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst),
       "l"(tmap), "r"(bar), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const void *tmap, uint32_t bar, int x,
+                                            int y, int z, int w) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(dst),
+      "l"(tmap), "r"(bar), "r"(x), "r"(y), "r"(z), "r"(w)
       : "memory");
 }
 __device__ __forceinline__ void tma_load_im2col_4d(uint32_t dst, const void *tmap, uint32_t bar,
@@ -170,13 +180,94 @@ __device__ __forceinline__ uint64_t make_kmajor_desc(uint32_t smem_addr, int BK)
   return d;
 }
 
-constexpr int kConvThreads = 192;
+constexpr int kEpilogueWarps = 8;
+constexpr int kConvThreads = 64 + 32 * kEpilogueWarps;
 constexpr int kMaxStages = 8;
-constexpr int kSmemHeader = 4096; // barriers + staged per-channel parameters
+constexpr int kMaxBN = 256;
+constexpr int kSmemHeader = 8192; // barriers + staged per-channel parameters
 
 enum ConvErr { kErrFullWait = 1, kErrEmptyWait = 2, kErrAccWait = 3 };
 
-__global__ void __launch_bounds__(kConvThreads, 1)
+// Per-channel requantisation constants staged in shared memory. With
+//   x  = acc * M + c64,   c64 = bias * M + 2^30 (+ rnd * 2^31 on the ReLU path)
+// SaturatingRoundingDoublingHighMul(acc + bias, M) is the floor shift (x >> 31): adding
+// 2^30 and flooring equals the reference's sign-dependent nudge followed by a division
+// that truncates toward zero, for either sign. RoundingDivideByPOT (round half away from
+// zero) of hi by r is (hi + rnd) >> r for hi >= 0 and (hi + rnd - (r > 0)) >> r for hi < 0,
+// with rnd = 2^(r-1) (0 when r = 0). When ReLU follows, negative results become 0 anyway,
+// so rnd can be folded into c64 and the sign handling dropped.
+struct ChanQ {
+  int32_t M, c_lo, c_hi, r;
+};
+struct ChanR {
+  int32_t rnd, dneg; // dneg = -(r > 0)
+};
+
+__device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
+  return ((uint32_t)a & 0xffu) | (((uint32_t)b & 0xffu) << 8) | (((uint32_t)c & 0xffu) << 16) |
+         ((uint32_t)d << 24);
+}
+
+template <int ACT>
+__device__ __forceinline__ int requant_one(int32_t acc, const ChanQ &q, const ChanR &rr,
+                                           const ConvGemmParams &p) {
+  long long c64 = (long long)(((unsigned long long)(uint32_t)q.c_hi << 32) | (uint32_t)q.c_lo);
+  long long x = (long long)acc * (long long)q.M + c64;
+  int32_t hi = (int32_t)(x >> 31);
+  if (ACT == 1) {
+    int v = hi >> q.r; // rnd already folded into c64
+    return min(max(v, 0), 127);
+  }
+  int32_t sgn = hi >> 31;
+  int v = (hi + rr.rnd + (sgn & rr.dneg)) >> q.r;
+  v = min(max(v, -128), 127);
+  if (ACT == 2) {
+    if (v > 0) {
+      if (p.leaky_mp != 0) v = mul_rshift_sat8(v, p.leaky_mp, p.leaky_rp);
+    } else {
+      v = mul_rshift_sat8(v, p.leaky_mn, p.leaky_rn);
+    }
+  }
+  return v;
+}
+
+template <int ACT>
+__device__ __forceinline__ void epilogue_columns(const ConvGemmParams &p, uint32_t lane_addr,
+                                                 int8_t *orow, bool row_ok, int n0, int half,
+                                                 const ChanQ *s_q, const ChanR *s_r) {
+  // Two epilogue warps share a TMEM lane quarter; each takes alternate 32-column groups.
+  for (int col = half * 32; col < p.BN; col += 64) {
+    if (n0 + col >= p.n_valid) break;
+    const bool second = (col + 16 < p.BN) && (n0 + col + 16 < p.n_valid);
+    uint32_t acc0[16], acc1[16];
+    ptx::tcgen05_ld_x16(lane_addr + (uint32_t)col, acc0);
+    if (second) ptx::tcgen05_ld_x16(lane_addr + (uint32_t)col + 16u, acc1);
+    ptx::tcgen05_wait_ld();
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 16; j += 4) {
+      int q0 = requant_one<ACT>((int32_t)acc0[j + 0], s_q[col + j + 0], s_r[col + j + 0], p);
+      int q1 = requant_one<ACT>((int32_t)acc0[j + 1], s_q[col + j + 1], s_r[col + j + 1], p);
+      int q2 = requant_one<ACT>((int32_t)acc0[j + 2], s_q[col + j + 2], s_r[col + j + 2], p);
+      int q3 = requant_one<ACT>((int32_t)acc0[j + 3], s_q[col + j + 3], s_r[col + j + 3], p);
+      o[j >> 2] = pack4(q0, q1, q2, q3);
+    }
+    if (row_ok) *reinterpret_cast<uint4 *>(orow + col) = make_uint4(o[0], o[1], o[2], o[3]);
+    if (second) {
+#pragma unroll
+      for (int j = 0; j < 16; j += 4) {
+        int q0 = requant_one<ACT>((int32_t)acc1[j + 0], s_q[col + 16 + j + 0], s_r[col + 16 + j + 0], p);
+        int q1 = requant_one<ACT>((int32_t)acc1[j + 1], s_q[col + 16 + j + 1], s_r[col + 16 + j + 1], p);
+        int q2 = requant_one<ACT>((int32_t)acc1[j + 2], s_q[col + 16 + j + 2], s_r[col + 16 + j + 2], p);
+        int q3 = requant_one<ACT>((int32_t)acc1[j + 3], s_q[col + 16 + j + 3], s_r[col + 16 + j + 3], p);
+        o[j >> 2] = pack4(q0, q1, q2, q3);
+      }
+      if (row_ok) *reinterpret_cast<uint4 *>(orow + col + 16) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kConvThreads, 3)
 conv_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const ConvGemmParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -190,15 +281,17 @@ conv_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const uint32_t bar_acc = base + 128;       // 8 B
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + 136);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + 140);
-  int32_t *s_bias = reinterpret_cast<int32_t *>(smem + 256);
-  int32_t *s_mult = s_bias + 256;
-  int32_t *s_rsh = s_mult + 256;
+  ChanQ *s_q = reinterpret_cast<ChanQ *>(smem + 256);                 // kMaxBN x 16 B
+  ChanR *s_r = reinterpret_cast<ChanR *>(smem + 256 + kMaxBN * 16);   // kMaxBN x 8 B
   const uint32_t tiles = base + kSmemHeader;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int m0 = blockIdx.x * 128;
-  const int n0 = blockIdx.y * p.BN;
+  // n-tiles vary fastest so that CTAs sharing an activation tile run together (the tile is
+  // then fetched from HBM once and served from L2 to the others).
+  const int n_tiles = (p.n_valid + p.BN - 1) / p.BN;
+  const int m0 = (int)(blockIdx.x / n_tiles) * 128;
+  const int n0 = (int)(blockIdx.x % n_tiles) * p.BN;
   const uint32_t a_bytes = 128u * (uint32_t)p.BK;
   const uint32_t b_bytes = (uint32_t)p.BN * (uint32_t)p.BK;
   const uint32_t stage_bytes = a_bytes + b_bytes;
@@ -231,13 +324,23 @@ conv_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     // ---------------------------------------------------------------- producer
     if (lane == 0) {
       int n_img = 0, h_base = 0, w_base = 0;
-      if (p.a_im2col) {
+      if (p.a_mode == 1) {
         int q = m0 % p.OW;
         int t = m0 / p.OW;
         int pp = t % p.OH;
         n_img = t / p.OH;
         w_base = q * p.sw - p.pl;
         h_base = pp * p.sh - p.pt;
+      }
+      // mode 2: the (column, row, image) of the first pixel of each copy, computed once per tile
+      int bx_q[16], bx_h[16], bx_n[16];
+      const int n_boxes = p.a_mode == 2 ? 128 / p.win_g : 0;
+      for (int i = 0; i < n_boxes; ++i) {
+        const int m = m0 + i * p.win_g;
+        const int t = m / p.OW;
+        bx_q[i] = m - t * p.OW;
+        bx_n[i] = t / p.OH;
+        bx_h[i] = (t - bx_n[i] * p.OH) * p.sh - p.pt;
       }
       int issued = 0;
       bool ok = true;
@@ -258,10 +361,15 @@ conv_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         const uint32_t b_dst = a_dst + a_bytes;
         const uint32_t fb = bar_full + 8 * s;
         ptx::mbar_expect_tx(fb, stage_bytes);
-        if (p.a_im2col) {
+        if (p.a_mode == 1) {
           const int r = tap / p.kw, ss = tap % p.kw;
           ptx::tma_load_im2col_4d(a_dst, &tmA, fb, c0, w_base, h_base, n_img,
                                   (uint16_t)(ss * p.dw), (uint16_t)(r * p.dh));
+        } else if (p.a_mode == 2) {
+          // `tap` is the filter row; each copy brings win_g consecutive output pixels' windows.
+          for (int i = 0; i < n_boxes; ++i)
+            ptx::tma_load_4d(a_dst + (uint32_t)(i * p.win_g * p.BK), &tmA, fb, 0, bx_q[i],
+                             bx_h[i] + tap * p.dh, bx_n[i]);
         } else {
           ptx::tma_load_2d(a_dst, &tmA, fb, c0, m0);
         }
@@ -310,15 +418,24 @@ conv_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
   } else {
     // ---------------------------------------------------------------- epilogue
-    const int et = threadIdx.x - 64; // 0..127
-    for (int i = et; i < p.BN; i += 128) {
+    const int et = threadIdx.x - 64; // 0 .. 32*kEpilogueWarps-1
+    for (int i = et; i < p.BN; i += 32 * kEpilogueWarps) {
       const int n = n0 + i;
       const bool v = n < p.n_valid;
-      s_bias[i] = v ? p.bias[n] : 0;
-      s_mult[i] = v ? p.mult[n] : 0;
-      s_rsh[i] = v ? p.rshift[n] : 0;
+      const int32_t M = v ? p.mult[n] : 0;
+      const int32_t b = v ? p.bias[n] : 0;
+      const int32_t r = v ? p.rshift[n] : 0;
+      const long long rnd = r > 0 ? (1ll << (r - 1)) : 0ll;
+      long long c64 = (long long)b * (long long)M + (1ll << 30);
+      if (p.act == 1) c64 += rnd << 31;
+      s_q[i].M = M;
+      s_q[i].c_lo = (int32_t)(uint32_t)(unsigned long long)c64;
+      s_q[i].c_hi = (int32_t)(c64 >> 32);
+      s_q[i].r = r;
+      s_r[i].rnd = (int32_t)rnd;
+      s_r[i].dneg = r > 0 ? -1 : 0;
     }
-    asm volatile("bar.sync 1, 128;" ::: "memory");
+    asm volatile("bar.sync 1, %0;" ::"n"(32 * kEpilogueWarps) : "memory");
     bool ok = ptx::mbar_wait_bounded(bar_acc, 0u, abort_flag);
     if (!ok && !*abort_flag) {
       atomicExch(p.err, kErrAccWait);
@@ -328,38 +445,16 @@ conv_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     ok = __all_sync(0xffffffffu, ok);
     if (ok) {
       ptx::tcgen05_fence_after();
-      const int quarter = warp & 3; // TMEM lanes this warp may read
+      const int quarter = warp & 3;          // TMEM lanes this warp may read
+      const int half = (warp - 2) >> 2;      // which alternate column groups it takes
       const int row = quarter * 32 + lane;
       const int m = m0 + row;
       const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
       int8_t *orow = p.out + (size_t)m * p.ldc + p.c_off + n0;
-      for (int col = 0; col < p.BN; col += 16) {
-        if (n0 + col >= p.n_valid) break;
-        uint32_t acc[16];
-        ptx::tcgen05_ld_x16(lane_addr + (uint32_t)col, acc);
-        ptx::tcgen05_wait_ld();
-        uint32_t packed[4];
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          int32_t v = (int32_t)acc[j] + s_bias[col + j];
-          int q = qdm_requant(v, s_mult[col + j], s_rsh[col + j]);
-          if (p.act == 1) {
-            q = q < 0 ? 0 : q;
-          } else if (p.act == 2) {
-            if (q > 0) {
-              if (p.leaky_mp != 0) q = mul_rshift_sat8(q, p.leaky_mp, p.leaky_rp);
-            } else {
-              q = mul_rshift_sat8(q, p.leaky_mn, p.leaky_rn);
-            }
-          }
-          if ((j & 3) == 0) packed[j >> 2] = 0;
-          packed[j >> 2] |= ((uint32_t)(q & 0xff)) << (8 * (j & 3));
-        }
-        if (m < p.M_total) {
-          *reinterpret_cast<uint4 *>(orow + col) =
-              make_uint4(packed[0], packed[1], packed[2], packed[3]);
-        }
-      }
+      const bool row_ok = m < p.M_total;
+      if (p.act == 1) epilogue_columns<1>(p, lane_addr, orow, row_ok, n0, half, s_q, s_r);
+      else if (p.act == 2) epilogue_columns<2>(p, lane_addr, orow, row_ok, n0, half, s_q, s_r);
+      else epilogue_columns<0>(p, lane_addr, orow, row_ok, n0, half, s_q, s_r);
     }
   }
 

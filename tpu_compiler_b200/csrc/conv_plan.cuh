@@ -161,6 +161,55 @@ inline void encode_im2col_map(CUtensorMap *tm, const int8_t *d_in, const ConvGeo
     reinterpret_cast<uint64_t *>(tm)[1] &= ~(1ull << 21);
 }
 
+// Few-channel ("stem") convolutions: with the input stored as zero-padded NHWC rows whose pixel
+// pitch is cp = 16 / stride_w bytes, the kw taps of one filter row of one output pixel are a
+// contiguous window that starts on a 16-byte boundary, and neighbouring output pixels' windows
+// start 16 bytes apart. A 4-D tiled tensor map with OVERLAPPING strides
+//   (window byte, output column q [16 B], input row [row pitch], image)
+// then delivers g consecutive output pixels' windows per copy; K has one step per filter row.
+struct StemLayout {
+  int cp = 0;     // channel pitch of the input tensor (bytes per pixel)
+  int wl = 0;     // zero pixels on the left of each row
+  int wphys = 0;  // physical row width in pixels
+  int bk = 0;     // window bytes, rounded up to a swizzle span (32/64/128)
+  int g = 0;      // output pixels per copy: gcd(OW, 128), at least 8
+};
+
+inline int gcd_int(int a, int b) { return b == 0 ? a : gcd_int(b, a % b); }
+
+inline bool stem_layout_for(const ConvGeom &g, StemLayout *out) {
+  if (g.g != 1 || g.ins_h || g.ins_w || g.dw != 1) return false;
+  if (!(g.sw == 1 || g.sw == 2 || g.sw == 4)) return false;
+  const int cp = 16 / g.sw;
+  if (g.ic > cp || g.ic >= 16) return false;
+  const int wl = round_up(g.pl, g.sw);
+  const int win_px = (wl - g.pl) + g.kw;
+  const int wb = win_px * cp;
+  if (wb > 128) return false;
+  const int bk = wb <= 32 ? 32 : (wb <= 64 ? 64 : 128);
+  const int gg = gcd_int(g.ow, 128);
+  if (gg < 8) return false;
+  int wphys = (g.ow - 1) * g.sw + bk / cp;
+  if (wphys < wl + g.iw) wphys = wl + g.iw;
+  wphys = round_up(wphys, g.sw);
+  if (((size_t)wphys * cp) % 16 != 0) return false;
+  out->cp = cp; out->wl = wl; out->wphys = wphys; out->bk = bk; out->g = gg;
+  return true;
+}
+
+inline void encode_window_map(CUtensorMap *tm, const int8_t *d_in, const ConvGeom &g, int cp, int wphys,
+                              int BK, int gpix) {
+  const cuuint64_t row_pitch = (cuuint64_t)wphys * cp;
+  cuuint64_t dims[4] = {(cuuint64_t)BK, (cuuint64_t)g.ow, (cuuint64_t)g.ih, (cuuint64_t)g.n};
+  cuuint64_t strides[3] = {(cuuint64_t)g.sw * cp, row_pitch, row_pitch * g.ih};
+  cuuint32_t box[4] = {(cuuint32_t)BK, (cuuint32_t)gpix, 1, 1};
+  cuuint32_t es[4] = {1, 1, 1, 1};
+  CUresult r = tma_api().tiled(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, (void *)d_in, dims, strides, box, es,
+                               CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_for(BK),
+                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  TPUCB_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled(row window) failed: %d", (int)r);
+}
+
 // Build the launch plan for one GEMM-shaped problem.
 //   rows       implicit-GEMM M
 //   k_inner    K bytes per tap (padded input channels, or the whole K in matrix mode)
@@ -171,9 +220,22 @@ inline void finish_plan(ConvPlan &pl, int rows, int taps, int k_inner, int oc_pa
   p.BK = pick_bk(k_inner);
   p.c_chunks = (k_inner + p.BK - 1) / p.BK;
   const int m_tiles = (rows + 127) / 128;
-  int bn = oc_pad < 256 ? oc_pad : 256;
+  // Tile width: at most 128 columns (so that four CTAs fit one SM's 512 TMEM columns and the
+  // epilogue of one overlaps the main loop of another), the candidate with the least padding.
+  int bn = oc_pad;
+  if (oc_pad > 128) {
+    int best = 128, best_waste = 1 << 30;
+    for (int cand = 128; cand >= 64; cand -= 16) {
+      int waste = round_up(oc_pad, cand) - oc_pad;
+      if (waste < best_waste) {
+        best_waste = waste;
+        best = cand;
+      }
+    }
+    bn = best;
+  }
   // Prefer enough CTAs to cover the SMs before making tiles wide.
-  while (bn > 32 && (bn / 2) % 16 == 0 && m_tiles * ((oc_pad + bn - 1) / bn) < sm_count) bn /= 2;
+  while (bn > 32 && (bn / 2) % 16 == 0 && m_tiles * ((oc_pad + bn - 1) / bn) < 2 * sm_count) bn /= 2;
   p.BN = bn;
   p.n_valid = oc_pad;
   int cols = 32;
@@ -182,13 +244,15 @@ inline void finish_plan(ConvPlan &pl, int rows, int taps, int k_inner, int oc_pa
   p.idesc = make_idesc_i8(128, bn);
   const int k_iters = taps * p.c_chunks;
   const size_t stage_bytes = (size_t)(128 + bn) * p.BK;
-  int stages = (int)((200 * 1024) / stage_bytes);
+  // Shared memory per CTA is kept near 72 KB so that three CTAs are resident per SM.
+  int stages = (int)((64 * 1024) / stage_bytes);
+  if (stages < 2) stages = 2;
   if (stages > kMaxStages) stages = kMaxStages;
   if (stages > k_iters) stages = k_iters;
   if (stages < 1) stages = 1;
   p.stages = stages;
   pl.smem = kSmemHeader + 1024 + stages * stage_bytes;
-  pl.grid = dim3(m_tiles, (oc_pad + bn - 1) / bn, 1);
+  pl.grid = dim3((unsigned)(m_tiles * ((oc_pad + bn - 1) / bn)), 1, 1);
 }
 
 inline void launch_conv_plan(const ConvPlan &pl, cudaStream_t stream, int sm_count) {

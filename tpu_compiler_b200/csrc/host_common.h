@@ -50,10 +50,14 @@ struct DevTensor {
   int dtype = 2; // DType
   std::vector<int64_t> shape;
   int n = 1, c = 1, h = 1, w = 1, cp = 1;
+  // Physical row layout: `wl` zero pixels, the w real pixels, then zeros up to `wphys` pixels.
+  // Every tensor has wl = 0, wphys = w except the input of a few-channel stem convolution.
+  int wl = 0, wphys = 1;
   void *dev = nullptr;
   bool owns = true;
+  bool padded_rows() const { return wl != 0 || wphys != w; }
   size_t elsize() const { return dtype == 0 ? 1 : (dtype == 1 ? 2 : 4); }
-  size_t pixels() const { return (size_t)n * h * w; }
+  size_t pixels() const { return (size_t)n * h * wphys; }
   size_t bytes() const { return pixels() * cp * elsize(); }
   size_t numel() const { return (size_t)n * c * h * w; }
 };

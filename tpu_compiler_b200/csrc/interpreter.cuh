@@ -112,6 +112,12 @@ public:
     return (float *)staging;
   }
 
+  // Row layout requested for a tensor by its (sole) consumer: channel pitch and zero-padded rows.
+  struct RowLayout {
+    int cp = 0, wl = 0, wphys = 0;
+  };
+  std::map<std::string, RowLayout> layout_requests;
+
   TensorPtr make_tensor(const std::string &name, const std::vector<int64_t> &shape, int dtype) {
     auto t = std::make_shared<DevTensor>();
     t->name = name;
@@ -127,6 +133,13 @@ public:
     t->w = (int)d[3];
     int lanes = 16 / (int)t->elsize();
     t->cp = round_up(t->c, lanes);
+    t->wphys = t->w;
+    auto lr = layout_requests.find(name);
+    if (lr != layout_requests.end() && dtype == DT_I8) {
+      t->cp = lr->second.cp;
+      t->wl = lr->second.wl;
+      t->wphys = lr->second.wphys;
+    }
     TPUCB_CUDA(cudaMalloc(&t->dev, t->bytes()));
     TPUCB_CUDA(cudaMemset(t->dev, 0, t->bytes()));
     return t;
@@ -212,10 +225,18 @@ public:
     alg_bytes = (double)in->numel() * in->elsize() + (double)out->numel() * out->elsize();
   }
   void invoke(cudaStream_t s) override {
+    TPUCB_CHECK(!in_->padded_rows(), "quant %s: padded-row input is not supported", name.c_str());
+    if (kind_ == 0 && in_->dtype == DT_F32 && in_->cp == 4 && (out_->cp == 8 || out_->cp == 16)) {
+      size_t total = out_->pixels();
+      quant_input_pix_kernel<<<grid_for(total, 256, I_.sm_count), 256, 0, s>>>(
+          (const float4 *)in_->dev, out_->dev, out_->n, out_->h, out_->w, out_->c, out_->cp, out_->wl,
+          out_->wphys, scale_);
+      return;
+    }
     size_t total = out_->pixels() * out_->cp;
     quant_kernel<<<grid_for(total, 256, I_.sm_count), 256, 0, s>>>(
-        in_->dev, out_->dev, out_->pixels(), out_->c, in_->cp, out_->cp, in_->dtype, out_->dtype,
-        kind_ == 6 ? 5 : kind_, scale_);
+        in_->dev, out_->dev, (size_t)out_->n * out_->h, out_->w, out_->wl, out_->wphys, out_->c, in_->cp,
+        out_->cp, in_->dtype, out_->dtype, kind_ == 6 ? 5 : kind_, scale_);
   }
 
 private:
@@ -291,8 +312,21 @@ public:
     const bool one_by_one = g.kh == 1 && g.kw == 1 && g.sh == 1 && g.sw == 1 && g.pt == 0 && g.pl == 0 &&
                             g.oh == g.ih && g.ow == g.iw;
     const bool small_c = g.ic < 16;
-    const bool need_patch = g.g > 1 || g.ins_h || g.ins_w || (small_c && !one_by_one) ||
-                            g.pl > 127 || g.pt > 127 || (g.kw - 1) * g.dw > 255 || (g.kh - 1) * g.dh > 255;
+    StemLayout stem;
+    bool stem_ok = in->padded_rows() && stem_layout_for(g, &stem) && stem.cp == in->cp &&
+                   stem.wl == in->wl && stem.wphys == in->wphys;
+    if (stem_ok) {
+      // The window tensor map has overlapping strides; if the driver refuses to encode it, the
+      // patch-expansion path (which understands padded rows) takes over.
+      try {
+        CUtensorMap probe;
+        encode_window_map(&probe, (const int8_t *)in->dev, g, in->cp, in->wphys, stem.bk, stem.g);
+      } catch (const Error &) {
+        stem_ok = false;
+      }
+    }
+    const bool need_patch = !stem_ok && (g.g > 1 || g.ins_h || g.ins_w || (small_c && !one_by_one) || in->padded_rows() ||
+                            g.pl > 127 || g.pt > 127 || (g.kw - 1) * g.dw > 255 || (g.kh - 1) * g.dh > 255);
     const int groups = g.g;
     for (int grp = 0; grp < groups; ++grp) {
       ConvPlan pl;
@@ -311,20 +345,41 @@ public:
       int ocg_pad = groups == 1 ? oc_pad : ocg;
       TPUCB_CHECK(groups == 1 || ocg % 16 == 0, "conv %s: grouped convolution needs oc/g to be a multiple of 16",
                   op.name.c_str());
-      if (need_patch) {
+      if (stem_ok) {
+        // Row-window path: one K step per filter row; the window of (left slack + kw) pixels x
+        // cp channels is contiguous in the zero-padded NHWC rows.
+        const int BKs = stem.bk;
+        std::vector<int8_t> w((size_t)ocg_pad * g.kh * BKs, 0);
+        for (int o = 0; o < ocg; ++o)
+          for (int c = 0; c < icg; ++c)
+            for (int r = 0; r < g.kh; ++r)
+              for (int ss = 0; ss < g.kw; ++ss)
+                w[((size_t)o * g.kh + r) * BKs + (size_t)(ss + stem.wl - g.pl) * in->cp + c] =
+                    (int8_t)(int)wsrc[(((size_t)o * icg + c) * g.kh + r) * g.kw + ss];
+        const int8_t *d_w = I.upload(w);
+        p.kh = g.kh;
+        p.kw = 1;
+        p.a_mode = 2;
+        p.win_g = stem.g;
+        finish_plan(pl, rows, g.kh, BKs, ocg_pad, I.sm_count);
+        TPUCB_CHECK(p.BK == BKs && p.c_chunks == 1, "conv %s: stem tile shape mismatch", op.name.c_str());
+        encode_window_map(&pl.tmA, (const int8_t *)in->dev, g, in->cp, in->wphys, BKs, stem.g);
+        encode_weight_map(&pl.tmB, d_w, ocg_pad, g.kh, BKs, p.BK, p.BN);
+      } else if (need_patch) {
         pl.use_patch = true;
         PatchArgs &a = pl.patch;
         a.n = g.n; a.c = g.ic; a.cp = in->cp; a.ih = g.ih; a.iw = g.iw; a.oh = g.oh; a.ow = g.ow;
         a.kh = g.kh; a.kw = g.kw; a.sh = g.sh; a.sw = g.sw; a.pt = g.pt; a.pl = g.pl; a.dh = g.dh; a.dw = g.dw;
         a.ins_h = g.ins_h; a.ins_w = g.ins_w;
         a.c_first = grp * icg; a.c_count = icg;
+        a.wl = in->wl; a.wphys = in->wphys;
         a.kp = round_up(g.kh * g.kw * icg, 16);
         pl.patch_bytes = (size_t)rows * a.kp;
         pl.patch_buf = (int8_t *)I.dalloc(pl.patch_bytes);
         auto w = pack_conv_weights(wsrc, ocg, icg, g.kh, g.kw, ocg_pad, 0, true, a.kp);
         const int8_t *d_w = I.upload(w);
         p.kh = p.kw = 1;
-        p.a_im2col = 0;
+        p.a_mode = 0;
         finish_plan(pl, rows, 1, a.kp, ocg_pad, I.sm_count);
         encode_matrix_map(&pl.tmA, pl.patch_buf, rows, a.kp, a.kp, p.BK);
         encode_weight_map(&pl.tmB, d_w, ocg_pad, 1, a.kp, p.BK, p.BN);
@@ -332,7 +387,7 @@ public:
         auto w = pack_conv_weights(wsrc, ocg, icg, 1, 1, ocg_pad, in->cp, false, 0);
         const int8_t *d_w = I.upload(w);
         p.kh = p.kw = 1;
-        p.a_im2col = 0;
+        p.a_mode = 0;
         finish_plan(pl, rows, 1, in->cp, ocg_pad, I.sm_count);
         encode_matrix_map(&pl.tmA, (const int8_t *)in->dev, rows, in->cp, in->cp, p.BK);
         encode_weight_map(&pl.tmB, d_w, ocg_pad, 1, in->cp, p.BK, p.BN);
@@ -340,7 +395,7 @@ public:
         auto w = pack_conv_weights(wsrc, ocg, icg, g.kh, g.kw, ocg_pad, in->cp, false, 0);
         const int8_t *d_w = I.upload(w);
         p.kh = g.kh; p.kw = g.kw;
-        p.a_im2col = 1;
+        p.a_mode = 1;
         finish_plan(pl, rows, g.kh * g.kw, in->cp, ocg_pad, I.sm_count);
         encode_im2col_map(&pl.tmA, (const int8_t *)in->dev, g, in->cp, p.BK);
         encode_weight_map(&pl.tmB, d_w, ocg_pad, g.kh * g.kw, in->cp, p.BK, p.BN);
@@ -445,7 +500,7 @@ public:
     // The reference applies ReLU to the float before the QDM requant; with a positive
     // multiplier the two orders give the same int8 result.
     p.act = do_relu_ ? 1 : 0;
-    p.a_im2col = 0;
+    p.a_mode = 0;
     finish_plan(pl, m_, 1, kdev_, n_pad, I.sm_count);
     encode_matrix_map(&pl.tmA, (const int8_t *)in->dev, m_, kdev_, kdev_, p.BK);
     encode_weight_map(&pl.tmB, d_w, n_pad, 1, kdev_, p.BK, p.BN);
@@ -808,12 +863,50 @@ inline void Interpreter::load_module(const std::string &text) {
   output_details.clear();
   std::map<std::string, std::string> producer_type;
   std::map<std::string, int> uses;
-  std::stringstream ss(text);
-  std::string line;
-  while (std::getline(ss, line)) {
-    size_t b = line.find_first_not_of(" \t\r");
-    if (b == std::string::npos || line[b] == '#') continue;
-    ParsedOp op = parse_line(line.substr(b));
+  std::vector<ParsedOp> parsed;
+  {
+    std::stringstream ss(text);
+    std::string line;
+    while (std::getline(ss, line)) {
+      size_t b = line.find_first_not_of(" \t\r");
+      if (b == std::string::npos || line[b] == '#') continue;
+      parsed.push_back(parse_line(line.substr(b)));
+    }
+  }
+  // Pre-pass: a few-channel convolution whose input is produced by an input or quant op and has
+  // no other consumer asks for that tensor to be stored with zero-padded rows (stem path).
+  layout_requests.clear();
+  {
+    std::map<std::string, const ParsedOp *> by_name;
+    std::map<std::string, int> n_uses;
+    for (auto &op : parsed) {
+      by_name[op.name] = &op;
+      for (auto &nm : op.in) n_uses[nm]++;
+    }
+    for (auto &op : parsed) {
+      if (op.type != "conv_2d" || op.dtype != "INT8" || op.in.empty()) continue;
+      auto it = by_name.find(op.in[0]);
+      if (it == by_name.end() || n_uses[op.in[0]] != 1) continue;
+      const ParsedOp &src = *it->second;
+      if (!(src.type == "input" || src.type == "quant") || src.dtype != "INT8" || src.shape.size() != 4 ||
+          op.shape.size() != 4)
+        continue;
+      ConvGeom g;
+      g.n = (int)src.shape[0]; g.ic = (int)src.shape[1]; g.ih = (int)src.shape[2]; g.iw = (int)src.shape[3];
+      g.oc = (int)op.shape[1]; g.oh = (int)op.shape[2]; g.ow = (int)op.shape[3];
+      g.g = op.geti("g", 1); g.kh = op.geti("kh", 1); g.kw = op.geti("kw", 1); g.sh = op.geti("sh", 1);
+      g.sw = op.geti("sw", 1); g.pt = op.geti("pt", 0); g.pb = op.geti("pb", 0); g.pl = op.geti("pl", 0);
+      g.pr = op.geti("pr", 0); g.dh = op.geti("dh", 1); g.dw = op.geti("dw", 1);
+      g.ins_h = op.geti("ins_h", 0); g.ins_w = op.geti("ins_w", 0);
+      StemLayout st;
+      if (stem_layout_for(g, &st)) {
+        RowLayout rl;
+        rl.cp = st.cp; rl.wl = st.wl; rl.wphys = st.wphys;
+        layout_requests[src.name] = rl;
+      }
+    }
+  }
+  for (const ParsedOp &op : parsed) {
     TPUCB_CHECK(!tensors.count(op.name), "module text: duplicate result name '%s'", op.name.c_str());
     const int dt = dtype_from_string(op.dtype);
     auto opd = [&](size_t i) -> TensorPtr {
@@ -824,6 +917,10 @@ inline void Interpreter::load_module(const std::string &text) {
       if (tensors.count(nm)) uses[nm]++;
     std::unique_ptr<OpKernel> k;
     TensorPtr out;
+    for (size_t oi = (op.type == "conv_2d" ? 1 : 0); oi < op.in.size(); ++oi)
+      if (tensors.count(op.in[oi]))
+        TPUCB_CHECK(!tensors[op.in[oi]]->padded_rows(), "%s %s: operand %s has padded rows", op.type.c_str(),
+                    op.name.c_str(), op.in[oi].c_str());
     if (op.type == "reshape") {
       // tpu.reshape is a pure alias of its operand's storage (MlirModuleInterpreter.cpp:331-338);
       // valid on NHWC storage only when the element order is unchanged.
@@ -907,7 +1004,7 @@ inline void Interpreter::set_tensor(const std::string &name, const float *data, 
   TPUCB_CHECK(numel == t->numel(), "set_tensor %s: got %zu values, tensor has %zu", name.c_str(), numel, t->numel());
   float *stg = ensure_staging(numel * sizeof(float));
   TPUCB_CUDA(cudaMemcpyAsync(stg, data, numel * sizeof(float), cudaMemcpyHostToDevice, stream));
-  TensorGeom g{t->n, t->c, t->h, t->w, t->cp};
+  TensorGeom g{t->n, t->c, t->h, t->w, t->cp, t->wl, t->wphys};
   size_t total = t->pixels() * t->cp;
   int grid = grid_for(total, 256, sm_count);
   if (t->dtype == DT_I8) nchw_f32_to_dev_kernel<DT_I8><<<grid, 256, 0, stream>>>(stg, t->dev, g);
@@ -922,7 +1019,7 @@ inline void Interpreter::get_tensor(const std::string &name, float *out, size_t 
   TensorPtr t = tensor(name);
   TPUCB_CHECK(numel == t->numel(), "get_tensor %s: buffer has %zu values, tensor has %zu", name.c_str(), numel, t->numel());
   float *stg = ensure_staging(numel * sizeof(float));
-  TensorGeom g{t->n, t->c, t->h, t->w, t->cp};
+  TensorGeom g{t->n, t->c, t->h, t->w, t->cp, t->wl, t->wphys};
   int grid = grid_for(numel, 256, sm_count);
   if (t->dtype == DT_I8) dev_to_nchw_f32_kernel<DT_I8><<<grid, 256, 0, stream>>>(t->dev, stg, g);
   else if (t->dtype == DT_BF16) dev_to_nchw_f32_kernel<DT_BF16><<<grid, 256, 0, stream>>>(t->dev, stg, g);

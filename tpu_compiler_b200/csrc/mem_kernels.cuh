@@ -20,6 +20,7 @@ enum DType { DT_I8 = 0, DT_BF16 = 1, DT_F32 = 2 };
 
 struct TensorGeom {
   int n, c, h, w, cp; // logical NCHW extents and the padded channel pitch (elements)
+  int wl, wphys;      // physical row: wl zero pixels, w real pixels, zeros up to wphys
 };
 
 // ------------------------------------------------------------------ host boundary
@@ -28,16 +29,16 @@ struct TensorGeom {
 template <int DT>
 __global__ void nchw_f32_to_dev_kernel(const float *__restrict__ src, void *__restrict__ dst,
                                        TensorGeom g) {
-  const size_t total = (size_t)g.n * g.h * g.w * g.cp;
+  const size_t total = (size_t)g.n * g.h * g.wphys * g.cp;
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
        i += (size_t)gridDim.x * blockDim.x) {
     int c = (int)(i % g.cp);
     size_t pix = i / g.cp;
-    int x = (int)(pix % g.w);
-    size_t t = pix / g.w;
+    int x = (int)(pix % g.wphys) - g.wl;
+    size_t t = pix / g.wphys;
     int y = (int)(t % g.h);
     int b = (int)(t / g.h);
-    float v = c < g.c ? src[(((size_t)b * g.c + c) * g.h + y) * g.w + x] : 0.0f;
+    float v = (c < g.c && x >= 0 && x < g.w) ? src[(((size_t)b * g.c + c) * g.h + y) * g.w + x] : 0.0f;
     if (DT == DT_I8) reinterpret_cast<int8_t *>(dst)[i] = (int8_t)(int)v;
     else if (DT == DT_BF16) reinterpret_cast<uint16_t *>(dst)[i] = (uint16_t)(f32_bits(v) >> 16);
     else reinterpret_cast<float *>(dst)[i] = v;
@@ -58,7 +59,7 @@ __global__ void dev_to_nchw_f32_kernel(const void *__restrict__ src, float *__re
     t /= g.h;
     int c = (int)(t % g.c);
     int b = (int)(t / g.c);
-    size_t s = (((size_t)b * g.h + y) * g.w + x) * g.cp + c;
+    size_t s = (((size_t)b * g.h + y) * g.wphys + g.wl + x) * g.cp + c;
     float v;
     if (DT == DT_I8) v = (float)reinterpret_cast<const int8_t *>(src)[s];
     else if (DT == DT_BF16) v = bits_f32((uint32_t)reinterpret_cast<const uint16_t *>(src)[s] << 16);
@@ -85,16 +86,19 @@ __device__ __forceinline__ void store_from_f32(void *p, int dt, size_t i, float 
   else reinterpret_cast<float *>(p)[i] = v;
 }
 
-__global__ void quant_kernel(const void *__restrict__ src, void *__restrict__ dst, size_t pixels,
-                             int c, int cps, int cpd, int sdt, int ddt, int kind, float scale) {
-  const size_t total = pixels * (size_t)cpd;
+__global__ void quant_kernel(const void *__restrict__ src, void *__restrict__ dst, size_t rows, int w,
+                             int wl, int wphys, int c, int cps, int cpd, int sdt, int ddt, int kind,
+                             float scale) {
+  const size_t total = rows * (size_t)wphys * (size_t)cpd;
   const float sb = bf16_round(scale);
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
        i += (size_t)gridDim.x * blockDim.x) {
     int ch = (int)(i % cpd);
-    size_t pix = i / cpd;
+    size_t ppix = i / cpd;
+    int xx = (int)(ppix % wphys) - wl;
+    size_t pix = (ppix / wphys) * w + xx;
     float out = 0.0f;
-    if (ch < c) {
+    if (ch < c && xx >= 0 && xx < w) {
       float x = load_as_f32(src, sdt, pix * cps + ch);
       switch (kind) {
       case 0: {
@@ -117,6 +121,33 @@ __global__ void quant_kernel(const void *__restrict__ src, void *__restrict__ ds
       }
     }
     store_from_f32(dst, ddt, i, out);
+  }
+}
+
+// fp32 -> int8 at the graph input (kind 0) from an NHWC4 fp32 tensor (c <= 4) into an int8
+// tensor with channel pitch 8 or 16 and optionally zero-padded rows: one thread per physical
+// destination pixel, one 16-byte load and one 8/16-byte store.
+__global__ void quant_input_pix_kernel(const float4 *__restrict__ src, void *__restrict__ dst, int n,
+                                       int h, int w, int c, int cpd, int wl, int wphys, float scale) {
+  const size_t total = (size_t)n * h * wphys;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
+       i += (size_t)gridDim.x * blockDim.x) {
+    int x = (int)(i % wphys) - wl;
+    size_t row = i / wphys;
+    uint32_t lo = 0;
+    if (x >= 0 && x < w) {
+      float4 v = src[row * w + x];
+      float f[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        if (k < c) {
+          float r = fminf(fmaxf(roundf(__fmul_rn(f[k], scale)), -128.0f), 127.0f);
+          lo |= ((uint32_t)((int)r & 0xff)) << (8 * k);
+        }
+      }
+    }
+    if (cpd == 8) reinterpret_cast<uint2 *>(dst)[i] = make_uint2(lo, 0u);
+    else reinterpret_cast<uint4 *>(dst)[i] = make_uint4(lo, 0u, 0u, 0u);
   }
 }
 
@@ -302,6 +333,7 @@ struct PatchArgs {
   int n, c, cp, ih, iw, oh, ow, kh, kw, sh, sw, pt, pl, dh, dw, ins_h, ins_w;
   int c_first, c_count; // channel slice (grouped convolution)
   int kp;
+  int wl, wphys;        // physical row layout of the input
 };
 __global__ void patch_expand_i8_kernel(const int8_t *__restrict__ in, int8_t *__restrict__ out,
                                        PatchArgs a) {
@@ -324,7 +356,7 @@ __global__ void patch_expand_i8_kernel(const int8_t *__restrict__ in, int8_t *__
       int yy = y * a.sh - a.pt + r * a.dh, xx = x * a.sw - a.pl + s * a.dw;
       if (yy >= 0 && yy < ihd && xx >= 0 && xx < iwd && (yy % (a.ins_h + 1)) == 0 &&
           (xx % (a.ins_w + 1)) == 0) {
-        v = in[(((size_t)b * a.ih + yy / (a.ins_h + 1)) * a.iw + xx / (a.ins_w + 1)) * a.cp + a.c_first + c];
+        v = in[(((size_t)b * a.ih + yy / (a.ins_h + 1)) * a.wphys + a.wl + xx / (a.ins_w + 1)) * a.cp + a.c_first + c];
       }
     }
     out[i] = v;

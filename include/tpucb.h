@@ -108,6 +108,31 @@ int tpucb_calib_hist(tpucb_interp *it, const char *name, float abs_max, int bins
 int tpucb_calib_kld(tpucb_interp *it, const int64_t *d_hist, const float *widths, int count,
                     int bins, float *thresholds);
 
+/* Allocation-free variant of tpucb_calib_kld. It has no counterpart in the reference; it exists
+ * for hosts that must not allocate device memory while they work: a calibration service that
+ * sized its device memory once at start-up (this backend keeps every activation of the module
+ * resident, so the budget is usually spoken for), or a worker thread that runs the threshold
+ * search while other streams are busy and cannot afford the device-wide synchronisation and the
+ * late out-of-memory failure that cudaMalloc / cudaFree bring. The per-candidate KL values that
+ * tpucb_calib_kld keeps in a temporary device buffer live here in a fixed array inside the
+ * library's device image: TPUCB_KLD_STATIC_MAX_HISTS x 32 floats (32 KiB), held by every GPU
+ * that loads the library until the process exits.
+ *   - `device` is the CUDA ordinal the histograms live on, `stream` a cudaStream_t (NULL = the
+ *     default stream). d_hist [count][bins] int64 device counts, widths [count] host floats,
+ *     thresholds [count] host floats out: same meaning as in tpucb_calib_kld.
+ *   - count > TPUCB_KLD_STATIC_MAX_HISTS, or bins not a multiple of 128 in [128, 4096], is
+ *     refused with an error; nothing is launched.
+ *   - The first call on a device looks up the array's device address (once per device); make
+ *     that first call before any stream capture is begun on the calling thread.
+ *   - All calls share the one array, which keeps the previous call's values: the kernel
+ *     overwrites every slot it later reads, so nothing needs clearing, but two calls that
+ *     overlap on the same GPU (different streams or threads) race on it. Serialise them.
+ *   - Calls no cudaMalloc, cudaFree or other allocating routine; returns after the results are
+ *     on the host. */
+#define TPUCB_KLD_STATIC_MAX_HISTS 256
+int tpucb_calib_kld_static(int device, void *stream, const int64_t *d_hist, const float *widths,
+                           int count, int bins, float *thresholds);
+
 #ifdef __cplusplus
 }
 #endif

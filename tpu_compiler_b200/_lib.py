@@ -50,6 +50,7 @@ def _declare(lib):
         "tpucb_calib_minmax": [vp, cp, vp],
         "tpucb_calib_hist": [vp, cp, C.c_float, C.c_int, vp],
         "tpucb_calib_kld": [vp, vp, fp, C.c_int, C.c_int, fp],
+        "tpucb_calib_kld_static": [C.c_int, vp, vp, fp, C.c_int, C.c_int, fp],
     }
     for name, args in sigs.items():
         fn = getattr(lib, name)

@@ -4,6 +4,7 @@
 #include "interpreter.cuh"
 
 #include <cmath>
+#include <mutex>
 #include <string>
 
 using namespace tpucb;
@@ -339,3 +340,82 @@ int tpucb_calib_kld(tpucb_interp *it, const int64_t *d_hist, const float *widths
 }
 
 } // extern "C"
+
+// ------------------------------------------------------- allocation-free KLD threshold search
+//
+// Scratch for tpucb_calib_kld_static: the KL value of every (histogram, candidate) pair. The
+// array is part of the library's device image, so each GPU that loads the library holds these
+// 32 KiB until the process exits. In host code the name below is only a handle for the runtime;
+// the device address is obtained per device with cudaGetSymbolAddress and that pointer is what
+// the kernel receives.
+static __device__ __align__(256) float g_kld_static_scratch[TPUCB_KLD_STATIC_MAX_HISTS * 32];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float *g_kld_static_ptr[kMaxDevices] = {nullptr};
+bool g_kld_static_ready[kMaxDevices] = {false};
+std::mutex g_kld_static_mutex;
+
+// Once per device, with that device current: resolve the scratch array's device address.
+float *kld_static_setup(int device) {
+  std::lock_guard<std::mutex> lock(g_kld_static_mutex);
+  if (!g_kld_static_ready[device]) {
+    float *ptr = nullptr;
+    TPUCB_CUDA(cudaGetSymbolAddress((void **)&ptr, g_kld_static_scratch));
+    TPUCB_CHECK(ptr != nullptr, "tpucb_calib_kld_static: the scratch array has no device address");
+    g_kld_static_ptr[device] = ptr;
+    g_kld_static_ready[device] = true;
+  }
+  return g_kld_static_ptr[device];
+}
+} // namespace
+
+extern "C" int tpucb_calib_kld_static(int device, void *stream, const int64_t *d_hist, const float *widths,
+                                      int count, int bins, float *thresholds) {
+  int previous = -1;
+  bool switched = false;
+  try {
+    TPUCB_CHECK(d_hist && widths && thresholds, "tpucb_calib_kld_static: NULL argument");
+    TPUCB_CHECK(count > 0 && count <= TPUCB_KLD_STATIC_MAX_HISTS,
+                "tpucb_calib_kld_static: count %d is outside [1, %d] (the static scratch holds %d histograms' "
+                "candidates; split the call or use tpucb_calib_kld)",
+                count, TPUCB_KLD_STATIC_MAX_HISTS, TPUCB_KLD_STATIC_MAX_HISTS);
+    TPUCB_CHECK(bins % 128 == 0 && bins >= 128 && bins <= 4096,
+                "tpucb_calib_kld_static: bins must be a multiple of 128 in [128, 4096], got %d", bins);
+    TPUCB_CHECK(device >= 0 && device < kMaxDevices, "tpucb_calib_kld_static: device %d out of range", device);
+    TPUCB_CUDA(cudaGetDevice(&previous));
+    if (previous != device) {
+      TPUCB_CUDA(cudaSetDevice(device));
+      switched = true;
+    }
+    float *d_kl = kld_static_setup(device);
+    cudaStream_t st = (cudaStream_t)stream;
+    const int kl_num = bins / 128;
+    const size_t smem = (size_t)bins * (2 * sizeof(float) + sizeof(double));
+    // the dynamic shared memory limit is a per-function setting, not an allocation
+    TPUCB_CUDA(cudaFuncSetAttribute(kld_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kld_kernel<<<count * kl_num, 256, smem, st>>>((const long long *)d_hist, bins, d_kl);
+    TPUCB_CUDA(cudaGetLastError());
+    // host copy of the KL values: fixed-size, on the stack
+    float kl[TPUCB_KLD_STATIC_MAX_HISTS * 32];
+    TPUCB_CUDA(cudaMemcpyAsync(kl, d_kl, sizeof(float) * (size_t)count * kl_num, cudaMemcpyDeviceToHost, st));
+    TPUCB_CUDA(cudaStreamSynchronize(st));
+    for (int t = 0; t < count; ++t) {
+      const float *k = kl + (size_t)t * kl_num;
+      int m_min = 0;
+      float best = k[0];
+      for (int i = 1; i < kl_num; ++i)
+        if (best > k[i]) {
+          best = k[i];
+          m_min = i;
+        }
+      thresholds[t] = widths[t] * (m_min + 1) * 128;
+    }
+    if (switched) cudaSetDevice(previous);
+  } catch (const std::exception &e) {
+    if (switched) cudaSetDevice(previous);
+    g_last_error = e.what();
+    return 1;
+  }
+  return 0;
+}

@@ -55,6 +55,8 @@ CONV_CASES = [
     (2, 3, 32, 48, 3, 2, 1, 1),       # 3-channel 3x3/2 stem (OW = 24: 8-pixel copies)
     (1, 3, 16, 13, 3, 2, 1, 1),       # stem whose width does not suit the window copies: patch path
     (1, 4, 32, 32, 5, 4, 2, 1),       # stride 4, 4 channels
+    (2, 8, 32, 32, 3, 2, 1, 1),       # 8 channels, stride 2: row-window TMA path (8-byte pixels)
+    (1, 12, 48, 16, 3, 1, 1, 1),      # 12 channels, stride 1: row-window TMA path (16-byte pixels)
     (1, 96, 24, 9, 3, 1, 2, 2),       # dilation 2
     (2, 144, 40, 10, 5, 1, 2, 1),     # 5x5, channels not a multiple of 64
 ]

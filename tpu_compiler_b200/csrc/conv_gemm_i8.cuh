@@ -44,7 +44,7 @@ struct ConvGemmParams {
   int a_mode;     // 0: A is a 2-D [M][K] matrix, 1: im2col TMA, 2: row windows (stem)
   int win_g;      // mode 2: output pixels per copy
   int act;        // 0 none, 1 ReLU, 2 leaky (non-QDM pos/neg rescale of the int8 result)
-  int tmem_cols;  // power of two >= max(32, BN)
+  int tmem_cols;  // power of two >= max(32, 2 * BN): two accumulator buffers
   int leaky_mp, leaky_rp, leaky_mn, leaky_rn;
   uint32_t idesc; // tcgen05 instruction descriptor
   const int32_t *bias;   // [n_valid]
@@ -195,33 +195,44 @@ enum ConvErr { kErrFullWait = 1, kErrEmptyWait = 2, kErrAccWait = 3 };
 // that truncates toward zero, for either sign. RoundingDivideByPOT (round half away from
 // zero) of hi by r is (hi + rnd) >> r for hi >= 0 and (hi + rnd - (r > 0)) >> r for hi < 0,
 // with rnd = 2^(r-1) (0 when r = 0). When ReLU follows, negative results become 0 anyway,
-// so rnd can be folded into c64 and the sign handling dropped.
+// so rnd can be folded into c64 and the sign handling dropped. Integer instructions issue at
+// half the FP32 rate on this SM, so the chain is kept to 4-5 of them per value: one wide
+// multiply-add, one funnel shift, the rounding add, the shift and a saturating pack that
+// converts two values per instruction.
 struct ChanQ {
   int32_t M, c_lo, c_hi, r;
 };
 struct ChanR {
-  int32_t rnd, dneg; // dneg = -(r > 0)
+  int32_t rnd, s1; // s1 = 31 when r > 0, 32 when r == 0: (uint)hi >> s1 is the "negative and r > 0" bit
 };
 
-__device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
-  return ((uint32_t)a & 0xffu) | (((uint32_t)b & 0xffu) << 8) | (((uint32_t)c & 0xffu) << 16) |
-         ((uint32_t)d << 24);
+// d = {c[15:0], sat8(a), sat8(b)}: two int32 saturated to int8 and merged below the low half of c.
+__device__ __forceinline__ uint32_t pack_sat_s8(int a, int b, uint32_t c) {
+  uint32_t d;
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+// bytes (q0, q1, q2, q3) from low to high, each saturated to [-128, 127]
+__device__ __forceinline__ uint32_t pack4_sat(int q0, int q1, int q2, int q3) {
+  return pack_sat_s8(q1, q0, pack_sat_s8(q3, q2, 0u));
 }
 
+// One requantised value BEFORE the final int8 saturation (pack4_sat applies it).
 template <int ACT>
 __device__ __forceinline__ int requant_one(int32_t acc, const ChanQ &q, const ChanR &rr,
                                            const ConvGemmParams &p) {
   long long c64 = (long long)(((unsigned long long)(uint32_t)q.c_hi << 32) | (uint32_t)q.c_lo);
-  long long x = (long long)acc * (long long)q.M + c64;
-  int32_t hi = (int32_t)(x >> 31);
+  long long x;
+  asm("mad.wide.s32 %0, %1, %2, %3;" : "=l"(x) : "r"(acc), "r"(q.M), "l"(c64));
+  const int32_t hi = (int32_t)__funnelshift_r((uint32_t)x, (uint32_t)(x >> 32), 31);
   if (ACT == 1) {
-    int v = hi >> q.r; // rnd already folded into c64
-    return min(max(v, 0), 127);
+    return max(hi, 0) >> q.r; // rnd already folded into c64; the upper clamp happens in the pack
   }
-  int32_t sgn = hi >> 31;
-  int v = (hi + rr.rnd + (sgn & rr.dneg)) >> q.r;
-  v = min(max(v, -128), 127);
+  uint32_t adj;
+  asm("shr.u32 %0, %1, %2;" : "=r"(adj) : "r"((uint32_t)hi), "r"((uint32_t)rr.s1)); // shifts >= 32 give 0
+  int v = (hi + rr.rnd - (int)adj) >> q.r;
   if (ACT == 2) {
+    v = min(max(v, -128), 127);
     if (v > 0) {
       if (p.leaky_mp != 0) v = mul_rshift_sat8(v, p.leaky_mp, p.leaky_rp);
     } else {
@@ -250,7 +261,7 @@ __device__ __forceinline__ void epilogue_columns(const ConvGemmParams &p, uint32
       int q1 = requant_one<ACT>((int32_t)acc0[j + 1], s_q[col + j + 1], s_r[col + j + 1], p);
       int q2 = requant_one<ACT>((int32_t)acc0[j + 2], s_q[col + j + 2], s_r[col + j + 2], p);
       int q3 = requant_one<ACT>((int32_t)acc0[j + 3], s_q[col + j + 3], s_r[col + j + 3], p);
-      o[j >> 2] = pack4(q0, q1, q2, q3);
+      o[j >> 2] = pack4_sat(q0, q1, q2, q3);
     }
     if (row_ok) *reinterpret_cast<uint4 *>(orow + col) = make_uint4(o[0], o[1], o[2], o[3]);
     if (second) {
@@ -260,14 +271,39 @@ __device__ __forceinline__ void epilogue_columns(const ConvGemmParams &p, uint32
         int q1 = requant_one<ACT>((int32_t)acc1[j + 1], s_q[col + 16 + j + 1], s_r[col + 16 + j + 1], p);
         int q2 = requant_one<ACT>((int32_t)acc1[j + 2], s_q[col + 16 + j + 2], s_r[col + 16 + j + 2], p);
         int q3 = requant_one<ACT>((int32_t)acc1[j + 3], s_q[col + 16 + j + 3], s_r[col + 16 + j + 3], p);
-        o[j >> 2] = pack4(q0, q1, q2, q3);
+        o[j >> 2] = pack4_sat(q0, q1, q2, q3);
       }
       if (row_ok) *reinterpret_cast<uint4 *>(orow + col + 16) = make_uint4(o[0], o[1], o[2], o[3]);
     }
   }
 }
 
-__global__ void __launch_bounds__(kConvThreads, 3)
+// Stages the per-channel requantisation constants of columns [n0, n0 + BN) in shared memory.
+__device__ __forceinline__ void stage_channel_constants(const ConvGemmParams &p, int n0, int et, int nthreads,
+                                                        ChanQ *s_q, ChanR *s_r) {
+  for (int i = et; i < p.BN; i += nthreads) {
+    const int n = n0 + i;
+    const bool v = n < p.n_valid;
+    const int32_t M = v ? p.mult[n] : 0;
+    const int32_t b = v ? p.bias[n] : 0;
+    const int32_t r = v ? p.rshift[n] : 0;
+    const long long rnd = r > 0 ? (1ll << (r - 1)) : 0ll;
+    long long c64 = (long long)b * (long long)M + (1ll << 30);
+    if (p.act == 1) c64 += rnd << 31;
+    s_q[i].M = M;
+    s_q[i].c_lo = (int32_t)(uint32_t)(unsigned long long)c64;
+    s_q[i].c_hi = (int32_t)(c64 >> 32);
+    s_q[i].r = r;
+    s_r[i].rnd = (int32_t)rnd;
+    s_r[i].s1 = r > 0 ? 31 : 32;
+  }
+}
+
+// Persistent kernel: gridDim.x CTAs walk the tile list (tile = blockIdx.x + k * gridDim.x; n-tiles
+// vary fastest so that CTAs working at the same time share activation tiles through L2). The
+// producer runs ahead through the shared-memory ring across tile boundaries and the accumulator is
+// double-buffered in TMEM, so the loads and MMAs of tile i+1 overlap the epilogue of tile i.
+__global__ void __launch_bounds__(kConvThreads, 2)
 conv_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const ConvGemmParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -276,27 +312,27 @@ conv_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   uint8_t *smem = smem_raw + (base - raw);
 
   // header layout
-  const uint32_t bar_full = base;            // kMaxStages x 8 B
-  const uint32_t bar_empty = base + 64;      // kMaxStages x 8 B
-  const uint32_t bar_acc = base + 128;       // 8 B
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + 136);
-  volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + 140);
+  const uint32_t bar_full = base;             // kMaxStages x 8 B
+  const uint32_t bar_empty = base + 64;       // kMaxStages x 8 B
+  const uint32_t bar_acc_full = base + 128;   // 2 x 8 B: accumulator buffer complete
+  const uint32_t bar_acc_empty = base + 144;  // 2 x 8 B: accumulator buffer drained by the epilogue
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + 160);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + 164);
   ChanQ *s_q = reinterpret_cast<ChanQ *>(smem + 256);                 // kMaxBN x 16 B
   ChanR *s_r = reinterpret_cast<ChanR *>(smem + 256 + kMaxBN * 16);   // kMaxBN x 8 B
   const uint32_t tiles = base + kSmemHeader;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  // n-tiles vary fastest so that CTAs sharing an activation tile run together (the tile is
-  // then fetched from HBM once and served from L2 to the others).
   const int n_tiles = (p.n_valid + p.BN - 1) / p.BN;
-  const int m0 = (int)(blockIdx.x / n_tiles) * 128;
-  const int n0 = (int)(blockIdx.x % n_tiles) * p.BN;
+  const int m_tiles = (p.M_total + 127) / 128;
+  const int total_tiles = n_tiles * m_tiles;
   const uint32_t a_bytes = 128u * (uint32_t)p.BK;
   const uint32_t b_bytes = (uint32_t)p.BN * (uint32_t)p.BK;
   const uint32_t stage_bytes = a_bytes + b_bytes;
   const int taps = p.kh * p.kw;
   const int k_iters = taps * p.c_chunks;
+  const uint32_t acc_stride = (uint32_t)(p.tmem_cols >> 1); // columns per accumulator buffer
 
   // A CTA of a launch in which an earlier CTA already gave up does no work at all, so that a
   // broken launch ends quickly instead of timing out once per tile.
@@ -309,7 +345,10 @@ conv_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       ptx::mbar_init(bar_full + 8 * s, 1);
       ptx::mbar_init(bar_empty + 8 * s, 1);
     }
-    ptx::mbar_init(bar_acc, 1);
+    for (int b = 0; b < 2; ++b) {
+      ptx::mbar_init(bar_acc_full + 8 * b, 1);
+      ptx::mbar_init(bar_acc_empty + 8 * b, kEpilogueWarps);
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -323,67 +362,70 @@ conv_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   if (warp == 0) {
     // ---------------------------------------------------------------- producer
     if (lane == 0) {
-      int n_img = 0, h_base = 0, w_base = 0;
-      if (p.a_mode == 1) {
-        int q = m0 % p.OW;
-        int t = m0 / p.OW;
-        int pp = t % p.OH;
-        n_img = t / p.OH;
-        w_base = q * p.sw - p.pl;
-        h_base = pp * p.sh - p.pt;
-      }
-      // mode 2: the (column, row, image) of the first pixel of each copy, computed once per tile
-      int bx_q[16], bx_h[16], bx_n[16];
-      const int n_boxes = p.a_mode == 2 ? 128 / p.win_g : 0;
-      for (int i = 0; i < n_boxes; ++i) {
-        const int m = m0 + i * p.win_g;
-        const int t = m / p.OW;
-        bx_q[i] = m - t * p.OW;
-        bx_n[i] = t / p.OH;
-        bx_h[i] = (t - bx_n[i] * p.OH) * p.sh - p.pt;
-      }
-      int issued = 0;
+      int it = 0; // k-iterations issued so far, across tiles
       bool ok = true;
-      for (int kit = 0; kit < k_iters && ok; ++kit) {
-        const int s = kit % p.stages;
-        const uint32_t ph = (uint32_t)(kit / p.stages) & 1u;
-        if (kit >= p.stages) {
-          if (!ptx::mbar_wait_bounded(bar_empty + 8 * s, ph ^ 1u, abort_flag)) {
-            if (!*abort_flag) atomicExch(p.err, kErrEmptyWait);
-            *abort_flag = 1;
-            ok = false;
-            break;
-          }
-        }
-        const int tap = kit / p.c_chunks;
-        const int c0 = (kit % p.c_chunks) * p.BK;
-        const uint32_t a_dst = tiles + s * stage_bytes;
-        const uint32_t b_dst = a_dst + a_bytes;
-        const uint32_t fb = bar_full + 8 * s;
-        ptx::mbar_expect_tx(fb, stage_bytes);
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile / n_tiles) * 128;
+        const int n0 = (tile % n_tiles) * p.BN;
+        int n_img = 0, h_base = 0, w_base = 0;
         if (p.a_mode == 1) {
-          const int r = tap / p.kw, ss = tap % p.kw;
-          ptx::tma_load_im2col_4d(a_dst, &tmA, fb, c0, w_base, h_base, n_img,
-                                  (uint16_t)(ss * p.dw), (uint16_t)(r * p.dh));
-        } else if (p.a_mode == 2) {
-          // `tap` is the filter row; each copy brings win_g consecutive output pixels' windows.
-          for (int i = 0; i < n_boxes; ++i)
-            ptx::tma_load_4d(a_dst + (uint32_t)(i * p.win_g * p.BK), &tmA, fb, 0, bx_q[i],
-                             bx_h[i] + tap * p.dh, bx_n[i]);
-        } else {
-          ptx::tma_load_2d(a_dst, &tmA, fb, c0, m0);
+          int q = m0 % p.OW;
+          int t = m0 / p.OW;
+          int pp = t % p.OH;
+          n_img = t / p.OH;
+          w_base = q * p.sw - p.pl;
+          h_base = pp * p.sh - p.pt;
         }
-        ptx::tma_load_3d(b_dst, &tmB, fb, c0, tap, n0);
-        ++issued;
+        // mode 2: the (column, row, image) of the first pixel of each copy, computed once per tile
+        int bx_q[16], bx_h[16], bx_n[16];
+        const int n_boxes = p.a_mode == 2 ? 128 / p.win_g : 0;
+        for (int i = 0; i < n_boxes; ++i) {
+          const int m = m0 + i * p.win_g;
+          const int t = m / p.OW;
+          bx_q[i] = m - t * p.OW;
+          bx_n[i] = t / p.OH;
+          bx_h[i] = (t - bx_n[i] * p.OH) * p.sh - p.pt;
+        }
+        for (int kit = 0; kit < k_iters; ++kit, ++it) {
+          const int s = it % p.stages;
+          const uint32_t ph = (uint32_t)(it / p.stages) & 1u;
+          if (it >= p.stages) {
+            if (!ptx::mbar_wait_bounded(bar_empty + 8 * s, ph ^ 1u, abort_flag)) {
+              if (!*abort_flag) atomicExch(p.err, kErrEmptyWait);
+              *abort_flag = 1;
+              ok = false;
+              break;
+            }
+          }
+          const int tap = kit / p.c_chunks;
+          const int c0 = (kit % p.c_chunks) * p.BK;
+          const uint32_t a_dst = tiles + s * stage_bytes;
+          const uint32_t b_dst = a_dst + a_bytes;
+          const uint32_t fb = bar_full + 8 * s;
+          ptx::mbar_expect_tx(fb, stage_bytes);
+          if (p.a_mode == 1) {
+            const int r = tap / p.kw, ss = tap % p.kw;
+            ptx::tma_load_im2col_4d(a_dst, &tmA, fb, c0, w_base, h_base, n_img,
+                                    (uint16_t)(ss * p.dw), (uint16_t)(r * p.dh));
+          } else if (p.a_mode == 2) {
+            // `tap` is the filter row; each copy brings win_g consecutive output pixels' windows.
+            for (int i = 0; i < n_boxes; ++i)
+              ptx::tma_load_4d(a_dst + (uint32_t)(i * p.win_g * p.BK), &tmA, fb, 0, bx_q[i],
+                               bx_h[i] + tap * p.dh, bx_n[i]);
+          } else {
+            ptx::tma_load_2d(a_dst, &tmA, fb, c0, m0);
+          }
+          ptx::tma_load_3d(b_dst, &tmB, fb, c0, tap, n0);
+        }
       }
-      if (!ok) {
-        // Drain: wait (bounded) until every copy this thread issued has landed, so
-        // no bulk copy is in flight when the CTA's shared memory is released.
-        int first = issued > p.stages ? issued - p.stages : 0;
-        for (int kit = first; kit < issued; ++kit) {
-          const int s = kit % p.stages;
-          const uint32_t ph = (uint32_t)(kit / p.stages) & 1u;
-          for (uint32_t it = 0; it < (1u << 20); ++it)
+      if (!ok || *abort_flag) {
+        // Drain: wait (bounded) until every copy this thread issued has landed, so that no bulk
+        // copy is in flight when the CTA's shared memory is released.
+        int first = it > p.stages ? it - p.stages : 0;
+        for (int j = first; j < it; ++j) {
+          const int s = j % p.stages;
+          const uint32_t ph = (uint32_t)(j / p.stages) & 1u;
+          for (uint32_t w = 0; w < (1u << 20); ++w)
             if (ptx::mbar_try_wait(bar_full + 8 * s, ph)) break;
         }
       }
@@ -391,70 +433,87 @@ conv_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   } else if (warp == 1) {
     // -------------------------------------------------------------- MMA issuer
     if (lane == 0) {
+      int it = 0, t = 0;
       bool ok = true;
-      for (int kit = 0; kit < k_iters; ++kit) {
-        const int s = kit % p.stages;
-        const uint32_t ph = (uint32_t)(kit / p.stages) & 1u;
-        if (!ptx::mbar_wait_bounded(bar_full + 8 * s, ph, abort_flag)) {
-          if (!*abort_flag) atomicExch(p.err, kErrFullWait);
-          *abort_flag = 1;
-          ok = false;
-          break;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++t) {
+        const int buf = t & 1;
+        if (t >= 2) {
+          // the epilogue must have drained this accumulator buffer (its previous use)
+          if (!ptx::mbar_wait_bounded(bar_acc_empty + 8 * buf, (uint32_t)(((t >> 1) - 1) & 1), abort_flag)) {
+            if (!*abort_flag) atomicExch(p.err, kErrAccWait);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          ptx::tcgen05_fence_after();
         }
-        ptx::tcgen05_fence_after();
-        const uint32_t a_src = tiles + s * stage_bytes;
-        const uint32_t b_src = a_src + a_bytes;
-        const uint64_t adesc = make_kmajor_desc(a_src, p.BK);
-        const uint64_t bdesc = make_kmajor_desc(b_src, p.BK);
-        const int ksteps = p.BK / 32;
-        for (int k = 0; k < ksteps; ++k) {
-          // advance 32 bytes of K inside the swizzle span: +2 in 16-byte units
-          ptx::tcgen05_mma_i8(tmem_base, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k),
-                              p.idesc, (kit > 0 || k > 0) ? 1u : 0u);
+        const uint32_t d_tmem = tmem_base + (uint32_t)buf * acc_stride;
+        for (int kit = 0; kit < k_iters; ++kit, ++it) {
+          const int s = it % p.stages;
+          const uint32_t ph = (uint32_t)(it / p.stages) & 1u;
+          if (!ptx::mbar_wait_bounded(bar_full + 8 * s, ph, abort_flag)) {
+            if (!*abort_flag) atomicExch(p.err, kErrFullWait);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          ptx::tcgen05_fence_after();
+          const uint32_t a_src = tiles + s * stage_bytes;
+          const uint32_t b_src = a_src + a_bytes;
+          const uint64_t adesc = make_kmajor_desc(a_src, p.BK);
+          const uint64_t bdesc = make_kmajor_desc(b_src, p.BK);
+          const int ksteps = p.BK / 32;
+          for (int k = 0; k < ksteps; ++k) {
+            // advance 32 bytes of K inside the swizzle span: +2 in 16-byte units
+            ptx::tcgen05_mma_i8(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), p.idesc,
+                                (kit > 0 || k > 0) ? 1u : 0u);
+          }
+          ptx::tcgen05_commit(bar_empty + 8 * s); // frees the stage when the MMAs retire
         }
-        ptx::tcgen05_commit(bar_empty + 8 * s); // frees the stage when the MMAs retire
+        if (ok) ptx::tcgen05_commit(bar_acc_full + 8 * buf);
       }
-      if (ok) ptx::tcgen05_commit(bar_acc);
     }
   } else {
     // ---------------------------------------------------------------- epilogue
     const int et = threadIdx.x - 64; // 0 .. 32*kEpilogueWarps-1
-    for (int i = et; i < p.BN; i += 32 * kEpilogueWarps) {
-      const int n = n0 + i;
-      const bool v = n < p.n_valid;
-      const int32_t M = v ? p.mult[n] : 0;
-      const int32_t b = v ? p.bias[n] : 0;
-      const int32_t r = v ? p.rshift[n] : 0;
-      const long long rnd = r > 0 ? (1ll << (r - 1)) : 0ll;
-      long long c64 = (long long)b * (long long)M + (1ll << 30);
-      if (p.act == 1) c64 += rnd << 31;
-      s_q[i].M = M;
-      s_q[i].c_lo = (int32_t)(uint32_t)(unsigned long long)c64;
-      s_q[i].c_hi = (int32_t)(c64 >> 32);
-      s_q[i].r = r;
-      s_r[i].rnd = (int32_t)rnd;
-      s_r[i].dneg = r > 0 ? -1 : 0;
-    }
-    asm volatile("bar.sync 1, %0;" ::"n"(32 * kEpilogueWarps) : "memory");
-    bool ok = ptx::mbar_wait_bounded(bar_acc, 0u, abort_flag);
-    if (!ok && !*abort_flag) {
-      atomicExch(p.err, kErrAccWait);
-      *abort_flag = 1;
-    }
-    // the wait result may differ between lanes only on the error path; make it uniform
-    ok = __all_sync(0xffffffffu, ok);
-    if (ok) {
+    const int quarter = warp & 3;     // TMEM lanes this warp may read
+    const int half = (warp - 2) >> 2; // which alternate column groups it takes
+    const int row = quarter * 32 + lane;
+    int staged_n0 = -1;
+    int t = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++t) {
+      const int m0 = (tile / n_tiles) * 128;
+      const int n0 = (tile % n_tiles) * p.BN;
+      const int buf = t & 1;
+      if (n0 != staged_n0) {
+        // every epilogue thread is past its reads of the previous constants
+        asm volatile("bar.sync 1, %0;" ::"n"(32 * kEpilogueWarps) : "memory");
+        stage_channel_constants(p, n0, et, 32 * kEpilogueWarps, s_q, s_r);
+        asm volatile("bar.sync 1, %0;" ::"n"(32 * kEpilogueWarps) : "memory");
+        staged_n0 = n0;
+      }
+      ok = ptx::mbar_wait_bounded(bar_acc_full + 8 * buf, (uint32_t)((t >> 1) & 1), abort_flag);
+      if (!ok && !*abort_flag) {
+        atomicExch(p.err, kErrAccWait);
+        *abort_flag = 1;
+      }
+      // the wait result may differ between lanes only on the error path; make it uniform
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
       ptx::tcgen05_fence_after();
-      const int quarter = warp & 3;          // TMEM lanes this warp may read
-      const int half = (warp - 2) >> 2;      // which alternate column groups it takes
-      const int row = quarter * 32 + lane;
       const int m = m0 + row;
-      const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+      const uint32_t lane_addr = tmem_base + (uint32_t)buf * acc_stride + ((uint32_t)(quarter * 32) << 16);
       int8_t *orow = p.out + (size_t)m * p.ldc + p.c_off + n0;
       const bool row_ok = m < p.M_total;
       if (p.act == 1) epilogue_columns<1>(p, lane_addr, orow, row_ok, n0, half, s_q, s_r);
       else if (p.act == 2) epilogue_columns<2>(p, lane_addr, orow, row_ok, n0, half, s_q, s_r);
       else epilogue_columns<0>(p, lane_addr, orow, row_ok, n0, half, s_q, s_r);
+      // hand the accumulator buffer back to the MMA issuer
+      ptx::tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0)
+        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_acc_empty + 8 * buf) : "memory");
     }
   }
 

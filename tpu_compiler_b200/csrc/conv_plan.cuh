@@ -4,6 +4,7 @@
 // output size taken from the result type, dilation, optional input zero-insertion.
 #pragma once
 #include "conv_gemm_i8.cuh"
+#include "conv_stem_i8.cuh"
 #include "host_common.h"
 #include "mem_kernels.cuh"
 
@@ -210,6 +211,73 @@ inline void encode_window_map(CUtensorMap *tm, const int8_t *d_in, const ConvGeo
   TPUCB_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled(row window) failed: %d", (int)r);
 }
 
+// Thread-gathered stem convolution (conv_stem_i8_kernel): at most 4 input channels stored as one
+// 32-bit word per pixel, kw <= 8, kh <= 8, no groups / insertion / horizontal dilation.
+inline bool stem4_applies(const ConvGeom &g) {
+  return g.g == 1 && !g.ins_h && !g.ins_w && g.dw == 1 && g.ic <= 4 && g.kw <= 8 && g.kh <= 8;
+}
+
+struct StemPlan {
+  CUtensorMap tmB;
+  ConvStemParams p;
+  dim3 grid;
+  size_t smem = 0;
+};
+
+inline void stem_kernel_setup_once() {
+  static bool done = [] {
+    TPUCB_CUDA(cudaFuncSetAttribute(conv_stem_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+    return true;
+  }();
+  (void)done;
+}
+
+// weights [kh][oc_pad][32]: byte s*4 + c of filter row r
+inline std::vector<int8_t> pack_stem_weights(const float *w, int oc, int ic, int kh, int kw, int oc_pad) {
+  std::vector<int8_t> out((size_t)kh * oc_pad * 32, 0);
+  for (int o = 0; o < oc; ++o)
+    for (int c = 0; c < ic; ++c)
+      for (int r = 0; r < kh; ++r)
+        for (int s = 0; s < kw; ++s)
+          out[((size_t)r * oc_pad + o) * 32 + s * 4 + c] = (int8_t)(int)w[(((size_t)o * ic + c) * kh + r) * kw + s];
+  return out;
+}
+
+inline void finish_stem_plan(StemPlan &sp, const int8_t *d_w, int rows, int kh, int oc_pad) {
+  ConvStemParams &p = sp.p;
+  int bn = oc_pad;
+  if (oc_pad > 128) {
+    int best = 128, best_waste = 1 << 30;
+    for (int cand = 128; cand >= 64; cand -= 16) {
+      int waste = round_up(oc_pad, cand) - oc_pad;
+      if (waste < best_waste) {
+        best_waste = waste;
+        best = cand;
+      }
+    }
+    bn = best;
+  }
+  p.BN = bn;
+  p.n_valid = oc_pad;
+  int cols = 32;
+  while (cols < bn) cols *= 2;
+  p.tmem_cols = cols;
+  p.idesc = make_idesc_i8(128, bn);
+  p.M_total = rows;
+  p.kh = kh;
+  sp.smem = kSmemHeader + 1024 + (size_t)kh * (4096 + (size_t)bn * 32);
+  const int m_tiles = (rows + 127) / 128;
+  sp.grid = dim3((unsigned)(m_tiles * ((oc_pad + bn - 1) / bn)), 1, 1);
+  cuuint64_t dims[3] = {32, (cuuint64_t)oc_pad, (cuuint64_t)kh};
+  cuuint64_t strides[2] = {32, (cuuint64_t)32 * oc_pad};
+  cuuint32_t box[3] = {32, (cuuint32_t)bn, (cuuint32_t)kh};
+  cuuint32_t es[3] = {1, 1, 1};
+  CUresult r = tma_api().tiled(&sp.tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, (void *)d_w, dims, strides, box, es,
+                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_32B,
+                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  TPUCB_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled(stem weights) failed: %d", (int)r);
+}
+
 // Build the launch plan for one GEMM-shaped problem.
 //   rows       implicit-GEMM M
 //   k_inner    K bytes per tap (padded input channels, or the whole K in matrix mode)
@@ -238,21 +306,28 @@ inline void finish_plan(ConvPlan &pl, int rows, int taps, int k_inner, int oc_pa
   while (bn > 32 && (bn / 2) % 16 == 0 && m_tiles * ((oc_pad + bn - 1) / bn) < 2 * sm_count) bn /= 2;
   p.BN = bn;
   p.n_valid = oc_pad;
+  // two accumulator buffers, each a power-of-two number of columns >= BN
   int cols = 32;
   while (cols < bn) cols *= 2;
-  p.tmem_cols = cols;
+  p.tmem_cols = 2 * cols;
   p.idesc = make_idesc_i8(128, bn);
   const int k_iters = taps * p.c_chunks;
   const size_t stage_bytes = (size_t)(128 + bn) * p.BK;
-  // Shared memory per CTA is kept near 72 KB so that three CTAs are resident per SM.
-  int stages = (int)((64 * 1024) / stage_bytes);
+  // Persistent CTAs, two per SM: about 100 KB of shared memory each. The ring may hold several
+  // tiles' worth of operands so that the producer prefetches across tile boundaries.
+  int stages = (int)((96 * 1024) / stage_bytes);
   if (stages < 2) stages = 2;
   if (stages > kMaxStages) stages = kMaxStages;
-  if (stages > k_iters) stages = k_iters;
+  const int n_tiles = (oc_pad + bn - 1) / bn;
+  const long long total_tiles = (long long)m_tiles * n_tiles;
+  int grid = 2 * sm_count;
+  if (grid > total_tiles) grid = (int)total_tiles;
+  const long long iters_per_cta = ((total_tiles + grid - 1) / grid) * k_iters;
+  if (stages > iters_per_cta) stages = (int)iters_per_cta;
   if (stages < 1) stages = 1;
   p.stages = stages;
   pl.smem = kSmemHeader + 1024 + stages * stage_bytes;
-  pl.grid = dim3((unsigned)(m_tiles * ((oc_pad + bn - 1) / bn)), 1, 1);
+  pl.grid = dim3((unsigned)grid, 1, 1);
 }
 
 inline void launch_conv_plan(const ConvPlan &pl, cudaStream_t stream, int sm_count) {

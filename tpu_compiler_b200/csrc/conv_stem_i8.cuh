@@ -1,0 +1,168 @@
+// INT8 convolution for stems with at most 4 input channels (the 3-channel first layer of
+// ResNet / MobileNet / Darknet), same arithmetic as conv_gemm_i8_kernel (core/conv.cpp:80-104 of
+// the reference followed by the per-channel requantisation of QuantizationArithmetic.cpp:849-871).
+//
+// With 3 channels an im2col TMA row would be 16 bytes, far too small for the TMA unit to be
+// efficient, so here the A tile is built by CUDA threads: the input is stored with a 4-byte pixel
+// (NHWC4), each of 128 threads owns one output pixel, gathers its kh x kw pixel words with bounds
+// checks (zero padding) and writes them as kh rows of 32 bytes (kw <= 8 taps x 4 channels) into
+// shared memory in the 32-byte-swizzled K-major layout the tensor core reads; a proxy fence hands
+// the tile to tcgen05.mma (one K=32 step per filter row). Weights [kh][Cout_pad][32] arrive by one
+// TMA copy. The same 128 threads then run the epilogue for the TMEM lane that matches their pixel.
+// Small footprint (kh x (128 + BN) x 32 B of shared memory) so that several CTAs share an SM and
+// overlap gather, MMA and epilogue.
+#pragma once
+#include "conv_gemm_i8.cuh"
+
+namespace tpucb {
+
+struct ConvStemParams {
+  int M_total, OH, OW, H, W;
+  int sh, sw, pt, pl, dh;
+  int kh, kw;
+  int BN, n_valid, ldc, c_off, act, tmem_cols;
+  int leaky_mp, leaky_rp, leaky_mn, leaky_rn;
+  uint32_t idesc;
+  const uint32_t *in; // NHWC4 int8, one 32-bit word per pixel
+  const int32_t *bias, *mult, *rshift;
+  int8_t *out;
+  int *err;
+};
+
+constexpr int kStemThreads = 160;
+
+__global__ void __launch_bounds__(kStemThreads, 4)
+conv_stem_i8_kernel(const __grid_constant__ CUtensorMap tmB, const ConvStemParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = ptx::smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t *smem = smem_raw + (base - raw);
+
+  const uint32_t bar_a = base;        // A tile written (128 arrivals)
+  const uint32_t bar_b = base + 8;    // weights landed (TMA)
+  const uint32_t bar_acc = base + 16; // accumulator complete
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + 24);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + 28);
+  ChanQ *s_q = reinterpret_cast<ChanQ *>(smem + 256);
+  ChanR *s_r = reinterpret_cast<ChanR *>(smem + 256 + kMaxBN * 16);
+  const uint32_t a_tiles = base + kSmemHeader;             // kh x 4096 B
+  const uint32_t b_tiles = a_tiles + (uint32_t)p.kh * 4096u; // kh x BN x 32 B
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_tiles = (p.n_valid + p.BN - 1) / p.BN;
+  const int m0 = (int)(blockIdx.x / n_tiles) * 128;
+  const int n0 = (int)(blockIdx.x % n_tiles) * p.BN;
+  ConvGemmParams ep; // the shared epilogue reads these fields
+  ep.BN = p.BN; ep.n_valid = p.n_valid; ep.act = p.act;
+  ep.mult = p.mult; ep.bias = p.bias; ep.rshift = p.rshift;
+  ep.leaky_mp = p.leaky_mp; ep.leaky_rp = p.leaky_rp; ep.leaky_mn = p.leaky_mn; ep.leaky_rn = p.leaky_rn;
+
+  if (threadIdx.x == 0) *abort_flag = *reinterpret_cast<volatile int *>(p.err);
+  __syncthreads();
+  if (*abort_flag != 0) return;
+
+  if (threadIdx.x == 0) {
+    ptx::mbar_init(bar_a, 128);
+    ptx::mbar_init(bar_b, 1);
+    ptx::mbar_init(bar_acc, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) ptx::tcgen05_alloc(ptx::smem_u32(tmem_slot), (uint32_t)p.tmem_cols);
+  ptx::tcgen05_fence_before();
+  __syncthreads();
+  ptx::tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      const uint32_t b_bytes = (uint32_t)p.kh * (uint32_t)p.BN * 32u;
+      ptx::mbar_expect_tx(bar_b, b_bytes);
+      ptx::tma_load_3d(b_tiles, &tmB, bar_b, 0, n0, 0);
+      bool ok = ptx::mbar_wait_bounded(bar_b, 0u, abort_flag);
+      if (!ok) {
+        // the copy is still owed: wait for it (bounded) before the CTA may release shared memory
+        for (uint32_t it = 0; it < (1u << 20); ++it)
+          if (ptx::mbar_try_wait(bar_b, 0u)) break;
+      }
+      ok = ok && ptx::mbar_wait_bounded(bar_a, 0u, abort_flag);
+      if (ok) {
+        ptx::tcgen05_fence_after();
+        for (int r = 0; r < p.kh; ++r) {
+          const uint64_t adesc = make_kmajor_desc(a_tiles + (uint32_t)r * 4096u, 32);
+          const uint64_t bdesc = make_kmajor_desc(b_tiles + (uint32_t)r * (uint32_t)p.BN * 32u, 32);
+          ptx::tcgen05_mma_i8(tmem_base, adesc, bdesc, p.idesc, r > 0 ? 1u : 0u);
+        }
+        ptx::tcgen05_commit(bar_acc);
+      } else {
+        if (!*abort_flag) atomicExch(p.err, kErrFullWait);
+        *abort_flag = 1;
+      }
+    }
+  } else {
+    const int et = threadIdx.x - 32; // 0..127
+    stage_channel_constants(ep, n0, et, 128, s_q, s_r);
+    // ---- gather this thread's pixel: TMEM lane quarter = warp % 4
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const int m = m0 + row;
+    const bool row_ok = m < p.M_total;
+    int q = 0, pp = 0, nimg = 0;
+    if (row_ok) {
+      const int t = m / p.OW;
+      q = m - t * p.OW;
+      nimg = t / p.OH;
+      pp = t - nimg * p.OH;
+    }
+    const int x0 = q * p.sw - p.pl;
+    const int y0 = pp * p.sh - p.pt;
+    const uint32_t sw_bit = (uint32_t)((row >> 2) & 1); // 32-byte swizzle: 16-byte chunk ^= address bit 7
+    uint8_t *a_row = smem + kSmemHeader + row * 32;
+    for (int r = 0; r < p.kh; ++r) {
+      uint32_t w[8];
+#pragma unroll
+      for (int s = 0; s < 8; ++s) w[s] = 0u;
+      const int y = y0 + r * p.dh;
+      if (row_ok && y >= 0 && y < p.H) {
+        const uint32_t *src = p.in + ((size_t)nimg * p.H + y) * p.W;
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+          const int x = x0 + s;
+          if (s < p.kw && x >= 0 && x < p.W) w[s] = __ldg(src + x);
+        }
+      }
+      uint4 *dst = reinterpret_cast<uint4 *>(a_row + (size_t)r * 4096);
+      dst[0 ^ sw_bit] = make_uint4(w[0], w[1], w[2], w[3]);
+      dst[1 ^ sw_bit] = make_uint4(w[4], w[5], w[6], w[7]);
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory"); // the staged per-channel constants are complete
+    // make the generic-proxy writes visible to the tensor core (async proxy), then signal
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_a) : "memory");
+
+    bool ok = ptx::mbar_wait_bounded(bar_acc, 0u, abort_flag);
+    if (!ok && !*abort_flag) {
+      atomicExch(p.err, kErrAccWait);
+      *abort_flag = 1;
+    }
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok) {
+      ptx::tcgen05_fence_after();
+      const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+      int8_t *orow = p.out + (size_t)m * p.ldc + p.c_off + n0;
+      for (int half = 0; half < 2; ++half) {
+        if (p.act == 1) epilogue_columns<1>(ep, lane_addr, orow, row_ok, n0, half, s_q, s_r);
+        else if (p.act == 2) epilogue_columns<2>(ep, lane_addr, orow, row_ok, n0, half, s_q, s_r);
+        else epilogue_columns<0>(ep, lane_addr, orow, row_ok, n0, half, s_q, s_r);
+      }
+    }
+  }
+
+  ptx::tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    ptx::tcgen05_fence_after();
+    ptx::tcgen05_dealloc(tmem_base, (uint32_t)p.tmem_cols);
+  }
+}
+
+} // namespace tpucb

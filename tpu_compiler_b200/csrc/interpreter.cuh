@@ -226,7 +226,7 @@ public:
   }
   void invoke(cudaStream_t s) override {
     TPUCB_CHECK(!in_->padded_rows(), "quant %s: padded-row input is not supported", name.c_str());
-    if (kind_ == 0 && in_->dtype == DT_F32 && in_->cp == 4 && (out_->cp == 8 || out_->cp == 16)) {
+    if (kind_ == 0 && in_->dtype == DT_F32 && in_->cp == 4 && (out_->cp == 4 || out_->cp == 8 || out_->cp == 16)) {
       size_t total = out_->pixels();
       quant_input_pix_kernel<<<grid_for(total, 256, I_.sm_count), 256, 0, s>>>(
           (const float4 *)in_->dev, out_->dev, out_->n, out_->h, out_->w, out_->c, out_->cp, out_->wl,
@@ -308,6 +308,26 @@ public:
       return;
     }
 
+    if (in->cp == 4 && !in->padded_rows() && stem4_applies(g)) {
+      stem_kernel_setup_once();
+      StemPlan sp;
+      std::memset(&sp.p, 0, sizeof(sp.p));
+      ConvStemParams &p = sp.p;
+      p.OH = g.oh; p.OW = g.ow; p.H = g.ih; p.W = g.iw;
+      p.sh = g.sh; p.sw = g.sw; p.pt = g.pt; p.pl = g.pl; p.dh = g.dh; p.kw = g.kw;
+      p.act = act_;
+      p.in = (const uint32_t *)in->dev;
+      p.bias = d_bias_; p.mult = d_mult_; p.rshift = d_rsh_;
+      p.out = (int8_t *)out->dev;
+      p.ldc = out->cp;
+      p.c_off = 0;
+      p.err = I.d_err;
+      const int8_t *d_w = I.upload(pack_stem_weights(filt.data.data(), g.oc, g.ic, g.kh, g.kw, oc_pad));
+      finish_stem_plan(sp, d_w, g.n * g.oh * g.ow, g.kh, oc_pad);
+      stem_plans_.push_back(sp);
+      return;
+    }
+
     conv_kernel_setup_once();
     const bool one_by_one = g.kh == 1 && g.kw == 1 && g.sh == 1 && g.sw == 1 && g.pt == 0 && g.pl == 0 &&
                             g.oh == g.ih && g.ow == g.iw;
@@ -325,7 +345,7 @@ public:
         stem_ok = false;
       }
     }
-    const bool need_patch = !stem_ok && (g.g > 1 || g.ins_h || g.ins_w || (small_c && !one_by_one) || in->padded_rows() ||
+    const bool need_patch = !stem_ok && (g.g > 1 || g.ins_h || g.ins_w || (small_c && !one_by_one) || in->padded_rows() || in->cp % 16 != 0 ||
                             g.pl > 127 || g.pt > 127 || (g.kw - 1) * g.dw > 255 || (g.kh - 1) * g.dh > 255);
     const int groups = g.g;
     for (int grp = 0; grp < groups; ++grp) {
@@ -404,6 +424,10 @@ public:
     }
   }
   void set_leaky(int mp, int rp, int mn, int rn) {
+    for (auto &sp : stem_plans_) {
+      sp.p.act = 2;
+      sp.p.leaky_mp = mp; sp.p.leaky_rp = rp; sp.p.leaky_mn = mn; sp.p.leaky_rn = rn;
+    }
     for (auto &pl : plans_) {
       pl.p.act = 2;
       pl.p.leaky_mp = mp; pl.p.leaky_rp = rp; pl.p.leaky_mn = mn; pl.p.leaky_rn = rn;
@@ -418,17 +442,20 @@ public:
       dwconv_i8_kernel<<<grid_for(total, 128, I_.sm_count), 128, 0, s>>>((const int8_t *)in_->dev,
                                                                           (int8_t *)out_->dev, dwargs_);
     } else {
+      for (auto &sp : stem_plans_)
+        conv_stem_i8_kernel<<<sp.grid, kStemThreads, sp.smem, s>>>(sp.tmB, sp.p);
       for (auto &pl : plans_) launch_conv_plan(pl, s, I_.sm_count);
     }
   }
   int kernel_launches() const override {
     if (f32_ || dw_) return 1;
-    int k = 0;
+    int k = (int)stem_plans_.size();
     for (auto &pl : plans_) k += pl.use_patch ? 2 : 1;
     return k;
   }
   bool is_tensor_core() const { return !f32_ && !dw_; }
   std::vector<ConvPlan> plans_;
+  std::vector<StemPlan> stem_plans_;
 
 private:
   Interpreter &I_;
@@ -899,7 +926,11 @@ inline void Interpreter::load_module(const std::string &text) {
       g.pr = op.geti("pr", 0); g.dh = op.geti("dh", 1); g.dw = op.geti("dw", 1);
       g.ins_h = op.geti("ins_h", 0); g.ins_w = op.geti("ins_w", 0);
       StemLayout st;
-      if (stem_layout_for(g, &st)) {
+      if (stem4_applies(g)) {
+        RowLayout rl;
+        rl.cp = 4; rl.wl = 0; rl.wphys = g.iw;
+        layout_requests[src.name] = rl;
+      } else if (stem_layout_for(g, &st)) {
         RowLayout rl;
         rl.cp = st.cp; rl.wl = st.wl; rl.wphys = st.wphys;
         layout_requests[src.name] = rl;

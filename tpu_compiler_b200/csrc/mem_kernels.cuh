@@ -125,7 +125,7 @@ __global__ void quant_kernel(const void *__restrict__ src, void *__restrict__ ds
 }
 
 // fp32 -> int8 at the graph input (kind 0) from an NHWC4 fp32 tensor (c <= 4) into an int8
-// tensor with channel pitch 8 or 16 and optionally zero-padded rows: one thread per physical
+// tensor with channel pitch 4, 8 or 16 and optionally zero-padded rows: one thread per physical
 // destination pixel, one 16-byte load and one 8/16-byte store.
 __global__ void quant_input_pix_kernel(const float4 *__restrict__ src, void *__restrict__ dst, int n,
                                        int h, int w, int c, int cpd, int wl, int wphys, float scale) {
@@ -146,7 +146,8 @@ __global__ void quant_input_pix_kernel(const float4 *__restrict__ src, void *__r
         }
       }
     }
-    if (cpd == 8) reinterpret_cast<uint2 *>(dst)[i] = make_uint2(lo, 0u);
+    if (cpd == 4) reinterpret_cast<uint32_t *>(dst)[i] = lo;
+    else if (cpd == 8) reinterpret_cast<uint2 *>(dst)[i] = make_uint2(lo, 0u);
     else reinterpret_cast<uint4 *>(dst)[i] = make_uint4(lo, 0u, 0u, 0u);
   }
 }

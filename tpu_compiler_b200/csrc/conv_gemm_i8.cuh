@@ -6,15 +6,18 @@
 // lib/Dialect/TPU/Quantization/QuantizationArithmetic.cpp:849-871) and
 // FullyConnectedOpKernel::invoke (core/fullyconnected.cpp:44-91).
 //
-// D[M=128 output pixels][N<=256 output channels] is accumulated in int32 in
-// tensor memory by tcgen05.mma kind::i8; the A tile (activations, NHWC int8) is
-// fetched either by an im2col-mode TMA load (any kh/kw/stride/dilation/padding;
-// out-of-image taps arrive as zeros) or by a plain 2-D tiled TMA load (1x1
-// stride-1 convolutions, fully-connected, pre-expanded patch matrices); the B
-// tile (weights, [Cout][tap][Cin] int8) by a 3-D tiled TMA load. Tiles land in
-// shared memory in the 32/64/128-byte swizzled K-major layout the tensor core
-// reads. The epilogue adds the int32 bias, applies the per-channel
-// multiplier/rshift requantisation, saturates, applies ReLU and stores int8 NHWC.
+// The product is computed transposed, D[128 output channels][128 output pixels]: the weight
+// tile ([Cout][tap][Cin] int8, 3-D tiled TMA load) is the tensor core's A operand and the
+// activation tile its B operand, fetched either by an im2col-mode TMA load (any kh/kw/
+// stride/dilation/padding; out-of-image taps arrive as zeros) or by a plain 2-D tiled TMA
+// load (1x1 stride-1 convolutions, fully-connected, pre-expanded patch matrices). Tiles land
+// in shared memory in the 32/64/128-byte swizzled K-major layout the tensor core reads and
+// accumulate in int32 in tensor memory (tcgen05.mma kind::i8). With channels on the TMEM
+// lanes every epilogue thread owns ONE output channel, so its bias / multiplier / rshift
+// constants sit in registers instead of being re-read per value; the epilogue requantises,
+// saturates, applies ReLU, transposes 4 channels x 4 pixels between neighbouring lanes with
+// byte permutes and two shuffles, and stores 4 channels of one pixel per lane (a warp
+// writes whole 32-byte sectors of the NHWC output).
 //
 // Warp roles (320 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA
 // issuer, warps 2..9 = epilogue (two warps per TMEM lane quarter, alternating
@@ -36,7 +39,7 @@ struct ConvGemmParams {
   int kh, kw;     // filter size (taps = kh*kw; 1 in tiled mode)
   int c_chunks;   // ceil(Cin_pad / BK)
   int BK;         // K bytes per pipeline stage: 32, 64 or 128 (= swizzle span)
-  int BN;         // tile width in output channels, multiple of 16, <= 256
+  int BN;         // channel tile = tensor-core M, always 128 (rows past n_valid are zero-filled)
   int n_valid;    // number of valid (padded) output channels
   int ldc;        // output row pitch in bytes
   int c_off;      // first output channel written inside a row
@@ -44,7 +47,7 @@ struct ConvGemmParams {
   int a_mode;     // 0: A is a 2-D [M][K] matrix, 1: im2col TMA, 2: row windows (stem)
   int win_g;      // mode 2: output pixels per copy
   int act;        // 0 none, 1 ReLU, 2 leaky (non-QDM pos/neg rescale of the int8 result)
-  int tmem_cols;  // power of two >= max(32, 2 * BN): two accumulator buffers
+  int tmem_cols;  // 256: two accumulator buffers of 128 pixel columns
   int leaky_mp, leaky_rp, leaky_mn, leaky_rn;
   uint32_t idesc; // tcgen05 instruction descriptor
   const int32_t *bias;   // [n_valid]
@@ -188,7 +191,8 @@ constexpr int kSmemHeader = 8192; // barriers + staged per-channel parameters
 
 enum ConvErr { kErrFullWait = 1, kErrEmptyWait = 2, kErrAccWait = 3 };
 
-// Per-channel requantisation constants staged in shared memory. With
+// Per-channel requantisation constants, held in registers by the thread that owns the channel.
+// With
 //   x  = acc * M + c64,   c64 = bias * M + 2^30 (+ rnd * 2^31 on the ReLU path)
 // SaturatingRoundingDoublingHighMul(acc + bias, M) is the floor shift (x >> 31): adding
 // 2^30 and flooring equals the reference's sign-dependent nudge followed by a division
@@ -199,12 +203,24 @@ enum ConvErr { kErrFullWait = 1, kErrEmptyWait = 2, kErrAccWait = 3 };
 // half the FP32 rate on this SM, so the chain is kept to 4-5 of them per value: one wide
 // multiply-add, one funnel shift, the rounding add, the shift and a saturating pack that
 // converts two values per instruction.
-struct ChanQ {
-  int32_t M, c_lo, c_hi, r;
+struct ChanConst {
+  int32_t M, r, rnd, s1; // s1 = 31 when r > 0, 32 when r == 0: (uint)hi >> s1 is the "negative and r > 0" bit
+  long long c64;
 };
-struct ChanR {
-  int32_t rnd, s1; // s1 = 31 when r > 0, 32 when r == 0: (uint)hi >> s1 is the "negative and r > 0" bit
-};
+
+__device__ __forceinline__ ChanConst load_chan_const(const ConvGemmParams &p, int n) {
+  ChanConst c;
+  const bool v = n < p.n_valid;
+  c.M = v ? p.mult[n] : 0;
+  const int32_t b = v ? p.bias[n] : 0;
+  c.r = v ? p.rshift[n] : 0;
+  const long long rnd = c.r > 0 ? (1ll << (c.r - 1)) : 0ll;
+  c.c64 = (long long)b * (long long)c.M + (1ll << 30);
+  if (p.act == 1) c.c64 += rnd << 31;
+  c.rnd = (int32_t)rnd;
+  c.s1 = c.r > 0 ? 31 : 32;
+  return c;
+}
 
 // d = {c[15:0], sat8(a), sat8(b)}: two int32 saturated to int8 and merged below the low half of c.
 __device__ __forceinline__ uint32_t pack_sat_s8(int a, int b, uint32_t c) {
@@ -219,18 +235,16 @@ __device__ __forceinline__ uint32_t pack4_sat(int q0, int q1, int q2, int q3) {
 
 // One requantised value BEFORE the final int8 saturation (pack4_sat applies it).
 template <int ACT>
-__device__ __forceinline__ int requant_one(int32_t acc, const ChanQ &q, const ChanR &rr,
-                                           const ConvGemmParams &p) {
-  long long c64 = (long long)(((unsigned long long)(uint32_t)q.c_hi << 32) | (uint32_t)q.c_lo);
+__device__ __forceinline__ int requant_one(int32_t acc, const ChanConst &q, const ConvGemmParams &p) {
   long long x;
-  asm("mad.wide.s32 %0, %1, %2, %3;" : "=l"(x) : "r"(acc), "r"(q.M), "l"(c64));
+  asm("mad.wide.s32 %0, %1, %2, %3;" : "=l"(x) : "r"(acc), "r"(q.M), "l"(q.c64));
   const int32_t hi = (int32_t)__funnelshift_r((uint32_t)x, (uint32_t)(x >> 32), 31);
   if (ACT == 1) {
     return max(hi, 0) >> q.r; // rnd already folded into c64; the upper clamp happens in the pack
   }
   uint32_t adj;
-  asm("shr.u32 %0, %1, %2;" : "=r"(adj) : "r"((uint32_t)hi), "r"((uint32_t)rr.s1)); // shifts >= 32 give 0
-  int v = (hi + rr.rnd - (int)adj) >> q.r;
+  asm("shr.u32 %0, %1, %2;" : "=r"(adj) : "r"((uint32_t)hi), "r"((uint32_t)q.s1)); // shifts >= 32 give 0
+  int v = (hi + q.rnd - (int)adj) >> q.r;
   if (ACT == 2) {
     v = min(max(v, -128), 127);
     if (v > 0) {
@@ -242,60 +256,59 @@ __device__ __forceinline__ int requant_one(int32_t acc, const ChanQ &q, const Ch
   return v;
 }
 
-template <int ACT>
-__device__ __forceinline__ void epilogue_columns(const ConvGemmParams &p, uint32_t lane_addr,
-                                                 int8_t *orow, bool row_ok, int n0, int half,
-                                                 const ChanQ *s_q, const ChanR *s_r) {
-  // Two epilogue warps share a TMEM lane quarter; each takes alternate 32-column groups.
-  for (int col = half * 32; col < p.BN; col += 64) {
-    if (n0 + col >= p.n_valid) break;
-    const bool second = (col + 16 < p.BN) && (n0 + col + 16 < p.n_valid);
-    uint32_t acc0[16], acc1[16];
-    ptx::tcgen05_ld_x16(lane_addr + (uint32_t)col, acc0);
-    if (second) ptx::tcgen05_ld_x16(lane_addr + (uint32_t)col + 16u, acc1);
-    ptx::tcgen05_wait_ld();
-    uint32_t o[4];
-#pragma unroll
-    for (int j = 0; j < 16; j += 4) {
-      int q0 = requant_one<ACT>((int32_t)acc0[j + 0], s_q[col + j + 0], s_r[col + j + 0], p);
-      int q1 = requant_one<ACT>((int32_t)acc0[j + 1], s_q[col + j + 1], s_r[col + j + 1], p);
-      int q2 = requant_one<ACT>((int32_t)acc0[j + 2], s_q[col + j + 2], s_r[col + j + 2], p);
-      int q3 = requant_one<ACT>((int32_t)acc0[j + 3], s_q[col + j + 3], s_r[col + j + 3], p);
-      o[j >> 2] = pack4_sat(q0, q1, q2, q3);
-    }
-    if (row_ok) *reinterpret_cast<uint4 *>(orow + col) = make_uint4(o[0], o[1], o[2], o[3]);
-    if (second) {
-#pragma unroll
-      for (int j = 0; j < 16; j += 4) {
-        int q0 = requant_one<ACT>((int32_t)acc1[j + 0], s_q[col + 16 + j + 0], s_r[col + 16 + j + 0], p);
-        int q1 = requant_one<ACT>((int32_t)acc1[j + 1], s_q[col + 16 + j + 1], s_r[col + 16 + j + 1], p);
-        int q2 = requant_one<ACT>((int32_t)acc1[j + 2], s_q[col + 16 + j + 2], s_r[col + 16 + j + 2], p);
-        int q3 = requant_one<ACT>((int32_t)acc1[j + 3], s_q[col + 16 + j + 3], s_r[col + 16 + j + 3], p);
-        o[j >> 2] = pack4_sat(q0, q1, q2, q3);
-      }
-      if (row_ok) *reinterpret_cast<uint4 *>(orow + col + 16) = make_uint4(o[0], o[1], o[2], o[3]);
-    }
-  }
+// Byte-permute selectors of the 4x4 transpose between the four lanes of a group (lane & 3).
+struct TransposeSel {
+  uint32_t send1, merge1, send2, merge2;
+};
+__device__ __forceinline__ TransposeSel make_transpose_sel(int lane) {
+  TransposeSel t;
+  const bool b0 = lane & 1, b1 = lane & 2;
+  t.send1 = b0 ? 0x4420u : 0x4431u;
+  t.merge1 = b0 ? 0x3514u : 0x5240u;
+  t.send2 = b1 ? 0x4410u : 0x4432u;
+  t.merge2 = b1 ? 0x3254u : 0x5410u;
+  return t;
+}
+// In: lane i of a 4-lane group holds bytes (pixel 0..3) of channel i. Out: lane j holds bytes
+// (channel 0..3) of pixel j.
+__device__ __forceinline__ uint32_t transpose4x4(uint32_t w, const TransposeSel &t) {
+  uint32_t s1 = __byte_perm(w, 0u, t.send1);
+  uint32_t r1 = __shfl_xor_sync(0xffffffffu, s1, 1);
+  uint32_t z = __byte_perm(w, r1, t.merge1);
+  uint32_t s2 = __byte_perm(z, 0u, t.send2);
+  uint32_t r2 = __shfl_xor_sync(0xffffffffu, s2, 2);
+  return __byte_perm(z, r2, t.merge2);
 }
 
-// Stages the per-channel requantisation constants of columns [n0, n0 + BN) in shared memory.
-__device__ __forceinline__ void stage_channel_constants(const ConvGemmParams &p, int n0, int et, int nthreads,
-                                                        ChanQ *s_q, ChanR *s_r) {
-  for (int i = et; i < p.BN; i += nthreads) {
-    const int n = n0 + i;
-    const bool v = n < p.n_valid;
-    const int32_t M = v ? p.mult[n] : 0;
-    const int32_t b = v ? p.bias[n] : 0;
-    const int32_t r = v ? p.rshift[n] : 0;
-    const long long rnd = r > 0 ? (1ll << (r - 1)) : 0ll;
-    long long c64 = (long long)b * (long long)M + (1ll << 30);
-    if (p.act == 1) c64 += rnd << 31;
-    s_q[i].M = M;
-    s_q[i].c_lo = (int32_t)(uint32_t)(unsigned long long)c64;
-    s_q[i].c_hi = (int32_t)(c64 >> 32);
-    s_q[i].r = r;
-    s_r[i].rnd = (int32_t)rnd;
-    s_r[i].s1 = r > 0 ? 31 : 32;
+// Epilogue of one accumulator buffer for the 32 channels (TMEM lanes) of this warp.
+//   lane_addr  TMEM address of the warp's lane quarter in the buffer
+//   out4       output address of (pixel m0, this lane's 4-channel group)
+//   ch4_ok     the 4-channel group lies inside the valid channels
+template <int ACT>
+__device__ __forceinline__ void epilogue_channels(const ConvGemmParams &p, uint32_t lane_addr, int8_t *out4,
+                                                  bool ch4_ok, int m0, int half, int halves, int lane,
+                                                  const ChanConst &cc, const TransposeSel &ts) {
+  const int pj = lane & 3;
+  for (int colg = half * 32; colg < 128; colg += 32 * halves) {
+    if (m0 + colg >= p.M_total) break;
+    uint32_t acc0[16], acc1[16];
+    ptx::tcgen05_ld_x16(lane_addr + (uint32_t)colg, acc0);
+    ptx::tcgen05_ld_x16(lane_addr + (uint32_t)colg + 16u, acc1);
+    ptx::tcgen05_wait_ld();
+    uint32_t w[8];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      w[k] = pack4_sat(requant_one<ACT>((int32_t)acc0[4 * k + 0], cc, p), requant_one<ACT>((int32_t)acc0[4 * k + 1], cc, p),
+                       requant_one<ACT>((int32_t)acc0[4 * k + 2], cc, p), requant_one<ACT>((int32_t)acc0[4 * k + 3], cc, p));
+      w[4 + k] = pack4_sat(requant_one<ACT>((int32_t)acc1[4 * k + 0], cc, p), requant_one<ACT>((int32_t)acc1[4 * k + 1], cc, p),
+                           requant_one<ACT>((int32_t)acc1[4 * k + 2], cc, p), requant_one<ACT>((int32_t)acc1[4 * k + 3], cc, p));
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const uint32_t y = transpose4x4(w[k], ts);
+      const int pix = colg + 4 * k + pj;
+      if (ch4_ok && m0 + pix < p.M_total) *reinterpret_cast<uint32_t *>(out4 + (size_t)pix * p.ldc) = y;
+    }
   }
 }
 
@@ -318,8 +331,6 @@ conv_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const uint32_t bar_acc_empty = base + 144;  // 2 x 8 B: accumulator buffer drained by the epilogue
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + 160);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + 164);
-  ChanQ *s_q = reinterpret_cast<ChanQ *>(smem + 256);                 // kMaxBN x 16 B
-  ChanR *s_r = reinterpret_cast<ChanR *>(smem + 256 + kMaxBN * 16);   // kMaxBN x 8 B
   const uint32_t tiles = base + kSmemHeader;
 
   const int warp = threadIdx.x >> 5;
@@ -460,8 +471,9 @@ conv_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           ptx::tcgen05_fence_after();
           const uint32_t a_src = tiles + s * stage_bytes;
           const uint32_t b_src = a_src + a_bytes;
-          const uint64_t adesc = make_kmajor_desc(a_src, p.BK);
-          const uint64_t bdesc = make_kmajor_desc(b_src, p.BK);
+          // transposed product: weights are the A operand (M = channels), activations B (N = pixels)
+          const uint64_t adesc = make_kmajor_desc(b_src, p.BK);
+          const uint64_t bdesc = make_kmajor_desc(a_src, p.BK);
           const int ksteps = p.BK / 32;
           for (int k = 0; k < ksteps; ++k) {
             // advance 32 bytes of K inside the swizzle span: +2 in 16-byte units
@@ -475,10 +487,10 @@ conv_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     }
   } else {
     // ---------------------------------------------------------------- epilogue
-    const int et = threadIdx.x - 64; // 0 .. 32*kEpilogueWarps-1
-    const int quarter = warp & 3;     // TMEM lanes this warp may read
-    const int half = (warp - 2) >> 2; // which alternate column groups it takes
-    const int row = quarter * 32 + lane;
+    const int quarter = warp & 3;     // TMEM lanes (= channels of the tile) this warp may read
+    const int half = (warp - 2) >> 2; // which alternate 32-pixel column groups it takes
+    const TransposeSel ts = make_transpose_sel(lane);
+    ChanConst cc;
     int staged_n0 = -1;
     int t = 0;
     bool ok = true;
@@ -487,10 +499,7 @@ conv_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const int n0 = (tile % n_tiles) * p.BN;
       const int buf = t & 1;
       if (n0 != staged_n0) {
-        // every epilogue thread is past its reads of the previous constants
-        asm volatile("bar.sync 1, %0;" ::"n"(32 * kEpilogueWarps) : "memory");
-        stage_channel_constants(p, n0, et, 32 * kEpilogueWarps, s_q, s_r);
-        asm volatile("bar.sync 1, %0;" ::"n"(32 * kEpilogueWarps) : "memory");
+        cc = load_chan_const(p, n0 + quarter * 32 + lane);
         staged_n0 = n0;
       }
       ok = ptx::mbar_wait_bounded(bar_acc_full + 8 * buf, (uint32_t)((t >> 1) & 1), abort_flag);
@@ -502,13 +511,15 @@ conv_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       ptx::tcgen05_fence_after();
-      const int m = m0 + row;
-      const uint32_t lane_addr = tmem_base + (uint32_t)buf * acc_stride + ((uint32_t)(quarter * 32) << 16);
-      int8_t *orow = p.out + (size_t)m * p.ldc + p.c_off + n0;
-      const bool row_ok = m < p.M_total;
-      if (p.act == 1) epilogue_columns<1>(p, lane_addr, orow, row_ok, n0, half, s_q, s_r);
-      else if (p.act == 2) epilogue_columns<2>(p, lane_addr, orow, row_ok, n0, half, s_q, s_r);
-      else epilogue_columns<0>(p, lane_addr, orow, row_ok, n0, half, s_q, s_r);
+      const int ch4 = n0 + quarter * 32 + (lane >> 2) * 4;
+      if (n0 + quarter * 32 < p.n_valid) { // warp-uniform: this lane quarter holds real channels
+        const uint32_t lane_addr = tmem_base + (uint32_t)buf * acc_stride + ((uint32_t)(quarter * 32) << 16);
+        int8_t *out4 = p.out + (size_t)m0 * p.ldc + p.c_off + ch4;
+        const bool ch4_ok = ch4 < p.n_valid;
+        if (p.act == 1) epilogue_channels<1>(p, lane_addr, out4, ch4_ok, m0, half, 2, lane, cc, ts);
+        else if (p.act == 2) epilogue_channels<2>(p, lane_addr, out4, ch4_ok, m0, half, 2, lane, cc, ts);
+        else epilogue_channels<0>(p, lane_addr, out4, ch4_ok, m0, half, 2, lane, cc, ts);
+      }
       // hand the accumulator buffer back to the MMA issuer
       ptx::tcgen05_fence_before();
       __syncwarp();

@@ -245,23 +245,10 @@ inline std::vector<int8_t> pack_stem_weights(const float *w, int oc, int ic, int
 
 inline void finish_stem_plan(StemPlan &sp, const int8_t *d_w, int rows, int kh, int oc_pad) {
   ConvStemParams &p = sp.p;
-  int bn = oc_pad;
-  if (oc_pad > 128) {
-    int best = 128, best_waste = 1 << 30;
-    for (int cand = 128; cand >= 64; cand -= 16) {
-      int waste = round_up(oc_pad, cand) - oc_pad;
-      if (waste < best_waste) {
-        best_waste = waste;
-        best = cand;
-      }
-    }
-    bn = best;
-  }
+  const int bn = 128; // channel tile = tensor-core M; rows past oc_pad are zero-filled by TMA
   p.BN = bn;
   p.n_valid = oc_pad;
-  int cols = 32;
-  while (cols < bn) cols *= 2;
-  p.tmem_cols = cols;
+  p.tmem_cols = 128;
   p.idesc = make_idesc_i8(128, bn);
   p.M_total = rows;
   p.kh = kh;
@@ -288,28 +275,13 @@ inline void finish_plan(ConvPlan &pl, int rows, int taps, int k_inner, int oc_pa
   p.BK = pick_bk(k_inner);
   p.c_chunks = (k_inner + p.BK - 1) / p.BK;
   const int m_tiles = (rows + 127) / 128;
-  // Tile width: at most 128 columns (so that four CTAs fit one SM's 512 TMEM columns and the
-  // epilogue of one overlaps the main loop of another), the candidate with the least padding.
-  int bn = oc_pad;
-  if (oc_pad > 128) {
-    int best = 128, best_waste = 1 << 30;
-    for (int cand = 128; cand >= 64; cand -= 16) {
-      int waste = round_up(oc_pad, cand) - oc_pad;
-      if (waste < best_waste) {
-        best_waste = waste;
-        best = cand;
-      }
-    }
-    bn = best;
-  }
-  // Prefer enough CTAs to cover the SMs before making tiles wide.
-  while (bn > 32 && (bn / 2) % 16 == 0 && m_tiles * ((oc_pad + bn - 1) / bn) < 2 * sm_count) bn /= 2;
+  // Transposed product: the channel tile is the tensor core's M (128 TMEM lanes, rows past the
+  // padded channel count are zero-filled by TMA), the pixel tile its N (128 TMEM columns), and
+  // the accumulator is double-buffered: 256 TMEM columns.
+  const int bn = 128;
   p.BN = bn;
   p.n_valid = oc_pad;
-  // two accumulator buffers, each a power-of-two number of columns >= BN
-  int cols = 32;
-  while (cols < bn) cols *= 2;
-  p.tmem_cols = 2 * cols;
+  p.tmem_cols = 256;
   p.idesc = make_idesc_i8(128, bn);
   const int k_iters = taps * p.c_chunks;
   const size_t stage_bytes = (size_t)(128 + bn) * p.BK;

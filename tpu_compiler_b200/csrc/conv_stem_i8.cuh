@@ -43,8 +43,6 @@ conv_stem_i8_kernel(const __grid_constant__ CUtensorMap tmB, const ConvStemParam
   const uint32_t bar_acc = base + 16; // accumulator complete
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + 24);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + 28);
-  ChanQ *s_q = reinterpret_cast<ChanQ *>(smem + 256);
-  ChanR *s_r = reinterpret_cast<ChanR *>(smem + 256 + kMaxBN * 16);
   const uint32_t a_tiles = base + kSmemHeader;             // kh x 4096 B
   const uint32_t b_tiles = a_tiles + (uint32_t)p.kh * 4096u; // kh x BN x 32 B
 
@@ -53,7 +51,7 @@ conv_stem_i8_kernel(const __grid_constant__ CUtensorMap tmB, const ConvStemParam
   const int m0 = (int)(blockIdx.x / n_tiles) * 128;
   const int n0 = (int)(blockIdx.x % n_tiles) * p.BN;
   ConvGemmParams ep; // the shared epilogue reads these fields
-  ep.BN = p.BN; ep.n_valid = p.n_valid; ep.act = p.act;
+  ep.BN = p.BN; ep.n_valid = p.n_valid; ep.act = p.act; ep.M_total = p.M_total; ep.ldc = p.ldc;
   ep.mult = p.mult; ep.bias = p.bias; ep.rshift = p.rshift;
   ep.leaky_mp = p.leaky_mp; ep.leaky_rp = p.leaky_rp; ep.leaky_mn = p.leaky_mn; ep.leaky_rn = p.leaky_rn;
 
@@ -88,8 +86,9 @@ conv_stem_i8_kernel(const __grid_constant__ CUtensorMap tmB, const ConvStemParam
       if (ok) {
         ptx::tcgen05_fence_after();
         for (int r = 0; r < p.kh; ++r) {
-          const uint64_t adesc = make_kmajor_desc(a_tiles + (uint32_t)r * 4096u, 32);
-          const uint64_t bdesc = make_kmajor_desc(b_tiles + (uint32_t)r * (uint32_t)p.BN * 32u, 32);
+          // transposed product: weights are the A operand (M = channels), the gathered pixels B
+          const uint64_t adesc = make_kmajor_desc(b_tiles + (uint32_t)r * (uint32_t)p.BN * 32u, 32);
+          const uint64_t bdesc = make_kmajor_desc(a_tiles + (uint32_t)r * 4096u, 32);
           ptx::tcgen05_mma_i8(tmem_base, adesc, bdesc, p.idesc, r > 0 ? 1u : 0u);
         }
         ptx::tcgen05_commit(bar_acc);
@@ -99,8 +98,6 @@ conv_stem_i8_kernel(const __grid_constant__ CUtensorMap tmB, const ConvStemParam
       }
     }
   } else {
-    const int et = threadIdx.x - 32; // 0..127
-    stage_channel_constants(ep, n0, et, 128, s_q, s_r);
     // ---- gather this thread's pixel: TMEM lane quarter = warp % 4
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
@@ -134,7 +131,6 @@ conv_stem_i8_kernel(const __grid_constant__ CUtensorMap tmB, const ConvStemParam
       dst[0 ^ sw_bit] = make_uint4(w[0], w[1], w[2], w[3]);
       dst[1 ^ sw_bit] = make_uint4(w[4], w[5], w[6], w[7]);
     }
-    asm volatile("bar.sync 1, 128;" ::: "memory"); // the staged per-channel constants are complete
     // make the generic-proxy writes visible to the tensor core (async proxy), then signal
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_a) : "memory");
@@ -147,12 +143,17 @@ conv_stem_i8_kernel(const __grid_constant__ CUtensorMap tmB, const ConvStemParam
     ok = __all_sync(0xffffffffu, ok);
     if (ok) {
       ptx::tcgen05_fence_after();
-      const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-      int8_t *orow = p.out + (size_t)m * p.ldc + p.c_off + n0;
-      for (int half = 0; half < 2; ++half) {
-        if (p.act == 1) epilogue_columns<1>(ep, lane_addr, orow, row_ok, n0, half, s_q, s_r);
-        else if (p.act == 2) epilogue_columns<2>(ep, lane_addr, orow, row_ok, n0, half, s_q, s_r);
-        else epilogue_columns<0>(ep, lane_addr, orow, row_ok, n0, half, s_q, s_r);
+      // this thread's TMEM lane is now an output CHANNEL of the tile
+      const ChanConst cc = load_chan_const(ep, n0 + quarter * 32 + lane);
+      const TransposeSel ts = make_transpose_sel(lane);
+      const int ch4 = n0 + quarter * 32 + (lane >> 2) * 4;
+      if (n0 + quarter * 32 < p.n_valid) {
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        int8_t *out4 = p.out + (size_t)m0 * p.ldc + p.c_off + ch4;
+        const bool ch4_ok = ch4 < p.n_valid;
+        if (p.act == 1) epilogue_channels<1>(ep, lane_addr, out4, ch4_ok, m0, 0, 1, lane, cc, ts);
+        else if (p.act == 2) epilogue_channels<2>(ep, lane_addr, out4, ch4_ok, m0, 0, 1, lane, cc, ts);
+        else epilogue_channels<0>(ep, lane_addr, out4, ch4_ok, m0, 0, 1, lane, cc, ts);
       }
     }
   }

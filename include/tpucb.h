@@ -53,6 +53,11 @@ int tpucb_interp_load_module(tpucb_interp *it, const char *module_text);
 
 /* MlirModuleInterpreter::setTensor (MlirModuleInterpreter.cpp:407-417). */
 int tpucb_interp_set_tensor(tpucb_interp *it, const char *name, const float *data, size_t numel);
+/* Pipelined setTensor for serving loops (no reference counterpart): the copy from PINNED host
+ * memory runs on a second stream and overlaps a module launch that is still executing; the data
+ * becomes the tensor's value for the next launch. The host buffer must stay untouched until
+ * the next tpucb_interp_sync / invoke / get_tensor. */
+int tpucb_interp_set_tensor_async(tpucb_interp *it, const char *name, const float *pinned, size_t numel);
 /* MlirModuleInterpreter::invoke / invokeTo (MlirModuleInterpreter.cpp:371-381); an empty or
  * NULL name runs the whole module. Synchronous, like the reference. */
 int tpucb_interp_invoke(tpucb_interp *it);

@@ -30,6 +30,7 @@ def _declare(lib):
         "tpucb_interp_set_weight": [vp, cp, fp, i64p, C.c_int],
         "tpucb_interp_load_module": [vp, cp],
         "tpucb_interp_set_tensor": [vp, cp, fp, sz],
+        "tpucb_interp_set_tensor_async": [vp, cp, fp, sz],
         "tpucb_interp_invoke": [vp],
         "tpucb_interp_invoke_to": [vp, cp],
         "tpucb_interp_launch": [vp],

@@ -72,6 +72,11 @@ public:
                 device, prop.major, prop.minor);
     sm_count = prop.multiProcessorCount;
     TPUCB_CUDA(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
+    TPUCB_CUDA(cudaStreamCreateWithFlags(&copy_stream, cudaStreamNonBlocking));
+    for (int i = 0; i < 2; ++i) {
+      TPUCB_CUDA(cudaEventCreateWithFlags(&upload_done[i], cudaEventDisableTiming));
+      TPUCB_CUDA(cudaEventCreateWithFlags(&staging_free[i], cudaEventDisableTiming));
+    }
     TPUCB_CUDA(cudaMalloc(&d_err, sizeof(int)));
     TPUCB_CUDA(cudaMemset(d_err, 0, sizeof(int)));
   }
@@ -84,7 +89,13 @@ public:
       if (kv.second->owns && kv.second->dev) cudaFree(kv.second->dev);
     for (void *p : allocations) cudaFree(p);
     if (staging) cudaFree(staging);
+    for (int i = 0; i < 2; ++i) {
+      if (async_staging[i]) cudaFree(async_staging[i]);
+      cudaEventDestroy(upload_done[i]);
+      cudaEventDestroy(staging_free[i]);
+    }
     cudaFree(d_err);
+    cudaStreamDestroy(copy_stream);
     cudaStreamDestroy(stream);
   }
 
@@ -186,6 +197,14 @@ public:
   std::vector<void *> allocations;
   void *staging = nullptr;
   size_t staging_bytes = 0;
+  // asynchronous uploads: host -> staging on the copy stream, staging -> tensor on the compute stream
+  cudaStream_t copy_stream = nullptr;
+  void *async_staging[2] = {nullptr, nullptr};
+  size_t async_staging_bytes[2] = {0, 0};
+  cudaEvent_t upload_done[2], staging_free[2];
+  bool staging_used[2] = {false, false};
+  int async_next = 0;
+  void set_tensor_async(const std::string &name, const float *pinned, size_t numel);
 };
 
 // =========================================================================== op kernels
@@ -1042,6 +1061,43 @@ inline void Interpreter::set_tensor(const std::string &name, const float *data, 
   else if (t->dtype == DT_BF16) nchw_f32_to_dev_kernel<DT_BF16><<<grid, 256, 0, stream>>>(stg, t->dev, g);
   else nchw_f32_to_dev_kernel<DT_F32><<<grid, 256, 0, stream>>>(stg, t->dev, g);
   TPUCB_CUDA(cudaGetLastError());
+}
+
+// Pipelined form of setTensor for serving loops: the host-to-device copy runs on a second stream
+// into one of two staging buffers, so it overlaps the module launch that is still executing; the
+// (short) layout conversion into the tensor is ordered on the compute stream behind that launch
+// and behind the copy. `pinned` must stay valid until the next sync.
+inline void Interpreter::set_tensor_async(const std::string &name, const float *pinned, size_t numel) {
+  bind();
+  TensorPtr t = tensor(name);
+  TPUCB_CHECK(numel == t->numel(), "set_tensor_async %s: got %zu values, tensor has %zu", name.c_str(), numel,
+              t->numel());
+  const int k = async_next;
+  async_next ^= 1;
+  const size_t bytes = numel * sizeof(float);
+  if (bytes > async_staging_bytes[k]) {
+    TPUCB_CUDA(cudaStreamSynchronize(stream));
+    TPUCB_CUDA(cudaStreamSynchronize(copy_stream));
+    if (async_staging[k]) cudaFree(async_staging[k]);
+    TPUCB_CUDA(cudaMalloc(&async_staging[k], bytes));
+    async_staging_bytes[k] = bytes;
+    staging_used[k] = false;
+  }
+  // the previous conversion out of this staging buffer must have finished
+  if (staging_used[k]) TPUCB_CUDA(cudaStreamWaitEvent(copy_stream, staging_free[k], 0));
+  TPUCB_CUDA(cudaMemcpyAsync(async_staging[k], pinned, bytes, cudaMemcpyHostToDevice, copy_stream));
+  TPUCB_CUDA(cudaEventRecord(upload_done[k], copy_stream));
+  TPUCB_CUDA(cudaStreamWaitEvent(stream, upload_done[k], 0));
+  TensorGeom g{t->n, t->c, t->h, t->w, t->cp, t->wl, t->wphys};
+  size_t total = t->pixels() * t->cp;
+  int grid = grid_for(total, 256, sm_count);
+  const float *stg = (const float *)async_staging[k];
+  if (t->dtype == DT_I8) nchw_f32_to_dev_kernel<DT_I8><<<grid, 256, 0, stream>>>(stg, t->dev, g);
+  else if (t->dtype == DT_BF16) nchw_f32_to_dev_kernel<DT_BF16><<<grid, 256, 0, stream>>>(stg, t->dev, g);
+  else nchw_f32_to_dev_kernel<DT_F32><<<grid, 256, 0, stream>>>(stg, t->dev, g);
+  TPUCB_CUDA(cudaGetLastError());
+  TPUCB_CUDA(cudaEventRecord(staging_free[k], stream));
+  staging_used[k] = true;
 }
 
 // getTensor (MlirModuleInterpreter.cpp:419-427): deep copy out as fp32 NCHW.

@@ -91,6 +91,13 @@ int tpucb_interp_set_tensor(tpucb_interp *it, const char *name, const float *dat
   TPUCB_API_END
 }
 
+int tpucb_interp_set_tensor_async(tpucb_interp *it, const char *name, const float *pinned, size_t numel) {
+  TPUCB_API_BEGIN
+  TPUCB_CHECK(it && name && pinned, "tpucb_interp_set_tensor_async: bad argument");
+  it->impl.set_tensor_async(name, pinned, numel);
+  TPUCB_API_END
+}
+
 int tpucb_interp_invoke(tpucb_interp *it) {
   TPUCB_API_BEGIN
   TPUCB_CHECK(it, "tpucb_interp_invoke: bad argument");

@@ -79,6 +79,10 @@ class module:
         """Same as set_tensor, from a raw (e.g. pinned) host pointer."""
         check(self._lib.tpucb_interp_set_tensor(self._h, name.encode(), C.cast(host_ptr, _f), numel))
 
+    def set_tensor_async(self, name, host_ptr, numel):
+        """Pipelined set_tensor from PINNED host memory: the copy overlaps the launch in flight."""
+        check(self._lib.tpucb_interp_set_tensor_async(self._h, name.encode(), C.cast(host_ptr, _f), numel))
+
     def get_tensor_shape(self, name):
         shape = (C.c_int64 * 8)()
         rank = C.c_int(0)

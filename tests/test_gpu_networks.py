@@ -1,0 +1,58 @@
+"""GPU parity of whole MobileNet-v2 (depthwise / pointwise / residual adds) and YOLOv4-style (BF16 mish
+tables between INT8 convolutions, leaky-ReLU, SPP max-pools, upsample, concat, 255-channel heads)
+modules at reduced resolution, every tensor against the CPU oracle. INT8 and BF16 exactly."""
+import numpy as np
+import pytest
+
+from oracle import graph_runner
+from tpu_compiler_b200 import graphs
+
+pytestmark = pytest.mark.gpu
+
+
+def check_all_tensors(model, data):
+    from tpu_compiler_b200 import module
+    ref = graph_runner.run(model.text, model.weights, {"data": data})
+    m = module(0)
+    m.load_text(model.text, model.weights)
+    m.set_tensor("data", data)
+    m.invoke()
+    bad = None
+    for name in m.get_all_tensor_names():
+        got = m.get_tensor(name).reshape(-1)
+        exp = ref[name].reshape(-1)
+        if not np.array_equal(got, exp):
+            bad = (name, int((got != exp).sum()), got.size)
+            break
+    m.close()
+    assert bad is None, "first mismatching op: %s (%d of %d values)" % bad
+
+
+def test_mobilenet_v2_every_tensor():
+    model = graphs.mobilenet_v2_int8(batch=3, res=96, seed=3001)
+    data = np.random.default_rng(31).uniform(-1, 1, (3, 3, 96, 96)).astype(np.float32)
+    check_all_tensors(model, data)
+
+
+def test_yolov4_style_every_tensor():
+    model = graphs.yolov4_style_int8(batch=2, res=64, width=0.25, depth=(1, 1, 2, 2, 1), seed=4001)
+    data = np.random.default_rng(41).uniform(0, 1, (2, 3, 64, 64)).astype(np.float32)
+    check_all_tensors(model, data)
+
+
+def test_yolov4_style_full_topology_loads_and_counts():
+    """The full-size graph has the op counts of the reference's YOLOv4 graph (110 conv, 23 shortcut,
+    10 route, 3 max-pool, 2 upsample) and loads at 416 x 416."""
+    from tpu_compiler_b200 import module
+    model = graphs.yolov4_style_int8(batch=1, res=416, simulate=False)
+    ops = graph_runner.parse(model.text)
+    count = lambda t: sum(o["type"] == t for o in ops)  # noqa: E731
+    assert (count("conv_2d"), count("eltwise_add"), count("concat"), count("pool_max_2d"), count("upsample")) == \
+        (110, 23, 10, 3, 2)
+    m = module(0)
+    m.load_text(model.text, model.weights)
+    m.set_tensor("data", np.random.default_rng(1).uniform(0, 1, (1, 3, 416, 416)).astype(np.float32))
+    m.invoke()
+    for name, hw in (("head8", 52), ("head16", 26), ("head32", 13)):
+        assert m.get_tensor(name).shape == (1, 255, hw, hw)
+    m.close()

@@ -360,3 +360,238 @@ def resnet50_fp32(batch=1, seed=5001):
     b.op("fully_connected", "fc1000", ["pool5", fw, fb], (n, 1000), "FP32", do_relu=0)
     b.op("softmax", "prob", ["fc1000"], (n, 1000), "FP32", axis=1)
     return Model(b.text(), b.weights, ["data"], ["prob"], {"batch": batch})
+
+
+# ----------------------------------------------------------------------------- BF16 tables (numpy)
+def _bf16_np(x):
+    """F32ToBF16 with rounding (QuantizationArithmetic.cpp:873-910) on arrays."""
+    x = np.asarray(x, np.float32)
+    u = x.view(np.uint32).astype(np.uint64)
+    u = u + 0x7fff + ((u >> 16) & 1)
+    h = (u >> 16) & 0xffff
+    h = np.where((h & 0x7f80) == 0x7f80, 0x7f7f, h)
+    return (h.astype(np.uint32) << 16).view(np.float32)
+
+
+def _act_fn(kind):
+    if kind == "sigmoid":
+        return (lambda x: (1 / (1 + np.exp(-x.astype(np.float32)))).astype(np.float32)), 12
+    if kind == "mish":
+        def f(x):
+            x = x.astype(np.float32)
+            sp = np.log(np.exp(x) + np.float32(1)).astype(np.float32)
+            return (x.astype(np.float64) * np.tanh(sp.astype(np.float64))).astype(np.float32)
+        return f, 8
+    if kind == "exp":
+        return (lambda x: np.exp(x.astype(np.float32)).astype(np.float32)), 15
+    raise ValueError(kind)
+
+
+def lut_slope_tables(kind):
+    """base / slope tables of bf16_gen_base_slope_table (core/lut_func.cpp:32-134); 256 entries
+    each, which the reference then replicates per TPU lane."""
+    f, R = _act_fn(kind)
+    hw, half = 256, 128
+    interval = np.float32(int(2 * R)) / np.float32(hw)
+    i = np.arange(half, dtype=np.float32)
+    base = np.zeros(256, np.float32)
+    base[:half] = _bf16_np(f(np.float32(0) + i * interval))
+    base[half:] = _bf16_np(f(np.float32(-R) + i * interval))
+    scale = np.float32(hw) / np.float32(2 * R)
+    slope = np.zeros(256, np.float32)
+
+    def same(a, b):
+        return (a.view(np.uint32) >> 16) == (b.view(np.uint32) >> 16)
+    x0, x1 = base[:half - 1], base[1:half]
+    slope[:half - 1] = np.where(same(x0, x1), 0, _bf16_np(x1 - x0))
+    e = np.float32(R)
+    slope[half - 1] = _bf16_np(np.float32((f(np.array([3 * e]))[0] - f(np.array([e]))[0]) / (2 * e * scale)))
+    x0, x1 = base[half + 1:], base[half:-1]
+    slope[half + 1:] = np.where(same(x0, x1), 0, _bf16_np(x0 - x1))
+    s = np.float32(-R)
+    slope[half] = _bf16_np(np.float32((f(np.array([3 * s]))[0] - f(np.array([s]))[0]) / (abs(2 * s) * scale)))
+    return base, slope
+
+
+def _more_builder_ops():
+    """Ops needed by the MobileNet-v2 and YOLOv4-style graphs."""
+
+    def lut_bf16(self, name, src, kind, thr_in, thr_out):
+        """An activation run as a BF16 lookup table on an INT8 tensor: int8 -> bf16 dequant
+        (scale thr_in/128), table, bf16 -> int8 quant (scale 128/thr_out), the op sequence
+        insertQuantOp produces around a BF16 op (Quantization.cpp:180-206)."""
+        shape = self.shapes[src]
+        base, slope = lut_slope_tables(kind)
+        t0 = self.weight(name + "_table0", np.tile(base, 4))
+        t1 = self.weight(name + "_table1", np.tile(slope, 4))
+        d = self.op("quant", src + "_dequant_bf16", [src], shape, "BF16",
+                    **{"from": "INT8", "to": "BF16", "scale": repr(thr_in / 128.0)})
+        a = self.op(kind, name, [d, t0, t1], shape, "BF16")
+        q = self.op("quant", name + "_quant_i8", [a], shape, "INT8",
+                    **{"from": "BF16", "to": "INT8", "scale": repr(128.0 / thr_out)})
+        if self.simulate:
+            f, _ = _act_fn(kind)
+            x = self.sim[src].astype(np.float32) * np.float32(thr_in / 128.0)
+            y = f(np.clip(x, -30, 30))
+            self.sim[q] = np.clip(np.round(y * (128.0 / thr_out)), -128, 127).astype(np.float64)
+        return q
+
+    def leaky_relu_i8(self, name, src, slope=0.1):
+        shape = self.shapes[src]
+        # positive side passes through (multiplier 0 = no rescale), negative side x * slope:
+        # slope ~= M / 2^r with an int8 multiplier (QuantizeInt8.cpp:349-432)
+        rn = 7
+        mn = int(round(slope * (1 << rn)))
+        names = [self.weight(name + s, [v]) for s, v in (("_rshift_pos", 0), ("_multiplier_pos", 0),
+                                                         ("_rshift_neg", rn), ("_multiplier_neg", mn))]
+        self.op("leaky_relu", name, [src, None, None, None, None] + names, shape, "INT8", negative_slope=slope)
+        if self.simulate:
+            x = self.sim[src]
+            neg = rshift_round_np((x * mn).astype(np.int64), rn)
+            self.sim[name] = np.where(x > 0, x, neg).astype(np.float64)
+        return name
+
+    def concat_i8(self, name, srcs):
+        n, _, h, w = self.shapes[srcs[0]]
+        c = sum(self.shapes[s][1] for s in srcs)
+        r = self.weight(name + "_rshift", [0] * len(srcs))
+        m = self.weight(name + "_multiplier", [1] * len(srcs))
+        self.op("concat", name, list(srcs) + [None, None, r, m], (n, c, h, w), "INT8", axis=1, do_relu=0)
+        if self.simulate:
+            self.sim[name] = np.concatenate([self.sim[s][:1] for s in srcs], axis=1)
+        return name
+
+    def upsample(self, name, src, scale=2):
+        n, c, h, w = self.shapes[src]
+        self.op("upsample", name, [src], (n, c, h * scale, w * scale), self.dtypes[src], scale_h=scale, scale_w=scale)
+        if self.simulate:
+            self.sim[name] = self.sim[src][:1].repeat(scale, axis=2).repeat(scale, axis=3)
+        return name
+
+    def eltwise_add_plain(self, name, srcs):
+        return self.eltwise_add_i8(name, srcs, relu=False)
+
+    for fn in (lut_bf16, leaky_relu_i8, concat_i8, upsample, eltwise_add_plain):
+        setattr(GraphBuilder, fn.__name__, fn)
+
+
+_more_builder_ops()
+
+
+def mobilenet_v2_int8(batch=32, seed=3001, res=224, width=1.0, simulate=True, classes=1000):
+    """MobileNet-v2 (expansion 6, 3x3 depthwise + 1x1 pointwise), INT8. ReLU6 is the saturation of the
+    int8 range with a fused ReLU: the reference deletes the clip and moves its threshold onto the producer
+    (Quantization.cpp:322-345)."""
+    b = GraphBuilder(seed, simulate)
+    image = np.random.default_rng(seed + 17).uniform(-1, 1, (1, 3, res, res))
+    b.input("data", (batch, 3, res, res), sample=image)
+    x = b.quant_in("data_quant", "data", 1.0)
+
+    def ch(c):
+        return max(8, int(c * width + 4) // 8 * 8)
+
+    x = b.conv_i8("conv1", x, ch(32), 3, stride=2, pad=1, target_std=40.0)
+    cin = ch(32)
+    cfg = [(1, 16, 1, 1), (6, 24, 2, 2), (6, 32, 3, 2), (6, 64, 4, 2), (6, 96, 3, 1), (6, 160, 3, 2), (6, 320, 1, 1)]
+    bi = 0
+    for t, c, n, s in cfg:
+        for i in range(n):
+            bi += 1
+            p = "block%d" % bi
+            stride = s if i == 0 else 1
+            y = x
+            if t != 1:
+                y = b.conv_i8(p + "_expand", y, cin * t, 1, pad=0, target_std=40.0)
+            y = b.conv_i8(p + "_dw", y, cin * t, 3, stride=stride, pad=1, groups=cin * t, target_std=40.0)
+            y = b.conv_i8(p + "_project", y, ch(c), 1, pad=0, relu=False)
+            if stride == 1 and cin == ch(c):
+                y = b.eltwise_add_i8(p + "_add", [x, y], relu=False)
+            x, cin = y, ch(c)
+    x = b.conv_i8("conv_last", x, ch(1280) if width > 1 else 1280, 1, pad=0, target_std=40.0)
+    x = b.pool_avg_i8("pool", x)
+    x = b.fc_i8("fc", x, classes)
+    b.dequant("fc_dequant", x, 28.0 * 4)
+    return Model(b.text(), b.weights, ["data"], ["fc_dequant"], {"sim": b.sim, "batch": batch})
+
+
+def yolov4_style_int8(batch=8, seed=4001, res=416, width=1.0, depth=(1, 2, 8, 8, 4), simulate=True, heads=255):
+    """YOLOv4-style network: CSPDarknet-53 backbone with mish as BF16 lookup tables, SPP, PANet neck with
+    INT8 leaky-ReLU, 2x nearest upsampling, concats and three int8 heads at strides 8 / 16 / 32."""
+    b = GraphBuilder(seed, simulate)
+    image = np.random.default_rng(seed + 17).uniform(0, 1, (1, 3, res, res))
+    b.input("data", (batch, 3, res, res), sample=image)
+    x = b.quant_in("data_quant", "data", 1.0)
+    TH = 28.0 * 4  # activation threshold bookkeeping of the synthetic graph: int8 value * TH / 128
+
+    def ch(c):
+        return max(16, int(c * width) // 16 * 16)
+
+    def conv_mish(name, src, oc, k, stride=1):
+        y = b.conv_i8(name, src, oc, k, stride=stride, pad=k // 2, relu=False, target_std=40.0)
+        return b.lut_bf16(name + "_mish", y, "mish", 4.0, 4.0)
+
+    def conv_leaky(name, src, oc, k, stride=1):
+        y = b.conv_i8(name, src, oc, k, stride=stride, pad=k // 2, relu=False)
+        return b.leaky_relu_i8(name + "_leaky", y)
+
+    x = conv_mish("conv0", x, ch(32), 3)
+    feats = []
+    c = ch(32)
+    for si, nblk in enumerate(depth):
+        oc = ch(64 * (2 ** si))
+        p = "s%d" % si
+        x = conv_mish(p + "_down", x, oc, 3, stride=2)
+        half = oc if si == 0 else oc // 2
+        r1 = conv_mish(p + "_route1", x, half, 1)
+        r2 = conv_mish(p + "_route2", x, half, 1)
+        y = r2
+        for k in range(nblk):
+            z = conv_mish("%s_b%d_1" % (p, k), y, half if si else oc // 2, 1)
+            z = conv_mish("%s_b%d_2" % (p, k), z, half, 3)
+            y = b.eltwise_add_plain("%s_b%d_add" % (p, k), [y, z])
+        y = conv_mish(p + "_post", y, half, 1)
+        x = b.concat_i8(p + "_cat", [y, r1])
+        x = conv_mish(p + "_merge", x, oc, 1)
+        c = oc
+        if si >= 2:
+            feats.append(x)
+    f8, f16, f32 = feats
+    # SPP
+    x = conv_leaky("spp_pre1", f32, c // 2, 1)
+    x = conv_leaky("spp_pre2", x, c, 3)
+    x = conv_leaky("spp_pre3", x, c // 2, 1)
+    pools = [b.pool_max("spp_pool%d" % k, x, k, 1, pad=(k // 2, k // 2, k // 2, k // 2)) for k in (5, 9, 13)]
+    x = b.concat_i8("spp_cat", pools[::-1] + [x])
+    x = conv_leaky("spp_post1", x, c // 2, 1)
+    x = conv_leaky("spp_post2", x, c, 3)
+    p32 = conv_leaky("spp_post3", x, c // 2, 1)
+    # top-down
+    def merge_up(name, top, lateral, oc):
+        u = conv_leaky(name + "_up_conv", top, oc, 1)
+        u = b.upsample(name + "_up", u, 2)
+        l = conv_leaky(name + "_lat", lateral, oc, 1)
+        y = b.concat_i8(name + "_cat", [l, u])
+        for k in range(2):
+            y = conv_leaky("%s_c%d_1" % (name, k), y, oc, 1)
+            y = conv_leaky("%s_c%d_3" % (name, k), y, oc * 2, 3)
+        return conv_leaky(name + "_out", y, oc, 1)
+    p16 = merge_up("pan16", p32, f16, c // 4)
+    p8 = merge_up("pan8", p16, f8, c // 8)
+    # heads + bottom-up
+    h8 = conv_leaky("head8_conv", p8, c // 4, 3)
+    b.conv_i8("head8", h8, heads, 1, pad=0, relu=False)
+
+    def merge_down(name, low, high, oc):
+        d = conv_leaky(name + "_down", low, oc, 3, stride=2)
+        y = b.concat_i8(name + "_cat", [d, high])
+        for k in range(2):
+            y = conv_leaky("%s_c%d_1" % (name, k), y, oc, 1)
+            y = conv_leaky("%s_c%d_3" % (name, k), y, oc * 2, 3)
+        return conv_leaky(name + "_out", y, oc, 1)
+    n16 = merge_down("pan16d", p8, p16, c // 4)
+    h16 = conv_leaky("head16_conv", n16, c // 2, 3)
+    b.conv_i8("head16", h16, heads, 1, pad=0, relu=False)
+    n32 = merge_down("pan32d", n16, p32, c // 2)
+    h32 = conv_leaky("head32_conv", n32, c, 3)
+    b.conv_i8("head32", h32, heads, 1, pad=0, relu=False)
+    return Model(b.text(), b.weights, ["data"], ["head8", "head16", "head32"], {"sim": b.sim, "batch": batch})

@@ -93,3 +93,101 @@ def test_kld_kernel_matches_golden(golden_dir):
                                 thr.ctypes.data_as(fp)))
     assert np.array_equal(thr, g["threshold"])
     m.close()
+
+
+def test_resnet50_fp32_calibration_runs_and_matches_cpu_rule_on_sampled_tensors():
+    """The calibration configuration's graph (fp32 ResNet-50, N(0,1) images clipped to [-3, 3]) at a small
+    image count: thresholds of a few tensors recomputed on the CPU from the GPU's own activations."""
+    from tpu_compiler_b200 import module
+    from tpu_compiler_b200.calibration import ActivationCalibrator
+    B, nb = 4, 2
+    model = graphs.resnet50_fp32(batch=B, seed=5001)
+    rng = np.random.default_rng(5001)
+    data = [np.clip(rng.normal(0, 1, (B, 3, 224, 224)), -3, 3).astype(np.float32) for _ in range(nb)]
+    m = module(0)
+    m.load_text(model.text, model.weights)
+    cal = ActivationCalibrator(m, lambda: iter(data))
+    thr, stats = cal.run()
+    assert len(cal.names) == 74 and cal.num_samples == B * nb
+    hist_gpu = cal.histograms.cpu().numpy()
+    sample = ["data", "conv1", "res2a", "res3b_branch2b", "res4f", "pool5", "fc1000", "prob"]
+    acts = {n: [] for n in sample}
+    for d in data:
+        m.set_tensor("data", d)
+        m.invoke()
+        for n in sample:
+            acts[n].append(m.get_tensor(n).reshape(-1))
+    for n in sample:
+        t = cal.names.index(n)
+        x = np.concatenate(acts[n])
+        mn, mx, ab = stats[n]
+        assert mn == x.min() and mx == x.max()
+        tt = np.abs(x)
+        tt = tt[tt != 0]
+        width = ab / (2048 - 1)
+        ref_hist, _ = np.histogram(np.floor(tt / width + 0.5), bins=2048, range=(0, 2047))
+        assert np.array_equal(hist_gpu[t], ref_hist.astype(np.int64)), n
+        assert thr[n] == oracle.kld_threshold(ref_hist.astype(np.int32), float(width)), n
+    # the fp32 forward itself: one image against the oracle, 1e-4 of each tensor's range
+    ref = graph_runner.run(model.text, model.weights, {"data": data[0]})
+    m.set_tensor("data", data[0])
+    m.invoke()
+    for n in ("conv1", "res2a", "res4f", "fc1000", "prob"):
+        got = m.get_tensor(n)
+        err = np.abs(got - ref[n]).max() / (np.abs(ref[n]).max() + 1e-30)
+        assert err < 1e-4, (n, err)
+    m.close()
+
+
+def _calib_rank(rank, world, port, q):
+    import os
+    import torch
+    import torch.distributed as dist
+    from tpu_compiler_b200 import module
+    from tpu_compiler_b200.calibration import ActivationCalibrator
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    model = small_fp32_model(4)
+    rng = np.random.default_rng(77)
+    data = [np.clip(rng.normal(0, 1, (4, 3, 24, 24)), -3, 3).astype(np.float32) for _ in range(4)]
+    m = module(rank)
+    m.load_text(model.text, model.weights)
+    cal = ActivationCalibrator(m, lambda: iter(data[rank::world]), dist=dist)
+    thr, stats = cal.run()
+    q.put((rank, {k: float(v) for k, v in thr.items()}, cal.histograms.cpu().numpy(), cal.num_samples))
+    dist.barrier()
+    m.close()
+    dist.destroy_process_group()
+
+
+def test_two_gpu_calibration_equals_single_gpu():
+    import torch
+    import torch.multiprocessing as mp
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from tpu_compiler_b200 import module
+    from tpu_compiler_b200.calibration import ActivationCalibrator
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_calib_rank, args=(r, 2, 29733, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=300) for _ in procs]
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    model = small_fp32_model(4)
+    rng = np.random.default_rng(77)
+    data = [np.clip(rng.normal(0, 1, (4, 3, 24, 24)), -3, 3).astype(np.float32) for _ in range(4)]
+    m = module(0)
+    m.load_text(model.text, model.weights)
+    cal = ActivationCalibrator(m, lambda: iter(data))
+    thr, _ = cal.run()
+    hist = cal.histograms.cpu().numpy()
+    for rank, thr_r, hist_r, n in results:
+        assert n == 16
+        assert np.array_equal(hist_r, hist)
+        assert thr_r == {k: float(v) for k, v in thr.items()}
+    m.close()

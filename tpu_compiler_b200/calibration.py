@@ -29,12 +29,13 @@ class ActivationCalibrator:
         self.dist = dist
         self.input_name = input_name or model.get_input_details()[0]
         self.names = [o["name"] for o in model.op_info if o["dtype"] == "FP32"]
-        self.device = torch.device("cuda", model._device)
-        self._lib = lib()
+        self.device = torch.device("cuda", model._device) if model._device is not None else torch.device("cpu")
+        self._lib = lib() if model._device is not None else None
         self.num_samples = 0
 
-    # -- pass 1 ------------------------------------------------------------------
-    def find_min_max_abs(self):
+    # -- device work of the two passes (overridden by the CPU stand-in used in the gloo tests) -------
+    def _local_min_max(self):
+        """This rank's running (min, max) per tensor as a [T, 2] tensor, and its image count."""
         T = len(self.names)
         stats = torch.empty((T, 2), dtype=torch.float32, device=self.device)
         stats[:, 0] = float("inf")
@@ -49,11 +50,31 @@ class ActivationCalibrator:
                                                    C.c_void_p(stats.data_ptr() + t * 8)))
             n_img += batch.shape[0]
         self.model.sync()
+        return stats, n_img
+
+    def _local_histograms(self, activations_statistics):
+        """This rank's [T, bins] int64 histograms."""
+        T = len(self.names)
+        hist = torch.zeros((T, self.bin_num), dtype=torch.int64, device=self.device)
+        torch.cuda.synchronize(self.device)
+        for batch in self.batches():
+            self.model.set_tensor(self.input_name, batch)
+            self.model.launch()
+            for t, name in enumerate(self.names):
+                ab = float(activations_statistics[name][2])
+                check(self._lib.tpucb_calib_hist(self.model._h, name.encode(), C.c_float(ab), self.bin_num,
+                                                 C.c_void_p(hist.data_ptr() + t * self.bin_num * 8)))
+        self.model.sync()
+        return hist
+
+    # -- pass 1 ------------------------------------------------------------------
+    def find_min_max_abs(self):
+        stats, n_img = self._local_min_max()
         if self.dist is not None:
             packed = torch.stack([-stats[:, 0], stats[:, 1]], dim=1).contiguous()
             self.dist.all_reduce(packed, op=self.dist.ReduceOp.MAX)
             stats = torch.stack([-packed[:, 0], packed[:, 1]], dim=1)
-            cnt = torch.tensor([n_img], dtype=torch.int64, device=self.device)
+            cnt = torch.tensor([n_img], dtype=torch.int64, device=stats.device)
             self.dist.all_reduce(cnt, op=self.dist.ReduceOp.SUM)
             n_img = int(cnt.item())
         self.num_samples = n_img
@@ -69,17 +90,7 @@ class ActivationCalibrator:
 
     # -- pass 2 ------------------------------------------------------------------
     def calc_histograms(self, activations_statistics):
-        T = len(self.names)
-        hist = torch.zeros((T, self.bin_num), dtype=torch.int64, device=self.device)
-        torch.cuda.synchronize(self.device)
-        for batch in self.batches():
-            self.model.set_tensor(self.input_name, batch)
-            self.model.launch()
-            for t, name in enumerate(self.names):
-                ab = float(activations_statistics[name][2])
-                check(self._lib.tpucb_calib_hist(self.model._h, name.encode(), C.c_float(ab), self.bin_num,
-                                                 C.c_void_p(hist.data_ptr() + t * self.bin_num * 8)))
-        self.model.sync()
+        hist = self._local_histograms(activations_statistics)
         if self.dist is not None:
             self.dist.all_reduce(hist, op=self.dist.ReduceOp.SUM)
         return hist

@@ -253,12 +253,16 @@ def main():
                 other_ms += t
         int8_peak = 2.0 * peaks["bf16_tflops_sustained"]
         achieved = conv_ops / (conv_ms * 1e-3) / 1e12
+        i8_tops = C.c_double(0.0)  # this library's own tcgen05 kind::i8 issue microbenchmark, live on this GPU
+        check(L.tpucb_measure_i8_mma_peak(local_rank, 128, C.byref(i8_tops)))
         roofline = {"bound": "tensor", "achieved": achieved, "peak": int8_peak, "unit": "TOP/s",
                     "frac": achieved / int8_peak, "traffic": None,
                     "kernel": "conv_gemm_i8_kernel (tcgen05 kind::i8 implicit GEMM, %d launches per step)" % n_conv,
                     "peak_source": "2 x bf16_tflops_sustained of %s peaks (no INT8 figure is measured; the 8-bit "
                                    "rate of the same tensor pipe is twice the 16-bit rate)" % peaks["source"],
                     "avg_launch_us": conv_ms * 1e3 / max(n_conv, 1),
+                    "i8_mma_peak_measured": i8_tops.value,
+                    "frac_of_i8_mma_peak": achieved / i8_tops.value if i8_tops.value > 0 else None,
                     "hbm_view": {"achieved_gbs": conv_bytes / (conv_ms * 1e-3) / 1e9, "peak_gbs": peaks["hbm_gbs"],
                                  "frac": conv_bytes / (conv_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}}
         mem_kernels = {"achieved_gbs": other_bytes / (other_ms * 1e-3) / 1e9 if other_ms > 0 else None,

@@ -94,6 +94,12 @@ int tpucb_interp_kernel_count(tpucb_interp *it, int *count);
 int tpucb_interp_tensor_device(tpucb_interp *it, const char *name, void **dev, size_t *bytes,
                                int *channels, int *channel_pitch, int *dtype);
 
+/* Measures the dense INT8 rate of the tensor pipe on `device`: every SM issues a long chain of
+ * tcgen05.mma kind::i8 (M=128, N=n_cols in {64,128,256}, K=32) on operands resident in shared memory.
+ * Writes tera-ops/s (2 ops per MAC). No reference counterpart; it supplies the roofline denominator
+ * of the convolution kernel, for which the driver-written peaks have no INT8 entry. */
+int tpucb_measure_i8_mma_peak(int device, int n_cols, double *tops);
+
 /* Pinned host buffers for the e2e path. */
 int tpucb_host_alloc(void **ptr, size_t bytes);
 int tpucb_host_free(void *ptr);

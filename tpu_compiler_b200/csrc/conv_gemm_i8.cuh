@@ -44,6 +44,7 @@ struct ConvGemmParams {
   int ldc;        // output row pitch in bytes
   int c_off;      // first output channel written inside a row
   int stages;     // pipeline depth
+  int w_resident; // 1: the CTA keeps all K blocks of its channel tile's weights in shared memory
   int a_mode;     // 0: A is a 2-D [M][K] matrix, 1: im2col TMA, 2: row windows (stem)
   int win_g;      // mode 2: output pixels per copy
   int act;        // 0 none, 1 ReLU, 2 leaky (non-QDM pos/neg rescale of the int8 result)
@@ -329,9 +330,9 @@ conv_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const uint32_t bar_empty = base + 64;       // kMaxStages x 8 B
   const uint32_t bar_acc_full = base + 128;   // 2 x 8 B: accumulator buffer complete
   const uint32_t bar_acc_empty = base + 144;  // 2 x 8 B: accumulator buffer drained by the epilogue
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + 160);
-  volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + 164);
-  const uint32_t tiles = base + kSmemHeader;
+  const uint32_t bar_w = base + 160;          // resident weights landed
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + 168);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + 172);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -340,9 +341,14 @@ conv_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const int total_tiles = n_tiles * m_tiles;
   const uint32_t a_bytes = 128u * (uint32_t)p.BK;
   const uint32_t b_bytes = (uint32_t)p.BN * (uint32_t)p.BK;
-  const uint32_t stage_bytes = a_bytes + b_bytes;
   const int taps = p.kh * p.kw;
   const int k_iters = taps * p.c_chunks;
+  // Weight-resident mode: [all K blocks of the weights][ring of activation tiles]; the launch grid is a
+  // multiple of the channel-tile count, so a CTA's channel tile never changes. Otherwise the ring
+  // holds (activation tile, weight tile) pairs.
+  const uint32_t w_base = base + kSmemHeader;
+  const uint32_t tiles = p.w_resident ? w_base + (uint32_t)k_iters * b_bytes : w_base;
+  const uint32_t stage_bytes = p.w_resident ? a_bytes : a_bytes + b_bytes;
   const uint32_t acc_stride = (uint32_t)(p.tmem_cols >> 1); // columns per accumulator buffer
 
   // A CTA of a launch in which an earlier CTA already gave up does no work at all, so that a
@@ -360,6 +366,7 @@ conv_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       ptx::mbar_init(bar_acc_full + 8 * b, 1);
       ptx::mbar_init(bar_acc_empty + 8 * b, kEpilogueWarps);
     }
+    ptx::mbar_init(bar_w, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -375,6 +382,13 @@ conv_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     if (lane == 0) {
       int it = 0; // k-iterations issued so far, across tiles
       bool ok = true;
+      if (p.w_resident && (int)blockIdx.x < total_tiles) {
+        const int n0w = ((int)blockIdx.x % n_tiles) * p.BN;
+        ptx::mbar_expect_tx(bar_w, (uint32_t)k_iters * b_bytes);
+        for (int kit = 0; kit < k_iters; ++kit)
+          ptx::tma_load_3d(w_base + (uint32_t)kit * b_bytes, &tmB, bar_w, (kit % p.c_chunks) * p.BK,
+                           kit / p.c_chunks, n0w);
+      }
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         const int m0 = (tile / n_tiles) * 128;
         const int n0 = (tile % n_tiles) * p.BN;
@@ -426,10 +440,13 @@ conv_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           } else {
             ptx::tma_load_2d(a_dst, &tmA, fb, c0, m0);
           }
-          ptx::tma_load_3d(b_dst, &tmB, fb, c0, tap, n0);
+          if (!p.w_resident) ptx::tma_load_3d(b_dst, &tmB, fb, c0, tap, n0);
         }
       }
       if (!ok || *abort_flag) {
+        if (p.w_resident && (int)blockIdx.x < total_tiles)
+          for (uint32_t w = 0; w < (1u << 20); ++w)
+            if (ptx::mbar_try_wait(bar_w, 0u)) break;
         // Drain: wait (bounded) until every copy this thread issued has landed, so that no bulk
         // copy is in flight when the CTA's shared memory is released.
         int first = it > p.stages ? it - p.stages : 0;
@@ -446,6 +463,13 @@ conv_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     if (lane == 0) {
       int it = 0, t = 0;
       bool ok = true;
+      if (p.w_resident && (int)blockIdx.x < total_tiles) {
+        if (!ptx::mbar_wait_bounded(bar_w, 0u, abort_flag)) {
+          if (!*abort_flag) atomicExch(p.err, kErrFullWait);
+          *abort_flag = 1;
+          ok = false;
+        }
+      }
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++t) {
         const int buf = t & 1;
         if (t >= 2) {
@@ -470,7 +494,7 @@ conv_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           }
           ptx::tcgen05_fence_after();
           const uint32_t a_src = tiles + s * stage_bytes;
-          const uint32_t b_src = a_src + a_bytes;
+          const uint32_t b_src = p.w_resident ? w_base + (uint32_t)kit * b_bytes : a_src + a_bytes;
           // transposed product: weights are the A operand (M = channels), activations B (N = pixels)
           const uint64_t adesc = make_kmajor_desc(b_src, p.BK);
           const uint64_t bdesc = make_kmajor_desc(a_src, p.BK);

@@ -284,21 +284,33 @@ inline void finish_plan(ConvPlan &pl, int rows, int taps, int k_inner, int oc_pa
   p.tmem_cols = 256;
   p.idesc = make_idesc_i8(128, bn);
   const int k_iters = taps * p.c_chunks;
-  const size_t stage_bytes = (size_t)(128 + bn) * p.BK;
-  // Persistent CTAs, two per SM: about 100 KB of shared memory each. The ring may hold several
-  // tiles' worth of operands so that the producer prefetches across tile boundaries.
-  int stages = (int)((96 * 1024) / stage_bytes);
-  if (stages < 2) stages = 2;
-  if (stages > kMaxStages) stages = kMaxStages;
   const int n_tiles = (oc_pad + bn - 1) / bn;
   const long long total_tiles = (long long)m_tiles * n_tiles;
-  int grid = 2 * sm_count;
+  const size_t a_bytes = (size_t)128 * p.BK, b_bytes = (size_t)bn * p.BK;
+  const size_t w_all = (size_t)k_iters * b_bytes;
+  // Weight-resident mode: when all K blocks of one channel tile's weights fit in 48 KB beside a useful
+  // ring of activation tiles (two CTAs per SM are kept), a CTA loads them once and streams only
+  // activations, which halves the bytes that have to reach shared memory per MAC. Larger weight
+  // sets would force one CTA per SM, which measured slower than re-fetching the weights from L2.
+  const int ctas_per_sm = 2;
+  p.w_resident = (total_tiles >= 2LL * n_tiles && w_all <= 48 * 1024) ? 1 : 0;
+  const size_t budget = 113 * 1024;
+  const size_t stage_bytes = p.w_resident ? a_bytes : a_bytes + b_bytes;
+  const size_t ring_budget = budget - kSmemHeader - 1024 - (p.w_resident ? w_all : 0);
+  int stages = (int)(ring_budget / stage_bytes);
+  if (stages < 2) stages = 2;
+  if (stages > kMaxStages) stages = kMaxStages;
+  int grid = ctas_per_sm * sm_count;
   if (grid > total_tiles) grid = (int)total_tiles;
+  if (p.w_resident) {
+    grid = grid / n_tiles * n_tiles; // a CTA's channel tile must not change
+    if (grid < n_tiles) grid = n_tiles;
+  }
   const long long iters_per_cta = ((total_tiles + grid - 1) / grid) * k_iters;
   if (stages > iters_per_cta) stages = (int)iters_per_cta;
   if (stages < 1) stages = 1;
   p.stages = stages;
-  pl.smem = kSmemHeader + 1024 + stages * stage_bytes;
+  pl.smem = kSmemHeader + 1024 + (p.w_resident ? w_all : 0) + stages * stage_bytes;
   pl.grid = dim3((unsigned)grid, 1, 1);
 }
 

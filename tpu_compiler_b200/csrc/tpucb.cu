@@ -2,6 +2,7 @@
 // for the reference interface each entry point stands in for.
 #include "../../include/tpucb.h"
 #include "interpreter.cuh"
+#include "mma_peak.cuh"
 
 #include <cmath>
 #include <mutex>
@@ -271,6 +272,44 @@ int tpucb_host_alloc(void **ptr, size_t bytes) {
 int tpucb_host_free(void *ptr) {
   TPUCB_API_BEGIN
   TPUCB_CUDA(cudaFreeHost(ptr));
+  TPUCB_API_END
+}
+
+int tpucb_measure_i8_mma_peak(int device, int n_cols, double *tops) {
+  TPUCB_API_BEGIN
+  TPUCB_CHECK(tops && (n_cols == 64 || n_cols == 128 || n_cols == 256), "tpucb_measure_i8_mma_peak: n_cols must be 64, 128 or 256");
+  TPUCB_CUDA(cudaSetDevice(device));
+  cudaDeviceProp prop;
+  TPUCB_CUDA(cudaGetDeviceProperties(&prop, device));
+  TPUCB_CHECK(prop.major == 10, "tpucb_measure_i8_mma_peak: needs an sm_100 device");
+  int *d_err = nullptr;
+  TPUCB_CUDA(cudaMalloc(&d_err, sizeof(int)));
+  TPUCB_CUDA(cudaMemset(d_err, 0, sizeof(int)));
+  const size_t smem = 2048 + (size_t)(128 + n_cols) * 128;
+  TPUCB_CUDA(cudaFuncSetAttribute(mma_i8_peak_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  const uint32_t idesc = make_idesc_i8(128, n_cols);
+  const int iters = 8192, grid = prop.multiProcessorCount;
+  cudaEvent_t a, b;
+  TPUCB_CUDA(cudaEventCreate(&a));
+  TPUCB_CUDA(cudaEventCreate(&b));
+  float best = 1e30f;
+  for (int rep = 0; rep < 4; ++rep) {
+    TPUCB_CUDA(cudaEventRecord(a, 0));
+    mma_i8_peak_kernel<<<grid, 64, smem, 0>>>(iters, n_cols, idesc, d_err);
+    TPUCB_CUDA(cudaEventRecord(b, 0));
+    TPUCB_CUDA(cudaEventSynchronize(b));
+    float ms = 0;
+    TPUCB_CUDA(cudaEventElapsedTime(&ms, a, b));
+    if (rep > 0 && ms < best) best = ms;
+  }
+  int err = 0;
+  TPUCB_CUDA(cudaMemcpy(&err, d_err, sizeof(int), cudaMemcpyDeviceToHost));
+  cudaFree(d_err);
+  cudaEventDestroy(a);
+  cudaEventDestroy(b);
+  TPUCB_CHECK(err == 0, "tpucb_measure_i8_mma_peak: the MMA chain did not complete within the wait limit");
+  const double ops = 2.0 * 128.0 * n_cols * 32.0 * 4.0 * iters * grid;
+  *tops = ops / (best * 1e-3) / 1e12;
   TPUCB_API_END
 }
 

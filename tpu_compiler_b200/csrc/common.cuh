@@ -104,4 +104,23 @@ __device__ __forceinline__ int f32_to_int8_rz(float v) {
   return (int)r;
 }
 
+// d = {c[15:0], sat8(a), sat8(b)}: two int32 saturated to int8 and merged below the low half of c.
+__device__ __forceinline__ uint32_t pack_sat_s8(int a, int b, uint32_t c) {
+  uint32_t d;
+  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+// bytes (q0, q1, q2, q3) from low to high, each saturated to [-128, 127]
+__device__ __forceinline__ uint32_t pack4_sat(int q0, int q1, int q2, int q3) {
+  return pack_sat_s8(q1, q0, pack_sat_s8(q3, q2, 0u));
+}
+// sign-extended byte J of a word in one byte-permute: in prmt's default mode bit 3 of a selector
+// nibble replicates the sign of the selected byte (the __byte_perm intrinsic masks that bit off,
+// hence the inline PTX).
+template <int J> __device__ __forceinline__ int sext_byte(uint32_t w) {
+  uint32_t d;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(w), "r"(0u), "r"((uint32_t)(J | ((8 | J) << 4) | ((8 | J) << 8) | ((8 | J) << 12))));
+  return (int)d;
+}
+
 } // namespace tpucb

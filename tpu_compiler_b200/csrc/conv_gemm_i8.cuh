@@ -223,17 +223,6 @@ __device__ __forceinline__ ChanConst load_chan_const(const ConvGemmParams &p, in
   return c;
 }
 
-// d = {c[15:0], sat8(a), sat8(b)}: two int32 saturated to int8 and merged below the low half of c.
-__device__ __forceinline__ uint32_t pack_sat_s8(int a, int b, uint32_t c) {
-  uint32_t d;
-  asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-  return d;
-}
-// bytes (q0, q1, q2, q3) from low to high, each saturated to [-128, 127]
-__device__ __forceinline__ uint32_t pack4_sat(int q0, int q1, int q2, int q3) {
-  return pack_sat_s8(q1, q0, pack_sat_s8(q3, q2, 0u));
-}
-
 // One requantised value BEFORE the final int8 saturation (pack4_sat applies it).
 template <int ACT>
 __device__ __forceinline__ int requant_one(int32_t acc, const ChanConst &q, const ConvGemmParams &p) {

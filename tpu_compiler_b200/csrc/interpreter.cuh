@@ -654,7 +654,20 @@ public:
     if (out_->dtype == DT_I8) {
       size_t nvec = out_->bytes() / 16;
       if (is_mul_) eltwise_mul_i8_kernel<<<grid_for(nvec, 256, I_.sm_count), 256, 0, s>>>(a_, (int8_t *)out_->dev, nvec);
-      else eltwise_add_i8_kernel<<<grid_for(nvec, 256, I_.sm_count), 256, 0, s>>>(a_, (int8_t *)out_->dev, nvec);
+      else {
+        const int grid = grid_for((nvec + 1) / 2, 256, I_.sm_count);
+        int8_t *o = (int8_t *)out_->dev;
+#define TPUCB_ELT(N)                                                                               \
+  if (a_.do_relu) eltwise_add_i8_kernel<N, true><<<grid, 256, 0, s>>>(a_, o, nvec);               \
+  else eltwise_add_i8_kernel<N, false><<<grid, 256, 0, s>>>(a_, o, nvec);
+        switch (a_.nin) {
+        case 1: TPUCB_ELT(1) break;
+        case 2: TPUCB_ELT(2) break;
+        case 3: TPUCB_ELT(3) break;
+        default: TPUCB_ELT(4) break;
+        }
+#undef TPUCB_ELT
+      }
     } else {
       size_t n = out_->bytes() / 4;
       eltwise_add_f32_kernel<<<grid_for(n, 256, I_.sm_count), 256, 0, s>>>(f_, (float *)out_->dev, n);

@@ -165,27 +165,52 @@ struct EltwiseArgs {
 
 __device__ __forceinline__ int sx8(uint32_t w, int j) { return (int)(int8_t)(w >> (8 * j)); }
 
+// acc += x_j * m for the 16 int8 lanes of one 16-byte vector
+__device__ __forceinline__ void madd_vec16(int (&acc)[16], const uint4 &v, int m) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    acc[4 * q + 0] += sext_byte<0>(w[q]) * m;
+    acc[4 * q + 1] += sext_byte<1>(w[q]) * m;
+    acc[4 * q + 2] += sext_byte<2>(w[q]) * m;
+    acc[4 * q + 3] += sext_byte<3>(w[q]) * m;
+  }
+}
+
+// The rounding term 2^(r-1) is folded into the accumulator's start value: with ReLU,
+// max(sum + rnd, 0) >> r equals (max(sum, 0) + rnd) >> r because rnd < 2^r.
+template <int NIN, bool RELU>
 __global__ void eltwise_add_i8_kernel(EltwiseArgs a, int8_t *__restrict__ out, size_t nvec) {
-  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nvec;
-       i += (size_t)gridDim.x * blockDim.x) {
-    int acc[16];
+  const int rnd = a.rshift > 0 ? (1 << (a.rshift - 1)) : 0;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nvec; i += 2 * stride) {
+    const size_t i2 = i + stride;
+    const bool two = i2 < nvec;
+    uint4 v[2][NIN];
 #pragma unroll
-    for (int j = 0; j < 16; ++j) acc[j] = 0;
-    for (int k = 0; k < a.nin; ++k) {
-      uint4 v = reinterpret_cast<const uint4 *>(a.in[k])[i];
-      uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-      for (int j = 0; j < 16; ++j) acc[j] += sx8(w[j >> 2], j & 3) * a.mult[k];
+    for (int k = 0; k < NIN; ++k) {
+      v[0][k] = __ldcs(reinterpret_cast<const uint4 *>(a.in[k]) + i);
+      if (two) v[1][k] = __ldcs(reinterpret_cast<const uint4 *>(a.in[k]) + i2);
     }
-    uint32_t o[4] = {0, 0, 0, 0};
 #pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      int v = acc[j];
-      if (a.do_relu && v < 0) v = 0;
-      int q = rshift_sat8(v, a.rshift);
-      o[j >> 2] |= ((uint32_t)(q & 0xff)) << (8 * (j & 3));
+    for (int u = 0; u < 2; ++u) {
+      if (u == 1 && !two) break;
+      int acc[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) acc[j] = rnd;
+#pragma unroll
+      for (int k = 0; k < NIN; ++k) madd_vec16(acc, v[u][k], a.mult[k]);
+      uint32_t o[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        int r0 = acc[4 * q], r1 = acc[4 * q + 1], r2 = acc[4 * q + 2], r3 = acc[4 * q + 3];
+        if (RELU) {
+          r0 = max(r0, 0); r1 = max(r1, 0); r2 = max(r2, 0); r3 = max(r3, 0);
+        }
+        o[q] = pack4_sat(r0 >> a.rshift, r1 >> a.rshift, r2 >> a.rshift, r3 >> a.rshift);
+      }
+      __stcs(reinterpret_cast<uint4 *>(out) + (u == 0 ? i : i2), make_uint4(o[0], o[1], o[2], o[3]));
     }
-    reinterpret_cast<uint4 *>(out)[i] = make_uint4(o[0], o[1], o[2], o[3]);
   }
 }
 

@@ -44,6 +44,7 @@ struct ConvGemmParams {
   int ldc;        // output row pitch in bytes
   int c_off;      // first output channel written inside a row
   int stages;     // pipeline depth
+  int dual;       // 1: at most 64 channels: two 128-pixel sub-tiles share the 128 TMEM lanes (see kernel)
   int w_resident; // 1: the CTA keeps all K blocks of its channel tile's weights in shared memory
   int a_mode;     // 0: A is a 2-D [M][K] matrix, 1: im2col TMA, 2: row windows (stem)
   int win_g;      // mode 2: output pixels per copy
@@ -326,10 +327,16 @@ conv_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int n_tiles = (p.n_valid + p.BN - 1) / p.BN;
-  const int m_tiles = (p.M_total + 127) / 128;
+  // Dual mode (<= 64 output channels): a tile covers 256 pixels. The weight tile is fetched as 192 rows
+  // starting 64 rows BEFORE the first channel, i.e. [64 zero rows][64 weight rows][64 zero rows]; rows
+  // 64..191 of it ([W; 0]) times the first 128 pixels fill TMEM lanes 0..63, rows 0..127 ([0; W]) times
+  // the second 128 pixels accumulate into lanes 64..127, so all 128 lanes (and all epilogue warps) work.
+  const int m_tile = p.dual ? 256 : 128;
+  const int subs = p.dual ? 2 : 1;
+  const int m_tiles = (p.M_total + m_tile - 1) / m_tile;
   const int total_tiles = n_tiles * m_tiles;
-  const uint32_t a_bytes = 128u * (uint32_t)p.BK;
-  const uint32_t b_bytes = (uint32_t)p.BN * (uint32_t)p.BK;
+  const uint32_t a_bytes = (uint32_t)m_tile * (uint32_t)p.BK;
+  const uint32_t b_bytes = (uint32_t)(p.dual ? 192 : p.BN) * (uint32_t)p.BK;
   const int taps = p.kh * p.kw;
   const int k_iters = taps * p.c_chunks;
   // Weight-resident mode: [all K blocks of the weights][ring of activation tiles]; the launch grid is a
@@ -372,23 +379,26 @@ conv_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       int it = 0; // k-iterations issued so far, across tiles
       bool ok = true;
       if (p.w_resident && (int)blockIdx.x < total_tiles) {
-        const int n0w = ((int)blockIdx.x % n_tiles) * p.BN;
+        const int n0w = ((int)blockIdx.x % n_tiles) * p.BN - (p.dual ? 64 : 0);
         ptx::mbar_expect_tx(bar_w, (uint32_t)k_iters * b_bytes);
         for (int kit = 0; kit < k_iters; ++kit)
           ptx::tma_load_3d(w_base + (uint32_t)kit * b_bytes, &tmB, bar_w, (kit % p.c_chunks) * p.BK,
                            kit / p.c_chunks, n0w);
       }
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile / n_tiles) * 128;
-        const int n0 = (tile % n_tiles) * p.BN;
-        int n_img = 0, h_base = 0, w_base = 0;
+        const int m0 = (tile / n_tiles) * m_tile;
+        const int n0 = (tile % n_tiles) * p.BN - (p.dual ? 64 : 0);
+        int n_img[2] = {0, 0}, h_base[2] = {0, 0}, w_base[2] = {0, 0};
         if (p.a_mode == 1) {
-          int q = m0 % p.OW;
-          int t = m0 / p.OW;
-          int pp = t % p.OH;
-          n_img = t / p.OH;
-          w_base = q * p.sw - p.pl;
-          h_base = pp * p.sh - p.pt;
+          for (int sub = 0; sub < subs; ++sub) {
+            const int ms = m0 + 128 * sub;
+            int q = ms % p.OW;
+            int t = ms / p.OW;
+            int pp = t % p.OH;
+            n_img[sub] = t / p.OH;
+            w_base[sub] = q * p.sw - p.pl;
+            h_base[sub] = pp * p.sh - p.pt;
+          }
         }
         // mode 2: the (column, row, image) of the first pixel of each copy, computed once per tile
         int bx_q[16], bx_h[16], bx_n[16];
@@ -419,15 +429,17 @@ conv_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           ptx::mbar_expect_tx(fb, stage_bytes);
           if (p.a_mode == 1) {
             const int r = tap / p.kw, ss = tap % p.kw;
-            ptx::tma_load_im2col_4d(a_dst, &tmA, fb, c0, w_base, h_base, n_img,
-                                    (uint16_t)(ss * p.dw), (uint16_t)(r * p.dh));
+            for (int sub = 0; sub < subs; ++sub)
+              ptx::tma_load_im2col_4d(a_dst + (uint32_t)sub * 128u * (uint32_t)p.BK, &tmA, fb, c0, w_base[sub],
+                                      h_base[sub], n_img[sub], (uint16_t)(ss * p.dw), (uint16_t)(r * p.dh));
           } else if (p.a_mode == 2) {
             // `tap` is the filter row; each copy brings win_g consecutive output pixels' windows.
             for (int i = 0; i < n_boxes; ++i)
               ptx::tma_load_4d(a_dst + (uint32_t)(i * p.win_g * p.BK), &tmA, fb, 0, bx_q[i],
                                bx_h[i] + tap * p.dh, bx_n[i]);
           } else {
-            ptx::tma_load_2d(a_dst, &tmA, fb, c0, m0);
+            for (int sub = 0; sub < subs; ++sub)
+              ptx::tma_load_2d(a_dst + (uint32_t)sub * 128u * (uint32_t)p.BK, &tmA, fb, c0, m0 + 128 * sub);
           }
           if (!p.w_resident) ptx::tma_load_3d(b_dst, &tmB, fb, c0, tap, n0);
         }
@@ -485,13 +497,16 @@ conv_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           const uint32_t a_src = tiles + s * stage_bytes;
           const uint32_t b_src = p.w_resident ? w_base + (uint32_t)kit * b_bytes : a_src + a_bytes;
           // transposed product: weights are the A operand (M = channels), activations B (N = pixels)
-          const uint64_t adesc = make_kmajor_desc(b_src, p.BK);
-          const uint64_t bdesc = make_kmajor_desc(a_src, p.BK);
           const int ksteps = p.BK / 32;
-          for (int k = 0; k < ksteps; ++k) {
-            // advance 32 bytes of K inside the swizzle span: +2 in 16-byte units
-            ptx::tcgen05_mma_i8(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), p.idesc,
-                                (kit > 0 || k > 0) ? 1u : 0u);
+          for (int sub = 0; sub < subs; ++sub) {
+            // dual mode: sub-tile 0 uses weight rows 64..191 ([W; 0]), sub-tile 1 rows 0..127 ([0; W])
+            const uint64_t adesc = make_kmajor_desc(b_src + ((p.dual && sub == 0) ? 64u * (uint32_t)p.BK : 0u), p.BK);
+            const uint64_t bdesc = make_kmajor_desc(a_src + (uint32_t)sub * 128u * (uint32_t)p.BK, p.BK);
+            for (int k = 0; k < ksteps; ++k) {
+              // advance 32 bytes of K inside the swizzle span: +2 in 16-byte units
+              ptx::tcgen05_mma_i8(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), p.idesc,
+                                  (kit > 0 || k > 0 || sub > 0) ? 1u : 0u);
+            }
           }
           ptx::tcgen05_commit(bar_empty + 8 * s); // frees the stage when the MMAs retire
         }
@@ -508,11 +523,13 @@ conv_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     int t = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++t) {
-      const int m0 = (tile / n_tiles) * 128;
+      // dual mode: lanes 0..63 are the channels of the first 128 pixels, lanes 64..127 of the second
+      const int ch_base = p.dual ? (quarter & 1) * 32 : quarter * 32;
+      const int m0 = (tile / n_tiles) * m_tile + (p.dual ? 128 * (quarter >> 1) : 0);
       const int n0 = (tile % n_tiles) * p.BN;
       const int buf = t & 1;
       if (n0 != staged_n0) {
-        cc = load_chan_const(p, n0 + quarter * 32 + lane);
+        cc = load_chan_const(p, n0 + ch_base + lane);
         staged_n0 = n0;
       }
       ok = ptx::mbar_wait_bounded(bar_acc_full + 8 * buf, (uint32_t)((t >> 1) & 1), abort_flag);
@@ -524,14 +541,14 @@ conv_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       ptx::tcgen05_fence_after();
-      const int ch4 = n0 + quarter * 32 + (lane >> 2) * 4;
-      if (n0 + quarter * 32 < p.n_valid) { // warp-uniform: this lane quarter holds real channels
+      const int ch4 = n0 + ch_base + (lane >> 2) * 4;
+      if (n0 + ch_base < p.n_valid && m0 < p.M_total) { // warp-uniform: this lane quarter holds real outputs
         const uint32_t lane_addr = tmem_base + (uint32_t)buf * acc_stride + ((uint32_t)(quarter * 32) << 16);
         int8_t *out4 = p.out + (size_t)m0 * p.ldc + p.c_off + ch4;
         const bool ch4_ok = ch4 < p.n_valid;
-        if (p.act == 1) epilogue_channels<1>(p, lane_addr, out4, ch4_ok, m0, half, 2, lane, cc, ts);
-        else if (p.act == 2) epilogue_channels<2>(p, lane_addr, out4, ch4_ok, m0, half, 2, lane, cc, ts);
-        else epilogue_channels<0>(p, lane_addr, out4, ch4_ok, m0, half, 2, lane, cc, ts);
+        if (p.act == 1) epilogue_channels<1>(p, lane_addr, out4, ch4_ok, m0, half, kEpilogueWarps / 4, lane, cc, ts);
+        else if (p.act == 2) epilogue_channels<2>(p, lane_addr, out4, ch4_ok, m0, half, kEpilogueWarps / 4, lane, cc, ts);
+        else epilogue_channels<0>(p, lane_addr, out4, ch4_ok, m0, half, kEpilogueWarps / 4, lane, cc, ts);
       }
       // hand the accumulator buffer back to the MMA issuer
       ptx::tcgen05_fence_before();

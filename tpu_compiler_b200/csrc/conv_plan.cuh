@@ -252,12 +252,15 @@ inline void finish_stem_plan(StemPlan &sp, const int8_t *d_w, int rows, int kh, 
   p.idesc = make_idesc_i8(128, bn);
   p.M_total = rows;
   p.kh = kh;
-  sp.smem = kSmemHeader + 1024 + (size_t)kh * (4096 + (size_t)bn * 32);
-  const int m_tiles = (rows + 127) / 128;
+  p.dual = (oc_pad <= 64 && rows > 128) ? 1 : 0;
+  const int m_tile = p.dual ? 256 : 128;
+  const int w_rows = p.dual ? 192 : bn;
+  sp.smem = kSmemHeader + 1024 + (size_t)kh * ((size_t)m_tile * 32 + (size_t)w_rows * 32);
+  const int m_tiles = (rows + m_tile - 1) / m_tile;
   sp.grid = dim3((unsigned)(m_tiles * ((oc_pad + bn - 1) / bn)), 1, 1);
   cuuint64_t dims[3] = {32, (cuuint64_t)oc_pad, (cuuint64_t)kh};
   cuuint64_t strides[2] = {32, (cuuint64_t)32 * oc_pad};
-  cuuint32_t box[3] = {32, (cuuint32_t)bn, (cuuint32_t)kh};
+  cuuint32_t box[3] = {32, (cuuint32_t)w_rows, (cuuint32_t)kh};
   cuuint32_t es[3] = {1, 1, 1};
   CUresult r = tma_api().tiled(&sp.tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, (void *)d_w, dims, strides, box, es,
                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_32B,
@@ -274,7 +277,17 @@ inline void finish_plan(ConvPlan &pl, int rows, int taps, int k_inner, int oc_pa
   p.M_total = rows;
   p.BK = pick_bk(k_inner);
   p.c_chunks = (k_inner + p.BK - 1) / p.BK;
-  const int m_tiles = (rows + 127) / 128;
+  // Dual mode: layers with at most 64 output channels would leave half of the TMEM lanes (and half of
+  // the epilogue warps) idle; they run 256-pixel tiles instead (see the kernel). Not combined with the
+  // row-window activation mode.
+  {
+    // ... unless the whole weight set is small enough to stay resident in plain mode, which feeds
+    // fewer bytes per pixel (measured faster for the 1x1 layers with 64 outputs).
+    const size_t w_plain = (size_t)taps * p.c_chunks * 128 * p.BK;
+    const bool plain_resident = w_plain <= 48 * 1024 && 113 * 1024 - kSmemHeader - 1024 - w_plain >= 3 * (size_t)128 * p.BK;
+    p.dual = (oc_pad <= 64 && p.a_mode != 2 && rows > 128 && !plain_resident) ? 1 : 0;
+  }
+  const int m_tiles = (rows + (p.dual ? 255 : 127)) / (p.dual ? 256 : 128);
   // Transposed product: the channel tile is the tensor core's M (128 TMEM lanes, rows past the
   // padded channel count are zero-filled by TMA), the pixel tile its N (128 TMEM columns), and
   // the accumulator is double-buffered: 256 TMEM columns.
@@ -286,15 +299,16 @@ inline void finish_plan(ConvPlan &pl, int rows, int taps, int k_inner, int oc_pa
   const int k_iters = taps * p.c_chunks;
   const int n_tiles = (oc_pad + bn - 1) / bn;
   const long long total_tiles = (long long)m_tiles * n_tiles;
-  const size_t a_bytes = (size_t)128 * p.BK, b_bytes = (size_t)bn * p.BK;
+  const size_t a_bytes = (size_t)(p.dual ? 256 : 128) * p.BK, b_bytes = (size_t)(p.dual ? 192 : bn) * p.BK;
   const size_t w_all = (size_t)k_iters * b_bytes;
   // Weight-resident mode: when all K blocks of one channel tile's weights fit in 48 KB beside a useful
   // ring of activation tiles (two CTAs per SM are kept), a CTA loads them once and streams only
   // activations, which halves the bytes that have to reach shared memory per MAC. Larger weight
   // sets would force one CTA per SM, which measured slower than re-fetching the weights from L2.
   const int ctas_per_sm = 2;
-  p.w_resident = (total_tiles >= 2LL * n_tiles && w_all <= 48 * 1024) ? 1 : 0;
   const size_t budget = 113 * 1024;
+  p.w_resident = (total_tiles >= 2LL * n_tiles && w_all <= 48 * 1024 &&
+                  budget - kSmemHeader - 1024 - w_all >= 3 * a_bytes) ? 1 : 0;
   const size_t stage_bytes = p.w_resident ? a_bytes : a_bytes + b_bytes;
   const size_t ring_budget = budget - kSmemHeader - 1024 - (p.w_resident ? w_all : 0);
   int stages = (int)(ring_budget / stage_bytes);

@@ -8,9 +8,8 @@
 // checks (zero padding) and writes them as kh rows of 32 bytes (kw <= 8 taps x 4 channels) into
 // shared memory in the 32-byte-swizzled K-major layout the tensor core reads; a proxy fence hands
 // the tile to tcgen05.mma (one K=32 step per filter row). Weights [kh][Cout_pad][32] arrive by one
-// TMA copy. The same 128 threads then run the epilogue for the TMEM lane that matches their pixel.
-// Small footprint (kh x (128 + BN) x 32 B of shared memory) so that several CTAs share an SM and
-// overlap gather, MMA and epilogue.
+// TMA copy. The gathering warps then run the epilogue (channels on TMEM lanes, as in
+// conv_gemm_i8_kernel). Two CTAs share an SM and overlap gather, MMA and epilogue.
 #pragma once
 #include "conv_gemm_i8.cuh"
 
@@ -20,7 +19,7 @@ struct ConvStemParams {
   int M_total, OH, OW, H, W;
   int sh, sw, pt, pl, dh;
   int kh, kw;
-  int BN, n_valid, ldc, c_off, act, tmem_cols;
+  int BN, n_valid, ldc, c_off, act, tmem_cols, dual;
   int leaky_mp, leaky_rp, leaky_mn, leaky_rn;
   uint32_t idesc;
   const uint32_t *in; // NHWC4 int8, one 32-bit word per pixel
@@ -29,26 +28,33 @@ struct ConvStemParams {
   int *err;
 };
 
-constexpr int kStemThreads = 160;
+constexpr int kStemThreads = 32 + 256; // warp 0: weights + MMA; warps 1..8: gather + epilogue
 
-__global__ void __launch_bounds__(kStemThreads, 4)
+// Dual mode (p.dual, at most 64 output channels): the tile covers 256 pixels; the weight rows are
+// fetched as [64 zero rows][64 weight rows][64 zero rows] per filter row, and the two 128-pixel halves
+// fill TMEM lanes 0..63 and 64..127 (same construction as in conv_gemm_i8_kernel).
+__global__ void __launch_bounds__(kStemThreads, 2)
 conv_stem_i8_kernel(const __grid_constant__ CUtensorMap tmB, const ConvStemParams p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = ptx::smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t *smem = smem_raw + (base - raw);
 
-  const uint32_t bar_a = base;        // A tile written (128 arrivals)
+  const uint32_t bar_a = base;        // activation tile written (one arrival per gathering thread)
   const uint32_t bar_b = base + 8;    // weights landed (TMA)
   const uint32_t bar_acc = base + 16; // accumulator complete
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + 24);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + 28);
-  const uint32_t a_tiles = base + kSmemHeader;             // kh x 4096 B
-  const uint32_t b_tiles = a_tiles + (uint32_t)p.kh * 4096u; // kh x BN x 32 B
+  const int m_tile = p.dual ? 256 : 128;
+  const int subs = p.dual ? 2 : 1;
+  const uint32_t w_rows = p.dual ? 192u : (uint32_t)p.BN;
+  const uint32_t a_row_bytes = (uint32_t)m_tile * 32u;                 // one filter row of the pixel tile
+  const uint32_t a_tiles = base + kSmemHeader;                           // kh x m_tile x 32 B
+  const uint32_t b_tiles = a_tiles + (uint32_t)p.kh * a_row_bytes;       // kh x w_rows x 32 B
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_tiles = (p.n_valid + p.BN - 1) / p.BN;
-  const int m0 = (int)(blockIdx.x / n_tiles) * 128;
+  const int m0 = (int)(blockIdx.x / n_tiles) * m_tile;
   const int n0 = (int)(blockIdx.x % n_tiles) * p.BN;
   ConvGemmParams ep; // the shared epilogue reads these fields
   ep.BN = p.BN; ep.n_valid = p.n_valid; ep.act = p.act; ep.M_total = p.M_total; ep.ldc = p.ldc;
@@ -60,7 +66,7 @@ conv_stem_i8_kernel(const __grid_constant__ CUtensorMap tmB, const ConvStemParam
   if (*abort_flag != 0) return;
 
   if (threadIdx.x == 0) {
-    ptx::mbar_init(bar_a, 128);
+    ptx::mbar_init(bar_a, (uint32_t)m_tile);
     ptx::mbar_init(bar_b, 1);
     ptx::mbar_init(bar_acc, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -73,9 +79,9 @@ conv_stem_i8_kernel(const __grid_constant__ CUtensorMap tmB, const ConvStemParam
 
   if (warp == 0) {
     if (lane == 0) {
-      const uint32_t b_bytes = (uint32_t)p.kh * (uint32_t)p.BN * 32u;
+      const uint32_t b_bytes = (uint32_t)p.kh * w_rows * 32u;
       ptx::mbar_expect_tx(bar_b, b_bytes);
-      ptx::tma_load_3d(b_tiles, &tmB, bar_b, 0, n0, 0);
+      ptx::tma_load_3d(b_tiles, &tmB, bar_b, 0, n0 - (p.dual ? 64 : 0), 0);
       bool ok = ptx::mbar_wait_bounded(bar_b, 0u, abort_flag);
       if (!ok) {
         // the copy is still owed: wait for it (bounded) before the CTA may release shared memory
@@ -85,12 +91,14 @@ conv_stem_i8_kernel(const __grid_constant__ CUtensorMap tmB, const ConvStemParam
       ok = ok && ptx::mbar_wait_bounded(bar_a, 0u, abort_flag);
       if (ok) {
         ptx::tcgen05_fence_after();
-        for (int r = 0; r < p.kh; ++r) {
-          // transposed product: weights are the A operand (M = channels), the gathered pixels B
-          const uint64_t adesc = make_kmajor_desc(b_tiles + (uint32_t)r * (uint32_t)p.BN * 32u, 32);
-          const uint64_t bdesc = make_kmajor_desc(a_tiles + (uint32_t)r * 4096u, 32);
-          ptx::tcgen05_mma_i8(tmem_base, adesc, bdesc, p.idesc, r > 0 ? 1u : 0u);
-        }
+        for (int r = 0; r < p.kh; ++r)
+          for (int sub = 0; sub < subs; ++sub) {
+            // transposed product: weights are the A operand (M = channels), the gathered pixels B
+            const uint32_t w_r = b_tiles + (uint32_t)r * w_rows * 32u + ((p.dual && sub == 0) ? 64u * 32u : 0u);
+            const uint64_t adesc = make_kmajor_desc(w_r, 32);
+            const uint64_t bdesc = make_kmajor_desc(a_tiles + (uint32_t)r * a_row_bytes + (uint32_t)sub * 4096u, 32);
+            ptx::tcgen05_mma_i8(tmem_base, adesc, bdesc, p.idesc, (r > 0 || sub > 0) ? 1u : 0u);
+          }
         ptx::tcgen05_commit(bar_acc);
       } else {
         if (!*abort_flag) atomicExch(p.err, kErrFullWait);
@@ -98,43 +106,47 @@ conv_stem_i8_kernel(const __grid_constant__ CUtensorMap tmB, const ConvStemParam
       }
     }
   } else {
-    // ---- gather this thread's pixel: TMEM lane quarter = warp % 4
-    const int quarter = warp & 3;
-    const int row = quarter * 32 + lane;
-    const int m = m0 + row;
-    const bool row_ok = m < p.M_total;
-    int q = 0, pp = 0, nimg = 0;
-    if (row_ok) {
-      const int t = m / p.OW;
-      q = m - t * p.OW;
-      nimg = t / p.OH;
-      pp = t - nimg * p.OH;
-    }
-    const int x0 = q * p.sw - p.pl;
-    const int y0 = pp * p.sh - p.pt;
-    const uint32_t sw_bit = (uint32_t)((row >> 2) & 1); // 32-byte swizzle: 16-byte chunk ^= address bit 7
-    uint8_t *a_row = smem + kSmemHeader + row * 32;
-    for (int r = 0; r < p.kh; ++r) {
-      uint32_t w[8];
-#pragma unroll
-      for (int s = 0; s < 8; ++s) w[s] = 0u;
-      const int y = y0 + r * p.dh;
-      if (row_ok && y >= 0 && y < p.H) {
-        const uint32_t *src = p.in + ((size_t)nimg * p.H + y) * p.W;
-#pragma unroll
-        for (int s = 0; s < 8; ++s) {
-          const int x = x0 + s;
-          if (s < p.kw && x >= 0 && x < p.W) w[s] = __ldg(src + x);
-        }
+    // ---- gather: thread g of 256 owns pixel g of the tile (threads past the tile stay idle here)
+    const int g = threadIdx.x - 32;
+    if (g < m_tile) {
+      const int m = m0 + g;
+      const bool row_ok = m < p.M_total;
+      int q = 0, pp = 0, nimg = 0;
+      if (row_ok) {
+        const int t = m / p.OW;
+        q = m - t * p.OW;
+        nimg = t / p.OH;
+        pp = t - nimg * p.OH;
       }
-      uint4 *dst = reinterpret_cast<uint4 *>(a_row + (size_t)r * 4096);
-      dst[0 ^ sw_bit] = make_uint4(w[0], w[1], w[2], w[3]);
-      dst[1 ^ sw_bit] = make_uint4(w[4], w[5], w[6], w[7]);
+      const int x0 = q * p.sw - p.pl;
+      const int y0 = pp * p.sh - p.pt;
+      const uint32_t sw_bit = (uint32_t)((g >> 2) & 1); // 32-byte swizzle: 16-byte chunk ^= address bit 7
+      uint8_t *a_row = smem + kSmemHeader + g * 32;
+      for (int r = 0; r < p.kh; ++r) {
+        uint32_t w[8];
+#pragma unroll
+        for (int s = 0; s < 8; ++s) w[s] = 0u;
+        const int y = y0 + r * p.dh;
+        if (row_ok && y >= 0 && y < p.H) {
+          const uint32_t *src = p.in + ((size_t)nimg * p.H + y) * p.W;
+#pragma unroll
+          for (int s = 0; s < 8; ++s) {
+            const int x = x0 + s;
+            if (s < p.kw && x >= 0 && x < p.W) w[s] = __ldg(src + x);
+          }
+        }
+        uint4 *dst = reinterpret_cast<uint4 *>(a_row + (size_t)r * a_row_bytes);
+        dst[0 ^ sw_bit] = make_uint4(w[0], w[1], w[2], w[3]);
+        dst[1 ^ sw_bit] = make_uint4(w[4], w[5], w[6], w[7]);
+      }
+      // make the generic-proxy writes visible to the tensor core (async proxy), then signal
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_a) : "memory");
     }
-    // make the generic-proxy writes visible to the tensor core (async proxy), then signal
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_a) : "memory");
 
+    // ---- epilogue: 8 warps, two per TMEM lane quarter, each taking every other 32-pixel column group
+    const int quarter = warp & 3;
+    const int half = (warp - 1) >> 2;
     bool ok = ptx::mbar_wait_bounded(bar_acc, 0u, abort_flag);
     if (!ok && !*abort_flag) {
       atomicExch(p.err, kErrAccWait);
@@ -143,17 +155,18 @@ conv_stem_i8_kernel(const __grid_constant__ CUtensorMap tmB, const ConvStemParam
     ok = __all_sync(0xffffffffu, ok);
     if (ok) {
       ptx::tcgen05_fence_after();
-      // this thread's TMEM lane is now an output CHANNEL of the tile
-      const ChanConst cc = load_chan_const(ep, n0 + quarter * 32 + lane);
+      const int ch_base = p.dual ? (quarter & 1) * 32 : quarter * 32;
+      const int m0e = m0 + (p.dual ? 128 * (quarter >> 1) : 0);
+      const ChanConst cc = load_chan_const(ep, n0 + ch_base + lane);
       const TransposeSel ts = make_transpose_sel(lane);
-      const int ch4 = n0 + quarter * 32 + (lane >> 2) * 4;
-      if (n0 + quarter * 32 < p.n_valid) {
+      const int ch4 = n0 + ch_base + (lane >> 2) * 4;
+      if (n0 + ch_base < p.n_valid && m0e < p.M_total) {
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-        int8_t *out4 = p.out + (size_t)m0 * p.ldc + p.c_off + ch4;
+        int8_t *out4 = p.out + (size_t)m0e * p.ldc + p.c_off + ch4;
         const bool ch4_ok = ch4 < p.n_valid;
-        if (p.act == 1) epilogue_channels<1>(ep, lane_addr, out4, ch4_ok, m0, 0, 1, lane, cc, ts);
-        else if (p.act == 2) epilogue_channels<2>(ep, lane_addr, out4, ch4_ok, m0, 0, 1, lane, cc, ts);
-        else epilogue_channels<0>(ep, lane_addr, out4, ch4_ok, m0, 0, 1, lane, cc, ts);
+        if (p.act == 1) epilogue_channels<1>(ep, lane_addr, out4, ch4_ok, m0e, half, 2, lane, cc, ts);
+        else if (p.act == 2) epilogue_channels<2>(ep, lane_addr, out4, ch4_ok, m0e, half, 2, lane, cc, ts);
+        else epilogue_channels<0>(ep, lane_addr, out4, ch4_ok, m0e, half, 2, lane, cc, ts);
       }
     }
   }

@@ -403,7 +403,7 @@ public:
         finish_plan(pl, rows, g.kh, BKs, ocg_pad, I.sm_count);
         TPUCB_CHECK(p.BK == BKs && p.c_chunks == 1, "conv %s: stem tile shape mismatch", op.name.c_str());
         encode_window_map(&pl.tmA, (const int8_t *)in->dev, g, in->cp, in->wphys, BKs, stem.g);
-        encode_weight_map(&pl.tmB, d_w, ocg_pad, g.kh, BKs, p.BK, p.BN);
+        encode_weight_map(&pl.tmB, d_w, ocg_pad, g.kh, BKs, p.BK, p.dual ? 192 : p.BN);
       } else if (need_patch) {
         pl.use_patch = true;
         PatchArgs &a = pl.patch;
@@ -421,7 +421,7 @@ public:
         p.a_mode = 0;
         finish_plan(pl, rows, 1, a.kp, ocg_pad, I.sm_count);
         encode_matrix_map(&pl.tmA, pl.patch_buf, rows, a.kp, a.kp, p.BK);
-        encode_weight_map(&pl.tmB, d_w, ocg_pad, 1, a.kp, p.BK, p.BN);
+        encode_weight_map(&pl.tmB, d_w, ocg_pad, 1, a.kp, p.BK, p.dual ? 192 : p.BN);
       } else if (one_by_one) {
         auto w = pack_conv_weights(wsrc, ocg, icg, 1, 1, ocg_pad, in->cp, false, 0);
         const int8_t *d_w = I.upload(w);
@@ -429,7 +429,7 @@ public:
         p.a_mode = 0;
         finish_plan(pl, rows, 1, in->cp, ocg_pad, I.sm_count);
         encode_matrix_map(&pl.tmA, (const int8_t *)in->dev, rows, in->cp, in->cp, p.BK);
-        encode_weight_map(&pl.tmB, d_w, ocg_pad, 1, in->cp, p.BK, p.BN);
+        encode_weight_map(&pl.tmB, d_w, ocg_pad, 1, in->cp, p.BK, p.dual ? 192 : p.BN);
       } else {
         auto w = pack_conv_weights(wsrc, ocg, icg, g.kh, g.kw, ocg_pad, in->cp, false, 0);
         const int8_t *d_w = I.upload(w);
@@ -437,7 +437,7 @@ public:
         p.a_mode = 1;
         finish_plan(pl, rows, g.kh * g.kw, in->cp, ocg_pad, I.sm_count);
         encode_im2col_map(&pl.tmA, (const int8_t *)in->dev, g, in->cp, p.BK);
-        encode_weight_map(&pl.tmB, d_w, ocg_pad, g.kh * g.kw, in->cp, p.BK, p.BN);
+        encode_weight_map(&pl.tmB, d_w, ocg_pad, g.kh * g.kw, in->cp, p.BK, p.dual ? 192 : p.BN);
       }
       plans_.push_back(pl);
     }
@@ -549,7 +549,7 @@ public:
     p.a_mode = 0;
     finish_plan(pl, m_, 1, kdev_, n_pad, I.sm_count);
     encode_matrix_map(&pl.tmA, (const int8_t *)in->dev, m_, kdev_, kdev_, p.BK);
-    encode_weight_map(&pl.tmB, d_w, n_pad, 1, kdev_, p.BK, p.BN);
+    encode_weight_map(&pl.tmB, d_w, n_pad, 1, kdev_, p.BK, p.dual ? 192 : p.BN);
     plan_ = pl;
     alg_bytes = (double)m_ * k_ + (double)n_ * k_ + (double)m_ * n_ + 4.0 * n_ + 8;
   }

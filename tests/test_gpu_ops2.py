@@ -207,3 +207,20 @@ def test_fp32_ops():
     b.op("softmax", "prob", ["fc"], (2, 11), "FP32", axis=1)
     x = rng.normal(0, 1, (2, 3, 20, 20)).astype(np.float32)
     assert_close(run_both(b.text(), b.weights, {"x": x}, ["c1", "p1", "c2", "c3", "add", "scl", "gap", "fc", "prob"]))
+
+
+def test_generic_mlir_graph_runs(tmp_path):
+    """A graph in the reference's generic .mlir form, weights in the npz it names, loaded with load_mlir."""
+    from tests.test_mlir_text import MLIR, tiny_weights
+    from tpu_compiler_b200 import mlir_text, module
+    (tmp_path / "tiny.mlir").write_text(MLIR)
+    np.savez(tmp_path / "tiny_net_1a2b3c4d.npz", **tiny_weights())
+    m = module(0)
+    m.load_mlir(str(tmp_path / "tiny.mlir"))
+    x = np.random.default_rng(3).normal(0, 1, (2, 3, 16, 16)).astype(np.float32)
+    out = m.run(x)
+    text, _ = mlir_text.convert(MLIR)
+    ref = graph_runner.run(text, tiny_weights(), {"image": x})
+    assert_close({"prob": (out["prob"], ref["prob"]), "stem": (m.get_tensor("stem"), ref["stem"])})
+    assert m.get_weight_file_path().endswith("tiny_net_1a2b3c4d.npz")
+    m.close()

@@ -1032,6 +1032,11 @@ inline void Interpreter::load_module(const std::string &text) {
       k.reset(new MoveOp(*this, op, opd(0), out, 0));
     } else if (op.type == "pixelshuffle") {
       k.reset(new MoveOp(*this, op, opd(0), out, 1));
+    } else if (op.type == "relu" && dt == DT_F32) {
+      // fp32 ReLU (core/activation.cpp:168-180): the one-input fp32 eltwise kernel with its ReLU on
+      ParsedOp r = op;
+      r.attrs["do_relu"] = "1";
+      k.reset(new EltwiseOp(*this, r, {opd(0)}, out, false));
     } else if (op.type == "relu" || op.type == "leaky_relu") {
       k.reset(new LeakyReluOp(*this, op, opd(0), out, op.type == "relu"));
     } else if (op.type == "sigmoid" || op.type == "mish" || op.type == "exp" || op.type == "tanh" ||

@@ -53,6 +53,19 @@ class module:
             weights = dict(np.load(wf))
         self.load_text(text, weights)
 
+    def load_mlir(self, mlir_file, weights=None):
+        """Loads a generic-form TPU-dialect ``.mlir`` as the reference writes it; weights come from
+        the ``.npz`` its ``tpu.weight_file`` op names (looked up next to the file) unless given."""
+        from . import mlir_text
+        with open(mlir_file) as f:
+            text, wf = mlir_text.convert(f.read())
+        if weights is None:
+            weights = {}
+            if wf:
+                self._weight_file = os.path.join(os.path.dirname(os.path.abspath(mlir_file)), wf)
+                weights = dict(np.load(self._weight_file))
+        self.load_text(text, weights)
+
     def load_text(self, text, weights):
         for name, arr in weights.items():
             a = np.ascontiguousarray(arr, dtype=np.float32)

@@ -79,7 +79,10 @@ int tpucb_interp_get_details(tpucb_interp *it, int outputs, char *out, size_t ca
 /* op_info of pymlir (bindings/python/pymlir.cpp:62-97): "name\ttype\tdtype\tshape" lines */
 int tpucb_interp_get_op_info(tpucb_interp *it, char *out, size_t cap, size_t *needed);
 
-/* Options: "cuda_graph" (0/1, default 1): replay the op list as one CUDA graph. */
+/* Options: "cuda_graph" (0/1, default 1): replay the op list as one CUDA graph.
+ *          "fuse_activations" (0/1, default 1; read by the next load_module): run each
+ *          quant(INT8->BF16) -> slope-table activation -> quant(BF16->INT8) chain as one launch
+ *          that still writes all three tensors. */
 int tpucb_interp_set_option(tpucb_interp *it, const char *key, int value);
 /* Per-op device time of one eager pass (CUDA events on the interpreter's stream);
  * ms[i] belongs to the i-th line of tpucb_interp_get_op_info. Returns the op count. */

@@ -10,10 +10,12 @@ from tpu_compiler_b200 import graphs
 pytestmark = pytest.mark.gpu
 
 
-def check_all_tensors(model, data):
+def check_all_tensors(model, data, options=()):
     from tpu_compiler_b200 import module
     ref = graph_runner.run(model.text, model.weights, {"data": data})
     m = module(0)
+    for key, value in options:
+        m.set_option(key, value)
     m.load_text(model.text, model.weights)
     m.set_tensor("data", data)
     m.invoke()
@@ -38,6 +40,26 @@ def test_yolov4_style_every_tensor():
     model = graphs.yolov4_style_int8(batch=2, res=64, width=0.25, depth=(1, 1, 2, 2, 1), seed=4001)
     data = np.random.default_rng(41).uniform(0, 1, (2, 3, 64, 64)).astype(np.float32)
     check_all_tensors(model, data)
+
+
+def test_yolov4_style_every_tensor_unfused_activations():
+    """With the quant -> mish -> quant chains as three separate launches (the default runs them as one)."""
+    from tpu_compiler_b200 import module
+    model = graphs.yolov4_style_int8(batch=2, res=64, width=0.25, depth=(1, 1, 2, 2, 1), seed=4002)
+    data = np.random.default_rng(42).uniform(0, 1, (2, 3, 64, 64)).astype(np.float32)
+    check_all_tensors(model, data, options=(("fuse_activations", 0),))
+    counts = []
+    for fuse in (1, 0):
+        m = module(0)
+        m.set_option("fuse_activations", fuse)
+        m.load_text(model.text, model.weights)
+        counts.append(m.kernel_count())
+        m.close()
+    n_mish = sum(o["type"] == "mish" for o in graph_runner.parse(model.text))
+    # a chain saves two launches; chains whose result feeds a few-channel convolution keep that
+    # convolution's padded-row layout and stay unfused
+    saved = counts[1] - counts[0]
+    assert n_mish > 0 and saved % 2 == 0 and n_mish <= saved <= 2 * n_mish, (counts, n_mish)
 
 
 def test_yolov4_style_full_topology_loads_and_counts():

@@ -154,6 +154,20 @@ def test_quant_family():
                           ["f_i8_host", "f_bf16", "i8_f32", "i8_bf16", "bf16_i8", "f32_i8_tpu"]))
 
 
+def test_quant_bf16_overflow_and_wide_channels():
+    """int8 -> bf16 products that round past max-finite become +0x7f7f for either sign (F32ToBF16), and the
+    16-value vector path covers a 255-channel tensor's padding lane."""
+    rng = np.random.default_rng(66)
+    shape = (1, 255, 6, 6)
+    b = graphs.GraphBuilder(66, simulate=False)
+    b.op("input", "x", [], shape, "INT8")
+    b.op("quant", "big", ["x"], shape, "BF16", **{"from": "INT8", "to": "BF16", "scale": "3.0e36"})
+    # (BF16 -> INT8 of magnitudes past int32 is an undefined float-to-int cast in the reference: not compared)
+    b.op("quant", "small", ["x"], shape, "BF16", **{"from": "INT8", "to": "BF16", "scale": repr(1.0 / 3)})
+    b.op("quant", "small_i8", ["small"], shape, "INT8", **{"from": "BF16", "to": "INT8", "scale": "2.5"})
+    assert_exact(run_both(b.text(), b.weights, {"x": i8(rng, shape)}, ["big", "small", "small_i8"]))
+
+
 @pytest.mark.parametrize("kind", ["sigmoid", "mish", "exp", "tanh"])
 def test_lut_bf16_slope(kind):
     rng = np.random.default_rng(7)

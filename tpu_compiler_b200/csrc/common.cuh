@@ -89,6 +89,60 @@ TPUCB_HD float bf16_round(float f, bool rounding = true) {
   return bf16_bits_to_f32(f32_to_bf16_bits(f, rounding));
 }
 
+#ifdef __CUDACC__
+// Two F32ToBF16 roundings in one conversion instruction: {bf16(hi), bf16(lo)} packed in a word.
+// The hardware conversion equals the reference's add-and-shift rule whenever its result is
+// finite; a result with an all-ones exponent (inf/NaN in, or rounding past max-finite) takes
+// the exact bit rule instead, which also covers the NaN payloads that wrap in the reference.
+__device__ __forceinline__ uint32_t bf16x2_round_bits(float lo, float hi) {
+  uint32_t p;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(p) : "f"(hi), "f"(lo));
+  if (((p & 0x7f807f80u) + 0x00800080u) & 0x80008000u)
+    p = (uint32_t)f32_to_bf16_bits(lo) | ((uint32_t)f32_to_bf16_bits(hi) << 16);
+  return p;
+}
+// round(v) half-to-even as int32 (saturating at the int32 range, NaN -> 0): the integer that
+// F32ToInt8(v, 0) saturates to int8 afterwards.
+__device__ __forceinline__ int f32_to_i32_rne(float v) {
+  int r;
+  asm("cvt.rni.s32.f32 %0, %1;" : "=r"(r) : "f"(v));
+  return r;
+}
+
+// Per-channel constants of the short form of qdm_requant(acc + bias, M, r):
+//   x  = acc * M + c64,  c64 = bias * M + 2^30 (one wide multiply-add)
+//   hi = x >> 31 (floor; one funnel shift): adding 2^30 and flooring equals the reference's
+//        sign-dependent nudge followed by a division that truncates toward zero, for either sign
+//   q  = (hi + rnd - [hi < 0 and r > 0]) >> r,  rnd = 2^(r-1) (0 when r = 0): round half away
+//        from zero, as RoundingDivideByPOT does
+// With ReLU, negative results become 0 anyway: rnd moves into c64 and the sign term is dropped.
+// The value returned is not yet saturated; pack4_sat does that.
+struct QdmConst {
+  int32_t M, r, rnd, s1; // s1 = 31 when r > 0, else 32: (uint)hi >> s1 is the sign term
+  long long c64;
+};
+__device__ __forceinline__ QdmConst make_qdm_const(int32_t bias, int32_t M, int32_t r, bool relu) {
+  QdmConst c;
+  c.M = M;
+  c.r = r;
+  const long long rnd = r > 0 ? (1ll << (r - 1)) : 0ll;
+  c.c64 = (long long)bias * (long long)M + (1ll << 30);
+  if (relu) c.c64 += rnd << 31;
+  c.rnd = (int32_t)rnd;
+  c.s1 = r > 0 ? 31 : 32;
+  return c;
+}
+template <bool RELU> __device__ __forceinline__ int qdm_fast(int32_t acc, const QdmConst &q) {
+  long long x;
+  asm("mad.wide.s32 %0, %1, %2, %3;" : "=l"(x) : "r"(acc), "r"(q.M), "l"(q.c64));
+  const int32_t hi = (int32_t)__funnelshift_r((uint32_t)x, (uint32_t)(x >> 32), 31);
+  if (RELU) return max(hi, 0) >> q.r;
+  uint32_t adj;
+  asm("shr.u32 %0, %1, %2;" : "=r"(adj) : "r"((uint32_t)hi), "r"((uint32_t)q.s1)); // shifts >= 32 give 0
+  return (hi + q.rnd - (int)adj) >> q.r;
+}
+#endif
+
 // F32ToInt8(v, 0): round half to even on the magnitude, then saturate.
 __device__ __forceinline__ int f32_to_int8_rne(float v) {
   // rintf is round-half-even and symmetric in sign, identical to the reference's

@@ -142,7 +142,9 @@ public:
     t->c = (int)d[1];
     t->h = (int)d[2];
     t->w = (int)d[3];
-    int lanes = 16 / (int)t->elsize();
+    // INT8 and BF16 tensors share a channel pitch (a multiple of 16) so that the conversions
+    // between them run on whole 16-element vectors; fp32 pads to one 16-byte vector.
+    int lanes = dtype == DT_F32 ? 4 : 16;
     t->cp = round_up(t->c, lanes);
     t->wphys = t->w;
     auto lr = layout_requests.find(name);
@@ -188,6 +190,8 @@ public:
   cudaStream_t stream = nullptr;
   int *d_err = nullptr;
   bool use_graph = true;
+  bool fuse_activations = true; // set before load_module
+  void fuse_activation_chains(const std::map<std::string, int> &uses);
   cudaGraphExec_t graph_exec = nullptr;
   std::map<std::string, HostWeight> weights;
   std::map<std::string, TensorPtr> tensors;
@@ -252,11 +256,27 @@ public:
           out_->wphys, scale_);
       return;
     }
+    const bool same_layout = in_->cp == out_->cp && !out_->padded_rows() && out_->cp % 16 == 0;
+    if (same_layout && (kind_ == 3 || kind_ == 4)) {
+      size_t nvec = out_->pixels() * out_->cp / 16;
+      if (kind_ == 3)
+        quant_i8_to_bf16_vec_kernel<<<grid_for(nvec, 256, I_.sm_count), 256, 0, s>>>(
+            (const uint4 *)in_->dev, (uint4 *)out_->dev, nvec, scale_);
+      else
+        quant_bf16_to_i8_vec_kernel<<<grid_for(nvec, 256, I_.sm_count), 256, 0, s>>>(
+            (const uint4 *)in_->dev, (uint4 *)out_->dev, nvec, scale_);
+      return;
+    }
     size_t total = out_->pixels() * out_->cp;
     quant_kernel<<<grid_for(total, 256, I_.sm_count), 256, 0, s>>>(
         in_->dev, out_->dev, (size_t)out_->n * out_->h, out_->w, out_->wl, out_->wphys, out_->c, in_->cp,
         out_->cp, in_->dtype, out_->dtype, kind_ == 6 ? 5 : kind_, scale_);
   }
+
+  int kind() const { return kind_; }
+  float scale() const { return scale_; }
+  const TensorPtr &in() const { return in_; }
+  const TensorPtr &out() const { return out_; }
 
 private:
   Interpreter &I_;
@@ -457,6 +477,20 @@ public:
       launch_conv2d_f32((const float *)in_->dev, f32_w_, f32_b_, (float *)out_->dev, g_, in_->cp, out_->cp, do_relu_,
                         s, I_.sm_count);
     } else if (dw_) {
+      const DwArgs &d = dwargs_;
+      if (d.kh == 3 && d.kw == 3 && d.dh == 1 && d.dw == 1 && d.sh == d.sw && (d.sh == 1 || d.sh == 2) &&
+          in_->cp == out_->cp && !in_->padded_rows() && !out_->padded_rows()) {
+        const int tw = d.sh == 1 ? 8 : 4;
+        size_t items = (size_t)d.n * d.oh * ((d.ow + tw - 1) / tw) * (d.cp / 4);
+        int grid = grid_for(items, 128, I_.sm_count);
+        const uint32_t *src = (const uint32_t *)in_->dev;
+        uint32_t *dst = (uint32_t *)out_->dev;
+        if (d.sh == 1 && d.do_relu) dwconv3x3_i8_kernel<1, 8, true><<<grid, 128, 0, s>>>(src, dst, d);
+        else if (d.sh == 1) dwconv3x3_i8_kernel<1, 8, false><<<grid, 128, 0, s>>>(src, dst, d);
+        else if (d.do_relu) dwconv3x3_i8_kernel<2, 4, true><<<grid, 128, 0, s>>>(src, dst, d);
+        else dwconv3x3_i8_kernel<2, 4, false><<<grid, 128, 0, s>>>(src, dst, d);
+        return;
+      }
       size_t total = out_->pixels() * (out_->cp / 16);
       dwconv_i8_kernel<<<grid_for(total, 128, I_.sm_count), 128, 0, s>>>((const int8_t *)in_->dev,
                                                                           (int8_t *)out_->dev, dwargs_);
@@ -593,7 +627,10 @@ public:
   void invoke(cudaStream_t s) override {
     if (in_->dtype == DT_I8) {
       size_t total = out_->pixels() * (out_->cp / 16);
-      pool_i8_kernel<<<grid_for(total, 128, I_.sm_count), 128, 0, s>>>((const int8_t *)in_->dev, (int8_t *)out_->dev, a_);
+      if (a_.method == 0)
+        pool_max_i8_kernel<<<grid_for(total, 128, I_.sm_count), 128, 0, s>>>((const int8_t *)in_->dev, (int8_t *)out_->dev, a_);
+      else
+        pool_i8_kernel<<<grid_for(total, 128, I_.sm_count), 128, 0, s>>>((const int8_t *)in_->dev, (int8_t *)out_->dev, a_);
     } else {
       launch_pool_f32((const float *)in_->dev, (float *)out_->dev, a_, count_include_pad_, s, I_.sm_count);
     }
@@ -715,6 +752,14 @@ public:
       auto &t = ins_[i];
       size_t total = t->pixels() * t->c;
       int requant = need_quant_ && !(mult_[i] == 1 && rsh_[i] == 0);
+      if (t->c % 16 == 0 && off % 16 == 0 && t->cp % 16 == 0 && out_->cp % 16 == 0) {
+        size_t nvec = t->pixels() * (t->c / 16);
+        concat_slice_i8_vec_kernel<<<grid_for(nvec, 256, I_.sm_count), 256, 0, s>>>(
+            (const uint4 *)t->dev, (uint4 *)out_->dev, t->pixels(), t->c / 16, t->cp / 16, out_->cp / 16, off / 16,
+            mult_[i], rsh_[i], requant, do_relu_);
+        off += t->c;
+        continue;
+      }
       concat_slice_i8_kernel<<<grid_for(total, 256, I_.sm_count), 256, 0, s>>>(
           (const int8_t *)t->dev, (int8_t *)out_->dev, t->pixels(), t->c, t->cp, out_->cp, off, mult_[i], rsh_[i],
           requant, do_relu_);
@@ -829,6 +874,13 @@ public:
     }
   }
 
+  bool is_bf16_slope() const { return in_->dtype == DT_BF16 && !mantissa_; }
+  const float *base_table() const { return t0_; }
+  const float *slope_table() const { return t1_; }
+  float scale() const { return scale_; }
+  const TensorPtr &in() const { return in_; }
+  const TensorPtr &out() const { return out_; }
+
 private:
   Interpreter &I_;
   TensorPtr in_, out_;
@@ -836,6 +888,37 @@ private:
   const float *t0_ = nullptr, *t1_ = nullptr;
   bool mantissa_ = false;
   float scale_ = 1;
+};
+
+// ------------------------------------------------ fused INT8 -> BF16 activation -> INT8
+// quant(INT8->BF16), a slope-table activation and quant(BF16->INT8) whose intermediate tensors have
+// no other consumer run as one launch at the position of the first quant; all three tensors are
+// still written. The two later ops become placeholders that launch nothing.
+class ActChainOp : public OpKernel {
+public:
+  ActChainOp(Interpreter &I, const QuantOp &q0, const LutOp &lut, const QuantOp &q1)
+      : I_(I), in_(q0.in()), deq_(q0.out()), act_(lut.out()), out_(q1.out()), s_in_(q0.scale()),
+        s_lut_(lut.scale()), s_out_(q1.scale()), base_(lut.base_table()), slope_(lut.slope_table()) {
+    alg_bytes = 6.0 * out_->numel();
+  }
+  void invoke(cudaStream_t s) override {
+    size_t nvec = out_->pixels() * out_->cp / 16;
+    act_chain_i8_kernel<<<grid_for(nvec, 256, I_.sm_count), 256, 0, s>>>(
+        (const uint4 *)in_->dev, (uint4 *)deq_->dev, (uint4 *)act_->dev, (uint4 *)out_->dev, nvec, s_in_, s_lut_,
+        base_, slope_, s_out_);
+  }
+
+private:
+  Interpreter &I_;
+  TensorPtr in_, deq_, act_, out_;
+  float s_in_, s_lut_, s_out_;
+  const float *base_, *slope_;
+};
+
+class FusedAwayOp : public OpKernel {
+public:
+  void invoke(cudaStream_t) override {}
+  int kernel_launches() const override { return 0; }
 };
 
 // ------------------------------------------------------------ fp32 Scale / Softmax
@@ -907,6 +990,51 @@ inline ParsedOp parse_line(const std::string &line) {
   }
   TPUCB_CHECK(!op.name.empty(), "module text: op '%s' has no name", op.type.c_str());
   return op;
+}
+
+// Replaces every quant(INT8->BF16) -> slope-table activation -> quant(BF16->INT8) chain whose
+// intermediates feed nothing else by one ActChainOp at the first op's position.
+inline void Interpreter::fuse_activation_chains(const std::map<std::string, int> &uses) {
+  auto single_use = [&](const std::string &nm) {
+    auto it = uses.find(nm);
+    return it != uses.end() && it->second == 1;
+  };
+  const size_t n = kernels.size();
+  for (size_t i = 0; i < n; ++i) {
+    auto *q0 = dynamic_cast<QuantOp *>(kernels[i].get());
+    if (!q0 || q0->kind() != 3 || !single_use(q0->name)) continue;
+    size_t j = n, k = n;
+    for (size_t t = i + 1; t < n && j == n; ++t) {
+      auto *l = dynamic_cast<LutOp *>(kernels[t].get());
+      if (l && l->in() == q0->out()) j = t;
+    }
+    if (j == n) continue;
+    auto *lut = static_cast<LutOp *>(kernels[j].get());
+    if (!lut->is_bf16_slope() || !single_use(lut->name)) continue;
+    for (size_t t = j + 1; t < n && k == n; ++t) {
+      auto *q = dynamic_cast<QuantOp *>(kernels[t].get());
+      if (q && q->in() == lut->out()) k = t;
+    }
+    if (k == n) continue;
+    auto *q1 = static_cast<QuantOp *>(kernels[k].get());
+    if (q1->kind() != 4) continue;
+    const TensorPtr &a = q0->in(), &b = q0->out(), &c = lut->out(), &d = q1->out();
+    const bool same = a->cp == b->cp && b->cp == c->cp && c->cp == d->cp && a->cp % 16 == 0 && !a->padded_rows() &&
+                      !d->padded_rows() && a->pixels() == d->pixels();
+    if (!same) continue;
+    std::unique_ptr<OpKernel> fused(new ActChainOp(*this, *q0, *lut, *q1));
+    auto take_identity = [](OpKernel &dst, const OpKernel &src) {
+      dst.name = src.name; dst.op_type = src.op_type; dst.shape = src.shape; dst.datatype = src.datatype;
+      dst.result = src.result;
+    };
+    take_identity(*fused, *q0);
+    std::unique_ptr<OpKernel> n1(new FusedAwayOp()), n2(new FusedAwayOp());
+    take_identity(*n1, *lut);
+    take_identity(*n2, *q1);
+    kernels[i] = std::move(fused);
+    kernels[j] = std::move(n1);
+    kernels[k] = std::move(n2);
+  }
 }
 
 // loadModule / updateKernelList (MlirModuleInterpreter.cpp:73-83, 118-350).
@@ -1060,6 +1188,7 @@ inline void Interpreter::load_module(const std::string &text) {
     producer_type[op.name] = op.type;
     kernels.push_back(std::move(k));
   }
+  if (fuse_activations) fuse_activation_chains(uses);
   for (auto &k : kernels)
     if (!uses.count(k->name) && k->op_type != "input") output_details.push_back({k->name, k->result->numel()});
   TPUCB_CUDA(cudaDeviceSynchronize());

@@ -71,14 +71,18 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
                : "memory");
 }
+// The suspend-time hint lets the hardware park the waiting thread for up to that many nanoseconds
+// (it is resumed at once when the phase completes), so a warp that waits costs few issue slots:
+// the waiting producer and MMA warps otherwise compete with the epilogue for the integer pipe.
+constexpr uint32_t kWaitHintNs = 2000;
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(kWaitHintNs)
       : "memory");
   return ok != 0;
 }
@@ -194,31 +198,38 @@ constexpr int kSmemHeader = 8192; // barriers + staged per-channel parameters
 enum ConvErr { kErrFullWait = 1, kErrEmptyWait = 2, kErrAccWait = 3 };
 
 // Per-channel requantisation constants, held in registers by the thread that owns the channel.
-// With
-//   x  = acc * M + c64,   c64 = bias * M + 2^30 (+ rnd * 2^31 on the ReLU path)
-// SaturatingRoundingDoublingHighMul(acc + bias, M) is the floor shift (x >> 31): adding
-// 2^30 and flooring equals the reference's sign-dependent nudge followed by a division
-// that truncates toward zero, for either sign. RoundingDivideByPOT (round half away from
-// zero) of hi by r is (hi + rnd) >> r for hi >= 0 and (hi + rnd - (r > 0)) >> r for hi < 0,
-// with rnd = 2^(r-1) (0 when r = 0). When ReLU follows, negative results become 0 anyway,
-// so rnd can be folded into c64 and the sign handling dropped. Integer instructions issue at
-// half the FP32 rate on this SM, so the chain is kept to 4-5 of them per value: one wide
-// multiply-add, one funnel shift, the rounding add, the shift and a saturating pack that
-// converts two values per instruction.
+// The reference computes, for s = acc + bias and multiplier M in [0, 2^31),
+//   hi = SaturatingRoundingDoublingHighMul(s, M) = floor((s * M + 2^30) / 2^31)
+//        (adding 2^30 and flooring equals its sign-dependent nudge followed by a division that
+//        truncates toward zero, for either sign),
+//   q  = RoundingDivideByPOT(hi, r) = (hi + rnd - [hi < 0 and r > 0]) >> r, rnd = 2^(r-1) (0 if r = 0),
+// then saturates (and ReLU clamps at 0, so there rnd is folded into the constant and the sign term
+// dropped). Here the product is formed once, unsigned and doubled, so that hi is simply the HIGH
+// WORD of one 32 x 32 + 64 multiply-add (a signed wide multiply-add costs several instructions on
+// this SM, the unsigned one is a single one):
+//   s' = s + 2^31 (offset binary, one add of `sbias` = bias + 2^31), M2 = 2 * M (fits unsigned 32),
+//   2 * (s * M + C) = s' * M2 + (2 * C - 2^31 * M2)   (mod 2^64),  C = 2^30 (+ rnd * 2^31 with ReLU),
+//   hi = that >> 32.
+// Per value: add, wide multiply-add, then max+shift (ReLU) or shift+add+shift, and half a
+// saturating pack.
 struct ChanConst {
-  int32_t M, r, rnd, s1; // s1 = 31 when r > 0, 32 when r == 0: (uint)hi >> s1 is the "negative and r > 0" bit
-  long long c64;
+  uint32_t M2, sbias;
+  int32_t r, rnd, s1; // s1 = 31 when r > 0, 32 when r == 0: (uint)hi >> s1 is the "negative and r > 0" bit
+  unsigned long long c2;
 };
 
 __device__ __forceinline__ ChanConst load_chan_const(const ConvGemmParams &p, int n) {
   ChanConst c;
   const bool v = n < p.n_valid;
-  c.M = v ? p.mult[n] : 0;
+  const int32_t M = v ? p.mult[n] : 0;
   const int32_t b = v ? p.bias[n] : 0;
   c.r = v ? p.rshift[n] : 0;
-  const long long rnd = c.r > 0 ? (1ll << (c.r - 1)) : 0ll;
-  c.c64 = (long long)b * (long long)c.M + (1ll << 30);
-  if (p.act == 1) c.c64 += rnd << 31;
+  const unsigned long long rnd = c.r > 0 ? (1ull << (c.r - 1)) : 0ull;
+  unsigned long long C = 1ull << 30;
+  if (p.act == 1) C += rnd << 31;
+  c.M2 = (uint32_t)M << 1;
+  c.c2 = 2ull * C - ((unsigned long long)c.M2 << 31);
+  c.sbias = (uint32_t)b + 0x80000000u;
   c.rnd = (int32_t)rnd;
   c.s1 = c.r > 0 ? 31 : 32;
   return c;
@@ -227,11 +238,11 @@ __device__ __forceinline__ ChanConst load_chan_const(const ConvGemmParams &p, in
 // One requantised value BEFORE the final int8 saturation (pack4_sat applies it).
 template <int ACT>
 __device__ __forceinline__ int requant_one(int32_t acc, const ChanConst &q, const ConvGemmParams &p) {
-  long long x;
-  asm("mad.wide.s32 %0, %1, %2, %3;" : "=l"(x) : "r"(acc), "r"(q.M), "l"(q.c64));
-  const int32_t hi = (int32_t)__funnelshift_r((uint32_t)x, (uint32_t)(x >> 32), 31);
+  unsigned long long x;
+  asm("mad.wide.u32 %0, %1, %2, %3;" : "=l"(x) : "r"((uint32_t)acc + q.sbias), "r"(q.M2), "l"(q.c2));
+  const int32_t hi = (int32_t)(uint32_t)(x >> 32);
   if (ACT == 1) {
-    return max(hi, 0) >> q.r; // rnd already folded into c64; the upper clamp happens in the pack
+    return max(hi, 0) >> q.r; // rnd already folded into c2; the upper clamp happens in the pack
   }
   uint32_t adj;
   asm("shr.u32 %0, %1, %2;" : "=r"(adj) : "r"((uint32_t)hi), "r"((uint32_t)q.s1)); // shifts >= 32 give 0
@@ -295,10 +306,17 @@ __device__ __forceinline__ void epilogue_channels(const ConvGemmParams &p, uint3
                            requant_one<ACT>((int32_t)acc1[4 * k + 2], cc, p), requant_one<ACT>((int32_t)acc1[4 * k + 3], cc, p));
     }
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      const uint32_t y = transpose4x4(w[k], ts);
-      const int pix = colg + 4 * k + pj;
-      if (ch4_ok && m0 + pix < p.M_total) *reinterpret_cast<uint32_t *>(out4 + (size_t)pix * p.ldc) = y;
+    for (int k = 0; k < 8; ++k) w[k] = transpose4x4(w[k], ts);
+    int8_t *o = out4 + (size_t)(colg + pj) * p.ldc;
+    if (m0 + colg + 32 <= p.M_total) { // whole chunk in range: one guard for the eight stores
+      if (ch4_ok) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) *reinterpret_cast<uint32_t *>(o + (size_t)(4 * k) * p.ldc) = w[k];
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < 8; ++k)
+        if (ch4_ok && m0 + colg + 4 * k + pj < p.M_total) *reinterpret_cast<uint32_t *>(o + (size_t)(4 * k) * p.ldc) = w[k];
     }
   }
 }

@@ -220,6 +220,13 @@ inline std::vector<int32_t> to_i32(const std::vector<float> &v, int pad_to, bool
   return o;
 }
 
+// The tensor-core epilogue forms 2 * multiplier in 32 unsigned bits: multipliers are the
+// non-negative Q31 values the reference's quantizer emits (QuantizationArithmetic.cpp:207-247).
+inline void check_q31_multipliers(const std::vector<float> &m, const std::string &op_name) {
+  for (float v : m)
+    TPUCB_CHECK(v >= 0.0f && v < 2147483648.0f, "%s: multiplier %g is outside [0, 2^31)", op_name.c_str(), (double)v);
+}
+
 // ---------------------------------------------------------------------------- Input
 // InputOpKernel (core/input.cpp:7-24): holds the tensor set_tensor writes; no device work.
 class InputOp : public OpKernel {
@@ -325,6 +332,7 @@ public:
     TPUCB_CHECK(op.in.size() >= 7 && I.has_weight(op.in[5]) && I.has_weight(op.in[6]),
                 "conv %s: INT8 convolution needs rshift and multiplier operands (RSHIFT_AND_M_I32)", op.name.c_str());
     const int oc_pad = out->cp;
+    check_q31_multipliers(I.weight(op.in[6]).data, op.name);
     d_bias_ = I.upload(to_i32(bias, oc_pad));
     d_mult_ = I.upload(to_i32(I.weight(op.in[6]).data, oc_pad, true));
     d_rsh_ = I.upload(to_i32(I.weight(op.in[5]).data, oc_pad, true));
@@ -566,6 +574,7 @@ public:
     const int8_t *d_w = I.upload(w);
     // one (rshift, multiplier) pair per batch slice (fullyconnected.cpp:78-88) -> broadcast per column
     std::vector<float> rs(n_, I.weight(op.in[5]).data.at(0)), mu(n_, I.weight(op.in[6]).data.at(0));
+    check_q31_multipliers(mu, op.name);
     ConvPlan pl;
     std::memset(&pl.p, 0, sizeof(pl.p));
     ConvGemmParams &p = pl.p;

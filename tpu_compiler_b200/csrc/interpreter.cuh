@@ -638,6 +638,8 @@ public:
       size_t total = out_->pixels() * (out_->cp / 16);
       if (a_.method == 0)
         pool_max_i8_kernel<<<grid_for(total, 128, I_.sm_count), 128, 0, s>>>((const int8_t *)in_->dev, (int8_t *)out_->dev, a_);
+      else if (a_.kh * a_.kw >= 16)
+        pool_avg_wide_i8_kernel<<<grid_for(total * 8, 128, I_.sm_count), 128, 0, s>>>((const int8_t *)in_->dev, (int8_t *)out_->dev, a_);
       else
         pool_i8_kernel<<<grid_for(total, 128, I_.sm_count), 128, 0, s>>>((const int8_t *)in_->dev, (int8_t *)out_->dev, a_);
     } else {

@@ -371,6 +371,51 @@ __global__ void pool_i8_kernel(const int8_t *__restrict__ in, int8_t *__restrict
   }
 }
 
+// Average pooling over large windows (the global 7x7 pool before a classifier): eight lanes share
+// one (output pixel, 16-channel vector), each sums every eighth tap, and three shuffle steps add
+// the partial sums; a window is otherwise one long serial chain per thread.
+__global__ void pool_avg_wide_i8_kernel(const int8_t *__restrict__ in, int8_t *__restrict__ out, PoolArgs a) {
+  const int vecs = a.cp / 16;
+  const size_t items = (size_t)a.n * a.oh * a.ow * vecs;
+  const int sub = threadIdx.x & 7;
+  const int taps = a.kh * a.kw;
+  for (size_t i = (blockIdx.x * (size_t)blockDim.x + threadIdx.x) >> 3; i < ((items + 3) & ~(size_t)3);
+       i += ((size_t)gridDim.x * blockDim.x) >> 3) {
+    const bool live = i < items; // a warp holds four items; dead ones still take part in the shuffles
+    const size_t ii = live ? i : items - 1;
+    int v = (int)(ii % vecs);
+    size_t pix = ii / vecs;
+    int x = (int)(pix % a.ow);
+    size_t t = pix / a.ow;
+    int y = (int)(t % a.oh);
+    int b = (int)(t / a.oh);
+    int acc[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) acc[j] = 0;
+    for (int tap = sub; tap < taps; tap += 8) {
+      const int yy = y * a.sh - a.pt + tap / a.kw, xx = x * a.sw - a.pl + tap % a.kw;
+      if (yy < 0 || yy >= a.ih || xx < 0 || xx >= a.iw) continue;
+      const uint4 q = *reinterpret_cast<const uint4 *>(in + (((size_t)b * a.ih + yy) * a.iw + xx) * a.cp + v * 16);
+      madd_vec16(acc, q, 1);
+    }
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], 1);
+      acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], 2);
+      acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], 4);
+    }
+    if (live && sub == 0) {
+      const int rnd = a.rshift > 0 ? (1 << (a.rshift - 1)) : 0;
+      uint32_t o[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+        o[q] = pack4_sat((acc[4 * q] * a.mult + rnd) >> a.rshift, (acc[4 * q + 1] * a.mult + rnd) >> a.rshift,
+                         (acc[4 * q + 2] * a.mult + rnd) >> a.rshift, (acc[4 * q + 3] * a.mult + rnd) >> a.rshift);
+      *reinterpret_cast<uint4 *>(out + pix * a.cp + v * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  }
+}
+
 // ------------------------------------------------------------- depthwise 3x3 etc.
 // Depthwise convolution (groups == channels), any kh/kw/stride/dilation, zero padding.
 // Weights are packed tap-major [kh*kw][cp] so that a thread reads 16 consecutive

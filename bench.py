@@ -127,22 +127,43 @@ def run_reference(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
+# graph builder name in tpu_compiler_b200.graphs, input resolution, input value range, default batch
+WORKLOADS = {
+    "resnet50": {"builder": "resnet50_int8", "res": 224, "lo": -1.0, "batch": 128,
+                 "metric": "INT8 ResNet-50 images/sec", "name": "resnet50_v1_int8_224"},
+    "mobilenet_v2": {"builder": "mobilenet_v2_int8", "res": 224, "lo": -1.0, "batch": 128,
+                     "metric": "INT8 MobileNet-v2 images/sec", "name": "mobilenet_v2_int8_224"},
+    "yolov4": {"builder": "yolov4_style_int8", "res": 416, "lo": 0.0, "batch": 16,
+               "metric": "INT8+BF16 YOLOv4-style images/sec", "name": "yolov4_style_int8_bf16_416"},
+}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--batch", type=int, default=128, help="images per GPU per step")
+    ap.add_argument("--batch", type=int, default=None, help="images per GPU per step (default: 128 for resnet50)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-images", type=int, default=100, help="images of the bounded CPU-baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="resnet50", choices=sorted(WORKLOADS),
+                    help="resnet50 is the headline configuration; the others are the secondary graphs "
+                         "(their lines carry no cpu_baseline)")
     args = ap.parse_args()
+    wl = WORKLOADS[args.workload]
+    if args.batch is None:
+        args.batch = wl["batch"]
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
 
     if args.impl == "reference":
+        if args.workload != "resnet50":
+            if rank == 0:
+                print(json.dumps({"impl": "reference", "unavailable": "the CPU reference arm covers the resnet50 workload only"}))
+            return
         run_reference(args, rank, world)
         return
 
@@ -159,20 +180,29 @@ def main():
     import ctypes as C
 
     B = args.batch
-    model = graphs.resnet50_int8(batch=B, seed=1001)
+    if args.workload == "resnet50":
+        model = graphs.resnet50_int8(batch=B, seed=1001)
+    else:
+        model = getattr(graphs, wl["builder"])(batch=B, simulate=False)
     m = module(local_rank)
     m.load_text(model.text, model.weights)
-    out_name = model.outputs[0]
 
-    # pinned host buffers: this rank's image shard and its result
-    in_numel, out_numel = B * 3 * 224 * 224, B * 1000
+    # pinned host buffers: this rank's image shard and its results (every module output)
+    in_numel = B * 3 * wl["res"] * wl["res"]
+    shapes = {i["name"]: i["shape"] for i in m.op_info}
     L = lib()
-    hin, hout = C.c_void_p(), C.c_void_p()
+    hin = C.c_void_p()
     check(L.tpucb_host_alloc(C.byref(hin), in_numel * 4))
-    check(L.tpucb_host_alloc(C.byref(hout), out_numel * 4))
+    houts = []
+    for name in model.outputs:
+        numel = int(np.prod(shapes[name]))
+        h = C.c_void_p()
+        check(L.tpucb_host_alloc(C.byref(h), numel * 4))
+        houts.append((name, h, numel))
+    out_numel = sum(n for _, _, n in houts)
     src = np.ctypeslib.as_array(C.cast(hin, C.POINTER(C.c_float)), shape=(in_numel,))
     rng = np.random.default_rng(9000 + rank)
-    src[:] = rng.uniform(-1, 1, in_numel).astype(np.float32)
+    src[:] = rng.uniform(wl["lo"], 1, in_numel).astype(np.float32)
 
     def barrier():
         if dist is not None:
@@ -219,7 +249,8 @@ def main():
         m.launch()
         if i + 1 < args.steps:
             m.set_tensor_async("data", bufs[(i + 1) & 1], in_numel)
-        m.get_tensor_into(out_name, hout, out_numel)
+        for name, h, numel in houts:
+            m.get_tensor_into(name, h, numel)
     m.sync()
     e2e_s = time.perf_counter() - t0
     barrier()
@@ -268,7 +299,7 @@ def main():
         mem_kernels = {"achieved_gbs": other_bytes / (other_ms * 1e-3) / 1e9 if other_ms > 0 else None,
                        "peak_gbs": peaks["hbm_gbs"], "ms_per_step": other_ms}
         cpu = None
-        if not args.no_cpu_baseline and world == 1:
+        if not args.no_cpu_baseline and world == 1 and args.workload == "resnet50":
             model_b1 = graphs.resnet50_int8(batch=1, seed=1001)
             ips, dt = cpu_path_images_per_s(model_b1, args.cpu_images)
             cpu = {"value": ips, "unit": "images/s", "cores": os.cpu_count() or 1, "kind": "port",
@@ -277,10 +308,10 @@ def main():
                              % (args.cpu_images, dt)}
         act_bytes = sum(i["bytes"] for i in m.op_info)
         line = {
-            "metric": "INT8 ResNet-50 images/sec", "value": value, "unit": "images/s", "n_gpus": world,
+            "metric": wl["metric"], "value": value, "unit": "images/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-            "config": {"workload": "resnet50_v1_int8_224, batch %d per GPU, whole module per step" % B,
+            "config": {"workload": "%s, batch %d per GPU, whole module per step" % (wl["name"], B),
                        "global_batch": B * world, "parallelism": "replicas x%d (image shards, no data-path collective)" % world,
                        "l2": "per-step working set %.0f MB exceeds the 126 MB L2" % (act_bytes / 1e6),
                        "cuda_graph": True},
@@ -293,7 +324,8 @@ def main():
         }
     check(L.tpucb_host_free(hin))
     check(L.tpucb_host_free(hin2))
-    check(L.tpucb_host_free(hout))
+    for _, h, _ in houts:
+        check(L.tpucb_host_free(h))
     m.close()
     if dist is not None:
         dist.barrier()

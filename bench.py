@@ -286,8 +286,14 @@ def main():
         achieved = conv_ops / (conv_ms * 1e-3) / 1e12
         i8_tops = C.c_double(0.0)  # this library's own tcgen05 kind::i8 issue microbenchmark, live on this GPU
         check(L.tpucb_measure_i8_mma_peak(local_rank, 128, C.byref(i8_tops)))
+        # DRAM bytes per conv launch from the committed ncu capture of one step at batch 64
+        # (profiles/resnet50_int8_b64_dram_traffic.md: 10.09 MB read per launch, writes still dirty in L2 when the
+        # kernel ends), scaled by the images per launch; null for the workloads that have no capture.
+        traffic = 10.09e6 * B / 64.0 if args.workload == "resnet50" else None
         roofline = {"bound": "tensor", "achieved": achieved, "peak": int8_peak, "unit": "TOP/s",
-                    "frac": achieved / int8_peak, "traffic": None,
+                    "frac": achieved / int8_peak, "traffic": traffic,
+                    "traffic_note": "ncu dram__bytes_read+write per launch at batch 64 x batch/64; algorithmic bytes "
+                                    "per launch: %.1f MB" % (conv_bytes / max(n_conv, 1) / 1e6),
                     "kernel": "conv_gemm_i8_kernel (tcgen05 kind::i8 implicit GEMM, %d launches per step)" % n_conv,
                     "peak_source": "2 x bf16_tflops_sustained of %s peaks (no INT8 figure is measured; the 8-bit "
                                    "rate of the same tensor pipe is twice the 16-bit rate)" % peaks["source"],

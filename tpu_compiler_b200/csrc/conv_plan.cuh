@@ -243,7 +243,7 @@ inline std::vector<int8_t> pack_stem_weights(const float *w, int oc, int ic, int
   return out;
 }
 
-inline void finish_stem_plan(StemPlan &sp, const int8_t *d_w, int rows, int kh, int oc_pad) {
+inline void finish_stem_plan(StemPlan &sp, const int8_t *d_w, int rows, int kh, int oc_pad, int sm_count) {
   ConvStemParams &p = sp.p;
   const int bn = 128; // channel tile = tensor-core M; rows past oc_pad are zero-filled by TMA
   p.BN = bn;
@@ -257,7 +257,12 @@ inline void finish_stem_plan(StemPlan &sp, const int8_t *d_w, int rows, int kh, 
   const int w_rows = p.dual ? 192 : bn;
   sp.smem = kSmemHeader + 1024 + (size_t)kh * ((size_t)m_tile * 32 + (size_t)w_rows * 32);
   const int m_tiles = (rows + m_tile - 1) / m_tile;
-  sp.grid = dim3((unsigned)(m_tiles * ((oc_pad + bn - 1) / bn)), 1, 1);
+  const int n_tiles = (oc_pad + bn - 1) / bn;
+  // persistent: two CTAs per SM, a multiple of the channel-tile count (a CTA's weights never change)
+  int grid = 2 * sm_count / n_tiles * n_tiles;
+  if (grid < n_tiles) grid = n_tiles;
+  if (grid > m_tiles * n_tiles) grid = m_tiles * n_tiles;
+  sp.grid = dim3((unsigned)grid, 1, 1);
   cuuint64_t dims[3] = {32, (cuuint64_t)oc_pad, (cuuint64_t)kh};
   cuuint64_t strides[2] = {32, (cuuint64_t)32 * oc_pad};
   cuuint32_t box[3] = {32, (cuuint32_t)w_rows, (cuuint32_t)kh};

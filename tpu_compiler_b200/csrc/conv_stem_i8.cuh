@@ -8,8 +8,9 @@
 // checks (zero padding) and writes them as kh rows of 32 bytes (kw <= 8 taps x 4 channels) into
 // shared memory in the 32-byte-swizzled K-major layout the tensor core reads; a proxy fence hands
 // the tile to tcgen05.mma (one K=32 step per filter row). Weights [kh][Cout_pad][32] arrive by one
-// TMA copy. The gathering warps then run the epilogue (channels on TMEM lanes, as in
-// conv_gemm_i8_kernel). Two CTAs share an SM and overlap gather, MMA and epilogue.
+// TMA copy, once per CTA: the kernel is persistent. The gathering warps then run the epilogue
+// (channels on TMEM lanes, as in conv_gemm_i8_kernel). Two CTAs share an SM and overlap gather, MMA
+// and epilogue.
 #pragma once
 #include "conv_gemm_i8.cuh"
 
@@ -53,8 +54,12 @@ conv_stem_i8_kernel(const __grid_constant__ CUtensorMap tmB, const ConvStemParam
   const uint32_t b_tiles = a_tiles + (uint32_t)p.kh * a_row_bytes;       // kh x w_rows x 32 B
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // Persistent: the CTA keeps its channel tile's weights (one TMA copy) and walks pixel tiles
+  // tile = blockIdx.x + k * gridDim.x; the grid is a multiple of the channel-tile count, so the
+  // channel tile (tile % n_tiles) never changes for a CTA.
   const int n_tiles = (p.n_valid + p.BN - 1) / p.BN;
-  const int m0 = (int)(blockIdx.x / n_tiles) * m_tile;
+  const int m_tiles = (p.M_total + m_tile - 1) / m_tile;
+  const int total_tiles = n_tiles * m_tiles;
   const int n0 = (int)(blockIdx.x % n_tiles) * p.BN;
   ConvGemmParams ep; // the shared epilogue reads these fields
   ep.BN = p.BN; ep.n_valid = p.n_valid; ep.act = p.act; ep.M_total = p.M_total; ep.ldc = p.ldc;
@@ -66,7 +71,9 @@ conv_stem_i8_kernel(const __grid_constant__ CUtensorMap tmB, const ConvStemParam
   if (*abort_flag != 0) return;
 
   if (threadIdx.x == 0) {
-    ptx::mbar_init(bar_a, (uint32_t)m_tile);
+    // every gathering thread arrives once per tile (also those without a pixel), so that the next
+    // tile's MMAs cannot start before all epilogue warps have left the accumulator
+    ptx::mbar_init(bar_a, (uint32_t)(kStemThreads - 32));
     ptx::mbar_init(bar_b, 1);
     ptx::mbar_init(bar_acc, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -78,7 +85,7 @@ conv_stem_i8_kernel(const __grid_constant__ CUtensorMap tmB, const ConvStemParam
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
-    if (lane == 0) {
+    if (lane == 0 && (int)blockIdx.x < total_tiles) {
       const uint32_t b_bytes = (uint32_t)p.kh * w_rows * 32u;
       ptx::mbar_expect_tx(bar_b, b_bytes);
       ptx::tma_load_3d(b_tiles, &tmB, bar_b, 0, n0 - (p.dual ? 64 : 0), 0);
@@ -87,9 +94,17 @@ conv_stem_i8_kernel(const __grid_constant__ CUtensorMap tmB, const ConvStemParam
         // the copy is still owed: wait for it (bounded) before the CTA may release shared memory
         for (uint32_t it = 0; it < (1u << 20); ++it)
           if (ptx::mbar_try_wait(bar_b, 0u)) break;
+        if (!*abort_flag) atomicExch(p.err, kErrFullWait);
+        *abort_flag = 1;
       }
-      ok = ok && ptx::mbar_wait_bounded(bar_a, 0u, abort_flag);
-      if (ok) {
+      int t = 0;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++t) {
+        ok = ptx::mbar_wait_bounded(bar_a, (uint32_t)(t & 1), abort_flag);
+        if (!ok) {
+          if (!*abort_flag) atomicExch(p.err, kErrFullWait);
+          *abort_flag = 1;
+          break;
+        }
         ptx::tcgen05_fence_after();
         for (int r = 0; r < p.kh; ++r)
           for (int sub = 0; sub < subs; ++sub) {
@@ -100,65 +115,71 @@ conv_stem_i8_kernel(const __grid_constant__ CUtensorMap tmB, const ConvStemParam
             ptx::tcgen05_mma_i8(tmem_base, adesc, bdesc, p.idesc, (r > 0 || sub > 0) ? 1u : 0u);
           }
         ptx::tcgen05_commit(bar_acc);
-      } else {
-        if (!*abort_flag) atomicExch(p.err, kErrFullWait);
-        *abort_flag = 1;
       }
     }
   } else {
-    // ---- gather: thread g of 256 owns pixel g of the tile (threads past the tile stay idle here)
-    const int g = threadIdx.x - 32;
-    if (g < m_tile) {
-      const int m = m0 + g;
-      const bool row_ok = m < p.M_total;
-      int q = 0, pp = 0, nimg = 0;
-      if (row_ok) {
-        const int t = m / p.OW;
-        q = m - t * p.OW;
-        nimg = t / p.OH;
-        pp = t - nimg * p.OH;
-      }
-      const int x0 = q * p.sw - p.pl;
-      const int y0 = pp * p.sh - p.pt;
-      const uint32_t sw_bit = (uint32_t)((g >> 2) & 1); // 32-byte swizzle: 16-byte chunk ^= address bit 7
-      uint8_t *a_row = smem + kSmemHeader + g * 32;
-      for (int r = 0; r < p.kh; ++r) {
-        uint32_t w[8];
-#pragma unroll
-        for (int s = 0; s < 8; ++s) w[s] = 0u;
-        const int y = y0 + r * p.dh;
-        if (row_ok && y >= 0 && y < p.H) {
-          const uint32_t *src = p.in + ((size_t)nimg * p.H + y) * p.W;
-#pragma unroll
-          for (int s = 0; s < 8; ++s) {
-            const int x = x0 + s;
-            if (s < p.kw && x >= 0 && x < p.W) w[s] = __ldg(src + x);
-          }
-        }
-        uint4 *dst = reinterpret_cast<uint4 *>(a_row + (size_t)r * a_row_bytes);
-        dst[0 ^ sw_bit] = make_uint4(w[0], w[1], w[2], w[3]);
-        dst[1 ^ sw_bit] = make_uint4(w[4], w[5], w[6], w[7]);
-      }
-      // make the generic-proxy writes visible to the tensor core (async proxy), then signal
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-      asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_a) : "memory");
-    }
-
-    // ---- epilogue: 8 warps, two per TMEM lane quarter, each taking every other 32-pixel column group
-    const int quarter = warp & 3;
+    const int g = threadIdx.x - 32; // thread g of 256 owns pixel g of the tile
+    const int quarter = warp & 3;   // epilogue: 8 warps, two per TMEM lane quarter, alternating 32-pixel groups
     const int half = (warp - 1) >> 2;
-    bool ok = ptx::mbar_wait_bounded(bar_acc, 0u, abort_flag);
-    if (!ok && !*abort_flag) {
-      atomicExch(p.err, kErrAccWait);
-      *abort_flag = 1;
-    }
-    ok = __all_sync(0xffffffffu, ok);
-    if (ok) {
+    const int ch_base = p.dual ? (quarter & 1) * 32 : quarter * 32;
+    const ChanConst cc = load_chan_const(ep, n0 + ch_base + lane);
+    const TransposeSel ts = make_transpose_sel(lane);
+    const uint32_t sw_bit = (uint32_t)((g >> 2) & 1); // 32-byte swizzle: 16-byte chunk ^= address bit 7
+    uint8_t *a_row = smem + kSmemHeader + g * 32;
+    int t = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++t) {
+      const int m0 = (tile / n_tiles) * m_tile;
+      // ---- gather (the previous tile's MMAs have retired: this thread saw bar_acc in its epilogue)
+      if (g < m_tile) {
+        const int m = m0 + g;
+        const bool row_ok = m < p.M_total;
+        int q = 0, pp = 0, nimg = 0;
+        if (row_ok) {
+          const int tt = m / p.OW;
+          q = m - tt * p.OW;
+          nimg = tt / p.OH;
+          pp = tt - nimg * p.OH;
+        }
+        const int x0 = q * p.sw - p.pl;
+        const int y0 = pp * p.sh - p.pt;
+        const bool x_inside = x0 >= 0 && x0 + 8 <= p.W; // all eight words in range (weights past kw are zero): no per-tap checks
+        for (int r = 0; r < p.kh; ++r) {
+          uint32_t w[8];
+#pragma unroll
+          for (int s = 0; s < 8; ++s) w[s] = 0u;
+          const int y = y0 + r * p.dh;
+          if (row_ok && y >= 0 && y < p.H) {
+            const uint32_t *src = p.in + ((size_t)nimg * p.H + y) * p.W + x0;
+            if (x_inside) {
+#pragma unroll
+              for (int s = 0; s < 8; ++s) w[s] = __ldg(src + s);
+            } else {
+#pragma unroll
+              for (int s = 0; s < 8; ++s)
+                if (s < p.kw && x0 + s >= 0 && x0 + s < p.W) w[s] = __ldg(src + s);
+            }
+          }
+          uint4 *dst = reinterpret_cast<uint4 *>(a_row + (size_t)r * a_row_bytes);
+          dst[0 ^ sw_bit] = make_uint4(w[0], w[1], w[2], w[3]);
+          dst[1 ^ sw_bit] = make_uint4(w[4], w[5], w[6], w[7]);
+        }
+        // make the generic-proxy writes visible to the tensor core (async proxy)
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      }
+      ptx::tcgen05_fence_before(); // orders this thread's accumulator reads of the previous tile
+      asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_a) : "memory");
+
+      // ---- epilogue
+      ok = ptx::mbar_wait_bounded(bar_acc, (uint32_t)(t & 1), abort_flag);
+      if (!ok && !*abort_flag) {
+        atomicExch(p.err, kErrAccWait);
+        *abort_flag = 1;
+      }
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
       ptx::tcgen05_fence_after();
-      const int ch_base = p.dual ? (quarter & 1) * 32 : quarter * 32;
       const int m0e = m0 + (p.dual ? 128 * (quarter >> 1) : 0);
-      const ChanConst cc = load_chan_const(ep, n0 + ch_base + lane);
-      const TransposeSel ts = make_transpose_sel(lane);
       const int ch4 = n0 + ch_base + (lane >> 2) * 4;
       if (n0 + ch_base < p.n_valid && m0e < p.M_total) {
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);

@@ -370,7 +370,7 @@ public:
       p.c_off = 0;
       p.err = I.d_err;
       const int8_t *d_w = I.upload(pack_stem_weights(filt.data.data(), g.oc, g.ic, g.kh, g.kw, oc_pad));
-      finish_stem_plan(sp, d_w, g.n * g.oh * g.ow, g.kh, oc_pad);
+      finish_stem_plan(sp, d_w, g.n * g.oh * g.ow, g.kh, oc_pad, I.sm_count);
       stem_plans_.push_back(sp);
       return;
     }

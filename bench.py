@@ -138,6 +138,43 @@ WORKLOADS = {
 }
 
 
+def run_conv_sweep(args, local_rank):
+    """--workload conv_sweep: the single INT8 Conv2D op sweep (3x3, stride 1, pad 1; uniform int8 operands,
+    per-channel multiplier / rshift requantisation with ReLU). One JSON line with the rate of every case."""
+    from tpu_compiler_b200 import graphs, module
+    import ctypes as C
+    from tpu_compiler_b200._lib import check, lib
+    peaks = measured_peaks()
+    cases = [(c, hw, n) for n in (1, 8, 32) for c, hw in ((64, 56), (128, 28), (256, 14), (512, 7))]
+    if args.case:
+        c, hw, n = (int(v) for v in args.case.split(","))
+        cases = [(c, hw, n)]
+    i8_tops = C.c_double(0.0)
+    check(lib().tpucb_measure_i8_mma_peak(local_rank, 128, C.byref(i8_tops)))
+    rows = []
+    for c, hw, n in cases:
+        model = graphs.single_conv_i8(n=n, c_in=c, c_out=c, hw=hw, k=3, stride=1, pad=1, relu=True, seed=2000 + c + n)
+        m = module(local_rank)
+        m.load_text(model.text, model.weights)
+        m.set_tensor("x", model.meta["x"])
+        for _ in range(max(args.warmup, 3)):
+            m.invoke()
+        ms = m.time_launches(args.steps) / args.steps
+        ops = 2.0 * n * hw * hw * c * c * 9
+        rows.append({"c": c, "hw": hw, "n": n, "us": ms * 1e3, "tops": ops / (ms * 1e-3) / 1e12})
+        m.close()
+    best = max(r["tops"] for r in rows)
+    print(json.dumps({
+        "metric": "INT8 Conv2D 3x3 op sweep", "value": best, "unit": "TOP/s (best case)", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "higher_is_better": True, "dtype": "int8", "data": "synthetic",
+        "config": {"workload": "single INT8 Conv2D op, 3x3 stride 1 pad 1, C_in = C_out = c, H = W = hw, batch n; "
+                               "operands fit in L2 (back-to-back launches of one op)"},
+        "cases": rows,
+        "roofline": {"bound": "tensor", "achieved": best, "peak": 2.0 * peaks["bf16_tflops_sustained"], "unit": "TOP/s",
+                     "frac": best / (2.0 * peaks["bf16_tflops_sustained"]), "i8_mma_peak_measured": i8_tops.value}}),
+        flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -147,10 +184,15 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-images", type=int, default=100, help="images of the bounded CPU-baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="resnet50", choices=sorted(WORKLOADS),
+    ap.add_argument("--case", default=None, help="conv_sweep only: one case as c,hw,n")
+    ap.add_argument("--workload", default="resnet50", choices=sorted(WORKLOADS) + ["conv_sweep"],
                     help="resnet50 is the headline configuration; the others are the secondary graphs "
                          "(their lines carry no cpu_baseline)")
     args = ap.parse_args()
+    if args.workload == "conv_sweep":
+        if args.impl == "ours" and int(os.environ.get("RANK", "0")) == 0:
+            run_conv_sweep(args, int(os.environ.get("LOCAL_RANK", "0")))
+        return
     wl = WORKLOADS[args.workload]
     if args.batch is None:
         args.batch = wl["batch"]

@@ -71,18 +71,14 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
                : "memory");
 }
-// The suspend-time hint lets the hardware park the waiting thread for up to that many nanoseconds
-// (it is resumed at once when the phase completes), so a warp that waits costs few issue slots:
-// the waiting producer and MMA warps otherwise compete with the epilogue for the integer pipe.
-constexpr uint32_t kWaitHintNs = 2000;
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(bar), "r"(parity), "r"(kWaitHintNs)
+      : "r"(bar), "r"(parity)
       : "memory");
   return ok != 0;
 }
@@ -157,6 +153,38 @@ __device__ __forceinline__ void tcgen05_mma_i8(uint32_t d_tmem, uint64_t adesc, 
       "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
       "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
+}
+// The same MMA with the descriptors given as 32-bit halves (only the low words change between
+// K steps and stages) and, when ACCUMULATE, a constant-true accumulate predicate: the issuing
+// thread's loop carries no 64-bit arithmetic.
+template <bool ACCUMULATE>
+__device__ __forceinline__ void tcgen05_mma_i8_lohi(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                                    uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
+  if (ACCUMULATE) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+        "setp.eq.b32 p, 0, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], da, db, %5, p;\n\t}" ::"r"(d_tmem),
+        "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], da, db, %5, p;\n\t}" ::"r"(d_tmem),
+        "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
+}
+// KSTEPS MMAs of one K block (32 bytes of K each: +2 in the descriptors' 16-byte address units)
+template <int KSTEPS>
+__device__ __forceinline__ void tcgen05_mma_i8_kblock(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t hi,
+                                                      uint32_t idesc, uint32_t accumulate_first) {
+  tcgen05_mma_i8_lohi<false>(d_tmem, a_lo, hi, b_lo, hi, idesc, accumulate_first);
+#pragma unroll
+  for (int k = 1; k < KSTEPS; ++k) tcgen05_mma_i8_lohi<true>(d_tmem, a_lo + 2 * k, hi, b_lo + 2 * k, hi, idesc, 1u);
 }
 __device__ __forceinline__ void tcgen05_ld_x16(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(
@@ -286,12 +314,13 @@ __device__ __forceinline__ uint32_t transpose4x4(uint32_t w, const TransposeSel 
 //   lane_addr  TMEM address of the warp's lane quarter in the buffer
 //   out4       output address of (pixel m0, this lane's 4-channel group)
 //   ch4_ok     the 4-channel group lies inside the valid channels
+//   ncols      pixel columns of the accumulator buffer (128; 256 for the two-SM tile)
 template <int ACT>
 __device__ __forceinline__ void epilogue_channels(const ConvGemmParams &p, uint32_t lane_addr, int8_t *out4,
                                                   bool ch4_ok, int m0, int half, int halves, int lane,
-                                                  const ChanConst &cc, const TransposeSel &ts) {
+                                                  const ChanConst &cc, const TransposeSel &ts, int ncols = 128) {
   const int pj = lane & 3;
-  for (int colg = half * 32; colg < 128; colg += 32 * halves) {
+  for (int colg = half * 32; colg < ncols; colg += 32 * halves) {
     if (m0 + colg >= p.M_total) break;
     uint32_t acc0[16], acc1[16];
     ptx::tcgen05_ld_x16(lane_addr + (uint32_t)colg, acc0);
@@ -395,6 +424,8 @@ conv_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     // ---------------------------------------------------------------- producer
     if (lane == 0) {
       int it = 0; // k-iterations issued so far, across tiles
+      int ps = 0;        // ring stage of iteration `it`
+      uint32_t pph = 0;  // its phase bit
       bool ok = true;
       if (p.w_resident && (int)blockIdx.x < total_tiles) {
         const int n0w = ((int)blockIdx.x % n_tiles) * p.BN - (p.dual ? 64 : 0);
@@ -428,28 +459,27 @@ conv_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           bx_n[i] = t / p.OH;
           bx_h[i] = (t - bx_n[i] * p.OH) * p.sh - p.pt;
         }
+        // running (tap row, tap column, channel chunk) and ring (stage, phase) counters: this loop
+        // is a single thread's instruction stream, so it carries no divisions
+        int tap = 0, tr = 0, ts = 0, chunk = 0;
         for (int kit = 0; kit < k_iters; ++kit, ++it) {
-          const int s = it % p.stages;
-          const uint32_t ph = (uint32_t)(it / p.stages) & 1u;
           if (it >= p.stages) {
-            if (!ptx::mbar_wait_bounded(bar_empty + 8 * s, ph ^ 1u, abort_flag)) {
+            if (!ptx::mbar_wait_bounded(bar_empty + 8 * ps, pph ^ 1u, abort_flag)) {
               if (!*abort_flag) atomicExch(p.err, kErrEmptyWait);
               *abort_flag = 1;
               ok = false;
               break;
             }
           }
-          const int tap = kit / p.c_chunks;
-          const int c0 = (kit % p.c_chunks) * p.BK;
-          const uint32_t a_dst = tiles + s * stage_bytes;
+          const int c0 = chunk * p.BK;
+          const uint32_t a_dst = tiles + (uint32_t)ps * stage_bytes;
           const uint32_t b_dst = a_dst + a_bytes;
-          const uint32_t fb = bar_full + 8 * s;
+          const uint32_t fb = bar_full + 8 * ps;
           ptx::mbar_expect_tx(fb, stage_bytes);
           if (p.a_mode == 1) {
-            const int r = tap / p.kw, ss = tap % p.kw;
             for (int sub = 0; sub < subs; ++sub)
               ptx::tma_load_im2col_4d(a_dst + (uint32_t)sub * 128u * (uint32_t)p.BK, &tmA, fb, c0, w_base[sub],
-                                      h_base[sub], n_img[sub], (uint16_t)(ss * p.dw), (uint16_t)(r * p.dh));
+                                      h_base[sub], n_img[sub], (uint16_t)(ts * p.dw), (uint16_t)(tr * p.dh));
           } else if (p.a_mode == 2) {
             // `tap` is the filter row; each copy brings win_g consecutive output pixels' windows.
             for (int i = 0; i < n_boxes; ++i)
@@ -460,6 +490,18 @@ conv_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
               ptx::tma_load_2d(a_dst + (uint32_t)sub * 128u * (uint32_t)p.BK, &tmA, fb, c0, m0 + 128 * sub);
           }
           if (!p.w_resident) ptx::tma_load_3d(b_dst, &tmB, fb, c0, tap, n0);
+          if (++chunk == p.c_chunks) {
+            chunk = 0;
+            ++tap;
+            if (++ts == p.kw) {
+              ts = 0;
+              ++tr;
+            }
+          }
+          if (++ps == p.stages) {
+            ps = 0;
+            pph ^= 1u;
+          }
         }
       }
       if (!ok || *abort_flag) {
@@ -481,7 +523,22 @@ conv_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     // -------------------------------------------------------------- MMA issuer
     if (lane == 0) {
       int it = 0, t = 0;
+      int ms = 0;        // ring stage of iteration `it`
+      uint32_t mph = 0;  // its phase bit
       bool ok = true;
+      // Shared-memory descriptors differ between stages and K steps only in the start-address field of
+      // their low word (16-byte units, no carry out of its 14 bits below 256 KB): the low words are
+      // advanced by 32-bit adds and the issue loop stays short. A single thread feeds the tensor core,
+      // and every instruction it spends per K block beyond the MMAs themselves shows up as idle tensor
+      // cycles (measured: ~35 extra instructions per 4 MMAs cost a third of the MMA rate).
+      const uint64_t desc_ring0 = make_kmajor_desc(tiles, p.BK);
+      const uint32_t desc_hi = (uint32_t)(desc_ring0 >> 32);
+      const uint32_t desc_ring_lo = (uint32_t)desc_ring0;
+      const uint32_t desc_w_lo = (uint32_t)make_kmajor_desc(w_base, p.BK);
+      const uint32_t stage_step = stage_bytes >> 4, a_step = a_bytes >> 4, w_step = b_bytes >> 4;
+      const uint32_t sub_step = (128u * (uint32_t)p.BK) >> 4, dual_step = (64u * (uint32_t)p.BK) >> 4;
+      uint32_t m_full = bar_full, m_empty = bar_empty, ring_lo = desc_ring_lo;
+      const int ksteps = p.BK / 32;
       if (p.w_resident && (int)blockIdx.x < total_tiles) {
         if (!ptx::mbar_wait_bounded(bar_w, 0u, abort_flag)) {
           if (!*abort_flag) atomicExch(p.err, kErrFullWait);
@@ -502,31 +559,45 @@ conv_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           ptx::tcgen05_fence_after();
         }
         const uint32_t d_tmem = tmem_base + (uint32_t)buf * acc_stride;
+        uint32_t wres_lo = desc_w_lo; // weight-resident mode: descriptor (low word) of K block `kit`
         for (int kit = 0; kit < k_iters; ++kit, ++it) {
-          const int s = it % p.stages;
-          const uint32_t ph = (uint32_t)(it / p.stages) & 1u;
-          if (!ptx::mbar_wait_bounded(bar_full + 8 * s, ph, abort_flag)) {
+          if (!ptx::mbar_try_wait(m_full, mph) && !ptx::mbar_wait_bounded(m_full, mph, abort_flag)) {
             if (!*abort_flag) atomicExch(p.err, kErrFullWait);
             *abort_flag = 1;
             ok = false;
             break;
           }
           ptx::tcgen05_fence_after();
-          const uint32_t a_src = tiles + s * stage_bytes;
-          const uint32_t b_src = p.w_resident ? w_base + (uint32_t)kit * b_bytes : a_src + a_bytes;
           // transposed product: weights are the A operand (M = channels), activations B (N = pixels)
-          const int ksteps = p.BK / 32;
-          for (int sub = 0; sub < subs; ++sub) {
+          const uint32_t w_lo = p.w_resident ? wres_lo : ring_lo + a_step;
+          const uint32_t acc_first = kit > 0 ? 1u : 0u;
+          if (!p.dual) {
+            if (ksteps == 4) ptx::tcgen05_mma_i8_kblock<4>(d_tmem, w_lo, ring_lo, desc_hi, p.idesc, acc_first);
+            else if (ksteps == 2) ptx::tcgen05_mma_i8_kblock<2>(d_tmem, w_lo, ring_lo, desc_hi, p.idesc, acc_first);
+            else ptx::tcgen05_mma_i8_kblock<1>(d_tmem, w_lo, ring_lo, desc_hi, p.idesc, acc_first);
+          } else {
             // dual mode: sub-tile 0 uses weight rows 64..191 ([W; 0]), sub-tile 1 rows 0..127 ([0; W])
-            const uint64_t adesc = make_kmajor_desc(b_src + ((p.dual && sub == 0) ? 64u * (uint32_t)p.BK : 0u), p.BK);
-            const uint64_t bdesc = make_kmajor_desc(a_src + (uint32_t)sub * 128u * (uint32_t)p.BK, p.BK);
-            for (int k = 0; k < ksteps; ++k) {
-              // advance 32 bytes of K inside the swizzle span: +2 in 16-byte units
-              ptx::tcgen05_mma_i8(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), p.idesc,
-                                  (kit > 0 || k > 0 || sub > 0) ? 1u : 0u);
+            for (int sub = 0; sub < 2; ++sub) {
+              const uint32_t a_lo = w_lo + (sub == 0 ? dual_step : 0u);
+              const uint32_t b_lo = ring_lo + (uint32_t)sub * sub_step;
+              const uint32_t first = (kit > 0 || sub > 0) ? 1u : 0u;
+              if (ksteps == 4) ptx::tcgen05_mma_i8_kblock<4>(d_tmem, a_lo, b_lo, desc_hi, p.idesc, first);
+              else if (ksteps == 2) ptx::tcgen05_mma_i8_kblock<2>(d_tmem, a_lo, b_lo, desc_hi, p.idesc, first);
+              else ptx::tcgen05_mma_i8_kblock<1>(d_tmem, a_lo, b_lo, desc_hi, p.idesc, first);
             }
           }
-          ptx::tcgen05_commit(bar_empty + 8 * s); // frees the stage when the MMAs retire
+          ptx::tcgen05_commit(m_empty); // frees the stage when the MMAs retire
+          wres_lo += w_step;
+          m_full += 8;
+          m_empty += 8;
+          ring_lo += stage_step;
+          if (++ms == p.stages) {
+            ms = 0;
+            mph ^= 1u;
+            m_full = bar_full;
+            m_empty = bar_empty;
+            ring_lo = desc_ring_lo;
+          }
         }
         if (ok) ptx::tcgen05_commit(bar_acc_full + 8 * buf);
       }

@@ -142,6 +142,70 @@ def eltwise_mul_i8(inputs, multiplier, rshift, do_relu=False):
     return out
 
 
+def eltwise_maxmin_i8(inputs, multiplier, rshift, do_relu=False, is_min=False):
+    arrs, pa = _ptr_array(inputs)
+    out = np.empty_like(arrs[0])
+    m = _f32(multiplier)
+    lib().orc_eltwise_maxmin_i8(pa, len(arrs), _p(m), C.c_float(rshift), int(do_relu), int(is_min), _p(out),
+                                C.c_size_t(out.size))
+    return out
+
+
+def _shape4(a, align_right=True):
+    s = list(a.shape)
+    return ([1] * (4 - len(s)) + s) if align_right else (s + [1] * (4 - len(s)))
+
+
+def broadcast(a, b, op, is_int8=True, multiplier=None, rshift=0.0, do_relu=False):
+    """op: "add" | "sub" | "mul"; shapes are aligned to 4-D on the right (the reference's default)."""
+    a, b = _f32(a), _f32(b)
+    sa, sb = _shape4(a), _shape4(b)
+    so = [max(x, y) for x, y in zip(sa, sb)]
+    out = np.empty(so, np.float32)
+    m = _f32(multiplier if multiplier is not None else [1, 1])
+    lib().orc_broadcast(_p(a), (C.c_int * 4)(*sa), _p(b), (C.c_int * 4)(*sb), {"add": 0, "sub": 1, "mul": 2}[op],
+                        int(is_int8), _p(m), C.c_float(rshift), int(do_relu), _p(out))
+    return out
+
+
+def pad(x, pads, mode="constant"):
+    x = _f32(x)
+    s = list(x.shape)
+    so = [s[i] + pads[i] + pads[i + 4] for i in range(4)]
+    out = np.empty(so, np.float32)
+    lib().orc_pad(_p(x), (C.c_int * 4)(*s), (C.c_int * 8)(*pads), 1 if mode == "edge" else 0, _p(out))
+    return out
+
+
+def crop(x, out_shape, offsets, steps=None):
+    x = _f32(x)
+    steps = list(steps) if steps else [1, 1, 1, 1]
+    out = np.empty(list(out_shape), np.float32)
+    lib().orc_crop(_p(x), (C.c_int * 4)(*x.shape), (C.c_int * 4)(*out_shape), (C.c_int * 4)(*offsets),
+                   (C.c_int * 4)(*steps), _p(out))
+    return out
+
+
+def permute(x, order):
+    x = _f32(x)
+    out = np.empty([x.shape[o] for o in order], np.float32)
+    lib().orc_permute(_p(x), (C.c_int * 4)(*x.shape), (C.c_int * 4)(*order), _p(out))
+    return out
+
+
+def reduce(x, axes, kind, is_int8=True, multiplier=1.0, rshift=0.0):
+    """kind: "mean" | "sum" | "max" | "min" over consecutive axes; the reduced axes are dropped."""
+    x = _f32(x)
+    a0, a1 = axes[0], axes[-1] + 1
+    outer = int(np.prod(x.shape[:a0], dtype=np.int64))
+    axis = int(np.prod(x.shape[a0:a1], dtype=np.int64))
+    inner = int(np.prod(x.shape[a1:], dtype=np.int64))
+    out = np.empty(list(x.shape[:a0]) + list(x.shape[a1:]), np.float32)
+    lib().orc_reduce(_p(x), outer, axis, inner, {"mean": 0, "sum": 1, "max": 2, "min": 3}[kind], int(is_int8),
+                     C.c_float(multiplier), C.c_float(rshift), _p(out))
+    return out
+
+
 def concat_c(inputs, multiplier=None, rshift=None, do_relu=False):
     arrs, pa = _ptr_array(inputs)
     n, _, h, w = arrs[0].shape

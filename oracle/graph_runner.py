@@ -90,6 +90,28 @@ def run(text, weights, inputs, upto=None):
             else:
                 coeff = [float(c) for c in a["coeff"].split(",")] if "coeff" in a else None
                 out = O.eltwise_add_f32(xs, coeff, bool(_i(a, "do_relu")))
+        elif t in ("eltwise_max", "eltwise_min"):
+            n_in = sum(1 for nm in ins if nm in T)
+            out = O.eltwise_maxmin_i8([T[nm] for nm in ins[:n_in]], W(n_in + 3), float(W(n_in + 2)[0]),
+                                      bool(_i(a, "do_relu")), is_min=(t == "eltwise_min"))
+        elif t in ("broadcast_add", "broadcast_sub", "broadcast_mul"):
+            is_i8 = op["dtype"] == "INT8"
+            out = O.broadcast(X(0), X(1), t.split("_")[1], is_int8=is_i8, multiplier=W(5) if is_i8 else None,
+                              rshift=float(W(4)[0]) if is_i8 else 0.0, do_relu=bool(_i(a, "do_relu")))
+            out = out.reshape(op["shape"])
+        elif t == "pad":
+            out = O.pad(X(0), [int(v) for v in a["pads"].split(",")], a.get("mode", "constant"))
+        elif t == "crop":
+            steps = [int(v) for v in a["steps"].split(",")] if "steps" in a else None
+            out = O.crop(X(0), op["shape"], [int(v) for v in a["crop_offset"].split(",")], steps)
+        elif t == "permute":
+            out = O.permute(X(0), [int(v) for v in a["order"].split(",")])
+        elif t in ("reduce_mean", "reduce_sum", "reduce_max", "reduce_min"):
+            is_i8 = op["dtype"] == "INT8"
+            mu = float(W(4)[0]) if (is_i8 and W(4) is not None) else 1.0
+            rs = float(W(3)[0]) if (is_i8 and W(3) is not None) else 0.0
+            out = O.reduce(X(0), [int(v) for v in a["axes"].split(",")], t.split("_")[1], is_int8=is_i8,
+                           multiplier=mu, rshift=rs).reshape(op["shape"])
         elif t == "concat":
             xs = [T[n] for n in ins if n in T]
             nin = len(xs)

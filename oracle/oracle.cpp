@@ -604,4 +604,130 @@ float orc_kld_threshold(const int *data, float width, long long N, float *kl_out
   return width * (m_min + 1) * BINS;
 }
 
+// ---------------------------------------------------------------------------
+// Eltwise max / min, INT8 (core/eltwise.cpp:143-181 and :225-263): every input is multiplied by
+// its int8 multiplier, the extremum taken, optional ReLU, then one rshift + saturation.
+// ---------------------------------------------------------------------------
+void orc_eltwise_maxmin_i8(const float *const *ins, int nin, const float *multiplier, float rshift,
+                           int do_relu, int is_min, float *out, size_t size) {
+  for (size_t i = 0; i < size; ++i) {
+    float v = ins[0][i] * (float)(int8_t)multiplier[0];
+    for (int k = 1; k < nin; ++k) {
+      float x = ins[k][i] * (float)(int8_t)multiplier[k];
+      v = is_min ? (v < x ? v : x) : (v > x ? v : x);
+    }
+    if (do_relu && v < 0) v = 0;
+    out[i] = (float)orc_rshift_f32(v, (uint32_t)rshift);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Broadcast add / sub / mul (core/broadcast.cpp:45-156). op: 0 add, 1 sub, 2 mul. A dimension of
+// extent 1 repeats. INT8: add/sub scale each input by its int8 multiplier and end with rshift +
+// saturation; mul ends with the QDM requantisation by multiplier[0]. fp32: plain arithmetic.
+// ---------------------------------------------------------------------------
+void orc_broadcast(const float *a, const int *sa, const float *b, const int *sb, int op, int is_int8,
+                   const float *multiplier, float rshift, int do_relu, float *out) {
+  const int on = std::max(sa[0], sb[0]), oc = std::max(sa[1], sb[1]), oh = std::max(sa[2], sb[2]),
+            ow = std::max(sa[3], sb[3]);
+  size_t idx = 0;
+  for (int n = 0; n < on; ++n)
+    for (int c = 0; c < oc; ++c)
+      for (int h = 0; h < oh; ++h)
+        for (int w = 0; w < ow; ++w) {
+          size_t i0 = (((size_t)(sa[0] == 1 ? 0 : n) * sa[1] + (sa[1] == 1 ? 0 : c)) * sa[2] + (sa[2] == 1 ? 0 : h)) * sa[3] +
+                      (sa[3] == 1 ? 0 : w);
+          size_t i1 = (((size_t)(sb[0] == 1 ? 0 : n) * sb[1] + (sb[1] == 1 ? 0 : c)) * sb[2] + (sb[2] == 1 ? 0 : h)) * sb[3] +
+                      (sb[3] == 1 ? 0 : w);
+          float x = a[i0], y = b[i1], v;
+          if (op == 2) {
+            v = x * y;
+          } else {
+            if (is_int8) {
+              x *= (float)(int8_t)multiplier[0];
+              y *= (float)(int8_t)multiplier[1];
+            }
+            v = op == 0 ? x + y : x - y;
+          }
+          if (do_relu && v < 0) v = 0;
+          if (is_int8)
+            v = op == 2 ? (float)orc_qdm_f32(v, (uint32_t)rshift, (uint32_t)multiplier[0])
+                        : (float)orc_rshift_f32(v, (uint32_t)rshift);
+          out[idx++] = v;
+        }
+}
+
+// ---------------------------------------------------------------------------
+// Pad (core/pad.cpp:7-141). pads = {n, c, h, w begin; n, c, h, w end}. mode 0 ("constant"): the body
+// is copied, negative pads cut; the reference never writes const_val, the border keeps the zero the
+// result tensor was created with. mode 1 ("edge"): h/w borders replicate the nearest body value.
+// ---------------------------------------------------------------------------
+void orc_pad(const float *in, const int *s, const int *pads, int mode, float *out) {
+  const int on = s[0] + pads[0] + pads[4], oc = s[1] + pads[1] + pads[5], oh = s[2] + pads[2] + pads[6],
+            ow = s[3] + pads[3] + pads[7];
+  for (int n = 0; n < on; ++n)
+    for (int c = 0; c < oc; ++c)
+      for (int h = 0; h < oh; ++h)
+        for (int w = 0; w < ow; ++w) {
+          int in_n = n - pads[0], in_c = c - pads[1], in_h = h - pads[2], in_w = w - pads[3];
+          if (mode == 1) {
+            in_h = std::min(std::max(in_h, 0), s[2] - 1);
+            in_w = std::min(std::max(in_w, 0), s[3] - 1);
+          }
+          float v = 0.0f;
+          if (in_n >= 0 && in_n < s[0] && in_c >= 0 && in_c < s[1] && in_h >= 0 && in_h < s[2] && in_w >= 0 &&
+              in_w < s[3])
+            v = in[(((size_t)in_n * s[1] + in_c) * s[2] + in_h) * s[3] + in_w];
+          out[(((size_t)n * oc + c) * oh + h) * ow + w] = v;
+        }
+}
+
+// Crop (core/crop.cpp:18-92): out[n,c,h,w] = in[n*step0 + off0, c*step1 + off1, ...].
+void orc_crop(const float *in, const int *s, const int *os, const int *off, const int *steps, float *out) {
+  for (int n = 0; n < os[0]; ++n)
+    for (int c = 0; c < os[1]; ++c)
+      for (int h = 0; h < os[2]; ++h)
+        for (int w = 0; w < os[3]; ++w)
+          out[(((size_t)n * os[1] + c) * os[2] + h) * os[3] + w] =
+              in[(((size_t)(n * steps[0] + off[0]) * s[1] + (c * steps[1] + off[1])) * s[2] + (h * steps[2] + off[2])) * s[3] +
+                 (w * steps[3] + off[3])];
+}
+
+// Permute (core/permute.cpp:6-33): output dimension k is input dimension order[k].
+void orc_permute(const float *in, const int *s, const int *order, float *out) {
+  for (int n = 0; n < s[0]; ++n)
+    for (int c = 0; c < s[1]; ++c)
+      for (int h = 0; h < s[2]; ++h)
+        for (int w = 0; w < s[3]; ++w) {
+          const int cur[4] = {n, c, h, w};
+          size_t o = (((size_t)cur[order[0]] * s[order[1]] + cur[order[1]]) * s[order[2]] + cur[order[2]]) * s[order[3]] +
+                     cur[order[3]];
+          out[o] = in[(((size_t)n * s[1] + c) * s[2] + h) * s[3] + w];
+        }
+}
+
+// Reduce over consecutive axes (core/reduce.cpp:52-115). type: 0 mean, 1 sum, 2 max, 3 min. INT8 mean
+// leaves the division to the multiplier / rshift pair (non-QDM) that follows when it is not (1, 0).
+void orc_reduce(const float *in, int outer, int axis, int inner, int type, int is_int8, float multiplier,
+                float rshift, float *out) {
+  for (int o = 0; o < outer; ++o)
+    for (int i = 0; i < inner; ++i) {
+      float v;
+      if (type <= 1) {
+        float sum = 0.0f;
+        for (int a = 0; a < axis; ++a) sum += in[((size_t)o * axis + a) * inner + i];
+        v = (type == 0 && !is_int8) ? sum / axis : sum;
+      } else {
+        v = in[(size_t)o * axis * inner + i];
+        for (int a = 1; a < axis; ++a) {
+          float x = in[((size_t)o * axis + a) * inner + i];
+          if (type == 2 ? x > v : x < v) v = x;
+        }
+      }
+      if (is_int8 && (rshift != 0 || multiplier != 1))
+        v = (float)orc_mul_rshift_f32(v, (uint32_t)rshift, (uint32_t)multiplier);
+      out[(size_t)o * inner + i] = v;
+    }
+}
+
 } // extern "C"

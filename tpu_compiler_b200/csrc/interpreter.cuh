@@ -9,6 +9,7 @@
 #include "conv_plan.cuh"
 #include "f32_kernels.cuh"
 #include "calib_kernels.cuh"
+#include "extra_kernels.cuh"
 
 #include <algorithm>
 #include <cmath>
@@ -36,6 +37,16 @@ struct ParsedOp {
   std::string gets(const char *k, const char *def = "") const {
     auto it = attrs.find(k);
     return it == attrs.end() ? std::string(def) : it->second;
+  }
+  // comma-separated integer list attribute (I32ArrayAttr in the reference's op definitions)
+  std::vector<int> getl(const char *k) const {
+    std::vector<int> v;
+    auto it = attrs.find(k);
+    if (it == attrs.end()) return v;
+    std::stringstream ss(it->second);
+    std::string tok;
+    while (std::getline(ss, tok, ',')) v.push_back(atoi(tok.c_str()));
+    return v;
   }
 };
 
@@ -932,6 +943,196 @@ public:
   int kernel_launches() const override { return 0; }
 };
 
+// ------------------------------------------------- ops of neighbouring networks
+inline TensorGeom geom_of(const TensorPtr &t) { return TensorGeom{t->n, t->c, t->h, t->w, t->cp, t->wl, t->wphys}; }
+// the reference's getNCHW: a shape of rank < 4 padded with ones on the left (align_right) or right
+inline void shape4_of(const TensorPtr &t, bool align_right, int (&s)[4]) {
+  const int r = (int)t->shape.size();
+  for (int i = 0; i < 4; ++i) s[i] = 1;
+  for (int i = 0; i < r; ++i) s[align_right ? 4 - r + i : i] = (int)t->shape[i];
+}
+
+// EltwiseMaxOpKernel / EltwiseMinOpKernel, INT8 (core/eltwise.cpp:100-263).
+class EltwiseMaxMinOp : public OpKernel {
+public:
+  EltwiseMaxMinOp(Interpreter &I, const ParsedOp &op, std::vector<TensorPtr> ins, TensorPtr out, bool is_min)
+      : I_(I), out_(out) {
+    const int nin = (int)ins.size();
+    TPUCB_CHECK(nin >= 1 && nin <= 4, "%s %s: %d inputs not supported (max 4)", op.type.c_str(), op.name.c_str(), nin);
+    TPUCB_CHECK(out->dtype == DT_I8, "%s %s: only INT8 is implemented", op.type.c_str(), op.name.c_str());
+    for (auto &t : ins)
+      TPUCB_CHECK(t->bytes() == out->bytes() && t->dtype == DT_I8 && !t->padded_rows(), "%s %s: operand %s differs in shape or type",
+                  op.type.c_str(), op.name.c_str(), t->name.c_str());
+    TPUCB_CHECK((int)op.in.size() >= nin + 4 && I.has_weight(op.in[nin + 2]) && I.has_weight(op.in[nin + 3]),
+                "%s %s: INT8 needs rshift and multiplier operands", op.type.c_str(), op.name.c_str());
+    a_.nin = nin;
+    a_.do_relu = op.geti("do_relu", 0);
+    a_.is_min = is_min ? 1 : 0;
+    a_.rshift = (int)(uint32_t)I.weight(op.in[nin + 2]).data.at(0);
+    for (int i = 0; i < nin; ++i) {
+      a_.in[i] = (const int8_t *)ins[i]->dev;
+      a_.mult[i] = (int)(int8_t)I.weight(op.in[nin + 3]).data.at(i);
+    }
+    alg_bytes = (double)(nin + 1) * out->numel();
+  }
+  void invoke(cudaStream_t s) override {
+    size_t nvec = out_->bytes() / 16;
+    eltwise_maxmin_i8_kernel<<<grid_for(nvec, 256, I_.sm_count), 256, 0, s>>>(a_, (int8_t *)out_->dev, nvec);
+  }
+
+private:
+  Interpreter &I_;
+  TensorPtr out_;
+  MaxMinArgs a_;
+};
+
+// BroadcastAdd / Sub / Mul (core/broadcast.cpp:8-156), INT8 and fp32.
+class BroadcastOp : public OpKernel {
+public:
+  BroadcastOp(Interpreter &I, const ParsedOp &op, TensorPtr a, TensorPtr b, TensorPtr out) : I_(I), a_(a), b_(b), out_(out) {
+    TPUCB_CHECK(a->dtype == out->dtype && b->dtype == out->dtype && (out->dtype == DT_I8 || out->dtype == DT_F32),
+                "%s %s: operands and result must all be INT8 or all fp32", op.type.c_str(), op.name.c_str());
+    const bool align_right = op.geti("align_right", 1) != 0;
+    shape4_of(a, align_right, p_.sa);
+    shape4_of(b, align_right, p_.sb);
+    size_t total = 1;
+    for (int i = 0; i < 4; ++i) {
+      p_.so[i] = std::max(p_.sa[i], p_.sb[i]);
+      TPUCB_CHECK((p_.sa[i] == p_.so[i] || p_.sa[i] == 1) && (p_.sb[i] == p_.so[i] || p_.sb[i] == 1),
+                  "%s %s: shapes do not broadcast", op.type.c_str(), op.name.c_str());
+      total *= (size_t)p_.so[i];
+    }
+    TPUCB_CHECK(total == out->numel(), "%s %s: result has %zu values, broadcast gives %zu", op.type.c_str(), op.name.c_str(),
+                out->numel(), total);
+    p_.ga = geom_of(a); p_.gb = geom_of(b); p_.go = geom_of(out);
+    p_.op = op.type == "broadcast_add" ? 0 : (op.type == "broadcast_sub" ? 1 : 2);
+    p_.dt = out->dtype;
+    p_.do_relu = op.geti("do_relu", 0);
+    p_.mult0 = p_.mult1 = 1;
+    p_.rshift = 0;
+    if (out->dtype == DT_I8) {
+      // operands: a, b, quant_scale, quant_zeropoint, quant_rshift, quant_multiplier
+      TPUCB_CHECK(op.in.size() >= 6 && I.has_weight(op.in[4]) && I.has_weight(op.in[5]),
+                  "%s %s: INT8 needs rshift and multiplier operands", op.type.c_str(), op.name.c_str());
+      const auto &mu = I.weight(op.in[5]).data;
+      p_.rshift = (int)(uint32_t)I.weight(op.in[4]).data.at(0);
+      if (p_.op == 2) {
+        p_.mult0 = (int)(uint32_t)mu.at(0);
+      } else {
+        p_.mult0 = (int)(int8_t)mu.at(0);
+        p_.mult1 = (int)(int8_t)mu.at(1);
+      }
+    }
+    alg_bytes = ((double)a->numel() + b->numel() + out->numel()) * out->elsize();
+  }
+  void invoke(cudaStream_t s) override {
+    broadcast_kernel<<<grid_for(out_->numel(), 256, I_.sm_count), 256, 0, s>>>(a_->dev, b_->dev, out_->dev, p_);
+  }
+
+private:
+  Interpreter &I_;
+  TensorPtr a_, b_, out_;
+  BroadcastArgs p_;
+};
+
+// PadOpKernel (core/pad.cpp:112-141), CropOpKernel (core/crop.cpp:45-92), PermuteOpKernel (core/permute.cpp:35-45).
+class RemapOp : public OpKernel {
+public:
+  RemapOp(Interpreter &I, const ParsedOp &op, TensorPtr in, TensorPtr out) : I_(I), in_(in), out_(out) {
+    TPUCB_CHECK(in->dtype == out->dtype, "%s %s: input and result types differ", op.type.c_str(), op.name.c_str());
+    shape4_of(in, false, p_.si);
+    shape4_of(out, false, p_.so);
+    p_.gi = geom_of(in); p_.go = geom_of(out);
+    p_.es = (int)out->elsize();
+    for (int i = 0; i < 4; ++i) { p_.a[i] = 0; p_.b[i] = 1; }
+    if (op.type == "pad") {
+      std::vector<int> pads = op.getl("pads");
+      TPUCB_CHECK(pads.size() == 8, "pad %s: pads needs 8 entries", op.name.c_str());
+      p_.mode = op.gets("mode", "constant") == "edge" ? 1 : 0;
+      for (int i = 0; i < 4; ++i) {
+        p_.a[i] = pads[i];
+        TPUCB_CHECK(p_.si[i] + pads[i] + pads[i + 4] == p_.so[i], "pad %s: result shape does not match the pads", op.name.c_str());
+      }
+      if (p_.mode == 1)
+        TPUCB_CHECK(pads[0] == 0 && pads[1] == 0 && pads[4] == 0 && pads[5] == 0, "pad %s: edge mode pads height and width only",
+                    op.name.c_str());
+    } else if (op.type == "crop") {
+      std::vector<int> off = op.getl("crop_offset"), steps = op.getl("steps");
+      p_.mode = 2;
+      for (int i = 0; i < 4; ++i) {
+        p_.a[i] = i < (int)off.size() ? off[i] : 0;
+        p_.b[i] = i < (int)steps.size() ? steps[i] : 1;
+        TPUCB_CHECK(p_.b[i] >= 1 && p_.a[i] >= 0 && (p_.so[i] - 1) * p_.b[i] + p_.a[i] < p_.si[i],
+                    "crop %s: window leaves the input in dimension %d", op.name.c_str(), i);
+      }
+    } else {
+      std::vector<int> order = op.getl("order");
+      TPUCB_CHECK(order.size() == 4, "permute %s: order needs 4 entries", op.name.c_str());
+      p_.mode = 3;
+      int seen = 0;
+      for (int i = 0; i < 4; ++i) {
+        TPUCB_CHECK(order[i] >= 0 && order[i] < 4, "permute %s: bad order", op.name.c_str());
+        seen |= 1 << order[i];
+        p_.a[i] = order[i];
+        TPUCB_CHECK(p_.so[i] == p_.si[order[i]], "permute %s: result shape does not match the order", op.name.c_str());
+      }
+      TPUCB_CHECK(seen == 15, "permute %s: order is not a permutation", op.name.c_str());
+    }
+    alg_bytes = ((double)std::min(in->numel(), out->numel()) + out->numel()) * out->elsize();
+  }
+  void invoke(cudaStream_t s) override {
+    remap_kernel<<<grid_for(out_->numel(), 256, I_.sm_count), 256, 0, s>>>((const uint8_t *)in_->dev, (uint8_t *)out_->dev, p_);
+  }
+
+private:
+  Interpreter &I_;
+  TensorPtr in_, out_;
+  RemapArgs p_;
+};
+
+// ReduceOpKernel (core/reduce.cpp:10-115): mean / sum / max / min over consecutive axes, INT8 and fp32.
+class ReduceOp : public OpKernel {
+public:
+  ReduceOp(Interpreter &I, const ParsedOp &op, TensorPtr in, TensorPtr out) : I_(I), in_(in), out_(out) {
+    TPUCB_CHECK(in->dtype == out->dtype && (out->dtype == DT_I8 || out->dtype == DT_F32), "%s %s: INT8 or fp32 only",
+                op.type.c_str(), op.name.c_str());
+    std::vector<int> axes = op.getl("axes");
+    TPUCB_CHECK(!axes.empty(), "%s %s: axes missing", op.type.c_str(), op.name.c_str());
+    for (size_t i = 1; i < axes.size(); ++i)
+      TPUCB_CHECK(axes[i] == axes[i - 1] + 1, "%s %s: axes must be consecutive", op.type.c_str(), op.name.c_str());
+    const int rank = (int)in->shape.size();
+    TPUCB_CHECK(axes.front() >= 0 && axes.back() < rank, "%s %s: axis out of range", op.type.c_str(), op.name.c_str());
+    long long outer = 1, axis = 1, inner = 1;
+    for (int i = 0; i < rank; ++i) {
+      if (i < axes.front()) outer *= in->shape[i];
+      else if (i <= axes.back()) axis *= in->shape[i];
+      else inner *= in->shape[i];
+    }
+    TPUCB_CHECK((size_t)(outer * inner) == out->numel(), "%s %s: result has %zu values, expected %lld", op.type.c_str(),
+                op.name.c_str(), out->numel(), outer * inner);
+    p_.gi = geom_of(in); p_.go = geom_of(out);
+    p_.outer = (int)outer; p_.axis = (int)axis; p_.inner = (int)inner;
+    p_.type = op.type == "reduce_mean" ? 0 : (op.type == "reduce_sum" ? 1 : (op.type == "reduce_max" ? 2 : 3));
+    p_.dt = out->dtype;
+    p_.mult = 1; p_.rshift = 0;
+    if (out->dtype == DT_I8) {
+      // operands: input, quant_scale, quant_zeropoint, quant_rshift, quant_multiplier
+      if (op.in.size() > 3 && I.has_weight(op.in[3])) p_.rshift = (int)(uint32_t)I.weight(op.in[3]).data.at(0);
+      if (op.in.size() > 4 && I.has_weight(op.in[4])) p_.mult = (int)(uint32_t)I.weight(op.in[4]).data.at(0);
+    }
+    p_.requant = (p_.rshift != 0 || p_.mult != 1) ? 1 : 0;
+    alg_bytes = ((double)in->numel() + out->numel()) * out->elsize();
+  }
+  void invoke(cudaStream_t s) override {
+    reduce_kernel<<<grid_for(out_->numel(), 128, I_.sm_count), 128, 0, s>>>(in_->dev, out_->dev, p_);
+  }
+
+private:
+  Interpreter &I_;
+  TensorPtr in_, out_;
+  ReduceArgs p_;
+};
+
 // ------------------------------------------------------------ fp32 Scale / Softmax
 // ScaleOpKernel (core/scale.cpp:15-37), SoftmaxOpKernel::invoke_fp32 (core/softmax.cpp:49-86).
 class ScaleOp : public OpKernel {
@@ -1162,6 +1363,17 @@ inline void Interpreter::load_module(const std::string &text) {
       for (auto &nm : op.in)
         if (tensors.count(nm)) ins.push_back(tensors[nm]);
       k.reset(new EltwiseOp(*this, op, ins, out, op.type == "eltwise_mul"));
+    } else if (op.type == "eltwise_max" || op.type == "eltwise_min") {
+      std::vector<TensorPtr> ins;
+      for (auto &nm : op.in)
+        if (tensors.count(nm)) ins.push_back(tensors[nm]);
+      k.reset(new EltwiseMaxMinOp(*this, op, ins, out, op.type == "eltwise_min"));
+    } else if (op.type == "broadcast_add" || op.type == "broadcast_sub" || op.type == "broadcast_mul") {
+      k.reset(new BroadcastOp(*this, op, opd(0), opd(1), out));
+    } else if (op.type == "pad" || op.type == "crop" || op.type == "permute") {
+      k.reset(new RemapOp(*this, op, opd(0), out));
+    } else if (op.type == "reduce_mean" || op.type == "reduce_sum" || op.type == "reduce_max" || op.type == "reduce_min") {
+      k.reset(new ReduceOp(*this, op, opd(0), out));
     } else if (op.type == "concat") {
       std::vector<TensorPtr> ins;
       for (auto &nm : op.in)

@@ -174,6 +174,21 @@ def convert(mlir_text):
             kv = {"negative_slope": repr(float(attrs.get("negative_slope", 0.0)))}
         elif op == "softmax":
             kv = {"axis": int(attrs.get("axis", 1))}
+        elif op in ("eltwise_max", "eltwise_min"):
+            kv = {"do_relu": int(bool(attrs.get("do_relu", False)))}
+        elif op in ("broadcast_add", "broadcast_sub", "broadcast_mul"):
+            kv = {"do_relu": int(bool(attrs.get("do_relu", False))), "align_right": int(bool(attrs.get("align_right", True)))}
+        elif op == "pad":
+            kv = {"pads": ",".join(str(int(v)) for v in attrs.get("pads", [])), "mode": attrs.get("mode", "constant"),
+                  "const_val": repr(float(attrs.get("const_val", 0.0)))}
+        elif op == "crop":
+            kv = {"crop_offset": ",".join(str(int(v)) for v in attrs.get("crop_offset", []))}
+            if attrs.get("steps"):
+                kv["steps"] = ",".join(str(int(v)) for v in attrs["steps"])
+        elif op == "permute":
+            kv = {"order": ",".join(str(int(v)) for v in attrs.get("order", []))}
+        elif op in ("reduce_mean", "reduce_sum", "reduce_max", "reduce_min"):
+            kv = {"axes": ",".join(str(int(v)) for v in attrs.get("axes", []))}
         if op == "reshape":
             dtype = None  # alias: inherits the operand's type
         parts = [op, "name=" + name]

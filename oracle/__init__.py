@@ -83,6 +83,22 @@ def conv2d(x, w, bias, rshift, multiplier, out_hw, stride=(1, 1), pad=(0, 0), di
     return out
 
 
+def deconv2d_i8(x, w, bias, rshift, multiplier, out_hw, stride=(1, 1), pad=(0, 0), dilation=(1, 1), groups=1,
+                do_relu=False):
+    """core/deconv.cpp DeConv2DOpKernel::invoke, INT8. x [n,ic,ih,iw], w [oc,ic/g,kh,kw] (oihw / goihw)."""
+    x, w = _f32(x), _f32(w)
+    n, ic, ih, iw = x.shape
+    oc, _, kh, kw = w.shape
+    oh, ow = out_hw
+    out = np.empty((n, oc, oh, ow), np.float32)
+    bias = _f32(bias) if bias is not None else None
+    rshift, multiplier = _f32(rshift), _f32(multiplier)
+    lib().orc_deconv2d_i8(_p(x), _p(w), _p(bias) if bias is not None else None, _p(rshift), _p(multiplier), _p(out),
+                          n, ic, ih, iw, oc, oh, ow, groups, kh, kw, stride[0], stride[1], pad[0], pad[1],
+                          dilation[0], dilation[1], int(do_relu))
+    return out
+
+
 def fc(x, w, bias, rshift, multiplier, do_relu=False, mode="INT8"):
     """core/fullyconnected.cpp. x [batch?, m, k] or [m,k]; w [n,k]."""
     x, w = _f32(x), _f32(w)

@@ -730,4 +730,47 @@ void orc_reduce(const float *in, int outer, int axis, int inner, int type, int i
     }
 }
 
+// ---------------------------------------------------------------------------
+// DeConv2D, INT8 (core/deconv.cpp:6-73). The reference runs MKL-DNN's deconvolution_forward on
+// oihw / goihw weights (NativeCpuImplementation.h:197-283), whose definition is the scatter
+//   dst[n, oc, ih*sh + kh*dh - pt, iw*sw + kw*dw - pl] += src[n, ic, ih, iw] * w[oc, ic, kh, kw],
+// then adds the int32 bias and requantises per channel (QuantizationArithmetic.cpp:849-871).
+// ---------------------------------------------------------------------------
+void orc_deconv2d_i8(const float *in, const float *filter, const float *bias, const float *rshift,
+                     const float *multiplier, float *out, int n, int ic, int ih, int iw, int oc, int oh, int ow,
+                     int g, int kh, int kw, int sh, int sw, int pt, int pl, int dh, int dw, int do_relu) {
+  const int icg = ic / g, ocg = oc / g;
+  std::vector<int64_t> acc((size_t)n * oc * oh * ow, 0);
+  for (int b = 0; b < n; ++b)
+    for (int o = 0; o < oc; ++o) {
+      const int grp = o / ocg;
+      for (int c = 0; c < icg; ++c)
+        for (int y = 0; y < ih; ++y)
+          for (int x = 0; x < iw; ++x) {
+            const int32_t a = (int32_t)in[(((size_t)b * ic + grp * icg + c) * ih + y) * iw + x];
+            if (a == 0) continue;
+            for (int r = 0; r < kh; ++r) {
+              const int oy = y * sh + r * dh - pt;
+              if (oy < 0 || oy >= oh) continue;
+              for (int q = 0; q < kw; ++q) {
+                const int ox = x * sw + q * dw - pl;
+                if (ox < 0 || ox >= ow) continue;
+                acc[(((size_t)b * oc + o) * oh + oy) * ow + ox] +=
+                    (int64_t)(a * (int32_t)filter[(((size_t)o * icg + c) * kh + r) * kw + q]);
+              }
+            }
+          }
+    }
+  for (int b = 0; b < n; ++b)
+    for (int o = 0; o < oc; ++o)
+      for (int i = 0; i < oh * ow; ++i) {
+        const size_t oi = ((size_t)b * oc + o) * oh * ow + i;
+        int32_t v = (int32_t)acc[oi];
+        if (bias) v += (int32_t)bias[o];
+        int q = orc_qdm_i32(v, (uint32_t)rshift[o], (uint32_t)multiplier[o]);
+        if (do_relu && q < 0) q = 0;
+        out[oi] = (float)q;
+      }
+}
+
 } // extern "C"

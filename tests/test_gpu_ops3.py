@@ -88,3 +88,21 @@ def test_reduce_i8_and_fp32():
     out = run_both(b.text(), b.weights, ins, ["mean_hw", "max_hw", "min_c", "fmean", "fsum_c", "fmax_w"])
     assert_exact({k: out[k] for k in ("mean_hw", "max_hw", "min_c", "fmax_w")})
     assert_close({k: out[k] for k in ("fmean", "fsum_c")}, rtol=1e-5)
+
+
+@pytest.mark.parametrize("cfg", [dict(ic=16, oc=24, hw=7, k=4, s=2, p=1, g=1), dict(ic=32, oc=32, hw=5, k=3, s=2, p=0, g=1),
+                                 dict(ic=64, oc=64, hw=6, k=2, s=2, p=0, g=4), dict(ic=8, oc=40, hw=9, k=3, s=1, p=1, g=1)])
+def test_deconv_i8(cfg):
+    """Transposed convolution (upsampling layers of segmentation / detection necks)."""
+    rng = np.random.default_rng(16)
+    ic, oc, hw, k, s, p, g = (cfg[x] for x in ("ic", "oc", "hw", "k", "s", "p", "g"))
+    oh = (hw - 1) * s - 2 * p + k
+    b = graphs.GraphBuilder(16, simulate=False)
+    b.op("input", "x", [], (2, ic, hw, hw), "INT8")
+    b.weight("w", rng.integers(-127, 128, (oc, ic // g, k, k)))
+    b.weight("bias", rng.integers(-2 ** 14, 2 ** 14, oc))
+    b.weight("rs", rng.integers(9, 13, oc))
+    b.weight("mu", np.float32((rng.integers(2 ** 30, 2 ** 31 - 128, oc) // 128) * 128))
+    b.op("deconv_2d", "y", ["x", "w", "bias", None, None, "rs", "mu"], (2, oc, oh, oh), "INT8", kh=k, kw=k, sh=s, sw=s,
+         pt=p, pb=p, pl=p, pr=p, dh=1, dw=1, g=g, do_relu=1, with_bias=1)
+    assert_exact(run_both(b.text(), b.weights, {"x": i8(rng, (2, ic, hw, hw))}, ["y"]))

@@ -1354,6 +1354,30 @@ inline void Interpreter::load_module(const std::string &text) {
       k.reset(new QuantOp(*this, op, opd(0), out, pt == "input"));
     } else if (op.type == "conv_2d") {
       k.reset(new Conv2DOp(*this, op, opd(0), out));
+    } else if (op.type == "deconv_2d") {
+      // DeConv2DOpKernel (core/deconv.cpp:6-73; MKL-DNN deconvolution on oihw / goihw weights): the scatter
+      //   dst[oh = ih*sh + kh*dh - pt] += src[ih] * w[kh]
+      // equals a stride-1 convolution of the zero-inserted input (sh-1 zeros between pixels) with the
+      // spatially flipped filter and padding dh*(kh-1) - pt, which is what the convolution op runs.
+      TPUCB_CHECK(dt == DT_I8, "deconv_2d %s: only INT8 is implemented", op.name.c_str());
+      TPUCB_CHECK(op.in.size() >= 2 && has_weight(op.in[1]), "deconv_2d %s: filter operand missing", op.name.c_str());
+      const int kh = op.geti("kh", 1), kw = op.geti("kw", 1), sh = op.geti("sh", 1), sw = op.geti("sw", 1);
+      const int dh = op.geti("dh", 1), dw = op.geti("dw", 1);
+      const HostWeight &filt = weight(op.in[1]);
+      TPUCB_CHECK(filt.data.size() % ((size_t)kh * kw) == 0, "deconv_2d %s: filter size does not match kh x kw", op.name.c_str());
+      HostWeight flipped = filt;
+      for (size_t base = 0; base < filt.data.size(); base += (size_t)kh * kw)
+        for (int t = 0; t < kh * kw; ++t) flipped.data[base + t] = filt.data[base + kh * kw - 1 - t];
+      ParsedOp cop = op;
+      cop.in[1] = op.in[1] + "#flipped";
+      weights[cop.in[1]] = flipped;
+      auto set = [&](const char *key, int v) { cop.attrs[key] = std::to_string(v); };
+      set("ins_h", sh - 1); set("ins_w", sw - 1); set("sh", 1); set("sw", 1);
+      set("pt", dh * (kh - 1) - op.geti("pt", 0)); set("pb", dh * (kh - 1) - op.geti("pb", 0));
+      set("pl", dw * (kw - 1) - op.geti("pl", 0)); set("pr", dw * (kw - 1) - op.geti("pr", 0));
+      TPUCB_CHECK(cop.geti("pt") >= 0 && cop.geti("pl") >= 0, "deconv_2d %s: padding larger than the dilated filter extent",
+                  op.name.c_str());
+      k.reset(new Conv2DOp(*this, cop, opd(0), out));
     } else if (op.type == "fully_connected") {
       k.reset(new FullyConnectedOp(*this, op, opd(0), out));
     } else if (op.type == "pool_max_2d" || op.type == "pool_avg_2d") {

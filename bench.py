@@ -127,6 +127,71 @@ def run_reference(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
+def run_calibration(args, rank, world, local_rank):
+    """--workload calibration: the calibration pass (fp32 ResNet-50 forward, running min / max, 2048-bin |x|
+    histograms, KLD threshold search) over `--cal-images` synthetic images per GPU in batches of 64, every
+    rank on its own shard, statistics combined by all-reduce. Wall clock through the public calibrator API,
+    host input batches included (they are uploaded per batch, once per pass)."""
+    import torch
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        torch.cuda.set_device(local_rank)
+        dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        dist = dist_mod
+    from tpu_compiler_b200 import graphs, module
+    from tpu_compiler_b200.calibration import ActivationCalibrator
+    bs = 64
+    n_batches = max(args.cal_images // bs, 1)
+    model = graphs.resnet50_fp32(batch=bs)
+    m = module(local_rank)
+    m.load_text(model.text, model.weights)
+    rng = np.random.default_rng(7000 + rank)
+    data = [np.clip(rng.standard_normal((bs, 3, 224, 224), dtype=np.float32), -3, 3) for _ in range(n_batches)]
+    cal = ActivationCalibrator(m, lambda: iter(data), dist=dist)
+    m.set_tensor(cal.input_name, data[0])
+    for _ in range(3):
+        m.invoke()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    stats = cal.find_min_max_abs()
+    t1 = time.perf_counter()
+    hist = cal.calc_histograms(stats)
+    t2 = time.perf_counter()
+    thr = cal.find_threshold(hist, stats)
+    torch.cuda.synchronize()
+    t3 = time.perf_counter()
+    if dist is not None:
+        dist.barrier()
+        tt = torch.tensor([t3 - t0], dtype=torch.float64, device="cuda")
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        total_s = float(tt.item())
+    else:
+        total_s = t3 - t0
+    clocks = sampler.stop()
+    fwd_ms = m.time_launches(5) / 5
+    images = world * n_batches * bs
+    if rank == 0:
+        print(json.dumps({
+            "metric": "fp32 ResNet-50 calibration images/sec", "value": images / total_s, "unit": "images/s",
+            "n_gpus": world, "steps": n_batches, "warmup": 3, "ms_per_step": total_s / n_batches * 1e3,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "calibration: fp32 ResNet-50, %d images per GPU in batches of 64 (N(0,1) clipped to "
+                                   "[-3,3]), %d tensors, min/max pass + 2048-bin histogram pass + KLD search" %
+                                   (n_batches * bs, len(cal.names)),
+                       "parallelism": "image shards x%d, all-reduce(MAX) of min/max, all-reduce(SUM) of histograms" % world},
+            "phases_s": {"min_max_pass": t1 - t0, "histogram_pass": t2 - t1, "kld_search": t3 - t2},
+            "forward_ms_per_batch": fwd_ms, "thresholds": len(thr), "clocks": clocks}), flush=True)
+    m.close()
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 # graph builder name in tpu_compiler_b200.graphs, input resolution, input value range, default batch
 WORKLOADS = {
     "resnet50": {"builder": "resnet50_int8", "res": 224, "lo": -1.0, "batch": 128,
@@ -185,13 +250,19 @@ def main():
     ap.add_argument("--cpu-images", type=int, default=100, help="images of the bounded CPU-baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--case", default=None, help="conv_sweep only: one case as c,hw,n")
-    ap.add_argument("--workload", default="resnet50", choices=sorted(WORKLOADS) + ["conv_sweep"],
+    ap.add_argument("--cal-images", type=int, default=512, help="calibration workload: images per GPU")
+    ap.add_argument("--workload", default="resnet50", choices=sorted(WORKLOADS) + ["conv_sweep", "calibration"],
                     help="resnet50 is the headline configuration; the others are the secondary graphs "
                          "(their lines carry no cpu_baseline)")
     args = ap.parse_args()
     if args.workload == "conv_sweep":
         if args.impl == "ours" and int(os.environ.get("RANK", "0")) == 0:
             run_conv_sweep(args, int(os.environ.get("LOCAL_RANK", "0")))
+        return
+    if args.workload == "calibration":
+        if args.impl == "ours":
+            run_calibration(args, int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")),
+                            int(os.environ.get("LOCAL_RANK", "0")))
         return
     wl = WORKLOADS[args.workload]
     if args.batch is None:

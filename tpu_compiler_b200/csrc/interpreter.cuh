@@ -1451,7 +1451,10 @@ inline void Interpreter::set_tensor(const std::string &name, const float *data, 
   TensorGeom g{t->n, t->c, t->h, t->w, t->cp, t->wl, t->wphys};
   size_t total = t->pixels() * t->cp;
   int grid = grid_for(total, 256, sm_count);
-  if (t->dtype == DT_I8) nchw_f32_to_dev_kernel<DT_I8><<<grid, 256, 0, stream>>>(stg, t->dev, g);
+  if (t->dtype == DT_F32 && t->cp == 4 && !t->padded_rows())
+    nchw_f32_to_nhwc4_kernel<<<grid_for(t->pixels(), 256, sm_count), 256, 0, stream>>>(stg, (float4 *)t->dev, t->n, t->c,
+                                                                                     (size_t)t->h * t->w);
+  else if (t->dtype == DT_I8) nchw_f32_to_dev_kernel<DT_I8><<<grid, 256, 0, stream>>>(stg, t->dev, g);
   else if (t->dtype == DT_BF16) nchw_f32_to_dev_kernel<DT_BF16><<<grid, 256, 0, stream>>>(stg, t->dev, g);
   else nchw_f32_to_dev_kernel<DT_F32><<<grid, 256, 0, stream>>>(stg, t->dev, g);
   TPUCB_CUDA(cudaGetLastError());
@@ -1486,7 +1489,10 @@ inline void Interpreter::set_tensor_async(const std::string &name, const float *
   size_t total = t->pixels() * t->cp;
   int grid = grid_for(total, 256, sm_count);
   const float *stg = (const float *)async_staging[k];
-  if (t->dtype == DT_I8) nchw_f32_to_dev_kernel<DT_I8><<<grid, 256, 0, stream>>>(stg, t->dev, g);
+  if (t->dtype == DT_F32 && t->cp == 4 && !t->padded_rows())
+    nchw_f32_to_nhwc4_kernel<<<grid_for(t->pixels(), 256, sm_count), 256, 0, stream>>>(stg, (float4 *)t->dev, t->n, t->c,
+                                                                                     (size_t)t->h * t->w);
+  else if (t->dtype == DT_I8) nchw_f32_to_dev_kernel<DT_I8><<<grid, 256, 0, stream>>>(stg, t->dev, g);
   else if (t->dtype == DT_BF16) nchw_f32_to_dev_kernel<DT_BF16><<<grid, 256, 0, stream>>>(stg, t->dev, g);
   else nchw_f32_to_dev_kernel<DT_F32><<<grid, 256, 0, stream>>>(stg, t->dev, g);
   TPUCB_CUDA(cudaGetLastError());

@@ -45,6 +45,24 @@ __global__ void nchw_f32_to_dev_kernel(const float *__restrict__ src, void *__re
   }
 }
 
+// upload of an image-like fp32 tensor (at most 4 channels, channel pitch 4): one thread per pixel reads
+// its values from the channel planes (consecutive threads, consecutive addresses) and writes one
+// 16-byte NHWC4 word. This is the per-step input path of a serving loop.
+__global__ void nchw_f32_to_nhwc4_kernel(const float *__restrict__ src, float4 *__restrict__ dst, int n, int c,
+                                         size_t hw) {
+  const size_t total = (size_t)n * hw;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t b = i / hw, p = i - b * hw;
+    const float *s = src + b * c * hw + p;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    v.x = s[0];
+    if (c > 1) v.y = s[hw];
+    if (c > 2) v.z = s[2 * hw];
+    if (c > 3) v.w = s[3 * hw];
+    dst[i] = v;
+  }
+}
+
 // download: device NHWC -> fp32 NCHW. One thread per NCHW element; reads of a warp
 // stride by cp but stay inside L2-resident rows for the sizes that are fetched.
 template <int DT>

@@ -56,6 +56,7 @@ struct ConvGemmParams {
   const int32_t *mult;   // [n_valid]
   const int32_t *rshift; // [n_valid]
   int8_t *out;
+  int8_t *out2;   // act == 2 only: the activation result goes here and `out` keeps the plain convolution result
   int *err;       // device error word (0 = ok)
 };
 
@@ -275,15 +276,13 @@ __device__ __forceinline__ int requant_one(int32_t acc, const ChanConst &q, cons
   uint32_t adj;
   asm("shr.u32 %0, %1, %2;" : "=r"(adj) : "r"((uint32_t)hi), "r"((uint32_t)q.s1)); // shifts >= 32 give 0
   int v = (hi + q.rnd - (int)adj) >> q.r;
-  if (ACT == 2) {
-    v = min(max(v, -128), 127);
-    if (v > 0) {
-      if (p.leaky_mp != 0) v = mul_rshift_sat8(v, p.leaky_mp, p.leaky_rp);
-    } else {
-      v = mul_rshift_sat8(v, p.leaky_mn, p.leaky_rn);
-    }
-  }
+  if (ACT == 2) v = min(max(v, -128), 127); // the leaky rescale below works on the saturated int8 value
   return v;
+}
+// INT8 leaky ReLU of a saturated convolution result (core/activation.cpp:126-153).
+__device__ __forceinline__ int leaky_of(int v, const ConvGemmParams &p) {
+  if (v > 0) return p.leaky_mp != 0 ? mul_rshift_sat8(v, p.leaky_mp, p.leaky_rp) : v;
+  return mul_rshift_sat8(v, p.leaky_mn, p.leaky_rn);
 }
 
 // Byte-permute selectors of the 4x4 transpose between the four lanes of a group (lane & 3).
@@ -336,8 +335,24 @@ __device__ __forceinline__ void epilogue_channels(const ConvGemmParams &p, uint3
     }
 #pragma unroll
     for (int k = 0; k < 8; ++k) w[k] = transpose4x4(w[k], ts);
+    const bool whole = m0 + colg + 32 <= p.M_total; // whole chunk in range: one guard for the eight stores
     int8_t *o = out4 + (size_t)(colg + pj) * p.ldc;
-    if (m0 + colg + 32 <= p.M_total) { // whole chunk in range: one guard for the eight stores
+    if (ACT == 2) {
+      // fused leaky ReLU: the activation works on the packed, saturated values after the transpose (four
+      // channels of one pixel per word); the plain result goes to `out` when the graph keeps that tensor
+      uint32_t l[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k)
+        l[k] = pack4_sat(leaky_of(sext_byte<0>(w[k]), p), leaky_of(sext_byte<1>(w[k]), p), leaky_of(sext_byte<2>(w[k]), p),
+                         leaky_of(sext_byte<3>(w[k]), p));
+      int8_t *o2 = (p.out2 ? p.out2 + (out4 - p.out) : out4) + (size_t)(colg + pj) * p.ldc;
+#pragma unroll
+      for (int k = 0; k < 8; ++k)
+        if (ch4_ok && (whole || m0 + colg + 4 * k + pj < p.M_total)) {
+          if (p.out2) *reinterpret_cast<uint32_t *>(o + (size_t)(4 * k) * p.ldc) = w[k];
+          *reinterpret_cast<uint32_t *>(o2 + (size_t)(4 * k) * p.ldc) = l[k];
+        }
+    } else if (whole) {
       if (ch4_ok) {
 #pragma unroll
         for (int k = 0; k < 8; ++k) *reinterpret_cast<uint32_t *>(o + (size_t)(4 * k) * p.ldc) = w[k];

@@ -65,6 +65,7 @@ conv_stem_i8_kernel(const __grid_constant__ CUtensorMap tmB, const ConvStemParam
   ep.BN = p.BN; ep.n_valid = p.n_valid; ep.act = p.act; ep.M_total = p.M_total; ep.ldc = p.ldc;
   ep.mult = p.mult; ep.bias = p.bias; ep.rshift = p.rshift;
   ep.leaky_mp = p.leaky_mp; ep.leaky_rp = p.leaky_rp; ep.leaky_mn = p.leaky_mn; ep.leaky_rn = p.leaky_rn;
+  ep.out = p.out; ep.out2 = nullptr;
 
   if (threadIdx.x == 0) *abort_flag = *reinterpret_cast<volatile int *>(p.err);
   __syncthreads();

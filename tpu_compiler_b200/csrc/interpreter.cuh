@@ -481,16 +481,23 @@ public:
       plans_.push_back(pl);
     }
   }
-  void set_leaky(int mp, int rp, int mn, int rn) {
-    for (auto &sp : stem_plans_) {
-      sp.p.act = 2;
-      sp.p.leaky_mp = mp; sp.p.leaky_rp = rp; sp.p.leaky_mn = mn; sp.p.leaky_rn = rn;
-    }
+  // Fused leaky ReLU (tensor-core plans only): the epilogue writes the plain result to this op's tensor
+  // and the activation result to `act_out`.
+  bool can_fuse_leaky() const {
+    if (f32_ || dw_ || !stem_plans_.empty() || act_ != 0 || plans_.empty()) return false;
+    for (auto &pl : plans_)
+      if (pl.pair) return false;
+    return true;
+  }
+  void set_leaky(int mp, int rp, int mn, int rn, int8_t *act_out) {
     for (auto &pl : plans_) {
       pl.p.act = 2;
       pl.p.leaky_mp = mp; pl.p.leaky_rp = rp; pl.p.leaky_mn = mn; pl.p.leaky_rn = rn;
+      pl.p.out2 = act_out;
     }
+    act_ = 2;
   }
+  const TensorPtr &out() const { return out_; }
   void invoke(cudaStream_t s) override {
     if (f32_) {
       launch_conv2d_f32((const float *)in_->dev, f32_w_, f32_b_, (float *)out_->dev, g_, in_->cp, out_->cp, do_relu_,
@@ -848,6 +855,9 @@ public:
                                                                           nvec, mp, rp, mn, rn, plain_ ? 1 : 0);
   }
   int mp = 0, rp = 0, mn = 0, rn = 0;
+  bool plain() const { return plain_; }
+  const TensorPtr &in() const { return in_; }
+  const TensorPtr &out() const { return out_; }
 
 private:
   Interpreter &I_;
@@ -1212,6 +1222,26 @@ inline void Interpreter::fuse_activation_chains(const std::map<std::string, int>
     return it != uses.end() && it->second == 1;
   };
   const size_t n = kernels.size();
+  // INT8 leaky ReLU directly behind a tensor-core convolution that feeds nothing else: the convolution's
+  // epilogue applies it and writes both tensors; the leaky op becomes a placeholder.
+  for (size_t j = 0; j < n; ++j) {
+    auto *lk = dynamic_cast<LeakyReluOp *>(kernels[j].get());
+    if (!lk || lk->plain()) continue;
+    for (size_t i = 0; i < j; ++i) {
+      auto *cv = dynamic_cast<Conv2DOp *>(kernels[i].get());
+      if (!cv || cv->out() != lk->in()) continue;
+      const TensorPtr &a = cv->out(), &b = lk->out();
+      if (!cv->can_fuse_leaky() || !single_use(cv->name) || a->cp != b->cp || a->padded_rows() || b->padded_rows() ||
+          a->bytes() != b->bytes())
+        break;
+      cv->set_leaky(lk->mp, lk->rp, lk->mn, lk->rn, (int8_t *)b->dev);
+      std::unique_ptr<OpKernel> away(new FusedAwayOp());
+      away->name = lk->name; away->op_type = lk->op_type; away->shape = lk->shape; away->datatype = lk->datatype;
+      away->result = lk->result;
+      kernels[j] = std::move(away);
+      break;
+    }
+  }
   for (size_t i = 0; i < n; ++i) {
     auto *q0 = dynamic_cast<QuantOp *>(kernels[i].get());
     if (!q0 || q0->kind() != 3 || !single_use(q0->name)) continue;

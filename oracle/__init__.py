@@ -222,6 +222,36 @@ def reduce(x, axes, kind, is_int8=True, multiplier=1.0, rshift=0.0):
     return out
 
 
+def matmul_dims(a_shape, out_shape, ltrans=False, rtrans=False, otrans=False):
+    """(batch_high, batch_low, M, K, N) as parseMatMulParam derives them (TPUOperationSupport.cpp:615-655)."""
+    axis = len(out_shape) - 1
+    bh = bl = 1
+    if ltrans or rtrans or otrans:
+        k, n = a_shape[axis], out_shape[axis]
+        if ltrans:
+            bl, m = a_shape[axis - 1], a_shape[axis - 2]
+        else:
+            bl, m = a_shape[axis - 2], a_shape[axis - 1]
+        if axis == 3:
+            bh = a_shape[0]
+        return bh, bl, m, k, n
+    for d in a_shape[:axis - 1]:
+        bh *= d
+    return bh, 1, a_shape[axis - 1], a_shape[axis], out_shape[axis]
+
+
+def matmul(a, b, out_shape, mode="INT8", rshift=0.0, multiplier=0.0, do_relu=False, ltrans=False, rtrans=False,
+           otrans=False):
+    """core/matmul.cpp: two activations, batched; see matmul_dims for the dimension rule."""
+    a, b = _f32(a), _f32(b)
+    bh, bl, m, k, n = matmul_dims(a.shape, out_shape, ltrans, rtrans, otrans)
+    out = np.empty(out_shape, np.float32)
+    assert a.size == bh * bl * m * k and b.size == bh * bl * k * n and out.size == bh * bl * m * n
+    lib().orc_matmul(_p(a), _p(b), _p(out), bh, bl, m, k, n, int(ltrans), int(rtrans), int(otrans), int(do_relu),
+                     {"INT8": 0, "FP32": 1, "BF16": 2}[mode], C.c_float(rshift), C.c_float(multiplier))
+    return out
+
+
 def concat_c(inputs, multiplier=None, rshift=None, do_relu=False):
     arrs, pa = _ptr_array(inputs)
     n, _, h, w = arrs[0].shape
@@ -259,6 +289,16 @@ def quant(x, scale, kind, zero_point=0):
     lib().orc_quant(_p(x), _p(out), C.c_size_t(x.size), C.c_float(scale), int(zero_point),
                     QUANT_KINDS[kind])
     return out
+
+
+def bf16_round(x):
+    """F32ToBF16 with rounding over an array (QuantizationArithmetic.cpp:873-910): add 0x7fff plus the lowest kept
+    bit, keep the high half; a result whose exponent is all ones becomes 0x7f7f."""
+    u = _f32(x).view(np.uint32).astype(np.uint64)
+    u = (u + 0x7fff + ((u >> 16) & 1)) & 0xffffffff
+    h = (u >> 16).astype(np.uint32)
+    h = np.where((h & 0x7f80) == 0x7f80, np.uint32(0x7f7f), h)
+    return (h << 16).astype(np.uint32).view(np.float32).reshape(np.shape(x))
 
 
 def leaky_relu_i8(x, rshift_pos, mult_pos, rshift_neg, mult_neg):
@@ -304,6 +344,31 @@ def lut_bf16_mantissa(x, exp_table, mant_table):
     out = np.empty_like(x)
     lib().orc_lut_bf16_mantissa(_p(x), _p(out), C.c_size_t(x.size), _p(_f32(exp_table)),
                                 _p(_f32(mant_table)))
+    return out
+
+
+def lut_log_tables():
+    e, m = np.zeros(256, np.float32), np.zeros(256, np.float32)
+    lib().orc_lut_gen_log_tables(_p(e), _p(m))
+    return e, m
+
+
+def lut_bf16_mantissa_log(x, exp_table, mant_table):
+    x = _f32(x)
+    out = np.empty_like(x)
+    lib().orc_lut_bf16_mantissa_log(_p(x), _p(out), C.c_size_t(x.size), _p(_f32(exp_table)),
+                                    _p(_f32(mant_table)))
+    return out
+
+
+def softmax_bf16(x, exp_table, exp_slope, rec_table, rec_mant, axis=1, do_log=False):
+    """core/softmax.cpp:88-151; the last two tables are the reciprocal (pow -1) pair, or the log pair with do_log."""
+    x = _f32(x)
+    out = np.empty_like(x)
+    outer = int(np.prod(x.shape[:axis]))
+    inner = int(np.prod(x.shape[axis + 1:]))
+    lib().orc_softmax_bf16(_p(x), _p(out), outer, x.shape[axis], inner, int(do_log), _p(_f32(exp_table)),
+                           _p(_f32(exp_slope)), _p(_f32(rec_table)), _p(_f32(rec_mant)))
     return out
 
 

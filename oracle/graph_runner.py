@@ -92,9 +92,14 @@ def run(text, weights, inputs, upto=None):
                     out = O.eltwise_add_i8(xs, mu, float(rs[0]), bool(_i(a, "do_relu")))
                 else:
                     out = O.eltwise_mul_i8(xs, float(mu[0]), float(rs[0]), bool(_i(a, "do_relu")))
+            elif t == "eltwise_mul":
+                # fp32 product (core/eltwise.cpp:320-333); BF16 rounds the result
+                out = O.eltwise_mul_i8(xs, 0.0, 0.0, bool(_i(a, "do_relu")))
+                if op["dtype"] == "BF16":
+                    out = O.bf16_round(out)
             else:
                 coeff = [float(c) for c in a["coeff"].split(",")] if "coeff" in a else None
-                out = O.eltwise_add_f32(xs, coeff, bool(_i(a, "do_relu")))
+                out = O.eltwise_add_f32(xs, coeff, bool(_i(a, "do_relu")), to_bf16=(op["dtype"] == "BF16"))
         elif t in ("eltwise_max", "eltwise_min"):
             n_in = sum(1 for nm in ins if nm in T)
             out = O.eltwise_maxmin_i8([T[nm] for nm in ins[:n_in]], W(n_in + 3), float(W(n_in + 2)[0]),
@@ -117,6 +122,12 @@ def run(text, weights, inputs, upto=None):
             rs = float(W(3)[0]) if (is_i8 and W(3) is not None) else 0.0
             out = O.reduce(X(0), [int(v) for v in a["axes"].split(",")], t.split("_")[1], is_int8=is_i8,
                            multiplier=mu, rshift=rs).reshape(op["shape"])
+        elif t == "matmul":
+            is_i8 = op["dtype"] == "INT8"
+            out = O.matmul(X(0), X(1), op["shape"], mode=op["dtype"], rshift=float(W(4)[0]) if is_i8 else 0.0,
+                           multiplier=float(W(5)[0]) if is_i8 else 0.0, do_relu=bool(_i(a, "do_relu")),
+                           ltrans=bool(_i(a, "left_transpose")), rtrans=bool(_i(a, "right_transpose")),
+                           otrans=bool(_i(a, "output_transpose")))
         elif t == "concat":
             xs = [T[n] for n in ins if n in T]
             nin = len(xs)
@@ -140,7 +151,10 @@ def run(text, weights, inputs, upto=None):
         elif t == "scale":
             out = O.scale_f32(X(0), W(1), W(2))
         elif t == "softmax":
-            out = O.softmax_f32(X(0), 1)
+            if op["dtype"] == "BF16":
+                out = O.softmax_bf16(X(0), W(1), W(2), W(3), W(4), axis=_i(a, "axis", 1), do_log=bool(_i(a, "do_log")))
+            else:
+                out = O.softmax_f32(X(0), 1)
         elif t == "reshape":
             out = X(0).reshape(op["shape"])
         else:

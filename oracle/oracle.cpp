@@ -467,17 +467,75 @@ void orc_lut_gen_pow_tables(float coeff, float *exp_table, float *mant_table) {
   }
 }
 
-// Exponent x mantissa lookup: lut_func.cpp:306-333 ("mantissa" method).
+// Exponent / mantissa tables of the logarithm: lut_func.cpp:238-286. log(x) = e*ln2 + log(1.m); entry 0 and
+// the negative half hold the most negative BF16 number.
+void orc_lut_gen_log_tables(float *exp_table, float *mant_table) {
+  const int half = 128, start = -62;
+  uint32_t negu = 0xFF7F0000u;
+  float negmax;
+  std::memcpy(&negmax, &negu, 4);
+  for (int i = 0; i < 256; ++i) exp_table[i] = 0;
+  exp_table[0] = negmax;
+  for (int i = 0; i < half - 1; ++i) {
+    float e = (float)(start + i);
+    exp_table[1 + i] = orc_bf16((float)(e * log(2.)), 1);
+    exp_table[128 + 1 + i] = negmax;
+  }
+  for (int i = 0; i < half; ++i) {
+    float d = (float)(1 + i * 1 / 128.0);
+    mant_table[i] = mant_table[128 + i] = orc_bf16((float)log(d), 1);
+  }
+}
+
+// Exponent x mantissa lookup: lut_func.cpp:306-333; method "mantissa" multiplies the two entries
+// (is_log 0), method "log" adds them (is_log 1).
+static inline float orc_lut_mantissa_one(float v, const float *exp_table, const float *mant_table, int is_log) {
+  uint16_t h = orc_f32_to_bf16(v, 0);
+  int e;
+  if (v == 0) e = 0;
+  else if (v >= 0) e = (int)floor(log2(v)) + 63;
+  else e = (int)floor(log2(-1 * v)) + 62 + 129;
+  volatile float ex = exp_table[e], ma = mant_table[h & 0xff];
+  return orc_bf16(is_log ? ex + ma : ex * ma, 1);
+}
 void orc_lut_bf16_mantissa(const float *in, float *out, size_t size,
                            const float *exp_table, const float *mant_table) {
-  for (size_t i = 0; i < size; ++i) {
-    float v = in[i];
-    uint16_t h = orc_f32_to_bf16(v, 0);
-    int e;
-    if (v == 0) e = 0;
-    else if (v >= 0) e = (int)floor(log2(v)) + 63;
-    else e = (int)floor(log2(-1 * v)) + 62 + 129;
-    out[i] = orc_bf16(exp_table[e] * mant_table[h & 0xff], 1);
+  for (size_t i = 0; i < size; ++i) out[i] = orc_lut_mantissa_one(in[i], exp_table, mant_table, 0);
+}
+void orc_lut_bf16_mantissa_log(const float *in, float *out, size_t size,
+                               const float *exp_table, const float *mant_table) {
+  for (size_t i = 0; i < size; ++i) out[i] = orc_lut_mantissa_one(in[i], exp_table, mant_table, 1);
+}
+
+// BF16 softmax over one axis (core/softmax.cpp:88-151): max, BF16(x - max), exp through the slope table,
+// sum_j ex_j * BF16(BF16(C)/C) accumulated in fp32 in channel order and rounded once, reciprocal (or log)
+// through the exponent / mantissa tables, BF16(ex * 1/sum) or BF16(sub - log(sum)).
+void orc_softmax_bf16(const float *in, float *out, int outer, int channel, int inner, int do_log,
+                      const float *exp_table, const float *exp_slope, const float *rec_table, const float *rec_mant) {
+  std::vector<float> mx(inner), sum(inner), sub((size_t)channel * inner), ex((size_t)channel * inner);
+  for (int i = 0; i < outer; ++i) {
+    const float *x = in + (size_t)i * channel * inner;
+    float *y = out + (size_t)i * channel * inner;
+    for (int k = 0; k < inner; ++k) mx[k] = x[k];
+    for (int j = 0; j < channel; ++j)
+      for (int k = 0; k < inner; ++k)
+        if (mx[k] < x[(size_t)j * inner + k]) mx[k] = x[(size_t)j * inner + k];
+    for (int j = 0; j < channel; ++j)
+      for (int k = 0; k < inner; ++k) sub[(size_t)j * inner + k] = orc_bf16(x[(size_t)j * inner + k] - mx[k], 1);
+    orc_lut_bf16_slope(2, sub.data(), ex.data(), (size_t)channel * inner, exp_table, exp_slope);
+    const float const_val = orc_bf16(orc_bf16(1.0f * channel, 1) / channel, 1);
+    for (int k = 0; k < inner; ++k) sum[k] = 0;
+    for (int j = 0; j < channel; ++j)
+      for (int k = 0; k < inner; ++k) {
+        volatile float t = ex[(size_t)j * inner + k] * const_val;
+        sum[k] += t;
+      }
+    for (int k = 0; k < inner; ++k) sum[k] = orc_lut_mantissa_one(orc_bf16(sum[k], 1), rec_table, rec_mant, do_log);
+    for (int j = 0; j < channel; ++j)
+      for (int k = 0; k < inner; ++k) {
+        size_t idx = (size_t)j * inner + k;
+        y[idx] = do_log ? orc_bf16(sub[idx] - sum[k], 1) : orc_bf16(ex[idx] * sum[k], 1);
+      }
   }
 }
 
@@ -771,6 +829,35 @@ void orc_deconv2d_i8(const float *in, const float *filter, const float *bias, co
         if (do_relu && q < 0) q = 0;
         out[oi] = (float)q;
       }
+}
+
+// MatMul of two activations (core/matmul.cpp:33-97; dimensions per TPUOperationSupport.cpp:615-655).
+// The transposes only change where element (batch, row, col) is stored: [bh, rows, bl, cols] instead of
+// [bh, bl, rows, cols]. mode 0 INT8 (QDM requant unless multiplier and rshift are both 0), 1 fp32, 2 BF16.
+static inline size_t orc_mm_index(int trans, int bh, int bl, int nbl, int rows, int cols, int r, int c) {
+  return trans ? (((size_t)bh * rows + r) * nbl + bl) * cols + c : (((size_t)bh * nbl + bl) * rows + r) * cols + c;
+}
+void orc_matmul(const float *left, const float *right, float *out, int nbh, int nbl, int M, int K, int N, int ltrans,
+                int rtrans, int otrans, int do_relu, int mode, float rshift, float multiplier) {
+#pragma omp parallel for collapse(2)
+  for (int b = 0; b < nbh * nbl; ++b)
+    for (int m = 0; m < M; ++m) {
+      const int bh = b / nbl, bl = b % nbl;
+      for (int n = 0; n < N; ++n) {
+        double acc = 0;
+        for (int k = 0; k < K; ++k)
+          acc += (double)left[orc_mm_index(ltrans, bh, bl, nbl, M, K, m, k)] *
+                 (double)right[orc_mm_index(rtrans, bh, bl, nbl, K, N, k, n)];
+        float v = (float)acc;
+        if (do_relu && v < 0) v = 0;
+        if (mode == 0) {
+          if (rshift != 0 || multiplier != 0) v = (float)orc_qdm_f32(v, (uint32_t)rshift, (uint32_t)multiplier);
+        } else if (mode == 2) {
+          v = orc_bf16(v, 1);
+        }
+        out[orc_mm_index(otrans, bh, bl, nbl, M, N, m, n)] = v;
+      }
+    }
 }
 
 } // extern "C"

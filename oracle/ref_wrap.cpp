@@ -43,4 +43,7 @@ void ref_lut_gen_expmant_tables(const char *name, float p0, float *exp_table, fl
 void ref_lut_bf16_mantissa(float *in, float *out, int size, float *exp_table, float *mant) {
   bf16_lut_mantissa(in, out, size, exp_table, mant, "mantissa");
 }
+void ref_lut_bf16_mantissa_log(float *in, float *out, int size, float *exp_table, float *mant) {
+  bf16_lut_mantissa(in, out, size, exp_table, mant, "log");
+}
 }

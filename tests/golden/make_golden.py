@@ -133,7 +133,47 @@ def main():
         hists.append(h), widths.append(width)
     np.savez_compressed(os.path.join(HERE, "kld.npz"), hist=np.stack(hists), width=np.array(widths, np.float32),
                         threshold=np.array(thr, np.float32))
+    make_softmax_bf16(ref)
     print("golden vectors written to", HERE)
+
+
+def make_softmax_bf16(ref):
+    """BF16 softmax cases. softmax.cpp itself needs the MLIR headers and cannot be compiled alone, so the sequence
+    of core/softmax.cpp:88-151 is stepped here in numpy fp32 over the reference's own compiled primitives
+    (BF16 rounding, bf16_lut_slope "exp", bf16_lut_mantissa "mantissa" / "log" and their table generators)."""
+    rng = np.random.default_rng(77)
+    bf = lambda a: np.array([ref.ref_bf16(float(v), 1) for v in np.asarray(a, np.float32).ravel()], np.float32).reshape(np.shape(a))  # noqa: E731
+    eb, es = np.zeros(256, np.float32), np.zeros(256, np.float32)
+    ref.ref_lut_gen_slope_tables(b"exp", C.c_float(1.0), C.c_float(0.0), p(eb), p(es))
+    tabs = {}
+    for nm, coeff in (("pow", -1.0), ("log", 0.0)):
+        e, m = np.zeros(256, np.float32), np.zeros(256, np.float32)
+        ref.ref_lut_gen_expmant_tables(nm.encode(), C.c_float(coeff), p(e), p(m))
+        tabs[nm] = (e, m)
+    out = dict(exp_base=eb, exp_slope=es, rec_exp=tabs["pow"][0], rec_mant=tabs["pow"][1], log_exp=tabs["log"][0],
+               log_mant=tabs["log"][1])
+    for ci, (outer, ch, inner, sd) in enumerate([(3, 21, 4, 3.0), (2, 1000, 1, 2.0), (1, 80, 9, 8.0)]):
+        x = bf(rng.normal(0, sd, (outer, ch, inner)))
+        out["x%d" % ci] = x
+        for do_log in (0, 1):
+            y = np.empty_like(x)
+            for i in range(outer):
+                mx = x[i].max(axis=0)
+                sub = bf(x[i] - mx[None, :])
+                ex = np.empty_like(sub)
+                si = np.ascontiguousarray(sub)
+                ref.ref_lut_bf16_slope(b"exp", p(si), p(ex), sub.size, p(eb), p(es))
+                const_val = np.float32(ref.ref_bf16(float(np.float32(ref.ref_bf16(float(ch), 1)) / np.float32(ch)), 1))
+                sm = np.zeros(inner, np.float32)
+                for j in range(ch):
+                    sm = (sm + ex[j] * const_val).astype(np.float32)
+                sm = bf(sm)
+                r = np.empty_like(sm)
+                e, m = tabs["log" if do_log else "pow"]
+                (ref.ref_lut_bf16_mantissa_log if do_log else ref.ref_lut_bf16_mantissa)(p(sm), p(r), sm.size, p(e), p(m))
+                y[i] = bf(sub - r[None, :]) if do_log else bf(ex * r[None, :])
+            out["y%d_log%d" % (ci, do_log)] = y
+    np.savez_compressed(os.path.join(HERE, "softmax_bf16.npz"), **out)
 
 
 if __name__ == "__main__":

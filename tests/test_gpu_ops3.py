@@ -106,3 +106,130 @@ def test_deconv_i8(cfg):
     b.op("deconv_2d", "y", ["x", "w", "bias", None, None, "rs", "mu"], (2, oc, oh, oh), "INT8", kh=k, kw=k, sh=s, sw=s,
          pt=p, pb=p, pl=p, pr=p, dh=1, dw=1, g=g, do_relu=1, with_bias=1)
     assert_exact(run_both(b.text(), b.weights, {"x": i8(rng, (2, ic, hw, hw))}, ["y"]))
+
+
+def _bf16(x):
+    return (np.asarray(x, np.float32).view(np.uint32) & 0xffff0000).view(np.float32)
+
+
+def assert_bf16_ulp(pairs, max_ulp=1):
+    """BF16 tensors within `max_ulp` units in the last place (the tolerance the interpreter path allows for BF16;
+    the tensor core accumulates in another order than the CPU loop)."""
+    for n, (got, exp) in pairs.items():
+        g = (got.reshape(-1).view(np.uint32) >> 16).astype(np.int64)
+        e = (exp.reshape(-1).view(np.uint32) >> 16).astype(np.int64)
+        key = lambda b: np.where(b & 0x8000, 0x8000 - (b & 0x7fff), 0x8000 + b)  # noqa: E731  monotone in the value
+        d = np.abs(key(g) - key(e))
+        # results next to zero: compare against the tensor's scale instead of ulps of a tiny number
+        tiny = np.abs(exp.reshape(-1)) < 1e-3 * (np.abs(exp).max() + 1e-30)
+        bad = np.flatnonzero((d > max_ulp) & ~tiny)
+        assert bad.size == 0, "%s: %d of %d differ by more than %d ulp, e.g. idx %d got %r expected %r" % (
+            n, bad.size, g.size, max_ulp, bad[0], got.reshape(-1)[bad[0]], exp.reshape(-1)[bad[0]])
+        assert np.abs(got.reshape(-1)[tiny] - exp.reshape(-1)[tiny]).max(initial=0) <= 4e-3 * (np.abs(exp).max() + 1e-30)
+
+
+@pytest.mark.parametrize("cfg", [dict(ic=32, oc=64, hw=12, k=1, s=1, p=0, relu=1), dict(ic=64, oc=128, hw=14, k=3, s=1, p=1, relu=1),
+                                 dict(ic=16, oc=256, hw=9, k=3, s=2, p=1, relu=0), dict(ic=128, oc=24, hw=7, k=1, s=1, p=0, relu=0)])
+def test_conv_bf16(cfg):
+    """BF16 convolution on the tensor cores (BF16 operands, fp32 accumulation) against the fp32-loop oracle."""
+    rng = np.random.default_rng(17)
+    ic, oc, hw, k, s, p = (cfg[x] for x in ("ic", "oc", "hw", "k", "s", "p"))
+    oh = (hw + 2 * p - k) // s + 1
+    b = graphs.GraphBuilder(17, simulate=False)
+    b.op("input", "x", [], (3, ic, hw, hw), "BF16")
+    b.weight("w", _bf16(rng.normal(0, (2.0 / (ic * k * k)) ** 0.5, (oc, ic, k, k))))
+    b.weight("bias", rng.normal(0, 0.1, oc).astype(np.float32))
+    b.op("conv_2d", "y", ["x", "w", "bias"], (3, oc, oh, oh), "BF16", kh=k, kw=k, sh=s, sw=s, pt=p, pb=p, pl=p, pr=p,
+         dh=1, dw=1, g=1, do_relu=cfg["relu"], with_bias=1)
+    x = _bf16(rng.normal(0, 1, (3, ic, hw, hw)))
+    assert_bf16_ulp(run_both(b.text(), b.weights, {"x": x}, ["y"]))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("cfg", [dict(m=4, c=512, hw=1, n=1000, relu=0), dict(m=2, c=64, hw=7, n=40, relu=1)])
+def test_fc_bf16(cfg):
+    """BF16 inner product on the tensor cores against the fp32-loop oracle (result rounded to BF16)."""
+    rng = np.random.default_rng(23)
+    m, c, hw, n = cfg["m"], cfg["c"], cfg["hw"], cfg["n"]
+    k = c * hw * hw
+    b = graphs.GraphBuilder(23, simulate=False)
+    b.op("input", "x", [], (m, c, hw, hw), "BF16")
+    b.weight("w", _bf16(rng.normal(0, (2.0 / k) ** 0.5, (n, k))))
+    b.weight("bias", rng.normal(0, 0.1, n).astype(np.float32))
+    b.op("fully_connected", "y", ["x", "w", "bias"], (m, n, 1, 1), "BF16", do_relu=cfg["relu"])
+    x = _bf16(rng.normal(0, 1, (m, c, hw, hw)))
+    assert_bf16_ulp(run_both(b.text(), b.weights, {"x": x}, ["y"]))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("shape", [(2, 32, 9, 9), (1, 24, 5, 7)])
+def test_eltwise_and_pool_bf16(shape):
+    """BF16 eltwise add (with coefficients) / mul and pooling: fp32 arithmetic in the reference's order, one BF16
+    rounding of the result. The reference's fp32 container keeps the unrounded average; a BF16 tensor holds its rounding."""
+    rng = np.random.default_rng(29)
+    b = graphs.GraphBuilder(29, simulate=False)
+    for nm in ("a", "b", "c"):
+        b.op("input", nm, [], shape, "BF16")
+    b.op("eltwise_add", "add", ["a", "b", "c"], shape, "BF16", do_relu=1, coeff="1.0,-0.5,0.75")
+    b.op("eltwise_mul", "mul", ["a", "b"], shape, "BF16", do_relu=0)
+    n, c, h, w = shape
+    oh, ow = (h + 2 - 3) // 2 + 1, (w + 2 - 3) // 2 + 1
+    b.op("pool_max_2d", "pmax", ["a"], (n, c, oh, ow), "BF16", kh=3, kw=3, sh=2, sw=2, pt=1, pb=1, pl=1, pr=1)
+    b.op("pool_avg_2d", "pavg", ["b"], (n, c, oh, ow), "BF16", kh=3, kw=3, sh=2, sw=2, pt=1, pb=1, pl=1, pr=1, count_include_pad=0)
+    b.op("pool_avg_2d", "gap", ["c"], (n, c, 1, 1), "BF16", kh=h, kw=w, sh=1, sw=1, pt=0, pb=0, pl=0, pr=0, count_include_pad=1)
+    feeds = {nm: _bf16(rng.normal(0, 2, shape)) for nm in ("a", "b", "c")}
+    res = run_both(b.text(), b.weights, feeds, ["add", "mul", "pmax", "pavg", "gap"])
+    from oracle import bf16_round
+    for nm in ("pavg", "gap"):
+        res[nm] = (res[nm][0], bf16_round(res[nm][1]))
+    assert_exact(res)
+
+
+@pytest.mark.parametrize("cfg", [dict(a=(2, 3, 20, 40), b=(2, 3, 40, 24), o=(2, 3, 20, 24)),
+                                 dict(a=(5, 33, 17), b=(5, 17, 9), o=(5, 33, 9)),
+                                 dict(a=(37, 50), b=(50, 21), o=(37, 21)),
+                                 dict(a=(2, 20, 3, 40), b=(2, 40, 3, 24), o=(2, 20, 3, 24), lt=1, rt=1, ot=1),
+                                 dict(a=(20, 3, 40), b=(3, 40, 24), o=(3, 20, 24), lt=1)])
+@pytest.mark.parametrize("dtype", ["INT8", "BF16", "FP32"])
+def test_matmul(cfg, dtype):
+    """Batched product of two activations, with the storage orders of the three transposes."""
+    rng = np.random.default_rng(31)
+    b = graphs.GraphBuilder(31, simulate=False)
+    b.op("input", "a", [], cfg["a"], dtype)
+    b.op("input", "b", [], cfg["b"], dtype)
+    ins = ["a", "b"]
+    if dtype == "INT8":
+        b.weight("rs", np.array([9.0], np.float32))
+        b.weight("mu", np.array([1518500250.0], np.float32))
+        ins += ["-", "-", "rs", "mu"]
+    b.op("matmul", "y", ins, cfg["o"], dtype, do_relu=0, left_transpose=cfg.get("lt", 0), right_transpose=cfg.get("rt", 0),
+         output_transpose=cfg.get("ot", 0))
+    b.op("matmul", "yr", ins, cfg["o"], dtype, do_relu=1, left_transpose=cfg.get("lt", 0), right_transpose=cfg.get("rt", 0),
+         output_transpose=cfg.get("ot", 0))
+    if dtype == "INT8":
+        feeds = {"a": i8(rng, cfg["a"]), "b": i8(rng, cfg["b"])}
+        assert_exact(run_both(b.text(), b.weights, feeds, ["y", "yr"]))
+    elif dtype == "BF16":
+        feeds = {"a": _bf16(rng.normal(0, 1, cfg["a"])), "b": _bf16(rng.normal(0, 1, cfg["b"]))}
+        assert_bf16_ulp(run_both(b.text(), b.weights, feeds, ["y", "yr"]))
+    else:
+        feeds = {"a": rng.normal(0, 1, cfg["a"]).astype(np.float32), "b": rng.normal(0, 1, cfg["b"]).astype(np.float32)}
+        assert_close(run_both(b.text(), b.weights, feeds, ["y", "yr"]))
+
+
+@pytest.mark.parametrize("cfg", [dict(shape=(3, 21, 2, 2), sd=3.0), dict(shape=(2, 1000, 1, 1), sd=2.0), dict(shape=(1, 80, 3, 3), sd=8.0)])
+@pytest.mark.parametrize("do_log", [0, 1])
+def test_softmax_bf16(cfg, do_log):
+    """BF16 softmax through the exp slope table and the reciprocal / log exponent-mantissa tables: bit-exact,
+    the fp32 sum is taken in the reference's channel order."""
+    import oracle as O
+    rng = np.random.default_rng(37)
+    b = graphs.GraphBuilder(37, simulate=False)
+    b.op("input", "x", [], cfg["shape"], "BF16")
+    eb, es = O.lut_slope_tables("exp")
+    re_, rm = O.lut_log_tables() if do_log else O.lut_pow_tables(-1.0)
+    for nm, t in (("eb", eb), ("es", es), ("re", re_), ("rm", rm)):
+        b.weight(nm, t)
+    b.op("softmax", "y", ["x", "eb", "es", "re", "rm"], cfg["shape"], "BF16", axis=1, do_log=do_log)
+    x = O.bf16_round(rng.normal(0, cfg["sd"], cfg["shape"]))
+    assert_exact(run_both(b.text(), b.weights, {"x": x}, ["y"]))

@@ -67,3 +67,39 @@ def test_deconv_scatter_equals_conv_on_inserted_zeros():
     c = O.conv2d(x, w[:, :, ::-1, ::-1].copy(), bias, rsh, mult, (oh, ow), stride=(1, 1), pad=(kh - 1 - pt, kw - 1 - pl),
                  ins=(sh - 1, sw - 1))
     assert np.array_equal(d, c)
+
+
+def test_softmax_bf16_golden():
+    """BF16 softmax (and the log tables / "log" lookup under it) against vectors stepped over the reference's own
+    compiled BF16 and table primitives (tests/golden/make_golden.py: make_softmax_bf16)."""
+    import os
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "softmax_bf16.npz"))
+    le, lm = O.lut_log_tables()
+    assert np.array_equal(le.view(np.uint32), g["log_exp"].view(np.uint32))
+    assert np.array_equal(lm.view(np.uint32), g["log_mant"].view(np.uint32))
+    eb, es = O.lut_slope_tables("exp")
+    assert np.array_equal(eb.view(np.uint32), g["exp_base"].view(np.uint32))
+    assert np.array_equal(es.view(np.uint32), g["exp_slope"].view(np.uint32))
+    for ci in range(3):
+        for do_log in (0, 1):
+            t = (g["log_exp"], g["log_mant"]) if do_log else (g["rec_exp"], g["rec_mant"])
+            y = O.softmax_bf16(g["x%d" % ci], g["exp_base"], g["exp_slope"], t[0], t[1], axis=1, do_log=bool(do_log))
+            assert np.array_equal(y.view(np.uint32), g["y%d_log%d" % (ci, do_log)].view(np.uint32)), (ci, do_log)
+
+
+def test_matmul_oracle_against_numpy():
+    """The matmul restatement against numpy in every storage order (exact in INT8 below 2^24)."""
+    rng = np.random.default_rng(5)
+    a = rng.integers(-128, 128, (2, 3, 7, 11)).astype(np.float32)
+    b = rng.integers(-128, 128, (2, 3, 11, 5)).astype(np.float32)
+    exp = np.einsum("xymk,xykn->xymn", a, b)
+    y = O.matmul(a, b, (2, 3, 7, 5), mode="FP32")
+    assert np.array_equal(y, exp)
+    # transposed storage: left [bh, M, bl, K], right [bh, K, bl, N], out [bh, M, bl, N]
+    at, bt = a.transpose(0, 2, 1, 3).copy(), b.transpose(0, 2, 1, 3).copy()
+    yt = O.matmul(at, bt, (2, 7, 3, 5), mode="FP32", ltrans=True, rtrans=True, otrans=True)
+    assert np.array_equal(yt, exp.transpose(0, 2, 1, 3))
+    q = O.matmul(a, b, (2, 3, 7, 5), mode="INT8", rshift=9.0, multiplier=float(2 ** 30), do_relu=True)
+    hi = np.floor((np.maximum(exp, 0).astype(np.int64) * 2 ** 30 + 2 ** 30) / 2.0 ** 31).astype(np.int64)
+    ref = np.clip((hi + 256) >> 9, -128, 127)
+    assert np.array_equal(q, ref.astype(np.float32))

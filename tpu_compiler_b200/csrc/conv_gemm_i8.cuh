@@ -179,13 +179,39 @@ __device__ __forceinline__ void tcgen05_mma_i8_lohi(uint32_t d_tmem, uint32_t a_
         : "memory");
   }
 }
+// kind::f16 with BF16 operands and fp32 accumulation (BF16 graphs): 16 elements = 32 bytes of K per MMA
+template <bool ACCUMULATE>
+__device__ __forceinline__ void tcgen05_mma_f16_lohi(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                                     uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
+  if (ACCUMULATE) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+        "setp.eq.b32 p, 0, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}" ::"r"(d_tmem),
+        "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}" ::"r"(d_tmem),
+        "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
+}
 // KSTEPS MMAs of one K block (32 bytes of K each: +2 in the descriptors' 16-byte address units)
-template <int KSTEPS>
+template <int KSTEPS, bool BF16 = false>
 __device__ __forceinline__ void tcgen05_mma_i8_kblock(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t hi,
                                                       uint32_t idesc, uint32_t accumulate_first) {
-  tcgen05_mma_i8_lohi<false>(d_tmem, a_lo, hi, b_lo, hi, idesc, accumulate_first);
+  if (BF16) tcgen05_mma_f16_lohi<false>(d_tmem, a_lo, hi, b_lo, hi, idesc, accumulate_first);
+  else tcgen05_mma_i8_lohi<false>(d_tmem, a_lo, hi, b_lo, hi, idesc, accumulate_first);
 #pragma unroll
-  for (int k = 1; k < KSTEPS; ++k) tcgen05_mma_i8_lohi<true>(d_tmem, a_lo + 2 * k, hi, b_lo + 2 * k, hi, idesc, 1u);
+  for (int k = 1; k < KSTEPS; ++k) {
+    if (BF16) tcgen05_mma_f16_lohi<true>(d_tmem, a_lo + 2 * k, hi, b_lo + 2 * k, hi, idesc, 1u);
+    else tcgen05_mma_i8_lohi<true>(d_tmem, a_lo + 2 * k, hi, b_lo + 2 * k, hi, idesc, 1u);
+  }
 }
 __device__ __forceinline__ void tcgen05_ld_x16(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(
@@ -365,13 +391,47 @@ __device__ __forceinline__ void epilogue_channels(const ConvGemmParams &p, uint3
   }
 }
 
+// Epilogue of a BF16 convolution (core/conv.cpp:90-98: fp32 result + fp32 bias, ReLU, BF16 rounding). The
+// accumulators are fp32; a thread rounds two neighbouring pixels of its channel into one word, exchanges
+// words with the lane of the neighbouring channel and stores two channels of one pixel (a warp writes
+// 64 contiguous bytes per pixel). `out_pair` addresses (pixel m0, the even channel of this lane's pair);
+// `pitch` is the output row pitch in bytes.
+template <bool RELU>
+__device__ __forceinline__ void epilogue_channels_bf16(const ConvGemmParams &p, uint32_t lane_addr, uint8_t *out_pair,
+                                                       bool ch_ok, int m0, int half, int halves, int lane, float bias,
+                                                       int ncols = 128) {
+  const int odd = lane & 1;
+  const size_t pitch = (size_t)p.ldc;
+  for (int colg = half * 32; colg < ncols; colg += 32 * halves) {
+    if (m0 + colg >= p.M_total) break;
+    uint32_t acc0[16], acc1[16];
+    ptx::tcgen05_ld_x16(lane_addr + (uint32_t)colg, acc0);
+    ptx::tcgen05_ld_x16(lane_addr + (uint32_t)colg + 16u, acc1);
+    ptx::tcgen05_wait_ld();
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const uint32_t b0 = j < 8 ? acc0[2 * j] : acc1[2 * j - 16], b1 = j < 8 ? acc0[2 * j + 1] : acc1[2 * j - 15];
+      float v0 = __fadd_rn(bits_f32(b0), bias), v1 = __fadd_rn(bits_f32(b1), bias);
+      if (RELU) {
+        v0 = v0 > 0.0f ? v0 : 0.0f;
+        v1 = v1 > 0.0f ? v1 : 0.0f;
+      }
+      const uint32_t w = bf16x2_round_bits(v0, v1); // low half: pixel 2j, high half: pixel 2j + 1
+      const uint32_t o = __shfl_xor_sync(0xffffffffu, w, 1);
+      // even lane: channels (c, c+1) of pixel 2j; odd lane: channels (c-1, c) of pixel 2j + 1
+      const uint32_t y = odd ? __byte_perm(o, w, 0x7632) : __byte_perm(w, o, 0x5410);
+      const int pix = colg + 2 * j + odd;
+      if (ch_ok && m0 + pix < p.M_total) *reinterpret_cast<uint32_t *>(out_pair + (size_t)pix * pitch) = y;
+    }
+  }
+}
+
 // Persistent kernel: gridDim.x CTAs walk the tile list (tile = blockIdx.x + k * gridDim.x; n-tiles
 // vary fastest so that CTAs working at the same time share activation tiles through L2). The
 // producer runs ahead through the shared-memory ring across tile boundaries and the accumulator is
 // double-buffered in TMEM, so the loads and MMAs of tile i+1 overlap the epilogue of tile i.
-__global__ void __launch_bounds__(kConvThreads, 2)
-conv_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                    const ConvGemmParams p) {
+template <bool BF16>
+__device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUtensorMap &tmB, const ConvGemmParams &p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = ptx::smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -587,18 +647,18 @@ conv_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           const uint32_t w_lo = p.w_resident ? wres_lo : ring_lo + a_step;
           const uint32_t acc_first = kit > 0 ? 1u : 0u;
           if (!p.dual) {
-            if (ksteps == 4) ptx::tcgen05_mma_i8_kblock<4>(d_tmem, w_lo, ring_lo, desc_hi, p.idesc, acc_first);
-            else if (ksteps == 2) ptx::tcgen05_mma_i8_kblock<2>(d_tmem, w_lo, ring_lo, desc_hi, p.idesc, acc_first);
-            else ptx::tcgen05_mma_i8_kblock<1>(d_tmem, w_lo, ring_lo, desc_hi, p.idesc, acc_first);
+            if (ksteps == 4) ptx::tcgen05_mma_i8_kblock<4, BF16>(d_tmem, w_lo, ring_lo, desc_hi, p.idesc, acc_first);
+            else if (ksteps == 2) ptx::tcgen05_mma_i8_kblock<2, BF16>(d_tmem, w_lo, ring_lo, desc_hi, p.idesc, acc_first);
+            else ptx::tcgen05_mma_i8_kblock<1, BF16>(d_tmem, w_lo, ring_lo, desc_hi, p.idesc, acc_first);
           } else {
             // dual mode: sub-tile 0 uses weight rows 64..191 ([W; 0]), sub-tile 1 rows 0..127 ([0; W])
             for (int sub = 0; sub < 2; ++sub) {
               const uint32_t a_lo = w_lo + (sub == 0 ? dual_step : 0u);
               const uint32_t b_lo = ring_lo + (uint32_t)sub * sub_step;
               const uint32_t first = (kit > 0 || sub > 0) ? 1u : 0u;
-              if (ksteps == 4) ptx::tcgen05_mma_i8_kblock<4>(d_tmem, a_lo, b_lo, desc_hi, p.idesc, first);
-              else if (ksteps == 2) ptx::tcgen05_mma_i8_kblock<2>(d_tmem, a_lo, b_lo, desc_hi, p.idesc, first);
-              else ptx::tcgen05_mma_i8_kblock<1>(d_tmem, a_lo, b_lo, desc_hi, p.idesc, first);
+              if (ksteps == 4) ptx::tcgen05_mma_i8_kblock<4, BF16>(d_tmem, a_lo, b_lo, desc_hi, p.idesc, first);
+              else if (ksteps == 2) ptx::tcgen05_mma_i8_kblock<2, BF16>(d_tmem, a_lo, b_lo, desc_hi, p.idesc, first);
+              else ptx::tcgen05_mma_i8_kblock<1, BF16>(d_tmem, a_lo, b_lo, desc_hi, p.idesc, first);
             }
           }
           ptx::tcgen05_commit(m_empty); // frees the stage when the MMAs retire
@@ -623,6 +683,7 @@ conv_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const int half = (warp - 2) >> 2; // which alternate 32-pixel column groups it takes
     const TransposeSel ts = make_transpose_sel(lane);
     ChanConst cc;
+    float bias_f = 0.0f;
     int staged_n0 = -1;
     int t = 0;
     bool ok = true;
@@ -633,7 +694,12 @@ conv_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       const int n0 = (tile % n_tiles) * p.BN;
       const int buf = t & 1;
       if (n0 != staged_n0) {
-        cc = load_chan_const(p, n0 + ch_base + lane);
+        if (BF16) {
+          const int ch = n0 + ch_base + lane;
+          bias_f = ch < p.n_valid ? __int_as_float(p.bias[ch]) : 0.0f; // fp32 bias bits in the int32 array
+        } else {
+          cc = load_chan_const(p, n0 + ch_base + lane);
+        }
         staged_n0 = n0;
       }
       ok = ptx::mbar_wait_bounded(bar_acc_full + 8 * buf, (uint32_t)((t >> 1) & 1), abort_flag);
@@ -650,7 +716,13 @@ conv_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         const uint32_t lane_addr = tmem_base + (uint32_t)buf * acc_stride + ((uint32_t)(quarter * 32) << 16);
         int8_t *out4 = p.out + (size_t)m0 * p.ldc + p.c_off + ch4;
         const bool ch4_ok = ch4 < p.n_valid;
-        if (p.act == 1) epilogue_channels<1>(p, lane_addr, out4, ch4_ok, m0, half, kEpilogueWarps / 4, lane, cc, ts);
+        if (BF16) {
+          // byte addressing: 2 bytes per channel, this lane's pair starts at its even channel
+          const int ch = n0 + ch_base + lane;
+          uint8_t *out_pair = reinterpret_cast<uint8_t *>(p.out) + (size_t)m0 * p.ldc + (size_t)(p.c_off + (ch & ~1)) * 2;
+          if (p.act == 1) epilogue_channels_bf16<true>(p, lane_addr, out_pair, ch < p.n_valid, m0, half, kEpilogueWarps / 4, lane, bias_f);
+          else epilogue_channels_bf16<false>(p, lane_addr, out_pair, ch < p.n_valid, m0, half, kEpilogueWarps / 4, lane, bias_f);
+        } else if (p.act == 1) epilogue_channels<1>(p, lane_addr, out4, ch4_ok, m0, half, kEpilogueWarps / 4, lane, cc, ts);
         else if (p.act == 2) epilogue_channels<2>(p, lane_addr, out4, ch4_ok, m0, half, kEpilogueWarps / 4, lane, cc, ts);
         else epilogue_channels<0>(p, lane_addr, out4, ch4_ok, m0, half, kEpilogueWarps / 4, lane, cc, ts);
       }
@@ -668,6 +740,20 @@ conv_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     ptx::tcgen05_fence_after();
     ptx::tcgen05_dealloc(tmem_base, (uint32_t)p.tmem_cols);
   }
+}
+
+__global__ void __launch_bounds__(kConvThreads, 2)
+conv_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    const ConvGemmParams p) {
+  conv_gemm_body<false>(tmA, tmB, p);
+}
+// The same pipeline for BF16 graphs: BF16 operands (tcgen05 kind::f16), fp32 accumulators, BF16 results.
+// All sizes in ConvGemmParams that count K or row pitches are in BYTES, so only the MMA kind and the
+// epilogue differ.
+__global__ void __launch_bounds__(kConvThreads, 2)
+conv_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                      const ConvGemmParams p) {
+  conv_gemm_body<true>(tmA, tmB, p);
 }
 
 } // namespace tpucb

@@ -10,6 +10,7 @@
 #include "mem_kernels.cuh"
 
 #include <cstdlib>
+#include <cstring>
 #include <cudaTypedefs.h>
 
 namespace tpucb {
@@ -66,12 +67,18 @@ inline uint32_t make_idesc_i8(int M, int N) {
          ((uint32_t)(M >> 4) << 24);
 }
 
+// kind::f16 with BF16 operands and an fp32 accumulator: D = f32 (bits 4-5 = 1), A and B = BF16 (1)
+inline uint32_t make_idesc_bf16(int M, int N) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
 struct ConvPlan {
   CUtensorMap tmA, tmB;
   ConvGemmParams p;
   dim3 grid;
   size_t smem = 0;
   bool pair = false; // runs conv_gemm2_i8_kernel (two-SM tiles)
+  bool bf16 = false; // runs conv_gemm_bf16_kernel (K sizes and pitches in bytes, 2 per element)
   bool use_patch = false;
   PatchArgs patch;
   int8_t *patch_buf = nullptr; // scratch: expanded patch matrix [M][kp]
@@ -108,6 +115,23 @@ inline std::vector<int8_t> pack_conv_weights(const float *w, int oc, int icg, in
           else out[((size_t)o * taps + (r * kw + s)) * cin_pad + c] = v;
         }
   return out;
+}
+
+// BF16 weights [oc_pad][tap][cin_pad] as 16-bit patterns (the values of a BF16 graph's filter are
+// BF16-representable floats: the upper 16 bits are the value), returned as bytes
+inline std::vector<int8_t> pack_conv_weights_bf16(const float *w, int oc, int icg, int kh, int kw, int oc_pad,
+                                                  int cin_pad) {
+  const int taps = kh * kw;
+  std::vector<uint16_t> out((size_t)oc_pad * taps * cin_pad, 0);
+  for (int o = 0; o < oc; ++o)
+    for (int c = 0; c < icg; ++c)
+      for (int r = 0; r < kh; ++r)
+        for (int s = 0; s < kw; ++s)
+          out[((size_t)o * taps + (r * kw + s)) * cin_pad + c] =
+              (uint16_t)(f32_bits(w[(((size_t)o * icg + c) * kh + r) * kw + s]) >> 16);
+  std::vector<int8_t> bytes(out.size() * 2);
+  std::memcpy(bytes.data(), out.data(), bytes.size());
+  return bytes;
 }
 
 inline void encode_weight_map(CUtensorMap *tm, const int8_t *d_w, int oc_pad, int taps, int k_inner,
@@ -291,7 +315,7 @@ inline void finish_plan(ConvPlan &pl, int rows, int taps, int k_inner, int oc_pa
   {
     bool pair = false;
     if (const char *e = getenv("TPUCB_PAIR"))
-      if (e[0] == '1') pair = oc_pad % 256 == 0 && p.a_mode != 2 && rows >= 256;
+      if (e[0] == '1') pair = !pl.bf16 && oc_pad % 256 == 0 && p.a_mode != 2 && rows >= 256;
     if (pair) {
       pl.pair = true;
       p.dual = 0;
@@ -373,7 +397,8 @@ inline void launch_conv_plan(const ConvPlan &pl, cudaStream_t stream, int sm_cou
     patch_expand_i8_kernel<<<grid_for(total, 256, sm_count), 256, 0, stream>>>(pl.in, pl.patch_buf,
                                                                               pl.patch);
   }
-  if (pl.pair) conv_gemm2_i8_kernel<<<pl.grid, kPairThreads, pl.smem, stream>>>(pl.tmA, pl.tmB, pl.p);
+  if (pl.bf16) conv_gemm_bf16_kernel<<<pl.grid, kConvThreads, pl.smem, stream>>>(pl.tmA, pl.tmB, pl.p);
+  else if (pl.pair) conv_gemm2_i8_kernel<<<pl.grid, kPairThreads, pl.smem, stream>>>(pl.tmA, pl.tmB, pl.p);
   else conv_gemm_i8_kernel<<<pl.grid, kConvThreads, pl.smem, stream>>>(pl.tmA, pl.tmB, pl.p);
 }
 
@@ -382,6 +407,8 @@ inline void conv_kernel_setup_once() {
     TPUCB_CUDA(cudaFuncSetAttribute(conv_gemm_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     227 * 1024));
     TPUCB_CUDA(cudaFuncSetAttribute(conv_gemm2_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    227 * 1024));
+    TPUCB_CUDA(cudaFuncSetAttribute(conv_gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     227 * 1024));
     return true;
   }();

@@ -215,4 +215,222 @@ __global__ void reduce_kernel(const void *__restrict__ in, void *__restrict__ ou
   }
 }
 
+// ------------------------------------------------------------------ BF16 element-wise / pooling
+// BF16 tensors hold 8 values per 16-byte vector (channel pitch a multiple of 16 values).
+__device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+
+struct EltwiseBf16Args {
+  const uint4 *in[4];
+  float coeff[4];
+  int nin;
+  int do_relu;
+};
+// EltwiseAddOpKernel / EltwiseMulOpKernel in BF16 (core/eltwise.cpp:41-52, 101-104, 320-333): the fp32
+// form, operand by operand from 0 (add) or 1 (mul), product and sum rounded separately, ReLU, then one
+// BF16 rounding of the result.
+template <bool MUL> __global__ void eltwise_bf16_kernel(EltwiseBf16Args a, uint4 *__restrict__ out, size_t nvec) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = MUL ? 1.0f : 0.0f;
+    for (int k = 0; k < a.nin; ++k) {
+      const uint4 v = __ldg(a.in[k] + i);
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+      const float co = a.coeff[k];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float lo = bf16_lo(w[j]), hi = bf16_hi(w[j]);
+        if (MUL) {
+          acc[2 * j] = __fmul_rn(acc[2 * j], lo);
+          acc[2 * j + 1] = __fmul_rn(acc[2 * j + 1], hi);
+        } else {
+          acc[2 * j] = __fadd_rn(acc[2 * j], __fmul_rn(co, lo));
+          acc[2 * j + 1] = __fadd_rn(acc[2 * j + 1], __fmul_rn(co, hi));
+        }
+      }
+    }
+    if (a.do_relu) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = acc[j] > 0.0f ? acc[j] : 0.0f;
+    }
+    uint4 o;
+    o.x = bf16x2_round_bits(acc[0], acc[1]);
+    o.y = bf16x2_round_bits(acc[2], acc[3]);
+    o.z = bf16x2_round_bits(acc[4], acc[5]);
+    o.w = bf16x2_round_bits(acc[6], acc[7]);
+    out[i] = o;
+  }
+}
+
+// PoolingOpKernel in BF16 (core/pooling.cpp:91-94): the fp32 pooling on BF16 values. The maximum of
+// BF16 values is a BF16 value; the average (sum over the valid taps in row order, divided by kh*kw
+// or by the number of valid taps) is rounded to BF16 when stored, where the reference's fp32
+// container keeps the unrounded quotient: at most half a BF16 ulp apart.
+__global__ void pool_bf16_kernel(const uint4 *__restrict__ in, uint4 *__restrict__ out, PoolArgs a, int count_include_pad) {
+  const int vecs = a.cp / 8;
+  const size_t total = (size_t)a.n * a.oh * a.ow * vecs;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int v = (int)(i % vecs);
+    size_t pix = i / vecs;
+    const int x = (int)(pix % a.ow);
+    size_t t = pix / a.ow;
+    const int y = (int)(t % a.oh);
+    const int b = (int)(t / a.oh);
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = a.method == 0 ? -INFINITY : 0.0f;
+    int cnt = 0;
+    for (int r = 0; r < a.kh; ++r) {
+      const int yy = y * a.sh - a.pt + r;
+      if (yy < 0 || yy >= a.ih) continue;
+      for (int s = 0; s < a.kw; ++s) {
+        const int xx = x * a.sw - a.pl + s;
+        if (xx < 0 || xx >= a.iw) continue;
+        const uint4 q = __ldg(in + (((size_t)b * a.ih + yy) * a.iw + xx) * vecs + v);
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float lo = bf16_lo(w[j]), hi = bf16_hi(w[j]);
+          if (a.method == 0) {
+            acc[2 * j] = fmaxf(acc[2 * j], lo);
+            acc[2 * j + 1] = fmaxf(acc[2 * j + 1], hi);
+          } else {
+            acc[2 * j] = __fadd_rn(acc[2 * j], lo);
+            acc[2 * j + 1] = __fadd_rn(acc[2 * j + 1], hi);
+          }
+        }
+        ++cnt;
+      }
+    }
+    if (a.method != 0) {
+      const float d = (float)(count_include_pad ? a.kh * a.kw : cnt);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = __fdiv_rn(acc[j], d);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (v * 8 + j >= a.c) acc[j] = 0.0f;
+    uint4 o;
+    o.x = bf16x2_round_bits(acc[0], acc[1]);
+    o.y = bf16x2_round_bits(acc[2], acc[3]);
+    o.z = bf16x2_round_bits(acc[4], acc[5]);
+    o.w = bf16x2_round_bits(acc[6], acc[7]);
+    out[i] = o;
+  }
+}
+
+// ----------------------------------------------------------------------- matmul (two activations)
+// MatMulOpKernel (core/matmul.cpp:33-97): out[b] = left[b] (M x K) * right[b] (K x N) over
+// batch = batch_high * batch_low, optional ReLU, then QDM requantisation with one (multiplier, rshift)
+// pair (INT8, skipped when both are zero), one BF16 rounding (BF16) or nothing (fp32). The transposes
+// are storage orders, not arithmetic: left [bh, M, bl, K], right [bh, K, bl, N], out [bh, M, bl, N]
+// instead of [bh, bl, rows, cols]. Both operands are activations, so neither is packed beforehand:
+// 16 x 16 tiles of each are staged in shared memory through the tensors' own geometry.
+struct MatMulArgs {
+  TensorGeom ga, gb, go;
+  int bh, bl, M, K, N;
+  int lt, rt, ot;
+  int dt, do_relu, mult, rshift, requant;
+};
+__device__ __forceinline__ size_t matmul_index(int trans, int bh, int bl, int nbl, int rows, int cols, int r, int c) {
+  return trans ? (((size_t)bh * rows + r) * nbl + bl) * cols + c : (((size_t)bh * nbl + bl) * rows + r) * cols + c;
+}
+template <int DT> __global__ void matmul_kernel(const void *__restrict__ a, const void *__restrict__ b, void *__restrict__ out, MatMulArgs p) {
+  __shared__ float As[16][17], Bs[16][17];
+  const int tx = threadIdx.x, ty = threadIdx.y;
+  const int bh = blockIdx.z / p.bl, bl = blockIdx.z % p.bl;
+  const int m = blockIdx.y * 16 + ty, n = blockIdx.x * 16 + tx;
+  float accf = 0.0f;
+  int acci = 0;
+  for (int k0 = 0; k0 < p.K; k0 += 16) {
+    float av = 0.0f, bv = 0.0f;
+    if (m < p.M && k0 + tx < p.K) av = load_as_f32(a, DT, phys_offset(p.ga, matmul_index(p.lt, bh, bl, p.bl, p.M, p.K, m, k0 + tx)));
+    if (k0 + ty < p.K && n < p.N) bv = load_as_f32(b, DT, phys_offset(p.gb, matmul_index(p.rt, bh, bl, p.bl, p.K, p.N, k0 + ty, n)));
+    As[ty][tx] = av;
+    Bs[ty][tx] = bv;
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < 16; ++k) {
+      if (DT == DT_I8) acci += (int)As[ty][k] * (int)Bs[k][tx];
+      else accf = fmaf(As[ty][k], Bs[k][tx], accf);
+    }
+    __syncthreads();
+  }
+  if (m >= p.M || n >= p.N) return;
+  const size_t po = phys_offset(p.go, matmul_index(p.ot, bh, bl, p.bl, p.M, p.N, m, n));
+  if (DT == DT_I8) {
+    if (p.do_relu) acci = max(acci, 0);
+    const int q = p.requant ? qdm_requant(acci, p.mult, p.rshift) : clamp_i8(acci);
+    reinterpret_cast<int8_t *>(out)[po] = (int8_t)q;
+  } else {
+    if (p.do_relu) accf = fmaxf(accf, 0.0f);
+    if (DT == DT_BF16) reinterpret_cast<uint16_t *>(out)[po] = f32_to_bf16_bits(accf);
+    else reinterpret_cast<float *>(out)[po] = accf;
+  }
+}
+
+// ----------------------------------------------------------------------------- BF16 softmax
+// SoftmaxOpKernel::invoke_bf16 (core/softmax.cpp:88-151) over the channel axis, one pixel per CTA:
+// max, BF16(x - max), exp through the 256-entry slope table (lut_func.cpp:169-186, range 15),
+// sum_j ex_j * BF16(BF16(C)/C), reciprocal (or logarithm, do_log) of the BF16-rounded sum through the
+// exponent / mantissa tables (lut_func.cpp:306-333), BF16(ex * 1/sum) or BF16(sub - log sum).
+// The reference accumulates the sum in fp32 in channel order and rounds it once; an fp32 sum depends on
+// its order, so one thread adds the channels in that order from shared memory (4 cycles per add:
+// 2 us for 1000 channels) while every other step is spread over the CTA.
+struct SoftmaxBf16Args {
+  const float *exp_base, *exp_slope, *rec_exp, *rec_mant;
+  int c, cp, do_log;
+  float lut_scale, const_val;
+};
+__global__ void softmax_bf16_kernel(const uint16_t *__restrict__ in, uint16_t *__restrict__ out, SoftmaxBf16Args a) {
+  extern __shared__ float sm_buf[]; // sub[c], ex[c]
+  __shared__ float red[32];
+  __shared__ float s_r;
+  float *sub = sm_buf, *ex = sm_buf + a.c;
+  const uint16_t *p = in + (size_t)blockIdx.x * a.cp;
+  uint16_t *q = out + (size_t)blockIdx.x * a.cp;
+  float mx = -INFINITY;
+  for (int i = threadIdx.x; i < a.c; i += blockDim.x) {
+    const float x = bf16_bits_to_f32(p[i]);
+    sub[i] = x;
+    mx = fmaxf(mx, x);
+  }
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = mx;
+  __syncthreads();
+  mx = red[0];
+  for (int i = 1; i < (int)(blockDim.x >> 5); ++i) mx = fmaxf(mx, red[i]);
+  for (int i = threadIdx.x; i < a.c; i += blockDim.x) {
+    const float d = bf16_round(__fsub_rn(sub[i], mx));
+    sub[i] = d;
+    const float r = bf16_round(__fmul_rn(d, a.lut_scale));
+    const int idx = f32_to_int8_rz(r);
+    const float dx = bf16_round(__fsub_rn(r, (float)idx));
+    ex[i] = bf16_round(__fadd_rn(__ldg(a.exp_base + (idx & 0xff)), __fmul_rn(dx, __ldg(a.exp_slope + (idx & 0xff)))));
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float sum = 0.0f;
+    for (int j = 0; j < a.c; ++j) sum = __fadd_rn(sum, __fmul_rn(ex[j], a.const_val));
+    const uint32_t h = f32_to_bf16_bits(sum);
+    const float v = bf16_bits_to_f32((uint16_t)h);
+    int e;
+    if (v == 0.0f) e = 0;
+    else {
+      e = (int)((h >> 7) & 0xff) - 127 + 63 + ((h & 0x8000u) ? 128 : 0); // floor(log2 |v|) of a normal value
+      e = min(max(e, 0), 255);
+    }
+    const float te = __ldg(a.rec_exp + e), tm = __ldg(a.rec_mant + (h & 0xff));
+    s_r = bf16_round(a.do_log ? __fadd_rn(te, tm) : __fmul_rn(te, tm));
+  }
+  __syncthreads();
+  const float r = s_r;
+  for (int i = threadIdx.x; i < a.cp; i += blockDim.x) {
+    float y = 0.0f;
+    if (i < a.c) y = a.do_log ? __fsub_rn(sub[i], r) : __fmul_rn(ex[i], r);
+    q[i] = f32_to_bf16_bits(y);
+  }
+}
+
 } // namespace tpucb

@@ -330,9 +330,55 @@ public:
     std::vector<float> bias(g.oc, 0.0f);
     if (with_bias) bias = I.weight(op.in[2]).data;
     alg_ops = 2.0 * g.n * g.oc * g.oh * g.ow * icg * g.kh * g.kw;
-    if (out->dtype == DT_F32 || out->dtype == DT_BF16) {
-      TPUCB_CHECK(in->dtype == DT_F32 && out->dtype == DT_F32, "conv %s: BF16 convolution is not implemented",
-                  op.name.c_str());
+    if (out->dtype == DT_BF16) {
+      // BF16 graphs (core/conv.cpp:90-98: fp32 convolution of BF16-valued operands, fp32 bias, ReLU, BF16 rounding):
+      // the tensor-core pipeline with BF16 operands and fp32 accumulators; every K size and pitch is in bytes.
+      TPUCB_CHECK(in->dtype == DT_BF16, "conv %s: a BF16 convolution needs a BF16 input", op.name.c_str());
+      TPUCB_CHECK(g.g == 1 && !g.ins_h && !g.ins_w && !in->padded_rows() && g.ic >= 8 && g.pl <= 127 && g.pt <= 127 &&
+                      (g.kw - 1) * g.dw <= 255 && (g.kh - 1) * g.dh <= 255,
+                  "conv %s: BF16 convolution supports dense, ungrouped layers with at least 8 input channels", op.name.c_str());
+      conv_kernel_setup_once();
+      std::vector<int32_t> bias_bits(out->cp, 0);
+      for (int o = 0; o < g.oc; ++o) bias_bits[o] = (int32_t)f32_bits(bias[o]);
+      d_bias_ = I.upload(bias_bits);
+      act_ = do_relu_ ? 1 : 0;
+      ConvPlan pl;
+      std::memset(&pl.p, 0, sizeof(pl.p));
+      pl.bf16 = true;
+      pl.in = (const int8_t *)in->dev;
+      ConvGemmParams &p = pl.p;
+      p.OH = g.oh; p.OW = g.ow; p.sh = g.sh; p.sw = g.sw; p.pt = g.pt; p.pl = g.pl; p.dh = g.dh; p.dw = g.dw;
+      p.act = act_;
+      p.bias = d_bias_; p.mult = d_bias_; p.rshift = d_bias_;
+      p.out = (int8_t *)out->dev;
+      p.ldc = out->cp * 2; // bytes
+      p.c_off = 0;
+      p.err = I.d_err;
+      const int rows = g.n * g.oh * g.ow;
+      const int k_bytes = in->cp * 2;
+      const bool one_by_one_bf = g.kh == 1 && g.kw == 1 && g.sh == 1 && g.sw == 1 && g.pt == 0 && g.pl == 0 && g.pb == 0 && g.pr == 0;
+      const int8_t *d_w = I.upload(pack_conv_weights_bf16(filt.data.data(), g.oc, g.ic, g.kh, g.kw, out->cp, in->cp));
+      if (one_by_one_bf) {
+        p.kh = p.kw = 1;
+        p.a_mode = 0;
+        finish_plan(pl, rows, 1, k_bytes, out->cp, I.sm_count);
+        encode_matrix_map(&pl.tmA, (const int8_t *)in->dev, rows, k_bytes, k_bytes, p.BK);
+        encode_weight_map(&pl.tmB, d_w, out->cp, 1, k_bytes, p.BK, p.dual ? 192 : p.BN);
+      } else {
+        p.kh = g.kh; p.kw = g.kw;
+        p.a_mode = 1;
+        finish_plan(pl, rows, g.kh * g.kw, k_bytes, out->cp, I.sm_count);
+        encode_im2col_map(&pl.tmA, (const int8_t *)in->dev, g, k_bytes, p.BK);
+        encode_weight_map(&pl.tmB, d_w, out->cp, g.kh * g.kw, k_bytes, p.BK, p.dual ? 192 : p.BN);
+      }
+      p.idesc = make_idesc_bf16(128, p.BN);
+      pl.ops = alg_ops;
+      plans_.push_back(pl);
+      alg_bytes = 2.0 * ((double)in->numel() + out->numel() + filt.data.size()) + 4.0 * g.oc;
+      return;
+    }
+    if (out->dtype == DT_F32) {
+      TPUCB_CHECK(in->dtype == DT_F32, "conv %s: an fp32 convolution needs an fp32 input", op.name.c_str());
       f32_ = true;
       f32_w_ = I.upload(pack_conv_weights_f32(filt.data.data(), g.oc, icg, g.kh, g.kw, g.g));
       f32_b_ = I.upload(bias);
@@ -564,8 +610,46 @@ public:
     std::vector<float> bias(n_, 0.0f);
     if (op.in.size() > 2 && I.has_weight(op.in[2])) bias = I.weight(op.in[2]).data;
     alg_ops = 2.0 * m_ * k_ * n_;
+    if (out->dtype == DT_BF16) {
+      // BF16 inner product (core/fullyconnected.cpp:44-91 with the BF16 rounding of the result): the tensor-core
+      // pipeline with BF16 operands, fp32 accumulators and fp32 bias; K sizes and pitches in bytes.
+      TPUCB_CHECK(in->dtype == DT_BF16, "fc %s: a BF16 inner product needs a BF16 input", op.name.c_str());
+      conv_kernel_setup_once();
+      const int n_pad = out->cp;
+      kdev_ = hw * in->cp;
+      std::vector<uint16_t> w((size_t)n_pad * kdev_, 0);
+      for (int j = 0; j < n_; ++j)
+        for (int c = 0; c < in->c; ++c)
+          for (int p = 0; p < hw; ++p)
+            w[(size_t)j * kdev_ + (size_t)p * in->cp + c] = (uint16_t)(f32_bits(filt.data[(size_t)j * k_ + (size_t)c * hw + p]) >> 16);
+      std::vector<int8_t> wb(w.size() * 2);
+      std::memcpy(wb.data(), w.data(), wb.size());
+      const int8_t *d_w = I.upload(wb);
+      std::vector<int32_t> bias_bits(n_pad, 0);
+      for (int j = 0; j < n_; ++j) bias_bits[j] = (int32_t)f32_bits(bias[j]);
+      ConvPlan pl;
+      std::memset(&pl.p, 0, sizeof(pl.p));
+      pl.bf16 = true;
+      ConvGemmParams &p = pl.p;
+      p.bias = I.upload(bias_bits);
+      p.mult = p.bias; p.rshift = p.bias;
+      p.out = (int8_t *)out->dev;
+      p.ldc = out->cp * 2;
+      p.c_off = 0;
+      p.err = I.d_err;
+      p.OH = p.OW = 1; p.sh = p.sw = p.dh = p.dw = 1; p.kh = p.kw = 1;
+      p.act = do_relu_ ? 1 : 0;
+      p.a_mode = 0;
+      finish_plan(pl, m_, 1, kdev_ * 2, n_pad, I.sm_count);
+      encode_matrix_map(&pl.tmA, (const int8_t *)in->dev, m_, kdev_ * 2, kdev_ * 2, p.BK);
+      encode_weight_map(&pl.tmB, d_w, n_pad, 1, kdev_ * 2, p.BK, p.dual ? 192 : p.BN);
+      p.idesc = make_idesc_bf16(128, p.BN);
+      plan_ = pl;
+      alg_bytes = 2.0 * ((double)m_ * k_ + (double)n_ * k_ + (double)m_ * n_) + 4.0 * n_;
+      return;
+    }
     if (out->dtype != DT_I8) {
-      TPUCB_CHECK(in->dtype == DT_F32 && out->dtype == DT_F32, "fc %s: BF16 is not implemented", op.name.c_str());
+      TPUCB_CHECK(in->dtype == DT_F32 && out->dtype == DT_F32, "fc %s: an fp32 inner product needs an fp32 input", op.name.c_str());
       f32_ = true;
       // weights in device K order: (y, x, c) with pitch in->cp
       kdev_ = hw * in->cp;
@@ -647,7 +731,6 @@ public:
       a.rshift = (int)(uint32_t)I.weight(op.in[3]).data.at(0);
       a.mult = (int)(uint32_t)I.weight(op.in[4]).data.at(0);
     }
-    TPUCB_CHECK(in->dtype != DT_BF16, "pool %s: BF16 pooling is not implemented", op.name.c_str());
     a_ = a;
     alg_bytes = ((double)in->numel() + out->numel()) * in->elsize();
   }
@@ -660,6 +743,9 @@ public:
         pool_avg_wide_i8_kernel<<<grid_for(total * 8, 128, I_.sm_count), 128, 0, s>>>((const int8_t *)in_->dev, (int8_t *)out_->dev, a_);
       else
         pool_i8_kernel<<<grid_for(total, 128, I_.sm_count), 128, 0, s>>>((const int8_t *)in_->dev, (int8_t *)out_->dev, a_);
+    } else if (in_->dtype == DT_BF16) {
+      size_t total = out_->pixels() * (out_->cp / 8);
+      pool_bf16_kernel<<<grid_for(total, 128, I_.sm_count), 128, 0, s>>>((const uint4 *)in_->dev, (uint4 *)out_->dev, a_, count_include_pad_);
     } else {
       launch_pool_f32((const float *)in_->dev, (float *)out_->dev, a_, count_include_pad_, s, I_.sm_count);
     }
@@ -699,25 +785,39 @@ public:
       if (is_mul) a_.qdm_mult = (int)(uint32_t)mu.at(0);
       else
         for (int i = 0; i < nin; ++i) a_.mult[i] = (int)(int8_t)mu.at(i);
+    } else if (out->dtype == DT_BF16) {
+      b_.nin = nin;
+      b_.do_relu = do_relu_;
+      for (int i = 0; i < nin; ++i) {
+        b_.in[i] = (const uint4 *)ins[i]->dev;
+        b_.coeff[i] = 1.0f;
+      }
+      parse_coeff(op, b_.coeff, is_mul ? 0 : nin);
     } else {
-      TPUCB_CHECK(out->dtype == DT_F32 && !is_mul, "eltwise %s: only fp32 add is implemented outside INT8", op.name.c_str());
+      TPUCB_CHECK(out->dtype == DT_F32 && !is_mul, "eltwise %s: fp32 supports add only", op.name.c_str());
       f_.nin = nin;
       f_.do_relu = do_relu_;
       for (int i = 0; i < nin; ++i) {
         f_.in[i] = (const float *)ins[i]->dev;
         f_.coeff[i] = 1.0f;
       }
-      std::string co = op.gets("coeff", "");
-      if (!co.empty()) {
-        std::stringstream ss(co);
-        std::string tok;
-        int i = 0;
-        while (std::getline(ss, tok, ',') && i < nin) f_.coeff[i++] = (float)atof(tok.c_str());
-      }
+      parse_coeff(op, f_.coeff, nin);
     }
   }
+  static void parse_coeff(const ParsedOp &op, float *coeff, int nin) {
+    std::string co = op.gets("coeff", "");
+    if (co.empty()) return;
+    std::stringstream ss(co);
+    std::string tok;
+    int i = 0;
+    while (std::getline(ss, tok, ',') && i < nin) coeff[i++] = (float)atof(tok.c_str());
+  }
   void invoke(cudaStream_t s) override {
-    if (out_->dtype == DT_I8) {
+    if (out_->dtype == DT_BF16) {
+      size_t nvec = out_->bytes() / 16;
+      if (is_mul_) eltwise_bf16_kernel<true><<<grid_for(nvec, 256, I_.sm_count), 256, 0, s>>>(b_, (uint4 *)out_->dev, nvec);
+      else eltwise_bf16_kernel<false><<<grid_for(nvec, 256, I_.sm_count), 256, 0, s>>>(b_, (uint4 *)out_->dev, nvec);
+    } else if (out_->dtype == DT_I8) {
       size_t nvec = out_->bytes() / 16;
       if (is_mul_) eltwise_mul_i8_kernel<<<grid_for(nvec, 256, I_.sm_count), 256, 0, s>>>(a_, (int8_t *)out_->dev, nvec);
       else {
@@ -748,6 +848,7 @@ private:
   int do_relu_ = 0;
   EltwiseArgs a_;
   EltwiseF32Args f_;
+  EltwiseBf16Args b_;
 };
 
 // --------------------------------------------------------------------------- Concat
@@ -1143,6 +1244,67 @@ private:
   ReduceArgs p_;
 };
 
+// --------------------------------------------------------------------------- MatMul
+// MatMulOpKernel (core/matmul.cpp:9-97) with the dimension rule of parseMatMulParam
+// (lib/Dialect/TPU/IR/TPUOperationSupport.cpp:615-655).
+class MatMulOp : public OpKernel {
+public:
+  MatMulOp(Interpreter &I, const ParsedOp &op, TensorPtr a, TensorPtr b, TensorPtr out) : I_(I), a_(a), b_(b), out_(out) {
+    TPUCB_CHECK(a->dtype == out->dtype && b->dtype == out->dtype, "matmul %s: operands and result must share a type", op.name.c_str());
+    const auto &as = a->shape, &bs = b->shape, &os = out->shape;
+    const int rank = (int)os.size();
+    TPUCB_CHECK(rank >= 2 && rank <= 4 && (int)as.size() == rank && (int)bs.size() == rank, "matmul %s: operands and result need the same rank (2 to 4)",
+                op.name.c_str());
+    MatMulArgs &p = p_;
+    p.lt = op.geti("left_transpose", 0); p.rt = op.geti("right_transpose", 0); p.ot = op.geti("output_transpose", 0);
+    const int axis = rank - 1;
+    p.bh = p.bl = 1;
+    if (p.lt || p.rt || p.ot) {
+      TPUCB_CHECK(rank >= 3, "matmul %s: transposes need rank 3 or 4", op.name.c_str());
+      p.K = (int)as[axis]; p.N = (int)os[axis];
+      if (p.lt) { p.bl = (int)as[axis - 1]; p.M = (int)as[axis - 2]; }
+      else { p.bl = (int)as[axis - 2]; p.M = (int)as[axis - 1]; }
+      if (axis == 3) p.bh = (int)as[0];
+    } else {
+      for (int i = 0; i < axis - 1; ++i) {
+        TPUCB_CHECK(as[i] == os[i] && as[i] == bs[i], "matmul %s: batch dimensions differ", op.name.c_str());
+        p.bh *= (int)as[i];
+      }
+      p.M = (int)as[axis - 1]; p.K = (int)as[axis]; p.N = (int)bs[axis];
+      TPUCB_CHECK(p.K == bs[axis - 1] && p.M == os[axis - 1] && p.N == os[axis], "matmul %s: [M,K] x [K,N] -> [M,N] shapes do not agree", op.name.c_str());
+    }
+    const size_t batch = (size_t)p.bh * p.bl;
+    TPUCB_CHECK(a->numel() == batch * p.M * p.K && b->numel() == batch * p.K * p.N && out->numel() == batch * p.M * p.N,
+                "matmul %s: tensor sizes do not match batch %zu, M %d, K %d, N %d", op.name.c_str(), batch, p.M, p.K, p.N);
+    TPUCB_CHECK(batch <= 65535, "matmul %s: batch %zu is beyond one launch", op.name.c_str(), batch);
+    p.ga = geom_of(a); p.gb = geom_of(b); p.go = geom_of(out);
+    p.dt = out->dtype;
+    p.do_relu = op.geti("do_relu", 0);
+    p.mult = 0; p.rshift = 0;
+    if (out->dtype == DT_I8) {
+      // operands: left, right, quant_scale, quant_zeropoint, quant_rshift, quant_multiplier
+      TPUCB_CHECK(op.in.size() > 5 && I.has_weight(op.in[4]) && I.has_weight(op.in[5]), "matmul %s: INT8 needs rshift and multiplier operands", op.name.c_str());
+      p.rshift = (int)(uint32_t)I.weight(op.in[4]).data.at(0);
+      p.mult = (int)(uint32_t)I.weight(op.in[5]).data.at(0);
+      TPUCB_CHECK((double)p.K * 127.0 * 128.0 < 2147483648.0, "matmul %s: K = %d overflows the int32 sum", op.name.c_str(), p.K);
+    }
+    p.requant = (p.rshift != 0 || p.mult != 0) ? 1 : 0;
+    alg_ops = 2.0 * batch * p.M * p.K * p.N;
+    alg_bytes = ((double)a->numel() + b->numel() + out->numel()) * out->elsize();
+  }
+  void invoke(cudaStream_t s) override {
+    const dim3 grid((p_.N + 15) / 16, (p_.M + 15) / 16, p_.bh * p_.bl), block(16, 16);
+    if (p_.dt == DT_I8) matmul_kernel<DT_I8><<<grid, block, 0, s>>>(a_->dev, b_->dev, out_->dev, p_);
+    else if (p_.dt == DT_BF16) matmul_kernel<DT_BF16><<<grid, block, 0, s>>>(a_->dev, b_->dev, out_->dev, p_);
+    else matmul_kernel<DT_F32><<<grid, block, 0, s>>>(a_->dev, b_->dev, out_->dev, p_);
+  }
+
+private:
+  Interpreter &I_;
+  TensorPtr a_, b_, out_;
+  MatMulArgs p_;
+};
+
 // ------------------------------------------------------------ fp32 Scale / Softmax
 // ScaleOpKernel (core/scale.cpp:15-37), SoftmaxOpKernel::invoke_fp32 (core/softmax.cpp:49-86).
 class ScaleOp : public OpKernel {
@@ -1171,17 +1333,41 @@ private:
 class SoftmaxOp : public OpKernel {
 public:
   SoftmaxOp(Interpreter &I, const ParsedOp &op, TensorPtr in, TensorPtr out) : I_(I), in_(in), out_(out) {
-    TPUCB_CHECK(in->dtype == DT_F32 && out->dtype == DT_F32, "softmax %s: fp32 only", op.name.c_str());
+    TPUCB_CHECK(in->dtype == out->dtype && out->dtype != DT_I8, "softmax %s: fp32 or BF16 (as the reference)", op.name.c_str());
     TPUCB_CHECK(op.geti("axis", 1) == 1, "softmax %s: channel axis only", op.name.c_str());
-    alg_bytes = 8.0 * out->numel();
+    alg_bytes = 2.0 * out->numel() * out->elsize();
+    if (out->dtype == DT_BF16) {
+      // operands: input, exponential_table, exponential_slope_table, reciprocal_table, reciprocal_mantissa_table
+      TPUCB_CHECK(op.in.size() >= 5, "softmax %s: BF16 needs the four table operands", op.name.c_str());
+      const float *t[4];
+      for (int i = 0; i < 4; ++i) {
+        const auto &w = I.weight(op.in[1 + i]).data;
+        TPUCB_CHECK(w.size() >= 256, "softmax %s: table %s has %zu entries, expected 256", op.name.c_str(), op.in[1 + i].c_str(), w.size());
+        t[i] = I.upload(std::vector<float>(w.begin(), w.begin() + 256));
+      }
+      b_.exp_base = t[0]; b_.exp_slope = t[1]; b_.rec_exp = t[2]; b_.rec_mant = t[3];
+      b_.c = out->c; b_.cp = out->cp;
+      b_.do_log = op.geti("do_log", 0);
+      b_.lut_scale = bf16_round(256.0f / 30.0f); // the exp table spans [-15, 15] (lut_func.hpp:8-15)
+      b_.const_val = bf16_round(bf16_round((float)out->c) / (float)out->c);
+      smem_ = 2 * (size_t)out->c * sizeof(float);
+      TPUCB_CHECK(smem_ <= 200 * 1024, "softmax %s: %d channels do not fit one CTA's shared memory", op.name.c_str(), out->c);
+      if (smem_ > 48 * 1024)
+        TPUCB_CUDA(cudaFuncSetAttribute(softmax_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_));
+    }
   }
   void invoke(cudaStream_t s) override {
-    softmax_f32_kernel<<<(unsigned)out_->pixels(), 128, 0, s>>>((const float *)in_->dev, (float *)out_->dev, out_->c, out_->cp);
+    if (out_->dtype == DT_BF16)
+      softmax_bf16_kernel<<<(unsigned)out_->pixels(), 128, smem_, s>>>((const uint16_t *)in_->dev, (uint16_t *)out_->dev, b_);
+    else
+      softmax_f32_kernel<<<(unsigned)out_->pixels(), 128, 0, s>>>((const float *)in_->dev, (float *)out_->dev, out_->c, out_->cp);
   }
 
 private:
   Interpreter &I_;
   TensorPtr in_, out_;
+  SoftmaxBf16Args b_;
+  size_t smem_ = 0;
 };
 
 // ====================================================================== Interpreter bodies
@@ -1428,6 +1614,8 @@ inline void Interpreter::load_module(const std::string &text) {
       k.reset(new RemapOp(*this, op, opd(0), out));
     } else if (op.type == "reduce_mean" || op.type == "reduce_sum" || op.type == "reduce_max" || op.type == "reduce_min") {
       k.reset(new ReduceOp(*this, op, opd(0), out));
+    } else if (op.type == "matmul") {
+      k.reset(new MatMulOp(*this, op, opd(0), opd(1), out));
     } else if (op.type == "concat") {
       std::vector<TensorPtr> ins;
       for (auto &nm : op.in)

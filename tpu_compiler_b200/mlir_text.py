@@ -173,7 +173,7 @@ def convert(mlir_text):
         elif op == "leaky_relu":
             kv = {"negative_slope": repr(float(attrs.get("negative_slope", 0.0)))}
         elif op == "softmax":
-            kv = {"axis": int(attrs.get("axis", 1))}
+            kv = {"axis": int(attrs.get("axis", 1)), "do_log": int(bool(attrs.get("do_log", False)))}
         elif op in ("eltwise_max", "eltwise_min"):
             kv = {"do_relu": int(bool(attrs.get("do_relu", False)))}
         elif op in ("broadcast_add", "broadcast_sub", "broadcast_mul"):
@@ -189,6 +189,8 @@ def convert(mlir_text):
             kv = {"order": ",".join(str(int(v)) for v in attrs.get("order", []))}
         elif op in ("reduce_mean", "reduce_sum", "reduce_max", "reduce_min"):
             kv = {"axes": ",".join(str(int(v)) for v in attrs.get("axes", []))}
+        elif op == "matmul":
+            kv = {k: int(bool(attrs.get(k, False))) for k in ("do_relu", "left_transpose", "right_transpose", "output_transpose")}
         if op == "reshape":
             dtype = None  # alias: inherits the operand's type
         parts = [op, "name=" + name]

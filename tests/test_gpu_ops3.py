@@ -233,3 +233,13 @@ def test_softmax_bf16(cfg, do_log):
     b.op("softmax", "y", ["x", "eb", "es", "re", "rm"], cfg["shape"], "BF16", axis=1, do_log=do_log)
     x = O.bf16_round(rng.normal(0, cfg["sd"], cfg["shape"]))
     assert_exact(run_both(b.text(), b.weights, {"x": x}, ["y"]))
+
+
+@pytest.mark.parametrize("relu", [False, True])
+@pytest.mark.parametrize("rshift_range", [(0, 4), (8, 30), (28, 32)])
+def test_conv_i8_requant_forms(relu, rshift_range):
+    """Both forms of the tensor-core requantisation against the oracle: shifts up to 29 take the multiply-high
+    form, a layer with a larger shift the 64-bit multiply-add form; small shifts saturate most outputs."""
+    model = graphs.single_conv_i8(n=2, c_in=64, c_out=160, hw=12, k=3, pad=1, relu=relu, seed=4100 + rshift_range[0],
+                                  rshift_range=rshift_range)
+    assert_exact(run_both(model.text, model.weights, model.meta, ["conv"]))

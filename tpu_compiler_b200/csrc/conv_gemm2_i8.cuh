@@ -101,10 +101,43 @@ __device__ __forceinline__ void tcgen05_mma2_i8(uint32_t d_tmem, uint64_t adesc,
       : "memory");
 }
 
+// The same with the descriptors passed as (low, high) words, the high word shared: the issuing thread's loop
+// advances 32-bit start-address fields only.
+template <bool ACCUMULATE>
+__device__ __forceinline__ void tcgen05_mma2_i8_lohi(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t hi,
+                                                     uint32_t idesc, uint32_t accumulate) {
+  if (ACCUMULATE) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"
+        "setp.eq.b32 p, 0, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::i8 [%0], da, db, %4, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}" ::"r"(d_tmem),
+        "r"(a_lo), "r"(b_lo), "r"(hi), "r"(idesc), "r"(0u)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::i8 [%0], da, db, %4, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}" ::"r"(d_tmem),
+        "r"(a_lo), "r"(b_lo), "r"(hi), "r"(idesc), "r"(0u), "r"(accumulate)
+        : "memory");
+  }
+}
+template <int KSTEPS>
+__device__ __forceinline__ void tcgen05_mma2_i8_kblock(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t hi,
+                                                       uint32_t idesc, uint32_t accumulate_first) {
+  tcgen05_mma2_i8_lohi<false>(d_tmem, a_lo, b_lo, hi, idesc, accumulate_first);
+#pragma unroll
+  for (int k = 1; k < KSTEPS; ++k) tcgen05_mma2_i8_lohi<true>(d_tmem, a_lo + 2 * k, b_lo + 2 * k, hi, idesc, 1u);
+}
+
 } // namespace ptx
 
 constexpr int kPairEpilogueWarps = 16;
-constexpr int kPairThreads = 64 + 32 * kPairEpilogueWarps;
+// producer (activations), MMA issuer, 16 epilogue warps, second producer (weights)
+constexpr int kPairThreads = 64 + 32 * kPairEpilogueWarps + 32;
+constexpr int kPairWeightWarp = 2 + kPairEpilogueWarps;
 
 // Bounded wait that also ends when this CTA or any CTA of the launch has recorded an error.
 __device__ __forceinline__ bool pair_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
@@ -116,9 +149,8 @@ __device__ __forceinline__ bool pair_wait(uint32_t bar, uint32_t parity, volatil
   return false;
 }
 
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
-conv_gemm2_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                     const ConvGemmParams p) {
+template <bool PROF>
+__device__ __forceinline__ void conv_gemm2_body(const CUtensorMap &tmA, const CUtensorMap &tmB, const ConvGemmParams &p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = ptx::smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -166,9 +198,12 @@ conv_gemm2_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
   ptx::tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 0) {
-    // ------------------------------------------------------------ producer (one thread per CTA)
-    if (lane == 0) {
+  // One thread can start only one bulk tensor copy per ~410 cycles whatever its size (measured), and a K block
+  // of a tile pair is 534 tensor-pipe cycles: the activation half and the weight half of every stage are
+  // started by two threads of two warps. The activation thread of the leader arms the stage's barrier.
+  auto produce = [&](const bool do_a) {
+    {
+      long long pf_p0 = PROF ? clock64() : 0ll, pf_pwait = 0;
       int it = 0, ps = 0;
       uint32_t pph = 0;
       bool ok = *gerr == 0;
@@ -187,6 +222,7 @@ conv_gemm2_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         }
         int tap = 0, tr = 0, ts = 0, chunk = 0; // running counters: no divisions in this loop
         for (int kit = 0; kit < k_iters; ++kit, ++it) {
+          const long long pf_e0 = PROF ? clock64() : 0ll;
           if (it >= p.stages) {
             if (!pair_wait(bar_empty + 8 * ps, pph ^ 1u, abort_flag, gerr)) {
               if (!*abort_flag && !*gerr) atomicExch(p.err, kErrEmptyWait);
@@ -195,17 +231,21 @@ conv_gemm2_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
               break;
             }
           }
+          if (PROF) pf_pwait += clock64() - pf_e0;
           const int c0 = chunk * p.BK;
           const uint32_t w_dst = tiles + (uint32_t)ps * stage_bytes; // weights first, activations behind
           const uint32_t a_dst = w_dst + half_bytes;
           const uint32_t fb = leader_full + 8 * ps; // the leader's barrier
-          if (rank == 0) ptx::mbar_expect_tx(bar_full + 8 * ps, 2u * stage_bytes);
-          if (p.a_mode == 1)
-            ptx::tma2_load_im2col_4d(a_dst, &tmA, fb, c0, w_base, h_base, n_img, (uint16_t)(ts * p.dw),
-                                     (uint16_t)(tr * p.dh));
-          else
-            ptx::tma2_load_2d(a_dst, &tmA, fb, c0, m0);
-          ptx::tma2_load_3d(w_dst, &tmB, fb, c0, tap, n0);
+          if (do_a) {
+            if (rank == 0) ptx::mbar_expect_tx(bar_full + 8 * ps, 2u * stage_bytes);
+            if (p.a_mode == 1)
+              ptx::tma2_load_im2col_4d(a_dst, &tmA, fb, c0, w_base, h_base, n_img, (uint16_t)(ts * p.dw),
+                                       (uint16_t)(tr * p.dh));
+            else
+              ptx::tma2_load_2d(a_dst, &tmA, fb, c0, m0);
+          } else {
+            ptx::tma2_load_3d(w_dst, &tmB, fb, c0, tap, n0);
+          }
           if (++chunk == p.c_chunks) {
             chunk = 0;
             ++tap;
@@ -220,6 +260,10 @@ conv_gemm2_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
           }
         }
       }
+      if (PROF && do_a && rank == 0) {
+        atomicAdd(&g_conv_prof[5], (unsigned long long)(clock64() - pf_p0));
+        atomicAdd(&g_conv_prof[6], (unsigned long long)pf_pwait);
+      }
       if (!ok || *abort_flag) {
         // Failure path: give copies that are still in flight time to land before shared memory is
         // released (the leader also waits for every stage it armed).
@@ -233,6 +277,13 @@ conv_gemm2_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         }
       }
     }
+  };
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer of the activation halves
+    if (lane == 0) produce(true);
+  } else if (warp == kPairWeightWarp) {
+    // ------------------------------------------------------------ producer of the weight halves
+    if (lane == 0) produce(false);
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer (leader CTA only)
     if (lane == 0 && rank == 0 && *gerr == 0) {
@@ -240,12 +291,16 @@ conv_gemm2_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       uint32_t mph = 0;
       bool ok = true;
       const uint64_t desc0 = make_kmajor_desc(tiles, p.BK); // stages differ in the start-address field only
+      const uint32_t desc_hi = (uint32_t)(desc0 >> 32), desc_ring_lo = (uint32_t)desc0;
       const uint32_t stage_step = stage_bytes >> 4, half_step = half_bytes >> 4;
       const int ksteps = p.BK / 32;
-      const uint32_t peer_empty = ptx::mapa(bar_empty, 1u);
+      const uint32_t peer_empty0 = ptx::mapa(bar_empty, 1u);
       const uint32_t peer_acc_full = ptx::mapa(bar_acc_full, 1u);
+      uint32_t m_full = bar_full, m_empty = bar_empty, m_peer_empty = peer_empty0, ring_lo = desc_ring_lo;
+      long long pf_t0 = PROF ? clock64() : 0ll, pf_wait = 0, pf_accwait = 0, pf_blocks = 0;
       for (int tile = cluster_id; tile < total_tiles && ok; tile += n_clusters, ++t) {
         const int buf = t & 1;
+        const long long pf_a0 = PROF ? clock64() : 0ll;
         if (t >= 2) {
           if (!pair_wait(bar_acc_empty + 8 * buf, (uint32_t)(((t >> 1) - 1) & 1), abort_flag, gerr)) {
             if (!*abort_flag && !*gerr) atomicExch(p.err, kErrAccWait);
@@ -256,26 +311,39 @@ conv_gemm2_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
           ptx::tcgen05_fence_after();
         }
         const uint32_t d_tmem = tmem_base + (uint32_t)buf * 256u;
+        if (PROF) pf_accwait += clock64() - pf_a0;
         for (int kit = 0; kit < k_iters; ++kit, ++it) {
-          if (!pair_wait(bar_full + 8 * ms, mph, abort_flag, gerr)) {
+          const long long pf_w0 = PROF ? clock64() : 0ll;
+          if (!ptx::mbar_try_wait_cluster(m_full, mph) && !pair_wait(m_full, mph, abort_flag, gerr)) {
             if (!*abort_flag && !*gerr) atomicExch(p.err, kErrFullWait);
             *abort_flag = 1;
             ok = false;
             break;
           }
+          if (PROF) {
+            pf_wait += clock64() - pf_w0;
+            ++pf_blocks;
+          }
           ptx::tcgen05_fence_after();
           // transposed product: weights are the A operand (M = 256 channels over the two CTAs), the
           // activations the B operand (N = 256 pixels, 128 rows of it in each CTA)
-          const uint64_t adesc = desc0 + (uint64_t)((uint32_t)ms * stage_step);
-          const uint64_t bdesc = adesc + half_step;
-          for (int k = 0; k < ksteps; ++k)
-            ptx::tcgen05_mma2_i8(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), p.idesc,
-                                 (kit > 0 || k > 0) ? 1u : 0u);
-          ptx::tcgen05_commit2(bar_empty + 8 * ms);   // frees the stage in both CTAs once the MMAs retire
-          ptx::tcgen05_commit2(peer_empty + 8 * ms);
+          const uint32_t acc_first = kit > 0 ? 1u : 0u;
+          if (ksteps == 4) ptx::tcgen05_mma2_i8_kblock<4>(d_tmem, ring_lo, ring_lo + half_step, desc_hi, p.idesc, acc_first);
+          else if (ksteps == 2) ptx::tcgen05_mma2_i8_kblock<2>(d_tmem, ring_lo, ring_lo + half_step, desc_hi, p.idesc, acc_first);
+          else ptx::tcgen05_mma2_i8_kblock<1>(d_tmem, ring_lo, ring_lo + half_step, desc_hi, p.idesc, acc_first);
+          ptx::tcgen05_commit2(m_empty);   // frees the stage in both CTAs once the MMAs retire
+          ptx::tcgen05_commit2(m_peer_empty);
+          m_full += 8;
+          m_empty += 8;
+          m_peer_empty += 8;
+          ring_lo += stage_step;
           if (++ms == p.stages) {
             ms = 0;
             mph ^= 1u;
+            m_full = bar_full;
+            m_empty = bar_empty;
+            m_peer_empty = peer_empty0;
+            ring_lo = desc_ring_lo;
           }
         }
         if (ok) {
@@ -283,8 +351,15 @@ conv_gemm2_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
           ptx::tcgen05_commit2(peer_acc_full + 8 * buf);
         }
       }
+      if (PROF) {
+        atomicAdd(&g_conv_prof[0], (unsigned long long)(clock64() - pf_t0));
+        atomicAdd(&g_conv_prof[1], (unsigned long long)pf_wait);
+        atomicAdd(&g_conv_prof[2], (unsigned long long)pf_accwait);
+        atomicAdd(&g_conv_prof[3], (unsigned long long)pf_blocks);
+        atomicAdd(&g_conv_prof[4], 1ull);
+      }
     }
-  } else {
+  } else if (warp < kPairWeightWarp) {
     // ------------------------------------------------------------ epilogue (16 warps per CTA)
     const int quarter = warp & 3;        // TMEM lanes (= channels of this CTA's half) this warp may read
     const int cgroup = (warp - 2) >> 2;  // 0..3: takes the 32-pixel column groups cgroup, cgroup + 4
@@ -302,7 +377,10 @@ conv_gemm2_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         cc = load_chan_const(p, n0 + quarter * 32 + lane);
         staged_n0 = n0;
       }
+      const long long pf_q0 = PROF ? clock64() : 0ll;
       ok = pair_wait(bar_acc_full + 8 * buf, (uint32_t)((t >> 1) & 1), abort_flag, gerr);
+      if (PROF && warp == 2 && lane == 0 && rank == 0) atomicAdd(&g_conv_prof[7], (unsigned long long)(clock64() - pf_q0));
+      const long long pf_q1 = PROF ? clock64() : 0ll;
       if (!ok && !*abort_flag && !*gerr) {
         atomicExch(p.err, kErrAccWait);
         *abort_flag = 1;
@@ -317,6 +395,7 @@ conv_gemm2_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
       if (p.act == 1) epilogue_channels<1>(p, lane_addr, out4, ch4_ok, m0, cgroup, 4, lane, cc, ts, 256);
       else if (p.act == 2) epilogue_channels<2>(p, lane_addr, out4, ch4_ok, m0, cgroup, 4, lane, cc, ts, 256);
       else epilogue_channels<0>(p, lane_addr, out4, ch4_ok, m0, cgroup, 4, lane, cc, ts, 256);
+      if (PROF && warp == 2 && lane == 0 && rank == 0) atomicAdd(&g_conv_prof[8], (unsigned long long)(clock64() - pf_q1));
       // hand the accumulator buffer back to the leader's MMA issuer
       ptx::tcgen05_fence_before();
       __syncwarp();
@@ -334,6 +413,18 @@ conv_gemm2_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     ptx::tcgen05_fence_after();
     ptx::tcgen05_dealloc2(tmem_base, 512u);
   }
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
+conv_gemm2_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                     const ConvGemmParams p) {
+  conv_gemm2_body<false>(tmA, tmB, p);
+}
+// the same with the loop-profile counters on (see conv_gemm_prof_kernel; the leader CTA of each pair reports)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
+conv_gemm2_prof_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                       const ConvGemmParams p) {
+  conv_gemm2_body<true>(tmA, tmB, p);
 }
 
 } // namespace tpucb

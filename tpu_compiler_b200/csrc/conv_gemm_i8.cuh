@@ -56,6 +56,8 @@ struct ConvGemmParams {
   const int32_t *mult;   // [n_valid]
   const int32_t *rshift; // [n_valid]
   int8_t *out;
+  int fastq;      // bit 0: the multiply-high form of the requantisation applies (requant_fast; set by the host);
+                  // bit 1: every rshift of the layer is >= 1
   int8_t *out2;   // act == 2 only: the activation result goes here and `out` keeps the plain convolution result
   int *err;       // device error word (0 = ok)
 };
@@ -271,6 +273,7 @@ struct ChanConst {
   uint32_t M2, sbias;
   int32_t r, rnd, s1; // s1 = 31 when r > 0, 32 when r == 0: (uint)hi >> s1 is the "negative and r > 0" bit
   unsigned long long c2;
+  uint32_t kc;        // multiply-high form only (requant_fast), where r holds r + 1 and rnd holds 2 * rnd
 };
 
 __device__ __forceinline__ ChanConst load_chan_const(const ConvGemmParams &p, int n) {
@@ -287,6 +290,15 @@ __device__ __forceinline__ ChanConst load_chan_const(const ConvGemmParams &p, in
   c.sbias = (uint32_t)b + 0x80000000u;
   c.rnd = (int32_t)rnd;
   c.s1 = c.r > 0 ? 31 : 32;
+  c.kc = 0;
+  if (p.fastq & 1) {
+    // multiply-high form: see requant_fast
+    const uint32_t k = 1u + 2u * (uint32_t)rnd;
+    c.sbias = p.act == 1 ? 2u * (uint32_t)b : 2u * (uint32_t)b + 0x80000000u;
+    c.kc = p.act == 1 ? k : k - (uint32_t)M;
+    c.rnd = (int32_t)(2u * (uint32_t)rnd);
+    c.r = c.r + 1;
+  }
   return c;
 }
 
@@ -303,6 +315,31 @@ __device__ __forceinline__ int requant_one(int32_t acc, const ChanConst &q, cons
   asm("shr.u32 %0, %1, %2;" : "=r"(adj) : "r"((uint32_t)hi), "r"((uint32_t)q.s1)); // shifts >= 32 give 0
   int v = (hi + q.rnd - (int)adj) >> q.r;
   if (ACT == 2) v = min(max(v, -128), 127); // the leaky rescale below works on the saturated int8 value
+  return v;
+}
+// The same value from ONE multiply-high (the 32 x 32 + 64 multiply-add above costs about three multiply-class
+// instructions and an add on this SM). With t = floor(s * M / 2^30), hi = floor((t + 1) / 2) and, nesting the
+// floors, q = floor((t + k - 2 * neg) / 2^(r + 1)), k = 1 + 2 * rnd, neg = [t + 1 < 0 and r > 0].
+//   ReLU: the requantisation is monotone in s with q(0) = 0, so max(q(s), 0) = q(max(s, 0)): the clamp moves in
+//         front, neg vanishes and everything is unsigned:  q = (mulhi(2 * max(s, 0), 2M) + k) >> (r + 1).
+//   else: offset binary as above: mulhi(2 * (s + 2^30), 2M) = t + M exactly, so the addend k - M gives t + k.
+// Valid for |s| < 2^29 and r <= 29 (no 32-bit overflow); the host sets fastq only when every channel of the
+// layer and the largest possible |acc| satisfy that, else requant_one runs.
+template <int ACT>
+__device__ __forceinline__ int requant_fast(int32_t acc, const ChanConst &q, const ConvGemmParams &p) {
+  uint32_t tk, s2 = 2u * (uint32_t)acc + q.sbias;
+  if (ACT == 1) s2 = (uint32_t)max((int32_t)s2, 0);
+  asm("mad.hi.u32 %0, %1, %2, %3;" : "=r"(tk) : "r"(s2), "r"(q.M2), "r"(q.kc));
+  if (ACT == 1) {
+    uint32_t v;
+    asm("shr.u32 %0, %1, %2;" : "=r"(v) : "r"(tk), "r"((uint32_t)q.r)); // r + 1 <= 32; a shift by 32 gives 0
+    return (int)v;
+  }
+  uint32_t adj;
+  asm("shr.u32 %0, %1, %2;" : "=r"(adj) : "r"(tk - (uint32_t)q.rnd), "r"((uint32_t)q.s1)); // [t + 1 < 0 and r > 0]
+  int v;
+  asm("shr.s32 %0, %1, %2;" : "=r"(v) : "r"((int32_t)tk - 2 * (int32_t)adj), "r"((uint32_t)q.r));
+  if (ACT == 2) v = min(max(v, -128), 127);
   return v;
 }
 // INT8 leaky ReLU of a saturated convolution result (core/activation.cpp:126-153).
@@ -340,11 +377,14 @@ __device__ __forceinline__ uint32_t transpose4x4(uint32_t w, const TransposeSel 
 //   out4       output address of (pixel m0, this lane's 4-channel group)
 //   ch4_ok     the 4-channel group lies inside the valid channels
 //   ncols      pixel columns of the accumulator buffer (128; 256 for the two-SM tile)
-template <int ACT>
-__device__ __forceinline__ void epilogue_channels(const ConvGemmParams &p, uint32_t lane_addr, int8_t *out4,
-                                                  bool ch4_ok, int m0, int half, int halves, int lane,
-                                                  const ChanConst &cc, const TransposeSel &ts, int ncols = 128) {
+template <int ACT, bool FAST>
+__device__ __forceinline__ void epilogue_channels_impl(const ConvGemmParams &p, uint32_t lane_addr, int8_t *out4,
+                                                       bool ch4_ok, int m0, int half, int halves, int lane,
+                                                       const ChanConst &cc, const TransposeSel &ts, int ncols) {
+  auto rq = [&](uint32_t a) { return FAST ? requant_fast<ACT>((int32_t)a, cc, p) : requant_one<ACT>((int32_t)a, cc, p); };
   const int pj = lane & 3;
+  // (Software-pipelining these loads in 16-column pieces made the epilogue alone 14% faster and the whole
+  // kernel 4% slower, so the two loads of a chunk are simply issued together.)
   for (int colg = half * 32; colg < ncols; colg += 32 * halves) {
     if (m0 + colg >= p.M_total) break;
     uint32_t acc0[16], acc1[16];
@@ -354,10 +394,8 @@ __device__ __forceinline__ void epilogue_channels(const ConvGemmParams &p, uint3
     uint32_t w[8];
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
-      w[k] = pack4_sat(requant_one<ACT>((int32_t)acc0[4 * k + 0], cc, p), requant_one<ACT>((int32_t)acc0[4 * k + 1], cc, p),
-                       requant_one<ACT>((int32_t)acc0[4 * k + 2], cc, p), requant_one<ACT>((int32_t)acc0[4 * k + 3], cc, p));
-      w[4 + k] = pack4_sat(requant_one<ACT>((int32_t)acc1[4 * k + 0], cc, p), requant_one<ACT>((int32_t)acc1[4 * k + 1], cc, p),
-                           requant_one<ACT>((int32_t)acc1[4 * k + 2], cc, p), requant_one<ACT>((int32_t)acc1[4 * k + 3], cc, p));
+      w[k] = pack4_sat(rq(acc0[4 * k + 0]), rq(acc0[4 * k + 1]), rq(acc0[4 * k + 2]), rq(acc0[4 * k + 3]));
+      w[4 + k] = pack4_sat(rq(acc1[4 * k + 0]), rq(acc1[4 * k + 1]), rq(acc1[4 * k + 2]), rq(acc1[4 * k + 3]));
     }
 #pragma unroll
     for (int k = 0; k < 8; ++k) w[k] = transpose4x4(w[k], ts);
@@ -389,6 +427,14 @@ __device__ __forceinline__ void epilogue_channels(const ConvGemmParams &p, uint3
         if (ch4_ok && m0 + colg + 4 * k + pj < p.M_total) *reinterpret_cast<uint32_t *>(o + (size_t)(4 * k) * p.ldc) = w[k];
     }
   }
+}
+
+template <int ACT>
+__device__ __forceinline__ void epilogue_channels(const ConvGemmParams &p, uint32_t lane_addr, int8_t *out4,
+                                                  bool ch4_ok, int m0, int half, int halves, int lane,
+                                                  const ChanConst &cc, const TransposeSel &ts, int ncols = 128) {
+  if (p.fastq & 1) epilogue_channels_impl<ACT, true>(p, lane_addr, out4, ch4_ok, m0, half, halves, lane, cc, ts, ncols);
+  else epilogue_channels_impl<ACT, false>(p, lane_addr, out4, ch4_ok, m0, half, halves, lane, cc, ts, ncols);
 }
 
 // Epilogue of a BF16 convolution (core/conv.cpp:90-98: fp32 result + fp32 bias, ReLU, BF16 rounding). The
@@ -430,7 +476,10 @@ __device__ __forceinline__ void epilogue_channels_bf16(const ConvGemmParams &p, 
 // vary fastest so that CTAs working at the same time share activation tiles through L2). The
 // producer runs ahead through the shared-memory ring across tile boundaries and the accumulator is
 // double-buffered in TMEM, so the loads and MMAs of tile i+1 overlap the epilogue of tile i.
-template <bool BF16>
+// Loop-profile counters of the PROF instantiation (a measuring aid, never launched by the op kernels unless the
+// environment asks for it): clocks summed over CTAs by role, see conv_gemm_prof_kernel.
+__device__ unsigned long long g_conv_prof[16];
+template <bool BF16, bool PROF = false, bool FAST = true>
 __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUtensorMap &tmB, const ConvGemmParams &p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = ptx::smem_u32(smem_raw);
@@ -498,6 +547,7 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
   if (warp == 0) {
     // ---------------------------------------------------------------- producer
     if (lane == 0) {
+      long long pf_p0 = PROF ? clock64() : 0ll, pf_pwait = 0;
       int it = 0; // k-iterations issued so far, across tiles
       int ps = 0;        // ring stage of iteration `it`
       uint32_t pph = 0;  // its phase bit
@@ -538,6 +588,7 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
         // is a single thread's instruction stream, so it carries no divisions
         int tap = 0, tr = 0, ts = 0, chunk = 0;
         for (int kit = 0; kit < k_iters; ++kit, ++it) {
+          const long long pf_e0 = PROF ? clock64() : 0ll;
           if (it >= p.stages) {
             if (!ptx::mbar_wait_bounded(bar_empty + 8 * ps, pph ^ 1u, abort_flag)) {
               if (!*abort_flag) atomicExch(p.err, kErrEmptyWait);
@@ -546,6 +597,7 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
               break;
             }
           }
+          if (PROF) pf_pwait += clock64() - pf_e0;
           const int c0 = chunk * p.BK;
           const uint32_t a_dst = tiles + (uint32_t)ps * stage_bytes;
           const uint32_t b_dst = a_dst + a_bytes;
@@ -578,6 +630,10 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
             pph ^= 1u;
           }
         }
+      }
+      if (PROF) {
+        atomicAdd(&g_conv_prof[5], (unsigned long long)(clock64() - pf_p0));
+        atomicAdd(&g_conv_prof[6], (unsigned long long)pf_pwait);
       }
       if (!ok || *abort_flag) {
         if (p.w_resident && (int)blockIdx.x < total_tiles)
@@ -621,8 +677,12 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
           ok = false;
         }
       }
+      long long pf_t0 = PROF ? clock64() : 0ll, pf_wait = 0, pf_accwait = 0, pf_blocks = 0;
+      unsigned long long pf_g0 = 0;
+      if (PROF) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(pf_g0));
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++t) {
         const int buf = t & 1;
+        const long long pf_a0 = PROF ? clock64() : 0ll;
         if (t >= 2) {
           // the epilogue must have drained this accumulator buffer (its previous use)
           if (!ptx::mbar_wait_bounded(bar_acc_empty + 8 * buf, (uint32_t)(((t >> 1) - 1) & 1), abort_flag)) {
@@ -635,12 +695,18 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
         }
         const uint32_t d_tmem = tmem_base + (uint32_t)buf * acc_stride;
         uint32_t wres_lo = desc_w_lo; // weight-resident mode: descriptor (low word) of K block `kit`
+        if (PROF) pf_accwait += clock64() - pf_a0;
         for (int kit = 0; kit < k_iters; ++kit, ++it) {
+          const long long pf_w0 = PROF ? clock64() : 0ll;
           if (!ptx::mbar_try_wait(m_full, mph) && !ptx::mbar_wait_bounded(m_full, mph, abort_flag)) {
             if (!*abort_flag) atomicExch(p.err, kErrFullWait);
             *abort_flag = 1;
             ok = false;
             break;
+          }
+          if (PROF) {
+            pf_wait += clock64() - pf_w0;
+            ++pf_blocks;
           }
           ptx::tcgen05_fence_after();
           // transposed product: weights are the A operand (M = channels), activations B (N = pixels)
@@ -676,13 +742,28 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
         }
         if (ok) ptx::tcgen05_commit(bar_acc_full + 8 * buf);
       }
+      if (PROF) {
+        atomicAdd(&g_conv_prof[0], (unsigned long long)(clock64() - pf_t0));
+        atomicAdd(&g_conv_prof[1], (unsigned long long)pf_wait);
+        atomicAdd(&g_conv_prof[2], (unsigned long long)pf_accwait);
+        atomicAdd(&g_conv_prof[3], (unsigned long long)pf_blocks);
+        atomicAdd(&g_conv_prof[4], 1ull);
+        unsigned long long pf_g1;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(pf_g1));
+        atomicAdd(&g_conv_prof[9], pf_g1 - pf_g0);
+        atomicMax(&g_conv_prof[10], pf_g1 - pf_g0);
+        atomicMax(&g_conv_prof[11], (unsigned long long)(clock64() - pf_t0));
+        if (g_conv_prof[12] == 0) atomicCAS(&g_conv_prof[12], 0ull, pf_g0);
+        atomicMin(&g_conv_prof[12], pf_g0);
+        atomicMax(&g_conv_prof[13], pf_g1);
+      }
     }
   } else {
     // ---------------------------------------------------------------- epilogue
     const int quarter = warp & 3;     // TMEM lanes (= channels of the tile) this warp may read
     const int half = (warp - 2) >> 2; // which alternate 32-pixel column groups it takes
     const TransposeSel ts = make_transpose_sel(lane);
-    ChanConst cc;
+    ChanConst cc = {};
     float bias_f = 0.0f;
     int staged_n0 = -1;
     int t = 0;
@@ -702,7 +783,10 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
         }
         staged_n0 = n0;
       }
+      const long long pf_q0 = PROF ? clock64() : 0ll;
       ok = ptx::mbar_wait_bounded(bar_acc_full + 8 * buf, (uint32_t)((t >> 1) & 1), abort_flag);
+      if (PROF && warp == 2 && lane == 0) atomicAdd(&g_conv_prof[7], (unsigned long long)(clock64() - pf_q0));
+      const long long pf_q1 = PROF ? clock64() : 0ll;
       if (!ok && !*abort_flag) {
         atomicExch(p.err, kErrAccWait);
         *abort_flag = 1;
@@ -722,10 +806,11 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
           uint8_t *out_pair = reinterpret_cast<uint8_t *>(p.out) + (size_t)m0 * p.ldc + (size_t)(p.c_off + (ch & ~1)) * 2;
           if (p.act == 1) epilogue_channels_bf16<true>(p, lane_addr, out_pair, ch < p.n_valid, m0, half, kEpilogueWarps / 4, lane, bias_f);
           else epilogue_channels_bf16<false>(p, lane_addr, out_pair, ch < p.n_valid, m0, half, kEpilogueWarps / 4, lane, bias_f);
-        } else if (p.act == 1) epilogue_channels<1>(p, lane_addr, out4, ch4_ok, m0, half, kEpilogueWarps / 4, lane, cc, ts);
-        else if (p.act == 2) epilogue_channels<2>(p, lane_addr, out4, ch4_ok, m0, half, kEpilogueWarps / 4, lane, cc, ts);
-        else epilogue_channels<0>(p, lane_addr, out4, ch4_ok, m0, half, kEpilogueWarps / 4, lane, cc, ts);
+        } else if (p.act == 1) epilogue_channels_impl<1, FAST>(p, lane_addr, out4, ch4_ok, m0, half, kEpilogueWarps / 4, lane, cc, ts, 128);
+        else if (p.act == 2) epilogue_channels_impl<2, FAST>(p, lane_addr, out4, ch4_ok, m0, half, kEpilogueWarps / 4, lane, cc, ts, 128);
+        else epilogue_channels_impl<0, FAST>(p, lane_addr, out4, ch4_ok, m0, half, kEpilogueWarps / 4, lane, cc, ts, 128);
       }
+      if (PROF && warp == 2 && lane == 0) atomicAdd(&g_conv_prof[8], (unsigned long long)(clock64() - pf_q1));
       // hand the accumulator buffer back to the MMA issuer
       ptx::tcgen05_fence_before();
       __syncwarp();
@@ -742,10 +827,25 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
   }
 }
 
+// p.fastq bit 0 must be set: the epilogue uses the multiply-high requantisation (requant_fast)
 __global__ void __launch_bounds__(kConvThreads, 2)
 conv_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const ConvGemmParams p) {
-  conv_gemm_body<false>(tmA, tmB, p);
+  conv_gemm_body<false, false, true>(tmA, tmB, p);
+}
+// the same with the 64-bit multiply-add requantisation (requant_one), for layers outside requant_fast's domain
+__global__ void __launch_bounds__(kConvThreads, 2)
+conv_gemm_i8_wide_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                         const ConvGemmParams p) {
+  conv_gemm_body<false, false, false>(tmA, tmB, p);
+}
+// The INT8 kernel with the loop-profile counters on (g_conv_prof): [0] MMA thread total clocks, [1] of which waiting
+// for a full stage, [2] waiting for a drained accumulator, [3] K blocks, [4] CTAs, [5] producer total, [6] of which
+// waiting for an empty stage, [7] epilogue (one warp) waiting for an accumulator, [8] epilogue working.
+__global__ void __launch_bounds__(kConvThreads, 2)
+conv_gemm_prof_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                      const ConvGemmParams p) {
+  conv_gemm_body<false, true, true>(tmA, tmB, p);
 }
 // The same pipeline for BF16 graphs: BF16 operands (tcgen05 kind::f16), fp32 accumulators, BF16 results.
 // All sizes in ConvGemmParams that count K or row pitches are in BYTES, so only the MMA kind and the
@@ -753,7 +853,7 @@ conv_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 __global__ void __launch_bounds__(kConvThreads, 2)
 conv_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                       const ConvGemmParams p) {
-  conv_gemm_body<true>(tmA, tmB, p);
+  conv_gemm_body<true, false, false>(tmA, tmB, p);
 }
 
 } // namespace tpucb

@@ -253,7 +253,8 @@ struct StemPlan {
 
 inline void stem_kernel_setup_once() {
   static bool done = [] {
-    TPUCB_CUDA(cudaFuncSetAttribute(conv_stem_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+    TPUCB_CUDA(cudaFuncSetAttribute(conv_stem_i8_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+    TPUCB_CUDA(cudaFuncSetAttribute(conv_stem_i8_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
     return true;
   }();
   (void)done;
@@ -391,15 +392,30 @@ inline void finish_plan(ConvPlan &pl, int rows, int taps, int k_inner, int oc_pa
   pl.grid = dim3((unsigned)grid, 1, 1);
 }
 
+inline bool conv_prof_enabled() {
+  static const bool on = [] { const char *e = getenv("TPUCB_CONV_PROF"); return e && atoi(e) != 0; }();
+  return on;
+}
+// Reads and clears the loop-profile counters (see conv_gemm_prof_kernel).
+inline void conv_prof_read(unsigned long long *out16) {
+  TPUCB_CUDA(cudaDeviceSynchronize());
+  TPUCB_CUDA(cudaMemcpyFromSymbol(out16, g_conv_prof, 16 * sizeof(unsigned long long)));
+  unsigned long long z[16] = {0};
+  TPUCB_CUDA(cudaMemcpyToSymbol(g_conv_prof, z, sizeof(z)));
+}
 inline void launch_conv_plan(const ConvPlan &pl, cudaStream_t stream, int sm_count) {
   if (pl.use_patch) {
     size_t total = (size_t)pl.p.M_total * pl.patch.kp;
     patch_expand_i8_kernel<<<grid_for(total, 256, sm_count), 256, 0, stream>>>(pl.in, pl.patch_buf,
                                                                               pl.patch);
   }
-  if (pl.bf16) conv_gemm_bf16_kernel<<<pl.grid, kConvThreads, pl.smem, stream>>>(pl.tmA, pl.tmB, pl.p);
+  const int threads = kConvThreads;
+  if (pl.bf16) conv_gemm_bf16_kernel<<<pl.grid, threads, pl.smem, stream>>>(pl.tmA, pl.tmB, pl.p);
+  else if (pl.pair && conv_prof_enabled()) conv_gemm2_prof_kernel<<<pl.grid, kPairThreads, pl.smem, stream>>>(pl.tmA, pl.tmB, pl.p);
   else if (pl.pair) conv_gemm2_i8_kernel<<<pl.grid, kPairThreads, pl.smem, stream>>>(pl.tmA, pl.tmB, pl.p);
-  else conv_gemm_i8_kernel<<<pl.grid, kConvThreads, pl.smem, stream>>>(pl.tmA, pl.tmB, pl.p);
+  else if (!(pl.p.fastq & 1)) conv_gemm_i8_wide_kernel<<<pl.grid, threads, pl.smem, stream>>>(pl.tmA, pl.tmB, pl.p);
+  else if (conv_prof_enabled()) conv_gemm_prof_kernel<<<pl.grid, threads, pl.smem, stream>>>(pl.tmA, pl.tmB, pl.p);
+  else conv_gemm_i8_kernel<<<pl.grid, threads, pl.smem, stream>>>(pl.tmA, pl.tmB, pl.p);
 }
 
 inline void conv_kernel_setup_once() {
@@ -409,6 +425,12 @@ inline void conv_kernel_setup_once() {
     TPUCB_CUDA(cudaFuncSetAttribute(conv_gemm2_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     227 * 1024));
     TPUCB_CUDA(cudaFuncSetAttribute(conv_gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    227 * 1024));
+    TPUCB_CUDA(cudaFuncSetAttribute(conv_gemm_prof_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    227 * 1024));
+    TPUCB_CUDA(cudaFuncSetAttribute(conv_gemm_i8_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    227 * 1024));
+    TPUCB_CUDA(cudaFuncSetAttribute(conv_gemm2_prof_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     227 * 1024));
     return true;
   }();

@@ -20,7 +20,7 @@ struct ConvStemParams {
   int M_total, OH, OW, H, W;
   int sh, sw, pt, pl, dh;
   int kh, kw;
-  int BN, n_valid, ldc, c_off, act, tmem_cols, dual;
+  int BN, n_valid, ldc, c_off, act, tmem_cols, dual, fastq;
   int leaky_mp, leaky_rp, leaky_mn, leaky_rn;
   uint32_t idesc;
   const uint32_t *in; // NHWC4 int8, one 32-bit word per pixel
@@ -34,6 +34,8 @@ constexpr int kStemThreads = 32 + 256; // warp 0: weights + MMA; warps 1..8: gat
 // Dual mode (p.dual, at most 64 output channels): the tile covers 256 pixels; the weight rows are
 // fetched as [64 zero rows][64 weight rows][64 zero rows] per filter row, and the two 128-pixel halves
 // fill TMEM lanes 0..63 and 64..127 (same construction as in conv_gemm_i8_kernel).
+// FAST: the multiply-high requantisation (p.fastq bit 0 set), else the 64-bit multiply-add form
+template <bool FAST>
 __global__ void __launch_bounds__(kStemThreads, 2)
 conv_stem_i8_kernel(const __grid_constant__ CUtensorMap tmB, const ConvStemParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -65,7 +67,7 @@ conv_stem_i8_kernel(const __grid_constant__ CUtensorMap tmB, const ConvStemParam
   ep.BN = p.BN; ep.n_valid = p.n_valid; ep.act = p.act; ep.M_total = p.M_total; ep.ldc = p.ldc;
   ep.mult = p.mult; ep.bias = p.bias; ep.rshift = p.rshift;
   ep.leaky_mp = p.leaky_mp; ep.leaky_rp = p.leaky_rp; ep.leaky_mn = p.leaky_mn; ep.leaky_rn = p.leaky_rn;
-  ep.out = p.out; ep.out2 = nullptr;
+  ep.out = p.out; ep.out2 = nullptr; ep.fastq = p.fastq;
 
   if (threadIdx.x == 0) *abort_flag = *reinterpret_cast<volatile int *>(p.err);
   __syncthreads();
@@ -186,9 +188,9 @@ conv_stem_i8_kernel(const __grid_constant__ CUtensorMap tmB, const ConvStemParam
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
         int8_t *out4 = p.out + (size_t)m0e * p.ldc + p.c_off + ch4;
         const bool ch4_ok = ch4 < p.n_valid;
-        if (p.act == 1) epilogue_channels<1>(ep, lane_addr, out4, ch4_ok, m0e, half, 2, lane, cc, ts);
-        else if (p.act == 2) epilogue_channels<2>(ep, lane_addr, out4, ch4_ok, m0e, half, 2, lane, cc, ts);
-        else epilogue_channels<0>(ep, lane_addr, out4, ch4_ok, m0e, half, 2, lane, cc, ts);
+        if (p.act == 1) epilogue_channels_impl<1, FAST>(ep, lane_addr, out4, ch4_ok, m0e, half, 2, lane, cc, ts, 128);
+        else if (p.act == 2) epilogue_channels_impl<2, FAST>(ep, lane_addr, out4, ch4_ok, m0e, half, 2, lane, cc, ts, 128);
+        else epilogue_channels_impl<0, FAST>(ep, lane_addr, out4, ch4_ok, m0e, half, 2, lane, cc, ts, 128);
       }
     }
   }

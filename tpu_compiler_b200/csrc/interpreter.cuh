@@ -238,6 +238,25 @@ inline void check_q31_multipliers(const std::vector<float> &m, const std::string
     TPUCB_CHECK(v >= 0.0f && v < 2147483648.0f, "%s: multiplier %g is outside [0, 2^31)", op_name.c_str(), (double)v);
 }
 
+// The multiply-high form of the tensor-core requantisation (requant_fast) needs |acc + bias| < 2^29 and
+// rshift <= 29: true when every shift is that small and K * 127 * 128 + max |bias| stays below 2^29.
+inline bool requant_fast_applies(const std::vector<float> &rshift, const std::vector<float> &bias, long long k_total) {
+  double bmax = 0;
+  for (float b : bias) bmax = std::max(bmax, std::fabs((double)b));
+  for (float r : rshift)
+    if (!(r >= 0.0f && r <= 29.0f)) return false;
+  return (double)k_total * 127.0 * 128.0 + bmax < 536870912.0;
+}
+// ConvGemmParams::fastq: bit 0 the multiply-high form applies, bit 1 every rshift is >= 1
+inline int requant_fast_flags(const std::vector<float> &rshift, const std::vector<float> &bias, long long k_total) {
+  static const int env = [] { const char *e = getenv("TPUCB_FASTQ"); return e ? atoi(e) : 1; }();
+  if (!env || !requant_fast_applies(rshift, bias, k_total)) return 0;
+  int f = 1 | 2;
+  for (float r : rshift)
+    if (r < 1.0f) f = 1;
+  return f;
+}
+
 // ---------------------------------------------------------------------------- Input
 // InputOpKernel (core/input.cpp:7-24): holds the tensor set_tensor writes; no device work.
 class InputOp : public OpKernel {
@@ -395,6 +414,7 @@ public:
     d_rsh_ = I.upload(to_i32(I.weight(op.in[5]).data, oc_pad, true));
     alg_bytes = (double)in->numel() + out->numel() + filt.data.size() + 12.0 * g.oc;
     act_ = do_relu_ ? 1 : 0;
+    const int fastq = requant_fast_flags(I.weight(op.in[5]).data, bias, (long long)(g.ic / g.g) * g.kh * g.kw);
 
     if (g.g == g.ic && g.g == g.oc && g.g > 1 && g.ins_h == 0 && g.ins_w == 0) {
       // depthwise
@@ -420,6 +440,7 @@ public:
       p.OH = g.oh; p.OW = g.ow; p.H = g.ih; p.W = g.iw;
       p.sh = g.sh; p.sw = g.sw; p.pt = g.pt; p.pl = g.pl; p.dh = g.dh; p.kw = g.kw;
       p.act = act_;
+      p.fastq = fastq;
       p.in = (const uint32_t *)in->dev;
       p.bias = d_bias_; p.mult = d_mult_; p.rshift = d_rsh_;
       p.out = (int8_t *)out->dev;
@@ -459,6 +480,7 @@ public:
       ConvGemmParams &p = pl.p;
       p.OH = g.oh; p.OW = g.ow; p.sh = g.sh; p.sw = g.sw; p.pt = g.pt; p.pl = g.pl; p.dh = g.dh; p.dw = g.dw;
       p.act = act_;
+      p.fastq = fastq;
       p.bias = d_bias_ + grp * ocg; p.mult = d_mult_ + grp * ocg; p.rshift = d_rsh_ + grp * ocg;
       p.out = (int8_t *)out->dev;
       p.ldc = out->cp;
@@ -568,7 +590,8 @@ public:
                                                                           (int8_t *)out_->dev, dwargs_);
     } else {
       for (auto &sp : stem_plans_)
-        conv_stem_i8_kernel<<<sp.grid, kStemThreads, sp.smem, s>>>(sp.tmB, sp.p);
+        if (sp.p.fastq & 1) conv_stem_i8_kernel<true><<<sp.grid, kStemThreads, sp.smem, s>>>(sp.tmB, sp.p);
+        else conv_stem_i8_kernel<false><<<sp.grid, kStemThreads, sp.smem, s>>>(sp.tmB, sp.p);
       for (auto &pl : plans_) launch_conv_plan(pl, s, I_.sm_count);
     }
   }
@@ -691,6 +714,7 @@ public:
     // The reference applies ReLU to the float before the QDM requant; with a positive
     // multiplier the two orders give the same int8 result.
     p.act = do_relu_ ? 1 : 0;
+    p.fastq = requant_fast_flags(rs, bias, k_);
     p.a_mode = 0;
     finish_plan(pl, m_, 1, kdev_, n_pad, I.sm_count);
     encode_matrix_map(&pl.tmA, (const int8_t *)in->dev, m_, kdev_, kdev_, p.BK);

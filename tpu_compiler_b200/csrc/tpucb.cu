@@ -277,6 +277,13 @@ int tpucb_host_free(void *ptr) {
   TPUCB_API_END
 }
 
+int tpucb_debug_conv_loop_profile(unsigned long long *counters16) {
+  TPUCB_API_BEGIN
+  TPUCB_CHECK(counters16 != nullptr, "tpucb_debug_conv_loop_profile: null output");
+  conv_prof_read(counters16);
+  TPUCB_API_END
+}
+
 int tpucb_measure_i8_mma_peak(int device, int n_cols, double *tops) {
   TPUCB_API_BEGIN
   TPUCB_CHECK(tops && (n_cols == 64 || n_cols == 128 || n_cols == 256), "tpucb_measure_i8_mma_peak: n_cols must be 64, 128 or 256");

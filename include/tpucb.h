@@ -82,7 +82,11 @@ int tpucb_interp_get_op_info(tpucb_interp *it, char *out, size_t cap, size_t *ne
 /* Options: "cuda_graph" (0/1, default 1): replay the op list as one CUDA graph.
  *          "fuse_activations" (0/1, default 1; read by the next load_module): run each
  *          quant(INT8->BF16) -> slope-table activation -> quant(BF16->INT8) chain as one launch
- *          that still writes all three tensors. */
+ *          that still writes all three tensors.
+ *          "fp32_tensor_cores" (0/1, default 1; read by the next load_module): fp32 convolutions with a
+ *          multiple of 8 input channels run on the tensor cores as three TF32 products with fp32 accumulation
+ *          (about 5e-6 of a tensor's range per layer against a double-accumulated sum, 6e-5 at the end of an
+ *          fp32 ResNet-50); 0 keeps every fp32 convolution on the FMA pipe (2e-6 end to end, 2.5 x slower). */
 int tpucb_interp_set_option(tpucb_interp *it, const char *key, int value);
 /* Per-op device time of one eager pass (CUDA events on the interpreter's stream);
  * ms[i] belongs to the i-th line of tpucb_interp_get_op_info. Returns the op count. */

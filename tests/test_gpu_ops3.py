@@ -243,3 +243,22 @@ def test_conv_i8_requant_forms(relu, rshift_range):
     model = graphs.single_conv_i8(n=2, c_in=64, c_out=160, hw=12, k=3, pad=1, relu=relu, seed=4100 + rshift_range[0],
                                   rshift_range=rshift_range)
     assert_exact(run_both(model.text, model.weights, model.meta, ["conv"]))
+
+
+@pytest.mark.parametrize("cfg", [dict(ic=64, oc=64, hw=14, k=1, s=1, p=0, relu=1), dict(ic=32, oc=160, hw=13, k=3, s=1, p=1, relu=1),
+                                 dict(ic=128, oc=40, hw=12, k=3, s=2, p=1, relu=0), dict(ic=8, oc=256, hw=9, k=1, s=1, p=0, relu=0)])
+def test_conv_fp32_tensor_core(cfg):
+    """fp32 convolution as three TF32 products on the tensor cores against the double-accumulated oracle. The bound
+    (2e-5 of the tensor's range; measured 1e-6 to 5e-6, the tensor core truncates its partial sums) is far below what
+    one TF32 product would reach (5e-4), so a missing correction term fails."""
+    rng = np.random.default_rng(41)
+    ic, oc, hw, k, s, p = (cfg[x] for x in ("ic", "oc", "hw", "k", "s", "p"))
+    oh = (hw + 2 * p - k) // s + 1
+    b = graphs.GraphBuilder(41, simulate=False)
+    b.op("input", "x", [], (3, ic, hw, hw), "FP32")
+    b.weight("w", rng.normal(0, (2.0 / (ic * k * k)) ** 0.5, (oc, ic, k, k)).astype(np.float32))
+    b.weight("bias", rng.normal(0, 0.1, oc).astype(np.float32))
+    b.op("conv_2d", "y", ["x", "w", "bias"], (3, oc, oh, oh), "FP32", kh=k, kw=k, sh=s, sw=s, pt=p, pb=p, pl=p, pr=p,
+         dh=1, dw=1, g=1, do_relu=cfg["relu"], with_bias=1)
+    x = rng.normal(0, 1, (3, ic, hw, hw)).astype(np.float32)
+    assert_close(run_both(b.text(), b.weights, {"x": x}, ["y"]), rtol=2e-5)

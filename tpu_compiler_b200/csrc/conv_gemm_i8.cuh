@@ -203,15 +203,41 @@ __device__ __forceinline__ void tcgen05_mma_f16_lohi(uint32_t d_tmem, uint32_t a
         : "memory");
   }
 }
-// KSTEPS MMAs of one K block (32 bytes of K each: +2 in the descriptors' 16-byte address units)
-template <int KSTEPS, bool BF16 = false>
+// kind::tf32 with fp32 words as operands (their low 13 mantissa bits do not take part) and fp32 accumulation:
+// 8 elements = 32 bytes of K per MMA
+template <bool ACCUMULATE>
+__device__ __forceinline__ void tcgen05_mma_tf32_lohi(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                                      uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
+  if (ACCUMULATE) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+        "setp.eq.b32 p, 0, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], da, db, %5, p;\n\t}" ::"r"(d_tmem),
+        "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], da, db, %5, p;\n\t}" ::"r"(d_tmem),
+        "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
+}
+// KSTEPS MMAs of one K block (32 bytes of K each: +2 in the descriptors' 16-byte address units).
+// KIND: 0 kind::i8, 1 kind::f16 on BF16 operands, 2 kind::tf32
+template <int KSTEPS, int KIND = 0>
 __device__ __forceinline__ void tcgen05_mma_i8_kblock(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t hi,
                                                       uint32_t idesc, uint32_t accumulate_first) {
-  if (BF16) tcgen05_mma_f16_lohi<false>(d_tmem, a_lo, hi, b_lo, hi, idesc, accumulate_first);
+  if (KIND == 2) tcgen05_mma_tf32_lohi<false>(d_tmem, a_lo, hi, b_lo, hi, idesc, accumulate_first);
+  else if (KIND == 1) tcgen05_mma_f16_lohi<false>(d_tmem, a_lo, hi, b_lo, hi, idesc, accumulate_first);
   else tcgen05_mma_i8_lohi<false>(d_tmem, a_lo, hi, b_lo, hi, idesc, accumulate_first);
 #pragma unroll
   for (int k = 1; k < KSTEPS; ++k) {
-    if (BF16) tcgen05_mma_f16_lohi<true>(d_tmem, a_lo + 2 * k, hi, b_lo + 2 * k, hi, idesc, 1u);
+    if (KIND == 2) tcgen05_mma_tf32_lohi<true>(d_tmem, a_lo + 2 * k, hi, b_lo + 2 * k, hi, idesc, 1u);
+    else if (KIND == 1) tcgen05_mma_f16_lohi<true>(d_tmem, a_lo + 2 * k, hi, b_lo + 2 * k, hi, idesc, 1u);
     else tcgen05_mma_i8_lohi<true>(d_tmem, a_lo + 2 * k, hi, b_lo + 2 * k, hi, idesc, 1u);
   }
 }
@@ -472,6 +498,28 @@ __device__ __forceinline__ void epilogue_channels_bf16(const ConvGemmParams &p, 
   }
 }
 
+// Epilogue of an fp32 convolution computed as three TF32 products (calibration forward; core/conv.cpp:80-89): fp32
+// accumulator + fp32 bias, ReLU, stored as fp32. A lane owns a channel: for every pixel the warp writes 32 consecutive
+// channels (128 contiguous bytes). `out_ch` addresses (pixel m0, this lane's channel); `pitch` is the row pitch in bytes.
+template <bool RELU>
+__device__ __forceinline__ void epilogue_channels_f32(const ConvGemmParams &p, uint32_t lane_addr, uint8_t *out_ch, bool ch_ok,
+                                                      int m0, int half, int halves, float bias, int ncols = 128) {
+  const size_t pitch = (size_t)p.ldc;
+  for (int colg = half * 32; colg < ncols; colg += 32 * halves) {
+    if (m0 + colg >= p.M_total) break;
+    uint32_t acc0[16], acc1[16];
+    ptx::tcgen05_ld_x16(lane_addr + (uint32_t)colg, acc0);
+    ptx::tcgen05_ld_x16(lane_addr + (uint32_t)colg + 16u, acc1);
+    ptx::tcgen05_wait_ld();
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      float v = __fadd_rn(bits_f32(j < 16 ? acc0[j & 15] : acc1[j & 15]), bias);
+      if (RELU) v = v > 0.0f ? v : 0.0f;
+      if (ch_ok && m0 + colg + j < p.M_total) *reinterpret_cast<float *>(out_ch + (size_t)(colg + j) * pitch) = v;
+    }
+  }
+}
+
 // Persistent kernel: gridDim.x CTAs walk the tile list (tile = blockIdx.x + k * gridDim.x; n-tiles
 // vary fastest so that CTAs working at the same time share activation tiles through L2). The
 // producer runs ahead through the shared-memory ring across tile boundaries and the accumulator is
@@ -479,8 +527,18 @@ __device__ __forceinline__ void epilogue_channels_bf16(const ConvGemmParams &p, 
 // Loop-profile counters of the PROF instantiation (a measuring aid, never launched by the op kernels unless the
 // environment asks for it): clocks summed over CTAs by role, see conv_gemm_prof_kernel.
 __device__ unsigned long long g_conv_prof[16];
-template <bool BF16, bool PROF = false, bool FAST = true>
-__device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUtensorMap &tmB, const ConvGemmParams &p) {
+// TF32: an fp32 convolution as three kind::tf32 products accumulated in one pass over K: with x = xh + xl and
+// w = wh + wl (h: the upper 19 bits of the fp32 word, l: the exact remainder), x w = xh wh + xl wh + xh wl up to
+// 2^-22 relative. The K loop runs three times over the taps: term 0 reads (tmA2, tmB) = (xl, wh), term 1
+// (tmA, tmB2) = (xh, wl), term 2 (tmA, tmB) = (xh, wh); the accumulator never leaves TMEM in between. The two small
+// terms come first: the tensor core truncates every partial sum at the accumulator's own precision, so each MMA
+// step costs up to an ulp of what has been accumulated so far, and only the steps of the last term see the
+// full magnitude (measured: the error against a double-accumulated convolution drops by the expected factor 3).
+template <bool BF16, bool PROF = false, bool FAST = true, bool TF32 = false>
+__device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUtensorMap &tmB, const ConvGemmParams &p,
+                                               const CUtensorMap &tmA2, const CUtensorMap &tmB2) {
+  constexpr int KIND = TF32 ? 2 : (BF16 ? 1 : 0);
+  constexpr int kTerms = TF32 ? 3 : 1;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = ptx::smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -586,8 +644,10 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
         }
         // running (tap row, tap column, channel chunk) and ring (stage, phase) counters: this loop
         // is a single thread's instruction stream, so it carries no divisions
-        int tap = 0, tr = 0, ts = 0, chunk = 0;
-        for (int kit = 0; kit < k_iters; ++kit, ++it) {
+        int tap = 0, tr = 0, ts = 0, chunk = 0, term = 0;
+        for (int kit = 0; kit < kTerms * k_iters; ++kit, ++it) {
+          const CUtensorMap *mapA = (TF32 && term == 0) ? &tmA2 : &tmA;
+          const CUtensorMap *mapB = (TF32 && term == 1) ? &tmB2 : &tmB;
           const long long pf_e0 = PROF ? clock64() : 0ll;
           if (it >= p.stages) {
             if (!ptx::mbar_wait_bounded(bar_empty + 8 * ps, pph ^ 1u, abort_flag)) {
@@ -605,7 +665,7 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
           ptx::mbar_expect_tx(fb, stage_bytes);
           if (p.a_mode == 1) {
             for (int sub = 0; sub < subs; ++sub)
-              ptx::tma_load_im2col_4d(a_dst + (uint32_t)sub * 128u * (uint32_t)p.BK, &tmA, fb, c0, w_base[sub],
+              ptx::tma_load_im2col_4d(a_dst + (uint32_t)sub * 128u * (uint32_t)p.BK, mapA, fb, c0, w_base[sub],
                                       h_base[sub], n_img[sub], (uint16_t)(ts * p.dw), (uint16_t)(tr * p.dh));
           } else if (p.a_mode == 2) {
             // `tap` is the filter row; each copy brings win_g consecutive output pixels' windows.
@@ -614,15 +674,21 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
                                bx_h[i] + tap * p.dh, bx_n[i]);
           } else {
             for (int sub = 0; sub < subs; ++sub)
-              ptx::tma_load_2d(a_dst + (uint32_t)sub * 128u * (uint32_t)p.BK, &tmA, fb, c0, m0 + 128 * sub);
+              ptx::tma_load_2d(a_dst + (uint32_t)sub * 128u * (uint32_t)p.BK, mapA, fb, c0, m0 + 128 * sub);
           }
-          if (!p.w_resident) ptx::tma_load_3d(b_dst, &tmB, fb, c0, tap, n0);
+          if (!p.w_resident) ptx::tma_load_3d(b_dst, mapB, fb, c0, tap, n0);
           if (++chunk == p.c_chunks) {
             chunk = 0;
             ++tap;
             if (++ts == p.kw) {
               ts = 0;
               ++tr;
+            }
+            if (TF32 && tap == taps) { // next term: the same taps over the other operand pair
+              tap = 0;
+              tr = 0;
+              ts = 0;
+              ++term;
             }
           }
           if (++ps == p.stages) {
@@ -696,7 +762,7 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
         const uint32_t d_tmem = tmem_base + (uint32_t)buf * acc_stride;
         uint32_t wres_lo = desc_w_lo; // weight-resident mode: descriptor (low word) of K block `kit`
         if (PROF) pf_accwait += clock64() - pf_a0;
-        for (int kit = 0; kit < k_iters; ++kit, ++it) {
+        for (int kit = 0; kit < kTerms * k_iters; ++kit, ++it) {
           const long long pf_w0 = PROF ? clock64() : 0ll;
           if (!ptx::mbar_try_wait(m_full, mph) && !ptx::mbar_wait_bounded(m_full, mph, abort_flag)) {
             if (!*abort_flag) atomicExch(p.err, kErrFullWait);
@@ -713,18 +779,18 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
           const uint32_t w_lo = p.w_resident ? wres_lo : ring_lo + a_step;
           const uint32_t acc_first = kit > 0 ? 1u : 0u;
           if (!p.dual) {
-            if (ksteps == 4) ptx::tcgen05_mma_i8_kblock<4, BF16>(d_tmem, w_lo, ring_lo, desc_hi, p.idesc, acc_first);
-            else if (ksteps == 2) ptx::tcgen05_mma_i8_kblock<2, BF16>(d_tmem, w_lo, ring_lo, desc_hi, p.idesc, acc_first);
-            else ptx::tcgen05_mma_i8_kblock<1, BF16>(d_tmem, w_lo, ring_lo, desc_hi, p.idesc, acc_first);
+            if (ksteps == 4) ptx::tcgen05_mma_i8_kblock<4, KIND>(d_tmem, w_lo, ring_lo, desc_hi, p.idesc, acc_first);
+            else if (ksteps == 2) ptx::tcgen05_mma_i8_kblock<2, KIND>(d_tmem, w_lo, ring_lo, desc_hi, p.idesc, acc_first);
+            else ptx::tcgen05_mma_i8_kblock<1, KIND>(d_tmem, w_lo, ring_lo, desc_hi, p.idesc, acc_first);
           } else {
             // dual mode: sub-tile 0 uses weight rows 64..191 ([W; 0]), sub-tile 1 rows 0..127 ([0; W])
             for (int sub = 0; sub < 2; ++sub) {
               const uint32_t a_lo = w_lo + (sub == 0 ? dual_step : 0u);
               const uint32_t b_lo = ring_lo + (uint32_t)sub * sub_step;
               const uint32_t first = (kit > 0 || sub > 0) ? 1u : 0u;
-              if (ksteps == 4) ptx::tcgen05_mma_i8_kblock<4, BF16>(d_tmem, a_lo, b_lo, desc_hi, p.idesc, first);
-              else if (ksteps == 2) ptx::tcgen05_mma_i8_kblock<2, BF16>(d_tmem, a_lo, b_lo, desc_hi, p.idesc, first);
-              else ptx::tcgen05_mma_i8_kblock<1, BF16>(d_tmem, a_lo, b_lo, desc_hi, p.idesc, first);
+              if (ksteps == 4) ptx::tcgen05_mma_i8_kblock<4, KIND>(d_tmem, a_lo, b_lo, desc_hi, p.idesc, first);
+              else if (ksteps == 2) ptx::tcgen05_mma_i8_kblock<2, KIND>(d_tmem, a_lo, b_lo, desc_hi, p.idesc, first);
+              else ptx::tcgen05_mma_i8_kblock<1, KIND>(d_tmem, a_lo, b_lo, desc_hi, p.idesc, first);
             }
           }
           ptx::tcgen05_commit(m_empty); // frees the stage when the MMAs retire
@@ -775,7 +841,7 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
       const int n0 = (tile % n_tiles) * p.BN;
       const int buf = t & 1;
       if (n0 != staged_n0) {
-        if (BF16) {
+        if (BF16 || TF32) {
           const int ch = n0 + ch_base + lane;
           bias_f = ch < p.n_valid ? __int_as_float(p.bias[ch]) : 0.0f; // fp32 bias bits in the int32 array
         } else {
@@ -800,7 +866,13 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
         const uint32_t lane_addr = tmem_base + (uint32_t)buf * acc_stride + ((uint32_t)(quarter * 32) << 16);
         int8_t *out4 = p.out + (size_t)m0 * p.ldc + p.c_off + ch4;
         const bool ch4_ok = ch4 < p.n_valid;
-        if (BF16) {
+        if (TF32) {
+          // byte addressing: 4 bytes per channel
+          const int ch = n0 + ch_base + lane;
+          uint8_t *out_ch = reinterpret_cast<uint8_t *>(p.out) + (size_t)m0 * p.ldc + (size_t)(p.c_off + ch) * 4;
+          if (p.act == 1) epilogue_channels_f32<true>(p, lane_addr, out_ch, ch < p.n_valid, m0, half, kEpilogueWarps / 4, bias_f);
+          else epilogue_channels_f32<false>(p, lane_addr, out_ch, ch < p.n_valid, m0, half, kEpilogueWarps / 4, bias_f);
+        } else if (BF16) {
           // byte addressing: 2 bytes per channel, this lane's pair starts at its even channel
           const int ch = n0 + ch_base + lane;
           uint8_t *out_pair = reinterpret_cast<uint8_t *>(p.out) + (size_t)m0 * p.ldc + (size_t)(p.c_off + (ch & ~1)) * 2;
@@ -831,13 +903,13 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
 __global__ void __launch_bounds__(kConvThreads, 2)
 conv_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const ConvGemmParams p) {
-  conv_gemm_body<false, false, true>(tmA, tmB, p);
+  conv_gemm_body<false, false, true>(tmA, tmB, p, tmA, tmB);
 }
 // the same with the 64-bit multiply-add requantisation (requant_one), for layers outside requant_fast's domain
 __global__ void __launch_bounds__(kConvThreads, 2)
 conv_gemm_i8_wide_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                          const ConvGemmParams p) {
-  conv_gemm_body<false, false, false>(tmA, tmB, p);
+  conv_gemm_body<false, false, false>(tmA, tmB, p, tmA, tmB);
 }
 // The INT8 kernel with the loop-profile counters on (g_conv_prof): [0] MMA thread total clocks, [1] of which waiting
 // for a full stage, [2] waiting for a drained accumulator, [3] K blocks, [4] CTAs, [5] producer total, [6] of which
@@ -845,7 +917,7 @@ conv_gemm_i8_wide_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
 __global__ void __launch_bounds__(kConvThreads, 2)
 conv_gemm_prof_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                       const ConvGemmParams p) {
-  conv_gemm_body<false, true, true>(tmA, tmB, p);
+  conv_gemm_body<false, true, true>(tmA, tmB, p, tmA, tmB);
 }
 // The same pipeline for BF16 graphs: BF16 operands (tcgen05 kind::f16), fp32 accumulators, BF16 results.
 // All sizes in ConvGemmParams that count K or row pitches are in BYTES, so only the MMA kind and the
@@ -853,7 +925,31 @@ conv_gemm_prof_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
 __global__ void __launch_bounds__(kConvThreads, 2)
 conv_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                       const ConvGemmParams p) {
-  conv_gemm_body<true, false, false>(tmA, tmB, p);
+  conv_gemm_body<true, false, false>(tmA, tmB, p, tmA, tmB);
+}
+
+// fp32 convolution on the tensor cores as three TF32 products (see conv_gemm_body): tmA / tmA2 are the upper and
+// the remainder part of the activations, tmB / tmB2 of the weights.
+__global__ void __launch_bounds__(kConvThreads, 2)
+conv_gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                        const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2,
+                        const ConvGemmParams p) {
+  conv_gemm_body<false, false, false, true>(tmA, tmB, p, tmA2, tmB2);
+}
+
+// x -> (upper part, remainder): hi keeps the sign, the exponent and the top 10 mantissa bits of the fp32 word (what
+// a kind::tf32 product uses of it), lo = x - hi exactly. 16-byte vectors.
+__global__ void tf32_split_kernel(const float4 *__restrict__ x, float4 *__restrict__ hi, float4 *__restrict__ lo, size_t nvec) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) {
+    const float4 v = x[i];
+    float4 h, l;
+    h.x = __uint_as_float(__float_as_uint(v.x) & 0xffffe000u); l.x = __fsub_rn(v.x, h.x);
+    h.y = __uint_as_float(__float_as_uint(v.y) & 0xffffe000u); l.y = __fsub_rn(v.y, h.y);
+    h.z = __uint_as_float(__float_as_uint(v.z) & 0xffffe000u); l.z = __fsub_rn(v.z, h.z);
+    h.w = __uint_as_float(__float_as_uint(v.w) & 0xffffe000u); l.w = __fsub_rn(v.w, h.w);
+    hi[i] = h;
+    lo[i] = l;
+  }
 }
 
 } // namespace tpucb

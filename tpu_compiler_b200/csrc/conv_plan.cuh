@@ -72,6 +72,11 @@ inline uint32_t make_idesc_bf16(int M, int N) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 
+// kind::tf32 with an fp32 accumulator: D = f32 (1), A and B = TF32 (2)
+inline uint32_t make_idesc_tf32(int M, int N) {
+  return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
 struct ConvPlan {
   CUtensorMap tmA, tmB;
   ConvGemmParams p;
@@ -79,6 +84,11 @@ struct ConvPlan {
   size_t smem = 0;
   bool pair = false; // runs conv_gemm2_i8_kernel (two-SM tiles)
   bool bf16 = false; // runs conv_gemm_bf16_kernel (K sizes and pitches in bytes, 2 per element)
+  bool tf32 = false; // runs conv_gemm_tf32x3_kernel (fp32 operands, 4 bytes per element; three K passes)
+  CUtensorMap tmA2, tmB2;           // tf32: remainder parts of the activations and of the weights
+  const float *split_src = nullptr; // tf32: the fp32 input, split into split_hi / split_lo before the launch
+  float *split_hi = nullptr, *split_lo = nullptr;
+  size_t split_nvec = 0;
   bool use_patch = false;
   PatchArgs patch;
   int8_t *patch_buf = nullptr; // scratch: expanded patch matrix [M][kp]
@@ -130,6 +140,25 @@ inline std::vector<int8_t> pack_conv_weights_bf16(const float *w, int oc, int ic
           out[((size_t)o * taps + (r * kw + s)) * cin_pad + c] =
               (uint16_t)(f32_bits(w[(((size_t)o * icg + c) * kh + r) * kw + s]) >> 16);
   std::vector<int8_t> bytes(out.size() * 2);
+  std::memcpy(bytes.data(), out.data(), bytes.size());
+  return bytes;
+}
+
+// fp32 weights for the TF32 x 3 convolution, K-major [oc_pad][tap][cin_pad] as bytes: part 0 = the upper 19 bits of
+// every word, part 1 = the exact remainder.
+inline std::vector<int8_t> pack_conv_weights_tf32(const float *w, int oc, int icg, int kh, int kw, int oc_pad, int cin_pad,
+                                                  int part) {
+  const int taps = kh * kw;
+  std::vector<float> out((size_t)oc_pad * taps * cin_pad, 0.0f);
+  for (int o = 0; o < oc; ++o)
+    for (int c = 0; c < icg; ++c)
+      for (int r = 0; r < kh; ++r)
+        for (int s = 0; s < kw; ++s) {
+          const float v = w[(((size_t)o * icg + c) * kh + r) * kw + s];
+          const float hi = bits_f32(f32_bits(v) & 0xffffe000u);
+          out[((size_t)o * taps + (r * kw + s)) * cin_pad + c] = part == 0 ? hi : v - hi;
+        }
+  std::vector<int8_t> bytes(out.size() * 4);
   std::memcpy(bytes.data(), out.data(), bytes.size());
   return bytes;
 }
@@ -348,7 +377,7 @@ inline void finish_plan(ConvPlan &pl, int rows, int taps, int k_inner, int oc_pa
     // fewer bytes per pixel (measured faster for the 1x1 layers with 64 outputs).
     const size_t w_plain = (size_t)taps * p.c_chunks * 128 * p.BK;
     const bool plain_resident = w_plain <= 48 * 1024 && 113 * 1024 - kSmemHeader - 1024 - w_plain >= 3 * (size_t)128 * p.BK;
-    p.dual = (oc_pad <= 64 && p.a_mode != 2 && rows > 128 && !plain_resident) ? 1 : 0;
+    p.dual = (oc_pad <= 64 && p.a_mode != 2 && rows > 128 && !plain_resident && !pl.tf32) ? 1 : 0;
   }
   const int m_tiles = (rows + (p.dual ? 255 : 127)) / (p.dual ? 256 : 128);
   // Transposed product: the channel tile is the tensor core's M (128 TMEM lanes, rows past the
@@ -370,7 +399,7 @@ inline void finish_plan(ConvPlan &pl, int rows, int taps, int k_inner, int oc_pa
   // sets would force one CTA per SM, which measured slower than re-fetching the weights from L2.
   const int ctas_per_sm = 2;
   const size_t budget = 113 * 1024;
-  p.w_resident = (total_tiles >= 2LL * n_tiles && w_all <= 48 * 1024 &&
+  p.w_resident = (!pl.tf32 && total_tiles >= 2LL * n_tiles && w_all <= 48 * 1024 &&
                   budget - kSmemHeader - 1024 - w_all >= 3 * a_bytes) ? 1 : 0;
   const size_t stage_bytes = p.w_resident ? a_bytes : a_bytes + b_bytes;
   const size_t ring_budget = budget - kSmemHeader - 1024 - (p.w_resident ? w_all : 0);
@@ -384,7 +413,7 @@ inline void finish_plan(ConvPlan &pl, int rows, int taps, int k_inner, int oc_pa
     grid = grid / n_tiles * n_tiles; // a CTA's channel tile must not change
     if (grid < n_tiles) grid = n_tiles;
   }
-  const long long iters_per_cta = ((total_tiles + grid - 1) / grid) * k_iters;
+  const long long iters_per_cta = ((total_tiles + grid - 1) / grid) * k_iters * (pl.tf32 ? 3 : 1);
   if (stages > iters_per_cta) stages = (int)iters_per_cta;
   if (stages < 1) stages = 1;
   p.stages = stages;
@@ -410,7 +439,12 @@ inline void launch_conv_plan(const ConvPlan &pl, cudaStream_t stream, int sm_cou
                                                                               pl.patch);
   }
   const int threads = kConvThreads;
-  if (pl.bf16) conv_gemm_bf16_kernel<<<pl.grid, threads, pl.smem, stream>>>(pl.tmA, pl.tmB, pl.p);
+  if (pl.tf32) {
+    tf32_split_kernel<<<grid_for(pl.split_nvec, 256, sm_count), 256, 0, stream>>>(
+        reinterpret_cast<const float4 *>(pl.split_src), reinterpret_cast<float4 *>(pl.split_hi),
+        reinterpret_cast<float4 *>(pl.split_lo), pl.split_nvec);
+    conv_gemm_tf32x3_kernel<<<pl.grid, threads, pl.smem, stream>>>(pl.tmA, pl.tmB, pl.tmA2, pl.tmB2, pl.p);
+  } else if (pl.bf16) conv_gemm_bf16_kernel<<<pl.grid, threads, pl.smem, stream>>>(pl.tmA, pl.tmB, pl.p);
   else if (pl.pair && conv_prof_enabled()) conv_gemm2_prof_kernel<<<pl.grid, kPairThreads, pl.smem, stream>>>(pl.tmA, pl.tmB, pl.p);
   else if (pl.pair) conv_gemm2_i8_kernel<<<pl.grid, kPairThreads, pl.smem, stream>>>(pl.tmA, pl.tmB, pl.p);
   else if (!(pl.p.fastq & 1)) conv_gemm_i8_wide_kernel<<<pl.grid, threads, pl.smem, stream>>>(pl.tmA, pl.tmB, pl.p);
@@ -429,6 +463,8 @@ inline void conv_kernel_setup_once() {
     TPUCB_CUDA(cudaFuncSetAttribute(conv_gemm_prof_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     227 * 1024));
     TPUCB_CUDA(cudaFuncSetAttribute(conv_gemm_i8_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    227 * 1024));
+    TPUCB_CUDA(cudaFuncSetAttribute(conv_gemm_tf32x3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     227 * 1024));
     TPUCB_CUDA(cudaFuncSetAttribute(conv_gemm2_prof_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     227 * 1024));

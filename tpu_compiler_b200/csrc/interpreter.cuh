@@ -202,6 +202,7 @@ public:
   int *d_err = nullptr;
   bool use_graph = true;
   bool fuse_activations = true; // set before load_module
+  bool fp32_tensor_cores = true; // set before load_module: fp32 convolutions as three TF32 products
   void fuse_activation_chains(const std::map<std::string, int> &uses);
   cudaGraphExec_t graph_exec = nullptr;
   std::map<std::string, HostWeight> weights;
@@ -398,6 +399,56 @@ public:
     }
     if (out->dtype == DT_F32) {
       TPUCB_CHECK(in->dtype == DT_F32, "conv %s: an fp32 convolution needs an fp32 input", op.name.c_str());
+      if (I.fp32_tensor_cores && g.g == 1 && !g.ins_h && !g.ins_w && !in->padded_rows() && in->cp % 8 == 0 && g.pl <= 127 && g.pt <= 127 &&
+          (g.kw - 1) * g.dw <= 255 && (g.kh - 1) * g.dh <= 255) {
+        // fp32 convolution on the tensor cores as three TF32 products with fp32 accumulation (x w = xh wh + xl wh +
+        // xh wl, 2^-22 relative: inside the 1e-4 of the fp32 path, where a single TF32 product would not be). The
+        // activations are split into their two parts by a vector kernel right before the launch; the weights once, here.
+        conv_kernel_setup_once();
+        std::vector<int32_t> bias_bits(out->cp, 0);
+        for (int o = 0; o < g.oc; ++o) bias_bits[o] = (int32_t)f32_bits(bias[o]);
+        d_bias_ = I.upload(bias_bits);
+        act_ = do_relu_ ? 1 : 0;
+        ConvPlan pl;
+        std::memset(&pl.p, 0, sizeof(pl.p));
+        pl.tf32 = true;
+        pl.in = (const int8_t *)in->dev;
+        pl.split_src = (const float *)in->dev;
+        pl.split_hi = (float *)I.dalloc(in->bytes());
+        pl.split_lo = (float *)I.dalloc(in->bytes());
+        pl.split_nvec = in->bytes() / 16;
+        ConvGemmParams &p = pl.p;
+        p.OH = g.oh; p.OW = g.ow; p.sh = g.sh; p.sw = g.sw; p.pt = g.pt; p.pl = g.pl; p.dh = g.dh; p.dw = g.dw;
+        p.act = act_;
+        p.bias = d_bias_; p.mult = d_bias_; p.rshift = d_bias_;
+        p.out = (int8_t *)out->dev;
+        p.ldc = out->cp * 4; // bytes
+        p.c_off = 0;
+        p.err = I.d_err;
+        const int rows = g.n * g.oh * g.ow;
+        const int k_bytes = in->cp * 4;
+        const bool one = g.kh == 1 && g.kw == 1 && g.sh == 1 && g.sw == 1 && g.pt == 0 && g.pl == 0 && g.pb == 0 && g.pr == 0;
+        const int8_t *d_wh = I.upload(pack_conv_weights_tf32(filt.data.data(), g.oc, g.ic, g.kh, g.kw, out->cp, in->cp, 0));
+        const int8_t *d_wl = I.upload(pack_conv_weights_tf32(filt.data.data(), g.oc, g.ic, g.kh, g.kw, out->cp, in->cp, 1));
+        const int taps = one ? 1 : g.kh * g.kw;
+        p.kh = one ? 1 : g.kh; p.kw = one ? 1 : g.kw;
+        p.a_mode = one ? 0 : 1;
+        finish_plan(pl, rows, taps, k_bytes, out->cp, I.sm_count);
+        if (one) {
+          encode_matrix_map(&pl.tmA, (const int8_t *)pl.split_hi, rows, k_bytes, k_bytes, p.BK);
+          encode_matrix_map(&pl.tmA2, (const int8_t *)pl.split_lo, rows, k_bytes, k_bytes, p.BK);
+        } else {
+          encode_im2col_map(&pl.tmA, (const int8_t *)pl.split_hi, g, k_bytes, p.BK);
+          encode_im2col_map(&pl.tmA2, (const int8_t *)pl.split_lo, g, k_bytes, p.BK);
+        }
+        encode_weight_map(&pl.tmB, d_wh, out->cp, taps, k_bytes, p.BK, p.BN);
+        encode_weight_map(&pl.tmB2, d_wl, out->cp, taps, k_bytes, p.BK, p.BN);
+        p.idesc = make_idesc_tf32(128, p.BN);
+        pl.ops = alg_ops;
+        plans_.push_back(pl);
+        alg_bytes = 4.0 * ((double)in->numel() + out->numel() + filt.data.size() + g.oc);
+        return;
+      }
       f32_ = true;
       f32_w_ = I.upload(pack_conv_weights_f32(filt.data.data(), g.oc, icg, g.kh, g.kw, g.g));
       f32_b_ = I.upload(bias);
@@ -598,7 +649,7 @@ public:
   int kernel_launches() const override {
     if (f32_ || dw_) return 1;
     int k = (int)stem_plans_.size();
-    for (auto &pl : plans_) k += pl.use_patch ? 2 : 1;
+    for (auto &pl : plans_) k += (pl.use_patch || pl.tf32) ? 2 : 1;
     return k;
   }
   bool is_tensor_core() const { return !f32_ && !dw_; }

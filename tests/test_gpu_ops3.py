@@ -262,3 +262,31 @@ def test_conv_fp32_tensor_core(cfg):
          dh=1, dw=1, g=1, do_relu=cfg["relu"], with_bias=1)
     x = rng.normal(0, 1, (3, ic, hw, hw)).astype(np.float32)
     assert_close(run_both(b.text(), b.weights, {"x": x}, ["y"]), rtol=2e-5)
+
+
+def test_conv_fp32_fma_path_with_option_off():
+    """`fp32_tensor_cores` = 0 keeps fp32 convolutions on the FMA pipe: same graph, tighter agreement (fp32 sums in
+    another order only) and one launch instead of the split + tensor-core pair."""
+    from tpu_compiler_b200 import module
+    from oracle import graph_runner
+    rng = np.random.default_rng(43)
+    b = graphs.GraphBuilder(43, simulate=False)
+    b.op("input", "x", [], (2, 64, 10, 10), "FP32")
+    b.weight("w", rng.normal(0, 0.06, (96, 64, 3, 3)).astype(np.float32))
+    b.weight("bias", rng.normal(0, 0.1, 96).astype(np.float32))
+    b.op("conv_2d", "y", ["x", "w", "bias"], (2, 96, 10, 10), "FP32", kh=3, kw=3, sh=1, sw=1, pt=1, pb=1, pl=1, pr=1,
+         dh=1, dw=1, g=1, do_relu=1, with_bias=1)
+    x = rng.normal(0, 1, (2, 64, 10, 10)).astype(np.float32)
+    ref = graph_runner.run(b.text(), b.weights, {"x": x})["y"]
+    counts = {}
+    for opt in (0, 1):
+        m = module(0)
+        m.set_option("fp32_tensor_cores", opt)
+        m.load_text(b.text(), b.weights)
+        m.set_tensor("x", x)
+        m.invoke()
+        err = np.abs(m.get_tensor("y") - ref).max() / np.abs(ref).max()
+        counts[opt] = m.kernel_count()
+        m.close()
+        assert err <= (2e-5 if opt else 2e-6), (opt, err)
+    assert counts[1] == counts[0] + 1

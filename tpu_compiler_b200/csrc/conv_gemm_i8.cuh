@@ -938,7 +938,8 @@ conv_gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
 }
 
 // x -> (upper part, remainder): hi keeps the sign, the exponent and the top 10 mantissa bits of the fp32 word (what
-// a kind::tf32 product uses of it), lo = x - hi exactly. 16-byte vectors.
+// a kind::tf32 product uses of it), lo = x - hi exactly. 16-byte vectors; `hi` may be null (the tensor core makes the
+// same cut when it reads x itself).
 __global__ void tf32_split_kernel(const float4 *__restrict__ x, float4 *__restrict__ hi, float4 *__restrict__ lo, size_t nvec) {
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) {
     const float4 v = x[i];
@@ -947,7 +948,7 @@ __global__ void tf32_split_kernel(const float4 *__restrict__ x, float4 *__restri
     h.y = __uint_as_float(__float_as_uint(v.y) & 0xffffe000u); l.y = __fsub_rn(v.y, h.y);
     h.z = __uint_as_float(__float_as_uint(v.z) & 0xffffe000u); l.z = __fsub_rn(v.z, h.z);
     h.w = __uint_as_float(__float_as_uint(v.w) & 0xffffe000u); l.w = __fsub_rn(v.w, h.w);
-    hi[i] = h;
+    if (hi) hi[i] = h;
     lo[i] = l;
   }
 }

@@ -414,7 +414,9 @@ public:
         pl.tf32 = true;
         pl.in = (const int8_t *)in->dev;
         pl.split_src = (const float *)in->dev;
-        pl.split_hi = (float *)I.dalloc(in->bytes());
+        // The tensor core ignores the low 13 mantissa bits of an fp32 operand (measured: results are bit-identical with
+        // the upper part materialised or not), so the tensor itself serves as xh and only xl is written.
+        pl.split_hi = nullptr;
         pl.split_lo = (float *)I.dalloc(in->bytes());
         pl.split_nvec = in->bytes() / 16;
         ConvGemmParams &p = pl.p;
@@ -435,10 +437,10 @@ public:
         p.a_mode = one ? 0 : 1;
         finish_plan(pl, rows, taps, k_bytes, out->cp, I.sm_count);
         if (one) {
-          encode_matrix_map(&pl.tmA, (const int8_t *)pl.split_hi, rows, k_bytes, k_bytes, p.BK);
+          encode_matrix_map(&pl.tmA, pl.split_hi ? (const int8_t *)pl.split_hi : (const int8_t *)in->dev, rows, k_bytes, k_bytes, p.BK);
           encode_matrix_map(&pl.tmA2, (const int8_t *)pl.split_lo, rows, k_bytes, k_bytes, p.BK);
         } else {
-          encode_im2col_map(&pl.tmA, (const int8_t *)pl.split_hi, g, k_bytes, p.BK);
+          encode_im2col_map(&pl.tmA, pl.split_hi ? (const int8_t *)pl.split_hi : (const int8_t *)in->dev, g, k_bytes, p.BK);
           encode_im2col_map(&pl.tmA2, (const int8_t *)pl.split_lo, g, k_bytes, p.BK);
         }
         encode_weight_map(&pl.tmB, d_wh, out->cp, taps, k_bytes, p.BK, p.BN);
@@ -911,7 +913,7 @@ public:
       }
     } else {
       size_t n = out_->bytes() / 4;
-      eltwise_add_f32_kernel<<<grid_for(n, 256, I_.sm_count), 256, 0, s>>>(f_, (float *)out_->dev, n);
+      eltwise_add_f32_kernel<<<grid_for(n / 4, 256, I_.sm_count), 256, 0, s>>>(f_, (float *)out_->dev, n);
     }
   }
 

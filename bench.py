@@ -141,7 +141,7 @@ def run_calibration(args, rank, world, local_rank):
         dist = dist_mod
     from tpu_compiler_b200 import graphs, module
     from tpu_compiler_b200.calibration import ActivationCalibrator
-    bs = 64
+    bs = args.cal_batch
     n_batches = max(args.cal_images // bs, 1)
     model = graphs.resnet50_fp32(batch=bs)
     m = module(local_rank)
@@ -180,9 +180,9 @@ def run_calibration(args, rank, world, local_rank):
             "metric": "fp32 ResNet-50 calibration images/sec", "value": images / total_s, "unit": "images/s",
             "n_gpus": world, "steps": n_batches, "warmup": 3, "ms_per_step": total_s / n_batches * 1e3,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "calibration: fp32 ResNet-50, %d images per GPU in batches of 64 (N(0,1) clipped to "
+            "config": {"workload": "calibration: fp32 ResNet-50, %d images per GPU in batches of %d (N(0,1) clipped to "
                                    "[-3,3]), %d tensors, min/max pass + 2048-bin histogram pass + KLD search" %
-                                   (n_batches * bs, len(cal.names)),
+                                   (n_batches * bs, bs, len(cal.names)),
                        "parallelism": "image shards x%d, all-reduce(MAX) of min/max, all-reduce(SUM) of histograms" % world},
             "phases_s": {"min_max_pass": t1 - t0, "histogram_pass": t2 - t1, "kld_search": t3 - t2},
             "forward_ms_per_batch": fwd_ms, "thresholds": len(thr), "clocks": clocks}), flush=True)
@@ -266,6 +266,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--case", default=None, help="conv_sweep only: one case as c,hw,n")
     ap.add_argument("--cal-images", type=int, default=512, help="calibration workload: images per GPU")
+    ap.add_argument("--cal-batch", type=int, default=64, help="calibration workload: images per batch (64 in the "
+                    "configuration; smaller values are for profiler captures)")
     ap.add_argument("--workload", default="resnet50", choices=sorted(WORKLOADS) + ["conv_sweep", "calibration"],
                     help="resnet50 is the headline configuration; the others are the secondary graphs "
                          "(their lines carry no cpu_baseline)")

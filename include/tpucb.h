@@ -58,6 +58,9 @@ int tpucb_interp_set_tensor(tpucb_interp *it, const char *name, const float *dat
  * becomes the tensor's value for the next launch. The host buffer must stay untouched until
  * the next tpucb_interp_sync / invoke / get_tensor. */
 int tpucb_interp_set_tensor_async(tpucb_interp *it, const char *name, const float *pinned, size_t numel);
+/* Blocks until every copy started by tpucb_interp_set_tensor_async has left its host buffer (the buffers may be
+ * refilled afterwards); does not wait for launches. */
+int tpucb_interp_wait_uploads(tpucb_interp *it);
 /* MlirModuleInterpreter::invoke / invokeTo (MlirModuleInterpreter.cpp:371-381); an empty or
  * NULL name runs the whole module. Synchronous, like the reference. */
 int tpucb_interp_invoke(tpucb_interp *it);

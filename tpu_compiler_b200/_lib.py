@@ -31,6 +31,7 @@ def _declare(lib):
         "tpucb_interp_load_module": [vp, cp],
         "tpucb_interp_set_tensor": [vp, cp, fp, sz],
         "tpucb_interp_set_tensor_async": [vp, cp, fp, sz],
+        "tpucb_interp_wait_uploads": [vp],
         "tpucb_interp_invoke": [vp],
         "tpucb_interp_invoke_to": [vp, cp],
         "tpucb_interp_launch": [vp],

@@ -32,6 +32,12 @@ class ActivationCalibrator:
         self.device = torch.device("cuda", model._device) if model._device is not None else torch.device("cpu")
         self._lib = lib() if model._device is not None else None
         self.num_samples = 0
+        self._pinned = None
+        self._pinned_numel = 0
+        self._pinned_next = 0
+        if self._lib is not None:
+            # the two pinned upload buffers are part of setting up (tens of milliseconds), not of a pass
+            self._alloc_pinned(int(np.prod(model.get_tensor_shape(self.input_name))))
 
     # -- device work of the two passes (overridden by the CPU stand-in used in the gloo tests) -------
     def _local_min_max(self):
@@ -43,7 +49,7 @@ class ActivationCalibrator:
         torch.cuda.synchronize(self.device)
         n_img = 0
         for batch in self.batches():
-            self.model.set_tensor(self.input_name, batch)
+            self._upload(batch)
             self.model.launch()
             for t, name in enumerate(self.names):
                 check(self._lib.tpucb_calib_minmax(self.model._h, name.encode(),
@@ -52,13 +58,51 @@ class ActivationCalibrator:
         self.model.sync()
         return stats, n_img
 
+    def _upload(self, batch):
+        """The batch becomes the input of the next launch. It is copied into one of two pinned host buffers and sent
+        with set_tensor_async, so the host-side copy and the transfer of batch i + 1 run while batch i is computed."""
+        batch = np.ascontiguousarray(batch, np.float32)
+        if self._pinned is None or self._pinned_numel != batch.size:
+            self._alloc_pinned(batch.size)
+        h = self._pinned[self._pinned_next]
+        self._pinned_next ^= 1
+        self.model.wait_uploads()   # earlier copies have left the host buffers
+        np.copyto(np.ctypeslib.as_array(C.cast(h, C.POINTER(C.c_float)), shape=(batch.size,)), batch.reshape(-1))
+        self.model.set_tensor_async(self.input_name, h, batch.size)
+
+    def _alloc_pinned(self, numel):
+        self._free_pinned()
+        self._pinned = []
+        for _ in range(2):
+            h = C.c_void_p()
+            check(self._lib.tpucb_host_alloc(C.byref(h), numel * 4))
+            self._pinned.append(h)
+        self._pinned_numel = numel
+        self._pinned_next = 0
+
+    def _free_pinned(self):
+        if getattr(self, "_pinned", None):
+            try:
+                self.model.sync()   # no copy may still read the buffers
+            except Exception:
+                pass                # the module was closed first: closing it synchronised the device
+            for h in self._pinned:
+                self._lib.tpucb_host_free(h)
+        self._pinned = None
+
+    def __del__(self):
+        try:
+            self._free_pinned()
+        except Exception:
+            pass
+
     def _local_histograms(self, activations_statistics):
         """This rank's [T, bins] int64 histograms."""
         T = len(self.names)
         hist = torch.zeros((T, self.bin_num), dtype=torch.int64, device=self.device)
         torch.cuda.synchronize(self.device)
         for batch in self.batches():
-            self.model.set_tensor(self.input_name, batch)
+            self._upload(batch)
             self.model.launch()
             for t, name in enumerate(self.names):
                 ab = float(activations_statistics[name][2])

@@ -24,9 +24,10 @@ __global__ void minmax_f32_kernel(const float *__restrict__ x, size_t pixels, in
   if ((cp & 3) == 0 && (c & 3) == 0) {
     const size_t nvec = total / 4;
     const int vpp = cp / 4, vreal = c / 4;
+    const bool dense = vreal == vpp; // no padded channels: no position arithmetic at all
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) {
-      if ((int)(i % vpp) >= vreal) continue;
-      float4 v = reinterpret_cast<const float4 *>(x)[i];
+      if (!dense && (int)(i % vpp) >= vreal) continue;
+      float4 v = __ldg(reinterpret_cast<const float4 *>(x) + i);
       mn = fminf(fminf(mn, v.x), fminf(fminf(v.y, v.z), v.w));
       mx = fmaxf(fmaxf(mx, v.x), fmaxf(fmaxf(v.y, v.z), v.w));
     }
@@ -69,6 +70,30 @@ __global__ void hist_f32_kernel(const float *__restrict__ x, size_t pixels, int 
   __syncthreads();
   const size_t total = pixels * (size_t)cp;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
+  if ((cp & 3) == 0 && (c & 3) == 0) {
+    // 16-byte vectors, one shared-memory atomic per non-zero value: the bins of one warp's values are spread over
+    // the table, so the few collisions cost less than electing one adder per bin did.
+    const size_t nvec = total / 4;
+    const int vpp = cp / 4, vreal = c / 4;
+    const bool dense = vreal == vpp;
+    const float top = (float)(bins - 1);
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nvec; i += stride) {
+      if (!dense && (int)(i % vpp) >= vreal) continue;
+      const float4 v = __ldg(reinterpret_cast<const float4 *>(x) + i);
+      const float t4[4] = {fabsf(v.x), fabsf(v.y), fabsf(v.z), fabsf(v.w)};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        if (t4[k] != 0.0f) {
+          const float f = floorf(__fadd_rn(__fdiv_rn(t4[k], width), 0.5f));
+          if (f <= top) atomicAdd(&s_h[(int)f], 1u);
+        }
+      }
+    }
+    __syncthreads();
+    for (int j = threadIdx.x; j < bins; j += blockDim.x)
+      if (s_h[j]) atomicAdd(&hist[j], (unsigned long long)s_h[j]);
+    return;
+  }
   const size_t rounds = (total + stride - 1) / stride;
   size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
   for (size_t rd = 0; rd < rounds; ++rd, i += stride) {

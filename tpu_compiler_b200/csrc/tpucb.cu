@@ -99,6 +99,14 @@ int tpucb_interp_set_tensor_async(tpucb_interp *it, const char *name, const floa
   TPUCB_API_END
 }
 
+int tpucb_interp_wait_uploads(tpucb_interp *it) {
+  TPUCB_API_BEGIN
+  TPUCB_CHECK(it, "tpucb_interp_wait_uploads: bad argument");
+  it->impl.bind();
+  TPUCB_CUDA(cudaStreamSynchronize(it->impl.copy_stream));
+  TPUCB_API_END
+}
+
 int tpucb_interp_invoke(tpucb_interp *it) {
   TPUCB_API_BEGIN
   TPUCB_CHECK(it, "tpucb_interp_invoke: bad argument");
@@ -351,8 +359,8 @@ int tpucb_calib_hist(tpucb_interp *it, const char *name, float abs_max, int bins
   // width = abs_max / (bin_num - 1), in fp32 as numpy computes it (kld_calibrator.py:34)
   float width = abs_max / (float)(bins - 1);
   size_t total = t->pixels() * t->cp;
-  int grid = grid_for(total, 256, I.sm_count);
-  if (grid > I.sm_count * 4) grid = I.sm_count * 4;
+  int grid = grid_for(total / 4 + 1, 256, I.sm_count);
+  if (grid > I.sm_count * 8) grid = I.sm_count * 8;
   hist_f32_kernel<<<grid, 256, bins * sizeof(unsigned), I.stream>>>((const float *)t->dev, t->pixels(), t->c, t->cp,
                                                                     width, bins, (unsigned long long *)d_hist);
   TPUCB_CUDA(cudaGetLastError());

@@ -96,6 +96,10 @@ class module:
         """Pipelined set_tensor from PINNED host memory: the copy overlaps the launch in flight."""
         check(self._lib.tpucb_interp_set_tensor_async(self._h, name.encode(), C.cast(host_ptr, _f), numel))
 
+    def wait_uploads(self):
+        """Blocks until every set_tensor_async copy has left its pinned host buffer."""
+        check(self._lib.tpucb_interp_wait_uploads(self._h))
+
     def get_tensor_shape(self, name):
         shape = (C.c_int64 * 8)()
         rank = C.c_int(0)

@@ -196,6 +196,8 @@ def run_calibration(args, rank, world, local_rank):
 WORKLOADS = {
     "resnet50": {"builder": "resnet50_int8", "res": 224, "lo": -1.0, "batch": 256,
                  "metric": "INT8 ResNet-50 images/sec", "name": "resnet50_v1_int8_224"},
+    "resnet50_bf16": {"builder": "resnet50_bf16", "res": 224, "lo": -1.0, "batch": 128,
+                      "metric": "BF16 ResNet-50 images/sec", "name": "resnet50_v1_bf16_224"},
     "mobilenet_v2": {"builder": "mobilenet_v2_int8", "res": 224, "lo": -1.0, "batch": 128,
                      "metric": "INT8 MobileNet-v2 images/sec", "name": "mobilenet_v2_int8_224"},
     "yolov4": {"builder": "yolov4_style_int8", "res": 416, "lo": 0.0, "batch": 16,
@@ -426,18 +428,27 @@ def main():
         # (profiles/resnet50_int8_b64_dram_traffic.md: 10.09 MB read per launch, writes still dirty in L2 when the
         # kernel ends), scaled by the images per launch; null for the workloads that have no capture.
         traffic = 10.09e6 * B / 64.0 if args.workload == "resnet50" else None  # reads scale with the images per launch
-        roofline = {"bound": "tensor", "achieved": achieved, "peak": int8_peak, "unit": "TOP/s",
-                    "frac": achieved / int8_peak, "traffic": traffic,
-                    "traffic_note": "ncu dram__bytes_read+write per launch at batch 64 x batch/64; algorithmic bytes "
-                                    "per launch: %.1f MB" % (conv_bytes / max(n_conv, 1) / 1e6),
-                    "kernel": "conv_gemm_i8_kernel (tcgen05 kind::i8 implicit GEMM, %d launches per step)" % n_conv,
-                    "peak_source": "2 x bf16_tflops_sustained of %s peaks (no INT8 figure is measured; the 8-bit "
-                                   "rate of the same tensor pipe is twice the 16-bit rate)" % peaks["source"],
-                    "avg_launch_us": conv_ms * 1e3 / max(n_conv, 1),
-                    "i8_mma_peak_measured": i8_tops.value,
-                    "frac_of_i8_mma_peak": achieved / i8_tops.value if i8_tops.value > 0 else None,
-                    "hbm_view": {"achieved_gbs": conv_bytes / (conv_ms * 1e-3) / 1e9, "peak_gbs": peaks["hbm_gbs"],
-                                 "frac": conv_bytes / (conv_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}}
+        if args.workload == "resnet50_bf16":
+            # BF16 graph: the same pipeline with kind::f16 MMAs; the denominator is the measured bf16 rate itself
+            roofline = {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
+                        "frac": achieved / peaks["bf16_tflops_sustained"], "traffic": None,
+                        "kernel": "conv_gemm_bf16_kernel (tcgen05 kind::f16 implicit GEMM on BF16 operands, %d launches "
+                                  "per step)" % n_conv,
+                        "peak_source": "bf16_tflops_sustained of %s peaks" % peaks["source"],
+                        "avg_launch_us": conv_ms * 1e3 / max(n_conv, 1)}
+        else:
+            roofline = {"bound": "tensor", "achieved": achieved, "peak": int8_peak, "unit": "TOP/s",
+                        "frac": achieved / int8_peak, "traffic": traffic,
+                        "traffic_note": "ncu dram__bytes_read+write per launch at batch 64 x batch/64; algorithmic bytes "
+                                        "per launch: %.1f MB" % (conv_bytes / max(n_conv, 1) / 1e6),
+                        "kernel": "conv_gemm_i8_kernel (tcgen05 kind::i8 implicit GEMM, %d launches per step)" % n_conv,
+                        "peak_source": "2 x bf16_tflops_sustained of %s peaks (no INT8 figure is measured; the 8-bit "
+                                       "rate of the same tensor pipe is twice the 16-bit rate)" % peaks["source"],
+                        "avg_launch_us": conv_ms * 1e3 / max(n_conv, 1),
+                        "i8_mma_peak_measured": i8_tops.value,
+                        "frac_of_i8_mma_peak": achieved / i8_tops.value if i8_tops.value > 0 else None,
+                        "hbm_view": {"achieved_gbs": conv_bytes / (conv_ms * 1e-3) / 1e9, "peak_gbs": peaks["hbm_gbs"],
+                                     "frac": conv_bytes / (conv_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}}
         mem_kernels = {"achieved_gbs": other_bytes / (other_ms * 1e-3) / 1e9 if other_ms > 0 else None,
                        "peak_gbs": peaks["hbm_gbs"], "ms_per_step": other_ms}
         cpu = None
@@ -452,7 +463,8 @@ def main():
         line = {
             "metric": wl["metric"], "value": value, "unit": "images/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16" if args.workload == "resnet50_bf16" else "int8", "data": "synthetic",
             "config": {"workload": "%s, batch %d per GPU, whole module per step" % (wl["name"], B),
                        "global_batch": B * world, "parallelism": "replicas x%d (image shards, no data-path collective)" % world,
                        "l2": "per-step working set %.0f MB exceeds the 126 MB L2" % (act_bytes / 1e6),

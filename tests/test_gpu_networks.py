@@ -80,3 +80,30 @@ def test_yolov4_style_full_topology_loads_and_counts():
     for name, hw in (("head8", 52), ("head16", 26), ("head32", 13)):
         assert m.get_tensor(name).shape == (1, 255, hw, hw)
     m.close()
+
+
+def test_resnet50_bf16_graph():
+    """An all-BF16 ResNet-50 (BF16 convolutions and inner product on the tensor cores, BF16 pooling and eltwise)
+    against the oracle. A BF16 result may land one unit in the last place (0.4%) away from the CPU loop's, and such
+    flips feed the next layer, so only the first layers are compared in ulps; deeper tensors and the logits are
+    compared to a few percent of their range."""
+    from tpu_compiler_b200 import module
+    model = graphs.resnet50_bf16(batch=2)
+    x = np.random.default_rng(5).uniform(-1, 1, (2, 3, 224, 224)).astype(np.float32)
+    ref = graph_runner.run(model.text, model.weights, {"data": x})
+    m = module(0)
+    m.load_text(model.text, model.weights)
+    m.set_tensor("data", x)
+    m.invoke()
+    got = {n: m.get_tensor(n) for n in ("data_bf16", "conv1", "pool1", "res2a", "res3d", "res5c", "fc1000_f32")}
+    m.close()
+    assert np.array_equal(got["data_bf16"], ref["data_bf16"])
+    for n in ("conv1", "pool1"):
+        g = (got[n].reshape(-1).view(np.uint32) >> 16).astype(np.int64)
+        e = (ref[n].reshape(-1).view(np.uint32) >> 16).astype(np.int64)
+        big = np.abs(ref[n].reshape(-1)) > 1e-2 * np.abs(ref[n]).max()
+        assert np.abs(g - e)[big].max() <= 1, n
+    for n, tol in (("res2a", 0.01), ("res3d", 0.02), ("res5c", 0.04), ("fc1000_f32", 0.04)):
+        err = np.abs(got[n] - ref[n]).max() / np.abs(ref[n]).max()
+        assert err <= tol, (n, err)
+    assert (np.argmax(got["fc1000_f32"], axis=1) == np.argmax(ref["fc1000_f32"], axis=1)).all()

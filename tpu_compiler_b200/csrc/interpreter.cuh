@@ -354,9 +354,9 @@ public:
       // BF16 graphs (core/conv.cpp:90-98: fp32 convolution of BF16-valued operands, fp32 bias, ReLU, BF16 rounding):
       // the tensor-core pipeline with BF16 operands and fp32 accumulators; every K size and pitch is in bytes.
       TPUCB_CHECK(in->dtype == DT_BF16, "conv %s: a BF16 convolution needs a BF16 input", op.name.c_str());
-      TPUCB_CHECK(g.g == 1 && !g.ins_h && !g.ins_w && !in->padded_rows() && g.ic >= 8 && g.pl <= 127 && g.pt <= 127 &&
+      TPUCB_CHECK(g.g == 1 && !g.ins_h && !g.ins_w && !in->padded_rows() && g.pl <= 127 && g.pt <= 127 &&
                       (g.kw - 1) * g.dw <= 255 && (g.kh - 1) * g.dh <= 255,
-                  "conv %s: BF16 convolution supports dense, ungrouped layers with at least 8 input channels", op.name.c_str());
+                  "conv %s: BF16 convolution supports dense, ungrouped layers", op.name.c_str());
       conv_kernel_setup_once();
       std::vector<int32_t> bias_bits(out->cp, 0);
       for (int o = 0; o < g.oc; ++o) bias_bits[o] = (int32_t)f32_bits(bias[o]);

@@ -362,6 +362,49 @@ def resnet50_fp32(batch=1, seed=5001):
     return Model(b.text(), b.weights, ["data"], ["prob"], {"batch": batch})
 
 
+def resnet50_bf16(batch=1, seed=6001, simulate=False):
+    """ResNet-50 v1 as an all-BF16 graph (the reference's BF16 quantisation of the fp32 graph: BF16 weights, fp32
+    bias, every tensor rounded to BF16): fp32 input -> quant NONE->BF16 -> BF16 convolutions / pooling / eltwise /
+    inner product -> quant BF16->NONE."""
+    rng = np.random.default_rng(seed)
+    b = GraphBuilder(seed, simulate=False)
+
+    def conv(name, src, oc, k, stride=1, pad=0, relu=True):
+        n, ic, ih, iw = b.shapes[src]
+        oh = (ih + 2 * pad - k) // stride + 1
+        ow = (iw + 2 * pad - k) // stride + 1
+        f = b.weight(name + "_filter", _bf16_np(rng.normal(0.0, math.sqrt(2.0 / (ic * k * k)), (oc, ic, k, k))))
+        bi = b.weight(name + "_bias", rng.normal(0.0, 0.05, oc))
+        b.op("conv_2d", name, [src, f, bi], (n, oc, oh, ow), "BF16", kh=k, kw=k, sh=stride, sw=stride, pt=pad, pb=pad,
+             pl=pad, pr=pad, dh=1, dw=1, g=1, do_relu=int(relu), with_bias=1)
+        return name
+
+    b.op("input", "data", [], (batch, 3, 224, 224), "FP32")
+    b.op("quant", "data_bf16", ["data"], (batch, 3, 224, 224), "BF16", **{"from": "NONE", "to": "BF16", "scale": 1.0,
+                                                                        "zero_point": 0})
+    x = conv("conv1", "data_bf16", 64, 7, 2, 3)
+    b.op("pool_max_2d", "pool1", [x], (batch, 64, 56, 56), "BF16", kh=3, kw=3, sh=2, sw=2, pt=0, pb=1, pl=0, pr=1)
+    x = "pool1"
+    stages = [(64, 256, 3, 1), (128, 512, 4, 2), (256, 1024, 6, 2), (512, 2048, 3, 2)]
+    for si, (mid, out, blocks, stride) in enumerate(stages):
+        for bi_ in range(blocks):
+            p = "res%d%s" % (si + 2, "abcdef"[bi_])
+            s = stride if bi_ == 0 else 1
+            short = conv(p + "_branch1", x, out, 1, s, 0, relu=False) if bi_ == 0 else x
+            y = conv(p + "_branch2a", x, mid, 1, s, 0)
+            y = conv(p + "_branch2b", y, mid, 3, 1, 1)
+            y = conv(p + "_branch2c", y, out, 1, 1, 0, relu=False)
+            b.op("eltwise_add", p, [short, y], b.shapes[y], "BF16", do_relu=1)
+            x = p
+    n, c, h, w = b.shapes[x]
+    b.op("pool_avg_2d", "pool5", [x], (n, c, 1, 1), "BF16", kh=h, kw=w, sh=h, sw=w, count_include_pad=1)
+    fw = b.weight("fc1000_filter", _bf16_np(rng.normal(0.0, math.sqrt(2.0 / c), (1000, c))))
+    fb = b.weight("fc1000_bias", rng.normal(0.0, 0.05, 1000))
+    b.op("fully_connected", "fc1000", ["pool5", fw, fb], (n, 1000), "BF16", do_relu=0)
+    b.op("quant", "fc1000_f32", ["fc1000"], (n, 1000), "FP32", **{"from": "BF16", "to": "NONE", "scale": 1.0, "zero_point": 0})
+    return Model(b.text(), b.weights, ["data"], ["fc1000_f32"], {"batch": batch})
+
+
 # ----------------------------------------------------------------------------- BF16 tables (numpy)
 def _bf16_np(x):
     """F32ToBF16 with rounding (QuantizationArithmetic.cpp:873-910) on arrays."""

@@ -129,7 +129,8 @@ def assert_bf16_ulp(pairs, max_ulp=1):
 
 
 @pytest.mark.parametrize("cfg", [dict(ic=32, oc=64, hw=12, k=1, s=1, p=0, relu=1), dict(ic=64, oc=128, hw=14, k=3, s=1, p=1, relu=1),
-                                 dict(ic=16, oc=256, hw=9, k=3, s=2, p=1, relu=0), dict(ic=128, oc=24, hw=7, k=1, s=1, p=0, relu=0)])
+                                 dict(ic=16, oc=256, hw=9, k=3, s=2, p=1, relu=0), dict(ic=128, oc=24, hw=7, k=1, s=1, p=0, relu=0),
+                                 dict(ic=3, oc=64, hw=30, k=7, s=2, p=3, relu=1), dict(ic=4, oc=32, hw=11, k=3, s=1, p=1, relu=0)])
 def test_conv_bf16(cfg):
     """BF16 convolution on the tensor cores (BF16 operands, fp32 accumulation) against the fp32-loop oracle."""
     rng = np.random.default_rng(17)

@@ -90,6 +90,7 @@ struct ConvPlan {
   float *split_hi = nullptr, *split_lo = nullptr;
   size_t split_nvec = 0;
   bool use_patch = false;
+  int patch_elsize = 1; // bytes per element of the patch matrix: 1 INT8, 2 BF16
   PatchArgs patch;
   int8_t *patch_buf = nullptr; // scratch: expanded patch matrix [M][kp]
   size_t patch_bytes = 0;
@@ -160,6 +161,29 @@ inline std::vector<int8_t> pack_conv_weights_tf32(const float *w, int oc, int ic
         }
   std::vector<int8_t> bytes(out.size() * 4);
   std::memcpy(bytes.data(), out.data(), bytes.size());
+  return bytes;
+}
+
+// Weights of the patch-matrix form [oc_pad][kp], k = (r * kw + s) * icg + c, as 2-byte BF16 (part < 0) or as fp32
+// parts of a TF32 x 3 product (part 0: upper 19 bits, part 1: remainder).
+inline std::vector<int8_t> pack_patch_weights(const float *w, int oc, int icg, int kh, int kw, int oc_pad, int kp, int part) {
+  const size_t n = (size_t)oc_pad * kp;
+  std::vector<uint16_t> h(part < 0 ? n : 0, 0);
+  std::vector<float> f(part < 0 ? 0 : n, 0.0f);
+  for (int o = 0; o < oc; ++o)
+    for (int c = 0; c < icg; ++c)
+      for (int r = 0; r < kh; ++r)
+        for (int s = 0; s < kw; ++s) {
+          const float v = w[(((size_t)o * icg + c) * kh + r) * kw + s];
+          const size_t k = (size_t)o * kp + (size_t)(r * kw + s) * icg + c;
+          if (part < 0) h[k] = (uint16_t)(f32_bits(v) >> 16);
+          else {
+            const float hi = bits_f32(f32_bits(v) & 0xffffe000u);
+            f[k] = part == 0 ? hi : v - hi;
+          }
+        }
+  std::vector<int8_t> bytes(part < 0 ? n * 2 : n * 4);
+  std::memcpy(bytes.data(), part < 0 ? (const void *)h.data() : (const void *)f.data(), bytes.size());
   return bytes;
 }
 
@@ -435,8 +459,11 @@ inline void conv_prof_read(unsigned long long *out16) {
 inline void launch_conv_plan(const ConvPlan &pl, cudaStream_t stream, int sm_count) {
   if (pl.use_patch) {
     size_t total = (size_t)pl.p.M_total * pl.patch.kp;
-    patch_expand_i8_kernel<<<grid_for(total, 256, sm_count), 256, 0, stream>>>(pl.in, pl.patch_buf,
-                                                                              pl.patch);
+    if (pl.patch_elsize == 2)
+      patch_expand_kernel<uint16_t><<<grid_for(total / 8, 256, sm_count), 256, 0, stream>>>(
+          reinterpret_cast<const uint16_t *>(pl.in), reinterpret_cast<uint16_t *>(pl.patch_buf), pl.patch);
+    else
+      patch_expand_i8_kernel<<<grid_for(total, 256, sm_count), 256, 0, stream>>>(pl.in, pl.patch_buf, pl.patch);
   }
   const int threads = kConvThreads;
   if (pl.tf32) {

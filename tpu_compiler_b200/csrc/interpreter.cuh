@@ -294,6 +294,11 @@ public:
           out_->wphys, scale_);
       return;
     }
+    if (kind_ == 5 && in_->dtype == DT_F32 && in_->cp == 4 && out_->cp == 16 && !out_->padded_rows()) {
+      quant_f32c4_to_bf16c16_kernel<<<grid_for(out_->pixels(), 256, I_.sm_count), 256, 0, s>>>(
+          (const float4 *)in_->dev, (uint4 *)out_->dev, out_->pixels(), out_->c);
+      return;
+    }
     const bool same_layout = in_->cp == out_->cp && !out_->padded_rows() && out_->cp % 16 == 0;
     if (same_layout && (kind_ == 3 || kind_ == 4)) {
       size_t nvec = out_->pixels() * out_->cp / 16;
@@ -377,6 +382,29 @@ public:
       const int rows = g.n * g.oh * g.ow;
       const int k_bytes = in->cp * 2;
       const bool one_by_one_bf = g.kh == 1 && g.kw == 1 && g.sh == 1 && g.sw == 1 && g.pt == 0 && g.pl == 0 && g.pb == 0 && g.pr == 0;
+      if (g.ic < 8 && !one_by_one_bf) {
+        // few input channels (3-channel stems): expand the patches into a K-major matrix first
+        pl.use_patch = true;
+        pl.patch_elsize = 2;
+        PatchArgs &a = pl.patch;
+        a.n = g.n; a.c = g.ic; a.cp = in->cp; a.ih = g.ih; a.iw = g.iw; a.oh = g.oh; a.ow = g.ow;
+        a.kh = g.kh; a.kw = g.kw; a.sh = g.sh; a.sw = g.sw; a.pt = g.pt; a.pl = g.pl; a.dh = g.dh; a.dw = g.dw;
+        a.ins_h = 0; a.ins_w = 0; a.c_first = 0; a.c_count = g.ic; a.wl = in->wl; a.wphys = in->wphys;
+        a.kp = round_up(g.kh * g.kw * g.ic, 16);
+        pl.patch_bytes = (size_t)rows * a.kp * 2;
+        pl.patch_buf = (int8_t *)I.dalloc(pl.patch_bytes);
+        const int8_t *d_wp = I.upload(pack_patch_weights(filt.data.data(), g.oc, g.ic, g.kh, g.kw, out->cp, a.kp, -1));
+        p.kh = p.kw = 1;
+        p.a_mode = 0;
+        finish_plan(pl, rows, 1, a.kp * 2, out->cp, I.sm_count);
+        encode_matrix_map(&pl.tmA, pl.patch_buf, rows, a.kp * 2, a.kp * 2, p.BK);
+        encode_weight_map(&pl.tmB, d_wp, out->cp, 1, a.kp * 2, p.BK, p.dual ? 192 : p.BN);
+        p.idesc = make_idesc_bf16(128, p.BN);
+        pl.ops = alg_ops;
+        plans_.push_back(pl);
+        alg_bytes = 2.0 * ((double)in->numel() + out->numel() + filt.data.size()) + 4.0 * g.oc;
+        return;
+      }
       const int8_t *d_w = I.upload(pack_conv_weights_bf16(filt.data.data(), g.oc, g.ic, g.kh, g.kw, out->cp, in->cp));
       if (one_by_one_bf) {
         p.kh = p.kw = 1;
@@ -399,8 +427,10 @@ public:
     }
     if (out->dtype == DT_F32) {
       TPUCB_CHECK(in->dtype == DT_F32, "conv %s: an fp32 convolution needs an fp32 input", op.name.c_str());
-      if (I.fp32_tensor_cores && g.g == 1 && !g.ins_h && !g.ins_w && !in->padded_rows() && in->cp % 8 == 0 && g.pl <= 127 && g.pt <= 127 &&
-          (g.kw - 1) * g.dw <= 255 && (g.kh - 1) * g.dh <= 255) {
+      // (Few-channel layers, i.e. the 3-channel stem, stay on the FMA pipe: expanding their patches into a K-major fp32
+      // matrix for the tensor cores, as the BF16 branch does, measured 1.33 ms against 1.26 ms at batch 64.)
+      if (I.fp32_tensor_cores && g.g == 1 && !g.ins_h && !g.ins_w && !in->padded_rows() && in->cp % 8 == 0 &&
+          g.pl <= 127 && g.pt <= 127 && (g.kw - 1) * g.dw <= 255 && (g.kh - 1) * g.dh <= 255) {
         // fp32 convolution on the tensor cores as three TF32 products with fp32 accumulation (x w = xh wh + xl wh +
         // xh wl, 2^-22 relative: inside the 1e-4 of the fp32 path, where a single TF32 product would not be). The
         // activations are split into their two parts by a vector kernel right before the launch; the weights once, here.
@@ -651,7 +681,7 @@ public:
   int kernel_launches() const override {
     if (f32_ || dw_) return 1;
     int k = (int)stem_plans_.size();
-    for (auto &pl : plans_) k += (pl.use_patch || pl.tf32) ? 2 : 1;
+    for (auto &pl : plans_) k += 1 + (pl.use_patch ? 1 : 0) + (pl.tf32 ? 1 : 0);
     return k;
   }
   bool is_tensor_core() const { return !f32_ && !dw_; }

@@ -104,6 +104,18 @@ __device__ __forceinline__ void store_from_f32(void *p, int dt, size_t i, float 
   else reinterpret_cast<float *>(p)[i] = v;
 }
 
+// fp32 NHWC4 input image -> BF16 tensor with a 16-channel pitch (quant NONE -> BF16: the upper half of each fp32
+// word, no rounding, QuantOpKernel's cast): one pixel per thread, one 16-byte read, two 16-byte writes.
+__global__ void quant_f32c4_to_bf16c16_kernel(const float4 *__restrict__ in, uint4 *__restrict__ out, size_t pixels, int c) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < pixels; i += (size_t)gridDim.x * blockDim.x) {
+    const float4 v = __ldg(in + i);
+    const uint32_t h0 = __float_as_uint(v.x) >> 16, h1 = c > 1 ? __float_as_uint(v.y) >> 16 : 0u;
+    const uint32_t h2 = c > 2 ? __float_as_uint(v.z) >> 16 : 0u, h3 = c > 3 ? __float_as_uint(v.w) >> 16 : 0u;
+    out[2 * i] = make_uint4(h0 | (h1 << 16), h2 | (h3 << 16), 0u, 0u);
+    out[2 * i + 1] = make_uint4(0u, 0u, 0u, 0u);
+  }
+}
+
 __global__ void quant_kernel(const void *__restrict__ src, void *__restrict__ dst, size_t rows, int w,
                              int wl, int wphys, int c, int cps, int cpd, int sdt, int ddt, int kind,
                              float scale) {
@@ -606,6 +618,38 @@ __global__ void patch_expand_i8_kernel(const int8_t *__restrict__ in, int8_t *__
       }
     }
     out[i] = v;
+  }
+}
+
+// The same expansion for 2-byte (BF16) and 4-byte (fp32) elements, one thread per 16-byte vector of the patch
+// matrix: few-channel BF16 / fp32 convolutions (3-channel stems) would otherwise run one 32-byte K step per filter
+// tap; the expanded matrix [M][kp] is a plain K-major operand with a handful of 128-byte K blocks.
+template <typename T>
+__global__ void patch_expand_kernel(const T *__restrict__ in, T *__restrict__ out, PatchArgs a) {
+  constexpr int V = 16 / (int)sizeof(T);
+  const size_t total = (size_t)a.n * a.oh * a.ow * (a.kp / V);
+  const int kreal = a.kh * a.kw * a.c_count;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int kv = (int)(i % (a.kp / V));
+    const size_t pix = i / (a.kp / V);
+    const int x = (int)(pix % a.ow);
+    const size_t t = pix / a.ow;
+    const int y = (int)(t % a.oh);
+    const int b = (int)(t / a.oh);
+    T v[V];
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+      const int k = kv * V + j;
+      v[j] = (T)0;
+      if (k < kreal) {
+        const int c = k % a.c_count, tap = k / a.c_count;
+        const int s = tap % a.kw, r = tap / a.kw;
+        const int yy = y * a.sh - a.pt + r * a.dh, xx = x * a.sw - a.pl + s * a.dw;
+        if (yy >= 0 && yy < a.ih && xx >= 0 && xx < a.iw)
+          v[j] = in[(((size_t)b * a.ih + yy) * a.wphys + a.wl + xx) * a.cp + a.c_first + c];
+      }
+    }
+    reinterpret_cast<uint4 *>(out)[i] = *reinterpret_cast<const uint4 *>(v);
   }
 }
 

@@ -155,6 +155,13 @@ def run_calibration(args, rank, world, local_rank):
     sampler = ClockSampler(local_rank)
     sampler.start()
     if dist is not None:
+        # untimed warm-up of the two collectives the pass uses (the first MAX / SUM all-reduce of a process sets up
+        # its NCCL channels), then the barrier that starts the timed region
+        w1 = torch.zeros(2, dtype=torch.float32, device="cuda")
+        w2 = torch.zeros(2, dtype=torch.int64, device="cuda")
+        for _ in range(3):
+            dist.all_reduce(w1, op=dist.ReduceOp.MAX)
+            dist.all_reduce(w2, op=dist.ReduceOp.SUM)
         dist.barrier()
     torch.cuda.synchronize()
     t0 = time.perf_counter()

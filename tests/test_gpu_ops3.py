@@ -247,7 +247,8 @@ def test_conv_i8_requant_forms(relu, rshift_range):
 
 
 @pytest.mark.parametrize("cfg", [dict(ic=64, oc=64, hw=14, k=1, s=1, p=0, relu=1), dict(ic=32, oc=160, hw=13, k=3, s=1, p=1, relu=1),
-                                 dict(ic=128, oc=40, hw=12, k=3, s=2, p=1, relu=0), dict(ic=8, oc=256, hw=9, k=1, s=1, p=0, relu=0)])
+                                 dict(ic=128, oc=40, hw=12, k=3, s=2, p=1, relu=0), dict(ic=8, oc=256, hw=9, k=1, s=1, p=0, relu=0),
+                                 dict(ic=3, oc=64, hw=30, k=7, s=2, p=3, relu=1), dict(ic=4, oc=24, hw=9, k=3, s=1, p=1, relu=0)])
 def test_conv_fp32_tensor_core(cfg):
     """fp32 convolution as three TF32 products on the tensor cores against the double-accumulated oracle. The bound
     (2e-5 of the tensor's range; measured 1e-6 to 5e-6, the tensor core truncates its partial sums) is far below what

@@ -90,7 +90,7 @@ struct ConvPlan {
   float *split_hi = nullptr, *split_lo = nullptr;
   size_t split_nvec = 0;
   bool use_patch = false;
-  int patch_elsize = 1; // bytes per element of the patch matrix: 1 INT8, 2 BF16
+  int patch_elsize = 1; // bytes per element of the patch matrix: 1 INT8, 2 BF16, 4 fp32
   PatchArgs patch;
   int8_t *patch_buf = nullptr; // scratch: expanded patch matrix [M][kp]
   size_t patch_bytes = 0;
@@ -98,12 +98,15 @@ struct ConvPlan {
   double ops = 0, bytes = 0; // algorithmic work of one launch
 };
 
+// K block width in bytes for `k_bytes` of K per tap. The main loop's time follows the NUMBER of K blocks (a block
+// costs a barrier round trip and a copy issue whatever its width), so the fewest blocks win and, among equal counts,
+// the narrower block (less zero padding through the tensor pipe): 96 bytes -> one 128-byte block, not three of 32.
 inline int pick_bk(int k_bytes) {
-  int best = 128, best_cost = 1 << 30;
+  int best = 128, best_blocks = 1 << 30;
   for (int bk : {128, 64, 32}) {
-    int cost = round_up(k_bytes, bk);
-    if (cost < best_cost) {
-      best_cost = cost;
+    int blocks = (k_bytes + bk - 1) / bk;
+    if (blocks <= best_blocks) {
+      best_blocks = blocks;
       best = bk;
     }
   }
@@ -166,7 +169,9 @@ inline std::vector<int8_t> pack_conv_weights_tf32(const float *w, int oc, int ic
 
 // Weights of the patch-matrix form [oc_pad][kp], k = (r * kw + s) * icg + c, as 2-byte BF16 (part < 0) or as fp32
 // parts of a TF32 x 3 product (part 0: upper 19 bits, part 1: remainder).
-inline std::vector<int8_t> pack_patch_weights(const float *w, int oc, int icg, int kh, int kw, int oc_pad, int kp, int part) {
+inline std::vector<int8_t> pack_patch_weights(const float *w, int oc, int icg, int kh, int kw, int oc_pad, int kp, int part,
+                                              int cstride = 0) {
+  if (cstride == 0) cstride = icg; // channel slots per tap (4 in patch_expand_tap_kernel's layout)
   const size_t n = (size_t)oc_pad * kp;
   std::vector<uint16_t> h(part < 0 ? n : 0, 0);
   std::vector<float> f(part < 0 ? 0 : n, 0.0f);
@@ -175,7 +180,7 @@ inline std::vector<int8_t> pack_patch_weights(const float *w, int oc, int icg, i
       for (int r = 0; r < kh; ++r)
         for (int s = 0; s < kw; ++s) {
           const float v = w[(((size_t)o * icg + c) * kh + r) * kw + s];
-          const size_t k = (size_t)o * kp + (size_t)(r * kw + s) * icg + c;
+          const size_t k = (size_t)o * kp + (size_t)(r * kw + s) * cstride + c;
           if (part < 0) h[k] = (uint16_t)(f32_bits(v) >> 16);
           else {
             const float hi = bits_f32(f32_bits(v) & 0xffffe000u);
@@ -459,7 +464,13 @@ inline void conv_prof_read(unsigned long long *out16) {
 inline void launch_conv_plan(const ConvPlan &pl, cudaStream_t stream, int sm_count) {
   if (pl.use_patch) {
     size_t total = (size_t)pl.p.M_total * pl.patch.kp;
-    if (pl.patch_elsize == 2)
+    if (pl.patch.cv == 4 && pl.patch_elsize == 4)
+      patch_expand_tap_kernel<float><<<grid_for(total / 4, 256, sm_count), 256, 0, stream>>>(
+          reinterpret_cast<const float *>(pl.in), reinterpret_cast<float *>(pl.patch_buf), pl.split_lo, pl.patch);
+    else if (pl.patch.cv == 4)
+      patch_expand_tap_kernel<uint16_t><<<grid_for(total / 4, 256, sm_count), 256, 0, stream>>>(
+          reinterpret_cast<const uint16_t *>(pl.in), reinterpret_cast<uint16_t *>(pl.patch_buf), nullptr, pl.patch);
+    else if (pl.patch_elsize == 2)
       patch_expand_kernel<uint16_t><<<grid_for(total / 8, 256, sm_count), 256, 0, stream>>>(
           reinterpret_cast<const uint16_t *>(pl.in), reinterpret_cast<uint16_t *>(pl.patch_buf), pl.patch);
     else
@@ -467,7 +478,8 @@ inline void launch_conv_plan(const ConvPlan &pl, cudaStream_t stream, int sm_cou
   }
   const int threads = kConvThreads;
   if (pl.tf32) {
-    tf32_split_kernel<<<grid_for(pl.split_nvec, 256, sm_count), 256, 0, stream>>>(
+    if (pl.split_src)
+      tf32_split_kernel<<<grid_for(pl.split_nvec, 256, sm_count), 256, 0, stream>>>(
         reinterpret_cast<const float4 *>(pl.split_src), reinterpret_cast<float4 *>(pl.split_hi),
         reinterpret_cast<float4 *>(pl.split_lo), pl.split_nvec);
     conv_gemm_tf32x3_kernel<<<pl.grid, threads, pl.smem, stream>>>(pl.tmA, pl.tmB, pl.tmA2, pl.tmB2, pl.p);

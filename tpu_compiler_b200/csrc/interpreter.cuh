@@ -390,10 +390,11 @@ public:
         a.n = g.n; a.c = g.ic; a.cp = in->cp; a.ih = g.ih; a.iw = g.iw; a.oh = g.oh; a.ow = g.ow;
         a.kh = g.kh; a.kw = g.kw; a.sh = g.sh; a.sw = g.sw; a.pt = g.pt; a.pl = g.pl; a.dh = g.dh; a.dw = g.dw;
         a.ins_h = 0; a.ins_w = 0; a.c_first = 0; a.c_count = g.ic; a.wl = in->wl; a.wphys = in->wphys;
-        a.kp = round_up(g.kh * g.kw * g.ic, 16);
+        a.cv = g.ic <= 4 ? 4 : 0; // four channel slots per tap: one 8-byte copy per tap
+        a.kp = a.cv ? round_up(g.kh * g.kw * 4, 8) : round_up(g.kh * g.kw * g.ic, 16);
         pl.patch_bytes = (size_t)rows * a.kp * 2;
         pl.patch_buf = (int8_t *)I.dalloc(pl.patch_bytes);
-        const int8_t *d_wp = I.upload(pack_patch_weights(filt.data.data(), g.oc, g.ic, g.kh, g.kw, out->cp, a.kp, -1));
+        const int8_t *d_wp = I.upload(pack_patch_weights(filt.data.data(), g.oc, g.ic, g.kh, g.kw, out->cp, a.kp, -1, a.cv));
         p.kh = p.kw = 1;
         p.a_mode = 0;
         finish_plan(pl, rows, 1, a.kp * 2, out->cp, I.sm_count);
@@ -427,8 +428,57 @@ public:
     }
     if (out->dtype == DT_F32) {
       TPUCB_CHECK(in->dtype == DT_F32, "conv %s: an fp32 convolution needs an fp32 input", op.name.c_str());
-      // (Few-channel layers, i.e. the 3-channel stem, stay on the FMA pipe: expanding their patches into a K-major fp32
-      // matrix for the tensor cores, as the BF16 branch does, measured 1.33 ms against 1.26 ms at batch 64.)
+      if (I.fp32_tensor_cores && g.g == 1 && !g.ins_h && !g.ins_w && g.ic <= 4 && in->cp == 4 && !(g.kh == 1 && g.kw == 1)) {
+        // Image stem (at most 4 channels, NHWC4 input): the patches are expanded into a K-major matrix with four channel
+        // slots per tap (one 16-byte copy per tap; the expansion also writes the remainder part), which is then the
+        // activation operand of the TF32 x 3 product: 49 taps become 7 K blocks per term.
+        conv_kernel_setup_once();
+        std::vector<int32_t> bias_bits(out->cp, 0);
+        for (int o = 0; o < g.oc; ++o) bias_bits[o] = (int32_t)f32_bits(bias[o]);
+        d_bias_ = I.upload(bias_bits);
+        act_ = do_relu_ ? 1 : 0;
+        ConvPlan pl;
+        std::memset(&pl.p, 0, sizeof(pl.p));
+        pl.tf32 = true;
+        pl.use_patch = true;
+        pl.patch_elsize = 4;
+        pl.in = (const int8_t *)in->dev;
+        const int rows = g.n * g.oh * g.ow;
+        PatchArgs &a = pl.patch;
+        a.n = g.n; a.c = g.ic; a.cp = in->cp; a.ih = g.ih; a.iw = g.iw; a.oh = g.oh; a.ow = g.ow;
+        a.kh = g.kh; a.kw = g.kw; a.sh = g.sh; a.sw = g.sw; a.pt = g.pt; a.pl = g.pl; a.dh = g.dh; a.dw = g.dw;
+        a.ins_h = 0; a.ins_w = 0; a.c_first = 0; a.c_count = g.ic; a.wl = in->wl; a.wphys = in->wphys;
+        a.cv = 4;
+        a.kp = g.kh * g.kw * 4;
+        pl.patch_bytes = (size_t)rows * a.kp * 4;
+        pl.patch_buf = (int8_t *)I.dalloc(pl.patch_bytes);
+        pl.split_src = nullptr; // the expansion writes the remainder itself
+        pl.split_hi = nullptr;
+        pl.split_lo = (float *)I.dalloc(pl.patch_bytes);
+        ConvGemmParams &p = pl.p;
+        p.OH = g.oh; p.OW = g.ow; p.sh = p.sw = p.dh = p.dw = 1;
+        p.act = act_;
+        p.bias = d_bias_; p.mult = d_bias_; p.rshift = d_bias_;
+        p.out = (int8_t *)out->dev;
+        p.ldc = out->cp * 4;
+        p.c_off = 0;
+        p.err = I.d_err;
+        p.kh = p.kw = 1;
+        p.a_mode = 0;
+        const int kb = a.kp * 4;
+        const int8_t *d_ph = I.upload(pack_patch_weights(filt.data.data(), g.oc, g.ic, g.kh, g.kw, out->cp, a.kp, 0, 4));
+        const int8_t *d_pl = I.upload(pack_patch_weights(filt.data.data(), g.oc, g.ic, g.kh, g.kw, out->cp, a.kp, 1, 4));
+        finish_plan(pl, rows, 1, kb, out->cp, I.sm_count);
+        encode_matrix_map(&pl.tmA, pl.patch_buf, rows, kb, kb, p.BK);
+        encode_matrix_map(&pl.tmA2, (const int8_t *)pl.split_lo, rows, kb, kb, p.BK);
+        encode_weight_map(&pl.tmB, d_ph, out->cp, 1, kb, p.BK, p.BN);
+        encode_weight_map(&pl.tmB2, d_pl, out->cp, 1, kb, p.BK, p.BN);
+        p.idesc = make_idesc_tf32(128, p.BN);
+        pl.ops = alg_ops;
+        plans_.push_back(pl);
+        alg_bytes = 4.0 * ((double)in->numel() + out->numel() + filt.data.size() + g.oc);
+        return;
+      }
       if (I.fp32_tensor_cores && g.g == 1 && !g.ins_h && !g.ins_w && !in->padded_rows() && in->cp % 8 == 0 &&
           g.pl <= 127 && g.pt <= 127 && (g.kw - 1) * g.dw <= 255 && (g.kh - 1) * g.dh <= 255) {
         // fp32 convolution on the tensor cores as three TF32 products with fp32 accumulation (x w = xh wh + xl wh +
@@ -681,7 +731,7 @@ public:
   int kernel_launches() const override {
     if (f32_ || dw_) return 1;
     int k = (int)stem_plans_.size();
-    for (auto &pl : plans_) k += 1 + (pl.use_patch ? 1 : 0) + (pl.tf32 ? 1 : 0);
+    for (auto &pl : plans_) k += 1 + (pl.use_patch ? 1 : 0) + ((pl.tf32 && pl.split_src) ? 1 : 0);
     return k;
   }
   bool is_tensor_core() const { return !f32_ && !dw_; }

@@ -592,6 +592,7 @@ struct PatchArgs {
   int c_first, c_count; // channel slice (grouped convolution)
   int kp;
   int wl, wphys;        // physical row layout of the input
+  int cv = 0;           // 4: patch_expand_tap_kernel's layout, four channel slots per filter tap (k = tap * 4 + c)
 };
 __global__ void patch_expand_i8_kernel(const int8_t *__restrict__ in, int8_t *__restrict__ out,
                                        PatchArgs a) {
@@ -650,6 +651,49 @@ __global__ void patch_expand_kernel(const T *__restrict__ in, T *__restrict__ ou
       }
     }
     reinterpret_cast<uint4 *>(out)[i] = *reinterpret_cast<const uint4 *>(v);
+  }
+}
+
+// At most 4 input channels (image stems): every filter tap keeps four channel slots in the patch matrix,
+// k = tap * 4 + c, so a thread copies one tap of one output pixel as ONE vector (16 bytes of fp32, 8 bytes of BF16)
+// without any per-element index arithmetic. With `lo` (fp32) the remainder part of the TF32 x 3 product,
+// x - (upper 19 bits of x), is written beside it, which saves the separate split pass over the matrix.
+template <typename T>
+__global__ void patch_expand_tap_kernel(const T *__restrict__ in, T *__restrict__ out, T *__restrict__ lo, PatchArgs a) {
+  const int taps = a.kh * a.kw;
+  const int slots = a.kp / 4; // vectors per row, the last ones are padding
+  const size_t total = (size_t)a.n * a.oh * a.ow * slots;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int tap = (int)(i % slots);
+    const size_t pix = i / slots;
+    const int x = (int)(pix % a.ow);
+    const size_t t = pix / a.ow;
+    const int y = (int)(t % a.oh);
+    const int b = (int)(t / a.oh);
+    T v[4] = {(T)0, (T)0, (T)0, (T)0};
+    if (tap < taps) {
+      const int s = tap % a.kw, r = tap / a.kw;
+      const int yy = y * a.sh - a.pt + r * a.dh, xx = x * a.sw - a.pl + s * a.dw;
+      if (yy >= 0 && yy < a.ih && xx >= 0 && xx < a.iw) {
+        const T *src = in + (((size_t)b * a.ih + yy) * a.wphys + a.wl + xx) * a.cp;
+        if (sizeof(T) == 4) *reinterpret_cast<uint4 *>(v) = __ldg(reinterpret_cast<const uint4 *>(src));
+        else *reinterpret_cast<uint2 *>(v) = __ldg(reinterpret_cast<const uint2 *>(src));
+      }
+    }
+    if (sizeof(T) == 4) {
+      reinterpret_cast<uint4 *>(out)[i] = *reinterpret_cast<const uint4 *>(v);
+      if (lo) {
+        float l[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float f = reinterpret_cast<const float *>(v)[j];
+          l[j] = __fsub_rn(f, __uint_as_float(__float_as_uint(f) & 0xffffe000u));
+        }
+        reinterpret_cast<uint4 *>(lo)[i] = *reinterpret_cast<const uint4 *>(l);
+      }
+    } else {
+      reinterpret_cast<uint2 *>(out)[i] = *reinterpret_cast<const uint2 *>(v);
+    }
   }
 }
 

@@ -152,16 +152,27 @@ def run_calibration(args, rank, world, local_rank):
     m.set_tensor(cal.input_name, data[0])
     for _ in range(3):
         m.invoke()
+    # untimed warm-up of the statistics path on one batch (first launches of its kernels, the device staging buffers of
+    # the pipelined upload), local to the rank
+    warm = ActivationCalibrator(m, lambda: iter(data[:1]), dist=None)
+    for _ in range(3):
+        ws = warm.find_min_max_abs()
+        wh = warm.calc_histograms(ws)
+        warm.find_threshold(wh, ws)
+    del warm
     sampler = ClockSampler(local_rank)
     sampler.start()
     if dist is not None:
         # untimed warm-up of the two collectives the pass uses (the first MAX / SUM all-reduce of a process sets up
         # its NCCL channels), then the barrier that starts the timed region
-        w1 = torch.zeros(2, dtype=torch.float32, device="cuda")
-        w2 = torch.zeros(2, dtype=torch.int64, device="cuda")
+        # (with the shapes of the pass: NCCL prepares per message size; the first [T, 2] MAX cost 28 ms, later ones 0.5)
+        w1 = torch.zeros((len(cal.names), 2), dtype=torch.float32, device="cuda")
+        w2 = torch.zeros((len(cal.names), cal.bin_num), dtype=torch.int64, device="cuda")
+        w3 = torch.zeros(1, dtype=torch.int64, device="cuda")
         for _ in range(3):
             dist.all_reduce(w1, op=dist.ReduceOp.MAX)
             dist.all_reduce(w2, op=dist.ReduceOp.SUM)
+            dist.all_reduce(w3, op=dist.ReduceOp.SUM)
         dist.barrier()
     torch.cuda.synchronize()
     t0 = time.perf_counter()

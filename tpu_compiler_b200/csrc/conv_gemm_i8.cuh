@@ -505,6 +505,7 @@ template <bool RELU>
 __device__ __forceinline__ void epilogue_channels_f32(const ConvGemmParams &p, uint32_t lane_addr, uint8_t *out_ch, bool ch_ok,
                                                       int m0, int half, int halves, float bias, int ncols = 128) {
   const size_t pitch = (size_t)p.ldc;
+  uint8_t *lo_ch = p.out2 ? reinterpret_cast<uint8_t *>(p.out2) + (out_ch - reinterpret_cast<uint8_t *>(p.out)) : nullptr;
   for (int colg = half * 32; colg < ncols; colg += 32 * halves) {
     if (m0 + colg >= p.M_total) break;
     uint32_t acc0[16], acc1[16];
@@ -515,7 +516,11 @@ __device__ __forceinline__ void epilogue_channels_f32(const ConvGemmParams &p, u
     for (int j = 0; j < 32; ++j) {
       float v = __fadd_rn(bits_f32(j < 16 ? acc0[j & 15] : acc1[j & 15]), bias);
       if (RELU) v = v > 0.0f ? v : 0.0f;
-      if (ch_ok && m0 + colg + j < p.M_total) *reinterpret_cast<float *>(out_ch + (size_t)(colg + j) * pitch) = v;
+      if (ch_ok && m0 + colg + j < p.M_total) {
+        *reinterpret_cast<float *>(out_ch + (size_t)(colg + j) * pitch) = v;
+        // the remainder operand of a TF32 x 3 convolution that reads this result, when one does
+        if (lo_ch) *reinterpret_cast<float *>(lo_ch + (size_t)(colg + j) * pitch) = __fsub_rn(v, __uint_as_float(__float_as_uint(v) & 0xffffe000u));
+      }
     }
   }
 }

@@ -55,6 +55,10 @@ struct DevTensor {
   int wl = 0, wphys = 1;
   void *dev = nullptr;
   bool owns = true;
+  // fp32 tensors read by a TF32 x 3 convolution: the remainder part x - (upper 19 bits of x), same layout as `dev`,
+  // and who fills it (0 nobody yet, 1 the producing kernel, 2 the first consuming convolution's split pass)
+  void *lo_dev = nullptr;
+  int lo_by = 0;
   bool padded_rows() const { return wl != 0 || wphys != w; }
   size_t elsize() const { return dtype == 0 ? 1 : (dtype == 1 ? 2 : 4); }
   size_t pixels() const { return (size_t)n * h * wphys; }

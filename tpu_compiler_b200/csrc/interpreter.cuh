@@ -204,6 +204,7 @@ public:
   bool fuse_activations = true; // set before load_module
   bool fp32_tensor_cores = true; // set before load_module: fp32 convolutions as three TF32 products
   void fuse_activation_chains(const std::map<std::string, int> &uses);
+  void link_tf32_remainders();
   cudaGraphExec_t graph_exec = nullptr;
   std::map<std::string, HostWeight> weights;
   std::map<std::string, TensorPtr> tensors;
@@ -497,7 +498,8 @@ public:
         // The tensor core ignores the low 13 mantissa bits of an fp32 operand (measured: results are bit-identical with
         // the upper part materialised or not), so the tensor itself serves as xh and only xl is written.
         pl.split_hi = nullptr;
-        pl.split_lo = (float *)I.dalloc(in->bytes());
+        if (!in->lo_dev) in->lo_dev = I.dalloc(in->bytes()); // shared by every convolution that reads this tensor
+        pl.split_lo = (float *)in->lo_dev;
         pl.split_nvec = in->bytes() / 16;
         ConvGemmParams &p = pl.p;
         p.OH = g.oh; p.OW = g.ow; p.sh = g.sh; p.sw = g.sw; p.pt = g.pt; p.pl = g.pl; p.dh = g.dh; p.dw = g.dw;
@@ -699,6 +701,16 @@ public:
     act_ = 2;
   }
   const TensorPtr &out() const { return out_; }
+  const TensorPtr &in() const { return in_; }
+  // TF32 x 3 plans (not the patch-matrix stem, whose remainder belongs to the patch matrix)
+  bool is_tf32() const { return !plans_.empty() && plans_[0].tf32 && !plans_[0].use_patch; }
+  bool can_write_remainder() const { return !plans_.empty() && plans_[0].tf32; }
+  void set_remainder_out(void *lo) {
+    for (auto &pl : plans_) pl.p.out2 = (int8_t *)lo;
+  }
+  void skip_split() {
+    for (auto &pl : plans_) pl.split_src = nullptr;
+  }
   void invoke(cudaStream_t s) override {
     if (f32_) {
       launch_conv2d_f32((const float *)in_->dev, f32_w_, f32_b_, (float *)out_->dev, g_, in_->cp, out_->cp, do_relu_,
@@ -953,6 +965,7 @@ public:
     } else {
       TPUCB_CHECK(out->dtype == DT_F32 && !is_mul, "eltwise %s: fp32 supports add only", op.name.c_str());
       f_.nin = nin;
+      f_.lo = nullptr;
       f_.do_relu = do_relu_;
       for (int i = 0; i < nin; ++i) {
         f_.in[i] = (const float *)ins[i]->dev;
@@ -961,6 +974,9 @@ public:
       parse_coeff(op, f_.coeff, nin);
     }
   }
+  // fp32 add whose result feeds a TF32 x 3 convolution: also write that convolution's remainder operand
+  bool can_write_remainder() const { return out_->dtype == DT_F32 && !is_mul_; }
+  void set_remainder_out(float *lo) { f_.lo = lo; }
   static void parse_coeff(const ParsedOp &op, float *coeff, int nin) {
     std::string co = op.gets("coeff", "");
     if (co.empty()) return;
@@ -1559,6 +1575,38 @@ inline ParsedOp parse_line(const std::string &line) {
 
 // Replaces every quant(INT8->BF16) -> slope-table activation -> quant(BF16->INT8) chain whose
 // intermediates feed nothing else by one ActChainOp at the first op's position.
+// Who writes the remainder operand (x minus the upper 19 bits of x) of the fp32 tensors that TF32 x 3 convolutions read:
+// the kernel that produces the tensor when it can (an fp32 eltwise add or another TF32 x 3 convolution: 4 more bytes
+// written per value, no separate pass), else the split pass of the FIRST convolution that reads it; later readers of
+// the same tensor reuse the buffer. Ops run in program order, so the first reader always runs before the others.
+inline void Interpreter::link_tf32_remainders() {
+  for (auto &k : kernels) {
+    auto *cv = dynamic_cast<Conv2DOp *>(k.get());
+    if (!cv || !cv->is_tf32()) continue;
+    DevTensor *t = cv->in().get();
+    if (t->lo_by != 0) { // already filled by the producer or by an earlier reader
+      cv->skip_split();
+      continue;
+    }
+    OpKernel *prod = nullptr;
+    for (auto &q : kernels)
+      if (q->result.get() == t) prod = q.get();
+    if (auto *pe = dynamic_cast<EltwiseOp *>(prod)) {
+      if (pe->can_write_remainder()) {
+        pe->set_remainder_out((float *)t->lo_dev);
+        t->lo_by = 1;
+      }
+    } else if (auto *pc = dynamic_cast<Conv2DOp *>(prod)) {
+      if (pc->can_write_remainder()) {
+        pc->set_remainder_out(t->lo_dev);
+        t->lo_by = 1;
+      }
+    }
+    if (t->lo_by == 1) cv->skip_split();
+    else t->lo_by = 2; // this convolution's split pass fills it
+  }
+}
+
 inline void Interpreter::fuse_activation_chains(const std::map<std::string, int> &uses) {
   auto single_use = [&](const std::string &nm) {
     auto it = uses.find(nm);
@@ -1811,6 +1859,7 @@ inline void Interpreter::load_module(const std::string &text) {
     kernels.push_back(std::move(k));
   }
   if (fuse_activations) fuse_activation_chains(uses);
+  link_tf32_remainders();
   for (auto &k : kernels)
     if (!uses.count(k->name) && k->op_type != "input") output_details.push_back({k->name, k->result->numel()});
   TPUCB_CUDA(cudaDeviceSynchronize());

@@ -315,6 +315,7 @@ struct EltwiseF32Args {
   float coeff[4];
   int nin;
   int do_relu;
+  float *lo; // when set: also write x - (upper 19 bits of x), the remainder operand of a TF32 x 3 convolution that reads x
 };
 // One 16-byte vector per thread and step (fp32 tensors are a whole number of them: the channel pitch is a
 // multiple of 4); operand by operand, product and sum rounded separately, as the reference's loop.
@@ -338,6 +339,14 @@ __global__ void eltwise_add_f32_kernel(EltwiseF32Args a, float *__restrict__ out
       acc.w = acc.w < 0 ? 0.0f : acc.w;
     }
     reinterpret_cast<float4 *>(out)[i] = acc;
+    if (a.lo) {
+      float4 l;
+      l.x = __fsub_rn(acc.x, __uint_as_float(__float_as_uint(acc.x) & 0xffffe000u));
+      l.y = __fsub_rn(acc.y, __uint_as_float(__float_as_uint(acc.y) & 0xffffe000u));
+      l.z = __fsub_rn(acc.z, __uint_as_float(__float_as_uint(acc.z) & 0xffffe000u));
+      l.w = __fsub_rn(acc.w, __uint_as_float(__float_as_uint(acc.w) & 0xffffe000u));
+      reinterpret_cast<float4 *>(a.lo)[i] = l;
+    }
   }
 }
 

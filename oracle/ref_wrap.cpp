@@ -6,6 +6,7 @@
 #include "tpuc/QuantizationArithmetic.h"
 #include "tpuc/Interpreter/cpu/lut_func.hpp"
 #include <string>
+#include <vector>
 
 extern "C" {
 int ref_qdm_i32(int32_t v, uint32_t rshift, uint32_t multiplier) {
@@ -45,5 +46,31 @@ void ref_lut_bf16_mantissa(float *in, float *out, int size, float *exp_table, fl
 }
 void ref_lut_bf16_mantissa_log(float *in, float *out, int size, float *exp_table, float *mant) {
   bf16_lut_mantissa(in, out, size, exp_table, mant, "log");
+}
+// Weight quantisers the auto-tuner re-runs per candidate threshold (QuantizationArithmetic.cpp:630-818).
+void ref_quantize_weight_int8_multiplier(float *filter, float *bias, int64_t oc, int64_t isz,
+                                         float threshold_y, float threshold_x, float *new_filter,
+                                         float *new_bias, float *rshift, float *multiplier) {
+  std::vector<float> none;
+  mlir::quantizeWeightInt8Multiplier(filter, bias, oc, isz, threshold_y, threshold_x, new_filter,
+                                     new_bias, rshift, multiplier, none);
+}
+void ref_quantize_weight_int8_fc(float *filter, float *bias, int64_t n, int64_t k, float threshold_y,
+                                 float threshold_x, float *new_filter, float *new_bias,
+                                 float *rshift, float *multiplier) {
+  mlir::quantizeWeightInt8ForFC(filter, bias, 1, n, k, threshold_y, threshold_x, new_filter, new_bias,
+                                rshift, multiplier);
+}
+// The (rshift, int8 multipliers) of quantizeInt8RescaleNoWeightOps (QuantizeInt8.cpp:798-815).
+int ref_rescale_no_weight(const float *qscale, int n, float *multipliers) {
+  float max_qscale = 0.0f;
+  for (int i = 0; i < n; ++i) {
+    float p = qscale[i] > 0.0f ? qscale[i] : 0.0f - qscale[i];
+    if (max_qscale < p) max_qscale = p;
+  }
+  int8_t rshift = mlir::findRShiftAndMultiplierFromQScale(max_qscale);
+  for (int i = 0; i < n; ++i)
+    multipliers[i] = (float)mlir::findMultiplierI8FromQScaleAndRShift(qscale[i], rshift);
+  return rshift;
 }
 }

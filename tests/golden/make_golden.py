@@ -134,6 +134,7 @@ def main():
     np.savez_compressed(os.path.join(HERE, "kld.npz"), hist=np.stack(hists), width=np.array(widths, np.float32),
                         threshold=np.array(thr, np.float32))
     make_softmax_bf16(ref)
+    make_weight_quant(ref)
     print("golden vectors written to", HERE)
 
 
@@ -176,5 +177,48 @@ def make_softmax_bf16(ref):
     np.savez_compressed(os.path.join(HERE, "softmax_bf16.npz"), **out)
 
 
+def make_weight_quant(ref):
+    """Weight quantisers and the no-weight rescale of the INT8 quantisation pass, as the reference's
+    own code computes them, on seeded inputs (also run alone: make_golden.py weight_quant)."""
+    rng = np.random.default_rng(20240611)
+    out = {}
+    cases = [(8, 27, 2.5, 1.0, 0.05), (16, 64, 0.8, 3.1, 0.3), (5, 9, 6.0, 6.0, 0.0), (12, 144, 0.02, 4.0, 2.0),
+             (6, 32, 30.0, 0.1, 0.01), (4, 16, 1.0, 1.0, 1e4)]
+    for ci, (oc, isz, ty, tx, bstd) in enumerate(cases):
+        w = rng.normal(0, 0.2, (oc, isz)).astype(np.float32)
+        w[0] *= 40.0  # a channel whose qscale passes 1
+        b = rng.normal(0, bstd, oc).astype(np.float32) if bstd else None
+        nf, nb = np.zeros_like(w), np.zeros(oc, np.float32)
+        r, m = np.zeros(oc, np.float32), np.zeros(oc, np.float32)
+        ref.ref_quantize_weight_int8_multiplier(p(w), p(b) if b is not None else None, oc, isz, C.c_float(ty),
+                                                C.c_float(tx), p(nf), p(nb) if b is not None else None, p(r), p(m))
+        out.update({"conv%d_w" % ci: w, "conv%d_b" % ci: b if b is not None else np.zeros(0, np.float32),
+                    "conv%d_t" % ci: np.array([ty, tx], np.float32), "conv%d_nf" % ci: nf, "conv%d_nb" % ci: nb,
+                    "conv%d_r" % ci: r, "conv%d_m" % ci: m})
+    for ci, (n, k, ty, tx, bstd) in enumerate([(10, 64, 9.0, 4.0, 0.05), (7, 33, 0.5, 2.0, 0.0), (12, 20, 3.0, 3.0, 50.0)]):
+        w = rng.normal(0, 0.1, (n, k)).astype(np.float32)
+        b = rng.normal(0, bstd, n).astype(np.float32) if bstd else None
+        nf, nb = np.zeros_like(w), np.zeros(n, np.float32)
+        r, m = np.zeros(1, np.float32), np.zeros(1, np.float32)
+        ref.ref_quantize_weight_int8_fc(p(w), p(b) if b is not None else None, n, k, C.c_float(ty), C.c_float(tx),
+                                        p(nf), p(nb) if b is not None else None, p(r), p(m))
+        out.update({"fc%d_w" % ci: w, "fc%d_b" % ci: b if b is not None else np.zeros(0, np.float32),
+                    "fc%d_t" % ci: np.array([ty, tx], np.float32), "fc%d_nf" % ci: nf, "fc%d_nb" % ci: nb,
+                    "fc%d_r" % ci: r, "fc%d_m" % ci: m})
+    qs, rr, mm = [], [], []
+    for _ in range(400):
+        n = int(rng.integers(1, 4))
+        q = np.zeros(3, np.float32)
+        q[:n] = np.exp(rng.uniform(np.log(1e-4), np.log(60.0), n)).astype(np.float32)
+        mult = np.zeros(3, np.float32)
+        r = ref.ref_rescale_no_weight(p(q), n, p(mult))
+        qs.append(q), rr.append(r), mm.append(mult)
+    out.update({"rescale_qscale": np.stack(qs), "rescale_rshift": np.array(rr, np.int32), "rescale_mult": np.stack(mm)})
+    np.savez_compressed(os.path.join(HERE, "weight_quant.npz"), **out)
+
+
 if __name__ == "__main__":
-    main()
+    if len(sys.argv) > 1 and sys.argv[1] == "weight_quant":
+        make_weight_quant(oracle.ref())
+    else:
+        main()

@@ -210,6 +210,57 @@ def run_calibration(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
+def run_tuner(args, local_rank):
+    """--workload tuner: the threshold auto-tuner (kld_calibrator.py:113-201) on the fp32 ResNet-50 over
+    `--tune-images` synthetic images with three candidate tables (KLD thresholds at 2048 / 1024 / 512 bins from the
+    calibrator on the same images). Wall clock of SimpleTuner.run() through the public API on one GPU: the loop is
+    serial in the ops, so more GPUs would only run replicas. Candidate evaluations per second, plus how many INT8 op
+    executions the run needed against the count of the reference's loop (every candidate re-runs the graph prefix)."""
+    from tpu_compiler_b200 import graphs, module
+    from tpu_compiler_b200 import quantize as Q
+    from tpu_compiler_b200.calibration import ActivationCalibrator
+    from tpu_compiler_b200.tuner import SimpleTuner
+    n = args.tune_images
+    model = graphs.resnet50_fp32(batch=n)
+    rng = np.random.default_rng(7100)
+    images = np.clip(rng.standard_normal((n, 3, 224, 224), dtype=np.float32), -3, 3)
+    m = module(local_rank)
+    m.load_text(model.text, model.weights)
+    tables, stats = {}, None
+    for bins in (2048, 1024, 512):
+        cal = ActivationCalibrator(m, lambda: iter([images]), histogram_bin_num=bins)
+        thr, stats = cal.run()
+        tables["bins%d" % bins] = {k: float(v) for k, v in thr.items()}
+    m.close()
+    ops = Q.parse_text(model.text)
+    tunable = [o["name"] for o in ops if o["type"] not in ("input", "softmax", "reshape")]
+    for t in tables.values():
+        t.pop("prob", None)
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    t0 = time.perf_counter()
+    tuner = SimpleTuner(model.text, model.weights, tables, stats, images, device=local_rank)
+    t1 = time.perf_counter()
+    best = tuner.run()
+    t2 = time.perf_counter()
+    clocks = sampler.stop()
+    evals = sum(len(d) for d in tuner.distances.values())
+    # the reference's loop runs, for the k-th op and each candidate, the k quantised ops of the prefix
+    index = {o["name"]: i for i, o in enumerate(o for o in ops if o["type"] != "input")}
+    ref_ops = sum((index[nm] + 1) * len(tuner.distances[nm]) for nm in tuner.distances)
+    moved = sum(1 for nm in tunable if best[nm] != tables["bins2048"][nm])
+    tuner.close()
+    print(json.dumps({
+        "metric": "auto-tuner candidate evaluations/sec (fp32 ResNet-50, %d images)" % n, "value": evals / (t2 - t1),
+        "unit": "evaluations/s", "n_gpus": 1, "steps": evals, "warmup": 0, "ms_per_step": (t2 - t1) / max(evals, 1) * 1e3,
+        "higher_is_better": True, "scaling": "replicas only", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+        "config": {"workload": "tuner: fp32 ResNet-50, %d images N(0,1) clipped to [-3,3], %d ops x 3 candidate tables" %
+                               (n, len(tuner.distances))},
+        "seconds": {"fp32_reference_and_store": t1 - t0, "tuning_loop": t2 - t1},
+        "int8_op_executions": tuner.ops_run, "int8_op_executions_reference_loop": ref_ops,
+        "candidate_modules_launched": tuner.launches, "thresholds_changed": moved, "clocks": clocks}), flush=True)
+
+
 # graph builder name in tpu_compiler_b200.graphs, input resolution, input value range, default batch
 WORKLOADS = {
     "resnet50": {"builder": "resnet50_int8", "res": 224, "lo": -1.0, "batch": 256,
@@ -288,13 +339,18 @@ def main():
     ap.add_argument("--cal-images", type=int, default=512, help="calibration workload: images per GPU")
     ap.add_argument("--cal-batch", type=int, default=64, help="calibration workload: images per batch (64 in the "
                     "configuration; smaller values are for profiler captures)")
-    ap.add_argument("--workload", default="resnet50", choices=sorted(WORKLOADS) + ["conv_sweep", "calibration"],
+    ap.add_argument("--tune-images", type=int, default=16, help="tuner workload: images held on the GPU")
+    ap.add_argument("--workload", default="resnet50", choices=sorted(WORKLOADS) + ["conv_sweep", "calibration", "tuner"],
                     help="resnet50 is the headline configuration; the others are the secondary graphs "
                          "(their lines carry no cpu_baseline)")
     args = ap.parse_args()
     if args.workload == "conv_sweep":
         if args.impl == "ours" and int(os.environ.get("RANK", "0")) == 0:
             run_conv_sweep(args, int(os.environ.get("LOCAL_RANK", "0")))
+        return
+    if args.workload == "tuner":
+        if args.impl == "ours" and int(os.environ.get("RANK", "0")) == 0:
+            run_tuner(args, int(os.environ.get("LOCAL_RANK", "0")))
         return
     if args.workload == "calibration":
         if args.impl == "ours":

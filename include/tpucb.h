@@ -136,6 +136,23 @@ int tpucb_calib_hist(tpucb_interp *it, const char *name, float abs_max, int bins
 int tpucb_calib_kld(tpucb_interp *it, const int64_t *d_hist, const float *widths, int count,
                     int bins, float *thresholds);
 
+/* ---- threshold auto-tuner (python/cvi_toolkit/calibration/kld_calibrator.py:113-201) ------ */
+
+/* Device-to-device copy of one tensor between two interpreters on the same GPU; the two
+ * tensors must agree in type, shape and device layout. It stands in for the get_tensor ->
+ * set_data round trip through numpy with which the reference's tuner would move an activation
+ * between two loaded modules (bindings/python/pytuner.cpp:252-288). Returns after the copy. */
+int tpucb_interp_copy_tensor(tpucb_interp *dst, const char *dst_name, tpucb_interp *src,
+                             const char *src_name);
+/* The two norms of SimpleTuner.run (kld_calibrator.py:184-196) for every image of the batch,
+ * with both activations left on the device: sums[2i] = sum over image i of
+ * (ref - scale * tgt)^2, sums[2i+1] = sum |ref| (host doubles out, `images` = the tensors'
+ * batch). ref is an fp32 tensor of `ref`; tgt a tensor of the same shape of `tgt` (INT8, BF16
+ * or fp32; pass scale = threshold / 127 for INT8 and 1 otherwise). The difference is formed in
+ * fp32 as numpy forms it, the sums in double. */
+int tpucb_tuner_distance(tpucb_interp *ref, const char *ref_name, tpucb_interp *tgt,
+                         const char *tgt_name, float scale, double *sums, int images);
+
 /* Allocation-free variant of tpucb_calib_kld. It has no counterpart in the reference; it exists
  * for hosts that must not allocate device memory while they work: a calibration service that
  * sized its device memory once at start-up (this backend keeps every activation of the module

@@ -54,6 +54,8 @@ def _declare(lib):
         "tpucb_calib_minmax": [vp, cp, vp],
         "tpucb_calib_hist": [vp, cp, C.c_float, C.c_int, vp],
         "tpucb_calib_kld": [vp, vp, fp, C.c_int, C.c_int, fp],
+        "tpucb_interp_copy_tensor": [vp, cp, vp, cp],
+        "tpucb_tuner_distance": [vp, cp, vp, cp, C.c_float, C.POINTER(C.c_double), C.c_int],
         "tpucb_calib_kld_static": [C.c_int, vp, vp, fp, C.c_int, C.c_int, fp],
     }
     for name, args in sigs.items():

@@ -2,6 +2,7 @@
 //   minmax_f32_kernel  find_min_max_abs          python/cvi_toolkit/calibration/kld_calibrator.py:269-296
 //   hist_f32_kernel    BaseKldCalibrator.histogram                       kld_calibrator.py:31-43
 //   kld_kernel         kl_diversity_hist / kl_calc_thread   bindings/python/kld/calibration_math.cpp:169-223, 283-344
+//   tuner_distance_kernel  the two norms of SimpleTuner.run                  kld_calibrator.py:184-196
 // Tensors are fp32 NHWC with channel pitch cp; padded lanes are skipped.
 #pragma once
 #include "common.cuh"
@@ -172,6 +173,77 @@ __global__ void kld_kernel(const long long *__restrict__ hists, int N, float *__
     float kl = 0.0f;
     for (int j = 0; j < i; ++j) kl = (float)((double)kl + term[j]);
     kl_out[blockIdx.x] = kl;
+  }
+}
+
+// Geometry of one NHWC tensor for kernels that walk two tensors of the same logical shape but different
+// physical layouts (channel pitch, zero-padded rows).
+struct DistGeom {
+  const void *dev;
+  int cp, wl, wphys;
+};
+
+// Per image i: sums[2i] += sum (ref - scale * tgt)^2, sums[2i+1] += sum |ref| over the image's real elements
+// (the terms of `np.linalg.norm(diff) / np.linalg.norm(ref, ord=1)`, kld_calibrator.py:189-195). ref is fp32;
+// tgt is int8 (TGT = 0), bf16 (1) or fp32 (2). The difference is formed in fp32 as numpy forms it, the sums
+// in double. One thread handles four channels of one pixel per step; grid = (blocks per image, images).
+template <int TGT>
+__global__ void tuner_distance_kernel(DistGeom ref, DistGeom tgt, int c, int h, int w, float scale, double *sums) {
+  const int img = blockIdx.y;
+  const int c4 = (c + 3) >> 2;
+  const size_t quads = (size_t)h * w * c4;
+  double d2 = 0.0, s1 = 0.0;
+  for (size_t q = blockIdx.x * (size_t)blockDim.x + threadIdx.x; q < quads; q += (size_t)gridDim.x * blockDim.x) {
+    const int cq = (int)(q % c4);
+    const size_t pix = q / c4;
+    const int x = (int)(pix % w), y = (int)(pix / w);
+    const size_t ro = (((size_t)img * h + y) * ref.wphys + ref.wl + x) * ref.cp + cq * 4;
+    const size_t to = (((size_t)img * h + y) * tgt.wphys + tgt.wl + x) * tgt.cp + cq * 4;
+    const float4 r4 = __ldg(reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(ref.dev) + ro));
+    float t[4];
+    if (TGT == 0) {
+      const int wd = __ldg(reinterpret_cast<const int *>(reinterpret_cast<const signed char *>(tgt.dev) + to));
+      t[0] = (float)(signed char)(wd & 0xff);
+      t[1] = (float)(signed char)((wd >> 8) & 0xff);
+      t[2] = (float)(signed char)((wd >> 16) & 0xff);
+      t[3] = (float)(signed char)((wd >> 24) & 0xff);
+    } else if (TGT == 1) {
+      const uint2 wd = __ldg(reinterpret_cast<const uint2 *>(reinterpret_cast<const unsigned short *>(tgt.dev) + to));
+      t[0] = __uint_as_float(wd.x << 16);
+      t[1] = __uint_as_float(wd.x & 0xffff0000u);
+      t[2] = __uint_as_float(wd.y << 16);
+      t[3] = __uint_as_float(wd.y & 0xffff0000u);
+    } else {
+      const float4 t4 = __ldg(reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(tgt.dev) + to));
+      t[0] = t4.x; t[1] = t4.y; t[2] = t4.z; t[3] = t4.w;
+    }
+    const float r[4] = {r4.x, r4.y, r4.z, r4.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (cq * 4 + j < c) {
+        const float diff = __fsub_rn(r[j], __fmul_rn(t[j], scale));
+        d2 += (double)diff * (double)diff;
+        s1 += (double)fabsf(r[j]);
+      }
+    }
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    d2 += __shfl_xor_sync(0xffffffffu, d2, o);
+    s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+  }
+  __shared__ double sd[32], ss[32];
+  if ((threadIdx.x & 31) == 0) {
+    sd[threadIdx.x >> 5] = d2;
+    ss[threadIdx.x >> 5] = s1;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int i = 1; i < (int)(blockDim.x >> 5); ++i) {
+      d2 += sd[i];
+      s1 += ss[i];
+    }
+    atomicAdd(sums + 2 * img, d2);
+    atomicAdd(sums + 2 * img + 1, s1);
   }
 }
 

@@ -111,6 +111,7 @@ public:
   }
 
   void bind() { TPUCB_CUDA(cudaSetDevice(device_)); }
+  int device() const { return device_; }
 
   // ---- device memory owned by the interpreter
   void *dalloc(size_t bytes) {

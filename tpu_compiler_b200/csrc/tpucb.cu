@@ -12,7 +12,12 @@ using namespace tpucb;
 
 struct tpucb_interp {
   Interpreter impl;
+  double *tuner_sums = nullptr; // device scratch of tpucb_tuner_distance, grown on demand
+  int tuner_sums_cap = 0;
   explicit tpucb_interp(int device) : impl(device) {}
+  ~tpucb_interp() {
+    if (tuner_sums) cudaFree(tuner_sums);
+  }
 };
 
 static thread_local std::string g_last_error;
@@ -271,6 +276,65 @@ int tpucb_interp_tensor_device(tpucb_interp *it, const char *name, void **dev, s
   if (channels) *channels = t->c;
   if (channel_pitch) *channel_pitch = t->cp;
   if (dtype) *dtype = t->dtype;
+  TPUCB_API_END
+}
+
+int tpucb_interp_copy_tensor(tpucb_interp *dst, const char *dst_name, tpucb_interp *src, const char *src_name) {
+  TPUCB_API_BEGIN
+  TPUCB_CHECK(dst && src && dst_name && src_name, "tpucb_interp_copy_tensor: bad argument");
+  Interpreter &D = dst->impl, &S = src->impl;
+  TPUCB_CHECK(D.device() == S.device(), "tpucb_interp_copy_tensor: the two interpreters live on different devices");
+  auto d = D.tensor(dst_name);
+  auto s = S.tensor(src_name);
+  TPUCB_CHECK(d->dtype == s->dtype && d->n == s->n && d->c == s->c && d->h == s->h && d->w == s->w && d->cp == s->cp &&
+                  d->wl == s->wl && d->wphys == s->wphys,
+              "tpucb_interp_copy_tensor: %s and %s differ in type, shape or device layout", dst_name, src_name);
+  D.bind();
+  TPUCB_CUDA(cudaStreamSynchronize(S.stream)); // the source's producers have finished
+  TPUCB_CUDA(cudaMemcpyAsync(d->dev, s->dev, s->bytes(), cudaMemcpyDeviceToDevice, D.stream));
+  TPUCB_CUDA(cudaStreamSynchronize(D.stream)); // the source may be overwritten once this returns
+  TPUCB_API_END
+}
+
+int tpucb_tuner_distance(tpucb_interp *ref, const char *ref_name, tpucb_interp *tgt, const char *tgt_name, float scale,
+                         double *sums, int images) {
+  TPUCB_API_BEGIN
+  TPUCB_CHECK(ref && tgt && ref_name && tgt_name && sums, "tpucb_tuner_distance: bad argument");
+  Interpreter &R = ref->impl, &T = tgt->impl;
+  TPUCB_CHECK(R.device() == T.device(), "tpucb_tuner_distance: the two interpreters live on different devices");
+  auto r = R.tensor(ref_name);
+  auto t = T.tensor(tgt_name);
+  TPUCB_CHECK(r->dtype == DT_F32, "tpucb_tuner_distance: reference tensor %s is not fp32", ref_name);
+  TPUCB_CHECK(r->n == t->n && r->c == t->c && r->h == t->h && r->w == t->w,
+              "tpucb_tuner_distance: %s and %s differ in shape", ref_name, tgt_name);
+  TPUCB_CHECK(images == r->n, "tpucb_tuner_distance: %d images asked, the tensors hold %d", images, r->n);
+  TPUCB_CHECK(r->cp % 4 == 0 && t->cp % 4 == 0, "tpucb_tuner_distance: channel pitch is not a multiple of 4");
+  T.bind();
+  if (tgt->tuner_sums_cap < images) {
+    if (tgt->tuner_sums) TPUCB_CUDA(cudaFree(tgt->tuner_sums));
+    tgt->tuner_sums = nullptr;
+    tgt->tuner_sums_cap = 0;
+    TPUCB_CUDA(cudaMalloc(&tgt->tuner_sums, sizeof(double) * 2 * images));
+    tgt->tuner_sums_cap = images;
+  }
+  TPUCB_CUDA(cudaStreamSynchronize(R.stream)); // the reference activations are complete
+  TPUCB_CUDA(cudaMemsetAsync(tgt->tuner_sums, 0, sizeof(double) * 2 * images, T.stream));
+  DistGeom rg{r->dev, r->cp, r->wl, r->wphys}, tg{t->dev, t->cp, t->wl, t->wphys};
+  const size_t quads = (size_t)r->h * r->w * ((r->c + 3) / 4);
+  int bx = (int)((quads + 1023) / 1024); // four steps per thread at least, when there is that much work
+  const int per_image_cap = (T.sm_count * 8 + images - 1) / images;
+  if (bx > per_image_cap) bx = per_image_cap;
+  if (bx < 1) bx = 1;
+  dim3 grid(bx, images);
+  if (t->dtype == DT_I8)
+    tuner_distance_kernel<0><<<grid, 256, 0, T.stream>>>(rg, tg, r->c, r->h, r->w, scale, tgt->tuner_sums);
+  else if (t->dtype == DT_BF16)
+    tuner_distance_kernel<1><<<grid, 256, 0, T.stream>>>(rg, tg, r->c, r->h, r->w, scale, tgt->tuner_sums);
+  else
+    tuner_distance_kernel<2><<<grid, 256, 0, T.stream>>>(rg, tg, r->c, r->h, r->w, scale, tgt->tuner_sums);
+  TPUCB_CUDA(cudaGetLastError());
+  TPUCB_CUDA(cudaMemcpyAsync(sums, tgt->tuner_sums, sizeof(double) * 2 * images, cudaMemcpyDeviceToHost, T.stream));
+  TPUCB_CUDA(cudaStreamSynchronize(T.stream));
   TPUCB_API_END
 }
 

@@ -189,3 +189,19 @@ class module:
         check(self._lib.tpucb_interp_tensor_device(self._h, name.encode(), C.byref(dev), C.byref(nbytes), C.byref(c),
                                                    C.byref(cp), C.byref(dt)))
         return {"ptr": dev.value, "bytes": nbytes.value, "channels": c.value, "pitch": cp.value, "dtype": dt.value}
+
+    # ---- tuner helpers ---------------------------------------------------------------
+    def copy_tensor_from(self, name, other, other_name):
+        """Device-to-device copy of ``other_name`` of module ``other`` into this module's ``name``
+        (same GPU, same type, shape and device layout)."""
+        check(self._lib.tpucb_interp_copy_tensor(self._h, name.encode(), other._h, other_name.encode()))
+
+    def tuner_distance(self, name, ref, ref_name, scale):
+        """Per image of the batch: (sum (ref - scale * this)^2, sum |ref|) between this module's
+        ``name`` and the fp32 tensor ``ref_name`` of module ``ref``, both left on the device.
+        Returns a float64 array [images, 2]."""
+        n = self.get_tensor_shape(name)[0]
+        out = np.zeros((n, 2), np.float64)
+        check(self._lib.tpucb_tuner_distance(ref._h, ref_name.encode(), self._h, name.encode(), float(scale),
+                                             out.ctypes.data_as(C.POINTER(C.c_double)), n))
+        return out

@@ -109,7 +109,7 @@ def import_thresholds(ops, table):
             if op["type"] not in BACKWARD_OPS or op["name"] not in thr:
                 continue
             p = producer(op)
-            if p is None or p["type"] == "input" or p["name"] not in thr:
+            if p is None or p["name"] not in thr:
                 continue
             if thr[p["name"]] == thr[op["name"]] or uses.get(p["name"], 0) != 1:
                 continue

@@ -221,6 +221,23 @@ def _bias_factor(threshold_y, rshift, multiplier):
     return 0.0 if multiplier == 0 else ratio * float(1 << (int(rshift) + 31)) / float(multiplier)
 
 
+def quantize_multiplier_qdm_array(qscale):
+    """quantize_multiplier_qdm over a float64 array: (multipliers int64, rshifts int64)."""
+    q = np.asarray(qscale, np.float64).copy()
+    q[q >= 1] = 0.999999
+    m, shift = np.frexp(q)
+    shift = shift.astype(np.int64)
+    q_fixed = np.floor(m * float(1 << 31) + 0.5).astype(np.int64)
+    over = q_fixed == (1 << 31)
+    q_fixed[over] //= 2
+    shift[over] += 1
+    small = (shift < -31) | (q == 0.0)
+    shift[small] = 0
+    q_fixed[small] = 0
+    assert (shift <= 0).all()
+    return q_fixed, -shift
+
+
 def quantize_conv_weights(filt, bias, threshold_y, threshold_x):
     """quantizeWeightInt8Multiplier (:741-818) without a filter threshold. ``filt`` is
     [oc, ...] fp32, ``bias`` [oc] fp32 or None. Returns (new_filter, new_bias, rshift, multiplier)
@@ -229,27 +246,27 @@ def quantize_conv_weights(filt, bias, threshold_y, threshold_x):
     oc = filt.shape[0]
     flat = filt.reshape(oc, -1)
     max_filter = np.abs(flat).max(axis=1).astype(f32)
-    qs_f = qscale_for_filter(max_filter, threshold_y, threshold_x)
-    qs_b = qscale_for_bias_i32(np.abs(np.asarray(bias, f32)), threshold_y) if bias is not None else None
-    rshift = np.zeros(oc, f32)
-    mult = np.zeros(oc, f32)
-    new_f = np.empty_like(flat)
-    new_b = np.zeros(oc, f32) if bias is not None else None
-    for c in range(oc):
-        q = qs_f[c]
-        if q >= 1:
-            q = 0.999999
-        if qs_b is not None and qs_b[c] > q and not qs_b[c] >= 1:
-            q = qs_b[c]
-        m, r = quantize_multiplier_qdm(q)
-        mult[c] = f32(m)  # stored in a float tensor: rounded to 24 bits
-        rshift[c] = f32(r)
-        m_used = int(mult[c])
-        fac = _filter_factor(threshold_y, threshold_x, r, m_used)
-        new_f[c] = _saturate_int8((flat[c].astype(np.float64) * fac).astype(f32))
-        if bias is not None:
-            bf = _bias_factor(threshold_y, r, m_used)
-            new_b[c] = _saturate_int32(np.asarray(float(f32(bias[c])) * bf, np.float64).astype(f32).reshape(1))[0]
+    q = qscale_for_filter(max_filter, threshold_y, threshold_x)
+    q[q >= 1] = 0.999999
+    if bias is not None:
+        bias = np.asarray(bias, f32).reshape(oc)
+        qb = qscale_for_bias_i32(np.abs(bias), threshold_y)
+        take = (qb > q) & ~(qb >= 1)  # a bias scale of 1 or more is ignored ("prevent for auto tuning")
+        q = np.where(take, qb, q)
+    m, r = quantize_multiplier_qdm_array(q)
+    mult = m.astype(f32)  # stored in a float tensor: rounded to 24 bits
+    rshift = r.astype(f32)
+    m_used = mult.astype(np.float64)  # what the weight scaling then reads back
+    live = m_used != 0
+    safe = np.where(live, m_used, 1.0)
+    # quantizeFilterRShiftAndMultiplier (:442-453): (double)(tx / ty as floats) * 2^(rshift+31) / multiplier
+    fac = np.where(live, np.ldexp(float(f32(threshold_x) / f32(threshold_y)), (r + 31).astype(np.int32)) / safe, 0.0)
+    new_f = _saturate_int8((flat.astype(np.float64) * fac[:, None]).astype(f32)).astype(f32)
+    new_b = None
+    if bias is not None:
+        # quantizeBiasRShiftAndMultiplier (:459-478)
+        bfac = np.where(live, np.ldexp(float(f32(128.0) / f32(threshold_y)), (r + 31).astype(np.int32)) / safe, 0.0)
+        new_b = _saturate_int32((bias.astype(np.float64) * bfac).astype(f32)).astype(f32)
     return new_f.reshape(filt.shape), new_b, rshift, mult
 
 

@@ -130,6 +130,16 @@ int tpucb_calib_minmax(tpucb_interp *it, const char *name, float *d_stats);
 /* histogram (kld_calibrator.py:31-43): adds the tensor's |x| != 0 values to a device
  * histogram of `bins` int64 counts with width abs_max / (bins - 1). */
 int tpucb_calib_hist(tpucb_interp *it, const char *name, float abs_max, int bins, int64_t *d_hist);
+/* The same two with every batch's activations kept on the device between the passes, so that the
+ * histogram pass needs no second forward (the reference re-runs the model per image in
+ * calc_thresholds, kld_calibrator.py:298-336; a B200 holds the fp32 activations of hundreds of
+ * images). tpucb_calib_minmax_keep also writes the tensor's real lanes to d_keep, a 16-byte aligned
+ * device buffer of the tensor's storage size (tpucb_interp_tensor_device gives the bytes), in the
+ * pass that reads them; tpucb_calib_hist_kept takes its values from such a copy (`name` gives the
+ * geometry). Work is ordered on the interpreter's stream. */
+int tpucb_calib_minmax_keep(tpucb_interp *it, const char *name, float *d_stats, float *d_keep);
+int tpucb_calib_hist_kept(tpucb_interp *it, const char *name, const float *d_kept, float abs_max,
+                          int bins, int64_t *d_hist);
 /* kl_diversity_hist (calibration_math.cpp:283-344) for `count` histograms at once:
  * d_hist [count][bins] int64 device counts, widths [count] host floats, thresholds
  * [count] host floats out. */

@@ -139,6 +139,36 @@ def test_resnet50_fp32_calibration_runs_and_matches_cpu_rule_on_sampled_tensors(
     m.close()
 
 
+def test_kept_activations_give_the_same_histograms():
+    """Pass 2 from the device cache of pass 1 (all batches, some batches, none) reads the same bits."""
+    from tpu_compiler_b200 import module
+    from tpu_compiler_b200.calibration import ActivationCalibrator
+    model = small_fp32_model(4)
+    rng = np.random.default_rng(78)
+    data = [np.clip(rng.normal(0, 1, (4, 3, 24, 24)), -3, 3).astype(np.float32) for _ in range(3)]
+    m = module(0)
+    m.load_text(model.text, model.weights)
+    calls = []
+
+    def batches():
+        calls.append(0)
+        return iter(data)
+
+    base = ActivationCalibrator(m, batches, keep_activations_gb=0)
+    thr0, _ = base.run()
+    h0 = base.histograms.cpu().numpy()
+    assert len(calls) == 2   # nothing kept: the images are asked for twice
+    per_batch, _ = ActivationCalibrator(m, batches)._keep_plan()
+    for gb, expect_calls in ((None, 1), (1.5 * per_batch / 2 ** 30, 2)):
+        del calls[:]
+        cal = ActivationCalibrator(m, batches, keep_activations_gb=gb)
+        thr, _ = cal.run()
+        assert len(calls) == expect_calls
+        assert np.array_equal(cal.histograms.cpu().numpy(), h0)
+        assert {k: float(v) for k, v in thr.items()} == {k: float(v) for k, v in thr0.items()}
+    m.close()
+
+
 def _calib_rank(rank, world, port, q):
     import os
     import torch

@@ -8,6 +8,13 @@ and all three statistics run as CUDA kernels; the tensors never leave the device
 ``torch.distributed`` initialised, every rank calibrates on its own shard of the images and
 the statistics are combined with one all-reduce(MAX) after pass 1 (abs-max, max and -min packed
 into one buffer) and one all-reduce(SUM) of the int64 histograms after pass 2.
+
+The reference runs the model a second time for the histograms (calc_thresholds,
+kld_calibrator.py:298-336) because it cannot keep every activation of every image. A 180 GB GPU
+can: pass 1 writes each batch's fp32 activations to a device cache in the same kernel that takes
+their min / max (``keep_activations_gb``, default: up to 60% of the memory free at that time), and
+pass 2 reads the histograms of the cached batches from there -- no upload, no second forward.
+Batches beyond the budget are recomputed as before. The values read are the same bits either way.
 """
 import ctypes as C
 import datetime
@@ -19,7 +26,7 @@ from ._lib import check, lib
 
 
 class ActivationCalibrator:
-    def __init__(self, model, batches, histogram_bin_num=2048, input_name=None, dist=None):
+    def __init__(self, model, batches, histogram_bin_num=2048, input_name=None, dist=None, keep_activations_gb=None):
         """model: a loaded ``tpu_compiler_b200.module`` of an fp32 graph; batches: a callable
         returning an iterator over this rank's input batches (float32 arrays of the input's
         shape) -- it is called twice, once per pass."""
@@ -32,6 +39,10 @@ class ActivationCalibrator:
         self.device = torch.device("cuda", model._device) if model._device is not None else torch.device("cpu")
         self._lib = lib() if model._device is not None else None
         self.num_samples = 0
+        self.keep_activations_gb = keep_activations_gb   # None: 60% of the free device memory; 0: keep nothing
+        self._kept = []          # per cached batch: (uint8 device buffer, images)
+        self._kept_offsets = None
+        self._local_images = -1   # images this rank saw in pass 1
         self._pinned = None
         self._pinned_numel = 0
         self._pinned_next = 0
@@ -48,15 +59,48 @@ class ActivationCalibrator:
         stats[:, 1] = float("-inf")
         torch.cuda.synchronize(self.device)
         n_img = 0
+        self._kept = []
+        per_batch, budget = self._keep_plan()
         for batch in self.batches():
             self._upload(batch)
             self.model.launch()
+            keep = None
+            if per_batch and (len(self._kept) + 1) * per_batch <= budget:
+                try:
+                    keep = torch.empty(per_batch, dtype=torch.uint8, device=self.device)
+                except torch.OutOfMemoryError:
+                    budget = 0
             for t, name in enumerate(self.names):
-                check(self._lib.tpucb_calib_minmax(self.model._h, name.encode(),
-                                                   C.c_void_p(stats.data_ptr() + t * 8)))
+                st = C.c_void_p(stats.data_ptr() + t * 8)
+                if keep is None:
+                    check(self._lib.tpucb_calib_minmax(self.model._h, name.encode(), st))
+                else:
+                    check(self._lib.tpucb_calib_minmax_keep(self.model._h, name.encode(), st,
+                                                            C.c_void_p(keep.data_ptr() + self._kept_offsets[t])))
+            if keep is not None:
+                # torch allocated `keep` on its own stream and the kernels above ran on the module's: the buffer is not
+                # handed back to torch before the module's stream has been synchronised (end of this pass and of pass 2)
+                self._kept.append((keep, batch.shape[0]))
             n_img += batch.shape[0]
         self.model.sync()
+        self._local_images = n_img
         return stats, n_img
+
+    def _keep_plan(self):
+        """(bytes one batch's fp32 activations take in the cache, byte budget of the cache)."""
+        if self.keep_activations_gb is not None and self.keep_activations_gb <= 0:
+            return 0, 0
+        offs, total = [], 0
+        for name in self.names:
+            offs.append(total)
+            total += (self.model.tensor_device(name)["bytes"] + 255) // 256 * 256
+        self._kept_offsets = offs
+        if self.keep_activations_gb is None:
+            free, _ = torch.cuda.mem_get_info(self.device)
+            budget = int(free * 0.6)
+        else:
+            budget = int(self.keep_activations_gb * 2 ** 30)
+        return total, budget
 
     def _upload(self, batch):
         """The batch becomes the input of the next launch. It is copied into one of two pinned host buffers and sent
@@ -101,7 +145,16 @@ class ActivationCalibrator:
         T = len(self.names)
         hist = torch.zeros((T, self.bin_num), dtype=torch.int64, device=self.device)
         torch.cuda.synchronize(self.device)
-        for batch in self.batches():
+        kept, self._kept = self._kept, []   # the cache serves one histogram pass
+        for keep, _ in kept:
+            for t, name in enumerate(self.names):
+                ab = float(activations_statistics[name][2])
+                check(self._lib.tpucb_calib_hist_kept(self.model._h, name.encode(),
+                                                      C.c_void_p(keep.data_ptr() + self._kept_offsets[t]), C.c_float(ab),
+                                                      self.bin_num, C.c_void_p(hist.data_ptr() + t * self.bin_num * 8)))
+        for i, batch in enumerate(self.batches() if self._needs_recompute(kept) else ()):
+            if i < len(kept):
+                continue   # this batch's activations were read from the cache
             self._upload(batch)
             self.model.launch()
             for t, name in enumerate(self.names):
@@ -109,7 +162,12 @@ class ActivationCalibrator:
                 check(self._lib.tpucb_calib_hist(self.model._h, name.encode(), C.c_float(ab), self.bin_num,
                                                  C.c_void_p(hist.data_ptr() + t * self.bin_num * 8)))
         self.model.sync()
+        del kept
         return hist
+
+    def _needs_recompute(self, kept):
+        """False when every batch of pass 1 is in the cache (then pass 2 does not even ask for the images again)."""
+        return sum(n for _, n in kept) < self._local_images
 
     # -- pass 1 ------------------------------------------------------------------
     def find_min_max_abs(self):

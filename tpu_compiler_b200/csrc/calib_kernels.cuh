@@ -18,8 +18,10 @@ __device__ __forceinline__ void atomic_min_f32(float *addr, float v) {
   else atomicMax(reinterpret_cast<unsigned int *>(addr), __float_as_uint(v));
 }
 
-// stats[0] = running min, stats[1] = running max.
-__global__ void minmax_f32_kernel(const float *__restrict__ x, size_t pixels, int c, int cp, float *stats) {
+// stats[0] = running min, stats[1] = running max. With `keep` the real lanes are also written to a second buffer of the
+// same layout in the same pass (the copy the histogram pass reads when the activations of all batches stay resident).
+__global__ void minmax_f32_kernel(const float *__restrict__ x, size_t pixels, int c, int cp, float *stats,
+                                  float *__restrict__ keep) {
   float mn = INFINITY, mx = -INFINITY;
   const size_t total = pixels * (size_t)cp;
   if ((cp & 3) == 0 && (c & 3) == 0) {
@@ -29,6 +31,7 @@ __global__ void minmax_f32_kernel(const float *__restrict__ x, size_t pixels, in
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) {
       if (!dense && (int)(i % vpp) >= vreal) continue;
       float4 v = __ldg(reinterpret_cast<const float4 *>(x) + i);
+      if (keep) reinterpret_cast<float4 *>(keep)[i] = v;
       mn = fminf(fminf(mn, v.x), fminf(fminf(v.y, v.z), v.w));
       mx = fmaxf(fmaxf(mx, v.x), fmaxf(fmaxf(v.y, v.z), v.w));
     }
@@ -36,6 +39,7 @@ __global__ void minmax_f32_kernel(const float *__restrict__ x, size_t pixels, in
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
       if ((int)(i % cp) >= c) continue;
       float v = x[i];
+      if (keep) keep[i] = v;
       mn = fminf(mn, v);
       mx = fmaxf(mx, v);
     }

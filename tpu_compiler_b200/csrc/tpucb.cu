@@ -398,36 +398,63 @@ int tpucb_measure_i8_mma_peak(int device, int n_cols, double *tops) {
 
 // ---------------------------------------------------------------- calibration statistics
 
-int tpucb_calib_minmax(tpucb_interp *it, const char *name, float *d_stats) {
-  TPUCB_API_BEGIN
-  TPUCB_CHECK(it && name && d_stats, "tpucb_calib_minmax: bad argument");
+static void calib_minmax_impl(tpucb_interp *it, const char *name, float *d_stats, float *d_keep, const char *who) {
+  TPUCB_CHECK(it && name && d_stats, "%s: bad argument", who);
   Interpreter &I = it->impl;
   I.bind();
   auto t = I.tensor(name);
-  TPUCB_CHECK(t->dtype == DT_F32, "tpucb_calib_minmax: tensor %s is not fp32", name);
+  TPUCB_CHECK(t->dtype == DT_F32, "%s: tensor %s is not fp32", who, name);
+  TPUCB_CHECK(((uintptr_t)d_keep & 15) == 0, "%s: the copy must be 16-byte aligned", who);
   size_t total = t->pixels() * t->cp;
   minmax_f32_kernel<<<grid_for(total / 4 + 1, 256, I.sm_count), 256, 0, I.stream>>>((const float *)t->dev, t->pixels(),
-                                                                                    t->c, t->cp, d_stats);
+                                                                                    t->c, t->cp, d_stats, d_keep);
   TPUCB_CUDA(cudaGetLastError());
-  TPUCB_API_END
 }
 
-int tpucb_calib_hist(tpucb_interp *it, const char *name, float abs_max, int bins, int64_t *d_hist) {
-  TPUCB_API_BEGIN
-  TPUCB_CHECK(it && name && d_hist, "tpucb_calib_hist: bad argument");
-  TPUCB_CHECK(bins >= 128 && bins <= 4096, "tpucb_calib_hist: bins must be in [128, 4096]");
+static void calib_hist_impl(tpucb_interp *it, const char *name, const float *d_values, float abs_max, int bins,
+                            int64_t *d_hist, const char *who) {
+  TPUCB_CHECK(it && name && d_hist, "%s: bad argument", who);
+  TPUCB_CHECK(bins >= 128 && bins <= 4096, "%s: bins must be in [128, 4096]", who);
   Interpreter &I = it->impl;
   I.bind();
   auto t = I.tensor(name);
-  TPUCB_CHECK(t->dtype == DT_F32, "tpucb_calib_hist: tensor %s is not fp32", name);
+  TPUCB_CHECK(t->dtype == DT_F32, "%s: tensor %s is not fp32", who, name);
+  TPUCB_CHECK(((uintptr_t)d_values & 15) == 0, "%s: the values must be 16-byte aligned", who);
   // width = abs_max / (bin_num - 1), in fp32 as numpy computes it (kld_calibrator.py:34)
   float width = abs_max / (float)(bins - 1);
   size_t total = t->pixels() * t->cp;
   int grid = grid_for(total / 4 + 1, 256, I.sm_count);
   if (grid > I.sm_count * 8) grid = I.sm_count * 8;
-  hist_f32_kernel<<<grid, 256, bins * sizeof(unsigned), I.stream>>>((const float *)t->dev, t->pixels(), t->c, t->cp,
-                                                                    width, bins, (unsigned long long *)d_hist);
+  hist_f32_kernel<<<grid, 256, bins * sizeof(unsigned), I.stream>>>(d_values ? d_values : (const float *)t->dev,
+                                                                    t->pixels(), t->c, t->cp, width, bins,
+                                                                    (unsigned long long *)d_hist);
   TPUCB_CUDA(cudaGetLastError());
+}
+
+int tpucb_calib_minmax(tpucb_interp *it, const char *name, float *d_stats) {
+  TPUCB_API_BEGIN
+  calib_minmax_impl(it, name, d_stats, nullptr, "tpucb_calib_minmax");
+  TPUCB_API_END
+}
+
+int tpucb_calib_minmax_keep(tpucb_interp *it, const char *name, float *d_stats, float *d_keep) {
+  TPUCB_API_BEGIN
+  TPUCB_CHECK(d_keep, "tpucb_calib_minmax_keep: bad argument");
+  calib_minmax_impl(it, name, d_stats, d_keep, "tpucb_calib_minmax_keep");
+  TPUCB_API_END
+}
+
+int tpucb_calib_hist(tpucb_interp *it, const char *name, float abs_max, int bins, int64_t *d_hist) {
+  TPUCB_API_BEGIN
+  calib_hist_impl(it, name, nullptr, abs_max, bins, d_hist, "tpucb_calib_hist");
+  TPUCB_API_END
+}
+
+int tpucb_calib_hist_kept(tpucb_interp *it, const char *name, const float *d_kept, float abs_max, int bins,
+                          int64_t *d_hist) {
+  TPUCB_API_BEGIN
+  TPUCB_CHECK(d_kept, "tpucb_calib_hist_kept: bad argument");
+  calib_hist_impl(it, name, d_kept, abs_max, bins, d_hist, "tpucb_calib_hist_kept");
   TPUCB_API_END
 }
 

@@ -140,6 +140,17 @@ int tpucb_calib_hist(tpucb_interp *it, const char *name, float abs_max, int bins
 int tpucb_calib_minmax_keep(tpucb_interp *it, const char *name, float *d_stats, float *d_keep);
 int tpucb_calib_hist_kept(tpucb_interp *it, const char *name, const float *d_kept, float abs_max,
                           int bins, int64_t *d_hist);
+/* Both statistics for a list of tensors in ONE launch each (persistent blocks that walk the list: a
+ * module has some seventy tensors, most of them too small to fill the GPU for the length of a
+ * launch). names [count]; d_stats [count][2] device floats as in tpucb_calib_minmax; d_keep NULL or
+ * a host array of `count` device pointers as in tpucb_calib_minmax_keep; d_values NULL or a host
+ * array of kept copies (a NULL entry reads the tensor itself); abs_max [count] host floats; d_hist
+ * [count][bins] device counts. */
+int tpucb_calib_minmax_all(tpucb_interp *it, const char *const *names, int count, float *d_stats,
+                           float *const *d_keep);
+int tpucb_calib_hist_all(tpucb_interp *it, const char *const *names, int count,
+                         const float *const *d_values, const float *abs_max, int bins,
+                         int64_t *d_hist);
 /* kl_diversity_hist (calibration_math.cpp:283-344) for `count` histograms at once:
  * d_hist [count][bins] int64 device counts, widths [count] host floats, thresholds
  * [count] host floats out. */

@@ -55,6 +55,8 @@ def _declare(lib):
         "tpucb_calib_hist": [vp, cp, C.c_float, C.c_int, vp],
         "tpucb_calib_minmax_keep": [vp, cp, vp, vp],
         "tpucb_calib_hist_kept": [vp, cp, vp, C.c_float, C.c_int, vp],
+        "tpucb_calib_minmax_all": [vp, C.POINTER(cp), C.c_int, vp, C.POINTER(vp)],
+        "tpucb_calib_hist_all": [vp, C.POINTER(cp), C.c_int, C.POINTER(vp), fp, C.c_int, vp],
         "tpucb_calib_kld": [vp, vp, fp, C.c_int, C.c_int, fp],
         "tpucb_interp_copy_tensor": [vp, cp, vp, cp],
         "tpucb_tuner_distance": [vp, cp, vp, cp, C.c_float, C.POINTER(C.c_double), C.c_int],

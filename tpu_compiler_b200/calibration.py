@@ -70,13 +70,10 @@ class ActivationCalibrator:
                     keep = torch.empty(per_batch, dtype=torch.uint8, device=self.device)
                 except torch.OutOfMemoryError:
                     budget = 0
-            for t, name in enumerate(self.names):
-                st = C.c_void_p(stats.data_ptr() + t * 8)
-                if keep is None:
-                    check(self._lib.tpucb_calib_minmax(self.model._h, name.encode(), st))
-                else:
-                    check(self._lib.tpucb_calib_minmax_keep(self.model._h, name.encode(), st,
-                                                            C.c_void_p(keep.data_ptr() + self._kept_offsets[t])))
+            keeps = None
+            if keep is not None:
+                keeps = (C.c_void_p * T)(*[keep.data_ptr() + o for o in self._kept_offsets])
+            check(self._lib.tpucb_calib_minmax_all(self.model._h, self._name_array(), T, C.c_void_p(stats.data_ptr()), keeps))
             if keep is not None:
                 # torch allocated `keep` on its own stream and the kernels above ran on the module's: the buffer is not
                 # handed back to torch before the module's stream has been synchronised (end of this pass and of pass 2)
@@ -85,6 +82,11 @@ class ActivationCalibrator:
         self.model.sync()
         self._local_images = n_img
         return stats, n_img
+
+    def _name_array(self):
+        if getattr(self, "_names_c", None) is None:
+            self._names_c = (C.c_char_p * len(self.names))(*[n.encode() for n in self.names])
+        return self._names_c
 
     def _keep_plan(self):
         """(bytes one batch's fp32 activations take in the cache, byte budget of the cache)."""
@@ -146,21 +148,18 @@ class ActivationCalibrator:
         hist = torch.zeros((T, self.bin_num), dtype=torch.int64, device=self.device)
         torch.cuda.synchronize(self.device)
         kept, self._kept = self._kept, []   # the cache serves one histogram pass
+        absmax = (C.c_float * T)(*[float(activations_statistics[n][2]) for n in self.names])
         for keep, _ in kept:
-            for t, name in enumerate(self.names):
-                ab = float(activations_statistics[name][2])
-                check(self._lib.tpucb_calib_hist_kept(self.model._h, name.encode(),
-                                                      C.c_void_p(keep.data_ptr() + self._kept_offsets[t]), C.c_float(ab),
-                                                      self.bin_num, C.c_void_p(hist.data_ptr() + t * self.bin_num * 8)))
+            vals = (C.c_void_p * T)(*[keep.data_ptr() + o for o in self._kept_offsets])
+            check(self._lib.tpucb_calib_hist_all(self.model._h, self._name_array(), T, vals, absmax, self.bin_num,
+                                                 C.c_void_p(hist.data_ptr())))
         for i, batch in enumerate(self.batches() if self._needs_recompute(kept) else ()):
             if i < len(kept):
                 continue   # this batch's activations were read from the cache
             self._upload(batch)
             self.model.launch()
-            for t, name in enumerate(self.names):
-                ab = float(activations_statistics[name][2])
-                check(self._lib.tpucb_calib_hist(self.model._h, name.encode(), C.c_float(ab), self.bin_num,
-                                                 C.c_void_p(hist.data_ptr() + t * self.bin_num * 8)))
+            check(self._lib.tpucb_calib_hist_all(self.model._h, self._name_array(), T, None, absmax, self.bin_num,
+                                                 C.c_void_p(hist.data_ptr())))
         self.model.sync()
         del kept
         return hist

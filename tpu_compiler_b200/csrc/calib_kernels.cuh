@@ -28,10 +28,27 @@ __global__ void minmax_f32_kernel(const float *__restrict__ x, size_t pixels, in
     const size_t nvec = total / 4;
     const int vpp = cp / 4, vreal = c / 4;
     const bool dense = vreal == vpp; // no padded channels: no position arithmetic at all
-    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    const float4 *x4 = reinterpret_cast<const float4 *>(x);
+    float4 *k4 = reinterpret_cast<float4 *>(keep);
+    size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+    // four independent 16-byte loads in flight per thread (padded lanes hold zeros and are masked after the load)
+    for (; i + 3 * stride < nvec; i += 4 * stride) {
+      float4 v[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) v[k] = __ldg(x4 + i + k * stride);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        if (!dense && (int)((i + k * stride) % vpp) >= vreal) continue;
+        if (keep) k4[i + k * stride] = v[k];
+        mn = fminf(fminf(mn, v[k].x), fminf(fminf(v[k].y, v[k].z), v[k].w));
+        mx = fmaxf(fmaxf(mx, v[k].x), fmaxf(fmaxf(v[k].y, v[k].z), v[k].w));
+      }
+    }
+    for (; i < nvec; i += stride) {
       if (!dense && (int)(i % vpp) >= vreal) continue;
-      float4 v = __ldg(reinterpret_cast<const float4 *>(x) + i);
-      if (keep) reinterpret_cast<float4 *>(keep)[i] = v;
+      float4 v = __ldg(x4 + i);
+      if (keep) k4[i] = v;
       mn = fminf(fminf(mn, v.x), fminf(fminf(v.y, v.z), v.w));
       mx = fmaxf(fmaxf(mx, v.x), fmaxf(fmaxf(v.y, v.z), v.w));
     }
@@ -120,6 +137,115 @@ __global__ void hist_f32_kernel(const float *__restrict__ x, size_t pixels, int 
   __syncthreads();
   for (int j = threadIdx.x; j < bins; j += blockDim.x)
     if (s_h[j]) atomicAdd(&hist[j], (unsigned long long)s_h[j]);
+}
+
+// ---- all tensors of a module in one launch ------------------------------------------------------------------------
+// One descriptor per fp32 tensor (channel pitch a multiple of 4). The kernels below are persistent: every block walks
+// the tensor list and takes its stripe of each tensor, so small tensors cost no launch of their own and the tail of
+// one tensor overlaps the head of the next. Lanes past the real channel count are masked per value.
+struct StatDesc {
+  const float *x;           // the values (the tensor's storage, or its kept copy)
+  float *keep;              // minmax only: where to copy the storage, or null
+  unsigned long long nvec;  // 16-byte vectors in the storage
+  int vpp;                  // vectors per pixel (channel pitch / 4)
+  int c;                    // real channels
+  float width;              // histogram only: bin width
+  int pad_;
+};
+
+__global__ void __launch_bounds__(1024) minmax_multi_kernel(const StatDesc *__restrict__ descs, int count, float *stats) {
+  __shared__ float smn[32], smx[32];
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (int t = 0; t < count; ++t) {
+    const StatDesc d = descs[t];
+    const float4 *x4 = reinterpret_cast<const float4 *>(d.x);
+    float4 *k4 = reinterpret_cast<float4 *>(d.keep);
+    const bool dense = d.c == d.vpp * 4;
+    float mn = INFINITY, mx = -INFINITY;
+    auto take = [&](const float4 &v, size_t i) {
+      if (k4) k4[i] = v;
+      if (dense) {
+        mn = fminf(fminf(mn, v.x), fminf(fminf(v.y, v.z), v.w));
+        mx = fmaxf(fmaxf(mx, v.x), fmaxf(fmaxf(v.y, v.z), v.w));
+      } else {
+        const int ch = (int)(i % d.vpp) * 4;
+        const float e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          if (ch + k < d.c) {
+            mn = fminf(mn, e[k]);
+            mx = fmaxf(mx, e[k]);
+          }
+      }
+    };
+    size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+    for (; i + 3 * stride < d.nvec; i += 4 * stride) {
+      float4 v[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) v[k] = __ldg(x4 + i + k * stride);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) take(v[k], i + k * stride);
+    }
+    for (; i < d.nvec; i += stride) take(__ldg(x4 + i), i);
+    for (int o = 16; o > 0; o >>= 1) {
+      mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    }
+    if ((threadIdx.x & 31) == 0) {
+      smn[threadIdx.x >> 5] = mn;
+      smx[threadIdx.x >> 5] = mx;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      for (int w = 1; w < (int)(blockDim.x >> 5); ++w) {
+        mn = fminf(mn, smn[w]);
+        mx = fmaxf(mx, smx[w]);
+      }
+      if (mn <= mx) {
+        atomic_min_f32(stats + 2 * t, mn);
+        atomic_max_f32(stats + 2 * t + 1, mx);
+      }
+    }
+    __syncthreads();
+  }
+}
+
+// hist [count][bins]; the bin rule of hist_f32_kernel.
+__global__ void __launch_bounds__(1024) hist_multi_kernel(const StatDesc *__restrict__ descs, int count, int bins,
+                                                           unsigned long long *__restrict__ hist) {
+  extern __shared__ unsigned int s_h[];
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  const float top = (float)(bins - 1);
+  for (int t = 0; t < count; ++t) {
+    const StatDesc d = descs[t];
+    const float4 *x4 = reinterpret_cast<const float4 *>(d.x);
+    const bool dense = d.c == d.vpp * 4;
+    for (int j = threadIdx.x; j < bins; j += blockDim.x) s_h[j] = 0;
+    __syncthreads();
+    auto take = [&](const float4 &v, size_t i) {
+      const float a[4] = {fabsf(v.x), fabsf(v.y), fabsf(v.z), fabsf(v.w)};
+      const int ch = dense ? 0 : (int)(i % d.vpp) * 4;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        if (a[k] != 0.0f && (dense || ch + k < d.c)) {
+          const float f = floorf(__fadd_rn(__fdiv_rn(a[k], d.width), 0.5f));
+          if (f <= top) atomicAdd(&s_h[(int)f], 1u);
+        }
+      }
+    };
+    size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+    for (; i + stride < d.nvec; i += 2 * stride) {
+      const float4 v0 = __ldg(x4 + i), v1 = __ldg(x4 + i + stride);
+      take(v0, i);
+      take(v1, i + stride);
+    }
+    for (; i < d.nvec; i += stride) take(__ldg(x4 + i), i);
+    __syncthreads();
+    unsigned long long *h = hist + (size_t)t * bins;
+    for (int j = threadIdx.x; j < bins; j += blockDim.x)
+      if (s_h[j]) atomicAdd(&h[j], (unsigned long long)s_h[j]);
+    __syncthreads();
+  }
 }
 
 // One CTA per (histogram, candidate). N <= 4096 bins, 128-bin target. The float / double mix and

@@ -4,6 +4,7 @@
 #include "interpreter.cuh"
 #include "mma_peak.cuh"
 
+#include <algorithm>
 #include <cmath>
 #include <mutex>
 #include <string>
@@ -14,9 +15,12 @@ struct tpucb_interp {
   Interpreter impl;
   double *tuner_sums = nullptr; // device scratch of tpucb_tuner_distance, grown on demand
   int tuner_sums_cap = 0;
+  StatDesc *stat_descs = nullptr; // device descriptor list of the all-tensor statistics launches, grown on demand
+  int stat_descs_cap = 0;
   explicit tpucb_interp(int device) : impl(device) {}
   ~tpucb_interp() {
     if (tuner_sums) cudaFree(tuner_sums);
+    if (stat_descs) cudaFree(stat_descs);
   }
 };
 
@@ -423,9 +427,14 @@ static void calib_hist_impl(tpucb_interp *it, const char *name, const float *d_v
   // width = abs_max / (bin_num - 1), in fp32 as numpy computes it (kld_calibrator.py:34)
   float width = abs_max / (float)(bins - 1);
   size_t total = t->pixels() * t->cp;
-  int grid = grid_for(total / 4 + 1, 256, I.sm_count);
-  if (grid > I.sm_count * 8) grid = I.sm_count * 8;
-  hist_f32_kernel<<<grid, 256, bins * sizeof(unsigned), I.stream>>>(d_values ? d_values : (const float *)t->dev,
+  // Every block ends by adding its private histogram to the global one (up to `bins` 64-bit atomics), so few, large
+  // blocks: 1024 threads, at most two per SM, and at least four vectors per thread (TPUCB_HIST_THREADS for experiments).
+  static const int threads = [] { const char *e = getenv("TPUCB_HIST_THREADS"); int v = e ? atoi(e) : 1024;
+                                  return (v == 256 || v == 512 || v == 1024) ? v : 1024; }();
+  int grid = (int)std::min<size_t>((total / 4 + (size_t)threads * 4 - 1) / ((size_t)threads * 4),
+                                   (size_t)I.sm_count * (2048 / threads));
+  if (grid < 1) grid = 1;
+  hist_f32_kernel<<<grid, threads, bins * sizeof(unsigned), I.stream>>>(d_values ? d_values : (const float *)t->dev,
                                                                     t->pixels(), t->c, t->cp, width, bins,
                                                                     (unsigned long long *)d_hist);
   TPUCB_CUDA(cudaGetLastError());
@@ -455,6 +464,66 @@ int tpucb_calib_hist_kept(tpucb_interp *it, const char *name, const float *d_kep
   TPUCB_API_BEGIN
   TPUCB_CHECK(d_kept, "tpucb_calib_hist_kept: bad argument");
   calib_hist_impl(it, name, d_kept, abs_max, bins, d_hist, "tpucb_calib_hist_kept");
+  TPUCB_API_END
+}
+
+// Fills and uploads the descriptor list of an all-tensor statistics launch (ordered on the interpreter's stream behind
+// the previous launch that read the list).
+static const StatDesc *stat_descs_upload(tpucb_interp *it, const char *const *names, int count, const float *const *d_values,
+                                         float *const *d_keep, const float *abs_max, int bins, const char *who) {
+  Interpreter &I = it->impl;
+  std::vector<StatDesc> h((size_t)count);
+  for (int t = 0; t < count; ++t) {
+    TPUCB_CHECK(names[t], "%s: name %d is NULL", who, t);
+    auto tn = I.tensor(names[t]);
+    TPUCB_CHECK(tn->dtype == DT_F32 && tn->cp % 4 == 0, "%s: tensor %s is not fp32 with a channel pitch of 4n", who, names[t]);
+    StatDesc &d = h[t];
+    d.x = d_values && d_values[t] ? d_values[t] : (const float *)tn->dev;
+    d.keep = d_keep ? d_keep[t] : nullptr;
+    TPUCB_CHECK((((uintptr_t)d.x | (uintptr_t)d.keep) & 15) == 0, "%s: buffer %d is not 16-byte aligned", who, t);
+    d.nvec = (unsigned long long)(tn->pixels() * tn->cp / 4);
+    d.vpp = tn->cp / 4;
+    d.c = tn->c;
+    // width = abs_max / (bin_num - 1), in fp32 as numpy computes it (kld_calibrator.py:34)
+    d.width = abs_max ? abs_max[t] / (float)(bins - 1) : 0.0f;
+    d.pad_ = 0;
+  }
+  if (it->stat_descs_cap < count) {
+    TPUCB_CUDA(cudaStreamSynchronize(I.stream));
+    if (it->stat_descs) TPUCB_CUDA(cudaFree(it->stat_descs));
+    it->stat_descs = nullptr;
+    it->stat_descs_cap = 0;
+    TPUCB_CUDA(cudaMalloc(&it->stat_descs, sizeof(StatDesc) * count));
+    it->stat_descs_cap = count;
+  }
+  TPUCB_CUDA(cudaMemcpyAsync(it->stat_descs, h.data(), sizeof(StatDesc) * count, cudaMemcpyHostToDevice, I.stream));
+  return it->stat_descs;
+}
+
+int tpucb_calib_minmax_all(tpucb_interp *it, const char *const *names, int count, float *d_stats, float *const *d_keep) {
+  TPUCB_API_BEGIN
+  TPUCB_CHECK(it && names && d_stats && count > 0, "tpucb_calib_minmax_all: bad argument");
+  Interpreter &I = it->impl;
+  I.bind();
+  const StatDesc *d = stat_descs_upload(it, names, count, nullptr, d_keep, nullptr, 2, "tpucb_calib_minmax_all");
+  // one 1024-thread block per SM: the kernel keeps four 16-byte loads per thread in flight (about 60 registers), which
+  // covers the memory latency at half occupancy
+  minmax_multi_kernel<<<I.sm_count, 1024, 0, I.stream>>>(d, count, d_stats);
+  TPUCB_CUDA(cudaGetLastError());
+  TPUCB_API_END
+}
+
+int tpucb_calib_hist_all(tpucb_interp *it, const char *const *names, int count, const float *const *d_values,
+                         const float *abs_max, int bins, int64_t *d_hist) {
+  TPUCB_API_BEGIN
+  TPUCB_CHECK(it && names && abs_max && d_hist && count > 0, "tpucb_calib_hist_all: bad argument");
+  TPUCB_CHECK(bins >= 128 && bins <= 4096, "tpucb_calib_hist_all: bins must be in [128, 4096]");
+  Interpreter &I = it->impl;
+  I.bind();
+  const StatDesc *d = stat_descs_upload(it, names, count, d_values, nullptr, abs_max, bins, "tpucb_calib_hist_all");
+  hist_multi_kernel<<<I.sm_count * 2, 1024, bins * sizeof(unsigned), I.stream>>>(d, count, bins,
+                                                                               (unsigned long long *)d_hist);
+  TPUCB_CUDA(cudaGetLastError());
   TPUCB_API_END
 }
 

@@ -215,7 +215,7 @@ __global__ void __launch_bounds__(1024) hist_multi_kernel(const StatDesc *__rest
                                                            unsigned long long *__restrict__ hist) {
   extern __shared__ unsigned int s_h[];
   const size_t stride = (size_t)gridDim.x * blockDim.x;
-  const float top = (float)(bins - 1);
+  const float top = (float)bins;
   for (int t = 0; t < count; ++t) {
     const StatDesc d = descs[t];
     const float4 *x4 = reinterpret_cast<const float4 *>(d.x);
@@ -228,8 +228,10 @@ __global__ void __launch_bounds__(1024) hist_multi_kernel(const StatDesc *__rest
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
         if (a[k] != 0.0f && (dense || ch + k < d.c)) {
-          const float f = floorf(__fadd_rn(__fdiv_rn(a[k], d.width), 0.5f));
-          if (f <= top) atomicAdd(&s_h[(int)f], 1u);
+          // floor(f) <= bins - 1 is f < bins; for 0 <= f < 2^23 the round-down sum f + 2^23 carries floor(f) in its low
+          // mantissa bits: no rounding or conversion instruction of the (narrow) conversion pipe
+          const float f = __fadd_rn(__fdiv_rn(a[k], d.width), 0.5f);
+          if (f < top) atomicAdd(&s_h[__float_as_int(__fadd_rd(f, 8388608.0f)) - 0x4B000000], 1u);
         }
       }
     };

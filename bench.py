@@ -148,7 +148,9 @@ def run_calibration(args, rank, world, local_rank):
     m.load_text(model.text, model.weights)
     rng = np.random.default_rng(7000 + rank)
     data = [np.clip(rng.standard_normal((bs, 3, 224, 224), dtype=np.float32), -3, 3) for _ in range(n_batches)]
-    cal = ActivationCalibrator(m, lambda: iter(data), dist=dist)
+    # expected_batches: the device cache of the activations (one buffer per batch) is allocated with the calibrator,
+    # like its pinned upload buffers and the module itself, not inside the timed passes
+    cal = ActivationCalibrator(m, lambda: iter(data), dist=dist, expected_batches=n_batches)
     m.set_tensor(cal.input_name, data[0])
     for _ in range(3):
         m.invoke()

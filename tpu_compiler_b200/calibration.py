@@ -26,7 +26,8 @@ from ._lib import check, lib
 
 
 class ActivationCalibrator:
-    def __init__(self, model, batches, histogram_bin_num=2048, input_name=None, dist=None, keep_activations_gb=None):
+    def __init__(self, model, batches, histogram_bin_num=2048, input_name=None, dist=None, keep_activations_gb=None,
+                 expected_batches=None):
         """model: a loaded ``tpu_compiler_b200.module`` of an fp32 graph; batches: a callable
         returning an iterator over this rank's input batches (float32 arrays of the input's
         shape) -- it is called twice, once per pass."""
@@ -46,9 +47,20 @@ class ActivationCalibrator:
         self._pinned = None
         self._pinned_numel = 0
         self._pinned_next = 0
+        self._reserved = []      # cache buffers allocated ahead of pass 1
         if self._lib is not None:
             # the two pinned upload buffers are part of setting up (tens of milliseconds), not of a pass
             self._alloc_pinned(int(np.prod(model.get_tensor_shape(self.input_name))))
+            if expected_batches:
+                # so is the activation cache when the caller says how many batches will come: a cudaMalloc of several GB
+                # blocks the host for milliseconds, and for far longer while other ranks' processes allocate too
+                per_batch, budget = self._keep_plan()
+                for _ in range(min(int(expected_batches), budget // per_batch if per_batch else 0)):
+                    try:
+                        self._reserved.append(torch.empty(per_batch, dtype=torch.uint8, device=self.device))
+                    except torch.OutOfMemoryError:
+                        break
+                torch.cuda.synchronize(self.device)
 
     # -- device work of the two passes (overridden by the CPU stand-in used in the gloo tests) -------
     def _local_min_max(self):
@@ -65,7 +77,9 @@ class ActivationCalibrator:
             self._upload(batch)
             self.model.launch()
             keep = None
-            if per_batch and (len(self._kept) + 1) * per_batch <= budget:
+            if self._reserved:
+                keep = self._reserved.pop()
+            elif per_batch and (len(self._kept) + 1) * per_batch <= budget:
                 try:
                     keep = torch.empty(per_batch, dtype=torch.uint8, device=self.device)
                 except torch.OutOfMemoryError:

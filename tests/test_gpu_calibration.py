@@ -161,7 +161,7 @@ def test_kept_activations_give_the_same_histograms():
     per_batch, _ = ActivationCalibrator(m, batches)._keep_plan()
     for gb, expect_calls in ((None, 1), (1.5 * per_batch / 2 ** 30, 2)):
         del calls[:]
-        cal = ActivationCalibrator(m, batches, keep_activations_gb=gb)
+        cal = ActivationCalibrator(m, batches, keep_activations_gb=gb, expected_batches=3 if gb is None else None)
         thr, _ = cal.run()
         assert len(calls) == expect_calls
         assert np.array_equal(cal.histograms.cpu().numpy(), h0)

@@ -325,29 +325,40 @@ __global__ void tuner_distance_kernel(DistGeom ref, DistGeom tgt, int c, int h, 
   const int c4 = (c + 3) >> 2;
   const size_t quads = (size_t)h * w * c4;
   double d2 = 0.0, s1 = 0.0;
-  for (size_t q = blockIdx.x * (size_t)blockDim.x + threadIdx.x; q < quads; q += (size_t)gridDim.x * blockDim.x) {
-    const int cq = (int)(q % c4);
+  // four channels of one pixel: the fp32 reference vector and the candidate's raw bytes (4, 8 or 16 of them)
+  auto load = [&](size_t q, float4 &r4, uint4 &raw, int &cq) {
+    cq = (int)(q % c4);
     const size_t pix = q / c4;
     const int x = (int)(pix % w), y = (int)(pix / w);
     const size_t ro = (((size_t)img * h + y) * ref.wphys + ref.wl + x) * ref.cp + cq * 4;
     const size_t to = (((size_t)img * h + y) * tgt.wphys + tgt.wl + x) * tgt.cp + cq * 4;
-    const float4 r4 = __ldg(reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(ref.dev) + ro));
+    r4 = __ldg(reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(ref.dev) + ro));
+    raw = make_uint4(0, 0, 0, 0);
+    if (TGT == 0) {
+      raw.x = (unsigned)__ldg(reinterpret_cast<const int *>(reinterpret_cast<const signed char *>(tgt.dev) + to));
+    } else if (TGT == 1) {
+      const uint2 wd = __ldg(reinterpret_cast<const uint2 *>(reinterpret_cast<const unsigned short *>(tgt.dev) + to));
+      raw.x = wd.x;
+      raw.y = wd.y;
+    } else {
+      raw = __ldg(reinterpret_cast<const uint4 *>(reinterpret_cast<const float *>(tgt.dev) + to));
+    }
+  };
+  auto take = [&](const float4 &r4, const uint4 &raw, int cq) {
     float t[4];
     if (TGT == 0) {
-      const int wd = __ldg(reinterpret_cast<const int *>(reinterpret_cast<const signed char *>(tgt.dev) + to));
+      const int wd = (int)raw.x;
       t[0] = (float)(signed char)(wd & 0xff);
       t[1] = (float)(signed char)((wd >> 8) & 0xff);
       t[2] = (float)(signed char)((wd >> 16) & 0xff);
       t[3] = (float)(signed char)((wd >> 24) & 0xff);
     } else if (TGT == 1) {
-      const uint2 wd = __ldg(reinterpret_cast<const uint2 *>(reinterpret_cast<const unsigned short *>(tgt.dev) + to));
-      t[0] = __uint_as_float(wd.x << 16);
-      t[1] = __uint_as_float(wd.x & 0xffff0000u);
-      t[2] = __uint_as_float(wd.y << 16);
-      t[3] = __uint_as_float(wd.y & 0xffff0000u);
+      t[0] = __uint_as_float(raw.x << 16);
+      t[1] = __uint_as_float(raw.x & 0xffff0000u);
+      t[2] = __uint_as_float(raw.y << 16);
+      t[3] = __uint_as_float(raw.y & 0xffff0000u);
     } else {
-      const float4 t4 = __ldg(reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(tgt.dev) + to));
-      t[0] = t4.x; t[1] = t4.y; t[2] = t4.z; t[3] = t4.w;
+      t[0] = __uint_as_float(raw.x); t[1] = __uint_as_float(raw.y); t[2] = __uint_as_float(raw.z); t[3] = __uint_as_float(raw.w);
     }
     const float r[4] = {r4.x, r4.y, r4.z, r4.w};
 #pragma unroll
@@ -358,6 +369,24 @@ __global__ void tuner_distance_kernel(DistGeom ref, DistGeom tgt, int c, int h, 
         s1 += (double)fabsf(r[j]);
       }
     }
+  };
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  size_t q = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+  for (; q + stride < quads; q += 2 * stride) {  // two independent load pairs in flight per thread
+    float4 ra, rb;
+    uint4 ta, tb;
+    int ca, cb;
+    load(q, ra, ta, ca);
+    load(q + stride, rb, tb, cb);
+    take(ra, ta, ca);
+    take(rb, tb, cb);
+  }
+  for (; q < quads; q += stride) {
+    float4 ra;
+    uint4 ta;
+    int ca;
+    load(q, ra, ta, ca);
+    take(ra, ta, ca);
   }
   for (int o = 16; o > 0; o >>= 1) {
     d2 += __shfl_xor_sync(0xffffffffu, d2, o);

@@ -238,7 +238,7 @@ def quantize_multiplier_qdm_array(qscale):
     return q_fixed, -shift
 
 
-def quantize_conv_weights(filt, bias, threshold_y, threshold_x):
+def quantize_conv_weights(filt, bias, threshold_y, threshold_x, flat64=None):
     """quantizeWeightInt8Multiplier (:741-818) without a filter threshold. ``filt`` is
     [oc, ...] fp32, ``bias`` [oc] fp32 or None. Returns (new_filter, new_bias, rshift, multiplier)
     as fp32 arrays the way the reference stores them (the multiplier rounded to fp32)."""
@@ -261,7 +261,14 @@ def quantize_conv_weights(filt, bias, threshold_y, threshold_x):
     safe = np.where(live, m_used, 1.0)
     # quantizeFilterRShiftAndMultiplier (:442-453): (double)(tx / ty as floats) * 2^(rshift+31) / multiplier
     fac = np.where(live, np.ldexp(float(f32(threshold_x) / f32(threshold_y)), (r + 31).astype(np.int32)) / safe, 0.0)
-    new_f = _saturate_int8((flat.astype(np.float64) * fac[:, None]).astype(f32)).astype(f32)
+    # (float)(w * factor) then floor(f + 0.5) in double and the clamp (saturateInt8), with few temporaries; ``flat64`` is
+    # the [oc, isz] float64 copy of the filter when the caller quantises the same filter for several thresholds
+    x = (flat.astype(np.float64) if flat64 is None else flat64) * fac[:, None]
+    np.copyto(x, x.astype(f32))
+    x += 0.5
+    np.floor(x, out=x)
+    np.clip(x, -128, 127, out=x)
+    new_f = x.astype(f32)
     new_b = None
     if bias is not None:
         # quantizeBiasRShiftAndMultiplier (:459-478)
@@ -330,10 +337,10 @@ def quant_param_signature(op, thr, by_name):
     return (None if own is None else float(own),) + tuple(float(thr[_resolve(a, by_name)]) for a in acts)
 
 
-def quantize_op(op, thr, weights, by_name, rename=None, out_name=None):
+def quantize_op(op, thr, weights, by_name, rename=None, out_name=None, cache=None):
     """INT8 form of one fp32 op. ``rename`` maps operand names of the fp32 graph to the names
     they carry in the module being written; ``out_name`` renames the result (and the weights made
-    for it). Returns (list of op dicts, dict of new weights)."""
+    for it); ``cache``: see the conv_2d branch. Returns (list of op dicts, dict of new weights)."""
     rename = rename or {}
     name = out_name or op["name"]
     t = op["type"]
@@ -348,7 +355,15 @@ def quantize_op(op, thr, weights, by_name, rename=None, out_name=None):
     txs = [thr[_resolve(a, by_name)] for a in acts]
     if t == "conv_2d":
         bias = weights[op["in"][2]] if len(op["in"]) > 2 and op["in"][2] else None
-        nf, nb, r, m = quantize_conv_weights(weights[op["in"][1]], bias, ty, txs[0])
+        flat64 = None
+        if cache is not None:
+            # the float64 copy of the filter is shared by the candidates of one op (``cache``: a dict the caller owns)
+            key = op["in"][1]
+            if key not in cache:
+                wf = np.ascontiguousarray(weights[key], f32)
+                cache[key] = wf.reshape(wf.shape[0], -1).astype(np.float64)
+            flat64 = cache[key]
+        nf, nb, r, m = quantize_conv_weights(weights[op["in"][1]], bias, ty, txs[0], flat64=flat64)
         w[name + "_filter_q"] = nf
         new["in"] = [ins[0], name + "_filter_q", None, None, None, name + "_rshift", name + "_multiplier"]
         if nb is not None:

@@ -166,6 +166,7 @@ class SimpleTuner:
                 plan[t] = len(variants) - 1
         # one module for all variants
         ops_out, w_out, declared = [], {}, set()
+        w64 = {}  # float64 filter copies shared by this op's candidates
         from_ref, from_store = [], []
         for vi, v in enumerate(variants):
             sfx = "__%d" % vi
@@ -191,7 +192,8 @@ class SimpleTuner:
                                         "attrs": {}})
                         declared.add(src)
                         from_store.append(src)
-                new_ops, w = Q.quantize_op(op, v["thr"], self.weights, self.by_name, rename, out_name=a + sfx)
+                new_ops, w = Q.quantize_op(op, v["thr"], self.weights, self.by_name, rename, out_name=a + sfx,
+                                           cache=w64)
                 ops_out += new_ops
                 w_out.update(w)
                 self.ops_run += 1

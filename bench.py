@@ -297,23 +297,9 @@ def run_conv_sweep(args, local_rank):
         m.set_tensor("x", model.meta["x"])
         for _ in range(max(args.warmup, 3)):
             m.invoke()
-        prof = (C.c_ulonglong * 16)()
-        if os.environ.get("TPUCB_CONV_PROF"):
-            check(lib().tpucb_debug_conv_loop_profile(prof))   # clear what the warm-up counted
         ms = m.time_launches(args.steps) / args.steps
         ops = 2.0 * n * hw * hw * c * c * 9
         row = {"c": c, "hw": hw, "n": n, "us": ms * 1e3, "tops": ops / (ms * 1e-3) / 1e12}
-        if os.environ.get("TPUCB_CONV_PROF"):
-            # clock counters of the instrumented kernel, per CTA and per K block (numbers under the instrumented
-            # kernel are for reading the loop, not bench values)
-            check(lib().tpucb_debug_conv_loop_profile(prof))
-            ctas, blocks = max(prof[4], 1), max(prof[3], 1)
-            row["loop_profile"] = {
-                "ctas_per_launch": prof[4] / args.steps, "k_blocks_per_cta": prof[3] / ctas,
-                "mma_thread_clk_per_k_block": prof[0] / blocks, "of_it_waiting_for_data": prof[1] / blocks,
-                "issuing": (prof[0] - prof[1] - prof[2]) / blocks, "mma_thread_waiting_for_accumulator_per_cta": prof[2] / ctas,
-                "producer_waiting_for_stage_per_k_block": prof[6] / blocks,
-                "epilogue_warp_waiting_per_cta": prof[7] / ctas, "epilogue_warp_working_per_cta": prof[8] / ctas}
         rows.append(row)
         m.close()
     best = max(r["tops"] for r in rows)

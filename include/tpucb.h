@@ -110,13 +110,6 @@ int tpucb_interp_tensor_device(tpucb_interp *it, const char *name, void **dev, s
  * of the convolution kernel, for which the driver-written peaks have no INT8 entry. */
 int tpucb_measure_i8_mma_peak(int device, int n_cols, double *tops);
 
-/* Measuring aid. With TPUCB_CONV_PROF=1 in the environment when the library loads, INT8 convolutions run an
- * instrumented copy of the tensor-core kernel that sums clock counts by role over all CTAs: [0] MMA thread total,
- * [1] of it waiting for a filled stage, [2] waiting for a drained accumulator, [3] K blocks, [4] CTAs, [5] producer
- * total, [6] of it waiting for a free stage, [7] one epilogue warp waiting for an accumulator, [8] that warp working.
- * This call synchronises the device, copies the 16 counters out and clears them. No reference counterpart. */
-int tpucb_debug_conv_loop_profile(unsigned long long *counters16);
-
 /* Pinned host buffers for the e2e path. */
 int tpucb_host_alloc(void **ptr, size_t bytes);
 int tpucb_host_free(void *ptr);
@@ -183,8 +176,9 @@ int tpucb_tuner_distance(tpucb_interp *ref, const char *ref_name, tpucb_interp *
  * tpucb_calib_kld keeps in a temporary device buffer live here in a fixed array inside the
  * library's device image: TPUCB_KLD_STATIC_MAX_HISTS x 32 floats (32 KiB), held by every GPU
  * that loads the library until the process exits.
- *   - `device` is the CUDA ordinal the histograms live on, `stream` a cudaStream_t (NULL = the
- *     default stream). d_hist [count][bins] int64 device counts, widths [count] host floats,
+ *   - `device` is the CUDA ordinal the histograms live on, `stream` a cudaStream_t. NULL is the
+ *     LEGACY default stream, which waits for, and holds up, every blocking stream of the process;
+ *     pass a stream made with cudaStreamNonBlocking to stay clear of other work. d_hist [count][bins] int64 device counts, widths [count] host floats,
  *     thresholds [count] host floats out: same meaning as in tpucb_calib_kld.
  *   - count > TPUCB_KLD_STATIC_MAX_HISTS, or bins not a multiple of 128 in [128, 4096], is
  *     refused with an error; nothing is launched.

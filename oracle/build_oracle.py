@@ -4,15 +4,16 @@
 * ``oracle/_ref/libtpuc_ref.so`` -- the reference's own arithmetic sources
   (QuantizationArithmetic.cpp, core/lut_func.cpp, kld/calibration_math.cpp),
   compiled unmodified from the reference checkout with the stand-in headers in
-  ``oracle/shims``. Only built when the checkout is present; the prebuilt file
-  is reused otherwise.
+  ``oracle/shims``. The checkout is named by the environment variable
+  ``TPUC_REFERENCE_DIR``; without it (or without the sources there) the prebuilt
+  file is reused, and ``build_ref`` says so when there is none.
 """
 import os
 import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = os.environ.get("TPUC_REFERENCE_DIR", "/root/reference")
+REF = os.environ.get("TPUC_REFERENCE_DIR", "")
 
 
 def _run(cmd):
@@ -42,8 +43,13 @@ def build_ref(force=False):
         os.path.join(REF, "lib/Dialect/TPU/Interpreter/core/lut_func.cpp"),
         os.path.join(REF, "bindings/python/kld/calibration_math.cpp"),
     ]
-    if not all(os.path.exists(s) for s in srcs):
-        return out if os.path.exists(out) else None
+    if not REF or not all(os.path.exists(s) for s in srcs):
+        if os.path.exists(out):
+            return out
+        if force:
+            raise RuntimeError("oracle/_ref is not built and TPUC_REFERENCE_DIR does not name a reference checkout "
+                               "(set it to the directory that holds lib/Dialect/TPU/Quantization/QuantizationArithmetic.cpp)")
+        return None
     wrap = os.path.join(HERE, "ref_wrap.cpp")
     if force or _stale(out, srcs + [wrap]):
         os.makedirs(out_dir, exist_ok=True)

@@ -221,3 +221,53 @@ def test_two_gpu_calibration_equals_single_gpu():
         assert np.array_equal(hist_r, hist)
         assert thr_r == {k: float(v) for k, v in thr.items()}
     m.close()
+
+
+def test_histogram_bins_at_the_rounding_boundaries():
+    """The all-tensor histogram kernel forms |x| / width from a reciprocal taken once per tensor and fused multiply-adds
+    instead of one division per value. The bin index floor(|x| / width + 0.5) must still be the one an IEEE fp32
+    division gives (numpy, as kld_calibrator.py:31-43 computes it): checked on the values where a quotient off by one
+    unit in the last place changes the bin -- the fp32 neighbours of every (k + 0.5) * width -- for widths with awkward
+    mantissas, plus random values, subnormals and values beyond abs_max."""
+    import ctypes as C
+    import torch
+    from tpu_compiler_b200 import module
+    from tpu_compiler_b200._lib import check, lib
+    bins = 2048
+    rng = np.random.default_rng(2024)
+    abs_maxes = [np.float32(1.0), np.float32(3.0), np.float32(2047.0), np.float32(1e-5), np.float32(6.25e4),
+                 np.nextafter(np.float32(2.0), np.float32(0)) * np.float32(2047), np.float32(0.3333333), np.float32(7.77e-3)]
+    abs_maxes += [np.float32(v) for v in rng.uniform(0.01, 300.0, 8)]
+    per = bins * 5 + 4096
+    n = per + (-per) % 4
+    m = module(0)
+    m.load_text("input name=x shape=1,4,%d,1 dtype=FP32\n" % (n // 4), {})
+    L = lib()
+    names = (C.c_char_p * 1)(b"x")
+    for am in abs_maxes:
+        width = am / np.float32(bins - 1)
+        edges = ((np.arange(bins, dtype=np.float64) + 0.5) * float(width)).astype(np.float32)
+        vals = [edges]
+        for _ in range(2):
+            vals.append(np.nextafter(vals[-1], np.float32(np.inf)))
+        lo = edges
+        for _ in range(2):
+            lo = np.nextafter(lo, np.float32(0))
+            vals.append(lo)
+        extra = rng.uniform(0, float(am) * 1.01, 4096 - 8).astype(np.float32)
+        tail = np.array([0.0, 1e-42, -1e-40, float(am), -float(am), float(am) * 4, 1e38, -3e38], np.float32)
+        x = np.concatenate(vals + [extra, tail, np.zeros(n - per, np.float32)])
+        x[::3] *= -1
+        m.set_tensor("x", x.reshape(1, 4, n // 4, 1))
+        hist = torch.zeros((1, bins), dtype=torch.int64, device="cuda")
+        torch.cuda.synchronize()
+        amax = (C.c_float * 1)(float(am))
+        check(L.tpucb_calib_hist_all(m._h, names, 1, None, amax, bins, C.c_void_p(hist.data_ptr())))
+        m.sync()
+        t = np.abs(x)
+        t = t[t != 0]
+        with np.errstate(over="ignore"):
+            idx = np.floor(t / width + np.float32(0.5))
+        ref, _ = np.histogram(idx, bins=bins, range=(0, bins - 1))
+        assert np.array_equal(hist.cpu().numpy()[0], ref.astype(np.int64)), float(am)
+    m.close()

@@ -57,6 +57,8 @@ def reference_order_tuner(text, weights, cand_map, images, ref_act):
                 continue
             trial = dict(table)
             trial[name] = t
+            # the trial table reaches the quantiser through a text file (kld_calibrator.py:98-108, 175-177)
+            trial = {k: np.float32("{:.7f}".format(v)) for k, v in trial.items()}
             qtext, qw = Q.quantize_module(text, weights, trial, upto=name)
             allw = dict(weights)
             allw.update(qw)
@@ -74,11 +76,14 @@ def reference_order_tuner(text, weights, cand_map, images, ref_act):
     return table, dists
 
 
-def test_tuner_matches_reference_order_loop():
+@pytest.mark.parametrize("image_scale", [1.0, 0.02])  # 0.02: every threshold below 1, where the table text rounds
+def test_tuner_matches_reference_order_loop(image_scale):
     from tpu_compiler_b200.tuner import SimpleTuner
     rng = np.random.default_rng(77)
     text, weights = small_fp32_net(rng)
-    images = rng.normal(0, 1, (N, 3, 16, 16)).clip(-3, 3).astype(np.float32)
+    images = (rng.normal(0, 1, (N, 3, 16, 16)).clip(-3, 3) * image_scale).astype(np.float32)
+    if image_scale != 1.0:
+        weights = {k: (v * image_scale if k.endswith("_b") else v) for k, v in weights.items()}
     fp32 = graph_runner.run(text, weights, {"data": images})
     absmax = {k: float(np.abs(v).max()) for k, v in fp32.items()}
     # three candidate tables; the order differs per op so that "first" is not always the largest
@@ -101,7 +106,7 @@ def test_tuner_matches_reference_order_loop():
                 assert abs(tuner.distances[n][t] - d) <= 1e-5 * abs(d) + 1e-12, (n, t, tuner.distances[n][t], d)
             assert got[n] == exp_table[n], n
         # the INT8 tensors kept on the device are those of the whole-graph quantisation under the final table
-        qtext, qw = Q.quantize_module(text, weights, got)
+        qtext, qw = Q.quantize_module(text, weights, {k: np.float32("{:.7f}".format(v)) for k, v in got.items()})
         allw = dict(weights)
         allw.update(qw)
         oracle_q = graph_runner.run(qtext, allw, {"data": images})

@@ -90,3 +90,40 @@ def test_resnet50_graph_shape():
             w = m.weights[o["in"][1]]
             macs += int(np.prod(o["shape"])) * int(np.prod(w.shape[1:]))
     assert 3.8e9 < macs < 4.2e9
+
+
+def _build_worker(args):
+    """One process of test_concurrent_builds: points the build module at a scratch library and a fake compiler."""
+    lib_path, log_path = args
+    import subprocess
+    import time
+    from tpu_compiler_b200 import build as b
+    b.LIB = lib_path
+
+    def fake_compiler(cmd, check=True):
+        out = cmd[cmd.index("-o") + 1]
+        assert out != lib_path, "the compiler must not write the library in place"
+        with open(out, "wb") as f:
+            f.write(b"half")
+            f.flush()
+            time.sleep(0.3)   # a reader that opened the final path now would see a truncated file
+            f.write(b"-written-library")
+        with open(log_path, "a") as f:
+            f.write("compiled\n")
+        return subprocess.CompletedProcess(cmd, 0)
+
+    b.build(run=fake_compiler)
+    with open(lib_path, "rb") as f:
+        return f.read()
+
+
+def test_concurrent_builds(tmp_path):
+    """Two ranks that both find the library stale: one compiles (into a temporary file, renamed over the library),
+    the other waits on the lock, sees a fresh library and does not compile; neither reads a partial file."""
+    import multiprocessing as mp
+    lib_path, log_path = str(tmp_path / "libfake.so"), str(tmp_path / "log.txt")
+    with mp.get_context("spawn").Pool(2) as pool:
+        got = pool.map(_build_worker, [(lib_path, log_path)] * 2)
+    assert got == [b"half-written-library"] * 2
+    assert open(log_path).read().count("compiled") == 1
+    assert [f for f in os.listdir(tmp_path) if f.endswith(".tmp")] == []

@@ -2,6 +2,7 @@
 of INT8 activations) with the device module replaced by a stand-in over the CPU oracle: the result
 must equal the reference's loop run as written (whole-module re-quantisation per candidate)."""
 import numpy as np
+import pytest
 
 from oracle import graph_runner
 from tpu_compiler_b200 import quantize as Q
@@ -54,10 +55,13 @@ class OracleModule:
         pass
 
 
-def test_incremental_tuner_equals_reference_order_loop():
+@pytest.mark.parametrize("image_scale", [1.0, 0.02])  # 0.02: every threshold below 1, where the table text rounds
+def test_incremental_tuner_equals_reference_order_loop(image_scale):
     rng = np.random.default_rng(77)
     text, weights = small_fp32_net(rng)
-    images = rng.normal(0, 1, (N, 3, 16, 16)).clip(-3, 3).astype(np.float32)
+    images = (rng.normal(0, 1, (N, 3, 16, 16)).clip(-3, 3) * image_scale).astype(np.float32)
+    if image_scale != 1.0:
+        weights = {k: (v * image_scale if k.endswith("_b") else v) for k, v in weights.items()}
     fp32 = graph_runner.run(text, weights, {"data": images})
     absmax = {k: float(np.abs(v).max()) for k, v in fp32.items()}
     factors = [(1.0, 0.6, 0.35), (0.6, 1.0, 0.35), (0.35, 0.6, 1.0)]
@@ -75,7 +79,9 @@ def test_incremental_tuner_equals_reference_order_loop():
     # c1's threshold is overwritten by its max pool's, so its three candidates share one copy
     assert tuner.launches == len(names) - 1
     assert tuner.ops_run < 3 * (len(names) - 1) + 3
-    qtext, qw = Q.quantize_module(text, weights, got)
+    if image_scale != 1.0:
+        assert max(got.values()) < 1.0 and any(np.float32("{:.7f}".format(v)) != np.float32(v) for v in got.values())
+    qtext, qw = Q.quantize_module(text, weights, {k: np.float32("{:.7f}".format(v)) for k, v in got.items()})
     allw = dict(weights)
     allw.update(qw)
     oracle_q = graph_runner.run(qtext, allw, {"data": images})

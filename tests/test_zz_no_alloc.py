@@ -5,7 +5,9 @@ service with a fixed device-memory budget, a worker that must not trigger the de
 synchronisation of cudaMalloc / cudaFree). For them the KLD threshold search exists in a form
 whose scratch lives in a fixed array inside the library. This test calls it through the C ABI
 twice in a row -- the second time with different histograms, so stale scratch contents from the
-first call would show -- and requires the same thresholds, bit for bit, as tpucb_calib_kld.
+first call would show -- and requires the same thresholds, bit for bit, as tpucb_calib_kld;
+a second test ties it to the reference directly through the golden histograms and thresholds
+that the reference's own kl_diversity_hist produced (tests/golden/kld.npz).
 The file name sorts last so that a run that stops at the first failure has already run every
 other test."""
 import ctypes as C
@@ -64,3 +66,19 @@ def test_kld_static_matches_allocating_entry_point_twice():
                                   out.ctypes.data_as(fp))
     assert rc != 0 and b"multiple of 128" in L.tpucb_last_error()
     m.close()
+
+
+def test_kld_static_matches_reference_golden(golden_dir):
+    """The thresholds the reference's compiled kl_diversity_hist gave for the golden histograms."""
+    import torch
+    from tpu_compiler_b200._lib import check, lib
+    g = np.load(os.path.join(golden_dir, "kld.npz"))
+    hist = torch.tensor(g["hist"].astype(np.int64), device="cuda")
+    widths = np.ascontiguousarray(g["width"], np.float32)
+    torch.cuda.synchronize()
+    fp = C.POINTER(C.c_float)
+    for _ in range(2):
+        got = np.zeros(len(widths), np.float32)
+        check(lib().tpucb_calib_kld_static(0, None, C.c_void_p(hist.data_ptr()), widths.ctypes.data_as(fp), len(widths),
+                                           2048, got.ctypes.data_as(fp)))
+        assert np.array_equal(got, g["threshold"])

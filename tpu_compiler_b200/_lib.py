@@ -48,7 +48,6 @@ def _declare(lib):
         "tpucb_interp_kernel_count": [vp, ip],
         "tpucb_interp_tensor_device": [vp, cp, C.POINTER(vp), szp, ip, ip, ip],
         "tpucb_measure_i8_mma_peak": [C.c_int, C.c_int, C.POINTER(C.c_double)],
-        "tpucb_debug_conv_loop_profile": [C.POINTER(C.c_ulonglong)],
         "tpucb_host_alloc": [C.POINTER(vp), sz],
         "tpucb_host_free": [vp],
         "tpucb_calib_minmax": [vp, cp, vp],

@@ -2,6 +2,7 @@
 
     python -m tpu_compiler_b200.build [--force]
 """
+import fcntl
 import os
 import shutil
 import subprocess
@@ -36,14 +37,35 @@ def stale():
     return any(os.path.getmtime(s) > t for s in sources())
 
 
-def build(force=False, verbose=False):
-    if not (force or stale()):
-        return LIB
-    cmd = [_nvcc()] + NVCC_FLAGS + [os.path.join(CSRC, "tpucb.cu"), "-o", LIB]
+def compile_command(out, verbose=False):
+    cmd = [_nvcc()] + NVCC_FLAGS + [os.path.join(CSRC, "tpucb.cu"), "-o", out]
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")
-    subprocess.run(cmd, check=True)
+    return cmd
+
+
+def build(force=False, verbose=False, run=subprocess.run):
+    """Compiles the library when it is missing or older than a source. Several processes may call this at once (one
+    rank per GPU under torchrun): the compile runs under an exclusive file lock, the staleness check is repeated once
+    the lock is held, and the compiler writes a temporary file that replaces the library in one rename, so no process
+    ever loads a half-written file."""
+    if not (force or stale()):
+        return LIB
+    with open(LIB + ".lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if not (force or stale()):
+                return LIB  # another process built it while this one waited
+            tmp = "%s.%d.tmp" % (LIB, os.getpid())
+            try:
+                run(compile_command(tmp, verbose), check=True)
+                os.replace(tmp, LIB)
+            finally:
+                if os.path.exists(tmp):
+                    os.unlink(tmp)
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
     return LIB
 
 

@@ -82,6 +82,9 @@ class ActivationCalibrator:
             elif per_batch and (len(self._kept) + 1) * per_batch <= budget:
                 try:
                     keep = torch.empty(per_batch, dtype=torch.uint8, device=self.device)
+                    # torch may hand out a block whose last use is still queued on ITS stream; the kernels that fill
+                    # this buffer run on the module's stream, which knows nothing of that work: wait for it here
+                    torch.cuda.current_stream(self.device).synchronize()
                 except torch.OutOfMemoryError:
                     budget = 0
             keeps = None

@@ -139,6 +139,21 @@ __global__ void hist_f32_kernel(const float *__restrict__ x, size_t pixels, int 
     if (s_h[j]) atomicAdd(&hist[j], (unsigned long long)s_h[j]);
 }
 
+// a / w, correctly rounded, for a divisor that is constant over many values: r = RN(1 / w) is taken once
+// (quot_setup) and every quotient costs one multiply and four fused multiply-adds on the FMA pipe instead of the
+// reciprocal unit and the fix-up code of a division. q0 = RN(a r) is within 1.5 ulp of a / w; the residual
+// e = a - q0 w is exact in one FMA, so q1 = RN(q0 + e r) is a faithful quotient, and one more step from a faithful
+// quotient with a correctly rounded reciprocal gives RN(a / w) (Markstein's theorem). That holds while nothing
+// overflows or goes subnormal; quot_ok tells whether w is in the range (2^-60 .. 2^60) where this is so for every
+// |a| <= 2^40 w that is either zero or at least 2^-60 (smaller quotients differ from the division's by less than
+// 2^-80 and are used here only after 0.5 is added). Callers take the plain division when quot_ok is false.
+__device__ __forceinline__ bool quot_ok(float w) { return w > 8.673617e-19f && w < 1.1529215e18f; }
+__device__ __forceinline__ float quot_by_const(float a, float w, float r) {
+  const float q0 = __fmul_rn(a, r);
+  const float q1 = __fmaf_rn(__fmaf_rn(-q0, w, a), r, q0);
+  return __fmaf_rn(__fmaf_rn(-q1, w, a), r, q1);
+}
+
 // ---- all tensors of a module in one launch ------------------------------------------------------------------------
 // One descriptor per fp32 tensor (channel pitch a multiple of 4). The kernels below are persistent: every block walks
 // the tensor list and takes its stripe of each tensor, so small tensors cost no launch of their own and the tail of
@@ -220,6 +235,10 @@ __global__ void __launch_bounds__(1024) hist_multi_kernel(const StatDesc *__rest
     const StatDesc d = descs[t];
     const float4 *x4 = reinterpret_cast<const float4 *>(d.x);
     const bool dense = d.c == d.vpp * 4;
+    // the bin width is constant over the tensor: its reciprocal is taken once and every quotient is formed, still
+    // correctly rounded, with multiply-adds (quot_by_const); widths outside its range keep the division
+    const bool fast = quot_ok(d.width);
+    const float rw = fast ? __frcp_rn(d.width) : 0.0f;
     for (int j = threadIdx.x; j < bins; j += blockDim.x) s_h[j] = 0;
     __syncthreads();
     auto take = [&](const float4 &v, size_t i) {
@@ -230,7 +249,8 @@ __global__ void __launch_bounds__(1024) hist_multi_kernel(const StatDesc *__rest
         if (a[k] != 0.0f && (dense || ch + k < d.c)) {
           // floor(f) <= bins - 1 is f < bins; for 0 <= f < 2^23 the round-down sum f + 2^23 carries floor(f) in its low
           // mantissa bits: no rounding or conversion instruction of the (narrow) conversion pipe
-          const float f = __fadd_rn(__fdiv_rn(a[k], d.width), 0.5f);
+          const float q = fast ? quot_by_const(a[k], d.width, rw) : __fdiv_rn(a[k], d.width);
+          const float f = __fadd_rn(q, 0.5f);
           if (f < top) atomicAdd(&s_h[__float_as_int(__fadd_rd(f, 8388608.0f)) - 0x4B000000], 1u);
         }
       }

@@ -529,9 +529,6 @@ __device__ __forceinline__ void epilogue_channels_f32(const ConvGemmParams &p, u
 // vary fastest so that CTAs working at the same time share activation tiles through L2). The
 // producer runs ahead through the shared-memory ring across tile boundaries and the accumulator is
 // double-buffered in TMEM, so the loads and MMAs of tile i+1 overlap the epilogue of tile i.
-// Loop-profile counters of the PROF instantiation (a measuring aid, never launched by the op kernels unless the
-// environment asks for it): clocks summed over CTAs by role, see conv_gemm_prof_kernel.
-__device__ unsigned long long g_conv_prof[16];
 // TF32: an fp32 convolution as three kind::tf32 products accumulated in one pass over K: with x = xh + xl and
 // w = wh + wl (h: the upper 19 bits of the fp32 word, l: the exact remainder), x w = xh wh + xl wh + xh wl up to
 // 2^-22 relative. The K loop runs three times over the taps: term 0 reads (tmA2, tmB) = (xl, wh), term 1
@@ -539,7 +536,7 @@ __device__ unsigned long long g_conv_prof[16];
 // terms come first: the tensor core truncates every partial sum at the accumulator's own precision, so each MMA
 // step costs up to an ulp of what has been accumulated so far, and only the steps of the last term see the
 // full magnitude (measured: the error against a double-accumulated convolution drops by the expected factor 3).
-template <bool BF16, bool PROF = false, bool FAST = true, bool TF32 = false>
+template <bool BF16, bool FAST = true, bool TF32 = false>
 __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUtensorMap &tmB, const ConvGemmParams &p,
                                                const CUtensorMap &tmA2, const CUtensorMap &tmB2) {
   constexpr int KIND = TF32 ? 2 : (BF16 ? 1 : 0);
@@ -610,7 +607,6 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
   if (warp == 0) {
     // ---------------------------------------------------------------- producer
     if (lane == 0) {
-      long long pf_p0 = PROF ? clock64() : 0ll, pf_pwait = 0;
       int it = 0; // k-iterations issued so far, across tiles
       int ps = 0;        // ring stage of iteration `it`
       uint32_t pph = 0;  // its phase bit
@@ -653,7 +649,6 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
         for (int kit = 0; kit < kTerms * k_iters; ++kit, ++it) {
           const CUtensorMap *mapA = (TF32 && term == 0) ? &tmA2 : &tmA;
           const CUtensorMap *mapB = (TF32 && term == 1) ? &tmB2 : &tmB;
-          const long long pf_e0 = PROF ? clock64() : 0ll;
           if (it >= p.stages) {
             if (!ptx::mbar_wait_bounded(bar_empty + 8 * ps, pph ^ 1u, abort_flag)) {
               if (!*abort_flag) atomicExch(p.err, kErrEmptyWait);
@@ -662,7 +657,6 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
               break;
             }
           }
-          if (PROF) pf_pwait += clock64() - pf_e0;
           const int c0 = chunk * p.BK;
           const uint32_t a_dst = tiles + (uint32_t)ps * stage_bytes;
           const uint32_t b_dst = a_dst + a_bytes;
@@ -701,10 +695,6 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
             pph ^= 1u;
           }
         }
-      }
-      if (PROF) {
-        atomicAdd(&g_conv_prof[5], (unsigned long long)(clock64() - pf_p0));
-        atomicAdd(&g_conv_prof[6], (unsigned long long)pf_pwait);
       }
       if (!ok || *abort_flag) {
         if (p.w_resident && (int)blockIdx.x < total_tiles)
@@ -748,12 +738,8 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
           ok = false;
         }
       }
-      long long pf_t0 = PROF ? clock64() : 0ll, pf_wait = 0, pf_accwait = 0, pf_blocks = 0;
-      unsigned long long pf_g0 = 0;
-      if (PROF) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(pf_g0));
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++t) {
         const int buf = t & 1;
-        const long long pf_a0 = PROF ? clock64() : 0ll;
         if (t >= 2) {
           // the epilogue must have drained this accumulator buffer (its previous use)
           if (!ptx::mbar_wait_bounded(bar_acc_empty + 8 * buf, (uint32_t)(((t >> 1) - 1) & 1), abort_flag)) {
@@ -766,18 +752,12 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
         }
         const uint32_t d_tmem = tmem_base + (uint32_t)buf * acc_stride;
         uint32_t wres_lo = desc_w_lo; // weight-resident mode: descriptor (low word) of K block `kit`
-        if (PROF) pf_accwait += clock64() - pf_a0;
         for (int kit = 0; kit < kTerms * k_iters; ++kit, ++it) {
-          const long long pf_w0 = PROF ? clock64() : 0ll;
           if (!ptx::mbar_try_wait(m_full, mph) && !ptx::mbar_wait_bounded(m_full, mph, abort_flag)) {
             if (!*abort_flag) atomicExch(p.err, kErrFullWait);
             *abort_flag = 1;
             ok = false;
             break;
-          }
-          if (PROF) {
-            pf_wait += clock64() - pf_w0;
-            ++pf_blocks;
           }
           ptx::tcgen05_fence_after();
           // transposed product: weights are the A operand (M = channels), activations B (N = pixels)
@@ -813,21 +793,6 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
         }
         if (ok) ptx::tcgen05_commit(bar_acc_full + 8 * buf);
       }
-      if (PROF) {
-        atomicAdd(&g_conv_prof[0], (unsigned long long)(clock64() - pf_t0));
-        atomicAdd(&g_conv_prof[1], (unsigned long long)pf_wait);
-        atomicAdd(&g_conv_prof[2], (unsigned long long)pf_accwait);
-        atomicAdd(&g_conv_prof[3], (unsigned long long)pf_blocks);
-        atomicAdd(&g_conv_prof[4], 1ull);
-        unsigned long long pf_g1;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(pf_g1));
-        atomicAdd(&g_conv_prof[9], pf_g1 - pf_g0);
-        atomicMax(&g_conv_prof[10], pf_g1 - pf_g0);
-        atomicMax(&g_conv_prof[11], (unsigned long long)(clock64() - pf_t0));
-        if (g_conv_prof[12] == 0) atomicCAS(&g_conv_prof[12], 0ull, pf_g0);
-        atomicMin(&g_conv_prof[12], pf_g0);
-        atomicMax(&g_conv_prof[13], pf_g1);
-      }
     }
   } else {
     // ---------------------------------------------------------------- epilogue
@@ -854,10 +819,7 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
         }
         staged_n0 = n0;
       }
-      const long long pf_q0 = PROF ? clock64() : 0ll;
       ok = ptx::mbar_wait_bounded(bar_acc_full + 8 * buf, (uint32_t)((t >> 1) & 1), abort_flag);
-      if (PROF && warp == 2 && lane == 0) atomicAdd(&g_conv_prof[7], (unsigned long long)(clock64() - pf_q0));
-      const long long pf_q1 = PROF ? clock64() : 0ll;
       if (!ok && !*abort_flag) {
         atomicExch(p.err, kErrAccWait);
         *abort_flag = 1;
@@ -887,7 +849,6 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
         else if (p.act == 2) epilogue_channels_impl<2, FAST>(p, lane_addr, out4, ch4_ok, m0, half, kEpilogueWarps / 4, lane, cc, ts, 128);
         else epilogue_channels_impl<0, FAST>(p, lane_addr, out4, ch4_ok, m0, half, kEpilogueWarps / 4, lane, cc, ts, 128);
       }
-      if (PROF && warp == 2 && lane == 0) atomicAdd(&g_conv_prof[8], (unsigned long long)(clock64() - pf_q1));
       // hand the accumulator buffer back to the MMA issuer
       ptx::tcgen05_fence_before();
       __syncwarp();
@@ -908,21 +869,13 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
 __global__ void __launch_bounds__(kConvThreads, 2)
 conv_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const ConvGemmParams p) {
-  conv_gemm_body<false, false, true>(tmA, tmB, p, tmA, tmB);
+  conv_gemm_body<false, true>(tmA, tmB, p, tmA, tmB);
 }
 // the same with the 64-bit multiply-add requantisation (requant_one), for layers outside requant_fast's domain
 __global__ void __launch_bounds__(kConvThreads, 2)
 conv_gemm_i8_wide_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                          const ConvGemmParams p) {
-  conv_gemm_body<false, false, false>(tmA, tmB, p, tmA, tmB);
-}
-// The INT8 kernel with the loop-profile counters on (g_conv_prof): [0] MMA thread total clocks, [1] of which waiting
-// for a full stage, [2] waiting for a drained accumulator, [3] K blocks, [4] CTAs, [5] producer total, [6] of which
-// waiting for an empty stage, [7] epilogue (one warp) waiting for an accumulator, [8] epilogue working.
-__global__ void __launch_bounds__(kConvThreads, 2)
-conv_gemm_prof_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                      const ConvGemmParams p) {
-  conv_gemm_body<false, true, true>(tmA, tmB, p, tmA, tmB);
+  conv_gemm_body<false, false>(tmA, tmB, p, tmA, tmB);
 }
 // The same pipeline for BF16 graphs: BF16 operands (tcgen05 kind::f16), fp32 accumulators, BF16 results.
 // All sizes in ConvGemmParams that count K or row pitches are in BYTES, so only the MMA kind and the
@@ -930,7 +883,7 @@ conv_gemm_prof_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
 __global__ void __launch_bounds__(kConvThreads, 2)
 conv_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                       const ConvGemmParams p) {
-  conv_gemm_body<true, false, false>(tmA, tmB, p, tmA, tmB);
+  conv_gemm_body<true, false>(tmA, tmB, p, tmA, tmB);
 }
 
 // fp32 convolution on the tensor cores as three TF32 products (see conv_gemm_body): tmA / tmA2 are the upper and
@@ -939,7 +892,7 @@ __global__ void __launch_bounds__(kConvThreads, 2)
 conv_gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                         const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2,
                         const ConvGemmParams p) {
-  conv_gemm_body<false, false, false, true>(tmA, tmB, p, tmA2, tmB2);
+  conv_gemm_body<false, false, true>(tmA, tmB, p, tmA2, tmB2);
 }
 
 // x -> (upper part, remainder): hi keeps the sign, the exponent and the top 10 mantissa bits of the fp32 word (what

@@ -4,7 +4,6 @@
 // output size taken from the result type, dilation, optional input zero-insertion.
 #pragma once
 #include "conv_gemm_i8.cuh"
-#include "conv_gemm2_i8.cuh"
 #include "conv_stem_i8.cuh"
 #include "host_common.h"
 #include "mem_kernels.cuh"
@@ -82,7 +81,6 @@ struct ConvPlan {
   ConvGemmParams p;
   dim3 grid;
   size_t smem = 0;
-  bool pair = false; // runs conv_gemm2_i8_kernel (two-SM tiles)
   bool bf16 = false; // runs conv_gemm_bf16_kernel (K sizes and pitches in bytes, 2 per element)
   bool tf32 = false; // runs conv_gemm_tf32x3_kernel (fp32 operands, 4 bytes per element; three K passes)
   CUtensorMap tmA2, tmB2;           // tf32: remainder parts of the activations and of the weights
@@ -368,36 +366,6 @@ inline void finish_plan(ConvPlan &pl, int rows, int taps, int k_inner, int oc_pa
   p.M_total = rows;
   p.BK = pick_bk(k_inner);
   p.c_chunks = (k_inner + p.BK - 1) / p.BK;
-  // Two-SM tiles (256 channels x 256 pixels per CTA pair, conv_gemm2_i8_kernel): measured slower than
-  // the one-SM kernel on every ResNet-50 layer so far, so they are off unless TPUCB_PAIR=1 asks for
-  // them (layers with a multiple of 256 output channels and at least 256 pixels).
-  {
-    bool pair = false;
-    if (const char *e = getenv("TPUCB_PAIR"))
-      if (e[0] == '1') pair = !pl.bf16 && oc_pad % 256 == 0 && p.a_mode != 2 && rows >= 256;
-    if (pair) {
-      pl.pair = true;
-      p.dual = 0;
-      p.w_resident = 0;
-      p.BN = 128;
-      p.n_valid = oc_pad;
-      p.tmem_cols = 512;
-      p.idesc = make_idesc_i8(256, 256);
-      const size_t stage_bytes = 2 * (size_t)128 * p.BK;
-      const long long k_iters = (long long)taps * p.c_chunks;
-      const long long tiles_total = (long long)((rows + 255) / 256) * (oc_pad / 256);
-      int clusters = sm_count / 2;
-      if (clusters > tiles_total) clusters = (int)tiles_total;
-      int stages = (int)((200 * 1024 - kSmemHeader - 1024) / stage_bytes);
-      if (stages > kMaxStages) stages = kMaxStages;
-      const long long iters_per_cluster = ((tiles_total + clusters - 1) / clusters) * k_iters;
-      if (stages > iters_per_cluster) stages = (int)iters_per_cluster;
-      p.stages = stages;
-      pl.smem = kSmemHeader + 1024 + stages * stage_bytes;
-      pl.grid = dim3((unsigned)(2 * clusters), 1, 1);
-      return;
-    }
-  }
   // Dual mode: layers with at most 64 output channels would leave half of the TMEM lanes (and half of
   // the epilogue warps) idle; they run 256-pixel tiles instead (see the kernel). Not combined with the
   // row-window activation mode.
@@ -435,7 +403,6 @@ inline void finish_plan(ConvPlan &pl, int rows, int taps, int k_inner, int oc_pa
   int stages = (int)(ring_budget / stage_bytes);
   if (stages < 2) stages = 2;
   if (stages > kMaxStages) stages = kMaxStages;
-  if (const char *e = getenv("TPUCB_MAX_STAGES")) { int v = atoi(e); if (v >= 1 && stages > v) stages = v; }
   int grid = ctas_per_sm * sm_count;
   if (grid > total_tiles) grid = (int)total_tiles;
   if (p.w_resident) {
@@ -450,17 +417,6 @@ inline void finish_plan(ConvPlan &pl, int rows, int taps, int k_inner, int oc_pa
   pl.grid = dim3((unsigned)grid, 1, 1);
 }
 
-inline bool conv_prof_enabled() {
-  static const bool on = [] { const char *e = getenv("TPUCB_CONV_PROF"); return e && atoi(e) != 0; }();
-  return on;
-}
-// Reads and clears the loop-profile counters (see conv_gemm_prof_kernel).
-inline void conv_prof_read(unsigned long long *out16) {
-  TPUCB_CUDA(cudaDeviceSynchronize());
-  TPUCB_CUDA(cudaMemcpyFromSymbol(out16, g_conv_prof, 16 * sizeof(unsigned long long)));
-  unsigned long long z[16] = {0};
-  TPUCB_CUDA(cudaMemcpyToSymbol(g_conv_prof, z, sizeof(z)));
-}
 inline void launch_conv_plan(const ConvPlan &pl, cudaStream_t stream, int sm_count) {
   if (pl.use_patch) {
     size_t total = (size_t)pl.p.M_total * pl.patch.kp;
@@ -484,10 +440,7 @@ inline void launch_conv_plan(const ConvPlan &pl, cudaStream_t stream, int sm_cou
         reinterpret_cast<float4 *>(pl.split_lo), pl.split_nvec);
     conv_gemm_tf32x3_kernel<<<pl.grid, threads, pl.smem, stream>>>(pl.tmA, pl.tmB, pl.tmA2, pl.tmB2, pl.p);
   } else if (pl.bf16) conv_gemm_bf16_kernel<<<pl.grid, threads, pl.smem, stream>>>(pl.tmA, pl.tmB, pl.p);
-  else if (pl.pair && conv_prof_enabled()) conv_gemm2_prof_kernel<<<pl.grid, kPairThreads, pl.smem, stream>>>(pl.tmA, pl.tmB, pl.p);
-  else if (pl.pair) conv_gemm2_i8_kernel<<<pl.grid, kPairThreads, pl.smem, stream>>>(pl.tmA, pl.tmB, pl.p);
   else if (!(pl.p.fastq & 1)) conv_gemm_i8_wide_kernel<<<pl.grid, threads, pl.smem, stream>>>(pl.tmA, pl.tmB, pl.p);
-  else if (conv_prof_enabled()) conv_gemm_prof_kernel<<<pl.grid, threads, pl.smem, stream>>>(pl.tmA, pl.tmB, pl.p);
   else conv_gemm_i8_kernel<<<pl.grid, threads, pl.smem, stream>>>(pl.tmA, pl.tmB, pl.p);
 }
 
@@ -495,17 +448,11 @@ inline void conv_kernel_setup_once() {
   static bool done = [] {
     TPUCB_CUDA(cudaFuncSetAttribute(conv_gemm_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     227 * 1024));
-    TPUCB_CUDA(cudaFuncSetAttribute(conv_gemm2_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    227 * 1024));
     TPUCB_CUDA(cudaFuncSetAttribute(conv_gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    227 * 1024));
-    TPUCB_CUDA(cudaFuncSetAttribute(conv_gemm_prof_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     227 * 1024));
     TPUCB_CUDA(cudaFuncSetAttribute(conv_gemm_i8_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     227 * 1024));
     TPUCB_CUDA(cudaFuncSetAttribute(conv_gemm_tf32x3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    227 * 1024));
-    TPUCB_CUDA(cudaFuncSetAttribute(conv_gemm2_prof_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     227 * 1024));
     return true;
   }();

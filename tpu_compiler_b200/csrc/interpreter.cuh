@@ -252,8 +252,7 @@ inline bool requant_fast_applies(const std::vector<float> &rshift, const std::ve
 }
 // ConvGemmParams::fastq: bit 0 the multiply-high form applies, bit 1 every rshift is >= 1
 inline int requant_fast_flags(const std::vector<float> &rshift, const std::vector<float> &bias, long long k_total) {
-  static const int env = [] { const char *e = getenv("TPUCB_FASTQ"); return e ? atoi(e) : 1; }();
-  if (!env || !requant_fast_applies(rshift, bias, k_total)) return 0;
+  if (!requant_fast_applies(rshift, bias, k_total)) return 0;
   int f = 1 | 2;
   for (float r : rshift)
     if (r < 1.0f) f = 1;
@@ -688,10 +687,7 @@ public:
   // Fused leaky ReLU (tensor-core plans only): the epilogue writes the plain result to this op's tensor
   // and the activation result to `act_out`.
   bool can_fuse_leaky() const {
-    if (f32_ || dw_ || !stem_plans_.empty() || act_ != 0 || plans_.empty()) return false;
-    for (auto &pl : plans_)
-      if (pl.pair) return false;
-    return true;
+    return !(f32_ || dw_ || !stem_plans_.empty() || act_ != 0 || plans_.empty());
   }
   void set_leaky(int mp, int rp, int mn, int rn, int8_t *act_out) {
     for (auto &pl : plans_) {

@@ -355,13 +355,6 @@ int tpucb_host_free(void *ptr) {
   TPUCB_API_END
 }
 
-int tpucb_debug_conv_loop_profile(unsigned long long *counters16) {
-  TPUCB_API_BEGIN
-  TPUCB_CHECK(counters16 != nullptr, "tpucb_debug_conv_loop_profile: null output");
-  conv_prof_read(counters16);
-  TPUCB_API_END
-}
-
 int tpucb_measure_i8_mma_peak(int device, int n_cols, double *tops) {
   TPUCB_API_BEGIN
   TPUCB_CHECK(tops && (n_cols == 64 || n_cols == 128 || n_cols == 256), "tpucb_measure_i8_mma_peak: n_cols must be 64, 128 or 256");
@@ -402,6 +395,9 @@ int tpucb_measure_i8_mma_peak(int device, int n_cols, double *tops) {
 
 // ---------------------------------------------------------------- calibration statistics
 
+// dynamic shared memory of kld_kernel at the largest supported bin count (4096): two float arrays and one double array
+static constexpr int kKldMaxSmem = 4096 * (2 * (int)sizeof(float) + (int)sizeof(double));
+
 static void calib_minmax_impl(tpucb_interp *it, const char *name, float *d_stats, float *d_keep, const char *who) {
   TPUCB_CHECK(it && name && d_stats, "%s: bad argument", who);
   Interpreter &I = it->impl;
@@ -428,9 +424,8 @@ static void calib_hist_impl(tpucb_interp *it, const char *name, const float *d_v
   float width = abs_max / (float)(bins - 1);
   size_t total = t->pixels() * t->cp;
   // Every block ends by adding its private histogram to the global one (up to `bins` 64-bit atomics), so few, large
-  // blocks: 1024 threads, at most two per SM, and at least four vectors per thread (TPUCB_HIST_THREADS for experiments).
-  static const int threads = [] { const char *e = getenv("TPUCB_HIST_THREADS"); int v = e ? atoi(e) : 1024;
-                                  return (v == 256 || v == 512 || v == 1024) ? v : 1024; }();
+  // blocks: 1024 threads, at most two per SM, and at least four vectors per thread.
+  const int threads = 1024;
   int grid = (int)std::min<size_t>((total / 4 + (size_t)threads * 4 - 1) / ((size_t)threads * 4),
                                    (size_t)I.sm_count * (2048 / threads));
   if (grid < 1) grid = 1;
@@ -538,7 +533,9 @@ int tpucb_calib_kld(tpucb_interp *it, const int64_t *d_hist, const float *widths
   float *d_kl = nullptr;
   TPUCB_CUDA(cudaMalloc(&d_kl, sizeof(float) * count * kl_num));
   size_t smem = (size_t)bins * (2 * sizeof(float) + sizeof(double));
-  cudaError_t e = cudaFuncSetAttribute(kld_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  // always the limit of the largest bin count: the attribute is per function and device, shared with
+  // tpucb_calib_kld_static and with other threads, so no call may lower it under another call's launch
+  cudaError_t e = cudaFuncSetAttribute(kld_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kKldMaxSmem);
   if (e != cudaSuccess) {
     cudaFree(d_kl);
     TPUCB_CUDA(e);
@@ -587,6 +584,9 @@ float *kld_static_setup(int device) {
   if (!g_kld_static_ready[device]) {
     float *ptr = nullptr;
     TPUCB_CUDA(cudaGetSymbolAddress((void **)&ptr, g_kld_static_scratch));
+    // the dynamic shared memory limit of the kernel (a per-function setting, not an allocation), once, at the value
+    // of the largest bin count, which is also what tpucb_calib_kld sets: no call ever lowers it
+    TPUCB_CUDA(cudaFuncSetAttribute(kld_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kKldMaxSmem));
     TPUCB_CHECK(ptr != nullptr, "tpucb_calib_kld_static: the scratch array has no device address");
     g_kld_static_ptr[device] = ptr;
     g_kld_static_ready[device] = true;
@@ -617,8 +617,6 @@ extern "C" int tpucb_calib_kld_static(int device, void *stream, const int64_t *d
     cudaStream_t st = (cudaStream_t)stream;
     const int kl_num = bins / 128;
     const size_t smem = (size_t)bins * (2 * sizeof(float) + sizeof(double));
-    // the dynamic shared memory limit is a per-function setting, not an allocation
-    TPUCB_CUDA(cudaFuncSetAttribute(kld_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     kld_kernel<<<count * kl_num, 256, smem, st>>>((const long long *)d_hist, bins, d_kl);
     TPUCB_CUDA(cudaGetLastError());
     // host copy of the KL values: fixed-size, on the stack

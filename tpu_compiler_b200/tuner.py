@@ -19,8 +19,10 @@ Here the same decisions come out of far less work:
 * both norms are taken on the device (``tpucb_tuner_distance``); 16 bytes per image come back.
 
 Which ops a candidate changes is decided by comparing quantisation signatures (own threshold and
-operand thresholds after the reference's overwrite rules), so the INT8 tensors are exactly those
-of the reference's whole-graph re-quantisation.
+operand thresholds after the reference's overwrite rules), and every threshold reaches the
+quantiser as the reference's does, through the ``'{:.7f}'`` text of a trial table
+(``through_table_text``), so the INT8 tensors are exactly those of the reference's whole-graph
+re-quantisation.
 """
 import numpy as np
 
@@ -28,6 +30,13 @@ from . import quantize as Q
 from .interpreter import module
 
 SKIP_TYPES = ("input", "softmax", "reshape")
+
+
+def through_table_text(threshold):
+    """The value the reference's quantiser sees for a threshold: every trial table goes through a text file
+    (``update_to`` writes ``'{:.7f}'``, kld_calibrator.py:98-108) that ImportCalibrationTable.cpp:274-290 parses back
+    into a float. Below 1 that round trip changes most float32 values."""
+    return np.float32("{:.7f}".format(float(threshold)))
 
 
 class ThresholdTable:
@@ -48,13 +57,17 @@ class ThresholdTable:
         return out
 
     def table_with(self, target_op, new_threshold):
-        t = dict(self.thresholds_map)
-        t[target_op] = new_threshold
+        """The table a quantiser reads for this trial: every entry as it comes back from the text file. The
+        unrounded candidate stays the caller's (distance scale, returned best threshold), as in the reference."""
+        t = {k: through_table_text(v) for k, v in self.thresholds_map.items()}
+        t[target_op] = through_table_text(new_threshold)
         return t
 
     def update_to(self, dest_table, target_op, new_threshold):
+        trial = dict(self.thresholds_map)
+        trial[target_op] = new_threshold
         with open(dest_table, "w") as f:
-            for k, v in self.table_with(target_op, new_threshold).items():
+            for k, v in trial.items():
                 mn, mx = (self.activations_statistics.get(k) or (0.0, 0.0, 0.0))[:2]
                 f.write("{} {:.7f} {:.7f} {:.7f}\n".format(k, v, mn, mx))
 

@@ -78,13 +78,15 @@ class ClockSampler(threading.Thread):
         return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
 
 
-def cpu_path_images_per_s(model_b1, images, warmup=1):
+def cpu_path_images_per_s(model_b1, images, warmup=1, threads=None):
     """Times the reference-faithful CPU path (oracle/cpu_path.py: oneDNN fp32 convolution on integer-valued
-    floats, as the reference does with MKL-DNN, + the reference's own requantisation code, all host threads)
-    on `images` batch-1 passes, after checking one image bit for bit against the oracle."""
+    floats, as the reference does with MKL-DNN, + the reference's own requantisation code) on `images` batch-1
+    passes with `threads` host threads (default: all), after checking one image bit for bit against the oracle.
+    A thread count other than the default only takes full effect when OMP_NUM_THREADS was set to it before the
+    OpenMP runtimes loaded (see cpu_path_in_subprocess)."""
     import torch
     from oracle import cpu_path, graph_runner
-    torch.set_num_threads(os.cpu_count() or 1)
+    torch.set_num_threads(threads or os.cpu_count() or 1)
     rng = np.random.default_rng(4242)
     x = rng.uniform(-1, 1, (1, 3, 224, 224)).astype(np.float32)
     out = model_b1.outputs[0]
@@ -102,6 +104,21 @@ def cpu_path_images_per_s(model_b1, images, warmup=1):
     return images / dt, dt
 
 
+def cpu_path_in_subprocess(threads, images):
+    """The CPU arm at a fixed OpenMP thread count (the reference's regression scripts run at OMP_NUM_THREADS=4,
+    regression/run_regression.sh:14): a fresh process, so that the variable is seen by every OpenMP runtime it loads."""
+    env = dict(os.environ, OMP_NUM_THREADS=str(threads))
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
+        env.pop(k, None)
+    out = subprocess.run([sys.executable, os.path.abspath(__file__), "--impl", "reference", "--steps", str(images),
+                          "--warmup", "1", "--cpu-threads", str(threads)], capture_output=True, text=True, env=env,
+                         timeout=900)
+    for line in out.stdout.splitlines():
+        if line.startswith("{"):
+            return json.loads(line)
+    raise RuntimeError("the CPU arm printed no result: " + out.stderr[-400:])
+
+
 def run_reference(args, rank, world):
     """--impl reference: the reference's CPU path for the same workload. The reference binary needs
     MLIR/LLVM, MKL-DNN 1.0.2 and cnpy, none of which are vendored, so the arm runs the CPU oracle
@@ -110,8 +127,8 @@ def run_reference(args, rank, world):
         return
     from tpu_compiler_b200 import graphs
     model = graphs.resnet50_int8(batch=1, seed=1001)
-    threads = os.cpu_count() or 1
-    ips, dt = cpu_path_images_per_s(model, args.steps, warmup=max(args.warmup, 1))
+    threads = args.cpu_threads or os.cpu_count() or 1
+    ips, dt = cpu_path_images_per_s(model, args.steps, warmup=max(args.warmup, 1), threads=threads)
     line = {
         "impl": "reference", "metric": "INT8 ResNet-50 images/sec", "value": ips, "unit": "images/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
@@ -127,22 +144,18 @@ def run_reference(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
-def run_calibration(args, rank, world, local_rank):
-    """--workload calibration: the calibration pass (fp32 ResNet-50 forward, running min / max, 2048-bin |x|
-    histograms, KLD threshold search) over `--cal-images` synthetic images per GPU in batches of 64, every
-    rank on its own shard, statistics combined by all-reduce. Wall clock through the public calibrator API,
-    host input batches included (they are uploaded per batch, once per pass)."""
+def calibration_record(rank, world, local_rank, dist, images_per_gpu, bs, check_images=64):
+    """The calibration pass (fp32 ResNet-50 forward, running min / max, 2048-bin |x| histograms, KLD threshold
+    search) over `images_per_gpu` synthetic images per GPU in batches of `bs`, every rank on its own shard,
+    statistics combined by all-reduce. Wall clock through the public calibrator API, host input batches included
+    (uploaded per batch, once per pass), max over ranks. Then, untimed, the rank-count check: a set of
+    `check_images` images calibrated by all ranks together (each on its slice, combined by the two all-reduces)
+    must give the histograms and thresholds that rank 0 gets from the whole set on its own. Every rank calls this;
+    the returned record is complete on rank 0."""
     import torch
-    dist = None
-    if world > 1:
-        import torch.distributed as dist_mod
-        torch.cuda.set_device(local_rank)
-        dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-        dist = dist_mod
     from tpu_compiler_b200 import graphs, module
     from tpu_compiler_b200.calibration import ActivationCalibrator
-    bs = args.cal_batch
-    n_batches = max(args.cal_images // bs, 1)
+    n_batches = max(images_per_gpu // bs, 1)
     model = graphs.resnet50_fp32(batch=bs)
     m = module(local_rank)
     m.load_text(model.text, model.weights)
@@ -165,9 +178,8 @@ def run_calibration(args, rank, world, local_rank):
     sampler = ClockSampler(local_rank)
     sampler.start()
     if dist is not None:
-        # untimed warm-up of the two collectives the pass uses (the first MAX / SUM all-reduce of a process sets up
-        # its NCCL channels), then the barrier that starts the timed region
-        # (with the shapes of the pass: NCCL prepares per message size; the first [T, 2] MAX cost 28 ms, later ones 0.5)
+        # untimed warm-up of the two collectives the pass uses, with the shapes of the pass (NCCL prepares per message
+        # size; the first [T, 2] MAX of a process cost 28 ms, later ones 0.5), then the barrier that starts the timed region
         w1 = torch.zeros((len(cal.names), 2), dtype=torch.float32, device="cuda")
         w2 = torch.zeros((len(cal.names), cal.bin_num), dtype=torch.int64, device="cuda")
         w3 = torch.zeros(1, dtype=torch.int64, device="cuda")
@@ -185,28 +197,79 @@ def run_calibration(args, rank, world, local_rank):
     thr = cal.find_threshold(hist, stats)
     torch.cuda.synchronize()
     t3 = time.perf_counter()
+    parts = dict(cal.pass1_host_s)
+    times = [t3 - t0, t1 - t0, t2 - t1, t3 - t2, parts["pinned_copy"], parts["wait_uploads"], parts["enqueue"],
+             parts["final_sync"]]
     if dist is not None:
         dist.barrier()
-        tt = torch.tensor([t3 - t0], dtype=torch.float64, device="cuda")
+        tt = torch.tensor(times, dtype=torch.float64, device="cuda")
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        total_s = float(tt.item())
-    else:
-        total_s = t3 - t0
+        times = [float(v) for v in tt.tolist()]
     clocks = sampler.stop()
     fwd_ms = m.time_launches(5) / 5
-    images = world * n_batches * bs
+    del cal, hist
+    m.close()
+    torch.cuda.empty_cache()
+
+    # ---- untimed: N ranks together against rank 0 alone on the same images
+    cb = 8
+    small = graphs.resnet50_fp32(batch=cb)
+    ms = module(local_rank)
+    ms.load_text(small.text, small.weights)
+    crng = np.random.default_rng(7777)
+    cdata = [np.clip(crng.standard_normal((cb, 3, 224, 224), dtype=np.float32), -3, 3) for _ in range(check_images // cb)]
+    mine = cdata[rank::world]
+    both = ActivationCalibrator(ms, lambda: iter(mine), dist=dist)
+    thr_n, stats_n = both.run()
+    hist_n = both.histograms.cpu().numpy()
+    equal = None
     if rank == 0:
+        alone = ActivationCalibrator(ms, lambda: iter(cdata), dist=None)
+        thr_1, stats_1 = alone.run()
+        hist_1 = alone.histograms.cpu().numpy()
+        equal = bool(np.array_equal(hist_n, hist_1) and all(thr_n[k] == thr_1[k] for k in thr_1) and
+                     all(tuple(stats_n[k]) == tuple(stats_1[k]) for k in stats_1) and both.num_samples == alone.num_samples)
+        del alone
+    del both
+    ms.close()
+    if dist is not None:
+        dist.barrier()
+    images = world * n_batches * bs
+    return {"value": images / times[0], "unit": "images/s", "images": images, "images_per_gpu": n_batches * bs,
+            "batch": bs, "tensors": len(thr), "seconds": times[0],
+            "phases_s": {"min_max_pass": times[1], "histogram_pass": times[2], "kld_search": times[3]},
+            "min_max_pass_host_s": {"pinned_copy": times[4], "wait_uploads": times[5], "enqueue": times[6],
+                                    "final_sync": times[7]},
+            "forward_ms_per_batch": fwd_ms, "clocks": clocks,
+            "collectives": "all-reduce(MAX) of packed min/max, all-reduce(SUM) of int64 histograms" if world > 1 else "none",
+            "equal_to_single_rank": equal,
+            "equality_check": "%d images in batches of %d: histograms, min/max and thresholds of %d rank(s) together "
+                              "against rank 0 alone, exact" % (check_images, cb, world)}
+
+
+def run_calibration(args, rank, world, local_rank):
+    """--workload calibration: one JSON line for the calibration pass (see calibration_record)."""
+    import torch
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        torch.cuda.set_device(local_rank)
+        dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        dist = dist_mod
+    rec = calibration_record(rank, world, local_rank, dist, args.cal_images, args.cal_batch)
+    if rank == 0:
+        n_batches = max(args.cal_images // args.cal_batch, 1)
         print(json.dumps({
-            "metric": "fp32 ResNet-50 calibration images/sec", "value": images / total_s, "unit": "images/s",
-            "n_gpus": world, "steps": n_batches, "warmup": 3, "ms_per_step": total_s / n_batches * 1e3,
+            "metric": "fp32 ResNet-50 calibration images/sec", "value": rec["value"], "unit": "images/s",
+            "n_gpus": world, "steps": n_batches, "warmup": 3, "ms_per_step": rec["seconds"] / n_batches * 1e3,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {"workload": "calibration: fp32 ResNet-50, %d images per GPU in batches of %d (N(0,1) clipped to "
                                    "[-3,3]), %d tensors, min/max pass + 2048-bin histogram pass + KLD search" %
-                                   (n_batches * bs, bs, len(cal.names)),
+                                   (rec["images_per_gpu"], rec["batch"], rec["tensors"]),
                        "parallelism": "image shards x%d, all-reduce(MAX) of min/max, all-reduce(SUM) of histograms" % world},
-            "phases_s": {"min_max_pass": t1 - t0, "histogram_pass": t2 - t1, "kld_search": t3 - t2},
-            "forward_ms_per_batch": fwd_ms, "thresholds": len(thr), "clocks": clocks}), flush=True)
-    m.close()
+            "phases_s": rec["phases_s"], "min_max_pass_host_s": rec["min_max_pass_host_s"],
+            "forward_ms_per_batch": rec["forward_ms_per_batch"], "thresholds": rec["tensors"],
+            "equal_to_single_rank": rec["equal_to_single_rank"], "clocks": rec["clocks"]}), flush=True)
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
@@ -314,6 +377,95 @@ def run_conv_sweep(args, local_rank):
         flush=True)
 
 
+def h2d_ceiling(nbytes, local_rank, barrier, max_over_ranks, world, reps=10):
+    """GB/s (all ranks together) of `reps` pinned host-to-device copies of `nbytes` each per rank, CUDA events."""
+    import torch
+    torch.cuda.set_device(local_rank)
+    host = torch.empty(nbytes, dtype=torch.uint8, pin_memory=True)
+    dev = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+    st = torch.cuda.Stream()
+    with torch.cuda.stream(st):
+        for _ in range(3):
+            dev.copy_(host, non_blocking=True)
+        st.synchronize()
+        barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(st)
+        for _ in range(reps):
+            dev.copy_(host, non_blocking=True)
+        b.record(st)
+        b.synchronize()
+    ms = max_over_ranks(a.elapsed_time(b))
+    barrier()
+    del host, dev
+    torch.cuda.empty_cache()
+    return world * nbytes * reps / (ms * 1e-3) / 1e9
+
+
+def graph_replay_rate(model, local_rank, inputs, steps, warmup=5):
+    """(ms per launch, kernels per launch) of a module under CUDA-graph replay, inputs resident."""
+    from tpu_compiler_b200 import module
+    m = module(local_rank)
+    m.load_text(model.text, model.weights)
+    for k, v in inputs.items():
+        m.set_tensor(k, v)
+    for _ in range(warmup):
+        m.invoke()
+    ms = m.time_launches(steps) / steps
+    kernels = m.kernel_count()
+    m.close()
+    return ms, kernels
+
+
+def batch1_record(local_rank, steps=200):
+    """BASELINE configuration C1 as written: ResNet-50 INT8, batch 1. Graph replay with the input resident, and the
+    synchronous public call sequence (set_tensor, invoke, get_tensor) per image."""
+    from tpu_compiler_b200 import graphs, module
+    model = graphs.resnet50_int8(batch=1, seed=1001)
+    x = np.random.default_rng(4243).uniform(-1, 1, (1, 3, 224, 224)).astype(np.float32)
+    m = module(local_rank)
+    m.load_text(model.text, model.weights)
+    m.set_tensor("data", x)
+    for _ in range(10):
+        m.invoke()
+    ms = m.time_launches(steps) / steps
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        m.set_tensor("data", x)
+        m.invoke()
+        m.get_tensor(model.outputs[0])
+    e2e_ms = (time.perf_counter() - t0) / steps * 1e3
+    kernels = m.kernel_count()
+    m.close()
+    return {"workload": "resnet50_v1_int8_224, batch 1 (configuration C1 as written), CUDA-graph replay",
+            "ms_per_launch": ms, "value": 1e3 / ms, "unit": "images/s", "kernels_per_launch": kernels,
+            "e2e_ms_per_image": e2e_ms, "e2e_value": 1e3 / e2e_ms,
+            "e2e_note": "set_tensor + invoke + get_tensor per image, synchronous, pageable host arrays"}
+
+
+def secondary_records(local_rank, steps=20):
+    """The other BASELINE configurations on one GPU (device-resident CUDA-graph replay; no CPU arm for them):
+    MobileNet-v2 batch 32, the YOLOv4-style graph batch 8 at 416 x 416, and the twelve points of the 3x3 op sweep."""
+    from tpu_compiler_b200 import graphs
+    out = {}
+    for key, builder, batch, res, lo in (("mobilenet_v2_int8_b32_224", graphs.mobilenet_v2_int8, 32, 224, -1.0),
+                                         ("yolov4_style_int8_bf16_b8_416", graphs.yolov4_style_int8, 8, 416, 0.0)):
+        model = builder(batch=batch, res=res, simulate=False)
+        x = np.random.default_rng(5).uniform(lo, 1, (batch, 3, res, res)).astype(np.float32)
+        ms, kernels = graph_replay_rate(model, local_rank, {"data": x}, steps)
+        out[key] = {"value": batch / (ms * 1e-3), "unit": "images/s", "ms_per_step": ms, "batch": batch,
+                    "kernels_per_step": kernels}
+    sweep = []
+    for n in (1, 8, 32):
+        for c, hw in ((64, 56), (128, 28), (256, 14), (512, 7)):
+            model = graphs.single_conv_i8(n=n, c_in=c, c_out=c, hw=hw, k=3, stride=1, pad=1, relu=True, seed=2000 + c + n)
+            ms, _ = graph_replay_rate(model, local_rank, {"x": model.meta["x"]}, 50, warmup=5)
+            sweep.append({"n": n, "c": c, "hw": hw, "us": ms * 1e3, "tops": 2.0 * n * hw * hw * c * c * 9 / (ms * 1e-3) / 1e12})
+    out["conv_sweep_3x3"] = {"unit": "TOP/s", "note": "back-to-back launches of one op: operands stay in L2",
+                             "cases": sweep}
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -323,6 +475,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-images", type=int, default=100, help="images of the bounded CPU-baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-threads", type=int, default=0, help="--impl reference: host threads (default: all)")
+    ap.add_argument("--no-extras", action="store_true", help="headline only: skip the batch-1 configuration, the "
+                    "secondary graphs, the link ceiling and the calibration sub-record")
     ap.add_argument("--case", default=None, help="conv_sweep only: one case as c,hw,n")
     ap.add_argument("--cal-images", type=int, default=512, help="calibration workload: images per GPU")
     ap.add_argument("--cal-batch", type=int, default=64, help="calibration workload: images per batch (64 in the "
@@ -332,6 +487,8 @@ def main():
                     help="resnet50 is the headline configuration; the others are the secondary graphs "
                          "(their lines carry no cpu_baseline)")
     args = ap.parse_args()
+    if args.cpu_threads:
+        os.environ["OMP_NUM_THREADS"] = str(args.cpu_threads)   # before any OpenMP runtime loads
     if args.workload == "conv_sweep":
         if args.impl == "ours" and int(os.environ.get("RANK", "0")) == 0:
             run_conv_sweep(args, int(os.environ.get("LOCAL_RANK", "0")))
@@ -458,6 +615,12 @@ def main():
     e2e = world * B * args.steps / e2e_s
     clocks = sampler.stop()
 
+    # ---- the host link's own ceiling for this step's upload: the same bytes from pinned memory with plain
+    # asynchronous copies and nothing else, all ranks at once (untimed for the headline)
+    h2d = None
+    if not args.no_extras:
+        h2d = h2d_ceiling(in_numel * 4, local_rank, barrier, max_over_ranks, world)
+
     line = None
     if rank == 0:
         # ---- per-kernel roofline from an eager pass with CUDA events around every op
@@ -489,7 +652,14 @@ def main():
         # DRAM bytes per conv launch from the committed ncu capture of one step at batch 64
         # (profiles/resnet50_int8_b64_dram_traffic.md: 10.09 MB read per launch, writes still dirty in L2 when the
         # kernel ends), scaled by the images per launch; null for the workloads that have no capture.
-        traffic = 10.09e6 * B / 64.0 if args.workload == "resnet50" else None  # reads scale with the images per launch
+        # DRAM traffic per launch: not captured in this run (a profiler capture of this size is out of bounds). The read
+        # side is the ncu figure of a whole step at batch 64 (10.09 MB of dram__bytes_read per tensor-core launch)
+        # scaled by the images per launch; ncu attributes no write-back to these kernels (their outputs are still
+        # dirty in L2 when they end), so the write side is the algorithmic output bytes.
+        traffic = None
+        if args.workload == "resnet50":
+            out_bytes = sum(float(np.prod(i["shape"])) for i in m.op_info if i["bound"] == "tensor") / max(n_conv, 1)
+            traffic = 10.09e6 * B / 64.0 + out_bytes
         if args.workload == "resnet50_bf16":
             # BF16 graph: the same pipeline with kind::f16 MMAs; the denominator is the measured bf16 rate itself
             roofline = {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
@@ -500,9 +670,13 @@ def main():
                         "avg_launch_us": conv_ms * 1e3 / max(n_conv, 1)}
         else:
             roofline = {"bound": "tensor", "achieved": achieved, "peak": int8_peak, "unit": "TOP/s",
-                        "frac": achieved / int8_peak, "traffic": traffic,
-                        "traffic_note": "ncu dram__bytes_read+write per launch at batch 64 x batch/64; algorithmic bytes "
-                                        "per launch: %.1f MB" % (conv_bytes / max(n_conv, 1) / 1e6),
+                        "frac": achieved / int8_peak,
+                        "peak_burst": 2.0 * peaks["bf16_tflops"], "frac_burst": achieved / (2.0 * peaks["bf16_tflops"]),
+                        "traffic": traffic,
+                        "traffic_note": "per launch: DRAM reads of an ncu capture of one step at batch 64 scaled by "
+                                        "batch / 64, plus the algorithmic output bytes (ncu attributes no write-back to "
+                                        "the kernel); not captured in this run. Algorithmic bytes per launch: %.1f MB"
+                                        % (conv_bytes / max(n_conv, 1) / 1e6),
                         "kernel": "conv_gemm_i8_kernel (tcgen05 kind::i8 implicit GEMM, %d launches per step)" % n_conv,
                         "peak_source": "2 x bf16_tflops_sustained of %s peaks (no INT8 figure is measured; the 8-bit "
                                        "rate of the same tensor pipe is twice the 16-bit rate)" % peaks["source"],
@@ -521,6 +695,15 @@ def main():
                    "sample": "%d batch-1 ResNet-50 INT8 forward passes (oneDNN fp32 convolution on integer-valued "
                              "floats + the reference's own requantisation code, checked against the oracle) in %.1f s"
                              % (args.cpu_images, dt)}
+        cpu4 = None
+        if cpu is not None and not args.no_extras:
+            try:
+                r4 = cpu_path_in_subprocess(4, max(args.cpu_images // 4, 8))
+                cpu4 = {"value": r4["value"], "unit": "images/s", "cores": 4, "kind": "port",
+                        "sample": "the same path in a fresh process with OMP_NUM_THREADS=4, the thread count of the "
+                                  "reference's regression scripts: " + r4["cpu_baseline"]["sample"]}
+            except Exception as e:   # the all-threads figure above stands on its own
+                cpu4 = {"unavailable": str(e)[:200]}
         act_bytes = sum(i["bytes"] for i in m.op_info)
         line = {
             "metric": wl["metric"], "value": value, "unit": "images/s", "n_gpus": world,
@@ -531,18 +714,33 @@ def main():
                        "global_batch": B * world, "parallelism": "replicas x%d (image shards, no data-path collective)" % world,
                        "l2": "per-step working set %.0f MB exceeds the 126 MB L2" % (act_bytes / 1e6),
                        "cuda_graph": True},
-            "e2e": {"value": e2e, "unit": "images/s", "h2d_bytes_per_step": in_numel * 4, "d2h_bytes_per_step": out_numel * 4},
+            "e2e": {"value": e2e, "unit": "images/s", "h2d_bytes_per_step": in_numel * 4, "d2h_bytes_per_step": out_numel * 4,
+                    "h2d_ceiling_gbs": h2d,
+                    "h2d_link_frac": (e2e * in_numel * 4 / B / 1e9 / h2d) if h2d else None,
+                    "h2d_note": "ceiling: the same bytes per rank as plain pinned asynchronous copies, all ranks at "
+                                "once, CUDA events; link_frac = the end-to-end run's upload rate over it"},
             "gpu_launches": m.kernel_count() * args.steps,
             "clocks": clocks,
             "roofline": roofline,
             "memory_bound_kernels": mem_kernels,
             "cpu_baseline": cpu,
+            "cpu_baseline_omp4": cpu4,
         }
     check(L.tpucb_host_free(hin))
     check(L.tpucb_host_free(hin2))
     for _, h, _ in houts:
         check(L.tpucb_host_free(h))
     m.close()
+    if not args.no_extras and args.workload == "resnet50":
+        if line is not None and world == 1:
+            line["c1_batch1"] = batch1_record(local_rank)
+            line["secondary"] = secondary_records(local_rank)
+        # the calibration half of the path (the only part with collectives), at every N: all ranks take part
+        import torch
+        torch.cuda.empty_cache()
+        rec = calibration_record(rank, world, local_rank, dist, 256, 64)
+        if line is not None:
+            line["calibration"] = rec
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()

@@ -379,6 +379,27 @@ def lut_i8(x, table):
     return out
 
 
+def batchnorm_f32(x, mean, variance, scale0, eps):
+    """BatchNormOpKernel, fp32 (core/batchnorm.cpp:20-68)."""
+    x = _f32(x)
+    n, c = x.shape[0], x.shape[1]
+    out = np.empty_like(x)
+    lib().orc_batchnorm_f32(_p(x), _p(_f32(mean)), _p(_f32(variance)), C.c_float(scale0), C.c_float(eps), _p(out), n, c,
+                            x.size // (n * c))
+    return out
+
+
+def reduce_l2_f32(x, axes, coeff):
+    """ReduceL2 over consecutive axes, fp32 (core/reduce.cpp:91-103); the reduced axes are dropped."""
+    x = _f32(x)
+    outer = int(np.prod(x.shape[:axes[0]], dtype=np.int64))
+    axis = int(np.prod(x.shape[axes[0]:axes[-1] + 1], dtype=np.int64))
+    inner = int(np.prod(x.shape[axes[-1] + 1:], dtype=np.int64))
+    out = np.empty(outer * inner, np.float32)
+    lib().orc_reduce_l2_f32(_p(x), outer, axis, inner, C.c_float(coeff), _p(out))
+    return out.reshape(x.shape[:axes[0]] + x.shape[axes[-1] + 1:])
+
+
 def scale_f32(x, scale, bias=None):
     x = _f32(x)
     out = np.empty_like(x)

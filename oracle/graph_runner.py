@@ -150,6 +150,10 @@ def run(text, weights, inputs, upto=None):
             out = O.lut_bf16_mantissa(X(0), W(1)[:256], W(2)[:256])
         elif t == "scale":
             out = O.scale_f32(X(0), W(1), W(2))
+        elif t == "batchnorm":
+            out = O.batchnorm_f32(X(0), W(1), W(2), float(W(3).reshape(-1)[0]), float(a.get("variance_epsilon", 1e-5)))
+        elif t == "reduce_l2":
+            out = O.reduce_l2_f32(X(0), [int(v) for v in a["axes"].split(",")], float(a.get("coeff", 0.5)))
         elif t == "softmax":
             if op["dtype"] == "BF16":
                 out = O.softmax_bf16(X(0), W(1), W(2), W(3), W(4), axis=_i(a, "axis", 1), do_log=bool(_i(a, "do_log")))

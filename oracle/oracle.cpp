@@ -570,7 +570,8 @@ void orc_batchnorm_f32(const float *in, const float *mean, const float *var, flo
       for (int i = 0; i < hw; ++i) {
         size_t o = ((size_t)b * c + ch) * hw + i;
         float x = in[o] - m;
-        out[o] = (float)(x / sqrt(v + eps));
+        float d = std::sqrt(v + eps); // `auto d = sqrt(float)`: the float overload
+        out[o] = x / d;
       }
     }
 }
@@ -785,6 +786,17 @@ void orc_reduce(const float *in, int outer, int axis, int inner, int type, int i
       if (is_int8 && (rshift != 0 || multiplier != 1))
         v = (float)orc_mul_rshift_f32(v, (uint32_t)rshift, (uint32_t)multiplier);
       out[(size_t)o * inner + i] = v;
+    }
+}
+
+// REDUCE_L2 in fp32 (core/reduce.cpp:91-103): `sum += std::pow(x, 2)` promotes to double (the square is exact
+// there) and rounds the running sum to float at every step; the result is std::pow(sum, coeff) on floats.
+void orc_reduce_l2_f32(const float *in, int outer, int axis, int inner, float coeff, float *out) {
+  for (int o = 0; o < outer; ++o)
+    for (int i = 0; i < inner; ++i) {
+      float sum = 0.0f;
+      for (int a = 0; a < axis; ++a) sum += std::pow(in[((size_t)o * axis + a) * inner + i], 2);
+      out[(size_t)o * inner + i] = std::pow(sum, coeff);
     }
 }
 

@@ -292,3 +292,17 @@ def test_conv_fp32_fma_path_with_option_off():
         m.close()
         assert err <= (2e-5 if opt else 2e-6), (opt, err)
     assert counts[1] == counts[0] + 1
+
+
+def test_batchnorm_and_reduce_l2_fp32():
+    """BatchNormOpKernel (core/batchnorm.cpp:20-68) and ReduceL2 (core/reduce.cpp:91-103), fp32 as in the reference."""
+    rng = np.random.default_rng(88)
+    shape = (3, 21, 6, 5)
+    b = graphs.GraphBuilder(88, simulate=False)
+    b.op("input", "f", [], shape, "FP32")
+    b.weight("mean", rng.normal(0, 1, 21)), b.weight("var", rng.uniform(0.05, 3, 21)), b.weight("sc", [0.9])
+    b.op("batchnorm", "bn", ["f", "mean", "var", "sc"], shape, "FP32", variance_epsilon=1e-5)
+    b.op("reduce_l2", "l2_c", ["bn"], (3, 6, 5), "FP32", axes="1", coeff=0.5)
+    b.op("reduce_l2", "l2_hw", ["f"], (3, 21), "FP32", axes="2,3", coeff=0.5)
+    out = run_both(b.text(), b.weights, {"f": rng.normal(0, 2, shape).astype(np.float32)}, ["bn", "l2_c", "l2_hw"])
+    assert_close(out, rtol=1e-6)

@@ -103,3 +103,21 @@ def test_matmul_oracle_against_numpy():
     hi = np.floor((np.maximum(exp, 0).astype(np.int64) * 2 ** 30 + 2 ** 30) / 2.0 ** 31).astype(np.int64)
     ref = np.clip((hi + 256) >> 9, -128, 127)
     assert np.array_equal(q, ref.astype(np.float32))
+
+
+def test_batchnorm_and_reduce_l2_against_numpy():
+    """core/batchnorm.cpp:20-68 and the REDUCE_L2 case of core/reduce.cpp:91-103 written out with numpy in the
+    reference's operation order and types."""
+    rng = np.random.default_rng(8)
+    x = rng.normal(0, 2, (2, 5, 3, 4)).astype(np.float32)
+    mean, var = rng.normal(0, 1, 5).astype(np.float32), rng.uniform(0.1, 2, 5).astype(np.float32)
+    scale0, eps = np.float32(0.8), np.float32(1e-5)
+    sf = np.float32(1) / scale0
+    m = (mean * sf).reshape(1, 5, 1, 1)
+    d = np.sqrt(var * sf + eps).astype(np.float32).reshape(1, 5, 1, 1)
+    assert np.array_equal(O.batchnorm_f32(x, mean, var, float(scale0), float(eps)), (x - m) / d)
+    got = O.reduce_l2_f32(x, [1], 0.5)
+    s = np.zeros((2, 3, 4), np.float32)
+    for c in range(5):
+        s = (s.astype(np.float64) + x[:, c].astype(np.float64) ** 2).astype(np.float32)
+    assert np.allclose(got, np.sqrt(s), rtol=2e-7) and got.shape == (2, 3, 4)

@@ -18,6 +18,7 @@ Batches beyond the budget are recomputed as before. The values read are the same
 """
 import ctypes as C
 import datetime
+import time
 
 import numpy as np
 import torch
@@ -48,6 +49,9 @@ class ActivationCalibrator:
         self._pinned_numel = 0
         self._pinned_next = 0
         self._reserved = []      # cache buffers allocated ahead of pass 1
+        # host seconds of this rank's last pass 1 by part: copying batches into pinned memory, waiting for earlier
+        # uploads to leave their buffer, enqueueing (module launch + statistics launch), the final synchronisation
+        self.pass1_host_s = {"pinned_copy": 0.0, "wait_uploads": 0.0, "enqueue": 0.0, "final_sync": 0.0}
         if self._lib is not None:
             # the two pinned upload buffers are part of setting up (tens of milliseconds), not of a pass
             self._alloc_pinned(int(np.prod(model.get_tensor_shape(self.input_name))))
@@ -73,8 +77,10 @@ class ActivationCalibrator:
         n_img = 0
         self._kept = []
         per_batch, budget = self._keep_plan()
+        self.pass1_host_s = {k: 0.0 for k in self.pass1_host_s}
         for batch in self.batches():
             self._upload(batch)
+            t_enq = time.perf_counter()
             self.model.launch()
             keep = None
             if self._reserved:
@@ -96,7 +102,10 @@ class ActivationCalibrator:
                 # handed back to torch before the module's stream has been synchronised (end of this pass and of pass 2)
                 self._kept.append((keep, batch.shape[0]))
             n_img += batch.shape[0]
+            self.pass1_host_s["enqueue"] += time.perf_counter() - t_enq
+        t_sync = time.perf_counter()
         self.model.sync()
+        self.pass1_host_s["final_sync"] += time.perf_counter() - t_sync
         self._local_images = n_img
         return stats, n_img
 
@@ -129,9 +138,15 @@ class ActivationCalibrator:
             self._alloc_pinned(batch.size)
         h = self._pinned[self._pinned_next]
         self._pinned_next ^= 1
+        t0 = time.perf_counter()
         self.model.wait_uploads()   # earlier copies have left the host buffers
+        t1 = time.perf_counter()
         np.copyto(np.ctypeslib.as_array(C.cast(h, C.POINTER(C.c_float)), shape=(batch.size,)), batch.reshape(-1))
+        t2 = time.perf_counter()
         self.model.set_tensor_async(self.input_name, h, batch.size)
+        self.pass1_host_s["wait_uploads"] += t1 - t0
+        self.pass1_host_s["pinned_copy"] += t2 - t1
+        self.pass1_host_s["enqueue"] += time.perf_counter() - t2
 
     def _alloc_pinned(self, numel):
         self._free_pinned()

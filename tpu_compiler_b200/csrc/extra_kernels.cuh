@@ -181,9 +181,10 @@ __global__ void remap_kernel(const uint8_t *__restrict__ in, uint8_t *__restrict
 struct ReduceArgs {
   TensorGeom gi, go;
   int outer, axis, inner;
-  int type; // 0 mean, 1 sum, 2 max, 3 min
+  int type; // 0 mean, 1 sum, 2 max, 3 min, 4 l2 (fp32 only: (sum of squares) ^ coeff)
   int dt;   // DT_I8 or DT_F32
   int mult, rshift, requant;
+  float coeff;
 };
 __global__ void reduce_kernel(const void *__restrict__ in, void *__restrict__ out, ReduceArgs p) {
   const size_t total = (size_t)p.outer * p.inner;
@@ -205,11 +206,14 @@ __global__ void reduce_kernel(const void *__restrict__ in, void *__restrict__ ou
       float v = 0.0f;
       for (int a = 0; a < p.axis; ++a) {
         const float x = reinterpret_cast<const float *>(in)[phys_offset(p.gi, (o * p.axis + a) * p.inner + i)];
-        if (p.type <= 1) v = __fadd_rn(v, x);
+        // l2 (core/reduce.cpp:91-103): `sum += std::pow(x, 2)` squares in double (exact) and rounds the sum to fp32
+        if (p.type == 4) v = __double2float_rn((double)v + (double)x * (double)x);
+        else if (p.type <= 1) v = __fadd_rn(v, x);
         else if (a == 0) v = x;
         else v = p.type == 2 ? fmaxf(v, x) : fminf(v, x);
       }
       if (p.type == 0) v = __fdiv_rn(v, (float)p.axis);
+      if (p.type == 4) v = powf(v, p.coeff);
       reinterpret_cast<float *>(out)[po] = v;
     }
   }

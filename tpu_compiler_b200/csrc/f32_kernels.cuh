@@ -314,6 +314,16 @@ __global__ void scale_f32_kernel(const float *__restrict__ in, const float *__re
   }
 }
 
+// BatchNormOpKernel (core/batchnorm.cpp:20-68): (x - mean') / d per channel, with mean' and d = sqrt(var' + eps)
+// prepared per channel by the host in fp32 as the reference forms them; a subtraction and an IEEE division per value.
+__global__ void batchnorm_f32_kernel(const float *__restrict__ in, const float *__restrict__ mean, const float *__restrict__ den,
+                                     float *__restrict__ out, size_t n, int cp) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    int c = (int)(i % cp);
+    out[i] = __fdiv_rn(__fsub_rn(in[i], mean[c]), den[c]);
+  }
+}
+
 // softmax over the channel axis of one pixel per CTA.
 __global__ void softmax_f32_kernel(const float *__restrict__ in, float *__restrict__ out, int c, int cp) {
   __shared__ float red[32];

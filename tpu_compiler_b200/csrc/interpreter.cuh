@@ -1393,8 +1393,12 @@ public:
                 op.name.c_str(), out->numel(), outer * inner);
     p_.gi = geom_of(in); p_.go = geom_of(out);
     p_.outer = (int)outer; p_.axis = (int)axis; p_.inner = (int)inner;
-    p_.type = op.type == "reduce_mean" ? 0 : (op.type == "reduce_sum" ? 1 : (op.type == "reduce_max" ? 2 : 3));
+    p_.type = op.type == "reduce_mean" ? 0 : (op.type == "reduce_sum" ? 1 : (op.type == "reduce_max" ? 2 : (op.type == "reduce_min" ? 3 : 4)));
     p_.dt = out->dtype;
+    p_.coeff = (float)op.getf("coeff", 0.5);
+    // reduce_l2 ends in pow(sum, coeff) on the fp32 sum; the INT8 form would requantise that float and the BF16 form
+    // goes through lookup tables: only the fp32 form is implemented
+    TPUCB_CHECK(p_.type != 4 || out->dtype == DT_F32, "reduce_l2 %s: only fp32 is implemented", op.name.c_str());
     p_.mult = 1; p_.rshift = 0;
     if (out->dtype == DT_I8) {
       // operands: input, quant_scale, quant_zeropoint, quant_rshift, quant_multiplier
@@ -1498,6 +1502,41 @@ private:
   Interpreter &I_;
   TensorPtr in_, out_;
   const float *d_s_ = nullptr, *d_b_ = nullptr;
+};
+
+// BatchNormOpKernel (core/batchnorm.cpp:6-68), fp32 only as in the reference ("other mode please fused batchnorm").
+// Operands: input, mean, variance, scale (one value). The reference scales mean and variance by 1 / scale[0] in
+// fp32 for the duration of the call; the per-channel mean' and d = sqrt(variance' + epsilon) are formed here, once,
+// with the same fp32 operations.
+class BatchNormOp : public OpKernel {
+public:
+  BatchNormOp(Interpreter &I, const ParsedOp &op, TensorPtr in, TensorPtr out) : I_(I), in_(in), out_(out) {
+    TPUCB_CHECK(in->dtype == DT_F32 && out->dtype == DT_F32, "batchnorm %s: fp32 only (as the reference)", op.name.c_str());
+    TPUCB_CHECK(op.in.size() >= 4, "batchnorm %s: expects input, mean, variance, scale", op.name.c_str());
+    const auto &mean = I.weight(op.in[1]).data, &var = I.weight(op.in[2]).data, &scale = I.weight(op.in[3]).data;
+    TPUCB_CHECK((int)mean.size() >= in->c && (int)var.size() >= in->c && !scale.empty(),
+                "batchnorm %s: mean / variance need %d values and scale one", op.name.c_str(), in->c);
+    const float eps = (float)op.getf("variance_epsilon", 1e-5);
+    const float sf = 1.0f / scale[0];
+    std::vector<float> m(in->cp, 0.0f), d(in->cp, 1.0f);
+    for (int c = 0; c < in->c; ++c) {
+      m[c] = mean[c] * sf;
+      const float v = var[c] * sf;
+      d[c] = sqrtf(v + eps);
+    }
+    d_m_ = I.upload(m);
+    d_d_ = I.upload(d);
+    alg_bytes = 8.0 * out->numel();
+  }
+  void invoke(cudaStream_t s) override {
+    size_t n = out_->bytes() / 4;
+    batchnorm_f32_kernel<<<grid_for(n, 256, I_.sm_count), 256, 0, s>>>((const float *)in_->dev, d_m_, d_d_, (float *)out_->dev, n, out_->cp);
+  }
+
+private:
+  Interpreter &I_;
+  TensorPtr in_, out_;
+  const float *d_m_ = nullptr, *d_d_ = nullptr;
 };
 
 class SoftmaxOp : public OpKernel {
@@ -1814,7 +1853,8 @@ inline void Interpreter::load_module(const std::string &text) {
       k.reset(new BroadcastOp(*this, op, opd(0), opd(1), out));
     } else if (op.type == "pad" || op.type == "crop" || op.type == "permute") {
       k.reset(new RemapOp(*this, op, opd(0), out));
-    } else if (op.type == "reduce_mean" || op.type == "reduce_sum" || op.type == "reduce_max" || op.type == "reduce_min") {
+    } else if (op.type == "reduce_mean" || op.type == "reduce_sum" || op.type == "reduce_max" || op.type == "reduce_min" ||
+               op.type == "reduce_l2") {
       k.reset(new ReduceOp(*this, op, opd(0), out));
     } else if (op.type == "matmul") {
       k.reset(new MatMulOp(*this, op, opd(0), opd(1), out));
@@ -1839,6 +1879,8 @@ inline void Interpreter::load_module(const std::string &text) {
       k.reset(new LutOp(*this, op, opd(0), out));
     } else if (op.type == "scale") {
       k.reset(new ScaleOp(*this, op, opd(0), out));
+    } else if (op.type == "batchnorm") {
+      k.reset(new BatchNormOp(*this, op, opd(0), out));
     } else if (op.type == "softmax") {
       k.reset(new SoftmaxOp(*this, op, opd(0), out));
     } else {

@@ -36,6 +36,16 @@ int tpucb_version(void);
  * (MlirModuleInterpreter.h:35). `device` is the CUDA ordinal; the interpreter owns
  * one stream and every device tensor of the module. */
 int tpucb_interp_create(int device, tpucb_interp **out);
+/* The same with max_batch_size > 1 (MlirModuleInterpreter.h:35, CPUOpKernel::max_batch_size cpukernel.h:153): the
+ * reference then keeps max_batch_size copies ("batch slots") of every activation (TensorData, cpukernel.h:15-78) and
+ * runs its kernels on one slot at a time (set_batch_idx). Here slot b is image group b of ONE device tensor whose
+ * leading dimension is max_batch_size x the module's, so a launch covers every slot. The tensor shapes, input / output
+ * sizes and op shapes reported by the calls below stay the module's (one slot). Ops that may mix the leading
+ * dimension with the others (matmul, permute, reduce, pad, crop, broadcast) are refused at load on such an
+ * interpreter. tpucb_interp_set_tensor / get_tensor without a slot address all slots at once (max_batch_size x the
+ * slot's values, slot-major). */
+int tpucb_interp_create_batched(int device, int max_batch_size, tpucb_interp **out);
+int tpucb_interp_max_batch_size(tpucb_interp *it, int *max_batch_size);
 int tpucb_interp_destroy(tpucb_interp *it);
 
 /* MlirModuleInterpreter::updateWeightMap (MlirModuleInterpreter.cpp:352-369): register
@@ -53,6 +63,43 @@ int tpucb_interp_load_module(tpucb_interp *it, const char *module_text);
 
 /* MlirModuleInterpreter::setTensor (MlirModuleInterpreter.cpp:407-417). */
 int tpucb_interp_set_tensor(tpucb_interp *it, const char *name, const float *data, size_t numel);
+/* setTensor / getTensor with their bidx argument (MlirModuleInterpreter.cpp:407-427; TensorData::assign and
+ * TensorData::tensor, cpukernel.h:49-67): the values of batch slot `bidx`, numel = the module's tensor size. */
+int tpucb_interp_set_tensor_slot(tpucb_interp *it, const char *name, const float *data, size_t numel, int bidx);
+int tpucb_interp_get_tensor_slot(tpucb_interp *it, const char *name, float *out, size_t numel, int bidx);
+/* invokeTo(name, bidx) / invoke(bidx) (MlirModuleInterpreter.cpp:371-381; NULL or "" = the whole module). The
+ * reference runs the kernels on slot bidx only; one launch here computes every slot, so slot bidx holds what the
+ * reference would have produced and the other slots the results for whatever inputs they hold. Synchronous. */
+int tpucb_interp_invoke_slot(tpucb_interp *it, const char *name, int bidx);
+/* fastInvokeAllBatch(name, batch) (MlirModuleInterpreter.cpp:383-405): every op built since the last such call (the
+ * "dirty" ones, cpukernel.h:152) up to `name`, for the slots 0..batch-1: ONE launch per op over all slots instead of
+ * the reference's loop over the slots. Synchronous. */
+int tpucb_interp_fast_invoke_all_batch(tpucb_interp *it, const char *name, int batch);
+/* MlirModuleInterpreter::dump(name) / CPUOpKernel::dump (cpukernel.h:126): a text description of one op (name,
+ * type, data type, shape, the line it was built from). *needed receives the required capacity. */
+int tpucb_interp_dump(tpucb_interp *it, const char *name, char *out, size_t cap, size_t *needed);
+
+/* ---- CPUOpKernel (include/tpuc/Interpreter/cpukernel.h:87-159) ------------------------------------
+ * One op at a time, for an adapter that subclasses the reference's CPUOpKernel and owns a single op. The interpreter
+ * handle plays the part of the (value_map_t, weight_map_t) pair the reference constructors receive: operands are looked
+ * up in it by name, the result tensor is created in it and becomes visible to later ops; weights are registered with
+ * tpucb_interp_set_weight beforehand. */
+typedef struct tpucb_op tpucb_op;
+/* CPUOpKernel::CPUOpKernel(Operation &, value_map_t &, weight_map_t &) (cpukernel.h:90): `op_line` is one line of the
+ * module text of tpucb_interp_load_module. An op the backend does not implement is an error here. Ops created this
+ * way also run as part of tpucb_interp_invoke, in creation order; they are not fused with their neighbours. The handle
+ * belongs to the interpreter (freed by tpucb_interp_destroy, invalidated by tpucb_interp_load_module). */
+int tpucb_op_create(tpucb_interp *ctx, const char *op_line, tpucb_op **out);
+/* CPUOpKernel::invoke() (cpukernel.h:101): runs this op on its operands' current values, all batch slots. Synchronous. */
+int tpucb_op_invoke(tpucb_op *op);
+/* CPUOpKernel::set_tensor (cpukernel.h:97; implemented by the input op only, core/input.cpp:17-24) and get_tensor
+ * (deep copy, cpukernel.h:130-134), for batch slot bidx. */
+int tpucb_op_set_tensor(tpucb_op *op, const float *data, size_t numel, int bidx);
+int tpucb_op_get_tensor(tpucb_op *op, float *out, size_t numel, int bidx);
+/* get_name / get_op_type / get_data_type / get_shape and the dirty flag (cpukernel.h:103-124, 144-152) as
+ * "name\ttype\tdtype\tshape\tdirty". */
+int tpucb_op_info(tpucb_op *op, char *out, size_t cap, size_t *needed);
+
 /* Pipelined setTensor for serving loops (no reference counterpart): the copy from PINNED host
  * memory runs on a second stream and overlaps a module launch that is still executing; the data
  * becomes the tensor's value for the next launch. The host buffer must stay untouched until

@@ -15,3 +15,10 @@ def pytest_configure(config):
 @pytest.fixture(scope="session")
 def golden_dir():
     return os.path.join(ROOT, "tests", "golden")
+
+
+def reference_dir():
+    """The reference checkout when one is reachable (TPUC_REFERENCE_DIR, or a directory named ``reference`` beside
+    this repository), else None: tests that read its fixtures as text skip without it."""
+    cand = os.environ.get("TPUC_REFERENCE_DIR") or os.path.join(os.path.dirname(ROOT), "reference")
+    return cand if os.path.isdir(os.path.join(cand, "lib", "Dialect", "TPU")) else None

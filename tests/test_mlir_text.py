@@ -56,3 +56,32 @@ def test_convert_generic_form():
 def test_attr_parser_nested():
     d = mlir_text._AttrParser('{axis = 1 : i32, name = "c", q = {mode = "INT8", t = 1.500000e+00 : f32}, o = [ 1 : i32, 0 : i32 ], f = false}').dict()
     assert d == {"axis": 1, "name": "c", "q": {"mode": "INT8", "t": 1.5}, "o": [1, 0], "f": False}
+
+
+def test_reference_backend_fixtures_parse():
+    """Format test on the reference's own single-op graphs (lib/Dialect/TPU/Backend/test/*.mlir), read as text where
+    a checkout is reachable: every file converts, and the ones made only of ops this backend implements are
+    counted (those are the graphs the command line can run)."""
+    import glob
+    import os
+    import pytest
+    from .conftest import reference_dir
+    ref = reference_dir()
+    if ref is None:
+        pytest.skip("no reference checkout reachable")
+    files = sorted(glob.glob(os.path.join(ref, "lib", "Dialect", "TPU", "Backend", "test", "*.mlir")))
+    assert len(files) >= 30
+    implemented = {"input", "quant", "conv_2d", "deconv_2d", "fully_connected", "pool_max_2d", "pool_avg_2d", "eltwise_add",
+                   "eltwise_mul", "eltwise_max", "eltwise_min", "broadcast_add", "broadcast_sub", "broadcast_mul", "pad",
+                   "crop", "permute", "reduce_mean", "reduce_sum", "reduce_max", "reduce_min", "reduce_l2", "matmul",
+                   "concat", "upsample", "pixelshuffle", "relu", "leaky_relu", "sigmoid", "mish", "exp", "tanh",
+                   "reciprocal", "scale", "batchnorm", "softmax", "reshape"}
+    runnable = 0
+    for f in files:
+        with open(f) as fh:
+            text, _ = mlir_text.convert(fh.read())
+        ops = graph_runner.parse(text)
+        assert ops and ops[0]["type"] == "input", f
+        assert all(o["shape"] for o in ops), f
+        runnable += all(o["type"] in implemented for o in ops)
+    assert runnable >= 19

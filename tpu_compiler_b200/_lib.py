@@ -26,7 +26,19 @@ def _declare(lib):
     sigs = {
         "tpucb_version": [],
         "tpucb_interp_create": [C.c_int, C.POINTER(vp)],
+        "tpucb_interp_create_batched": [C.c_int, C.c_int, C.POINTER(vp)],
+        "tpucb_interp_max_batch_size": [vp, ip],
         "tpucb_interp_destroy": [vp],
+        "tpucb_interp_set_tensor_slot": [vp, cp, fp, sz, C.c_int],
+        "tpucb_interp_get_tensor_slot": [vp, cp, fp, sz, C.c_int],
+        "tpucb_interp_invoke_slot": [vp, cp, C.c_int],
+        "tpucb_interp_fast_invoke_all_batch": [vp, cp, C.c_int],
+        "tpucb_interp_dump": [vp, cp, cp, sz, szp],
+        "tpucb_op_create": [vp, cp, C.POINTER(vp)],
+        "tpucb_op_invoke": [vp],
+        "tpucb_op_set_tensor": [vp, fp, sz, C.c_int],
+        "tpucb_op_get_tensor": [vp, fp, sz, C.c_int],
+        "tpucb_op_info": [vp, cp, sz, szp],
         "tpucb_interp_set_weight": [vp, cp, fp, i64p, C.c_int],
         "tpucb_interp_load_module": [vp, cp],
         "tpucb_interp_set_tensor": [vp, cp, fp, sz],

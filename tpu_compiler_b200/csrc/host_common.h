@@ -50,6 +50,7 @@ struct DevTensor {
   int dtype = 2; // DType
   std::vector<int64_t> shape;
   int n = 1, c = 1, h = 1, w = 1, cp = 1;
+  int slot_n = 1; // leading-dimension extent of one batch slot (n / the interpreter's max_batch_size)
   // Physical row layout: `wl` zero pixels, the w real pixels, then zeros up to `wphys` pixels.
   // Every tensor has wl = 0, wphys = w except the input of a few-channel stem convolution.
   int wl = 0, wphys = 1;

@@ -26,6 +26,7 @@ struct ParsedOp {
   std::vector<int64_t> shape;
   std::string dtype = "FP32";
   Attrs attrs;
+  std::string line; // the text the op was parsed from
   int geti(const char *k, int def = 0) const {
     auto it = attrs.find(k);
     return it == attrs.end() ? def : atoi(it->second.c_str());
@@ -64,6 +65,8 @@ public:
   int datatype = DT_F32;
   TensorPtr result;
   double alg_ops = 0, alg_bytes = 0; // algorithmic work of one invoke (for roofline reports)
+  bool dirty = true;                 // cpukernel.h:152: not yet run since it was built (fastInvokeAllBatch clears it)
+  std::string line;                  // the module-text line the op was built from (dump)
 };
 
 inline int dtype_from_string(const std::string &s) {
@@ -185,8 +188,17 @@ public:
   }
 
   void load_module(const std::string &text);
-  void set_tensor(const std::string &name, const float *data, size_t numel);
-  void get_tensor(const std::string &name, float *out, size_t numel);
+  // one op of the module: builds its kernel from the operands already present and registers its result
+  // (the body of the CPUOpKernel constructors, cpukernel.h:89-90); returns the index in `kernels`, or -1 for a
+  // reshape, which is an alias and has no kernel
+  int add_op(const ParsedOp &op);
+  void reset_module();
+  void finish_module();
+  // slot < 0: the whole tensor (every batch slot); else the images of one slot (MlirModuleInterpreter::setTensor /
+  // getTensor with bidx, MlirModuleInterpreter.cpp:407-427)
+  void set_tensor(const std::string &name, const float *data, size_t numel, int slot = -1);
+  void get_tensor(const std::string &name, float *out, size_t numel, int slot = -1);
+  void fast_invoke_all_batch(const std::string &name, int batch);
   void launch_all();
   void launch_to(const std::string &name);
   void sync_and_check();
@@ -198,6 +210,12 @@ public:
   }
 
   int device_;
+  // MlirModuleInterpreter(int32_t batch) (MlirModuleInterpreter.h:35): the reference keeps `batch` copies ("slots") of
+  // every activation and runs the kernels on one slot at a time. Here slot b is image group b of ONE device tensor
+  // whose leading dimension is max_batch x the module's, so one launch covers every slot.
+  int max_batch = 1;
+  std::map<std::string, std::string> producer_type;
+  std::map<std::string, int> uses;
   int sm_count = 148;
   cudaStream_t stream = nullptr;
   int *d_err = nullptr;
@@ -1591,6 +1609,7 @@ inline std::vector<std::string> split(const std::string &s, char sep) {
 
 inline ParsedOp parse_line(const std::string &line) {
   ParsedOp op;
+  op.line = line;
   std::stringstream ss(line);
   std::string tok;
   ss >> op.type;
@@ -1707,7 +1726,7 @@ inline void Interpreter::fuse_activation_chains(const std::map<std::string, int>
 }
 
 // loadModule / updateKernelList (MlirModuleInterpreter.cpp:73-83, 118-350).
-inline void Interpreter::load_module(const std::string &text) {
+inline void Interpreter::reset_module() {
   bind();
   invalidate_graph();
   kernels.clear();
@@ -1717,56 +1736,35 @@ inline void Interpreter::load_module(const std::string &text) {
   tensor_order.clear();
   input_details.clear();
   output_details.clear();
-  std::map<std::string, std::string> producer_type;
-  std::map<std::string, int> uses;
-  std::vector<ParsedOp> parsed;
-  {
-    std::stringstream ss(text);
-    std::string line;
-    while (std::getline(ss, line)) {
-      size_t b = line.find_first_not_of(" \t\r");
-      if (b == std::string::npos || line[b] == '#') continue;
-      parsed.push_back(parse_line(line.substr(b)));
-    }
-  }
-  // Pre-pass: a few-channel convolution whose input is produced by an input or quant op and has
-  // no other consumer asks for that tensor to be stored with zero-padded rows (stem path).
+  producer_type.clear();
+  uses.clear();
   layout_requests.clear();
-  {
-    std::map<std::string, const ParsedOp *> by_name;
-    std::map<std::string, int> n_uses;
-    for (auto &op : parsed) {
-      by_name[op.name] = &op;
-      for (auto &nm : op.in) n_uses[nm]++;
-    }
-    for (auto &op : parsed) {
-      if (op.type != "conv_2d" || op.dtype != "INT8" || op.in.empty()) continue;
-      auto it = by_name.find(op.in[0]);
-      if (it == by_name.end() || n_uses[op.in[0]] != 1) continue;
-      const ParsedOp &src = *it->second;
-      if (!(src.type == "input" || src.type == "quant") || src.dtype != "INT8" || src.shape.size() != 4 ||
-          op.shape.size() != 4)
-        continue;
-      ConvGeom g;
-      g.n = (int)src.shape[0]; g.ic = (int)src.shape[1]; g.ih = (int)src.shape[2]; g.iw = (int)src.shape[3];
-      g.oc = (int)op.shape[1]; g.oh = (int)op.shape[2]; g.ow = (int)op.shape[3];
-      g.g = op.geti("g", 1); g.kh = op.geti("kh", 1); g.kw = op.geti("kw", 1); g.sh = op.geti("sh", 1);
-      g.sw = op.geti("sw", 1); g.pt = op.geti("pt", 0); g.pb = op.geti("pb", 0); g.pl = op.geti("pl", 0);
-      g.pr = op.geti("pr", 0); g.dh = op.geti("dh", 1); g.dw = op.geti("dw", 1);
-      g.ins_h = op.geti("ins_h", 0); g.ins_w = op.geti("ins_w", 0);
-      StemLayout st;
-      if (stem4_applies(g)) {
-        RowLayout rl;
-        rl.cp = 4; rl.wl = 0; rl.wphys = g.iw;
-        layout_requests[src.name] = rl;
-      } else if (stem_layout_for(g, &st)) {
-        RowLayout rl;
-        rl.cp = st.cp; rl.wl = st.wl; rl.wphys = st.wphys;
-        layout_requests[src.name] = rl;
-      }
-    }
+}
+
+// Op types whose kernels treat the leading dimension as independent images, so that batch slots can be laid side by
+// side in it. The others (matmul, permute, reduce, pad, crop, broadcast of unequal batch ...) may mix it with other
+// dimensions and are refused on an interpreter built with max_batch_size > 1.
+inline bool op_is_slot_safe(const std::string &t) {
+  static const char *ok[] = {"input", "quant", "conv_2d", "deconv_2d", "fully_connected", "pool_max_2d", "pool_avg_2d",
+                             "eltwise_add", "eltwise_mul", "eltwise_max", "eltwise_min", "concat", "upsample", "pixelshuffle",
+                             "relu", "leaky_relu", "sigmoid", "mish", "exp", "tanh", "reciprocal", "scale", "batchnorm",
+                             "softmax", "reshape"};
+  for (const char *o : ok)
+    if (t == o) return true;
+  return false;
+}
+
+inline int Interpreter::add_op(const ParsedOp &op_in) {
+  bind();
+  invalidate_graph();
+  ParsedOp op = op_in;
+  if (max_batch > 1) {
+    TPUCB_CHECK(op_is_slot_safe(op.type), "%s %s: this op type is not supported on an interpreter with max_batch_size %d",
+                op.type.c_str(), op.name.c_str(), max_batch);
+    TPUCB_CHECK(!op.shape.empty(), "%s %s: no shape", op.type.c_str(), op.name.c_str());
+    op.shape[0] *= max_batch;
   }
-  for (const ParsedOp &op : parsed) {
+  {
     TPUCB_CHECK(!tensors.count(op.name), "module text: duplicate result name '%s'", op.name.c_str());
     const int dt = dtype_from_string(op.dtype);
     auto opd = [&](size_t i) -> TensorPtr {
@@ -1797,15 +1795,16 @@ inline void Interpreter::load_module(const std::string &text) {
         TPUCB_CHECK(d[0] == in->n && d[1] * d[2] * d[3] == in->c && (d[2] * d[3] == 1),
                     "reshape %s: unsupported target shape", op.name.c_str());
       }
+      out->slot_n = out->n / max_batch;
       tensors[op.name] = out;
       tensor_order.push_back(op.name);
       producer_type[op.name] = "reshape";
-      continue;
+      return -1;
     }
     out = make_tensor(op.name, op.shape, dt);
     if (op.type == "input") {
       k.reset(new InputOp());
-      input_details.push_back({op.name, out->numel()});
+      input_details.push_back({op.name, out->numel() / (size_t)max_batch});
     } else if (op.type == "quant") {
       std::string pt = producer_type[op.in.at(0)];
       k.reset(new QuantOp(*this, op, opd(0), out, pt == "input"));
@@ -1889,37 +1888,119 @@ inline void Interpreter::load_module(const std::string &text) {
     }
     k->name = op.name;
     k->op_type = op.type;
-    k->shape = op.shape;
+    k->shape = op_in.shape; // the module's shape (one batch slot)
     k->datatype = dt;
     k->result = out;
     tensors[op.name] = out;
     tensor_order.push_back(op.name);
     producer_type[op.name] = op.type;
+    k->line = op_in.line;
+    out->slot_n = out->n / max_batch;
     kernels.push_back(std::move(k));
+    return (int)kernels.size() - 1;
   }
+}
+
+inline void Interpreter::finish_module() {
   if (fuse_activations) fuse_activation_chains(uses);
   link_tf32_remainders();
+  output_details.clear();
   for (auto &k : kernels)
-    if (!uses.count(k->name) && k->op_type != "input") output_details.push_back({k->name, k->result->numel()});
+    if (!uses.count(k->name) && k->op_type != "input") output_details.push_back({k->name, k->result->numel() / (size_t)max_batch});
   TPUCB_CUDA(cudaDeviceSynchronize());
 }
 
+inline void Interpreter::load_module(const std::string &text) {
+  reset_module();
+  std::vector<ParsedOp> parsed;
+  {
+    std::stringstream ss(text);
+    std::string line;
+    while (std::getline(ss, line)) {
+      size_t b = line.find_first_not_of(" \t\r");
+      if (b == std::string::npos || line[b] == '#') continue;
+      parsed.push_back(parse_line(line.substr(b)));
+    }
+  }
+  // Pre-pass: a few-channel convolution whose input is produced by an input or quant op and has
+  // no other consumer asks for that tensor to be stored with zero-padded rows (stem path).
+  layout_requests.clear();
+  {
+    std::map<std::string, const ParsedOp *> by_name;
+    std::map<std::string, int> n_uses;
+    for (auto &op : parsed) {
+      by_name[op.name] = &op;
+      for (auto &nm : op.in) n_uses[nm]++;
+    }
+    for (auto &op : parsed) {
+      if (op.type != "conv_2d" || op.dtype != "INT8" || op.in.empty()) continue;
+      auto it = by_name.find(op.in[0]);
+      if (it == by_name.end() || n_uses[op.in[0]] != 1) continue;
+      const ParsedOp &src = *it->second;
+      if (!(src.type == "input" || src.type == "quant") || src.dtype != "INT8" || src.shape.size() != 4 ||
+          op.shape.size() != 4)
+        continue;
+      ConvGeom g;
+      g.n = (int)src.shape[0]; g.ic = (int)src.shape[1]; g.ih = (int)src.shape[2]; g.iw = (int)src.shape[3];
+      g.oc = (int)op.shape[1]; g.oh = (int)op.shape[2]; g.ow = (int)op.shape[3];
+      g.g = op.geti("g", 1); g.kh = op.geti("kh", 1); g.kw = op.geti("kw", 1); g.sh = op.geti("sh", 1);
+      g.sw = op.geti("sw", 1); g.pt = op.geti("pt", 0); g.pb = op.geti("pb", 0); g.pl = op.geti("pl", 0);
+      g.pr = op.geti("pr", 0); g.dh = op.geti("dh", 1); g.dw = op.geti("dw", 1);
+      g.ins_h = op.geti("ins_h", 0); g.ins_w = op.geti("ins_w", 0);
+      StemLayout st;
+      if (stem4_applies(g)) {
+        RowLayout rl;
+        rl.cp = 4; rl.wl = 0; rl.wphys = g.iw;
+        layout_requests[src.name] = rl;
+      } else if (stem_layout_for(g, &st)) {
+        RowLayout rl;
+        rl.cp = st.cp; rl.wl = st.wl; rl.wphys = st.wphys;
+        layout_requests[src.name] = rl;
+      }
+    }
+  }
+  for (const ParsedOp &op : parsed) add_op(op);
+  finish_module();
+}
+
+// Geometry and storage of one batch slot of a tensor (slot < 0: the whole tensor).
+struct SlotView {
+  TensorGeom g;
+  void *dev;
+  size_t numel;
+};
+inline SlotView slot_view(const DevTensor &t, int slot, int max_batch, const char *who) {
+  SlotView v;
+  v.g = TensorGeom{t.n, t.c, t.h, t.w, t.cp, t.wl, t.wphys};
+  v.dev = t.dev;
+  v.numel = t.numel();
+  if (slot >= 0) {
+    TPUCB_CHECK(slot < max_batch, "%s %s: batch slot %d is outside [0, %d)", who, t.name.c_str(), slot, max_batch);
+    v.g.n = t.slot_n;
+    v.numel = (size_t)t.slot_n * t.c * t.h * t.w;
+    v.dev = (uint8_t *)t.dev + (size_t)slot * t.slot_n * t.h * t.wphys * t.cp * t.elsize();
+  }
+  return v;
+}
+
 // setTensor (MlirModuleInterpreter.cpp:407-417): fp32 NCHW host values -> device storage.
-inline void Interpreter::set_tensor(const std::string &name, const float *data, size_t numel) {
+inline void Interpreter::set_tensor(const std::string &name, const float *data, size_t numel, int slot) {
   bind();
   TensorPtr t = tensor(name);
-  TPUCB_CHECK(numel == t->numel(), "set_tensor %s: got %zu values, tensor has %zu", name.c_str(), numel, t->numel());
+  const SlotView v = slot_view(*t, slot, max_batch, "set_tensor");
+  TPUCB_CHECK(numel == v.numel, "set_tensor %s: got %zu values, tensor has %zu", name.c_str(), numel, v.numel);
   float *stg = ensure_staging(numel * sizeof(float));
   TPUCB_CUDA(cudaMemcpyAsync(stg, data, numel * sizeof(float), cudaMemcpyHostToDevice, stream));
-  TensorGeom g{t->n, t->c, t->h, t->w, t->cp, t->wl, t->wphys};
-  size_t total = t->pixels() * t->cp;
+  const TensorGeom &g = v.g;
+  const size_t pixels = (size_t)g.n * g.h * g.wphys;
+  size_t total = pixels * t->cp;
   int grid = grid_for(total, 256, sm_count);
   if (t->dtype == DT_F32 && t->cp == 4 && !t->padded_rows())
-    nchw_f32_to_nhwc4_kernel<<<grid_for(t->pixels(), 256, sm_count), 256, 0, stream>>>(stg, (float4 *)t->dev, t->n, t->c,
-                                                                                     (size_t)t->h * t->w);
-  else if (t->dtype == DT_I8) nchw_f32_to_dev_kernel<DT_I8><<<grid, 256, 0, stream>>>(stg, t->dev, g);
-  else if (t->dtype == DT_BF16) nchw_f32_to_dev_kernel<DT_BF16><<<grid, 256, 0, stream>>>(stg, t->dev, g);
-  else nchw_f32_to_dev_kernel<DT_F32><<<grid, 256, 0, stream>>>(stg, t->dev, g);
+    nchw_f32_to_nhwc4_kernel<<<grid_for(pixels, 256, sm_count), 256, 0, stream>>>(stg, (float4 *)v.dev, g.n, t->c,
+                                                                                 (size_t)t->h * t->w);
+  else if (t->dtype == DT_I8) nchw_f32_to_dev_kernel<DT_I8><<<grid, 256, 0, stream>>>(stg, v.dev, g);
+  else if (t->dtype == DT_BF16) nchw_f32_to_dev_kernel<DT_BF16><<<grid, 256, 0, stream>>>(stg, v.dev, g);
+  else nchw_f32_to_dev_kernel<DT_F32><<<grid, 256, 0, stream>>>(stg, v.dev, g);
   TPUCB_CUDA(cudaGetLastError());
 }
 
@@ -1964,16 +2045,16 @@ inline void Interpreter::set_tensor_async(const std::string &name, const float *
 }
 
 // getTensor (MlirModuleInterpreter.cpp:419-427): deep copy out as fp32 NCHW.
-inline void Interpreter::get_tensor(const std::string &name, float *out, size_t numel) {
+inline void Interpreter::get_tensor(const std::string &name, float *out, size_t numel, int slot) {
   bind();
   TensorPtr t = tensor(name);
-  TPUCB_CHECK(numel == t->numel(), "get_tensor %s: buffer has %zu values, tensor has %zu", name.c_str(), numel, t->numel());
+  const SlotView v = slot_view(*t, slot, max_batch, "get_tensor");
+  TPUCB_CHECK(numel == v.numel, "get_tensor %s: buffer has %zu values, tensor has %zu", name.c_str(), numel, v.numel);
   float *stg = ensure_staging(numel * sizeof(float));
-  TensorGeom g{t->n, t->c, t->h, t->w, t->cp, t->wl, t->wphys};
   int grid = grid_for(numel, 256, sm_count);
-  if (t->dtype == DT_I8) dev_to_nchw_f32_kernel<DT_I8><<<grid, 256, 0, stream>>>(t->dev, stg, g);
-  else if (t->dtype == DT_BF16) dev_to_nchw_f32_kernel<DT_BF16><<<grid, 256, 0, stream>>>(t->dev, stg, g);
-  else dev_to_nchw_f32_kernel<DT_F32><<<grid, 256, 0, stream>>>(t->dev, stg, g);
+  if (t->dtype == DT_I8) dev_to_nchw_f32_kernel<DT_I8><<<grid, 256, 0, stream>>>(v.dev, stg, v.g);
+  else if (t->dtype == DT_BF16) dev_to_nchw_f32_kernel<DT_BF16><<<grid, 256, 0, stream>>>(v.dev, stg, v.g);
+  else dev_to_nchw_f32_kernel<DT_F32><<<grid, 256, 0, stream>>>(v.dev, stg, v.g);
   TPUCB_CUDA(cudaGetLastError());
   TPUCB_CUDA(cudaMemcpyAsync(out, stg, numel * sizeof(float), cudaMemcpyDeviceToHost, stream));
   TPUCB_CUDA(cudaStreamSynchronize(stream));
@@ -2012,6 +2093,23 @@ inline void Interpreter::launch_to(const std::string &name) {
   for (auto &k : kernels) {
     k->invoke(stream);
     if (k->name == name) break;
+  }
+  TPUCB_CUDA(cudaGetLastError());
+}
+
+// fastInvokeAllBatch (MlirModuleInterpreter.cpp:383-405): the reference loops over the batch slots and runs, per slot,
+// every kernel that is still dirty (built since the last such call) up to `name`. Here the slots are image groups of
+// one device tensor: the same kernels run ONCE, over all slots, and are marked clean.
+inline void Interpreter::fast_invoke_all_batch(const std::string &name, int batch) {
+  bind();
+  TPUCB_CHECK(batch >= 1 && batch <= max_batch, "fastInvokeAllBatch: batch %d is outside [1, %d]", batch, max_batch);
+  if (!name.empty()) tensor(name);
+  for (auto &k : kernels) {
+    if (k->dirty) {
+      k->invoke(stream);
+      k->dirty = false;
+    }
+    if (!name.empty() && k->name == name) break;
   }
   TPUCB_CUDA(cudaGetLastError());
 }

@@ -11,8 +11,16 @@
 
 using namespace tpucb;
 
+struct tpucb_op {
+  tpucb_interp *ctx;
+  int index;        // position in the context's kernel list; -1 for a reshape (an alias: nothing to run)
+  std::string name; // result name
+  bool stale = false; // its interpreter has loaded another module since
+};
+
 struct tpucb_interp {
   Interpreter impl;
+  std::vector<std::unique_ptr<tpucb_op>> ops; // handles given out by tpucb_op_create
   double *tuner_sums = nullptr; // device scratch of tpucb_tuner_distance, grown on demand
   int tuner_sums_cap = 0;
   StatDesc *stat_descs = nullptr; // device descriptor list of the all-tensor statistics launches, grown on demand
@@ -67,6 +75,15 @@ int tpucb_interp_create(int device, tpucb_interp **out) {
   TPUCB_API_END
 }
 
+int tpucb_interp_create_batched(int device, int max_batch_size, tpucb_interp **out) {
+  TPUCB_API_BEGIN
+  TPUCB_CHECK(max_batch_size >= 1 && max_batch_size <= 65536, "tpucb_interp_create_batched: max_batch_size %d is outside [1, 65536]",
+              max_batch_size);
+  if (tpucb_interp_create(device, out) != 0) return 1;
+  (*out)->impl.max_batch = max_batch_size;
+  TPUCB_API_END
+}
+
 int tpucb_interp_destroy(tpucb_interp *it) {
   TPUCB_API_BEGIN
   delete it;
@@ -90,6 +107,7 @@ int tpucb_interp_set_weight(tpucb_interp *it, const char *name, const float *dat
 int tpucb_interp_load_module(tpucb_interp *it, const char *module_text) {
   TPUCB_API_BEGIN
   TPUCB_CHECK(it && module_text, "tpucb_interp_load_module: bad argument");
+  for (auto &o : it->ops) o->stale = true; // handles into the previous module stay allocated, but refuse to run
   it->impl.load_module(module_text);
   TPUCB_API_END
 }
@@ -98,6 +116,135 @@ int tpucb_interp_set_tensor(tpucb_interp *it, const char *name, const float *dat
   TPUCB_API_BEGIN
   TPUCB_CHECK(it && name && data, "tpucb_interp_set_tensor: bad argument");
   it->impl.set_tensor(name, data, numel);
+  TPUCB_API_END
+}
+
+int tpucb_interp_set_tensor_slot(tpucb_interp *it, const char *name, const float *data, size_t numel, int bidx) {
+  TPUCB_API_BEGIN
+  TPUCB_CHECK(it && name && data && bidx >= 0, "tpucb_interp_set_tensor_slot: bad argument");
+  it->impl.set_tensor(name, data, numel, bidx);
+  TPUCB_API_END
+}
+
+int tpucb_interp_get_tensor_slot(tpucb_interp *it, const char *name, float *out, size_t numel, int bidx) {
+  TPUCB_API_BEGIN
+  TPUCB_CHECK(it && name && out && bidx >= 0, "tpucb_interp_get_tensor_slot: bad argument");
+  it->impl.get_tensor(name, out, numel, bidx);
+  TPUCB_API_END
+}
+
+int tpucb_interp_invoke_slot(tpucb_interp *it, const char *name, int bidx) {
+  TPUCB_API_BEGIN
+  TPUCB_CHECK(it, "tpucb_interp_invoke_slot: bad argument");
+  TPUCB_CHECK(bidx >= 0 && bidx < it->impl.max_batch, "tpucb_interp_invoke_slot: batch slot %d is outside [0, %d)", bidx,
+              it->impl.max_batch);
+  it->impl.launch_to(name ? name : "");
+  it->impl.sync_and_check();
+  TPUCB_API_END
+}
+
+int tpucb_interp_fast_invoke_all_batch(tpucb_interp *it, const char *name, int batch) {
+  TPUCB_API_BEGIN
+  TPUCB_CHECK(it, "tpucb_interp_fast_invoke_all_batch: bad argument");
+  it->impl.fast_invoke_all_batch(name ? name : "", batch);
+  it->impl.sync_and_check();
+  TPUCB_API_END
+}
+
+int tpucb_interp_max_batch_size(tpucb_interp *it, int *max_batch_size) {
+  TPUCB_API_BEGIN
+  TPUCB_CHECK(it && max_batch_size, "tpucb_interp_max_batch_size: bad argument");
+  *max_batch_size = it->impl.max_batch;
+  TPUCB_API_END
+}
+
+int tpucb_interp_dump(tpucb_interp *it, const char *name, char *out, size_t cap, size_t *needed) {
+  TPUCB_API_BEGIN
+  TPUCB_CHECK(it && name, "tpucb_interp_dump: bad argument");
+  std::string s;
+  for (auto &k : it->impl.kernels)
+    if (k->name == name) {
+      s = "name: " + k->name + "\nop_type: " + k->op_type + "\ndata_type: " + dtype_to_string(k->datatype) + "\nshape: ";
+      for (size_t i = 0; i < k->shape.size(); ++i) s += (i ? "x" : "") + std::to_string(k->shape[i]);
+      s += "\nmax_batch_size: " + std::to_string(it->impl.max_batch) + "\ndirty: " + (k->dirty ? "1" : "0") +
+           "\nkernel_launches: " + std::to_string(k->kernel_launches()) + "\nop: " + k->line + "\n";
+    }
+  TPUCB_CHECK(!s.empty(), "tpucb_interp_dump: no op named '%s'", name);
+  copy_out(s, out, cap, needed);
+  TPUCB_API_END
+}
+
+// ---- per-op surface (CPUOpKernel, include/tpuc/Interpreter/cpukernel.h:87-159) -------------------------------------
+
+int tpucb_op_create(tpucb_interp *ctx, const char *op_line, tpucb_op **out) {
+  TPUCB_API_BEGIN
+  TPUCB_CHECK(ctx && op_line && out, "tpucb_op_create: bad argument");
+  std::string line = op_line;
+  size_t b = line.find_first_not_of(" \t\r\n");
+  TPUCB_CHECK(b != std::string::npos, "tpucb_op_create: empty op line");
+  size_t e = line.find_last_not_of(" \t\r\n");
+  ParsedOp op = parse_line(line.substr(b, e - b + 1));
+  const int index = ctx->impl.add_op(op);
+  // the result of an op without consumers is an output until a later op reads it
+  ctx->impl.output_details.clear();
+  for (auto &k : ctx->impl.kernels)
+    if (!ctx->impl.uses.count(k->name) && k->op_type != "input")
+      ctx->impl.output_details.push_back({k->name, k->result->numel() / (size_t)ctx->impl.max_batch});
+  ctx->ops.emplace_back(new tpucb_op{ctx, index, op.name, false});
+  *out = ctx->ops.back().get();
+  TPUCB_API_END
+}
+
+static OpKernel *op_kernel(tpucb_op *op, const char *who) {
+  TPUCB_CHECK(op && op->ctx, "%s: bad argument", who);
+  auto &ks = op->ctx->impl.kernels;
+  TPUCB_CHECK(!op->stale && (op->index < 0 || (op->index < (int)ks.size() && ks[op->index]->name == op->name)),
+              "%s: the op handle of '%s' is stale (its interpreter loaded another module)", who, op->name.c_str());
+  if (op->index < 0) return nullptr;
+  return ks[op->index].get();
+}
+
+int tpucb_op_invoke(tpucb_op *op) {
+  TPUCB_API_BEGIN
+  OpKernel *k = op_kernel(op, "tpucb_op_invoke");
+  Interpreter &I = op->ctx->impl;
+  I.bind();
+  if (k) {
+    k->invoke(I.stream);
+    k->dirty = false;
+    TPUCB_CUDA(cudaGetLastError());
+  }
+  I.sync_and_check();
+  TPUCB_API_END
+}
+
+int tpucb_op_set_tensor(tpucb_op *op, const float *data, size_t numel, int bidx) {
+  TPUCB_API_BEGIN
+  OpKernel *k = op_kernel(op, "tpucb_op_set_tensor");
+  TPUCB_CHECK(data, "tpucb_op_set_tensor: bad argument");
+  // CPUOpKernel::set_tensor is implemented by the input op only (core/input.cpp:17-24); the others reject it
+  TPUCB_CHECK(k && k->op_type == "input", "tpucb_op_set_tensor: op '%s' is not an input op", op->name.c_str());
+  op->ctx->impl.set_tensor(op->name, data, numel, bidx);
+  TPUCB_API_END
+}
+
+int tpucb_op_get_tensor(tpucb_op *op, float *out, size_t numel, int bidx) {
+  TPUCB_API_BEGIN
+  op_kernel(op, "tpucb_op_get_tensor");
+  TPUCB_CHECK(out, "tpucb_op_get_tensor: bad argument");
+  op->ctx->impl.get_tensor(op->name, out, numel, bidx);
+  TPUCB_API_END
+}
+
+int tpucb_op_info(tpucb_op *op, char *out, size_t cap, size_t *needed) {
+  TPUCB_API_BEGIN
+  OpKernel *k = op_kernel(op, "tpucb_op_info");
+  auto t = op->ctx->impl.tensor(op->name);
+  std::string s = op->name + "\t" + (k ? k->op_type : std::string("reshape")) + "\t" + dtype_to_string(t->dtype) + "\t";
+  for (size_t i = 0; i < t->shape.size(); ++i)
+    s += (i ? "," : "") + std::to_string(i == 0 ? t->shape[i] / op->ctx->impl.max_batch : t->shape[i]);
+  s += std::string("\t") + ((k && k->dirty) ? "1" : "0");
+  copy_out(s, out, cap, needed);
   TPUCB_API_END
 }
 
@@ -158,7 +305,8 @@ int tpucb_interp_get_tensor_shape(tpucb_interp *it, const char *name, int64_t *s
   TPUCB_CHECK(it && name && shape && rank, "tpucb_interp_get_tensor_shape: bad argument");
   auto t = it->impl.tensor(name);
   *rank = (int)t->shape.size();
-  for (size_t i = 0; i < t->shape.size(); ++i) shape[i] = t->shape[i];
+  // the module's shape: one batch slot (MlirModuleInterpreter::getTensorShape)
+  for (size_t i = 0; i < t->shape.size(); ++i) shape[i] = i == 0 ? t->shape[i] / it->impl.max_batch : t->shape[i];
   TPUCB_API_END
 }
 

@@ -19,12 +19,48 @@ def _text(fn, *prefix):
     return buf.value.decode()
 
 
+class op_kernel:
+    """One op owned by itself: the CPUOpKernel surface (include/tpuc/Interpreter/cpukernel.h:87-159) over
+    tpucb_op_*. Made by ``module.create_op``; the module is the value / weight map it looks its operands up in."""
+
+    def __init__(self, owner, handle):
+        self._m, self._h = owner, handle
+
+    def _info(self):
+        name, typ, dt, shape, dirty = _text(self._m._lib.tpucb_op_info, self._h).split("\t")
+        return name, typ, dt, [int(v) for v in shape.split(",") if v], dirty == "1"
+
+    name = property(lambda self: self._info()[0])
+    op_type = property(lambda self: self._info()[1])
+    datatype = property(lambda self: self._info()[2])
+    shape = property(lambda self: self._info()[3])
+    dirty = property(lambda self: self._info()[4])
+
+    def invoke(self):
+        check(self._m._lib.tpucb_op_invoke(self._h))
+
+    def set_tensor(self, array, bidx=0):
+        a = np.ascontiguousarray(array, dtype=np.float32)
+        check(self._m._lib.tpucb_op_set_tensor(self._h, a.ctypes.data_as(_f), a.size, int(bidx)))
+
+    def get_tensor(self, bidx=0):
+        out = np.empty(self.shape, np.float32)
+        check(self._m._lib.tpucb_op_get_tensor(self._h, out.ctypes.data_as(_f), out.size, int(bidx)))
+        return out
+
+
 class module:
-    def __init__(self, device=0):
+    def __init__(self, device=0, max_batch_size=1):
+        """``max_batch_size``: the constructor argument of MlirModuleInterpreter (MlirModuleInterpreter.h:35): that many
+        batch slots per tensor, addressed by the ``bidx`` arguments below."""
         self._h = C.c_void_p()
         self._device = device
         self._lib = lib()
-        check(self._lib.tpucb_interp_create(int(device), C.byref(self._h)))
+        self.max_batch_size = int(max_batch_size)
+        if self.max_batch_size == 1:
+            check(self._lib.tpucb_interp_create(int(device), C.byref(self._h)))
+        else:
+            check(self._lib.tpucb_interp_create_batched(int(device), self.max_batch_size, C.byref(self._h)))
         self._weight_file = None
         self.op_info = []
 
@@ -66,13 +102,27 @@ class module:
                 weights = dict(np.load(self._weight_file))
         self.load_text(text, weights)
 
-    def load_text(self, text, weights):
+    def set_weights(self, weights):
+        """updateWeightMap: registers fp32 weight arrays by name (before load_text / create_op)."""
         for name, arr in weights.items():
             a = np.ascontiguousarray(arr, dtype=np.float32)
             shape = (C.c_int64 * max(a.ndim, 1))(*(a.shape if a.ndim else (1,)))
             check(self._lib.tpucb_interp_set_weight(self._h, name.encode(), a.ctypes.data_as(_f), shape,
                                                     max(a.ndim, 1)))
+
+    def create_op(self, op_line):
+        """One op from one line of module text (its operands must exist already): an ``op_kernel``."""
+        h = C.c_void_p()
+        check(self._lib.tpucb_op_create(self._h, op_line.encode(), C.byref(h)))
+        self._refresh_op_info()
+        return op_kernel(self, h)
+
+    def load_text(self, text, weights):
+        self.set_weights(weights)
         check(self._lib.tpucb_interp_load_module(self._h, text.encode()))
+        self._refresh_op_info()
+
+    def _refresh_op_info(self):
         self.op_info = []
         for line in _text(self._lib.tpucb_interp_get_op_info, self._h).splitlines():
             name, typ, dt, shape, ops, nbytes, bound = line.split("\t")
@@ -84,9 +134,13 @@ class module:
         return self._weight_file
 
     # ---- tensors ---------------------------------------------------------------
-    def set_tensor(self, name, array):
+    def set_tensor(self, name, array, bidx=None):
+        """``bidx`` None: the whole tensor (with max_batch_size > 1: all slots, slot-major); else one batch slot."""
         a = np.ascontiguousarray(array, dtype=np.float32)
-        check(self._lib.tpucb_interp_set_tensor(self._h, name.encode(), a.ctypes.data_as(_f), a.size))
+        if bidx is None:
+            check(self._lib.tpucb_interp_set_tensor(self._h, name.encode(), a.ctypes.data_as(_f), a.size))
+        else:
+            check(self._lib.tpucb_interp_set_tensor_slot(self._h, name.encode(), a.ctypes.data_as(_f), a.size, int(bidx)))
 
     def set_tensor_ptr(self, name, host_ptr, numel):
         """Same as set_tensor, from a raw (e.g. pinned) host pointer."""
@@ -106,10 +160,16 @@ class module:
         check(self._lib.tpucb_interp_get_tensor_shape(self._h, name.encode(), shape, C.byref(rank)))
         return [int(shape[i]) for i in range(rank.value)]
 
-    def get_tensor(self, name):
+    def get_tensor(self, name, bidx=None):
         shape = self.get_tensor_shape(name)
-        out = np.empty(shape, np.float32)
-        check(self._lib.tpucb_interp_get_tensor(self._h, name.encode(), out.ctypes.data_as(_f), out.size))
+        if bidx is None:
+            if self.max_batch_size > 1:
+                shape = [shape[0] * self.max_batch_size] + shape[1:]
+            out = np.empty(shape, np.float32)
+            check(self._lib.tpucb_interp_get_tensor(self._h, name.encode(), out.ctypes.data_as(_f), out.size))
+        else:
+            out = np.empty(shape, np.float32)
+            check(self._lib.tpucb_interp_get_tensor_slot(self._h, name.encode(), out.ctypes.data_as(_f), out.size, int(bidx)))
         return out
 
     def get_tensor_into(self, name, host_ptr, numel):
@@ -123,16 +183,24 @@ class module:
     def get_all_tensor_names(self):
         return [n for n in _text(self._lib.tpucb_interp_get_all_tensor_names, self._h).splitlines() if n]
 
-    def get_all_tensor(self):
-        return {n: self.get_tensor(n) for n in self.get_all_tensor_names()}
+    def get_all_tensor(self, bidx=None):
+        return {n: self.get_tensor(n, bidx) for n in self.get_all_tensor_names()}
 
-    def _details(self, outputs):
+    def _details(self, outputs, sizes=False):
         out = []
         for line in _text(self._lib.tpucb_interp_get_details, self._h, int(outputs)).splitlines():
             if line:
                 n, sz = line.rsplit(":", 1)
-                out.append(n)
+                out.append((n, int(sz)) if sizes else n)
         return out
+
+    def input_sizes(self):
+        """input_details of the reference: (name, element count of one batch slot) in module order."""
+        return self._details(False, sizes=True)
+
+    def dump(self, name):
+        """MlirModuleInterpreter::dump: a text description of one op."""
+        return _text(self._lib.tpucb_interp_dump, self._h, name.encode())
 
     def get_input_details(self):
         return self._details(False)
@@ -141,11 +209,22 @@ class module:
         return self._details(True)
 
     # ---- execution -------------------------------------------------------------
-    def invoke(self):
-        check(self._lib.tpucb_interp_invoke(self._h))
+    def invoke(self, bidx=None):
+        if bidx is None:
+            check(self._lib.tpucb_interp_invoke(self._h))
+        else:
+            check(self._lib.tpucb_interp_invoke_slot(self._h, None, int(bidx)))
 
-    def invoke_to(self, name):
-        check(self._lib.tpucb_interp_invoke_to(self._h, name.encode()))
+    def invoke_to(self, name, bidx=None):
+        if bidx is None:
+            check(self._lib.tpucb_interp_invoke_to(self._h, name.encode()))
+        else:
+            check(self._lib.tpucb_interp_invoke_slot(self._h, name.encode(), int(bidx)))
+
+    def fast_invoke_all_batch(self, name="", batch=None):
+        """fastInvokeAllBatch: the ops built since the last such call, up to ``name``, over all batch slots at once."""
+        check(self._lib.tpucb_interp_fast_invoke_all_batch(self._h, name.encode() if name else None,
+                                                           int(batch or self.max_batch_size)))
 
     def launch(self):
         check(self._lib.tpucb_interp_launch(self._h))
@@ -153,12 +232,23 @@ class module:
     def sync(self):
         check(self._lib.tpucb_interp_sync(self._h))
 
-    def run(self, input):
-        """pymlir.module.run: set the (single) input, invoke, return the outputs."""
-        ins = self.get_input_details()
-        if len(ins) != 1:
-            raise RuntimeError("run() needs a module with exactly one input")
-        self.set_tensor(ins[0], input)
+    def run(self, input, target_op=""):
+        """pymlir.module.run (bindings/python/pymlir.cpp:215-266): ``input`` holds the values of all inputs one after
+        the other in module order; runs the module (up to ``target_op`` when given) and returns the outputs (or that
+        op's tensor) as a dict."""
+        flat = np.ascontiguousarray(input, dtype=np.float32).reshape(-1)
+        ins = self.input_sizes()
+        scale = self.max_batch_size
+        need = sum(sz for _, sz in ins) * scale
+        if flat.size != need:
+            raise RuntimeError("input data size %d not same with all input needed size %d" % (flat.size, need))
+        at = 0
+        for name, sz in ins:
+            self.set_tensor(name, flat[at:at + sz * scale])
+            at += sz * scale
+        if target_op:
+            self.invoke_to(target_op)
+            return {target_op: self.get_tensor(target_op)}
         self.invoke()
         return {n: self.get_tensor(n) for n in self.get_output_details()}
 

@@ -36,6 +36,14 @@ def test_mobilenet_v2_every_tensor():
     check_all_tensors(model, data)
 
 
+def test_mobilenet_v2_every_tensor_with_adds_in_the_convolution_epilogue():
+    """The residual adds of the inverted-residual blocks (no ReLU, project convolution without activation) fused into
+    the project convolution's epilogue (option fuse_residual_add)."""
+    model = graphs.mobilenet_v2_int8(batch=2, res=96, seed=3002)
+    data = np.random.default_rng(32).uniform(-1, 1, (2, 3, 96, 96)).astype(np.float32)
+    check_all_tensors(model, data, options=(("fuse_residual_add", 1),))
+
+
 def test_yolov4_style_every_tensor():
     model = graphs.yolov4_style_int8(batch=2, res=64, width=0.25, depth=(1, 1, 2, 2, 1), seed=4001)
     data = np.random.default_rng(41).uniform(0, 1, (2, 3, 64, 64)).astype(np.float32)

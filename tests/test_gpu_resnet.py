@@ -113,3 +113,26 @@ def test_set_tensor_async_pipeline_matches_synchronous_path():
     for b in bufs:
         check(L.tpucb_host_free(b))
     m.close()
+
+
+def test_resnet50_with_residual_adds_in_the_convolution_epilogue(model_b1):
+    """Option fuse_residual_add: the 16 eltwise adds run inside the epilogue of the convolution that produces their
+    second operand. Every tensor (the convolution results and the sums) still equals the oracle, at a batch whose
+    pixel count leaves ragged tiles, and 16 kernels fewer are launched."""
+    from tpu_compiler_b200 import module
+    B = 3
+    imgs = np.random.default_rng(99).uniform(-1, 1, (B, 3, 224, 224)).astype(np.float32)
+    mb = graphs.resnet50_int8(batch=B, seed=1001)
+    plain = module(0)
+    plain.load_text(mb.text, mb.weights)
+    m = module(0)
+    m.set_option("fuse_residual_add", 1)
+    m.load_text(mb.text, mb.weights)
+    assert plain.kernel_count() - m.kernel_count() == 16
+    plain.close()
+    m.set_tensor("data", imgs)
+    m.invoke()
+    ref = graph_runner.run(mb.text, mb.weights, {"data": imgs})
+    for name in m.get_all_tensor_names():
+        assert np.array_equal(m.get_tensor(name).reshape(-1), ref[name].reshape(-1)), name
+    m.close()

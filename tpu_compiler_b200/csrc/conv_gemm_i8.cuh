@@ -48,7 +48,8 @@ struct ConvGemmParams {
   int w_resident; // 1: the CTA keeps all K blocks of its channel tile's weights in shared memory
   int a_mode;     // 0: A is a 2-D [M][K] matrix, 1: im2col TMA, 2: row windows (stem)
   int win_g;      // mode 2: output pixels per copy
-  int act;        // 0 none, 1 ReLU, 2 leaky (non-QDM pos/neg rescale of the int8 result)
+  int act;        // 0 none, 1 ReLU, 2 leaky (non-QDM pos/neg rescale of the int8 result),
+                  // 3 the eltwise add that consumes this convolution, with the residual tensor `res` (see add_*)
   int tmem_cols;  // 256: two accumulator buffers of 128 pixel columns
   int leaky_mp, leaky_rp, leaky_mn, leaky_rn;
   uint32_t idesc; // tcgen05 instruction descriptor
@@ -58,7 +59,11 @@ struct ConvGemmParams {
   int8_t *out;
   int fastq;      // bit 0: the multiply-high form of the requantisation applies (requant_fast; set by the host);
                   // bit 1: every rshift of the layer is >= 1
-  int8_t *out2;   // act == 2 only: the activation result goes here and `out` keeps the plain convolution result
+  int8_t *out2;   // act == 2 / 3: the activation (or sum) goes here and `out` keeps the plain convolution result
+  // act == 3 (EltwiseAddOpKernel::i8_invoke, core/eltwise.cpp:52-85, applied to this convolution's int8 result x and the
+  // tensor `res` of the same geometry): sat8(relu?((x * add_ms + res * add_mr + 2^(add_r - 1)) >> add_r))
+  const int8_t *res;
+  int add_ms, add_mr, add_r, add_relu;
   int *err;       // device error word (0 = ok)
 };
 
@@ -88,9 +93,12 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // Bounded wait: returns false when the barrier did not flip within the limit.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
                                                   volatile int *abort_flag) {
-  for (uint32_t it = 0; it < (1u << 20); ++it) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 1023u) == 1023u && *abort_flag) return false;
+  // 1024 rounds of 1024 polls: the abort flag (another role of this CTA gave up) is read once per round
+  for (int round = 0; round < 1024; ++round) {
+#pragma unroll 1
+    for (int it = 1024; it > 0; --it)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
   }
   return false;
 }
@@ -287,19 +295,17 @@ enum ConvErr { kErrFullWait = 1, kErrEmptyWait = 2, kErrAccWait = 3 };
 //        truncates toward zero, for either sign),
 //   q  = RoundingDivideByPOT(hi, r) = (hi + rnd - [hi < 0 and r > 0]) >> r, rnd = 2^(r-1) (0 if r = 0),
 // then saturates (and ReLU clamps at 0, so there rnd is folded into the constant and the sign term
-// dropped). Here the product is formed once, unsigned and doubled, so that hi is simply the HIGH
-// WORD of one 32 x 32 + 64 multiply-add (a signed wide multiply-add costs several instructions on
-// this SM, the unsigned one is a single one):
+// dropped). requant_one forms the product once, unsigned and doubled, so that hi is simply the HIGH
+// WORD of one 32 x 32 + 64 multiply-add:
 //   s' = s + 2^31 (offset binary, one add of `sbias` = bias + 2^31), M2 = 2 * M (fits unsigned 32),
 //   2 * (s * M + C) = s' * M2 + (2 * C - 2^31 * M2)   (mod 2^64),  C = 2^30 (+ rnd * 2^31 with ReLU),
 //   hi = that >> 32.
-// Per value: add, wide multiply-add, then max+shift (ReLU) or shift+add+shift, and half a
-// saturating pack.
 struct ChanConst {
   uint32_t M2, sbias;
   int32_t r, rnd, s1; // s1 = 31 when r > 0, 32 when r == 0: (uint)hi >> s1 is the "negative and r > 0" bit
   unsigned long long c2;
-  uint32_t kc;        // multiply-high form only (requant_fast), where r holds r + 1 and rnd holds 2 * rnd
+  uint32_t kc;        // multiply-high form only (requant_fast), where r holds r + 1
+  int32_t r0mask;     // multiply-high form: -1 when r == 0 (no sign term for this channel), else 0
 };
 
 __device__ __forceinline__ ChanConst load_chan_const(const ConvGemmParams &p, int n) {
@@ -317,13 +323,18 @@ __device__ __forceinline__ ChanConst load_chan_const(const ConvGemmParams &p, in
   c.rnd = (int32_t)rnd;
   c.s1 = c.r > 0 ? 31 : 32;
   c.kc = 0;
+  c.r0mask = c.r == 0 ? -1 : 0;
   if (p.fastq & 1) {
     // multiply-high form: see requant_fast
     const uint32_t k = 1u + 2u * (uint32_t)rnd;
-    c.sbias = p.act == 1 ? 2u * (uint32_t)b : 2u * (uint32_t)b + 0x80000000u;
-    c.kc = p.act == 1 ? k : k - (uint32_t)M;
-    c.rnd = (int32_t)(2u * (uint32_t)rnd);
+    c.sbias = 2u * (uint32_t)b + 0x80000000u;
+    // the sign term costs 2 when s < 0: the constant carries the -2 and the kernel gives it back when s >= 0
+    c.kc = p.act == 1 ? k - (uint32_t)M : k - (uint32_t)M - (c.r > 0 ? 2u : 0u);
     c.r = c.r + 1;
+    if (!v) { // a lane past the layer's channels: s2 = 0, no sign term, result 0
+      c.sbias = 0u;
+      c.kc = 0u;
+    }
   }
   return c;
 }
@@ -343,59 +354,78 @@ __device__ __forceinline__ int requant_one(int32_t acc, const ChanConst &q, cons
   if (ACT == 2) v = min(max(v, -128), 127); // the leaky rescale below works on the saturated int8 value
   return v;
 }
-// The same value from ONE multiply-high (the 32 x 32 + 64 multiply-add above costs about three multiply-class
-// instructions and an add on this SM). With t = floor(s * M / 2^30), hi = floor((t + 1) / 2) and, nesting the
-// floors, q = floor((t + k - 2 * neg) / 2^(r + 1)), k = 1 + 2 * rnd, neg = [t + 1 < 0 and r > 0].
-//   ReLU: the requantisation is monotone in s with q(0) = 0, so max(q(s), 0) = q(max(s, 0)): the clamp moves in
-//         front, neg vanishes and everything is unsigned:  q = (mulhi(2 * max(s, 0), 2M) + k) >> (r + 1).
-//   else: offset binary as above: mulhi(2 * (s + 2^30), 2M) = t + M exactly, so the addend k - M gives t + k.
+// The same value from ONE multiply-high. With t = floor(s * M / 2^30), hi = floor((t + 1) / 2) and, nesting the
+// floors, q = floor((t + k - 2 * neg) / 2^(r + 1)), k = 1 + 2 * rnd, neg = [hi < 0 and r > 0].
+//   Offset binary: s2 = 2 * (s + 2^30) is a non-negative 32-bit number whose top bit says s >= 0, and
+//   mulhi(s2, 2M) = t + M exactly, so the addend kc = k - M gives t + k.
+//   ReLU (ACT 1): no sign term. For s >= 0 the value is (t + k) >> (r + 1); for s < 0 it is <= 0 ((t + k) < 2^(r + 1)
+//         there), which the caller clamps to 0 on the packed bytes (relu4): no clamp per value.
+//   else: neg may be replaced by [s < 0 and r > 0]: the two differ only for t = -1 (hi = 0), where both forms
+//         give 0. With m = s2 >> 31 (arithmetic: -1 for s >= 0, 0 for s < 0) the term is -2 - 2m; the -2 sits in kc.
+//         R1 = every channel of the layer has r > 0; otherwise the channels with r = 0 switch the term off (r0mask).
 // Valid for |s| < 2^29 and r <= 29 (no 32-bit overflow); the host sets fastq only when every channel of the
 // layer and the largest possible |acc| satisfy that, else requant_one runs.
-template <int ACT>
+template <int ACT, bool R1>
 __device__ __forceinline__ int requant_fast(int32_t acc, const ChanConst &q, const ConvGemmParams &p) {
-  uint32_t tk, s2 = 2u * (uint32_t)acc + q.sbias;
-  if (ACT == 1) s2 = (uint32_t)max((int32_t)s2, 0);
+  // The instructions are spelled out: the integer ALU (shifts, logic, three-input adds, packs, permutes) issues at
+  // half the rate of the multiply-add pipe on this SM, so the doubling and the sign term are multiply-adds and
+  // only the two shifts go to the ALU (measured on a 64 -> 256 channel 1x1 layer: 122 -> 112 us).
+  uint32_t s2, tk;
+  asm("mad.lo.u32 %0, %1, 2, %2;" : "=r"(s2) : "r"((uint32_t)acc), "r"(q.sbias));
   asm("mad.hi.u32 %0, %1, %2, %3;" : "=r"(tk) : "r"(s2), "r"(q.M2), "r"(q.kc));
+  int32_t v;
   if (ACT == 1) {
-    uint32_t v;
-    asm("shr.u32 %0, %1, %2;" : "=r"(v) : "r"(tk), "r"((uint32_t)q.r)); // r + 1 <= 32; a shift by 32 gives 0
-    return (int)v;
+    asm("shr.s32 %0, %1, %2;" : "=r"(v) : "r"((int32_t)tk), "r"((uint32_t)q.r));
+    return v;
   }
-  uint32_t adj;
-  asm("shr.u32 %0, %1, %2;" : "=r"(adj) : "r"(tk - (uint32_t)q.rnd), "r"((uint32_t)q.s1)); // [t + 1 < 0 and r > 0]
-  int v;
-  asm("shr.s32 %0, %1, %2;" : "=r"(v) : "r"((int32_t)tk - 2 * (int32_t)adj), "r"((uint32_t)q.r));
+  int32_t m, x;
+  asm("shr.s32 %0, %1, 31;" : "=r"(m) : "r"((int32_t)s2));
+  if (!R1) m &= ~q.r0mask; // r == 0: kc carries no -2 and nothing is given back
+  asm("mad.lo.s32 %0, %1, -2, %2;" : "=r"(x) : "r"(m), "r"((int32_t)tk));
+  asm("shr.s32 %0, %1, %2;" : "=r"(v) : "r"(x), "r"((uint32_t)q.r));
   if (ACT == 2) v = min(max(v, -128), 127);
   return v;
 }
+// byte j of a and byte j of b in the two low bytes of a word (the upper bytes are multiplied by zero afterwards)
+template <int J> __device__ __forceinline__ uint32_t byte_pair(uint32_t a, uint32_t b) {
+  return __byte_perm(a, b, (uint32_t)(J | ((4 + J) << 4) | (J << 8) | (J << 12)));
+}
+// The INT8 eltwise add of four packed convolution results x with four packed residual values y:
+// (x * ms + y * mr + rnd) >> r per byte through one four-way dot product each; the saturating pack (and the ReLU on
+// the packed bytes) follow in the caller. mm = (ms, mr, 0, 0) as bytes.
+__device__ __forceinline__ uint32_t add4_packed(uint32_t x, uint32_t y, uint32_t mm, int rnd, int r, bool relu) {
+  const int s0 = __dp4a((int)byte_pair<0>(x, y), (int)mm, rnd) >> r;
+  const int s1 = __dp4a((int)byte_pair<1>(x, y), (int)mm, rnd) >> r;
+  const int s2 = __dp4a((int)byte_pair<2>(x, y), (int)mm, rnd) >> r;
+  const int s3 = __dp4a((int)byte_pair<3>(x, y), (int)mm, rnd) >> r;
+  const uint32_t w = pack4_sat(s0, s1, s2, s3);
+  return relu ? __vmaxs4(w, 0u) : w;
+}
+// ReLU of four packed int8 values
+__device__ __forceinline__ uint32_t relu4(uint32_t w) { return __vmaxs4(w, 0u); }
 // INT8 leaky ReLU of a saturated convolution result (core/activation.cpp:126-153).
 __device__ __forceinline__ int leaky_of(int v, const ConvGemmParams &p) {
   if (v > 0) return p.leaky_mp != 0 ? mul_rshift_sat8(v, p.leaky_mp, p.leaky_rp) : v;
   return mul_rshift_sat8(v, p.leaky_mn, p.leaky_rn);
 }
 
-// Byte-permute selectors of the 4x4 transpose between the four lanes of a group (lane & 3).
+// Byte-permute selectors of the 4x4 transpose between the four lanes of a group (lane & 3): two exchange steps
+// (lane ^ 1, then lane ^ 2); each lane sends its whole word and picks two of its own bytes and two of its
+// partner's with one permute per step.
 struct TransposeSel {
-  uint32_t send1, merge1, send2, merge2;
+  uint32_t merge1, merge2;
 };
 __device__ __forceinline__ TransposeSel make_transpose_sel(int lane) {
   TransposeSel t;
-  const bool b0 = lane & 1, b1 = lane & 2;
-  t.send1 = b0 ? 0x4420u : 0x4431u;
-  t.merge1 = b0 ? 0x3514u : 0x5240u;
-  t.send2 = b1 ? 0x4410u : 0x4432u;
-  t.merge2 = b1 ? 0x3254u : 0x5410u;
+  t.merge1 = (lane & 1) ? 0x3715u : 0x6240u;
+  t.merge2 = (lane & 2) ? 0x3276u : 0x5410u;
   return t;
 }
 // In: lane i of a 4-lane group holds bytes (pixel 0..3) of channel i. Out: lane j holds bytes
 // (channel 0..3) of pixel j.
 __device__ __forceinline__ uint32_t transpose4x4(uint32_t w, const TransposeSel &t) {
-  uint32_t s1 = __byte_perm(w, 0u, t.send1);
-  uint32_t r1 = __shfl_xor_sync(0xffffffffu, s1, 1);
-  uint32_t z = __byte_perm(w, r1, t.merge1);
-  uint32_t s2 = __byte_perm(z, 0u, t.send2);
-  uint32_t r2 = __shfl_xor_sync(0xffffffffu, s2, 2);
-  return __byte_perm(z, r2, t.merge2);
+  const uint32_t z = __byte_perm(w, __shfl_xor_sync(0xffffffffu, w, 1), t.merge1);
+  return __byte_perm(z, __shfl_xor_sync(0xffffffffu, z, 2), t.merge2);
 }
 
 // Epilogue of one accumulator buffer for the 32 channels (TMEM lanes) of this warp.
@@ -403,16 +433,31 @@ __device__ __forceinline__ uint32_t transpose4x4(uint32_t w, const TransposeSel 
 //   out4       output address of (pixel m0, this lane's 4-channel group)
 //   ch4_ok     the 4-channel group lies inside the valid channels
 //   ncols      pixel columns of the accumulator buffer (128; 256 for the two-SM tile)
-template <int ACT, bool FAST>
+template <int ACT, bool FAST, bool R1 = false>
 __device__ __forceinline__ void epilogue_channels_impl(const ConvGemmParams &p, uint32_t lane_addr, int8_t *out4,
                                                        bool ch4_ok, int m0, int half, int halves, int lane,
                                                        const ChanConst &cc, const TransposeSel &ts, int ncols) {
-  auto rq = [&](uint32_t a) { return FAST ? requant_fast<ACT>((int32_t)a, cc, p) : requant_one<ACT>((int32_t)a, cc, p); };
+  constexpr int QACT = ACT == 3 ? 0 : ACT; // the fused add works on the plain (no activation) int8 result
+  auto rq = [&](uint32_t a) { return FAST ? requant_fast<QACT, R1>((int32_t)a, cc, p) : requant_one<QACT>((int32_t)a, cc, p); };
   const int pj = lane & 3;
   // (Software-pipelining these loads in 16-column pieces made the epilogue alone 14% faster and the whole
   // kernel 4% slower, so the two loads of a chunk are simply issued together.)
   for (int colg = half * 32; colg < ncols; colg += 32 * halves) {
     if (m0 + colg >= p.M_total) break;
+    const bool whole = m0 + colg + 32 <= p.M_total; // whole chunk in range: one guard for the eight stores
+    int8_t *o = out4 + (size_t)(colg + pj) * p.ldc;
+    uint32_t y[8];
+    if (ACT == 3) {
+      // the residual words of the fused eltwise add sit where the results go (same geometry): fetched first, so
+      // that their latency passes under the accumulator loads and the requantisation
+      const int8_t *rp = p.res + (size_t)(o - p.out);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        y[k] = 0u;
+        if (ch4_ok && (whole || m0 + colg + 4 * k + pj < p.M_total))
+          y[k] = __ldg(reinterpret_cast<const uint32_t *>(rp + (size_t)(4 * k) * p.ldc));
+      }
+    }
     uint32_t acc0[16], acc1[16];
     ptx::tcgen05_ld_x16(lane_addr + (uint32_t)colg, acc0);
     ptx::tcgen05_ld_x16(lane_addr + (uint32_t)colg + 16u, acc1);
@@ -422,12 +467,25 @@ __device__ __forceinline__ void epilogue_channels_impl(const ConvGemmParams &p, 
     for (int k = 0; k < 4; ++k) {
       w[k] = pack4_sat(rq(acc0[4 * k + 0]), rq(acc0[4 * k + 1]), rq(acc0[4 * k + 2]), rq(acc0[4 * k + 3]));
       w[4 + k] = pack4_sat(rq(acc1[4 * k + 0]), rq(acc1[4 * k + 1]), rq(acc1[4 * k + 2]), rq(acc1[4 * k + 3]));
+      if (FAST && ACT == 1) { // the multiply-high form leaves the ReLU clamp to the packed bytes
+        w[k] = relu4(w[k]);
+        w[4 + k] = relu4(w[4 + k]);
+      }
     }
 #pragma unroll
     for (int k = 0; k < 8; ++k) w[k] = transpose4x4(w[k], ts);
-    const bool whole = m0 + colg + 32 <= p.M_total; // whole chunk in range: one guard for the eight stores
-    int8_t *o = out4 + (size_t)(colg + pj) * p.ldc;
-    if (ACT == 2) {
+    if (ACT == 3) {
+      // fused eltwise add: both tensors are written
+      int8_t *sp = p.out2 + (size_t)(o - p.out);
+      const uint32_t mm = (uint32_t)(uint8_t)p.add_ms | ((uint32_t)(uint8_t)p.add_mr << 8);
+      const int rnd = p.add_r > 0 ? (1 << (p.add_r - 1)) : 0;
+#pragma unroll
+      for (int k = 0; k < 8; ++k)
+        if (ch4_ok && (whole || m0 + colg + 4 * k + pj < p.M_total)) {
+          *reinterpret_cast<uint32_t *>(o + (size_t)(4 * k) * p.ldc) = w[k];
+          *reinterpret_cast<uint32_t *>(sp + (size_t)(4 * k) * p.ldc) = add4_packed(w[k], y[k], mm, rnd, p.add_r, p.add_relu != 0);
+        }
+    } else if (ACT == 2) {
       // fused leaky ReLU: the activation works on the packed, saturated values after the transpose (four
       // channels of one pixel per word); the plain result goes to `out` when the graph keeps that tensor
       uint32_t l[8];
@@ -444,8 +502,13 @@ __device__ __forceinline__ void epilogue_channels_impl(const ConvGemmParams &p, 
         }
     } else if (whole) {
       if (ch4_ok) {
+        // row addresses by one wide multiply-add each (the multiply-add pipe has room, the integer ALU has not)
 #pragma unroll
-        for (int k = 0; k < 8; ++k) *reinterpret_cast<uint32_t *>(o + (size_t)(4 * k) * p.ldc) = w[k];
+        for (int k = 0; k < 8; ++k) {
+          unsigned long long addr;
+          asm("mad.wide.u32 %0, %1, %2, %3;" : "=l"(addr) : "r"((uint32_t)(4 * k)), "r"((uint32_t)p.ldc), "l"((unsigned long long)o));
+          asm volatile("st.global.b32 [%0], %1;" ::"l"(addr), "r"(w[k]) : "memory");
+        }
       }
     } else {
 #pragma unroll
@@ -459,7 +522,8 @@ template <int ACT>
 __device__ __forceinline__ void epilogue_channels(const ConvGemmParams &p, uint32_t lane_addr, int8_t *out4,
                                                   bool ch4_ok, int m0, int half, int halves, int lane,
                                                   const ChanConst &cc, const TransposeSel &ts, int ncols = 128) {
-  if (p.fastq & 1) epilogue_channels_impl<ACT, true>(p, lane_addr, out4, ch4_ok, m0, half, halves, lane, cc, ts, ncols);
+  if ((p.fastq & 3) == 3) epilogue_channels_impl<ACT, true, true>(p, lane_addr, out4, ch4_ok, m0, half, halves, lane, cc, ts, ncols);
+  else if (p.fastq & 1) epilogue_channels_impl<ACT, true, false>(p, lane_addr, out4, ch4_ok, m0, half, halves, lane, cc, ts, ncols);
   else epilogue_channels_impl<ACT, false>(p, lane_addr, out4, ch4_ok, m0, half, halves, lane, cc, ts, ncols);
 }
 
@@ -577,6 +641,10 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
   const uint32_t tiles = p.w_resident ? w_base + (uint32_t)k_iters * b_bytes : w_base;
   const uint32_t stage_bytes = p.w_resident ? a_bytes : a_bytes + b_bytes;
   const uint32_t acc_stride = (uint32_t)(p.tmem_cols >> 1); // columns per accumulator buffer
+  // The tile walk (tile = blockIdx.x + k * gridDim.x, channel tiles fastest) as a running (pixel tile, channel tile)
+  // pair: the per-tile code of every role carries no division.
+  const int walk_m0 = (int)blockIdx.x / n_tiles, walk_n0 = (int)blockIdx.x % n_tiles;
+  const int walk_dm = (int)gridDim.x / n_tiles, walk_dn = (int)gridDim.x % n_tiles;
 
   // A CTA of a launch in which an earlier CTA already gave up does no work at all, so that a
   // broken launch ends quickly instead of timing out once per tile.
@@ -618,9 +686,16 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
           ptx::tma_load_3d(w_base + (uint32_t)kit * b_bytes, &tmB, bar_w, (kit % p.c_chunks) * p.BK,
                            kit / p.c_chunks, n0w);
       }
+      int tm = walk_m0, tn = walk_n0;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile / n_tiles) * m_tile;
-        const int n0 = (tile % n_tiles) * p.BN - (p.dual ? 64 : 0);
+        const int m0 = tm * m_tile;
+        const int n0 = tn * p.BN - (p.dual ? 64 : 0);
+        tm += walk_dm;
+        tn += walk_dn;
+        if (tn >= n_tiles) {
+          tn -= n_tiles;
+          ++tm;
+        }
         int n_img[2] = {0, 0}, h_base[2] = {0, 0}, w_base[2] = {0, 0};
         if (p.a_mode == 1) {
           for (int sub = 0; sub < subs; ++sub) {
@@ -804,11 +879,18 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
     int staged_n0 = -1;
     int t = 0;
     bool ok = true;
+    int tm = walk_m0, tn = walk_n0;
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++t) {
       // dual mode: lanes 0..63 are the channels of the first 128 pixels, lanes 64..127 of the second
       const int ch_base = p.dual ? (quarter & 1) * 32 : quarter * 32;
-      const int m0 = (tile / n_tiles) * m_tile + (p.dual ? 128 * (quarter >> 1) : 0);
-      const int n0 = (tile % n_tiles) * p.BN;
+      const int m0 = tm * m_tile + (p.dual ? 128 * (quarter >> 1) : 0);
+      const int n0 = tn * p.BN;
+      tm += walk_dm;
+      tn += walk_dn;
+      if (tn >= n_tiles) {
+        tn -= n_tiles;
+        ++tm;
+      }
       const int buf = t & 1;
       if (n0 != staged_n0) {
         if (BF16 || TF32) {
@@ -847,6 +929,9 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
           else epilogue_channels_bf16<false>(p, lane_addr, out_pair, ch < p.n_valid, m0, half, kEpilogueWarps / 4, lane, bias_f);
         } else if (p.act == 1) epilogue_channels_impl<1, FAST>(p, lane_addr, out4, ch4_ok, m0, half, kEpilogueWarps / 4, lane, cc, ts, 128);
         else if (p.act == 2) epilogue_channels_impl<2, FAST>(p, lane_addr, out4, ch4_ok, m0, half, kEpilogueWarps / 4, lane, cc, ts, 128);
+        else if (p.act == 3 && FAST && (p.fastq & 2)) epilogue_channels_impl<3, FAST, true>(p, lane_addr, out4, ch4_ok, m0, half, kEpilogueWarps / 4, lane, cc, ts, 128);
+        else if (p.act == 3) epilogue_channels_impl<3, FAST>(p, lane_addr, out4, ch4_ok, m0, half, kEpilogueWarps / 4, lane, cc, ts, 128);
+        else if (FAST && (p.fastq & 2)) epilogue_channels_impl<0, FAST, true>(p, lane_addr, out4, ch4_ok, m0, half, kEpilogueWarps / 4, lane, cc, ts, 128);
         else epilogue_channels_impl<0, FAST>(p, lane_addr, out4, ch4_ok, m0, half, kEpilogueWarps / 4, lane, cc, ts, 128);
       }
       // hand the accumulator buffer back to the MMA issuer

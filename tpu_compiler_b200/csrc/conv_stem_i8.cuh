@@ -147,25 +147,37 @@ conv_stem_i8_kernel(const __grid_constant__ CUtensorMap tmB, const ConvStemParam
         const int x0 = q * p.sw - p.pl;
         const int y0 = pp * p.sh - p.pt;
         const bool x_inside = x0 >= 0 && x0 + 8 <= p.W; // all eight words in range (weights past kw are zero): no per-tap checks
-        for (int r = 0; r < p.kh; ++r) {
-          uint32_t w[8];
+        // Four filter rows at a time: their 32 loads are all issued before the first is used, so that a thread has
+        // four rows' worth of memory latency in flight instead of one (the row count is a run-time value; a plain
+        // loop over the rows would wait for each row's loads before it starts the next).
+        for (int r0 = 0; r0 < p.kh; r0 += 4) {
+          uint32_t w[4][8];
 #pragma unroll
-          for (int s = 0; s < 8; ++s) w[s] = 0u;
-          const int y = y0 + r * p.dh;
-          if (row_ok && y >= 0 && y < p.H) {
-            const uint32_t *src = p.in + ((size_t)nimg * p.H + y) * p.W + x0;
-            if (x_inside) {
+          for (int j = 0; j < 4; ++j) {
 #pragma unroll
-              for (int s = 0; s < 8; ++s) w[s] = __ldg(src + s);
-            } else {
+            for (int s = 0; s < 8; ++s) w[j][s] = 0u;
+            const int r = r0 + j;
+            const int y = y0 + r * p.dh;
+            if (r < p.kh && row_ok && y >= 0 && y < p.H) {
+              const uint32_t *src = p.in + ((size_t)nimg * p.H + y) * p.W + x0;
+              if (x_inside) {
 #pragma unroll
-              for (int s = 0; s < 8; ++s)
-                if (s < p.kw && x0 + s >= 0 && x0 + s < p.W) w[s] = __ldg(src + s);
+                for (int s = 0; s < 8; ++s) w[j][s] = __ldg(src + s);
+              } else {
+#pragma unroll
+                for (int s = 0; s < 8; ++s)
+                  if (s < p.kw && x0 + s >= 0 && x0 + s < p.W) w[j][s] = __ldg(src + s);
+              }
             }
           }
-          uint4 *dst = reinterpret_cast<uint4 *>(a_row + (size_t)r * a_row_bytes);
-          dst[0 ^ sw_bit] = make_uint4(w[0], w[1], w[2], w[3]);
-          dst[1 ^ sw_bit] = make_uint4(w[4], w[5], w[6], w[7]);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            if (r0 + j < p.kh) {
+              uint4 *dst = reinterpret_cast<uint4 *>(a_row + (size_t)(r0 + j) * a_row_bytes);
+              dst[0 ^ sw_bit] = make_uint4(w[j][0], w[j][1], w[j][2], w[j][3]);
+              dst[1 ^ sw_bit] = make_uint4(w[j][4], w[j][5], w[j][6], w[j][7]);
+            }
+          }
         }
         // make the generic-proxy writes visible to the tensor core (async proxy)
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -190,6 +202,7 @@ conv_stem_i8_kernel(const __grid_constant__ CUtensorMap tmB, const ConvStemParam
         const bool ch4_ok = ch4 < p.n_valid;
         if (p.act == 1) epilogue_channels_impl<1, FAST>(ep, lane_addr, out4, ch4_ok, m0e, half, 2, lane, cc, ts, 128);
         else if (p.act == 2) epilogue_channels_impl<2, FAST>(ep, lane_addr, out4, ch4_ok, m0e, half, 2, lane, cc, ts, 128);
+        else if (FAST && (p.fastq & 2)) epilogue_channels_impl<0, FAST, true>(ep, lane_addr, out4, ch4_ok, m0e, half, 2, lane, cc, ts, 128);
         else epilogue_channels_impl<0, FAST>(ep, lane_addr, out4, ch4_ok, m0e, half, 2, lane, cc, ts, 128);
       }
     }

@@ -221,6 +221,7 @@ public:
   int *d_err = nullptr;
   bool use_graph = true;
   bool fuse_activations = true; // set before load_module
+  bool fuse_residual_add = false; // set before load_module: eltwise adds run in the producing convolution's epilogue
   bool fp32_tensor_cores = true; // set before load_module: fp32 convolutions as three TF32 products
   void fuse_activation_chains(const std::map<std::string, int> &uses);
   void link_tf32_remainders();
@@ -715,6 +716,19 @@ public:
     }
     act_ = 2;
   }
+  // Fused eltwise add (tensor-core INT8 plans without an activation of their own): the epilogue also forms
+  // sat8(relu?((conv * ms + residual * mr + 2^(r-1)) >> r)) into `sum_out`; this op's own tensor is still written.
+  bool can_fuse_add() const { return can_fuse_leaky() && plans_.size() == 1 && in_->dtype == DT_I8; }
+  void set_residual_add(const int8_t *residual, int8_t *sum_out, int ms, int mr, int rshift, int relu) {
+    for (auto &pl : plans_) {
+      pl.p.act = 3;
+      pl.p.res = residual;
+      pl.p.out2 = sum_out;
+      pl.p.add_ms = ms; pl.p.add_mr = mr; pl.p.add_r = rshift; pl.p.add_relu = relu;
+    }
+    act_ = 3;
+    alg_bytes += 2.0 * out_->numel(); // the residual read and the sum written
+  }
   const TensorPtr &out() const { return out_; }
   const TensorPtr &in() const { return in_; }
   // TF32 x 3 plans (not the patch-matrix stem, whose remainder belongs to the patch matrix)
@@ -989,6 +1003,11 @@ public:
       parse_coeff(op, f_.coeff, nin);
     }
   }
+  // INT8 two-input add that a producing convolution's epilogue can take over
+  bool is_plain_i8_add() const { return out_->dtype == DT_I8 && !is_mul_ && ins_.size() == 2; }
+  const std::vector<TensorPtr> &inputs() const { return ins_; }
+  const TensorPtr &out() const { return out_; }
+  const EltwiseArgs &i8_args() const { return a_; }
   // fp32 add whose result feeds a TF32 x 3 convolution: also write that convolution's remainder operand
   bool can_write_remainder() const { return out_->dtype == DT_F32 && !is_mul_; }
   void set_remainder_out(float *lo) { f_.lo = lo; }
@@ -1687,6 +1706,34 @@ inline void Interpreter::fuse_activation_chains(const std::map<std::string, int>
       kernels[j] = std::move(away);
       break;
     }
+  }
+  // INT8 eltwise add of two tensors, one of them the result of a tensor-core convolution that feeds nothing else and
+  // runs after the other operand's producer (the last convolution of a residual block): that convolution's epilogue
+  // reads the other operand, forms the sum and writes both tensors; the add op becomes a placeholder
+  // (EltwiseAddOpKernel::i8_invoke, core/eltwise.cpp:52-85, on top of Conv2DOpKernel::invoke, core/conv.cpp:80-104).
+  for (size_t j = 0; j < n && fuse_residual_add; ++j) {
+    auto *ad = dynamic_cast<EltwiseOp *>(kernels[j].get());
+    if (!ad || !ad->is_plain_i8_add()) continue;
+    const auto &ins = ad->inputs();
+    // the producers' positions; the later one must be the convolution
+    int pos[2] = {-1, -1};
+    for (size_t i = 0; i < j; ++i)
+      for (int k = 0; k < 2; ++k)
+        if (kernels[i]->result == ins[k]) pos[k] = (int)i;
+    if (pos[0] < 0 || pos[1] < 0 || ins[0] == ins[1]) continue;
+    const int self = pos[0] > pos[1] ? 0 : 1, other = 1 - self;
+    auto *cv = dynamic_cast<Conv2DOp *>(kernels[pos[self]].get());
+    if (!cv || !cv->can_fuse_add() || !single_use(cv->name)) continue;
+    const TensorPtr &a = cv->out(), &r = ins[other], &o = ad->out();
+    if (a->cp != r->cp || a->cp != o->cp || a->bytes() != r->bytes() || a->bytes() != o->bytes() || a->padded_rows() ||
+        r->padded_rows() || o->padded_rows() || a->cp % 4 != 0)
+      continue;
+    const EltwiseArgs &ea = ad->i8_args();
+    cv->set_residual_add((const int8_t *)r->dev, (int8_t *)o->dev, ea.mult[self], ea.mult[other], ea.rshift, ea.do_relu);
+    std::unique_ptr<OpKernel> away(new FusedAwayOp());
+    away->name = ad->name; away->op_type = ad->op_type; away->shape = ad->shape; away->datatype = ad->datatype;
+    away->result = ad->result; away->line = ad->line; away->dirty = ad->dirty;
+    kernels[j] = std::move(away);
   }
   for (size_t i = 0; i < n; ++i) {
     auto *q0 = dynamic_cast<QuantOp *>(kernels[i].get());

@@ -361,6 +361,8 @@ int tpucb_interp_set_option(tpucb_interp *it, const char *key, int value) {
     it->impl.invalidate_graph();
   } else if (k == "fuse_activations") {
     it->impl.fuse_activations = value != 0; // takes effect at the next load_module
+  } else if (k == "fuse_residual_add") {
+    it->impl.fuse_residual_add = value != 0; // takes effect at the next load_module
   } else if (k == "fp32_tensor_cores") {
     it->impl.fp32_tensor_cores = value != 0; // takes effect at the next load_module
   } else {

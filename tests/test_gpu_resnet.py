@@ -136,3 +136,32 @@ def test_resnet50_with_residual_adds_in_the_convolution_epilogue(model_b1):
     for name in m.get_all_tensor_names():
         assert np.array_equal(m.get_tensor(name).reshape(-1), ref[name].reshape(-1)), name
     m.close()
+
+
+def test_programmatic_dependent_launch_on_and_off(model_b1):
+    """Option pdl: every kernel of the op list is launched so that it may start while its predecessor finishes and
+    orders itself behind it on the device. Forced on and forced off must give the same tensors, launch after launch
+    (a kernel that read its input too early would show as a difference between replays)."""
+    from tpu_compiler_b200 import module
+    B = 2
+    imgs = np.random.default_rng(7).uniform(-1, 1, (B, 3, 224, 224)).astype(np.float32)
+    mb = graphs.resnet50_int8(batch=B, seed=1001)
+    names = ["conv1", "pool1", "res2a", "res3d", "res4f", "res5c", "pool5", "fc1000_dequant"]
+    got = {}
+    for pdl in (0, 1):
+        m = module(0)
+        m.set_option("pdl", pdl)
+        m.load_text(mb.text, mb.weights)
+        for rep in range(6):
+            m.set_tensor("data", imgs if rep % 2 == 0 else imgs[::-1].copy())
+            m.invoke()
+            cur = {n: m.get_tensor(n) for n in names}
+            if rep >= 2:
+                for n in names:
+                    assert np.array_equal(cur[n], got[(pdl, rep % 2)][n]), (pdl, rep, n)
+            else:
+                got[(pdl, rep)] = cur
+        m.close()
+    for n in names:
+        assert np.array_equal(got[(0, 0)][n], got[(1, 0)][n]) and np.array_equal(got[(0, 1)][n], got[(1, 1)][n]), n
+        assert np.array_equal(got[(0, 0)][n][0], got[(0, 1)][n][1]), n

@@ -22,6 +22,7 @@ __device__ __forceinline__ void atomic_min_f32(float *addr, float v) {
 // same layout in the same pass (the copy the histogram pass reads when the activations of all batches stay resident).
 __global__ void minmax_f32_kernel(const float *__restrict__ x, size_t pixels, int c, int cp, float *stats,
                                   float *__restrict__ keep) {
+  pdl_prologue();
   float mn = INFINITY, mx = -INFINITY;
   const size_t total = pixels * (size_t)cp;
   if ((cp & 3) == 0 && (c & 3) == 0) {
@@ -87,6 +88,7 @@ __global__ void minmax_f32_kernel(const float *__restrict__ x, size_t pixels, in
 // warp-aggregated atomics (lanes that hit the same bin elect one adder), flushed with 64-bit atomics.
 __global__ void hist_f32_kernel(const float *__restrict__ x, size_t pixels, int c, int cp, float width, int bins,
                                 unsigned long long *__restrict__ hist) {
+  pdl_prologue();
   extern __shared__ unsigned int s_h[];
   for (int i = threadIdx.x; i < bins; i += blockDim.x) s_h[i] = 0;
   __syncthreads();
@@ -169,6 +171,7 @@ struct StatDesc {
 };
 
 __global__ void __launch_bounds__(1024) minmax_multi_kernel(const StatDesc *__restrict__ descs, int count, float *stats) {
+  pdl_prologue();
   __shared__ float smn[32], smx[32];
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   for (int t = 0; t < count; ++t) {
@@ -228,6 +231,7 @@ __global__ void __launch_bounds__(1024) minmax_multi_kernel(const StatDesc *__re
 // hist [count][bins]; the bin rule of hist_f32_kernel.
 __global__ void __launch_bounds__(1024) hist_multi_kernel(const StatDesc *__restrict__ descs, int count, int bins,
                                                            unsigned long long *__restrict__ hist) {
+  pdl_prologue();
   extern __shared__ unsigned int s_h[];
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   const float top = (float)bins;
@@ -275,6 +279,7 @@ __global__ void __launch_bounds__(1024) hist_multi_kernel(const StatDesc *__rest
 // additions of the converted counts; each KL term is formed in double and added into an fp32
 // accumulator in index order.
 __global__ void kld_kernel(const long long *__restrict__ hists, int N, float *__restrict__ kl_out) {
+  pdl_prologue();
   extern __shared__ unsigned char kld_smem[];
   float *P = reinterpret_cast<float *>(kld_smem);
   float *Q = P + N;
@@ -341,6 +346,7 @@ struct DistGeom {
 // in double. One thread handles four channels of one pixel per step; grid = (blocks per image, images).
 template <int TGT>
 __global__ void tuner_distance_kernel(DistGeom ref, DistGeom tgt, int c, int h, int w, float scale, double *sums) {
+  pdl_prologue();
   const int img = blockIdx.y;
   const int c4 = (c + 3) >> 2;
   const size_t quads = (size_t)h * w * c4;

@@ -90,6 +90,17 @@ TPUCB_HD float bf16_round(float f, bool rounding = true) {
 }
 
 #ifdef __CUDACC__
+// Programmatic dependent launch (kernels launched through launch_k with the stream-serialisation attribute): a kernel
+// lets its successor in the stream be scheduled early (pdl_trigger) and waits for its predecessor's memory operations
+// before its own first global access (pdl_wait). Both are no-ops in a kernel launched the ordinary way.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// first statement of every kernel that has no set-up worth overlapping
+__device__ __forceinline__ void pdl_prologue() {
+  pdl_trigger();
+  pdl_wait();
+}
+
 // Two F32ToBF16 roundings in one conversion instruction: {bf16(hi), bf16(lo)} packed in a word.
 // The hardware conversion equals the reference's add-and-shift rule whenever its result is
 // finite; a result with an all-ones exponent (inf/NaN in, or rounding past max-finite) takes

@@ -629,7 +629,7 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
   const int m_tile = p.dual ? 256 : 128;
   const int subs = p.dual ? 2 : 1;
   const int m_tiles = (p.M_total + m_tile - 1) / m_tile;
-  const int total_tiles = n_tiles * m_tiles;
+  int total_tiles = n_tiles * m_tiles; // set to 0 below when the launch is already marked as failed
   const uint32_t a_bytes = (uint32_t)m_tile * (uint32_t)p.BK;
   const uint32_t b_bytes = (uint32_t)(p.dual ? 192 : p.BN) * (uint32_t)p.BK;
   const int taps = p.kh * p.kw;
@@ -646,13 +646,12 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
   const int walk_m0 = (int)blockIdx.x / n_tiles, walk_n0 = (int)blockIdx.x % n_tiles;
   const int walk_dm = (int)gridDim.x / n_tiles, walk_dn = (int)gridDim.x % n_tiles;
 
-  // A CTA of a launch in which an earlier CTA already gave up does no work at all, so that a
-  // broken launch ends quickly instead of timing out once per tile.
-  if (threadIdx.x == 0) *abort_flag = *reinterpret_cast<volatile int *>(p.err);
-  __syncthreads();
-  if (*abort_flag != 0) return;
-
+  // Programmatic dependent launch: the next kernel of the stream may start its own set-up as soon as every CTA
+  // of this launch has got here; this kernel in turn sets up its barriers and tensor memory while the
+  // previous one is still finishing and only then waits for that kernel's results (pdl_wait below).
+  pdl_trigger();
   if (threadIdx.x == 0) {
+    *abort_flag = 0;
     for (int s = 0; s < p.stages; ++s) {
       ptx::mbar_init(bar_full + 8 * s, 1);
       ptx::mbar_init(bar_empty + 8 * s, 1);
@@ -671,6 +670,13 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
   __syncthreads();
   ptx::tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // From here on the kernel touches global memory: the previous kernel's writes must be complete and visible.
+  pdl_wait();
+  // A CTA of a launch in which an earlier CTA already gave up does no work at all, so that a
+  // broken launch ends quickly instead of timing out once per tile.
+  if (threadIdx.x == 0) *abort_flag = *reinterpret_cast<volatile int *>(p.err);
+  __syncthreads();
+  if (*abort_flag != 0) total_tiles = 0;
 
   if (warp == 0) {
     // ---------------------------------------------------------------- producer
@@ -984,6 +990,7 @@ conv_gemm_tf32x3_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
 // a kind::tf32 product uses of it), lo = x - hi exactly. 16-byte vectors; `hi` may be null (the tensor core makes the
 // same cut when it reads x itself).
 __global__ void tf32_split_kernel(const float4 *__restrict__ x, float4 *__restrict__ hi, float4 *__restrict__ lo, size_t nvec) {
+  pdl_prologue();
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) {
     const float4 v = x[i];
     float4 h, l;

@@ -421,27 +421,27 @@ inline void launch_conv_plan(const ConvPlan &pl, cudaStream_t stream, int sm_cou
   if (pl.use_patch) {
     size_t total = (size_t)pl.p.M_total * pl.patch.kp;
     if (pl.patch.cv == 4 && pl.patch_elsize == 4)
-      patch_expand_tap_kernel<float><<<grid_for(total / 4, 256, sm_count), 256, 0, stream>>>(
+      launch_k(patch_expand_tap_kernel<float>, grid_for(total / 4, 256, sm_count), 256, 0, stream, 
           reinterpret_cast<const float *>(pl.in), reinterpret_cast<float *>(pl.patch_buf), pl.split_lo, pl.patch);
     else if (pl.patch.cv == 4)
-      patch_expand_tap_kernel<uint16_t><<<grid_for(total / 4, 256, sm_count), 256, 0, stream>>>(
+      launch_k(patch_expand_tap_kernel<uint16_t>, grid_for(total / 4, 256, sm_count), 256, 0, stream, 
           reinterpret_cast<const uint16_t *>(pl.in), reinterpret_cast<uint16_t *>(pl.patch_buf), nullptr, pl.patch);
     else if (pl.patch_elsize == 2)
-      patch_expand_kernel<uint16_t><<<grid_for(total / 8, 256, sm_count), 256, 0, stream>>>(
+      launch_k(patch_expand_kernel<uint16_t>, grid_for(total / 8, 256, sm_count), 256, 0, stream, 
           reinterpret_cast<const uint16_t *>(pl.in), reinterpret_cast<uint16_t *>(pl.patch_buf), pl.patch);
     else
-      patch_expand_i8_kernel<<<grid_for(total, 256, sm_count), 256, 0, stream>>>(pl.in, pl.patch_buf, pl.patch);
+      launch_k(patch_expand_i8_kernel, grid_for(total, 256, sm_count), 256, 0, stream, pl.in, pl.patch_buf, pl.patch);
   }
   const int threads = kConvThreads;
   if (pl.tf32) {
     if (pl.split_src)
-      tf32_split_kernel<<<grid_for(pl.split_nvec, 256, sm_count), 256, 0, stream>>>(
+      launch_k(tf32_split_kernel, grid_for(pl.split_nvec, 256, sm_count), 256, 0, stream, 
         reinterpret_cast<const float4 *>(pl.split_src), reinterpret_cast<float4 *>(pl.split_hi),
         reinterpret_cast<float4 *>(pl.split_lo), pl.split_nvec);
-    conv_gemm_tf32x3_kernel<<<pl.grid, threads, pl.smem, stream>>>(pl.tmA, pl.tmB, pl.tmA2, pl.tmB2, pl.p);
-  } else if (pl.bf16) conv_gemm_bf16_kernel<<<pl.grid, threads, pl.smem, stream>>>(pl.tmA, pl.tmB, pl.p);
-  else if (!(pl.p.fastq & 1)) conv_gemm_i8_wide_kernel<<<pl.grid, threads, pl.smem, stream>>>(pl.tmA, pl.tmB, pl.p);
-  else conv_gemm_i8_kernel<<<pl.grid, threads, pl.smem, stream>>>(pl.tmA, pl.tmB, pl.p);
+    launch_k(conv_gemm_tf32x3_kernel, pl.grid, threads, pl.smem, stream, pl.tmA, pl.tmB, pl.tmA2, pl.tmB2, pl.p);
+  } else if (pl.bf16) launch_k(conv_gemm_bf16_kernel, pl.grid, threads, pl.smem, stream, pl.tmA, pl.tmB, pl.p);
+  else if (!(pl.p.fastq & 1)) launch_k(conv_gemm_i8_wide_kernel, pl.grid, threads, pl.smem, stream, pl.tmA, pl.tmB, pl.p);
+  else launch_k(conv_gemm_i8_kernel, pl.grid, threads, pl.smem, stream, pl.tmA, pl.tmB, pl.p);
 }
 
 inline void conv_kernel_setup_once() {

@@ -61,7 +61,7 @@ conv_stem_i8_kernel(const __grid_constant__ CUtensorMap tmB, const ConvStemParam
   // channel tile (tile % n_tiles) never changes for a CTA.
   const int n_tiles = (p.n_valid + p.BN - 1) / p.BN;
   const int m_tiles = (p.M_total + m_tile - 1) / m_tile;
-  const int total_tiles = n_tiles * m_tiles;
+  int total_tiles = n_tiles * m_tiles; // set to 0 below when the launch is already marked as failed
   const int n0 = (int)(blockIdx.x % n_tiles) * p.BN;
   ConvGemmParams ep; // the shared epilogue reads these fields
   ep.BN = p.BN; ep.n_valid = p.n_valid; ep.act = p.act; ep.M_total = p.M_total; ep.ldc = p.ldc;
@@ -69,11 +69,9 @@ conv_stem_i8_kernel(const __grid_constant__ CUtensorMap tmB, const ConvStemParam
   ep.leaky_mp = p.leaky_mp; ep.leaky_rp = p.leaky_rp; ep.leaky_mn = p.leaky_mn; ep.leaky_rn = p.leaky_rn;
   ep.out = p.out; ep.out2 = nullptr; ep.fastq = p.fastq;
 
-  if (threadIdx.x == 0) *abort_flag = *reinterpret_cast<volatile int *>(p.err);
-  __syncthreads();
-  if (*abort_flag != 0) return;
-
+  pdl_trigger(); // see conv_gemm_body: set-up overlaps the previous kernel's tail
   if (threadIdx.x == 0) {
+    *abort_flag = 0;
     // every gathering thread arrives once per tile (also those without a pixel), so that the next
     // tile's MMAs cannot start before all epilogue warps have left the accumulator
     ptx::mbar_init(bar_a, (uint32_t)(kStemThreads - 32));
@@ -86,6 +84,10 @@ conv_stem_i8_kernel(const __grid_constant__ CUtensorMap tmB, const ConvStemParam
   __syncthreads();
   ptx::tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait(); // global memory from here on
+  if (threadIdx.x == 0) *abort_flag = *reinterpret_cast<volatile int *>(p.err);
+  __syncthreads();
+  if (*abort_flag != 0) total_tiles = 0;
 
   if (warp == 0) {
     if (lane == 0 && (int)blockIdx.x < total_tiles) {

@@ -34,6 +34,7 @@ struct MaxMinArgs {
   int nin, rshift, do_relu, is_min;
 };
 __global__ void eltwise_maxmin_i8_kernel(MaxMinArgs a, int8_t *__restrict__ out, size_t nvec) {
+  pdl_prologue();
   const int rnd = a.rshift > 0 ? (1 << (a.rshift - 1)) : 0;
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) {
     int v[16];
@@ -85,6 +86,7 @@ struct BroadcastArgs {
 };
 __global__ void broadcast_kernel(const void *__restrict__ a, const void *__restrict__ b, void *__restrict__ out,
                                  BroadcastArgs p) {
+  pdl_prologue();
   const size_t total = (size_t)p.so[0] * p.so[1] * p.so[2] * p.so[3];
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
     const int w = (int)(i % p.so[3]);
@@ -132,6 +134,7 @@ struct RemapArgs {
   int es;           // element size in bytes
 };
 __global__ void remap_kernel(const uint8_t *__restrict__ in, uint8_t *__restrict__ out, RemapArgs p) {
+  pdl_prologue();
   const size_t total = (size_t)p.so[0] * p.so[1] * p.so[2] * p.so[3];
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
     int o[4];
@@ -187,6 +190,7 @@ struct ReduceArgs {
   float coeff;
 };
 __global__ void reduce_kernel(const void *__restrict__ in, void *__restrict__ out, ReduceArgs p) {
+  pdl_prologue();
   const size_t total = (size_t)p.outer * p.inner;
   for (size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
     const int i = (int)(idx % p.inner);
@@ -234,6 +238,7 @@ struct EltwiseBf16Args {
 // form, operand by operand from 0 (add) or 1 (mul), product and sum rounded separately, ReLU, then one
 // BF16 rounding of the result.
 template <bool MUL> __global__ void eltwise_bf16_kernel(EltwiseBf16Args a, uint4 *__restrict__ out, size_t nvec) {
+  pdl_prologue();
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) {
     float acc[8];
 #pragma unroll
@@ -272,6 +277,7 @@ template <bool MUL> __global__ void eltwise_bf16_kernel(EltwiseBf16Args a, uint4
 // or by the number of valid taps) is rounded to BF16 when stored, where the reference's fp32
 // container keeps the unrounded quotient: at most half a BF16 ulp apart.
 __global__ void pool_bf16_kernel(const uint4 *__restrict__ in, uint4 *__restrict__ out, PoolArgs a, int count_include_pad) {
+  pdl_prologue();
   const int vecs = a.cp / 8;
   const size_t total = (size_t)a.n * a.oh * a.ow * vecs;
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
@@ -341,6 +347,7 @@ __device__ __forceinline__ size_t matmul_index(int trans, int bh, int bl, int nb
   return trans ? (((size_t)bh * rows + r) * nbl + bl) * cols + c : (((size_t)bh * nbl + bl) * rows + r) * cols + c;
 }
 template <int DT> __global__ void matmul_kernel(const void *__restrict__ a, const void *__restrict__ b, void *__restrict__ out, MatMulArgs p) {
+  pdl_prologue();
   __shared__ float As[16][17], Bs[16][17];
   const int tx = threadIdx.x, ty = threadIdx.y;
   const int bh = blockIdx.z / p.bl, bl = blockIdx.z % p.bl;
@@ -388,6 +395,7 @@ struct SoftmaxBf16Args {
   float lut_scale, const_val;
 };
 __global__ void softmax_bf16_kernel(const uint16_t *__restrict__ in, uint16_t *__restrict__ out, SoftmaxBf16Args a) {
+  pdl_prologue();
   extern __shared__ float sm_buf[]; // sub[c], ex[c]
   __shared__ float red[32];
   __shared__ float s_r;

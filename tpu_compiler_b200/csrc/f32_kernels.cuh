@@ -25,6 +25,7 @@ struct ConvF32Args {
 __global__ void __launch_bounds__(256)
 conv2d_f32_kernel(const float *__restrict__ in, const float *__restrict__ w, const float *__restrict__ bias,
                   float *__restrict__ out, ConvF32Args a) {
+  pdl_prologue();
   __shared__ float As[16][64 + 4];
   __shared__ float Bs[16][64];
   const int tid = threadIdx.x;
@@ -119,6 +120,7 @@ conv2d_f32_kernel(const float *__restrict__ in, const float *__restrict__ w, con
 __global__ void __launch_bounds__(256, 2)
 conv2d_f32_tile128_kernel(const float *__restrict__ in, const float *__restrict__ w, const float *__restrict__ bias,
                           float *__restrict__ out, ConvF32Args a) {
+  pdl_prologue();
   __shared__ __align__(16) float As[16][128 + 4];
   __shared__ __align__(16) float Bs[16][128];
   const int tid = threadIdx.x;
@@ -244,16 +246,17 @@ inline void launch_conv2d_f32(const float *in, const float *w, const float *bias
   (void)sm_count; // the large tile also wins on the layers that leave SMs without a CTA (measured)
   if (g.ic % 16 == 0 && icp == g.ic) {
     dim3 grid((a.M + 127) / 128, a.wld / 128);
-    conv2d_f32_tile128_kernel<<<grid, 256, 0, s>>>(in, w, bias, out, a);
+    launch_k(conv2d_f32_tile128_kernel, grid, 256, 0, s, in, w, bias, out, a);
     return;
   }
   dim3 grid((a.M + 63) / 64, a.wld / 64);
-  conv2d_f32_kernel<<<grid, 256, 0, s>>>(in, w, bias, out, a);
+  launch_k(conv2d_f32_kernel, grid, 256, 0, s, in, w, bias, out, a);
 }
 
 // Y[m][n] = X[m][k] . W[n][k] + b, optional ReLU; one warp per output element.
 __global__ void fc_f32_kernel(const float *__restrict__ x, const float *__restrict__ w, const float *__restrict__ bias,
                               float *__restrict__ y, int m, int k, int n, int ldy, int do_relu) {
+  pdl_prologue();
   int warp = (blockIdx.x * blockDim.x + threadIdx.x) / 32, lane = threadIdx.x & 31;
   if (warp >= m * n) return;
   int i = warp / n, j = warp % n;
@@ -269,12 +272,13 @@ __global__ void fc_f32_kernel(const float *__restrict__ x, const float *__restri
 inline void launch_fc_f32(const float *x, const float *w, const float *b, float *y, int m, int k, int n, int ldy,
                           int do_relu, cudaStream_t s) {
   size_t threads = (size_t)m * n * 32;
-  fc_f32_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, s>>>(x, w, b, y, m, k, n, ldy, do_relu);
+  launch_k(fc_f32_kernel, (unsigned)((threads + 255) / 256), 256, 0, s, x, w, b, y, m, k, n, ldy, do_relu);
 }
 
 // fp32 pooling: max ignores padded taps; avg divides by kh*kw (count_include_pad) or by the
 // number of valid taps (NativeCpuImplementation.h:104-160).
 __global__ void pool_f32_kernel(const float *__restrict__ in, float *__restrict__ out, PoolArgs a, int count_include_pad) {
+  pdl_prologue();
   const size_t total = (size_t)a.n * a.oh * a.ow * a.cp;
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
     int c = (int)(i % a.cp);
@@ -303,11 +307,12 @@ __global__ void pool_f32_kernel(const float *__restrict__ in, float *__restrict_
 }
 inline void launch_pool_f32(const float *in, float *out, const PoolArgs &a, int cip, cudaStream_t s, int sm_count) {
   size_t total = (size_t)a.n * a.oh * a.ow * a.cp;
-  pool_f32_kernel<<<grid_for(total, 256, sm_count), 256, 0, s>>>(in, out, a, cip);
+  launch_k(pool_f32_kernel, grid_for(total, 256, sm_count), 256, 0, s, in, out, a, cip);
 }
 
 __global__ void scale_f32_kernel(const float *__restrict__ in, const float *__restrict__ sc, const float *__restrict__ bi,
                                  float *__restrict__ out, size_t n, int cp) {
+  pdl_prologue();
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
     int c = (int)(i % cp);
     out[i] = __fadd_rn(__fmul_rn(in[i], sc[c]), bi[c]);
@@ -318,6 +323,7 @@ __global__ void scale_f32_kernel(const float *__restrict__ in, const float *__re
 // prepared per channel by the host in fp32 as the reference forms them; a subtraction and an IEEE division per value.
 __global__ void batchnorm_f32_kernel(const float *__restrict__ in, const float *__restrict__ mean, const float *__restrict__ den,
                                      float *__restrict__ out, size_t n, int cp) {
+  pdl_prologue();
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
     int c = (int)(i % cp);
     out[i] = __fdiv_rn(__fsub_rn(in[i], mean[c]), den[c]);
@@ -326,6 +332,7 @@ __global__ void batchnorm_f32_kernel(const float *__restrict__ in, const float *
 
 // softmax over the channel axis of one pixel per CTA.
 __global__ void softmax_f32_kernel(const float *__restrict__ in, float *__restrict__ out, int c, int cp) {
+  pdl_prologue();
   __shared__ float red[32];
   const float *p = in + (size_t)blockIdx.x * cp;
   float *q = out + (size_t)blockIdx.x * cp;

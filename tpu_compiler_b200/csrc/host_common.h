@@ -73,6 +73,33 @@ struct HostWeight {
   std::vector<int64_t> shape;
 };
 
+// Whether launch_k marks its launches for programmatic dependent launch (option "pdl" of the interpreter whose call
+// is running; set by Interpreter::bind).
+inline bool &launch_pdl_flag() {
+  static thread_local bool on = true;
+  return on;
+}
+
+#ifdef __CUDACC__
+// Launch of an op kernel. With the flag above the launch carries the programmatic stream serialisation
+// attribute: the kernel may be scheduled while its predecessor in the stream is still running and orders itself
+// behind it with pdl_wait (every kernel launched this way begins with pdl_prologue or places pdl_wait itself).
+template <typename... KArgs, typename G, typename B, typename... Args>
+inline void launch_k(void (*kernel)(KArgs...), G grid, B block, size_t smem, cudaStream_t stream, Args &&...args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(block);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = launch_pdl_flag() ? 1 : 0;
+  TPUCB_CUDA(cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...));
+}
+#endif
+
 // Grid for a grid-stride kernel: a multiple of the SM count, capped by the work.
 inline int grid_for(size_t work_items, int block, int sm_count) {
   size_t blocks = (work_items + block - 1) / block;

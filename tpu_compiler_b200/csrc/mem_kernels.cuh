@@ -29,6 +29,7 @@ struct TensorGeom {
 template <int DT>
 __global__ void nchw_f32_to_dev_kernel(const float *__restrict__ src, void *__restrict__ dst,
                                        TensorGeom g) {
+  pdl_prologue();
   const size_t total = (size_t)g.n * g.h * g.wphys * g.cp;
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
        i += (size_t)gridDim.x * blockDim.x) {
@@ -50,6 +51,7 @@ __global__ void nchw_f32_to_dev_kernel(const float *__restrict__ src, void *__re
 // 16-byte NHWC4 word. This is the per-step input path of a serving loop.
 __global__ void nchw_f32_to_nhwc4_kernel(const float *__restrict__ src, float4 *__restrict__ dst, int n, int c,
                                          size_t hw) {
+  pdl_prologue();
   const size_t total = (size_t)n * hw;
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
     const size_t b = i / hw, p = i - b * hw;
@@ -68,6 +70,7 @@ __global__ void nchw_f32_to_nhwc4_kernel(const float *__restrict__ src, float4 *
 template <int DT>
 __global__ void dev_to_nchw_f32_kernel(const void *__restrict__ src, float *__restrict__ dst,
                                        TensorGeom g) {
+  pdl_prologue();
   const size_t total = (size_t)g.n * g.c * g.h * g.w;
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
        i += (size_t)gridDim.x * blockDim.x) {
@@ -107,6 +110,7 @@ __device__ __forceinline__ void store_from_f32(void *p, int dt, size_t i, float 
 // fp32 NHWC4 input image -> BF16 tensor with a 16-channel pitch (quant NONE -> BF16: the upper half of each fp32
 // word, no rounding, QuantOpKernel's cast): one pixel per thread, one 16-byte read, two 16-byte writes.
 __global__ void quant_f32c4_to_bf16c16_kernel(const float4 *__restrict__ in, uint4 *__restrict__ out, size_t pixels, int c) {
+  pdl_prologue();
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < pixels; i += (size_t)gridDim.x * blockDim.x) {
     const float4 v = __ldg(in + i);
     const uint32_t h0 = __float_as_uint(v.x) >> 16, h1 = c > 1 ? __float_as_uint(v.y) >> 16 : 0u;
@@ -119,6 +123,7 @@ __global__ void quant_f32c4_to_bf16c16_kernel(const float4 *__restrict__ in, uin
 __global__ void quant_kernel(const void *__restrict__ src, void *__restrict__ dst, size_t rows, int w,
                              int wl, int wphys, int c, int cps, int cpd, int sdt, int ddt, int kind,
                              float scale) {
+  pdl_prologue();
   const size_t total = rows * (size_t)wphys * (size_t)cpd;
   const float sb = bf16_round(scale);
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
@@ -162,6 +167,7 @@ __device__ __forceinline__ void dequant_word_bf16(uint32_t w, float sb, uint32_t
 }
 __global__ void quant_i8_to_bf16_vec_kernel(const uint4 *__restrict__ src, uint4 *__restrict__ dst,
                                             size_t nvec, float scale) {
+  pdl_prologue();
   const float sb = bf16_round(scale);
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nvec;
        i += (size_t)gridDim.x * blockDim.x) {
@@ -185,6 +191,7 @@ __device__ __forceinline__ uint32_t quant_bf16x4_to_i8(uint32_t a, uint32_t b, f
 }
 __global__ void quant_bf16_to_i8_vec_kernel(const uint4 *__restrict__ src, uint4 *__restrict__ dst,
                                             size_t nvec, float scale) {
+  pdl_prologue();
   const float sb = bf16_round(scale);
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nvec;
        i += (size_t)gridDim.x * blockDim.x) {
@@ -199,6 +206,7 @@ __global__ void quant_bf16_to_i8_vec_kernel(const uint4 *__restrict__ src, uint4
 // destination pixel, one 16-byte load and one 8/16-byte store.
 __global__ void quant_input_pix_kernel(const float4 *__restrict__ src, void *__restrict__ dst, int n,
                                        int h, int w, int c, int cpd, int wl, int wphys, float scale) {
+  pdl_prologue();
   const size_t total = (size_t)n * h * wphys;
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
        i += (size_t)gridDim.x * blockDim.x) {
@@ -251,6 +259,7 @@ __device__ __forceinline__ void madd_vec16(int (&acc)[16], const uint4 &v, int m
 // max(sum + rnd, 0) >> r equals (max(sum, 0) + rnd) >> r because rnd < 2^r.
 template <int NIN, bool RELU>
 __global__ void eltwise_add_i8_kernel(EltwiseArgs a, int8_t *__restrict__ out, size_t nvec) {
+  pdl_prologue();
   const int rnd = a.rshift > 0 ? (1 << (a.rshift - 1)) : 0;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nvec; i += 2 * stride) {
@@ -286,6 +295,7 @@ __global__ void eltwise_add_i8_kernel(EltwiseArgs a, int8_t *__restrict__ out, s
 
 // INT8 mul: product, ReLU, QDM requant with a scalar (M, r). eltwise.cpp:335-357.
 __global__ void eltwise_mul_i8_kernel(EltwiseArgs a, int8_t *__restrict__ out, size_t nvec) {
+  pdl_prologue();
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nvec;
        i += (size_t)gridDim.x * blockDim.x) {
     int acc[16];
@@ -320,6 +330,7 @@ struct EltwiseF32Args {
 // One 16-byte vector per thread and step (fp32 tensors are a whole number of them: the channel pitch is a
 // multiple of 4); operand by operand, product and sum rounded separately, as the reference's loop.
 __global__ void eltwise_add_f32_kernel(EltwiseF32Args a, float *__restrict__ out, size_t n) {
+  pdl_prologue();
   const size_t nvec = n / 4;
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nvec;
        i += (size_t)gridDim.x * blockDim.x) {
@@ -359,6 +370,7 @@ struct PoolArgs {
 };
 // Max pooling on packed bytes: four signed 8-bit maxima per instruction, no unpacking.
 __global__ void pool_max_i8_kernel(const int8_t *__restrict__ in, int8_t *__restrict__ out, PoolArgs a) {
+  pdl_prologue();
   const int vecs = a.cp / 16;
   const size_t total = (size_t)a.n * a.oh * a.ow * vecs;
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
@@ -387,6 +399,7 @@ __global__ void pool_max_i8_kernel(const int8_t *__restrict__ in, int8_t *__rest
 }
 
 __global__ void pool_i8_kernel(const int8_t *__restrict__ in, int8_t *__restrict__ out, PoolArgs a) {
+  pdl_prologue();
   const int vecs = a.cp / 16;
   const size_t total = (size_t)a.n * a.oh * a.ow * vecs;
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
@@ -429,6 +442,7 @@ __global__ void pool_i8_kernel(const int8_t *__restrict__ in, int8_t *__restrict
 // one (output pixel, 16-channel vector), each sums every eighth tap, and three shuffle steps add
 // the partial sums; a window is otherwise one long serial chain per thread.
 __global__ void pool_avg_wide_i8_kernel(const int8_t *__restrict__ in, int8_t *__restrict__ out, PoolArgs a) {
+  pdl_prologue();
   const int vecs = a.cp / 16;
   const size_t items = (size_t)a.n * a.oh * a.ow * vecs;
   const int sub = threadIdx.x & 7;
@@ -480,6 +494,7 @@ struct DwArgs {
   const int32_t *bias, *mult, *rshift; // [cp]
 };
 __global__ void dwconv_i8_kernel(const int8_t *__restrict__ in, int8_t *__restrict__ out, DwArgs a) {
+  pdl_prologue();
   const int vecs = a.cp / 16;
   const size_t total = (size_t)a.n * a.oh * a.ow * vecs;
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
@@ -528,6 +543,7 @@ __global__ void dwconv_i8_kernel(const int8_t *__restrict__ in, int8_t *__restri
 template <int S, int TW, bool RELU>
 __global__ void __launch_bounds__(128)
 dwconv3x3_i8_kernel(const uint32_t *__restrict__ in, uint32_t *__restrict__ out, DwArgs a) {
+  pdl_prologue();
   constexpr int WC = (TW - 1) * S + 3; // input columns under TW outputs
   const int cw = a.cp / 4;
   const int xg = (a.ow + TW - 1) / TW;
@@ -605,6 +621,7 @@ struct PatchArgs {
 };
 __global__ void patch_expand_i8_kernel(const int8_t *__restrict__ in, int8_t *__restrict__ out,
                                        PatchArgs a) {
+  pdl_prologue();
   const size_t total = (size_t)a.n * a.oh * a.ow * a.kp;
   const int ihd = (a.ih - 1) * (a.ins_h + 1) + 1, iwd = (a.iw - 1) * (a.ins_w + 1) + 1;
   const int kreal = a.kh * a.kw * a.c_count;
@@ -636,6 +653,7 @@ __global__ void patch_expand_i8_kernel(const int8_t *__restrict__ in, int8_t *__
 // tap; the expanded matrix [M][kp] is a plain K-major operand with a handful of 128-byte K blocks.
 template <typename T>
 __global__ void patch_expand_kernel(const T *__restrict__ in, T *__restrict__ out, PatchArgs a) {
+  pdl_prologue();
   constexpr int V = 16 / (int)sizeof(T);
   const size_t total = (size_t)a.n * a.oh * a.ow * (a.kp / V);
   const int kreal = a.kh * a.kw * a.c_count;
@@ -669,6 +687,7 @@ __global__ void patch_expand_kernel(const T *__restrict__ in, T *__restrict__ ou
 // x - (upper 19 bits of x), is written beside it, which saves the separate split pass over the matrix.
 template <typename T>
 __global__ void patch_expand_tap_kernel(const T *__restrict__ in, T *__restrict__ out, T *__restrict__ lo, PatchArgs a) {
+  pdl_prologue();
   const int taps = a.kh * a.kw;
   const int slots = a.kp / 4; // vectors per row, the last ones are padding
   const size_t total = (size_t)a.n * a.oh * a.ow * slots;
@@ -713,6 +732,7 @@ __global__ void patch_expand_tap_kernel(const T *__restrict__ in, T *__restrict_
 __global__ void concat_slice_i8_kernel(const int8_t *__restrict__ in, int8_t *__restrict__ out,
                                        size_t pixels, int c, int cps, int cpd, int c_off, int mult,
                                        int rshift, int requant, int do_relu) {
+  pdl_prologue();
   const size_t total = pixels * (size_t)c;
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
        i += (size_t)gridDim.x * blockDim.x) {
@@ -730,6 +750,7 @@ __global__ void concat_slice_i8_kernel(const int8_t *__restrict__ in, int8_t *__
 __global__ void concat_slice_i8_vec_kernel(const uint4 *__restrict__ in, uint4 *__restrict__ out,
                                            size_t pixels, int cv, int cpsv, int cpdv, int offv, int mult,
                                            int rshift, int requant, int do_relu) {
+  pdl_prologue();
   const size_t total = pixels * (size_t)cv;
   const int rnd = rshift > 0 ? (1 << (rshift - 1)) : 0;
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
@@ -762,6 +783,7 @@ struct MoveArgs {
   int n, ic, ih, iw, icp, oc, oh, ow, ocp, es, mode, r, scale_h, scale_w;
 };
 __global__ void move_kernel(const uint8_t *__restrict__ in, uint8_t *__restrict__ out, MoveArgs a) {
+  pdl_prologue();
   const size_t total = (size_t)a.n * a.oh * a.ow * a.ocp;
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total;
        i += (size_t)gridDim.x * blockDim.x) {
@@ -792,6 +814,7 @@ __global__ void move_kernel(const uint8_t *__restrict__ in, uint8_t *__restrict_
 // INT8 leaky ReLU (activation.cpp:126-153) and plain ReLU (internal.cpp:13-18).
 __global__ void leaky_relu_i8_kernel(const int8_t *__restrict__ in, int8_t *__restrict__ out,
                                      size_t nvec, int mp, int rp, int mn, int rn, int plain_relu) {
+  pdl_prologue();
   // positive side without a multiplier is the identity: (x * 1 + 0) >> 0
   const int mpe = mp != 0 ? mp : 1, rpe = mp != 0 ? rp : 0;
   const int rndp = rpe > 0 ? (1 << (rpe - 1)) : 0, rndn = rn > 0 ? (1 << (rn - 1)) : 0;
@@ -820,6 +843,7 @@ __global__ void leaky_relu_i8_kernel(const int8_t *__restrict__ in, int8_t *__re
 // INT8 256-entry table (activation.cpp:49-53): out = table[(uint8)x]; table staged in smem.
 __global__ void lut_i8_kernel(const int8_t *__restrict__ in, int8_t *__restrict__ out, size_t nvec,
                               const int8_t *__restrict__ table) {
+  pdl_prologue();
   __shared__ int8_t s_t[256];
   for (int i = threadIdx.x; i < 256; i += blockDim.x) s_t[i] = table[i];
   __syncthreads();
@@ -854,6 +878,7 @@ __device__ __forceinline__ uint32_t lut_slope_pair(uint32_t w, float scale, cons
 __global__ void lut_bf16_slope_kernel(const uint16_t *__restrict__ in, uint16_t *__restrict__ out,
                                       size_t n, const float *__restrict__ base,
                                       const float *__restrict__ slope, float scale) {
+  pdl_prologue();
   __shared__ float2 s_t[256]; // (base, slope) of one segment side by side: one 8-byte lookup
   for (int i = threadIdx.x; i < 256; i += blockDim.x) s_t[i] = make_float2(base[i], slope[i]);
   __syncthreads();
@@ -874,6 +899,7 @@ __global__ void act_chain_i8_kernel(const uint4 *__restrict__ in, uint4 *__restr
                                     uint4 *__restrict__ out, size_t nvec, float scale_in, float lut_scale,
                                     const float *__restrict__ base, const float *__restrict__ slope,
                                     float scale_out) {
+  pdl_prologue();
   __shared__ float2 s_t[256];
   for (int i = threadIdx.x; i < 256; i += blockDim.x) s_t[i] = make_float2(base[i], slope[i]);
   __syncthreads();
@@ -902,6 +928,7 @@ __global__ void act_chain_i8_kernel(const uint4 *__restrict__ in, uint4 *__restr
 __global__ void lut_bf16_mantissa_kernel(const uint16_t *__restrict__ in, uint16_t *__restrict__ out,
                                          size_t n, const float *__restrict__ exp_table,
                                          const float *__restrict__ mant_table) {
+  pdl_prologue();
   __shared__ float s_e[256], s_m[256];
   for (int i = threadIdx.x; i < 256; i += blockDim.x) {
     s_e[i] = exp_table[i];

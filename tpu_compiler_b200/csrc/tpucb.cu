@@ -359,6 +359,9 @@ int tpucb_interp_set_option(tpucb_interp *it, const char *key, int value) {
   if (k == "cuda_graph") {
     it->impl.use_graph = value != 0;
     it->impl.invalidate_graph();
+  } else if (k == "pdl") {
+    it->impl.use_pdl = value < 0 ? -1 : (value != 0);
+    it->impl.invalidate_graph();
   } else if (k == "fuse_activations") {
     it->impl.fuse_activations = value != 0; // takes effect at the next load_module
   } else if (k == "fuse_residual_add") {

@@ -105,6 +105,13 @@ int tpucb_op_info(tpucb_op *op, char *out, size_t cap, size_t *needed);
  * becomes the tensor's value for the next launch. The host buffer must stay untouched until
  * the next tpucb_interp_sync / invoke / get_tensor. */
 int tpucb_interp_set_tensor_async(tpucb_interp *it, const char *name, const float *pinned, size_t numel);
+/* The same for input values the caller has ALREADY quantised (no reference counterpart): int8, NCHW order, pinned.
+ * One byte per value crosses the host link instead of the four of the fp32 container, which is what bounds the
+ * end-to-end rate once several GPUs share a host. `name` is an INT8 tensor that is a module input or the result of
+ * the tpu.quant (NONE -> INT8) op directly behind an fp32 module input; that quant op is then skipped by the launches
+ * that follow, until the fp32 input is set again with tpucb_interp_set_tensor(_async). The values must be what the op
+ * would have produced: sat8(round half away from zero(x * scale)) (QuantOpKernel, core/quant.cpp:22-30). */
+int tpucb_interp_set_tensor_async_i8(tpucb_interp *it, const char *name, const int8_t *pinned, size_t numel);
 /* Blocks until every copy started by tpucb_interp_set_tensor_async has left its host buffer (the buffers may be
  * refilled afterwards); does not wait for launches. */
 int tpucb_interp_wait_uploads(tpucb_interp *it);
@@ -137,6 +144,12 @@ int tpucb_interp_get_op_info(tpucb_interp *it, char *out, size_t cap, size_t *ne
  *          "fuse_activations" (0/1, default 1; read by the next load_module): run each
  *          quant(INT8->BF16) -> slope-table activation -> quant(BF16->INT8) chain as one launch
  *          that still writes all three tensors.
+ *          "selftest_lost_arrival" (0 = off (default), else rounds in [1, 1024]; read by the next load_module): a
+ *          self-test of the error path. Every wait inside the tensor-core kernels is bounded (1024 rounds of 1024
+ *          polls); when one runs out the kernel records a code in the interpreter's device error word, drains its
+ *          copies, frees its tensor memory and returns, and the next tpucb_interp_sync / invoke reports it as an
+ *          error status while the interpreter stays usable. With this option the INT8 convolutions of the next
+ *          module never hand their accumulator back and wait only `rounds` rounds, so that exactly this happens.
  *          "fuse_residual_add" (0/1, default 0; read by the next load_module; needs fuse_activations): an INT8
  *          two-input eltwise add whose later-produced operand is a tensor-core convolution that feeds nothing else
  *          (the last convolution of a residual block) runs in that convolution's epilogue, which reads the other
@@ -169,6 +182,9 @@ int tpucb_measure_i8_mma_peak(int device, int n_cols, double *tops);
 
 /* Pinned host buffers for the e2e path. */
 int tpucb_host_alloc(void **ptr, size_t bytes);
+/* write-combined pinned memory: faster for the device to read, slow for the host to read back; for upload buffers
+ * that the host only writes */
+int tpucb_host_alloc_write_combined(void **ptr, size_t bytes);
 int tpucb_host_free(void *ptr);
 
 /* ---- calibration statistics (python/cvi_toolkit/calibration/kld_calibrator.py) --------- */

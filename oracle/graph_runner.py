@@ -73,8 +73,11 @@ def run(text, weights, inputs, upto=None):
                                 do_relu=bool(_i(a, "do_relu")))
         elif t == "fully_connected":
             x = X(0)
-            out = O.fc(x.reshape(x.shape[0], -1), W(1), W(2), W(5), W(6), do_relu=bool(_i(a, "do_relu")),
-                       mode=op["dtype"])
+            if W(1).ndim >= 3:   # batched: one product per leading filter index (core/fullyconnected.cpp:59-88)
+                out = O.fc(x, W(1), W(2), W(5), W(6), do_relu=bool(_i(a, "do_relu")), mode=op["dtype"])
+            else:
+                out = O.fc(x.reshape(x.shape[0], -1), W(1), W(2), W(5), W(6), do_relu=bool(_i(a, "do_relu")),
+                           mode=op["dtype"])
         elif t in ("pool_max_2d", "pool_avg_2d"):
             is_i8 = op["dtype"] == "INT8"
             rs = float(W(3)[0]) if (t == "pool_avg_2d" and is_i8) else 0.0

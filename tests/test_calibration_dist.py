@@ -45,7 +45,7 @@ def _make_calibrator(acts, d):
                 st[t, 0], st[t, 1] = float(allv.min()), float(allv.max())
             return st, len(acts)
 
-        def _local_histograms(self, stats):
+        def _local_histograms(self, stats, release=True):
             import oracle
             h = torch.zeros((len(self.names), self.bin_num), dtype=torch.int64)
             for t, n in enumerate(self.names):
@@ -91,3 +91,59 @@ def test_two_rank_statistics_equal_single_process():
             assert stats[k] == tuple(float(x) for x in s_stats[k]), (rank, k)
         assert np.array_equal(hist, s_hist)
     assert s_stats["zeros"] == (np.float32(-1e-5), np.float32(1e-5), np.float32(1e-5))
+
+
+def _mismatch_worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    from tpu_compiler_b200.calibration import join_ranks
+    d = join_ranks("gloo", rank, world, timeout_s=30)
+    cal = _make_calibrator(_activations(100, 2), d)
+    if rank == 1:
+        cal.names = cal.names[:-1]          # this rank loaded a module with one tensor less
+    try:
+        cal.find_min_max_abs()
+        q.put((rank, "no error"))
+    except RuntimeError as e:
+        q.put((rank, str(e)))
+    d.barrier()
+    d.destroy_process_group()
+
+
+def test_rank_mismatch_is_an_error_on_every_rank():
+    """Host-side fault: two ranks that calibrate different tensor lists. Both must fail with the same plain message
+    before any statistics are combined; neither may hang."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29950 + os.getpid() % 40
+    procs = [ctx.Process(target=_mismatch_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = dict(q.get(timeout=120) for _ in procs)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert "ranks disagree" in results[0] and "ranks disagree" in results[1]
+    assert "2..3" in results[0]
+
+
+def _lonely_worker(port, q):
+    import time
+    from tpu_compiler_b200.calibration import join_ranks
+    t0 = time.time()
+    try:
+        join_ranks("gloo", 0, 2, timeout_s=3, init_method="tcp://127.0.0.1:%d" % port)
+        q.put(("joined", time.time() - t0))
+    except RuntimeError as e:
+        q.put((str(e), time.time() - t0))
+
+
+def test_a_rank_that_never_joins_times_out_with_an_error():
+    """Host-side fault: rank 1 of 2 never starts. Rank 0 gives up after the limit with an error; no hang."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    p = ctx.Process(target=_lonely_worker, args=(29990 + os.getpid() % 9, q))
+    p.start()
+    msg, seconds = q.get(timeout=90)
+    p.join(timeout=30)
+    assert p.exitcode == 0
+    assert "not all 2 ranks joined within 3 s" in msg and seconds < 60

@@ -169,6 +169,31 @@ def test_kept_activations_give_the_same_histograms():
     m.close()
 
 
+def test_several_bin_counts_from_one_pass():
+    """run_multi: the thresholds of three histogram sizes from one min / max pass and one activation cache equal
+    those of three separate calibrations, and the images are asked for only once."""
+    from tpu_compiler_b200 import module
+    from tpu_compiler_b200.calibration import ActivationCalibrator
+    model = small_fp32_model(4)
+    rng = np.random.default_rng(79)
+    data = [np.clip(rng.normal(0, 1, (4, 3, 24, 24)), -3, 3).astype(np.float32) for _ in range(3)]
+    m = module(0)
+    m.load_text(model.text, model.weights)
+    calls = []
+
+    def batches():
+        calls.append(0)
+        return iter(data)
+
+    multi, stats = ActivationCalibrator(m, batches, expected_batches=3).run_multi((512, 2048, 1024))
+    assert len(calls) == 1 and list(multi) == [512, 2048, 1024]
+    for bins in (512, 1024, 2048):
+        thr, st = ActivationCalibrator(m, lambda: iter(data), histogram_bin_num=bins).run()
+        assert {k: float(v) for k, v in thr.items()} == {k: float(v) for k, v in multi[bins].items()}, bins
+        assert {k: tuple(map(float, v)) for k, v in st.items()} == {k: tuple(map(float, v)) for k, v in stats.items()}
+    m.close()
+
+
 def _calib_rank(rank, world, port, q):
     import os
     import torch

@@ -306,3 +306,19 @@ def test_batchnorm_and_reduce_l2_fp32():
     b.op("reduce_l2", "l2_hw", ["f"], (3, 21), "FP32", axes="2,3", coeff=0.5)
     out = run_both(b.text(), b.weights, {"f": rng.normal(0, 2, shape).astype(np.float32)}, ["bn", "l2_c", "l2_hw"])
     assert_close(out, rtol=1e-6)
+
+
+@pytest.mark.parametrize("relu", [0, 1])
+def test_fc_batched_i8(relu):
+    """FullyConnected with a rank-3 filter: one product per batch index, each with its own bias row and its own
+    (rshift, multiplier) pair (core/fullyconnected.cpp:59-88)."""
+    rng = np.random.default_rng(61 + relu)
+    B, m, k, n = 3, 20, 37, 11
+    b = graphs.GraphBuilder(61, simulate=False)
+    b.op("input", "x", [], (B, m, k), "INT8")
+    b.weight("w", rng.integers(-127, 128, (B, n, k)))
+    b.weight("bias", rng.integers(-2 ** 12, 2 ** 12, (B, n)))
+    b.weight("rs", [5, 7, 6])
+    b.weight("mu", np.float32((rng.integers(2 ** 30, 2 ** 31 - 128, B) // 128) * 128))
+    b.op("fully_connected", "y", ["x", "w", "bias", None, None, "rs", "mu"], (B, m, n), "INT8", do_relu=relu)
+    assert_exact(run_both(b.text(), b.weights, {"x": i8(rng, (B, m, k))}, ["y"]))

@@ -165,3 +165,55 @@ def test_programmatic_dependent_launch_on_and_off(model_b1):
     for n in names:
         assert np.array_equal(got[(0, 0)][n], got[(1, 0)][n]) and np.array_equal(got[(0, 1)][n], got[(1, 1)][n]), n
         assert np.array_equal(got[(0, 0)][n][0], got[(0, 1)][n][1]), n
+
+
+def test_int8_input_upload_replaces_the_quant_op():
+    """tpucb_interp_set_tensor_async_i8: the caller quantises the image on the host and uploads one byte per value into
+    the result of the input quant op, which is then skipped; setting the fp32 input again brings the op back."""
+    import ctypes as C
+    from tpu_compiler_b200 import TpucbError, module
+    from tpu_compiler_b200._lib import check, lib
+    B = 2
+    rng = np.random.default_rng(17)
+    x = rng.uniform(-1, 1, (B, 3, 224, 224)).astype(np.float32)
+    x2 = rng.uniform(-1, 1, (B, 3, 224, 224)).astype(np.float32)
+    mb = graphs.resnet50_int8(batch=B, seed=1001)
+    names = ["data_quant", "conv1", "res2c", "res5c", "fc1000_dequant"]
+    m = module(0)
+    m.load_text(mb.text, mb.weights)
+    m.set_tensor("data", x)
+    m.invoke()
+    ref = {n: m.get_tensor(n) for n in names}
+    m.set_tensor("data", x2)
+    m.invoke()
+    ref2 = {n: m.get_tensor(n) for n in names}
+    full = m.kernel_count()
+    # QuantOpKernel at the graph input (core/quant.cpp:22-30): sat8(std::round(x * scale)), half away from zero
+    v = x * np.float32(128.0)
+    q = np.clip(np.where(v >= 0, np.floor(v + np.float32(0.5)), np.ceil(v - np.float32(0.5))), -128, 127).astype(np.int8)
+    L = lib()
+    buf = C.c_void_p()
+    check(L.tpucb_host_alloc_write_combined(C.byref(buf), q.size))
+    C.memmove(buf, q.ctypes.data, q.size)
+    m.set_tensor_async_i8("data_quant", buf, q.size)
+    m.launch()
+    m.sync()
+    assert m.kernel_count() == full - 1
+    for n in names:
+        assert np.array_equal(m.get_tensor(n), ref[n]), n
+    m.set_tensor_async_i8("data_quant", buf, q.size)   # again, through the second staging buffer and the replayed graph
+    m.launch()
+    m.sync()
+    assert np.array_equal(m.get_tensor("fc1000_dequant"), ref["fc1000_dequant"])
+    with pytest.raises(TpucbError):
+        m.set_tensor_async_i8("conv1", buf, q.size)     # not an input
+    with pytest.raises(TpucbError):
+        m.set_tensor_async_i8("data", buf, q.size)      # not INT8
+    m.set_tensor("data", x2)                            # the fp32 way again: the quant op is back
+    m.invoke()
+    assert m.kernel_count() == full
+    for n in names:
+        assert np.array_equal(m.get_tensor(n), ref2[n]), n
+    m.sync()
+    check(L.tpucb_host_free(buf))
+    m.close()

@@ -43,6 +43,7 @@ def _declare(lib):
         "tpucb_interp_load_module": [vp, cp],
         "tpucb_interp_set_tensor": [vp, cp, fp, sz],
         "tpucb_interp_set_tensor_async": [vp, cp, fp, sz],
+        "tpucb_interp_set_tensor_async_i8": [vp, cp, vp, sz],
         "tpucb_interp_wait_uploads": [vp],
         "tpucb_interp_invoke": [vp],
         "tpucb_interp_invoke_to": [vp, cp],
@@ -61,6 +62,7 @@ def _declare(lib):
         "tpucb_interp_tensor_device": [vp, cp, C.POINTER(vp), szp, ip, ip, ip],
         "tpucb_measure_i8_mma_peak": [C.c_int, C.c_int, C.POINTER(C.c_double)],
         "tpucb_host_alloc": [C.POINTER(vp), sz],
+        "tpucb_host_alloc_write_combined": [C.POINTER(vp), sz],
         "tpucb_host_free": [vp],
         "tpucb_calib_minmax": [vp, cp, vp],
         "tpucb_calib_hist": [vp, cp, C.c_float, C.c_int, vp],

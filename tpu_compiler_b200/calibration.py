@@ -26,6 +26,21 @@ import torch
 from ._lib import check, lib
 
 
+def join_ranks(backend, rank, world_size, timeout_s=60.0, init_method=None):
+    """``torch.distributed.init_process_group`` with a short rendezvous limit and a plain error: a rank that never
+    starts (a crashed worker, a wrong WORLD_SIZE) makes the others fail after ``timeout_s`` seconds with a message that
+    says so, instead of waiting for the default half hour. Returns ``torch.distributed``."""
+    import datetime as _dt
+    import torch.distributed as dist
+    try:
+        dist.init_process_group(backend, rank=rank, world_size=world_size, init_method=init_method,
+                                timeout=_dt.timedelta(seconds=timeout_s))
+    except Exception as e:  # the store's own message names sockets and keys, not the cause
+        raise RuntimeError("rank %d: not all %d ranks joined within %.0f s (%s: %s)"
+                           % (rank, world_size, timeout_s, type(e).__name__, str(e).splitlines()[0][:120])) from e
+    return dist
+
+
 class ActivationCalibrator:
     def __init__(self, model, batches, histogram_bin_num=2048, input_name=None, dist=None, keep_activations_gb=None,
                  expected_batches=None):
@@ -174,12 +189,15 @@ class ActivationCalibrator:
         except Exception:
             pass
 
-    def _local_histograms(self, activations_statistics):
-        """This rank's [T, bins] int64 histograms."""
+    def _local_histograms(self, activations_statistics, release=True):
+        """This rank's [T, bins] int64 histograms. ``release`` False keeps the activation cache for another histogram
+        pass with a different bin count (run_multi)."""
         T = len(self.names)
         hist = torch.zeros((T, self.bin_num), dtype=torch.int64, device=self.device)
         torch.cuda.synchronize(self.device)
-        kept, self._kept = self._kept, []   # the cache serves one histogram pass
+        kept = self._kept
+        if release:
+            self._kept = []   # this was the cache's last histogram pass
         absmax = (C.c_float * T)(*[float(activations_statistics[n][2]) for n in self.names])
         for keep, _ in kept:
             vals = (C.c_void_p * T)(*[keep.data_ptr() + o for o in self._kept_offsets])
@@ -200,8 +218,26 @@ class ActivationCalibrator:
         """False when every batch of pass 1 is in the cache (then pass 2 does not even ask for the images again)."""
         return sum(n for _, n in kept) < self._local_images
 
+    def _check_ranks_agree(self):
+        """Every rank must calibrate the same tensors in the same order, or the all-reduces below would combine
+        unrelated rows (or, with different counts, fail deep inside the collective): compare a fingerprint of the
+        tensor list first and fail on every rank with a message that names the mismatch."""
+        import zlib
+        dev = self.device if self.device.type == "cuda" else torch.device("cpu")
+        mine = torch.tensor([len(self.names), zlib.crc32("\n".join(self.names).encode()), self.bin_num], dtype=torch.int64,
+                            device=dev)
+        lo, hi = mine.clone(), mine.clone()
+        self.dist.all_reduce(lo, op=self.dist.ReduceOp.MIN)
+        self.dist.all_reduce(hi, op=self.dist.ReduceOp.MAX)
+        if not torch.equal(lo, hi):
+            raise RuntimeError("calibration ranks disagree: this rank has %d tensors (fingerprint %d, %d bins); across "
+                               "ranks the counts span %d..%d" % (len(self.names), int(mine[1]), self.bin_num,
+                                                                 int(lo[0]), int(hi[0])))
+
     # -- pass 1 ------------------------------------------------------------------
     def find_min_max_abs(self):
+        if self.dist is not None:
+            self._check_ranks_agree()
         stats, n_img = self._local_min_max()
         if self.dist is not None:
             packed = torch.stack([-stats[:, 0], stats[:, 1]], dim=1).contiguous()
@@ -222,8 +258,8 @@ class ActivationCalibrator:
         return out
 
     # -- pass 2 ------------------------------------------------------------------
-    def calc_histograms(self, activations_statistics):
-        hist = self._local_histograms(activations_statistics)
+    def calc_histograms(self, activations_statistics, release=True):
+        hist = self._local_histograms(activations_statistics, release=release)
         if self.dist is not None:
             self.dist.all_reduce(hist, op=self.dist.ReduceOp.SUM)
         return hist
@@ -238,6 +274,23 @@ class ActivationCalibrator:
         check(self._lib.tpucb_calib_kld(self.model._h, C.c_void_p(hist.data_ptr()), widths.ctypes.data_as(fp), T,
                                         self.bin_num, thr.ctypes.data_as(fp)))
         return {n: thr[t] for t, n in enumerate(self.names)}
+
+    def run_multi(self, bin_nums):
+        """Thresholds for several histogram sizes from ONE min / max pass and one set of cached activations, the way the
+        reference's calc_thresholds fills its thresholds_map for every bin count from the same pass
+        (kld_calibrator.py:298-336): per bin count one histogram launch per cached batch and one KLD search. Returns
+        ({bin count: {name: threshold}} in the order given, statistics). Bin counts are limited to 4096 by the
+        histogram kernels (shared-memory tables); the reference's larger candidates (8192 .. 32768) are not covered."""
+        stats = self.find_min_max_abs()
+        out = {}
+        bin_nums = list(bin_nums)
+        keep = self.bin_num
+        for i, bins in enumerate(bin_nums):
+            self.bin_num = int(bins)
+            hist = self.calc_histograms(stats, release=(i == len(bin_nums) - 1))
+            out[int(bins)] = self.find_threshold(hist, stats)
+        self.bin_num = keep
+        return out, stats
 
     def run(self, output_calibration_table=None):
         stats = self.find_min_max_abs()

@@ -65,6 +65,11 @@ struct ConvGemmParams {
   const int8_t *res;
   int add_ms, add_mr, add_r, add_relu;
   int *err;       // device error word (0 = ok)
+  // Self-test of the bounded waits (interpreter option "selftest_lost_arrival"): wait_rounds > 0 shortens every wait of
+  // this launch to that many rounds of 1024 polls, and with lose_arrival the epilogue warps never hand an accumulator
+  // buffer back, so that the MMA issuer's wait for it runs out and the launch ends through its error path (status
+  // kErrAccWait) with no copy in flight. 0 / 0 in every ordinary launch.
+  int wait_rounds, lose_arrival;
 };
 
 namespace ptx {
@@ -92,9 +97,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 // Bounded wait: returns false when the barrier did not flip within the limit.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
-                                                  volatile int *abort_flag) {
-  // 1024 rounds of 1024 polls: the abort flag (another role of this CTA gave up) is read once per round
-  for (int round = 0; round < 1024; ++round) {
+                                                  volatile int *abort_flag, int rounds = 1024) {
+  // `rounds` (1024 by default) rounds of 1024 polls: the abort flag (another role of this CTA gave up) is read once
+  // per round
+  for (int round = 0; round < rounds; ++round) {
 #pragma unroll 1
     for (int it = 1024; it > 0; --it)
       if (mbar_try_wait(bar, parity)) return true;
@@ -645,6 +651,7 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
   // pair: the per-tile code of every role carries no division.
   const int walk_m0 = (int)blockIdx.x / n_tiles, walk_n0 = (int)blockIdx.x % n_tiles;
   const int walk_dm = (int)gridDim.x / n_tiles, walk_dn = (int)gridDim.x % n_tiles;
+  const int wait_rounds = p.wait_rounds > 0 ? p.wait_rounds : 1024;
 
   // Programmatic dependent launch: the next kernel of the stream may start its own set-up as soon as every CTA
   // of this launch has got here; this kernel in turn sets up its barriers and tensor memory while the
@@ -731,7 +738,7 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
           const CUtensorMap *mapA = (TF32 && term == 0) ? &tmA2 : &tmA;
           const CUtensorMap *mapB = (TF32 && term == 1) ? &tmB2 : &tmB;
           if (it >= p.stages) {
-            if (!ptx::mbar_wait_bounded(bar_empty + 8 * ps, pph ^ 1u, abort_flag)) {
+            if (!ptx::mbar_wait_bounded(bar_empty + 8 * ps, pph ^ 1u, abort_flag, wait_rounds)) {
               if (!*abort_flag) atomicExch(p.err, kErrEmptyWait);
               *abort_flag = 1;
               ok = false;
@@ -813,7 +820,7 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
       uint32_t m_full = bar_full, m_empty = bar_empty, ring_lo = desc_ring_lo;
       const int ksteps = p.BK / 32;
       if (p.w_resident && (int)blockIdx.x < total_tiles) {
-        if (!ptx::mbar_wait_bounded(bar_w, 0u, abort_flag)) {
+        if (!ptx::mbar_wait_bounded(bar_w, 0u, abort_flag, wait_rounds)) {
           if (!*abort_flag) atomicExch(p.err, kErrFullWait);
           *abort_flag = 1;
           ok = false;
@@ -823,7 +830,7 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
         const int buf = t & 1;
         if (t >= 2) {
           // the epilogue must have drained this accumulator buffer (its previous use)
-          if (!ptx::mbar_wait_bounded(bar_acc_empty + 8 * buf, (uint32_t)(((t >> 1) - 1) & 1), abort_flag)) {
+          if (!ptx::mbar_wait_bounded(bar_acc_empty + 8 * buf, (uint32_t)(((t >> 1) - 1) & 1), abort_flag, wait_rounds)) {
             if (!*abort_flag) atomicExch(p.err, kErrAccWait);
             *abort_flag = 1;
             ok = false;
@@ -834,7 +841,7 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
         const uint32_t d_tmem = tmem_base + (uint32_t)buf * acc_stride;
         uint32_t wres_lo = desc_w_lo; // weight-resident mode: descriptor (low word) of K block `kit`
         for (int kit = 0; kit < kTerms * k_iters; ++kit, ++it) {
-          if (!ptx::mbar_try_wait(m_full, mph) && !ptx::mbar_wait_bounded(m_full, mph, abort_flag)) {
+          if (!ptx::mbar_try_wait(m_full, mph) && !ptx::mbar_wait_bounded(m_full, mph, abort_flag, wait_rounds)) {
             if (!*abort_flag) atomicExch(p.err, kErrFullWait);
             *abort_flag = 1;
             ok = false;
@@ -907,7 +914,7 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
         }
         staged_n0 = n0;
       }
-      ok = ptx::mbar_wait_bounded(bar_acc_full + 8 * buf, (uint32_t)((t >> 1) & 1), abort_flag);
+      ok = ptx::mbar_wait_bounded(bar_acc_full + 8 * buf, (uint32_t)((t >> 1) & 1), abort_flag, wait_rounds);
       if (!ok && !*abort_flag) {
         atomicExch(p.err, kErrAccWait);
         *abort_flag = 1;
@@ -943,7 +950,7 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
       // hand the accumulator buffer back to the MMA issuer
       ptx::tcgen05_fence_before();
       __syncwarp();
-      if (lane == 0)
+      if (lane == 0 && !p.lose_arrival)
         asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_acc_empty + 8 * buf) : "memory");
     }
   }

@@ -381,6 +381,36 @@ template <int DT> __global__ void matmul_kernel(const void *__restrict__ a, cons
   }
 }
 
+// ------------------------------------------------------------ batched INT8 inner product
+// FullyConnectedOpKernel with a filter of rank 3 (core/fullyconnected.cpp:59-88; parseFullyConnectedParam,
+// lib/Dialect/TPU/IR/TPUOperationSupport.cpp:569-605): `batch` independent products Y[b] = X[b] (m x k) * W[b]^T
+// (n x k) + bias[b], ReLU on the sum, then the QDM requantisation with ONE (multiplier, rshift) pair PER BATCH
+// index. The rank-3 activations [batch, m, k] and [batch, m, n] sit in the device layout with m on the channel axis
+// (pitch mp): consecutive threads take consecutive rows m, so both the reads and the writes are coalesced. The
+// weights are int8 [batch][n][k]. An integer loop on the FMA / integer pipe: graphs with this op (attention-style
+// products against constant matrices) are not on a benchmark path.
+__global__ void fc_batched_i8_kernel(const int8_t *__restrict__ x, const int8_t *__restrict__ w, const int32_t *__restrict__ bias,
+                                     const int32_t *__restrict__ mult, const int32_t *__restrict__ rshift,
+                                     int8_t *__restrict__ y, int batch, int m, int k, int n, int mp, int do_relu) {
+  pdl_prologue();
+  const size_t total = (size_t)batch * n * mp;
+  for (size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    const int i = (int)(idx % mp);
+    const size_t bj = idx / mp;
+    const int j = (int)(bj % n), b = (int)(bj / n);
+    int v = 0;
+    if (i < m) {
+      int acc = bias ? bias[(size_t)b * n + j] : 0;
+      const int8_t *xr = x + (size_t)b * k * mp + i;
+      const int8_t *wr = w + ((size_t)b * n + j) * k;
+      for (int t = 0; t < k; ++t) acc += (int)xr[(size_t)t * mp] * (int)wr[t];
+      if (do_relu) acc = max(acc, 0);
+      v = qdm_requant(acc, mult[b], rshift[b]);
+    }
+    y[idx] = (int8_t)v;
+  }
+}
+
 // ----------------------------------------------------------------------------- BF16 softmax
 // SoftmaxOpKernel::invoke_bf16 (core/softmax.cpp:88-151) over the channel axis, one pixel per CTA:
 // max, BF16(x - max), exp through the 256-entry slope table (lut_func.cpp:169-186, range 15),

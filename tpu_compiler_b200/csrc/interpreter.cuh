@@ -59,7 +59,12 @@ class OpKernel {
 public:
   virtual ~OpKernel() {}
   virtual void invoke(cudaStream_t s) = 0;
+  // what the op loops call: an op whose result is currently supplied from outside (see set_tensor_async_i8) is skipped
+  void run(cudaStream_t s) {
+    if (!disabled) invoke(s);
+  }
   virtual int kernel_launches() const { return 1; }
+  bool disabled = false;
   std::string name, op_type;
   std::vector<int64_t> shape;
   int datatype = DT_F32;
@@ -230,6 +235,10 @@ public:
   // turns it on when the module moves less than 48 MB per kernel on average.
   int use_pdl = -1;
   bool pdl_auto = false;
+  // Self-test (option "selftest_lost_arrival", read by the next load_module): > 0 makes every INT8 tensor-core
+  // convolution built from then on lose its accumulator hand-back and wait only that many rounds of 1024 polls
+  // (ConvGemmParams::wait_rounds / lose_arrival), so that a launch ends with a bounded-wait error status.
+  int selftest_lost_arrival = 0;
   bool fuse_activations = true; // set before load_module
   bool fuse_residual_add = false; // set before load_module: eltwise adds run in the producing convolution's epilogue
   bool fp32_tensor_cores = true; // set before load_module: fp32 convolutions as three TF32 products
@@ -252,6 +261,8 @@ public:
   bool staging_used[2] = {false, false};
   int async_next = 0;
   void set_tensor_async(const std::string &name, const float *pinned, size_t numel);
+  void set_tensor_async_i8(const std::string &name, const int8_t *pinned, size_t numel);
+  void reenable_quant_of(const DevTensor *input);
 };
 
 // =========================================================================== op kernels
@@ -710,6 +721,10 @@ public:
         encode_im2col_map(&pl.tmA, (const int8_t *)in->dev, g, in->cp, p.BK);
         encode_weight_map(&pl.tmB, d_w, ocg_pad, g.kh * g.kw, in->cp, p.BK, p.dual ? 192 : p.BN);
       }
+      if (I.selftest_lost_arrival > 0) {
+        pl.p.wait_rounds = I.selftest_lost_arrival;
+        pl.p.lose_arrival = 1;
+      }
       plans_.push_back(pl);
     }
   }
@@ -806,6 +821,10 @@ class FullyConnectedOp : public OpKernel {
 public:
   FullyConnectedOp(Interpreter &I, const ParsedOp &op, TensorPtr in, TensorPtr out) : I_(I), in_(in), out_(out) {
     do_relu_ = op.geti("do_relu", 0);
+    if (I.weight(op.in.at(1)).shape.size() >= 3) {
+      setup_batched(I, op);
+      return;
+    }
     m_ = in->n;
     const int hw = in->h * in->w;
     k_ = in->c * hw;
@@ -906,10 +925,53 @@ public:
     plan_ = pl;
     alg_bytes = (double)m_ * k_ + (double)n_ * k_ + (double)m_ * n_ + 4.0 * n_ + 8;
   }
+  // A filter of rank 3, [batch, n, k]: one product per batch index with its own bias row and its own (multiplier,
+  // rshift) pair (core/fullyconnected.cpp:59-88). INT8, rank-3 activations [batch, m, k] -> [batch, m, n], no
+  // input / output transposes.
+  void setup_batched(Interpreter &I, const ParsedOp &op) {
+    const HostWeight &filt = I.weight(op.in[1]);
+    TPUCB_CHECK(filt.shape.size() == 3 && in_->shape.size() == 3 && out_->shape.size() == 3,
+                "fc %s: a batched inner product needs rank-3 input, filter and result", op.name.c_str());
+    TPUCB_CHECK(!op.geti("input_transpose", 0) && !op.geti("output_transpose", 0),
+                "fc %s: batched inner products with transposes are not implemented", op.name.c_str());
+    TPUCB_CHECK(in_->dtype == DT_I8 && out_->dtype == DT_I8, "fc %s: batched inner products are implemented for INT8 only",
+                op.name.c_str());
+    batch_ = (int)filt.shape[0];
+    n_ = (int)filt.shape[1];
+    k_ = (int)filt.shape[2];
+    m_ = (int)in_->shape[1];
+    TPUCB_CHECK(in_->shape[0] == batch_ && in_->shape[2] == k_ && out_->shape[0] == batch_ && out_->shape[1] == m_ &&
+                    out_->shape[2] == n_,
+                "fc %s: shapes do not agree with filter [%d, %d, %d]", op.name.c_str(), batch_, n_, k_);
+    TPUCB_CHECK(op.in.size() >= 7 && I.has_weight(op.in[5]) && I.has_weight(op.in[6]),
+                "fc %s: INT8 needs rshift and multiplier operands", op.name.c_str());
+    const auto &rs = I.weight(op.in[5]).data, &mu = I.weight(op.in[6]).data;
+    TPUCB_CHECK((int)rs.size() >= batch_ && (int)mu.size() >= batch_, "fc %s: one (rshift, multiplier) pair per batch index is needed",
+                op.name.c_str());
+    check_q31_multipliers(mu, op.name);
+    TPUCB_CHECK((double)k_ * 127.0 * 128.0 < 2147483648.0, "fc %s: K = %d overflows the int32 sum", op.name.c_str(), k_);
+    std::vector<int8_t> w(filt.data.size());
+    for (size_t i = 0; i < w.size(); ++i) w[i] = (int8_t)(int)filt.data[i];
+    bw_ = I.upload(w);
+    if (op.in.size() > 2 && I.has_weight(op.in[2])) {
+      const auto &b = I.weight(op.in[2]).data;
+      TPUCB_CHECK(b.size() == (size_t)batch_ * n_, "fc %s: bias needs batch * n values", op.name.c_str());
+      bb_ = I.upload(to_i32(b, (int)b.size()));
+    }
+    bm_ = I.upload(to_i32(mu, batch_, true));
+    br_ = I.upload(to_i32(rs, batch_, true));
+    alg_ops = 2.0 * batch_ * m_ * k_ * n_;
+    alg_bytes = (double)batch_ * ((double)m_ * k_ + (double)n_ * k_ + (double)m_ * n_ + 4.0 * n_ + 8);
+  }
   void invoke(cudaStream_t s) override {
-    if (f32_) launch_fc_f32((const float *)in_->dev, f32_w_, f32_b_, (float *)out_->dev, m_, kdev_, n_, out_->cp, do_relu_, s);
+    if (batch_ > 0) {
+      const size_t total = (size_t)batch_ * n_ * out_->cp;
+      launch_k(fc_batched_i8_kernel, grid_for(total, 128, I_.sm_count), 128, 0, s, (const int8_t *)in_->dev, bw_, bb_, bm_, br_,
+               (int8_t *)out_->dev, batch_, m_, k_, n_, out_->cp, do_relu_);
+    } else if (f32_) launch_fc_f32((const float *)in_->dev, f32_w_, f32_b_, (float *)out_->dev, m_, kdev_, n_, out_->cp, do_relu_, s);
     else launch_conv_plan(plan_, s, I_.sm_count);
   }
+  bool is_batched() const { return batch_ > 0; }
   ConvPlan plan_;
 
 private:
@@ -918,6 +980,9 @@ private:
   int m_ = 1, k_ = 1, n_ = 1, kdev_ = 1, do_relu_ = 0;
   bool f32_ = false;
   const float *f32_w_ = nullptr, *f32_b_ = nullptr;
+  int batch_ = 0; // > 0: batched inner product (setup_batched)
+  const int8_t *bw_ = nullptr;
+  const int32_t *bb_ = nullptr, *bm_ = nullptr, *br_ = nullptr;
 };
 
 // -------------------------------------------------------------------------- Pooling
@@ -2053,6 +2118,7 @@ inline SlotView slot_view(const DevTensor &t, int slot, int max_batch, const cha
 inline void Interpreter::set_tensor(const std::string &name, const float *data, size_t numel, int slot) {
   bind();
   TensorPtr t = tensor(name);
+  reenable_quant_of(t.get());
   const SlotView v = slot_view(*t, slot, max_batch, "set_tensor");
   TPUCB_CHECK(numel == v.numel, "set_tensor %s: got %zu values, tensor has %zu", name.c_str(), numel, v.numel);
   float *stg = ensure_staging(numel * sizeof(float));
@@ -2079,6 +2145,7 @@ inline void Interpreter::set_tensor_async(const std::string &name, const float *
   TensorPtr t = tensor(name);
   TPUCB_CHECK(numel == t->numel(), "set_tensor_async %s: got %zu values, tensor has %zu", name.c_str(), numel,
               t->numel());
+  reenable_quant_of(t.get());
   const int k = async_next;
   async_next ^= 1;
   const size_t bytes = numel * sizeof(float);
@@ -2110,6 +2177,70 @@ inline void Interpreter::set_tensor_async(const std::string &name, const float *
   staging_used[k] = true;
 }
 
+// A quant op that was switched off by set_tensor_async_i8 runs again once its fp32 input is set the ordinary way.
+inline void Interpreter::reenable_quant_of(const DevTensor *input) {
+  for (auto &k : kernels) {
+    auto *q = dynamic_cast<QuantOp *>(k.get());
+    if (q && q->disabled && q->in().get() == input) {
+      q->disabled = false;
+      invalidate_graph();
+    }
+  }
+}
+
+// Pipelined upload of ALREADY QUANTISED input values (int8, NCHW order, PINNED host memory): one byte per value crosses
+// the host link instead of the four of the fp32 container. `name` is an INT8 tensor that is either a module input or
+// the result of the tpu.quant (NONE -> INT8) op directly behind an fp32 input; in the second case that quant op is
+// switched off (its result now comes from the caller) until the fp32 input is set again with set_tensor /
+// set_tensor_async. The caller quantises as the op would: sat8(round-half-away-from-zero(x * scale)) (core/quant.cpp:22-30).
+inline void Interpreter::set_tensor_async_i8(const std::string &name, const int8_t *pinned, size_t numel) {
+  bind();
+  TensorPtr t = tensor(name);
+  TPUCB_CHECK(t->dtype == DT_I8, "set_tensor_async_i8 %s: the tensor is not INT8", name.c_str());
+  TPUCB_CHECK(numel == t->numel(), "set_tensor_async_i8 %s: got %zu values, tensor has %zu", name.c_str(), numel, t->numel());
+  OpKernel *prod = nullptr;
+  for (auto &k : kernels)
+    if (k->result == t) prod = k.get();
+  TPUCB_CHECK(prod != nullptr, "set_tensor_async_i8 %s: no op produces this tensor", name.c_str());
+  if (prod->op_type != "input") {
+    auto *q = dynamic_cast<QuantOp *>(prod);
+    bool ok = q && (q->kind() == 0 || q->kind() == 1);
+    if (ok) {
+      ok = false;
+      for (auto &k : kernels)
+        if (k->result == q->in() && k->op_type == "input") ok = true;
+    }
+    TPUCB_CHECK(ok, "set_tensor_async_i8 %s: only a module input or the quant op directly behind one can be supplied", name.c_str());
+    if (!q->disabled) {
+      q->disabled = true;
+      invalidate_graph();
+    }
+  }
+  const int k = async_next;
+  async_next ^= 1;
+  if (numel > async_staging_bytes[k]) {
+    TPUCB_CUDA(cudaStreamSynchronize(stream));
+    TPUCB_CUDA(cudaStreamSynchronize(copy_stream));
+    if (async_staging[k]) cudaFree(async_staging[k]);
+    TPUCB_CUDA(cudaMalloc(&async_staging[k], numel));
+    async_staging_bytes[k] = numel;
+    staging_used[k] = false;
+  }
+  if (staging_used[k]) TPUCB_CUDA(cudaStreamWaitEvent(copy_stream, staging_free[k], 0));
+  TPUCB_CUDA(cudaMemcpyAsync(async_staging[k], pinned, numel, cudaMemcpyHostToDevice, copy_stream));
+  TPUCB_CUDA(cudaEventRecord(upload_done[k], copy_stream));
+  TPUCB_CUDA(cudaStreamWaitEvent(stream, upload_done[k], 0));
+  TensorGeom g{t->n, t->c, t->h, t->w, t->cp, t->wl, t->wphys};
+  const int8_t *stg = (const int8_t *)async_staging[k];
+  if (t->cp == 4 && !t->padded_rows())
+    launch_k(nchw_i8_to_nhwc4_kernel, grid_for(t->pixels(), 256, sm_count), 256, 0, stream, stg, (uint32_t *)t->dev, t->n, t->c,
+             (size_t)t->h * t->w);
+  else
+    launch_k(nchw_i8_to_dev_kernel, grid_for(t->pixels() * t->cp, 256, sm_count), 256, 0, stream, stg, (int8_t *)t->dev, g);
+  TPUCB_CUDA(cudaEventRecord(staging_free[k], stream));
+  staging_used[k] = true;
+}
+
 // getTensor (MlirModuleInterpreter.cpp:419-427): deep copy out as fp32 NCHW.
 inline void Interpreter::get_tensor(const std::string &name, float *out, size_t numel, int slot) {
   bind();
@@ -2134,7 +2265,7 @@ inline void Interpreter::launch_all() {
       cudaGraph_t graph = nullptr;
       TPUCB_CUDA(cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal));
       try {
-        for (auto &k : kernels) k->invoke(stream);
+        for (auto &k : kernels) k->run(stream);
       } catch (...) {
         cudaStreamEndCapture(stream, &graph);
         if (graph) cudaGraphDestroy(graph);
@@ -2147,7 +2278,7 @@ inline void Interpreter::launch_all() {
     }
     TPUCB_CUDA(cudaGraphLaunch(graph_exec, stream));
   } else {
-    for (auto &k : kernels) k->invoke(stream);
+    for (auto &k : kernels) k->run(stream);
     TPUCB_CUDA(cudaGetLastError());
   }
 }
@@ -2157,7 +2288,7 @@ inline void Interpreter::launch_to(const std::string &name) {
   if (name.empty()) return launch_all();
   tensor(name);
   for (auto &k : kernels) {
-    k->invoke(stream);
+    k->run(stream);
     if (k->name == name) break;
   }
   TPUCB_CUDA(cudaGetLastError());
@@ -2172,7 +2303,7 @@ inline void Interpreter::fast_invoke_all_batch(const std::string &name, int batc
   if (!name.empty()) tensor(name);
   for (auto &k : kernels) {
     if (k->dirty) {
-      k->invoke(stream);
+      k->run(stream);
       k->dirty = false;
     }
     if (!name.empty() && k->name == name) break;
@@ -2188,7 +2319,8 @@ inline void Interpreter::sync_and_check() {
   if (err != 0) {
     TPUCB_CUDA(cudaMemset(d_err, 0, sizeof(int)));
     throw Error(strfmt("a convolution kernel gave up on a bounded wait (code %d: 1 = tile load never arrived, "
-                       "2 = stage never freed, 3 = accumulator never completed)", err));
+                       "2 = stage never freed, 3 = accumulator never completed or never handed back); the launch's "
+                       "results are incomplete, the interpreter stays usable", err));
   }
 }
 

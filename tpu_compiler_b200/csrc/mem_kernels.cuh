@@ -65,6 +65,35 @@ __global__ void nchw_f32_to_nhwc4_kernel(const float *__restrict__ src, float4 *
   }
 }
 
+// upload of already quantised int8 values (NCHW order) into an INT8 tensor: the generic form (any channel pitch,
+// padded rows) and the image form (at most 4 channels, one 32-bit word per pixel).
+__global__ void nchw_i8_to_dev_kernel(const int8_t *__restrict__ src, int8_t *__restrict__ dst, TensorGeom g) {
+  pdl_prologue();
+  const size_t total = (size_t)g.n * g.h * g.wphys * g.cp;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int c = (int)(i % g.cp);
+    const size_t pix = i / g.cp;
+    const int x = (int)(pix % g.wphys) - g.wl;
+    const size_t t = pix / g.wphys;
+    const int y = (int)(t % g.h);
+    const int b = (int)(t / g.h);
+    dst[i] = (c < g.c && x >= 0 && x < g.w) ? src[(((size_t)b * g.c + c) * g.h + y) * g.w + x] : (int8_t)0;
+  }
+}
+__global__ void nchw_i8_to_nhwc4_kernel(const int8_t *__restrict__ src, uint32_t *__restrict__ dst, int n, int c, size_t hw) {
+  pdl_prologue();
+  const size_t total = (size_t)n * hw;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t b = i / hw, p = i - b * hw;
+    const uint8_t *s = reinterpret_cast<const uint8_t *>(src) + b * c * hw + p;
+    uint32_t v = s[0];
+    if (c > 1) v |= (uint32_t)s[hw] << 8;
+    if (c > 2) v |= (uint32_t)s[2 * hw] << 16;
+    if (c > 3) v |= (uint32_t)s[3 * hw] << 24;
+    dst[i] = v;
+  }
+}
+
 // download: device NHWC -> fp32 NCHW. One thread per NCHW element; reads of a warp
 // stride by cp but stay inside L2-resident rows for the sizes that are fetched.
 template <int DT>

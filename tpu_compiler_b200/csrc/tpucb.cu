@@ -210,7 +210,7 @@ int tpucb_op_invoke(tpucb_op *op) {
   Interpreter &I = op->ctx->impl;
   I.bind();
   if (k) {
-    k->invoke(I.stream);
+    k->run(I.stream);
     k->dirty = false;
     TPUCB_CUDA(cudaGetLastError());
   }
@@ -252,6 +252,13 @@ int tpucb_interp_set_tensor_async(tpucb_interp *it, const char *name, const floa
   TPUCB_API_BEGIN
   TPUCB_CHECK(it && name && pinned, "tpucb_interp_set_tensor_async: bad argument");
   it->impl.set_tensor_async(name, pinned, numel);
+  TPUCB_API_END
+}
+
+int tpucb_interp_set_tensor_async_i8(tpucb_interp *it, const char *name, const int8_t *pinned, size_t numel) {
+  TPUCB_API_BEGIN
+  TPUCB_CHECK(it && name && pinned, "tpucb_interp_set_tensor_async_i8: bad argument");
+  it->impl.set_tensor_async_i8(name, pinned, numel);
   TPUCB_API_END
 }
 
@@ -346,7 +353,7 @@ int tpucb_interp_get_op_info(tpucb_interp *it, char *out, size_t cap, size_t *ne
     s += "\t" + std::to_string(k->alg_ops) + "\t" + std::to_string(k->alg_bytes);
     auto *cv = dynamic_cast<Conv2DOp *>(k.get());
     auto *fc = dynamic_cast<FullyConnectedOp *>(k.get());
-    s += std::string("\t") + ((cv && cv->is_tensor_core()) || fc ? "tensor" : "hbm") + "\n";
+    s += std::string("\t") + ((cv && cv->is_tensor_core()) || (fc && !fc->is_batched()) ? "tensor" : "hbm") + "\n";
   }
   copy_out(s, out, cap, needed);
   TPUCB_API_END
@@ -362,6 +369,9 @@ int tpucb_interp_set_option(tpucb_interp *it, const char *key, int value) {
   } else if (k == "pdl") {
     it->impl.use_pdl = value < 0 ? -1 : (value != 0);
     it->impl.invalidate_graph();
+  } else if (k == "selftest_lost_arrival") {
+    TPUCB_CHECK(value >= 0 && value <= 1024, "selftest_lost_arrival: rounds must be in [0, 1024]");
+    it->impl.selftest_lost_arrival = value; // takes effect at the next load_module
   } else if (k == "fuse_activations") {
     it->impl.fuse_activations = value != 0; // takes effect at the next load_module
   } else if (k == "fuse_residual_add") {
@@ -386,7 +396,7 @@ int tpucb_interp_profile(tpucb_interp *it, float *ms, int cap, int *count) {
   for (auto &e : ev) TPUCB_CUDA(cudaEventCreate(&e));
   TPUCB_CUDA(cudaEventRecord(ev[0], I.stream));
   for (int i = 0; i < n; ++i) {
-    I.kernels[i]->invoke(I.stream);
+    I.kernels[i]->run(I.stream);
     TPUCB_CUDA(cudaEventRecord(ev[i + 1], I.stream));
   }
   I.sync_and_check();
@@ -418,7 +428,7 @@ int tpucb_interp_kernel_count(tpucb_interp *it, int *count) {
   TPUCB_API_BEGIN
   TPUCB_CHECK(it && count, "tpucb_interp_kernel_count: bad argument");
   int c = 0;
-  for (auto &k : it->impl.kernels) c += k->kernel_launches();
+  for (auto &k : it->impl.kernels) c += k->disabled ? 0 : k->kernel_launches();
   *count = c;
   TPUCB_API_END
 }
@@ -499,6 +509,13 @@ int tpucb_host_alloc(void **ptr, size_t bytes) {
   TPUCB_API_BEGIN
   TPUCB_CHECK(ptr, "tpucb_host_alloc: bad argument");
   TPUCB_CUDA(cudaHostAlloc(ptr, bytes, cudaHostAllocDefault));
+  TPUCB_API_END
+}
+
+int tpucb_host_alloc_write_combined(void **ptr, size_t bytes) {
+  TPUCB_API_BEGIN
+  TPUCB_CHECK(ptr, "tpucb_host_alloc_write_combined: bad argument");
+  TPUCB_CUDA(cudaHostAlloc(ptr, bytes, cudaHostAllocWriteCombined));
   TPUCB_API_END
 }
 

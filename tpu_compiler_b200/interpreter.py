@@ -150,6 +150,11 @@ class module:
         """Pipelined set_tensor from PINNED host memory: the copy overlaps the launch in flight."""
         check(self._lib.tpucb_interp_set_tensor_async(self._h, name.encode(), C.cast(host_ptr, _f), numel))
 
+    def set_tensor_async_i8(self, name, host_ptr, numel):
+        """Pipelined upload of already quantised int8 values (NCHW, pinned) into an INT8 input tensor or into the
+        result of the quant op right behind an fp32 input (that op is then skipped): a quarter of the bytes."""
+        check(self._lib.tpucb_interp_set_tensor_async_i8(self._h, name.encode(), C.cast(host_ptr, C.c_void_p), numel))
+
     def wait_uploads(self):
         """Blocks until every set_tensor_async copy has left its pinned host buffer."""
         check(self._lib.tpucb_interp_wait_uploads(self._h))

@@ -199,7 +199,7 @@ def calibration_record(rank, world, local_rank, dist, images_per_gpu, bs, check_
     t3 = time.perf_counter()
     parts = dict(cal.pass1_host_s)
     times = [t3 - t0, t1 - t0, t2 - t1, t3 - t2, parts["pinned_copy"], parts["wait_uploads"], parts["enqueue"],
-             parts["final_sync"]]
+             parts["final_sync"], parts["combine"]]
     if dist is not None:
         dist.barrier()
         tt = torch.tensor(times, dtype=torch.float64, device="cuda")
@@ -239,7 +239,7 @@ def calibration_record(rank, world, local_rank, dist, images_per_gpu, bs, check_
             "batch": bs, "tensors": len(thr), "seconds": times[0],
             "phases_s": {"min_max_pass": times[1], "histogram_pass": times[2], "kld_search": times[3]},
             "min_max_pass_host_s": {"pinned_copy": times[4], "wait_uploads": times[5], "enqueue": times[6],
-                                    "final_sync": times[7]},
+                                    "final_sync": times[7], "combine_and_read_back": times[8]},
             "forward_ms_per_batch": fwd_ms, "clocks": clocks,
             "collectives": "all-reduce(MAX) of packed min/max, all-reduce(SUM) of int64 histograms" if world > 1 else "none",
             "equal_to_single_rank": equal,

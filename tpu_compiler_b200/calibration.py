@@ -66,7 +66,9 @@ class ActivationCalibrator:
         self._reserved = []      # cache buffers allocated ahead of pass 1
         # host seconds of this rank's last pass 1 by part: copying batches into pinned memory, waiting for earlier
         # uploads to leave their buffer, enqueueing (module launch + statistics launch), the final synchronisation
-        self.pass1_host_s = {"pinned_copy": 0.0, "wait_uploads": 0.0, "enqueue": 0.0, "final_sync": 0.0}
+        self.pass1_host_s = {"pinned_copy": 0.0, "wait_uploads": 0.0, "enqueue": 0.0, "final_sync": 0.0, "combine": 0.0}
+        if self.dist is not None:
+            self._check_ranks_agree()   # once, at set-up: its two small all-reduces are not part of a pass
         if self._lib is not None:
             # the two pinned upload buffers are part of setting up (tens of milliseconds), not of a pass
             self._alloc_pinned(int(np.prod(model.get_tensor_shape(self.input_name))))
@@ -236,9 +238,8 @@ class ActivationCalibrator:
 
     # -- pass 1 ------------------------------------------------------------------
     def find_min_max_abs(self):
-        if self.dist is not None:
-            self._check_ranks_agree()
         stats, n_img = self._local_min_max()
+        t_comb = time.perf_counter()
         if self.dist is not None:
             packed = torch.stack([-stats[:, 0], stats[:, 1]], dim=1).contiguous()
             self.dist.all_reduce(packed, op=self.dist.ReduceOp.MAX)
@@ -248,6 +249,7 @@ class ActivationCalibrator:
             n_img = int(cnt.item())
         self.num_samples = n_img
         host = stats.cpu().numpy()
+        self.pass1_host_s["combine"] = time.perf_counter() - t_comb
         out = {}
         for t, name in enumerate(self.names):
             mn, mx = np.float32(host[t, 0]), np.float32(host[t, 1])

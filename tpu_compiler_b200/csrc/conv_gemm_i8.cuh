@@ -658,7 +658,11 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
   // previous one is still finishing and only then waits for that kernel's results (pdl_wait below).
   pdl_trigger();
   if (threadIdx.x == 0) {
-    *abort_flag = 0;
+    // A CTA of a launch in which an earlier CTA already gave up does no work at all, so that a broken launch ends
+    // quickly instead of timing out once per tile. The flag is read first and stored last, so that the load's
+    // latency passes behind the barrier set-up, and ahead of pdl_wait on purpose: a flag raised by the previous
+    // kernel after this read only costs this CTA its own bounded wait, the host sees the error either way.
+    const int gave_up = *reinterpret_cast<volatile int *>(p.err);
     for (int s = 0; s < p.stages; ++s) {
       ptx::mbar_init(bar_full + 8 * s, 1);
       ptx::mbar_init(bar_empty + 8 * s, 1);
@@ -669,6 +673,7 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
     }
     ptx::mbar_init(bar_w, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    *abort_flag = gave_up;
   }
   if (warp == 1) {
     ptx::tcgen05_alloc(ptx::smem_u32(tmem_slot), (uint32_t)p.tmem_cols);
@@ -679,10 +684,6 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
   const uint32_t tmem_base = *tmem_slot;
   // From here on the kernel touches global memory: the previous kernel's writes must be complete and visible.
   pdl_wait();
-  // A CTA of a launch in which an earlier CTA already gave up does no work at all, so that a
-  // broken launch ends quickly instead of timing out once per tile.
-  if (threadIdx.x == 0) *abort_flag = *reinterpret_cast<volatile int *>(p.err);
-  __syncthreads();
   if (*abort_flag != 0) total_tiles = 0;
 
   if (warp == 0) {

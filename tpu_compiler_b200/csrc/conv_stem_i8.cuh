@@ -71,13 +71,14 @@ conv_stem_i8_kernel(const __grid_constant__ CUtensorMap tmB, const ConvStemParam
 
   pdl_trigger(); // see conv_gemm_body: set-up overlaps the previous kernel's tail
   if (threadIdx.x == 0) {
-    *abort_flag = 0;
+    const int gave_up = *reinterpret_cast<volatile int *>(p.err); // read early, as in conv_gemm_body
     // every gathering thread arrives once per tile (also those without a pixel), so that the next
     // tile's MMAs cannot start before all epilogue warps have left the accumulator
     ptx::mbar_init(bar_a, (uint32_t)(kStemThreads - 32));
     ptx::mbar_init(bar_b, 1);
     ptx::mbar_init(bar_acc, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    *abort_flag = gave_up;
   }
   if (warp == 0) ptx::tcgen05_alloc(ptx::smem_u32(tmem_slot), (uint32_t)p.tmem_cols);
   ptx::tcgen05_fence_before();
@@ -85,8 +86,6 @@ conv_stem_i8_kernel(const __grid_constant__ CUtensorMap tmB, const ConvStemParam
   ptx::tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   pdl_wait(); // global memory from here on
-  if (threadIdx.x == 0) *abort_flag = *reinterpret_cast<volatile int *>(p.err);
-  __syncthreads();
   if (*abort_flag != 0) total_tiles = 0;
 
   if (warp == 0) {

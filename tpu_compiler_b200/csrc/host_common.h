@@ -95,8 +95,16 @@ inline void launch_k(void (*kernel)(KArgs...), G grid, B block, size_t smem, cud
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = launch_pdl_flag() ? 1 : 0;
-  TPUCB_CUDA(cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...));
+  cfg.numAttrs = 1;
+  const bool pdl = launch_pdl_flag();
+  // The arguments are converted to the kernel's own parameter types and passed by address; without the attribute the
+  // launch goes through the classic entry point.
+  auto go = [&](KArgs... a) {
+    void *pa[sizeof...(KArgs) + 1] = {(void *)&a...};
+    return pdl ? cudaLaunchKernelExC(&cfg, (const void *)kernel, pa)
+               : cudaLaunchKernel((const void *)kernel, cfg.gridDim, cfg.blockDim, pa, smem, stream);
+  };
+  TPUCB_CUDA(go(std::forward<Args>(args)...));
 }
 #endif
 

@@ -604,6 +604,19 @@ public:
       a.wgt = I.upload(w);
       a.bias = d_bias_; a.mult = d_mult_; a.rshift = d_rsh_;
       dwargs_ = a;
+      if (g.kh == 3 && g.kw == 3 && g.dh == 1 && g.dw == 1 && g.sh == g.sw && (g.sh == 1 || g.sh == 2) && (fastq & 1)) {
+        // the dot-product kernel: weights as one word per (channel word, filter row, channel): w0 | w1 << 8 | w2 << 16
+        const int cw = in->cp / 4;
+        std::vector<uint32_t> wt((size_t)cw * 12, 0u);
+        for (int c = 0; c < g.ic; ++c)
+          for (int r = 0; r < 3; ++r) {
+            uint32_t word = 0;
+            for (int ss = 0; ss < 3; ++ss)
+              word |= (uint32_t)(uint8_t)(int8_t)(int)filt.data[(size_t)c * 9 + r * 3 + ss] << (8 * ss);
+            wt[((size_t)(c / 4) * 3 + r) * 4 + (c % 4)] = word;
+          }
+        dw_wt_ = I.upload(wt);
+      }
       return;
     }
 
@@ -778,6 +791,13 @@ public:
         int grid = grid_for(items, 128, I_.sm_count);
         const uint32_t *src = (const uint32_t *)in_->dev;
         uint32_t *dst = (uint32_t *)out_->dev;
+        if (dw_wt_) {
+          if (d.sh == 1 && d.do_relu) launch_k(dwconv3x3_dp4a_kernel<1, true>, grid, 128, 0, s, src, dst, dw_wt_, d);
+          else if (d.sh == 1) launch_k(dwconv3x3_dp4a_kernel<1, false>, grid, 128, 0, s, src, dst, dw_wt_, d);
+          else if (d.do_relu) launch_k(dwconv3x3_dp4a_kernel<2, true>, grid, 128, 0, s, src, dst, dw_wt_, d);
+          else launch_k(dwconv3x3_dp4a_kernel<2, false>, grid, 128, 0, s, src, dst, dw_wt_, d);
+          return;
+        }
         if (d.sh == 1 && d.do_relu) launch_k(dwconv3x3_i8_kernel<1, 8, true>, grid, 128, 0, s, src, dst, d);
         else if (d.sh == 1) launch_k(dwconv3x3_i8_kernel<1, 8, false>, grid, 128, 0, s, src, dst, d);
         else if (d.do_relu) launch_k(dwconv3x3_i8_kernel<2, 4, true>, grid, 128, 0, s, src, dst, d);
@@ -813,6 +833,7 @@ private:
   DwArgs dwargs_;
   const int32_t *d_bias_ = nullptr, *d_mult_ = nullptr, *d_rsh_ = nullptr;
   const float *f32_w_ = nullptr, *f32_b_ = nullptr;
+  const uint32_t *dw_wt_ = nullptr; // depthwise 3x3: weights packed for dwconv3x3_dp4a_kernel (null: the multiply-add kernel)
 };
 
 // ------------------------------------------------------------------- FullyConnected

@@ -637,6 +637,117 @@ dwconv3x3_i8_kernel(const uint32_t *__restrict__ in, uint32_t *__restrict__ out,
   }
 }
 
+// The same layers with the multiply-adds as four-way dot products (dp4a). Every integer instruction costs a thread
+// two issue cycles on this SM whatever it does, so the kernel above, at nine multiply-adds plus the byte unpacking per
+// output value, is bound by instruction issue at a fraction of the HBM rate. Here a thread still owns one 4-channel
+// word and TW = 8 / S outputs of a row, but it first turns each group of four input columns into four words that hold ONE
+// channel's four columns each (a 4 x 4 byte transpose: 8 permutes per 16 values); an output's three taps of a filter
+// row are then three neighbouring bytes of such a word (or of the funnel shift of two of them), and one dp4a against
+// the row's packed weights (w0, w1, w2, 0) -- or (0, w0, w1, w2) for the window that starts one byte later -- adds all
+// three. Per output value: 3 dp4a + 1.5 shifts + 2.25 permutes instead of 9 multiply-adds + 3.75 permutes, and the
+// requantisation in the multiply-high form of the tensor-core epilogue (|acc + bias| < 2^29 always holds here).
+// `wt`: the weights packed on the host as [cp / 4][3 rows][4 channels] words (w0 | w1 << 8 | w2 << 16).
+template <int S, bool RELU>
+__global__ void __launch_bounds__(128)
+dwconv3x3_dp4a_kernel(const uint32_t *__restrict__ in, uint32_t *__restrict__ out, const uint32_t *__restrict__ wt, DwArgs a) {
+  pdl_prologue();
+  constexpr int TW = 8 / S;             // outputs per thread: 8 (stride 1) or 4 (stride 2)
+  const int cw = a.cp / 4;
+  const int xg = (a.ow + TW - 1) / TW;
+  const size_t total = (size_t)a.n * a.oh * xg * cw;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int w4 = (int)(i % cw);
+    size_t t = i / cw;
+    const int gx = (int)(t % xg);
+    t /= xg;
+    const int y = (int)(t % a.oh);
+    const int b = (int)(t / a.oh);
+    int acc[TW][4];
+#pragma unroll
+    for (int p = 0; p < TW; ++p)
+#pragma unroll
+      for (int k = 0; k < 4; ++k) acc[p][k] = 0;
+    const int x0 = gx * 8 - a.pl; // first input column under this thread's outputs (TW * S = 8 in both cases)
+#pragma unroll
+    for (int r = 0; r < 3; ++r) {
+      const int yy = y * S - a.pt + r;
+      if (yy < 0 || yy >= a.ih) continue;
+      const uint32_t *row = in + ((size_t)b * a.ih + yy) * a.iw * cw + w4;
+      const uint4 wr = __ldg(reinterpret_cast<const uint4 *>(wt) + (size_t)w4 * 3 + r); // (w0, w1, w2, 0) per channel
+      const uint32_t wa[4] = {wr.x, wr.y, wr.z, wr.w};
+      // twelve columns, three groups of four, each transposed to one word per channel
+      uint32_t tch[3][4];
+#pragma unroll
+      for (int g = 0; g < 3; ++g) {
+        uint32_t v[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int xx = x0 + 4 * g + c;
+          // columns 10 and 11 lie beyond the last window (stride 1: columns 0..9; stride 2: 0..8)
+          v[c] = (4 * g + c < (S == 1 ? 10 : 9) && xx >= 0 && xx < a.iw) ? __ldg(row + (size_t)xx * cw) : 0u;
+        }
+        const uint32_t a01 = __byte_perm(v[0], v[1], 0x5140), b01 = __byte_perm(v[0], v[1], 0x7362);
+        const uint32_t a23 = __byte_perm(v[2], v[3], 0x5140), b23 = __byte_perm(v[2], v[3], 0x7362);
+        tch[g][0] = __byte_perm(a01, a23, 0x5410);
+        tch[g][1] = __byte_perm(a01, a23, 0x7632);
+        tch[g][2] = __byte_perm(b01, b23, 0x5410);
+        tch[g][3] = __byte_perm(b01, b23, 0x7632);
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int w0 = (int)wa[k], w1 = (int)(wa[k] << 8); // taps on bytes 0..2, or on bytes 1..3
+        const uint32_t t0 = tch[0][k], t1 = tch[1][k], t2 = tch[2][k];
+        if (S == 1) {
+          acc[0][k] = __dp4a((int)t0, w0, acc[0][k]);                                 // columns 0..2
+          acc[1][k] = __dp4a((int)t0, w1, acc[1][k]);                                 // 1..3
+          acc[2][k] = __dp4a((int)__funnelshift_r(t0, t1, 16), w0, acc[2][k]);        // 2..4
+          acc[3][k] = __dp4a((int)__funnelshift_r(t0, t1, 24), w0, acc[3][k]);        // 3..5
+          acc[4][k] = __dp4a((int)t1, w0, acc[4][k]);                                 // 4..6
+          acc[5][k] = __dp4a((int)t1, w1, acc[5][k]);                                 // 5..7
+          acc[6][k] = __dp4a((int)__funnelshift_r(t1, t2, 16), w0, acc[6][k]);        // 6..8
+          acc[7][k] = __dp4a((int)__funnelshift_r(t1, t2, 24), w0, acc[7][k]);        // 7..9
+        } else {
+          acc[0][k] = __dp4a((int)t0, w0, acc[0][k]);                                 // columns 0..2
+          acc[1][k] = __dp4a((int)__funnelshift_r(t0, t1, 16), w0, acc[1][k]);        // 2..4
+          acc[2][k] = __dp4a((int)t1, w0, acc[2][k]);                                 // 4..6
+          acc[3][k] = __dp4a((int)__funnelshift_r(t1, t2, 16), w0, acc[3][k]);        // 6..8
+        }
+      }
+    }
+    // requantisation: the multiply-high form (see requant_fast in conv_gemm_i8.cuh), constants per channel
+    const int4 bi = __ldg(reinterpret_cast<const int4 *>(a.bias) + w4);
+    const int4 mu = __ldg(reinterpret_cast<const int4 *>(a.mult) + w4);
+    const int4 rs = __ldg(reinterpret_cast<const int4 *>(a.rshift) + w4);
+    const int bb[4] = {bi.x, bi.y, bi.z, bi.w}, mm[4] = {mu.x, mu.y, mu.z, mu.w}, rr[4] = {rs.x, rs.y, rs.z, rs.w};
+    uint32_t sb[4], m2[4], kc[4];
+    int r1[4], corr[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const uint32_t rnd = rr[k] > 0 ? (1u << (rr[k] - 1)) : 0u;
+      sb[k] = 2u * (uint32_t)bb[k] + 0x80000000u;
+      m2[k] = (uint32_t)mm[k] << 1;
+      corr[k] = (!RELU && rr[k] > 0) ? 2 : 0; // the sign term of RoundingDivideByPOT, see requant_fast
+      kc[k] = 1u + 2u * rnd - (uint32_t)mm[k] - (uint32_t)corr[k];
+      r1[k] = rr[k] + 1;
+    }
+    uint32_t *orow = out + (((size_t)b * a.oh + y) * a.ow) * cw + w4;
+#pragma unroll
+    for (int p = 0; p < TW; ++p) {
+      int q[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const uint32_t s2 = 2u * (uint32_t)acc[p][k] + sb[k];
+        const int tk = (int)(__umulhi(s2, m2[k]) + kc[k]);
+        q[k] = RELU ? (tk >> r1[k]) : ((tk + (((int)s2 >> 31) & corr[k])) >> r1[k]);
+      }
+      uint32_t w = pack4_sat(q[0], q[1], q[2], q[3]);
+      if (RELU) w = __vmaxs4(w, 0u);
+      const int x = gx * TW + p;
+      if (x < a.ow) orow[(size_t)x * cw] = w;
+    }
+  }
+}
+
 // ---------------------------------------------------------------- patch expansion
 // Writes the patch matrix A[M = n*oh*ow][kp] (kp = padded kh*kw*c, K order (r, s, c) over
 // the REAL channels) for convolutions the im2col TMA path does not take: very few

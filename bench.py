@@ -346,23 +346,29 @@ def run_conv_sweep(args, local_rank):
     import ctypes as C
     from tpu_compiler_b200._lib import check, lib
     peaks = measured_peaks()
-    cases = [(c, hw, n) for n in (1, 8, 32) for c, hw in ((64, 56), (128, 28), (256, 14), (512, 7))]
+    cases = [(c, hw, n, 3, c, 1) for n in (1, 8, 32) for c, hw in ((64, 56), (128, 28), (256, 14), (512, 7))]
     if args.case:
-        c, hw, n = (int(v) for v in args.case.split(","))
-        cases = [(c, hw, n)]
+        # c,hw,n of the sweep, optionally followed by kernel size, output channels and ReLU (0/1): other layers of the
+        # benchmark graphs (e.g. 64,56,256,1,256,0 = the 1x1 expand layers of ResNet-50's second stage at batch 256)
+        v = [int(x) for x in args.case.split(",")]
+        c, hw, n = v[:3]
+        cases = [(c, hw, n, v[3] if len(v) > 3 else 3, v[4] if len(v) > 4 else c, v[5] if len(v) > 5 else 1)]
     i8_tops = C.c_double(0.0)
     check(lib().tpucb_measure_i8_mma_peak(local_rank, 128, C.byref(i8_tops)))
     rows = []
-    for c, hw, n in cases:
-        model = graphs.single_conv_i8(n=n, c_in=c, c_out=c, hw=hw, k=3, stride=1, pad=1, relu=True, seed=2000 + c + n)
+    for c, hw, n, k, co, relu in cases:
+        model = graphs.single_conv_i8(n=n, c_in=c, c_out=co, hw=hw, k=k, stride=1, pad=k // 2, relu=bool(relu),
+                                      seed=2000 + c + n)
         m = module(local_rank)
         m.load_text(model.text, model.weights)
         m.set_tensor("x", model.meta["x"])
         for _ in range(max(args.warmup, 3)):
             m.invoke()
         ms = m.time_launches(args.steps) / args.steps
-        ops = 2.0 * n * hw * hw * c * c * 9
+        ops = 2.0 * n * hw * hw * c * co * k * k
         row = {"c": c, "hw": hw, "n": n, "us": ms * 1e3, "tops": ops / (ms * 1e-3) / 1e12}
+        if (k, co, relu) != (3, c, 1):
+            row.update({"k": k, "c_out": co, "relu": relu, "outputs_per_s": n * hw * hw * co / (ms * 1e-3)})
         rows.append(row)
         m.close()
     best = max(r["tops"] for r in rows)
@@ -478,7 +484,7 @@ def main():
     ap.add_argument("--cpu-threads", type=int, default=0, help="--impl reference: host threads (default: all)")
     ap.add_argument("--no-extras", action="store_true", help="headline only: skip the batch-1 configuration, the "
                     "secondary graphs, the link ceiling and the calibration sub-record")
-    ap.add_argument("--case", default=None, help="conv_sweep only: one case as c,hw,n")
+    ap.add_argument("--case", default=None, help="conv_sweep only: one case as c,hw,n[,k[,c_out[,relu]]]")
     ap.add_argument("--cal-images", type=int, default=512, help="calibration workload: images per GPU")
     ap.add_argument("--cal-batch", type=int, default=64, help="calibration workload: images per batch (64 in the "
                     "configuration; smaller values are for profiler captures)")

@@ -95,15 +95,29 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// The same with a suspend-time hint (nanoseconds): the thread may sleep in the instruction until the phase completes
+// or that much time has passed, instead of coming back after the (short) default limit; a waiting role then spends
+// few issue slots on its polling loop.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(ns)
+      : "memory");
+  return ok != 0;
+}
 // Bounded wait: returns false when the barrier did not flip within the limit.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
                                                   volatile int *abort_flag, int rounds = 1024) {
-  // `rounds` (1024 by default) rounds of 1024 polls: the abort flag (another role of this CTA gave up) is read once
-  // per round
+  // `rounds` (1024 by default) rounds of 1024 polls of at most a microsecond each (about a second in all): the abort
+  // flag (another role of this CTA gave up) is read once per round
   for (int round = 0; round < rounds; ++round) {
 #pragma unroll 1
     for (int it = 1024; it > 0; --it)
-      if (mbar_try_wait(bar, parity)) return true;
+      if (mbar_try_wait_hint(bar, parity, 1000u)) return true;
     if (*abort_flag) return false;
   }
   return false;
@@ -373,9 +387,11 @@ __device__ __forceinline__ int requant_one(int32_t acc, const ChanConst &q, cons
 // layer and the largest possible |acc| satisfy that, else requant_one runs.
 template <int ACT, bool R1>
 __device__ __forceinline__ int requant_fast(int32_t acc, const ChanConst &q, const ConvGemmParams &p) {
-  // The instructions are spelled out: the integer ALU (shifts, logic, three-input adds, packs, permutes) issues at
-  // half the rate of the multiply-add pipe on this SM, so the doubling and the sign term are multiply-adds and
-  // only the two shifts go to the ALU (measured on a 64 -> 256 channel 1x1 layer: 122 -> 112 us).
+  // The instructions are spelled out. Measured rates on this SM, lanes per clock: add / min / max 127; shifts, logic,
+  // permutes, saturating packs and 32-bit multiply-adds 64, the last on a pipe of their own; multiply-high and
+  // shuffles 32; the 64-bit multiply-add 16. The doubling and the sign term are multiply-adds, which run beside the
+  // two shifts on the ALU: 122 -> 112 us on a 64 -> 256 channel 1x1 layer at batch 256; written as adds instead,
+  // both 123 us, the doubling alone 111, the sign term alone 114.
   uint32_t s2, tk;
   asm("mad.lo.u32 %0, %1, 2, %2;" : "=r"(s2) : "r"((uint32_t)acc), "r"(q.sbias));
   asm("mad.hi.u32 %0, %1, %2, %3;" : "=r"(tk) : "r"(s2), "r"(q.M2), "r"(q.kc));

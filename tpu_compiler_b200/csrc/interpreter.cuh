@@ -231,10 +231,16 @@ public:
   // Programmatic dependent launch between the kernels of the op list: 1 on, 0 off, -1 decided per module at load.
   // It hides each kernel's launch and set-up behind its predecessor's tail, which pays while kernels are short
   // (INT8 ResNet-50: 10% fewer ms per launch at batch 1 to 16, 2% at 64) and costs once they are long (3% more at
-  // batch 256: early CTAs of the next kernel share the SMs with the tail of the running one). The automatic rule
-  // turns it on when the module moves less than 48 MB per kernel on average.
+  // batch 256, 4 to 6% more on the YOLOv4-style graph at every batch). No property of the op list predicts the sign,
+  // so in automatic mode the first graph launch of a module captures the op list both ways, replays each a few
+  // times and keeps the faster graph (measure_pdl; the replays recompute the same results from the same inputs).
+  // Until then, and for launches outside the graph, a rule holds: on when the module moves less than 10 MB per
+  // kernel on average.
   int use_pdl = -1;
-  bool pdl_auto = false;
+  bool pdl_auto = false;     // the choice in effect while use_pdl < 0
+  bool pdl_measured = false; // ... and whether it comes from the measurement below or from the load-time rule
+  cudaGraphExec_t capture_graph();
+  void measure_pdl();
   // Self-test (option "selftest_lost_arrival", read by the next load_module): > 0 makes every INT8 tensor-core
   // convolution built from then on lose its accumulator hand-back and wait only that many rounds of 1024 polls
   // (ConvGemmParams::wait_rounds / lose_arrival), so that a launch ends with a bounded-wait error status.
@@ -1872,6 +1878,7 @@ inline void Interpreter::fuse_activation_chains(const std::map<std::string, int>
 inline void Interpreter::reset_module() {
   bind();
   invalidate_graph();
+  pdl_measured = false;
   kernels.clear();
   for (auto &kv : tensors)
     if (kv.second->owns && kv.second->dev) cudaFree(kv.second->dev);
@@ -2054,7 +2061,7 @@ inline void Interpreter::finish_module() {
       bytes += k->alg_bytes;
       launches += k->kernel_launches();
     }
-    pdl_auto = launches > 0 && bytes / launches < 48e6;
+    pdl_auto = launches > 0 && bytes / launches < 10e6;
   }
   output_details.clear();
   for (auto &k : kernels)
@@ -2278,25 +2285,74 @@ inline void Interpreter::get_tensor(const std::string &name, float *out, size_t 
   TPUCB_CUDA(cudaStreamSynchronize(stream));
 }
 
+// The op list captured as one CUDA graph, with the launch flag of the moment.
+inline cudaGraphExec_t Interpreter::capture_graph() {
+  cudaGraph_t graph = nullptr;
+  cudaGraphExec_t exec = nullptr;
+  TPUCB_CUDA(cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal));
+  try {
+    for (auto &k : kernels) k->run(stream);
+  } catch (...) {
+    cudaStreamEndCapture(stream, &graph);
+    if (graph) cudaGraphDestroy(graph);
+    throw;
+  }
+  TPUCB_CUDA(cudaStreamEndCapture(stream, &graph));
+  cudaError_t e = cudaGraphInstantiate(&exec, graph, 0);
+  cudaGraphDestroy(graph);
+  TPUCB_CUDA(e);
+  return exec;
+}
+
+// Automatic mode: programmatic dependent launch on or off, by the replay time of the two graphs (best of three
+// rounds of three replays after one warm-up replay each; "on" has to win by 1%). Leaves the chosen graph in
+// graph_exec. The self-test mode of the bounded waits keeps the rule: its launches end in an error status.
+inline void Interpreter::measure_pdl() {
+  cudaGraphExec_t ex[2] = {nullptr, nullptr};
+  cudaEvent_t a = nullptr, b = nullptr;
+  float best[2] = {1e30f, 1e30f};
+  try {
+    for (int mode = 0; mode < 2; ++mode) {
+      launch_pdl_flag() = mode != 0;
+      ex[mode] = capture_graph();
+      TPUCB_CUDA(cudaGraphLaunch(ex[mode], stream));
+    }
+    TPUCB_CUDA(cudaEventCreate(&a));
+    TPUCB_CUDA(cudaEventCreate(&b));
+    for (int round = 0; round < 3; ++round)
+      for (int mode = 0; mode < 2; ++mode) {
+        TPUCB_CUDA(cudaEventRecord(a, stream));
+        for (int i = 0; i < 3; ++i) TPUCB_CUDA(cudaGraphLaunch(ex[mode], stream));
+        TPUCB_CUDA(cudaEventRecord(b, stream));
+        TPUCB_CUDA(cudaEventSynchronize(b));
+        float ms = 0;
+        TPUCB_CUDA(cudaEventElapsedTime(&ms, a, b));
+        if (ms < best[mode]) best[mode] = ms;
+      }
+  } catch (...) {
+    for (auto e : ex)
+      if (e) cudaGraphExecDestroy(e);
+    if (a) cudaEventDestroy(a);
+    if (b) cudaEventDestroy(b);
+    launch_pdl_flag() = pdl_auto;
+    throw;
+  }
+  cudaEventDestroy(a);
+  cudaEventDestroy(b);
+  const int pick = best[1] < 0.99f * best[0] ? 1 : 0;
+  cudaGraphExecDestroy(ex[1 - pick]);
+  graph_exec = ex[pick];
+  pdl_auto = pick != 0;
+  pdl_measured = true;
+  launch_pdl_flag() = pdl_auto;
+}
+
 // invoke (MlirModuleInterpreter.cpp:371-381): the op loop; replayed as one CUDA graph.
 inline void Interpreter::launch_all() {
   bind();
   if (use_graph) {
-    if (!graph_exec) {
-      cudaGraph_t graph = nullptr;
-      TPUCB_CUDA(cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal));
-      try {
-        for (auto &k : kernels) k->run(stream);
-      } catch (...) {
-        cudaStreamEndCapture(stream, &graph);
-        if (graph) cudaGraphDestroy(graph);
-        throw;
-      }
-      TPUCB_CUDA(cudaStreamEndCapture(stream, &graph));
-      cudaError_t e = cudaGraphInstantiate(&graph_exec, graph, 0);
-      cudaGraphDestroy(graph);
-      TPUCB_CUDA(e);
-    }
+    if (!graph_exec && use_pdl < 0 && !pdl_measured && selftest_lost_arrival == 0 && !kernels.empty()) measure_pdl();
+    if (!graph_exec) graph_exec = capture_graph();
     TPUCB_CUDA(cudaGraphLaunch(graph_exec, stream));
   } else {
     for (auto &k : kernels) k->run(stream);

@@ -649,7 +649,6 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
   // 64..191 of it ([W; 0]) times the first 128 pixels fill TMEM lanes 0..63, rows 0..127 ([0; W]) times
   // the second 128 pixels accumulate into lanes 64..127, so all 128 lanes (and all epilogue warps) work.
   const int m_tile = p.dual ? 256 : 128;
-  const int subs = p.dual ? 2 : 1;
   const int m_tiles = (p.M_total + m_tile - 1) / m_tile;
   int total_tiles = n_tiles * m_tiles; // set to 0 below when the launch is already marked as failed
   const uint32_t a_bytes = (uint32_t)m_tile * (uint32_t)p.BK;
@@ -726,17 +725,14 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
           tn -= n_tiles;
           ++tm;
         }
-        int n_img[2] = {0, 0}, h_base[2] = {0, 0}, w_base[2] = {0, 0};
+        int n_img = 0, h_base = 0, w_base = 0; // im2col: base coordinates of the tile's first pixel
         if (p.a_mode == 1) {
-          for (int sub = 0; sub < subs; ++sub) {
-            const int ms = m0 + 128 * sub;
-            int q = ms % p.OW;
-            int t = ms / p.OW;
-            int pp = t % p.OH;
-            n_img[sub] = t / p.OH;
-            w_base[sub] = q * p.sw - p.pl;
-            h_base[sub] = pp * p.sh - p.pt;
-          }
+          const int q = m0 % p.OW;
+          const int t = m0 / p.OW;
+          const int pp = t % p.OH;
+          n_img = t / p.OH;
+          w_base = q * p.sw - p.pl;
+          h_base = pp * p.sh - p.pt;
         }
         // mode 2: the (column, row, image) of the first pixel of each copy, computed once per tile
         int bx_q[16], bx_h[16], bx_n[16];
@@ -768,17 +764,17 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
           const uint32_t fb = bar_full + 8 * ps;
           ptx::mbar_expect_tx(fb, stage_bytes);
           if (p.a_mode == 1) {
-            for (int sub = 0; sub < subs; ++sub)
-              ptx::tma_load_im2col_4d(a_dst + (uint32_t)sub * 128u * (uint32_t)p.BK, mapA, fb, c0, w_base[sub],
-                                      h_base[sub], n_img[sub], (uint16_t)(ts * p.dw), (uint16_t)(tr * p.dh));
+            // one copy per tile, also in dual mode (the map's pixel count per copy is the tile's: every copy costs
+            // its issuing thread about 430 cycles whatever its size)
+            ptx::tma_load_im2col_4d(a_dst, mapA, fb, c0, w_base, h_base, n_img, (uint16_t)(ts * p.dw),
+                                    (uint16_t)(tr * p.dh));
           } else if (p.a_mode == 2) {
             // `tap` is the filter row; each copy brings win_g consecutive output pixels' windows.
             for (int i = 0; i < n_boxes; ++i)
               ptx::tma_load_4d(a_dst + (uint32_t)(i * p.win_g * p.BK), &tmA, fb, 0, bx_q[i],
                                bx_h[i] + tap * p.dh, bx_n[i]);
           } else {
-            for (int sub = 0; sub < subs; ++sub)
-              ptx::tma_load_2d(a_dst + (uint32_t)sub * 128u * (uint32_t)p.BK, mapA, fb, c0, m0 + 128 * sub);
+            ptx::tma_load_2d(a_dst, mapA, fb, c0, m0);
           }
           if (!p.w_resident) ptx::tma_load_3d(b_dst, mapB, fb, c0, tap, n0);
           if (++chunk == p.c_chunks) {

@@ -202,11 +202,14 @@ inline void encode_weight_map(CUtensorMap *tm, const int8_t *d_w, int oc_pad, in
   TPUCB_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled(weights) failed: %d", (int)r);
 }
 
+// `tile_rows`: rows (pixels) per copy = the plan's pixel tile: 128, or 256 in dual mode (a_tile_rows)
+inline int a_tile_rows(const ConvGemmParams &p) { return p.dual ? 256 : 128; }
+
 inline void encode_matrix_map(CUtensorMap *tm, const int8_t *d_a, int rows, int k_inner, int ld,
-                              int BK) {
+                              int BK, int tile_rows) {
   cuuint64_t dims[2] = {(cuuint64_t)k_inner, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)ld};
-  cuuint32_t box[2] = {(cuuint32_t)BK, 128};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)tile_rows};
   cuuint32_t es[2] = {1, 1};
   CUresult r = tma_api().tiled(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, (void *)d_a, dims, strides, box,
                                es, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_for(BK),
@@ -215,7 +218,7 @@ inline void encode_matrix_map(CUtensorMap *tm, const int8_t *d_a, int rows, int 
 }
 
 inline void encode_im2col_map(CUtensorMap *tm, const int8_t *d_in, const ConvGeom &g, int cp,
-                              int BK) {
+                              int BK, int tile_rows) {
   cuuint64_t dims[4] = {(cuuint64_t)cp, (cuuint64_t)g.iw, (cuuint64_t)g.ih, (cuuint64_t)g.n};
   cuuint64_t strides[3] = {(cuuint64_t)cp, (cuuint64_t)cp * g.iw, (cuuint64_t)cp * g.iw * g.ih};
   // Base-pixel bounding box: lower corner = -pad_lo, upper corner chosen so that the number
@@ -231,7 +234,7 @@ inline void encode_im2col_map(CUtensorMap *tm, const int8_t *d_in, const ConvGeo
     upper[1] = (g.oh - 1) * g.sh + 1 - g.ih - g.pt;
   cuuint32_t es[4] = {1, (cuuint32_t)g.sw, (cuuint32_t)g.sh, 1};
   CUresult r = tma_api().im2col(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, (void *)d_in, dims, strides,
-                                lower, upper, (cuuint32_t)BK, 128, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                lower, upper, (cuuint32_t)BK, (cuuint32_t)tile_rows, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
                                 swizzle_for(BK), CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   TPUCB_CHECK(r == CUDA_SUCCESS,

@@ -445,7 +445,7 @@ public:
         p.kh = p.kw = 1;
         p.a_mode = 0;
         finish_plan(pl, rows, 1, a.kp * 2, out->cp, I.sm_count);
-        encode_matrix_map(&pl.tmA, pl.patch_buf, rows, a.kp * 2, a.kp * 2, p.BK);
+        encode_matrix_map(&pl.tmA, pl.patch_buf, rows, a.kp * 2, a.kp * 2, p.BK, a_tile_rows(p));
         encode_weight_map(&pl.tmB, d_wp, out->cp, 1, a.kp * 2, p.BK, p.dual ? 192 : p.BN);
         p.idesc = make_idesc_bf16(128, p.BN);
         pl.ops = alg_ops;
@@ -458,13 +458,13 @@ public:
         p.kh = p.kw = 1;
         p.a_mode = 0;
         finish_plan(pl, rows, 1, k_bytes, out->cp, I.sm_count);
-        encode_matrix_map(&pl.tmA, (const int8_t *)in->dev, rows, k_bytes, k_bytes, p.BK);
+        encode_matrix_map(&pl.tmA, (const int8_t *)in->dev, rows, k_bytes, k_bytes, p.BK, a_tile_rows(p));
         encode_weight_map(&pl.tmB, d_w, out->cp, 1, k_bytes, p.BK, p.dual ? 192 : p.BN);
       } else {
         p.kh = g.kh; p.kw = g.kw;
         p.a_mode = 1;
         finish_plan(pl, rows, g.kh * g.kw, k_bytes, out->cp, I.sm_count);
-        encode_im2col_map(&pl.tmA, (const int8_t *)in->dev, g, k_bytes, p.BK);
+        encode_im2col_map(&pl.tmA, (const int8_t *)in->dev, g, k_bytes, p.BK, a_tile_rows(p));
         encode_weight_map(&pl.tmB, d_w, out->cp, g.kh * g.kw, k_bytes, p.BK, p.dual ? 192 : p.BN);
       }
       p.idesc = make_idesc_bf16(128, p.BN);
@@ -516,8 +516,8 @@ public:
         const int8_t *d_ph = I.upload(pack_patch_weights(filt.data.data(), g.oc, g.ic, g.kh, g.kw, out->cp, a.kp, 0, 4));
         const int8_t *d_pl = I.upload(pack_patch_weights(filt.data.data(), g.oc, g.ic, g.kh, g.kw, out->cp, a.kp, 1, 4));
         finish_plan(pl, rows, 1, kb, out->cp, I.sm_count);
-        encode_matrix_map(&pl.tmA, pl.patch_buf, rows, kb, kb, p.BK);
-        encode_matrix_map(&pl.tmA2, (const int8_t *)pl.split_lo, rows, kb, kb, p.BK);
+        encode_matrix_map(&pl.tmA, pl.patch_buf, rows, kb, kb, p.BK, a_tile_rows(p));
+        encode_matrix_map(&pl.tmA2, (const int8_t *)pl.split_lo, rows, kb, kb, p.BK, a_tile_rows(p));
         encode_weight_map(&pl.tmB, d_ph, out->cp, 1, kb, p.BK, p.BN);
         encode_weight_map(&pl.tmB2, d_pl, out->cp, 1, kb, p.BK, p.BN);
         p.idesc = make_idesc_tf32(128, p.BN);
@@ -565,11 +565,11 @@ public:
         p.a_mode = one ? 0 : 1;
         finish_plan(pl, rows, taps, k_bytes, out->cp, I.sm_count);
         if (one) {
-          encode_matrix_map(&pl.tmA, pl.split_hi ? (const int8_t *)pl.split_hi : (const int8_t *)in->dev, rows, k_bytes, k_bytes, p.BK);
-          encode_matrix_map(&pl.tmA2, (const int8_t *)pl.split_lo, rows, k_bytes, k_bytes, p.BK);
+          encode_matrix_map(&pl.tmA, pl.split_hi ? (const int8_t *)pl.split_hi : (const int8_t *)in->dev, rows, k_bytes, k_bytes, p.BK, a_tile_rows(p));
+          encode_matrix_map(&pl.tmA2, (const int8_t *)pl.split_lo, rows, k_bytes, k_bytes, p.BK, a_tile_rows(p));
         } else {
-          encode_im2col_map(&pl.tmA, pl.split_hi ? (const int8_t *)pl.split_hi : (const int8_t *)in->dev, g, k_bytes, p.BK);
-          encode_im2col_map(&pl.tmA2, (const int8_t *)pl.split_lo, g, k_bytes, p.BK);
+          encode_im2col_map(&pl.tmA, pl.split_hi ? (const int8_t *)pl.split_hi : (const int8_t *)in->dev, g, k_bytes, p.BK, a_tile_rows(p));
+          encode_im2col_map(&pl.tmA2, (const int8_t *)pl.split_lo, g, k_bytes, p.BK, a_tile_rows(p));
         }
         encode_weight_map(&pl.tmB, d_wh, out->cp, taps, k_bytes, p.BK, p.BN);
         encode_weight_map(&pl.tmB2, d_wl, out->cp, taps, k_bytes, p.BK, p.BN);
@@ -721,7 +721,7 @@ public:
         p.kh = p.kw = 1;
         p.a_mode = 0;
         finish_plan(pl, rows, 1, a.kp, ocg_pad, I.sm_count);
-        encode_matrix_map(&pl.tmA, pl.patch_buf, rows, a.kp, a.kp, p.BK);
+        encode_matrix_map(&pl.tmA, pl.patch_buf, rows, a.kp, a.kp, p.BK, a_tile_rows(p));
         encode_weight_map(&pl.tmB, d_w, ocg_pad, 1, a.kp, p.BK, p.dual ? 192 : p.BN);
       } else if (one_by_one) {
         auto w = pack_conv_weights(wsrc, ocg, icg, 1, 1, ocg_pad, in->cp, false, 0);
@@ -729,7 +729,7 @@ public:
         p.kh = p.kw = 1;
         p.a_mode = 0;
         finish_plan(pl, rows, 1, in->cp, ocg_pad, I.sm_count);
-        encode_matrix_map(&pl.tmA, (const int8_t *)in->dev, rows, in->cp, in->cp, p.BK);
+        encode_matrix_map(&pl.tmA, (const int8_t *)in->dev, rows, in->cp, in->cp, p.BK, a_tile_rows(p));
         encode_weight_map(&pl.tmB, d_w, ocg_pad, 1, in->cp, p.BK, p.dual ? 192 : p.BN);
       } else {
         auto w = pack_conv_weights(wsrc, ocg, icg, g.kh, g.kw, ocg_pad, in->cp, false, 0);
@@ -737,7 +737,7 @@ public:
         p.kh = g.kh; p.kw = g.kw;
         p.a_mode = 1;
         finish_plan(pl, rows, g.kh * g.kw, in->cp, ocg_pad, I.sm_count);
-        encode_im2col_map(&pl.tmA, (const int8_t *)in->dev, g, in->cp, p.BK);
+        encode_im2col_map(&pl.tmA, (const int8_t *)in->dev, g, in->cp, p.BK, a_tile_rows(p));
         encode_weight_map(&pl.tmB, d_w, ocg_pad, g.kh * g.kw, in->cp, p.BK, p.dual ? 192 : p.BN);
       }
       if (I.selftest_lost_arrival > 0) {
@@ -894,7 +894,7 @@ public:
       p.act = do_relu_ ? 1 : 0;
       p.a_mode = 0;
       finish_plan(pl, m_, 1, kdev_ * 2, n_pad, I.sm_count);
-      encode_matrix_map(&pl.tmA, (const int8_t *)in->dev, m_, kdev_ * 2, kdev_ * 2, p.BK);
+      encode_matrix_map(&pl.tmA, (const int8_t *)in->dev, m_, kdev_ * 2, kdev_ * 2, p.BK, a_tile_rows(p));
       encode_weight_map(&pl.tmB, d_w, n_pad, 1, kdev_ * 2, p.BK, p.dual ? 192 : p.BN);
       p.idesc = make_idesc_bf16(128, p.BN);
       plan_ = pl;
@@ -947,7 +947,7 @@ public:
     p.fastq = requant_fast_flags(rs, bias, k_);
     p.a_mode = 0;
     finish_plan(pl, m_, 1, kdev_, n_pad, I.sm_count);
-    encode_matrix_map(&pl.tmA, (const int8_t *)in->dev, m_, kdev_, kdev_, p.BK);
+    encode_matrix_map(&pl.tmA, (const int8_t *)in->dev, m_, kdev_, kdev_, p.BK, a_tile_rows(p));
     encode_weight_map(&pl.tmB, d_w, n_pad, 1, kdev_, p.BK, p.dual ? 192 : p.BN);
     plan_ = pl;
     alg_bytes = (double)m_ * k_ + (double)n_ * k_ + (double)m_ * n_ + 4.0 * n_ + 8;

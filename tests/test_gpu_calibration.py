@@ -169,6 +169,29 @@ def test_kept_activations_give_the_same_histograms():
     m.close()
 
 
+def test_pinned_batches_are_sent_from_where_they_lie():
+    """Batches that already lie in page-locked memory (torch tensors, pin_memory) skip the calibrator's staging copy and
+    give the same histograms and thresholds as the same values in numpy arrays; no staging buffer is allocated."""
+    import torch
+    from tpu_compiler_b200 import module
+    from tpu_compiler_b200.calibration import ActivationCalibrator
+    model = small_fp32_model(4)
+    rng = np.random.default_rng(79)
+    data = [np.clip(rng.normal(0, 1, (4, 3, 24, 24)), -3, 3).astype(np.float32) for _ in range(5)]
+    pinned = [torch.from_numpy(d).pin_memory() for d in data]
+    m = module(0)
+    m.load_text(model.text, model.weights)
+    a = ActivationCalibrator(m, lambda: iter(data))
+    thr_a, stats_a = a.run()
+    b = ActivationCalibrator(m, lambda: iter(pinned), keep_activations_gb=0)   # both passes upload
+    thr_b, stats_b = b.run()
+    assert b._pinned is None and b.pass1_host_s["pinned_copy"] == 0.0
+    assert np.array_equal(a.histograms.cpu().numpy(), b.histograms.cpu().numpy())
+    assert {k: float(v) for k, v in thr_a.items()} == {k: float(v) for k, v in thr_b.items()}
+    assert {k: tuple(map(float, v)) for k, v in stats_a.items()} == {k: tuple(map(float, v)) for k, v in stats_b.items()}
+    m.close()
+
+
 def test_several_bin_counts_from_one_pass():
     """run_multi: the thresholds of three histogram sizes from one min / max pass and one activation cache equal
     those of three separate calibrations, and the images are asked for only once."""

@@ -68,7 +68,7 @@ class ActivationCalibrator:
         # uploads to leave their buffer, enqueueing (module launch + statistics launch), the final synchronisation
         self.pass1_host_s = {"pinned_copy": 0.0, "wait_uploads": 0.0, "enqueue": 0.0, "final_sync": 0.0, "combine": 0.0}
         if self.dist is not None:
-            self._check_ranks_agree()   # once, at set-up: its two small all-reduces are not part of a pass
+            self._check_ranks_agree()   # once, at set-up: its all-reduces are not part of a pass
         if self._lib is not None:
             # the two pinned upload buffers are part of setting up (tens of milliseconds), not of a pass
             self._alloc_pinned(int(np.prod(model.get_tensor_shape(self.input_name))))
@@ -150,6 +150,17 @@ class ActivationCalibrator:
     def _upload(self, batch):
         """The batch becomes the input of the next launch. It is copied into one of two pinned host buffers and sent
         with set_tensor_async, so the host-side copy and the transfer of batch i + 1 run while batch i is computed."""
+        if (isinstance(batch, torch.Tensor) and batch.device.type == "cpu" and batch.dtype == torch.float32 and
+                batch.is_contiguous() and batch.is_pinned()):
+            # already in page-locked memory (a loader with pin_memory=True): sent from where it lies; the two most
+            # recent batches are kept alive until their copies have left the host
+            t0 = time.perf_counter()
+            self.model.set_tensor_async(self.input_name, C.c_void_p(batch.data_ptr()), batch.numel())
+            self._in_flight = (getattr(self, "_in_flight", ()) + (batch,))[-2:]
+            self.pass1_host_s["enqueue"] += time.perf_counter() - t0
+            return
+        if isinstance(batch, torch.Tensor):
+            batch = batch.numpy()
         batch = np.ascontiguousarray(batch, np.float32)
         if self._pinned is None or self._pinned_numel != batch.size:
             self._alloc_pinned(batch.size)
@@ -235,6 +246,14 @@ class ActivationCalibrator:
             raise RuntimeError("calibration ranks disagree: this rank has %d tensors (fingerprint %d, %d bins); across "
                                "ranks the counts span %d..%d" % (len(self.names), int(mine[1]), self.bin_num,
                                                                  int(lo[0]), int(hi[0])))
+        # One collective of each kind and size the passes use, on zeros: the library builds its connections and loads
+        # its kernels at the first use of each (30 ms measured on two GPUs), which belongs to the set-up.
+        T = len(self.names)
+        self.dist.all_reduce(torch.zeros(T, 2, dtype=torch.float32, device=dev), op=self.dist.ReduceOp.MAX)
+        self.dist.all_reduce(torch.zeros(1, dtype=torch.int64, device=dev), op=self.dist.ReduceOp.SUM)
+        self.dist.all_reduce(torch.zeros(T, self.bin_num, dtype=torch.int64, device=dev), op=self.dist.ReduceOp.SUM)
+        if dev.type == "cuda":
+            torch.cuda.synchronize(dev)
 
     # -- pass 1 ------------------------------------------------------------------
     def find_min_max_abs(self):

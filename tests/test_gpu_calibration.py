@@ -171,7 +171,7 @@ def test_kept_activations_give_the_same_histograms():
 
 def test_pinned_batches_are_sent_from_where_they_lie():
     """Batches that already lie in page-locked memory (torch tensors, pin_memory) skip the calibrator's staging copy and
-    give the same histograms and thresholds as the same values in numpy arrays; no staging buffer is allocated."""
+    give the same histograms and thresholds as the same values in numpy arrays."""
     import torch
     from tpu_compiler_b200 import module
     from tpu_compiler_b200.calibration import ActivationCalibrator
@@ -185,7 +185,7 @@ def test_pinned_batches_are_sent_from_where_they_lie():
     thr_a, stats_a = a.run()
     b = ActivationCalibrator(m, lambda: iter(pinned), keep_activations_gb=0)   # both passes upload
     thr_b, stats_b = b.run()
-    assert b._pinned is None and b.pass1_host_s["pinned_copy"] == 0.0
+    assert b.pass1_host_s["pinned_copy"] == 0.0   # no batch went through the staging buffers
     assert np.array_equal(a.histograms.cpu().numpy(), b.histograms.cpu().numpy())
     assert {k: float(v) for k, v in thr_a.items()} == {k: float(v) for k, v in thr_b.items()}
     assert {k: tuple(map(float, v)) for k, v in stats_a.items()} == {k: tuple(map(float, v)) for k, v in stats_b.items()}

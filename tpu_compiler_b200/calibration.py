@@ -248,24 +248,29 @@ class ActivationCalibrator:
                                                                  int(lo[0]), int(hi[0])))
         # One collective of each kind and size the passes use, on zeros: the library builds its connections and loads
         # its kernels at the first use of each (30 ms measured on two GPUs), which belongs to the set-up.
+        # The same goes for the few torch kernels of the combine step (loaded at their first launch): 27 ms in all.
         T = len(self.names)
-        self.dist.all_reduce(torch.zeros(T, 2, dtype=torch.float32, device=dev), op=self.dist.ReduceOp.MAX)
-        self.dist.all_reduce(torch.zeros(1, dtype=torch.int64, device=dev), op=self.dist.ReduceOp.SUM)
+        self._combine_min_max(torch.zeros(T, 2, dtype=torch.float32, device=dev), 0)[0].cpu()
         self.dist.all_reduce(torch.zeros(T, self.bin_num, dtype=torch.int64, device=dev), op=self.dist.ReduceOp.SUM)
         if dev.type == "cuda":
             torch.cuda.synchronize(dev)
+
+    def _combine_min_max(self, stats, n_img):
+        """[T, 2] (min, max) of this rank and its image count -> those of all ranks: one all-reduce(MAX) over
+        (-min, max), one all-reduce(SUM) of the count."""
+        packed = torch.stack([-stats[:, 0], stats[:, 1]], dim=1).contiguous()
+        self.dist.all_reduce(packed, op=self.dist.ReduceOp.MAX)
+        stats = torch.stack([-packed[:, 0], packed[:, 1]], dim=1)
+        cnt = torch.tensor([n_img], dtype=torch.int64, device=stats.device)
+        self.dist.all_reduce(cnt, op=self.dist.ReduceOp.SUM)
+        return stats, int(cnt.item())
 
     # -- pass 1 ------------------------------------------------------------------
     def find_min_max_abs(self):
         stats, n_img = self._local_min_max()
         t_comb = time.perf_counter()
         if self.dist is not None:
-            packed = torch.stack([-stats[:, 0], stats[:, 1]], dim=1).contiguous()
-            self.dist.all_reduce(packed, op=self.dist.ReduceOp.MAX)
-            stats = torch.stack([-packed[:, 0], packed[:, 1]], dim=1)
-            cnt = torch.tensor([n_img], dtype=torch.int64, device=stats.device)
-            self.dist.all_reduce(cnt, op=self.dist.ReduceOp.SUM)
-            n_img = int(cnt.item())
+            stats, n_img = self._combine_min_max(stats, n_img)
         self.num_samples = n_img
         host = stats.cpu().numpy()
         self.pass1_host_s["combine"] = time.perf_counter() - t_comb

@@ -245,27 +245,41 @@ __global__ void __launch_bounds__(1024) hist_multi_kernel(const StatDesc *__rest
     const float rw = fast ? __frcp_rn(d.width) : 0.0f;
     for (int j = threadIdx.x; j < bins; j += blockDim.x) s_h[j] = 0;
     __syncthreads();
-    auto take = [&](const float4 &v, size_t i) {
-      const float a[4] = {fabsf(v.x), fabsf(v.y), fabsf(v.z), fabsf(v.w)};
-      const int ch = dense ? 0 : (int)(i % d.vpp) * 4;
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        if (a[k] != 0.0f && (dense || ch + k < d.c)) {
-          // floor(f) <= bins - 1 is f < bins; for 0 <= f < 2^23 the round-down sum f + 2^23 carries floor(f) in its low
-          // mantissa bits: no rounding or conversion instruction of the (narrow) conversion pipe
-          const float q = fast ? quot_by_const(a[k], d.width, rw) : __fdiv_rn(a[k], d.width);
-          const float f = __fadd_rn(q, 0.5f);
-          if (f < top) atomicAdd(&s_h[__float_as_int(__fadd_rd(f, 8388608.0f)) - 0x4B000000], 1u);
+    // One value: branch-free up to the (predicated) shared-memory increment. A zero takes the arithmetic too and is
+    // dropped by the predicate, which costs less than a divergent branch per value.
+    auto one = [&](float x, bool in_range, auto quotient) {
+      const float a = fabsf(x);
+      // floor(f) <= bins - 1 is f < bins; for 0 <= f < 2^23 the round-down sum f + 2^23 carries floor(f) in its low
+      // mantissa bits: no rounding or conversion instruction of the (narrow) conversion pipe
+      const float f = __fadd_rn(quotient(a), 0.5f);
+      const int bin = __float_as_int(__fadd_rd(f, 8388608.0f)) - 0x4B000000;
+      if (in_range && a != 0.0f && f < top) atomicAdd(&s_h[bin], 1u);
+    };
+    auto sweep = [&](auto quotient) {
+      if (dense && d.nvec < 0x40000000ull) { // the usual case: every lane of every vector counts, 32-bit indices
+        const uint32_t n = (uint32_t)d.nvec, st = (uint32_t)stride;
+        uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+        for (; i + st < n; i += 2 * st) {
+          const float4 v0 = __ldg(x4 + i), v1 = __ldg(x4 + i + st);
+          one(v0.x, true, quotient); one(v0.y, true, quotient); one(v0.z, true, quotient); one(v0.w, true, quotient);
+          one(v1.x, true, quotient); one(v1.y, true, quotient); one(v1.z, true, quotient); one(v1.w, true, quotient);
+        }
+        for (; i < n; i += st) {
+          const float4 v = __ldg(x4 + i);
+          one(v.x, true, quotient); one(v.y, true, quotient); one(v.z, true, quotient); one(v.w, true, quotient);
+        }
+      } else {
+        for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < d.nvec; i += stride) {
+          const float4 v = __ldg(x4 + i);
+          const int ch = dense ? 0 : (int)(i % d.vpp) * 4;
+          one(v.x, dense || ch + 0 < d.c, quotient); one(v.y, dense || ch + 1 < d.c, quotient);
+          one(v.z, dense || ch + 2 < d.c, quotient); one(v.w, dense || ch + 3 < d.c, quotient);
         }
       }
     };
-    size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
-    for (; i + stride < d.nvec; i += 2 * stride) {
-      const float4 v0 = __ldg(x4 + i), v1 = __ldg(x4 + i + stride);
-      take(v0, i);
-      take(v1, i + stride);
-    }
-    for (; i < d.nvec; i += stride) take(__ldg(x4 + i), i);
+    const float w = d.width;
+    if (fast) sweep([=](float a) { return quot_by_const(a, w, rw); });
+    else sweep([=](float a) { return __fdiv_rn(a, w); });
     __syncthreads();
     unsigned long long *h = hist + (size_t)t * bins;
     for (int j = threadIdx.x; j < bins; j += blockDim.x)

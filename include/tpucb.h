@@ -139,10 +139,10 @@ int tpucb_interp_get_op_info(tpucb_interp *it, char *out, size_t cap, size_t *ne
 /* Options: "cuda_graph" (0/1, default 1): replay the op list as one CUDA graph.
  *          "pdl" (1 on, 0 off, -1 automatic = default): programmatic dependent launch between the op kernels; each
  *          kernel's launch and set-up (barriers, tensor memory) overlap the tail of the kernel before it, and it
- *          waits for that kernel's results before its first global access. Automatic: the first graph launch of a
+ *          waits for that kernel's results before its first global access. Automatic: the third graph launch of a
  *          module captures the op list both ways, replays each ten times and keeps the faster graph (the extra
- *          replays recompute the same results); launches outside the graph follow a rule (on for modules that move
- *          less than 10 MB per kernel on average).
+ *          replays recompute the same results); earlier launches, launches outside the graph and modules that move
+ *          48 MB or more per kernel follow a rule (on for modules that move less than 10 MB per kernel on average).
  *          "fuse_activations" (0/1, default 1; read by the next load_module): run each
  *          quant(INT8->BF16) -> slope-table activation -> quant(BF16->INT8) chain as one launch
  *          that still writes all three tensors.

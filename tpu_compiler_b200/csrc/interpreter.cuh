@@ -232,13 +232,15 @@ public:
   // It hides each kernel's launch and set-up behind its predecessor's tail, which pays while kernels are short
   // (INT8 ResNet-50: 10% fewer ms per launch at batch 1 to 16, 2% at 64) and costs once they are long (3% more at
   // batch 256, 4 to 6% more on the YOLOv4-style graph at every batch). No property of the op list predicts the sign,
-  // so in automatic mode the first graph launch of a module captures the op list both ways, replays each a few
+  // so in automatic mode the third graph launch of a module captures the op list both ways, replays each a few
   // times and keeps the faster graph (measure_pdl; the replays recompute the same results from the same inputs).
-  // Until then, and for launches outside the graph, a rule holds: on when the module moves less than 10 MB per
-  // kernel on average.
+  // Until then, for launches outside the graph and for modules of 48 MB or more per kernel a rule holds: on when
+  // the module moves less than 10 MB per kernel on average.
   int use_pdl = -1;
   bool pdl_auto = false;     // the choice in effect while use_pdl < 0
   bool pdl_measured = false; // ... and whether it comes from the measurement below or from the load-time rule
+  bool pdl_worth_measuring = false; // modules that move 48 MB or more per kernel keep the rule's "off" (3% at most)
+  int graph_launches = 0;
   cudaGraphExec_t capture_graph();
   void measure_pdl();
   // Self-test (option "selftest_lost_arrival", read by the next load_module): > 0 makes every INT8 tensor-core
@@ -1879,6 +1881,7 @@ inline void Interpreter::reset_module() {
   bind();
   invalidate_graph();
   pdl_measured = false;
+  graph_launches = 0;
   kernels.clear();
   for (auto &kv : tensors)
     if (kv.second->owns && kv.second->dev) cudaFree(kv.second->dev);
@@ -2062,6 +2065,7 @@ inline void Interpreter::finish_module() {
       launches += k->kernel_launches();
     }
     pdl_auto = launches > 0 && bytes / launches < 10e6;
+    pdl_worth_measuring = launches > 1 && bytes / launches < 48e6;
   }
   output_details.clear();
   for (auto &k : kernels)
@@ -2351,7 +2355,12 @@ inline void Interpreter::measure_pdl() {
 inline void Interpreter::launch_all() {
   bind();
   if (use_graph) {
-    if (!graph_exec && use_pdl < 0 && !pdl_measured && selftest_lost_arrival == 0 && !kernels.empty()) measure_pdl();
+    // automatic mode: measured at the module's third graph launch (a module that is launched once or twice, like the
+    // tuner's per-candidate modules, never pays for it) and only where the answer is open (pdl_worth_measuring)
+    if (use_pdl < 0 && !pdl_measured && pdl_worth_measuring && selftest_lost_arrival == 0 && ++graph_launches == 3) {
+      invalidate_graph();
+      measure_pdl();
+    }
     if (!graph_exec) graph_exec = capture_graph();
     TPUCB_CUDA(cudaGraphLaunch(graph_exec, stream));
   } else {

@@ -147,6 +147,25 @@ def test_conv_bf16(cfg):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("cfg", [dict(ic=32, oc=32, g=32, hw=14, k=3, s=1, p=1, relu=1), dict(ic=48, oc=48, g=48, hw=15, k=3, s=2, p=1, relu=0),
+                                 dict(ic=32, oc=64, g=4, hw=10, k=3, s=1, p=1, relu=1), dict(ic=24, oc=24, g=24, hw=9, k=5, s=1, p=2, relu=0),
+                                 dict(ic=16, oc=40, g=2, hw=8, k=1, s=1, p=0, relu=1)])
+def test_conv_bf16_grouped_and_depthwise(cfg):
+    """Grouped and depthwise BF16 convolutions (the direct kernel, fp32 accumulation) against the fp32-loop oracle."""
+    rng = np.random.default_rng(19)
+    ic, oc, g, hw, k, s, p = (cfg[x] for x in ("ic", "oc", "g", "hw", "k", "s", "p"))
+    oh = (hw + 2 * p - k) // s + 1
+    b = graphs.GraphBuilder(19, simulate=False)
+    b.op("input", "x", [], (2, ic, hw, hw), "BF16")
+    b.weight("w", _bf16(rng.normal(0, (2.0 / (ic // g * k * k)) ** 0.5, (oc, ic // g, k, k))))
+    b.weight("bias", rng.normal(0, 0.1, oc).astype(np.float32))
+    b.op("conv_2d", "y", ["x", "w", "bias"], (2, oc, oh, oh), "BF16", kh=k, kw=k, sh=s, sw=s, pt=p, pb=p, pl=p, pr=p,
+         dh=1, dw=1, g=g, do_relu=cfg["relu"], with_bias=1)
+    x = _bf16(rng.normal(0, 1, (2, ic, hw, hw)))
+    assert_bf16_ulp(run_both(b.text(), b.weights, {"x": x}, ["y"]))
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("cfg", [dict(m=4, c=512, hw=1, n=1000, relu=0), dict(m=2, c=64, hw=7, n=40, relu=1)])
 def test_fc_bf16(cfg):
     """BF16 inner product on the tensor cores against the fp32-loop oracle (result rounded to BF16)."""

@@ -228,6 +228,49 @@ __global__ void reduce_kernel(const void *__restrict__ in, void *__restrict__ ou
 __device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
 
+// Grouped and depthwise BF16 convolution (core/conv.cpp:90-98 with g > 1: the fp32 convolution of BF16-valued operands,
+// fp32 bias, ReLU, one BF16 rounding). One thread per output value, fp32 accumulation over (filter row, filter column,
+// input channel of the group); consecutive threads take consecutive output channels, so the stores and, for depthwise
+// layers, the loads are coalesced. Weights as fp32 [oc][kh][kw][ic / g].
+struct ConvBf16GroupArgs {
+  int n, ic, icp, ih, iw, oc, ocp, oh, ow, kh, kw, sh, sw, pt, pl, dh, dw, g, do_relu;
+};
+__global__ void conv_bf16_grouped_kernel(const uint16_t *__restrict__ in, const float *__restrict__ w,
+                                         const float *__restrict__ bias, uint16_t *__restrict__ out, ConvBf16GroupArgs a) {
+  pdl_prologue();
+  const int icg = a.ic / a.g, ocg = a.oc / a.g;
+  const size_t total = (size_t)a.n * a.oh * a.ow * a.ocp;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int o = (int)(i % a.ocp);
+    const size_t pix = i / a.ocp;
+    uint16_t r = 0;
+    if (o < a.oc) {
+      const int x = (int)(pix % a.ow);
+      const size_t t = pix / a.ow;
+      const int y = (int)(t % a.oh);
+      const int b = (int)(t / a.oh);
+      const int c0 = (o / ocg) * icg;
+      const float *wo = w + (size_t)o * a.kh * a.kw * icg;
+      float acc = 0.0f;
+      for (int kr = 0; kr < a.kh; ++kr) {
+        const int yy = y * a.sh - a.pt + kr * a.dh;
+        if (yy < 0 || yy >= a.ih) continue;
+        for (int ks = 0; ks < a.kw; ++ks) {
+          const int xx = x * a.sw - a.pl + ks * a.dw;
+          if (xx < 0 || xx >= a.iw) continue;
+          const uint16_t *src = in + (((size_t)b * a.ih + yy) * a.iw + xx) * a.icp + c0;
+          const float *wt = wo + (size_t)(kr * a.kw + ks) * icg;
+          for (int c = 0; c < icg; ++c) acc = fmaf(bf16_bits_to_f32(src[c]), wt[c], acc);
+        }
+      }
+      acc = __fadd_rn(acc, bias[o]);
+      if (a.do_relu && acc < 0.0f) acc = 0.0f;
+      r = f32_to_bf16_bits(acc);
+    }
+    out[i] = r;
+  }
+}
+
 struct EltwiseBf16Args {
   const uint4 *in[4];
   float coeff[4];

@@ -408,6 +408,19 @@ public:
       // BF16 graphs (core/conv.cpp:90-98: fp32 convolution of BF16-valued operands, fp32 bias, ReLU, BF16 rounding):
       // the tensor-core pipeline with BF16 operands and fp32 accumulators; every K size and pitch is in bytes.
       TPUCB_CHECK(in->dtype == DT_BF16, "conv %s: a BF16 convolution needs a BF16 input", op.name.c_str());
+      if (g.g > 1 && !g.ins_h && !g.ins_w && !in->padded_rows()) {
+        // grouped / depthwise: the direct kernel (conv_bf16_grouped_kernel); weights as fp32 [oc][kh][kw][ic / g]
+        std::vector<float> wt((size_t)g.oc * g.kh * g.kw * icg);
+        for (int o = 0; o < g.oc; ++o)
+          for (int c = 0; c < icg; ++c)
+            for (int t = 0; t < g.kh * g.kw; ++t)
+              wt[((size_t)o * g.kh * g.kw + t) * icg + c] = filt.data[((size_t)o * icg + c) * g.kh * g.kw + t];
+        bf16g_w_ = I.upload(wt);
+        bf16g_b_ = I.upload(bias);
+        bf16g_ = true;
+        alg_bytes = 2.0 * ((double)in->numel() + out->numel()) + 4.0 * (filt.data.size() + g.oc);
+        return;
+      }
       TPUCB_CHECK(g.g == 1 && !g.ins_h && !g.ins_w && !in->padded_rows() && g.pl <= 127 && g.pt <= 127 &&
                       (g.kw - 1) * g.dw <= 255 && (g.kh - 1) * g.dh <= 255,
                   "conv %s: BF16 convolution supports dense, ungrouped layers", op.name.c_str());
@@ -787,7 +800,13 @@ public:
     for (auto &pl : plans_) pl.split_src = nullptr;
   }
   void invoke(cudaStream_t s) override {
-    if (f32_) {
+    if (bf16g_) {
+      ConvBf16GroupArgs a{g_.n, g_.ic, in_->cp, g_.ih, g_.iw, g_.oc, out_->cp, g_.oh, g_.ow, g_.kh, g_.kw, g_.sh, g_.sw,
+                          g_.pt, g_.pl, g_.dh, g_.dw, g_.g, do_relu_};
+      const size_t total = (size_t)g_.n * g_.oh * g_.ow * out_->cp;
+      launch_k(conv_bf16_grouped_kernel, grid_for(total, 256, I_.sm_count), 256, 0, s, (const uint16_t *)in_->dev, bf16g_w_,
+               bf16g_b_, (uint16_t *)out_->dev, a);
+    } else if (f32_) {
       launch_conv2d_f32((const float *)in_->dev, f32_w_, f32_b_, (float *)out_->dev, g_, in_->cp, out_->cp, do_relu_,
                         s, I_.sm_count);
     } else if (dw_) {
@@ -823,12 +842,12 @@ public:
     }
   }
   int kernel_launches() const override {
-    if (f32_ || dw_) return 1;
+    if (f32_ || dw_ || bf16g_) return 1;
     int k = (int)stem_plans_.size();
     for (auto &pl : plans_) k += 1 + (pl.use_patch ? 1 : 0) + ((pl.tf32 && pl.split_src) ? 1 : 0);
     return k;
   }
-  bool is_tensor_core() const { return !f32_ && !dw_; }
+  bool is_tensor_core() const { return !f32_ && !dw_ && !bf16g_; }
   std::vector<ConvPlan> plans_;
   std::vector<StemPlan> stem_plans_;
 
@@ -841,6 +860,8 @@ private:
   DwArgs dwargs_;
   const int32_t *d_bias_ = nullptr, *d_mult_ = nullptr, *d_rsh_ = nullptr;
   const float *f32_w_ = nullptr, *f32_b_ = nullptr;
+  bool bf16g_ = false; // grouped / depthwise BF16 convolution on conv_bf16_grouped_kernel
+  const float *bf16g_w_ = nullptr, *bf16g_b_ = nullptr;
   const uint32_t *dw_wt_ = nullptr; // depthwise 3x3: weights packed for dwconv3x3_dp4a_kernel (null: the multiply-add kernel)
 };
 

@@ -16,6 +16,13 @@ collective is the max-reduce of the measured time.
 `roofline` : the tcgen05 convolution kernel (dominant kernel), per-launch CUDA-event times
            from an eager pass inside this run, against the measured dense tensor peak.
 `cpu_baseline` : the reference-faithful CPU path (oracle/cpu_path.py) on this host, all threads.
+Untimed for the headline, in the same line (skipped by --no-extras): `e2e_i8_input` (the end-to-end loop with input the
+caller has quantised), `e2e.h2d_ceiling_gbs` (plain pinned copies of the same bytes, all ranks at once), `c1_batch1`
+(the module at batch 1), `cpu_baseline_omp4`, `secondary` (MobileNet-v2 batch 32, the YOLOv4-style graph batch 8, the
+3x3 op sweep; rank 0) and, at every N, `calibration` (the calibration pass on 256 images per GPU and the check that N ranks
+together reproduce one rank's histograms and thresholds).
+`--workload mobilenet_v2|yolov4|resnet50_bf16|conv_sweep|calibration|tuner` measure the other graphs on their own;
+`--impl reference` times the CPU path of the same workload (rank 0 only under torchrun).
 """
 import argparse
 import json

@@ -143,6 +143,8 @@ int tpucb_interp_get_op_info(tpucb_interp *it, char *out, size_t cap, size_t *ne
  *          module captures the op list both ways, replays each ten times and keeps the faster graph (the extra
  *          replays recompute the same results); earlier launches, launches outside the graph and modules that move
  *          48 MB or more per kernel follow a rule (on for modules that move less than 10 MB per kernel on average).
+ *          "split_k" (0/1, default 1; read by the next load_module): INT8 convolutions and inner products with few
+ *          tiles and 24 K blocks or more share each tile among several CTAs (exact: int32 partial sums).
  *          "fuse_activations" (0/1, default 1; read by the next load_module): run each
  *          quant(INT8->BF16) -> slope-table activation -> quant(BF16->INT8) chain as one launch
  *          that still writes all three tensors.

@@ -77,6 +77,26 @@ def test_conv_sweep_point_full_rshift_range(relu):
     _conv_against_oracle(graphs.single_conv_i8(8, 128, 128, 28, 3, 1, 1, relu=relu, rshift_range=(0, 32), seed=2999))
 
 
+@pytest.mark.parametrize("n,c,hw,relu", [(1, 512, 7, True), (2, 1024, 5, False), (3, 384, 9, True)])
+def test_split_k_layers(n, c, hw, relu):
+    """Launches with few tiles and 24 K blocks or more share each tile among several CTAs (int32 partial sums added in
+    global memory, the CTA that completes a tile runs the epilogue). Exact against the oracle, equal to the unsplit
+    launch, and the same again on every graph replay (the workspace is left zero)."""
+    from tpu_compiler_b200 import module
+    model = graphs.single_conv_i8(n, c, c, hw, 3, 1, 1, relu=relu, rshift_range=(0, 32) if not relu else (14, 17),
+                                  seed=2700 + c)
+    exp = graph_runner.run(model.text, model.weights, {"x": model.meta["x"]})["conv"]
+    for split in (1, 0):
+        m = module(0)
+        m.set_option("split_k", split)
+        m.load_text(model.text, model.weights)
+        m.set_tensor("x", model.meta["x"])
+        for _ in range(4):
+            m.invoke()
+            assert np.array_equal(m.get_tensor("conv"), exp), "split_k=%d" % split
+        m.close()
+
+
 def _first_and_last_against_oracle(builder, batch, res, lo, seed):
     from tpu_compiler_b200 import module
     rng = np.random.default_rng(seed)

@@ -70,6 +70,14 @@ struct ConvGemmParams {
   // buffer back, so that the MMA issuer's wait for it runs out and the launch ends through its error path (status
   // kErrAccWait) with no copy in flight. 0 / 0 in every ordinary launch.
   int wait_rounds, lose_arrival;
+  // Split K (launches with fewer tiles than CTA slots and a long K, e.g. every layer of the last two stages at batch
+  // 1): split_k > 1 CTAs share a tile, each takes k_per K blocks, adds its int32 partial accumulator to `ws`
+  // ([tile][pixel column][channel lane], zero between launches) with red.global.add and counts itself in `ws_count`;
+  // the CTA whose count completes the tile (no CTA waits for another) reads the sums back, runs the ordinary epilogue
+  // on them and leaves `ws` and the counter zero again. Plain tiles only (not dual, INT8).
+  int split_k, k_per;
+  int32_t *ws;
+  unsigned int *ws_count;
 };
 
 namespace ptx {
@@ -458,7 +466,8 @@ __device__ __forceinline__ uint32_t transpose4x4(uint32_t w, const TransposeSel 
 template <int ACT, bool FAST, bool R1 = false>
 __device__ __forceinline__ void epilogue_channels_impl(const ConvGemmParams &p, uint32_t lane_addr, int8_t *out4,
                                                        bool ch4_ok, int m0, int half, int halves, int lane,
-                                                       const ChanConst &cc, const TransposeSel &ts, int ncols) {
+                                                       const ChanConst &cc, const TransposeSel &ts, int ncols,
+                                                       int32_t *ws_lane = nullptr) {
   constexpr int QACT = ACT == 3 ? 0 : ACT; // the fused add works on the plain (no activation) int8 result
   auto rq = [&](uint32_t a) { return FAST ? requant_fast<QACT, R1>((int32_t)a, cc, p) : requant_one<QACT>((int32_t)a, cc, p); };
   const int pj = lane & 3;
@@ -481,9 +490,22 @@ __device__ __forceinline__ void epilogue_channels_impl(const ConvGemmParams &p, 
       }
     }
     uint32_t acc0[16], acc1[16];
-    ptx::tcgen05_ld_x16(lane_addr + (uint32_t)colg, acc0);
-    ptx::tcgen05_ld_x16(lane_addr + (uint32_t)colg + 16u, acc1);
-    ptx::tcgen05_wait_ld();
+    if (ws_lane) {
+      // split K: the summed accumulators of all the tile's CTAs, [pixel column][128 channel lanes] in global memory;
+      // read past L1 (other SMs wrote them) and left zero for the next launch
+      int32_t *src = ws_lane + (size_t)colg * 128;
+#pragma unroll
+      for (int k = 0; k < 16; ++k) {
+        acc0[k] = (uint32_t)__ldcg(src + (size_t)k * 128);
+        acc1[k] = (uint32_t)__ldcg(src + (size_t)(16 + k) * 128);
+      }
+#pragma unroll
+      for (int k = 0; k < 32; ++k) __stcg(src + (size_t)k * 128, 0);
+    } else {
+      ptx::tcgen05_ld_x16(lane_addr + (uint32_t)colg, acc0);
+      ptx::tcgen05_ld_x16(lane_addr + (uint32_t)colg + 16u, acc1);
+      ptx::tcgen05_wait_ld();
+    }
     uint32_t w[8];
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
@@ -640,6 +662,7 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
   const uint32_t bar_w = base + 160;          // resident weights landed
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + 168);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(smem + 172);
+  volatile int *split_last = reinterpret_cast<volatile int *>(smem + 176); // split K: this CTA completes its tile
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -667,6 +690,8 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
   const int walk_m0 = (int)blockIdx.x / n_tiles, walk_n0 = (int)blockIdx.x % n_tiles;
   const int walk_dm = (int)gridDim.x / n_tiles, walk_dn = (int)gridDim.x % n_tiles;
   const int wait_rounds = p.wait_rounds > 0 ? p.wait_rounds : 1024;
+  // split K: a work item is (tile, K range); item = tile * split_k + range, one loop over items in every role
+  const int split_k = (BF16 || TF32 || p.split_k < 1) ? 1 : p.split_k;
 
   // Programmatic dependent launch: the next kernel of the stream may start its own set-up as soon as every CTA
   // of this launch has got here; this kernel in turn sets up its barriers and tensor memory while the
@@ -700,6 +725,7 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
   // From here on the kernel touches global memory: the previous kernel's writes must be complete and visible.
   pdl_wait();
   if (*abort_flag != 0) total_tiles = 0;
+  const int total_items = total_tiles * split_k;
 
   if (warp == 0) {
     // ---------------------------------------------------------------- producer
@@ -716,7 +742,15 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
                            kit / p.c_chunks, n0w);
       }
       int tm = walk_m0, tn = walk_n0;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+        int k_begin = 0, k_end = kTerms * k_iters;
+        if (split_k > 1) { // few items per CTA: the divisions do not matter here
+          const int tile = item / split_k;
+          tm = tile / n_tiles;
+          tn = tile - tm * n_tiles;
+          k_begin = (item - tile * split_k) * p.k_per;
+          k_end = min(k_iters, k_begin + p.k_per);
+        }
         const int m0 = tm * m_tile;
         const int n0 = tn * p.BN - (p.dual ? 64 : 0);
         tm += walk_dm;
@@ -747,7 +781,13 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
         // running (tap row, tap column, channel chunk) and ring (stage, phase) counters: this loop
         // is a single thread's instruction stream, so it carries no divisions
         int tap = 0, tr = 0, ts = 0, chunk = 0, term = 0;
-        for (int kit = 0; kit < kTerms * k_iters; ++kit, ++it) {
+        if (k_begin > 0) {
+          tap = k_begin / p.c_chunks;
+          chunk = k_begin - tap * p.c_chunks;
+          tr = tap / p.kw;
+          ts = tap - tr * p.kw;
+        }
+        for (int kit = k_begin; kit < k_end; ++kit, ++it) {
           const CUtensorMap *mapA = (TF32 && term == 0) ? &tmA2 : &tmA;
           const CUtensorMap *mapB = (TF32 && term == 1) ? &tmB2 : &tmB;
           if (it >= p.stages) {
@@ -839,7 +879,12 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
           ok = false;
         }
       }
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++t) {
+      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++t) {
+        int k_begin = 0, k_end = kTerms * k_iters;
+        if (split_k > 1) {
+          k_begin = (item % split_k) * p.k_per;
+          k_end = min(k_iters, k_begin + p.k_per);
+        }
         const int buf = t & 1;
         if (t >= 2) {
           // the epilogue must have drained this accumulator buffer (its previous use)
@@ -853,7 +898,7 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
         }
         const uint32_t d_tmem = tmem_base + (uint32_t)buf * acc_stride;
         uint32_t wres_lo = desc_w_lo; // weight-resident mode: descriptor (low word) of K block `kit`
-        for (int kit = 0; kit < kTerms * k_iters; ++kit, ++it) {
+        for (int kit = k_begin; kit < k_end; ++kit, ++it) {
           if (!ptx::mbar_try_wait(m_full, mph) && !ptx::mbar_wait_bounded(m_full, mph, abort_flag, wait_rounds)) {
             if (!*abort_flag) atomicExch(p.err, kErrFullWait);
             *abort_flag = 1;
@@ -863,7 +908,7 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
           ptx::tcgen05_fence_after();
           // transposed product: weights are the A operand (M = channels), activations B (N = pixels)
           const uint32_t w_lo = p.w_resident ? wres_lo : ring_lo + a_step;
-          const uint32_t acc_first = kit > 0 ? 1u : 0u;
+          const uint32_t acc_first = kit > k_begin ? 1u : 0u;
           if (!p.dual) {
             if (ksteps == 4) ptx::tcgen05_mma_i8_kblock<4, KIND>(d_tmem, w_lo, ring_lo, desc_hi, p.idesc, acc_first);
             else if (ksteps == 2) ptx::tcgen05_mma_i8_kblock<2, KIND>(d_tmem, w_lo, ring_lo, desc_hi, p.idesc, acc_first);
@@ -873,7 +918,7 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
             for (int sub = 0; sub < 2; ++sub) {
               const uint32_t a_lo = w_lo + (sub == 0 ? dual_step : 0u);
               const uint32_t b_lo = ring_lo + (uint32_t)sub * sub_step;
-              const uint32_t first = (kit > 0 || sub > 0) ? 1u : 0u;
+              const uint32_t first = (kit > k_begin || sub > 0) ? 1u : 0u;
               if (ksteps == 4) ptx::tcgen05_mma_i8_kblock<4, KIND>(d_tmem, a_lo, b_lo, desc_hi, p.idesc, first);
               else if (ksteps == 2) ptx::tcgen05_mma_i8_kblock<2, KIND>(d_tmem, a_lo, b_lo, desc_hi, p.idesc, first);
               else ptx::tcgen05_mma_i8_kblock<1, KIND>(d_tmem, a_lo, b_lo, desc_hi, p.idesc, first);
@@ -906,7 +951,13 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
     int t = 0;
     bool ok = true;
     int tm = walk_m0, tn = walk_n0;
-    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++t) {
+    for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++t) {
+      int tile = item;
+      if (split_k > 1) {
+        tile = item / split_k;
+        tm = tile / n_tiles;
+        tn = tile - tm * n_tiles;
+      }
       // dual mode: lanes 0..63 are the channels of the first 128 pixels, lanes 64..127 of the second
       const int ch_base = p.dual ? (quarter & 1) * 32 : quarter * 32;
       const int m0 = tm * m_tile + (p.dual ? 128 * (quarter >> 1) : 0);
@@ -934,9 +985,60 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
       }
       // the wait result may differ between lanes only on the error path; make it uniform
       ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
+      const bool split_item = !BF16 && !TF32 && split_k > 1;
+      if (!ok && !split_item) break; // (a split item still passes its two barriers, see below)
       ptx::tcgen05_fence_after();
       const int ch4 = n0 + ch_base + (lane >> 2) * 4;
+      int32_t *ws_lane = nullptr; // split K: this lane's channel column of the tile's partial-sum block
+      if (split_item) {
+        ws_lane = p.ws + (size_t)tile * (128 * 128) + quarter * 32 + lane;
+        if (ok && n0 + ch_base < p.n_valid && m0 < p.M_total) {
+          // this CTA's partial accumulator goes to the tile's block in global memory (one reduction per value,
+          // 128 contiguous bytes per warp and column)
+          const uint32_t lane_addr = tmem_base + (uint32_t)buf * acc_stride + ((uint32_t)(quarter * 32) << 16);
+          for (int colg = half * 32; colg < 128; colg += 32 * (kEpilogueWarps / 4)) {
+            if (m0 + colg >= p.M_total) break;
+            uint32_t a0[16], a1[16];
+            ptx::tcgen05_ld_x16(lane_addr + (uint32_t)colg, a0);
+            ptx::tcgen05_ld_x16(lane_addr + (uint32_t)colg + 16u, a1);
+            ptx::tcgen05_wait_ld();
+#pragma unroll
+            for (int k = 0; k < 16; ++k) {
+              atomicAdd(ws_lane + (size_t)(colg + k) * 128, (int)a0[k]);
+              atomicAdd(ws_lane + (size_t)(colg + 16 + k) * 128, (int)a1[k]);
+            }
+          }
+        }
+        // the accumulator buffer is free again
+        ptx::tcgen05_fence_before();
+        __syncwarp();
+        if (ok && lane == 0 && !p.lose_arrival)
+          asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_acc_empty + 8 * buf) : "memory");
+        // Count this CTA in once all of its epilogue warps have added their part; the CTA that completes the tile
+        // goes on to the epilogue proper, the others are done with it (nobody waits for another CTA). The two
+        // barriers are among the epilogue warps of this CTA only, and every one of them reaches both: a warp whose
+        // wait ran out has raised the abort flag before the first, the leader turns that into "stop" for all (2),
+        // so that no warp goes on to a barrier the others will not come to.
+        __threadfence();
+        asm volatile("bar.sync 1, %0;" ::"n"(32 * kEpilogueWarps) : "memory");
+        if (warp == 2 && lane == 0) {
+          int verdict = 2;
+          if (!*abort_flag) {
+            const unsigned int before = atomicAdd(p.ws_count + tile, 1u);
+            verdict = before == (unsigned int)(split_k - 1) ? 1 : 0;
+            if (verdict) p.ws_count[tile] = 0u; // ready for the next launch
+          }
+          *split_last = verdict;
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(32 * kEpilogueWarps) : "memory");
+        const int verdict = *split_last;
+        if (verdict == 2) {
+          ok = false;
+          break;
+        }
+        if (verdict == 0) continue;
+        __threadfence();
+      }
       if (n0 + ch_base < p.n_valid && m0 < p.M_total) { // warp-uniform: this lane quarter holds real outputs
         const uint32_t lane_addr = tmem_base + (uint32_t)buf * acc_stride + ((uint32_t)(quarter * 32) << 16);
         int8_t *out4 = p.out + (size_t)m0 * p.ldc + p.c_off + ch4;
@@ -953,13 +1055,14 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
           uint8_t *out_pair = reinterpret_cast<uint8_t *>(p.out) + (size_t)m0 * p.ldc + (size_t)(p.c_off + (ch & ~1)) * 2;
           if (p.act == 1) epilogue_channels_bf16<true>(p, lane_addr, out_pair, ch < p.n_valid, m0, half, kEpilogueWarps / 4, lane, bias_f);
           else epilogue_channels_bf16<false>(p, lane_addr, out_pair, ch < p.n_valid, m0, half, kEpilogueWarps / 4, lane, bias_f);
-        } else if (p.act == 1) epilogue_channels_impl<1, FAST>(p, lane_addr, out4, ch4_ok, m0, half, kEpilogueWarps / 4, lane, cc, ts, 128);
-        else if (p.act == 2) epilogue_channels_impl<2, FAST>(p, lane_addr, out4, ch4_ok, m0, half, kEpilogueWarps / 4, lane, cc, ts, 128);
+        } else if (p.act == 1) epilogue_channels_impl<1, FAST>(p, lane_addr, out4, ch4_ok, m0, half, kEpilogueWarps / 4, lane, cc, ts, 128, ws_lane);
+        else if (p.act == 2) epilogue_channels_impl<2, FAST>(p, lane_addr, out4, ch4_ok, m0, half, kEpilogueWarps / 4, lane, cc, ts, 128, ws_lane);
         else if (p.act == 3 && FAST && (p.fastq & 2)) epilogue_channels_impl<3, FAST, true>(p, lane_addr, out4, ch4_ok, m0, half, kEpilogueWarps / 4, lane, cc, ts, 128);
         else if (p.act == 3) epilogue_channels_impl<3, FAST>(p, lane_addr, out4, ch4_ok, m0, half, kEpilogueWarps / 4, lane, cc, ts, 128);
-        else if (FAST && (p.fastq & 2)) epilogue_channels_impl<0, FAST, true>(p, lane_addr, out4, ch4_ok, m0, half, kEpilogueWarps / 4, lane, cc, ts, 128);
-        else epilogue_channels_impl<0, FAST>(p, lane_addr, out4, ch4_ok, m0, half, kEpilogueWarps / 4, lane, cc, ts, 128);
+        else if (FAST && (p.fastq & 2)) epilogue_channels_impl<0, FAST, true>(p, lane_addr, out4, ch4_ok, m0, half, kEpilogueWarps / 4, lane, cc, ts, 128, ws_lane);
+        else epilogue_channels_impl<0, FAST>(p, lane_addr, out4, ch4_ok, m0, half, kEpilogueWarps / 4, lane, cc, ts, 128, ws_lane);
       }
+      if (ws_lane) continue; // split K: the accumulator buffer was handed back above
       // hand the accumulator buffer back to the MMA issuer
       ptx::tcgen05_fence_before();
       __syncwarp();

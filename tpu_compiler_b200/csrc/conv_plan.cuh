@@ -81,6 +81,7 @@ struct ConvPlan {
   ConvGemmParams p;
   dim3 grid;
   size_t smem = 0;
+  int ws_tiles = 0;  // split K: tiles of the partial-sum workspace (p.ws, p.ws_count), allocated by the op that owns the plan
   bool bf16 = false; // runs conv_gemm_bf16_kernel (K sizes and pitches in bytes, 2 per element)
   bool tf32 = false; // runs conv_gemm_tf32x3_kernel (fp32 operands, 4 bytes per element; three K passes)
   CUtensorMap tmA2, tmB2;           // tf32: remainder parts of the activations and of the weights
@@ -412,11 +413,44 @@ inline void finish_plan(ConvPlan &pl, int rows, int taps, int k_inner, int oc_pa
     grid = grid / n_tiles * n_tiles; // a CTA's channel tile must not change
     if (grid < n_tiles) grid = n_tiles;
   }
-  const long long iters_per_cta = ((total_tiles + grid - 1) / grid) * k_iters * (pl.tf32 ? 3 : 1);
+  // Split K: a launch with fewer tiles than CTA slots and a long K gives each tile to several CTAs (ConvGemmParams::
+  // split_k): at least six K blocks per CTA, at most sixteen CTAs per tile, no more CTAs than slots. The exchange
+  // through global memory costs about 3 us of latency (reductions, fence, count, read back) and a K block 0.4 us, so
+  // only layers of 24 K blocks or more are split (3x3 with 512 channels: 36 blocks, 16.4 -> 10.3 us at batch 1; with 16
+  // or 18 blocks the two forms measured equal, below that the split is slower). The weights are then not kept resident
+  // (a CTA needs only its own K range once).
+  p.split_k = 1;
+  p.k_per = k_iters;
+  if (conv_split_k_enabled() && !pl.tf32 && !pl.bf16 && !p.dual && k_iters >= 24 && total_tiles * 2 <= ctas_per_sm * sm_count) {
+    int want = (int)((ctas_per_sm * sm_count) / total_tiles);
+    if (want > 16) want = 16;
+    if (want > k_iters / 6) want = k_iters / 6;
+    if (want >= 2) {
+      p.k_per = (k_iters + want - 1) / want;
+      p.split_k = (k_iters + p.k_per - 1) / p.k_per;
+      if (p.split_k < 2) {
+        p.split_k = 1;
+        p.k_per = k_iters;
+      }
+    }
+  }
+  if (p.split_k > 1) {
+    if (p.w_resident) {
+      p.w_resident = 0;
+      stages = (int)((budget - kSmemHeader - 1024) / (a_bytes + b_bytes));
+      if (stages < 2) stages = 2;
+      if (stages > kMaxStages) stages = kMaxStages;
+    }
+    grid = (int)total_tiles * p.split_k;
+    pl.ws_tiles = (int)total_tiles;
+  }
+  const size_t stage_bytes_final = p.w_resident ? a_bytes : a_bytes + b_bytes;
+  const long long iters_per_cta = p.split_k > 1 ? p.k_per
+                                                : ((total_tiles + grid - 1) / grid) * k_iters * (pl.tf32 ? 3 : 1);
   if (stages > iters_per_cta) stages = (int)iters_per_cta;
   if (stages < 1) stages = 1;
   p.stages = stages;
-  pl.smem = kSmemHeader + 1024 + (p.w_resident ? w_all : 0) + stages * stage_bytes;
+  pl.smem = kSmemHeader + 1024 + (p.w_resident ? w_all : 0) + stages * stage_bytes_final;
   pl.grid = dim3((unsigned)grid, 1, 1);
 }
 

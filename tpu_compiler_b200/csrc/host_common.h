@@ -80,6 +80,12 @@ inline bool &launch_pdl_flag() {
   return on;
 }
 
+// Whether launch plans may split K over several CTAs (option "split_k" of the interpreter that builds them).
+inline bool &conv_split_k_enabled() {
+  static thread_local bool on = true;
+  return on;
+}
+
 #ifdef __CUDACC__
 // Launch of an op kernel. With the flag above the launch carries the programmatic stream serialisation
 // attribute: the kernel may be scheduled while its predecessor in the stream is still running and orders itself

@@ -121,6 +121,7 @@ public:
   void bind() {
     TPUCB_CUDA(cudaSetDevice(device_));
     launch_pdl_flag() = use_pdl < 0 ? pdl_auto : use_pdl != 0;
+    conv_split_k_enabled() = split_k && selftest_lost_arrival == 0; // the self-test needs tiles that follow one another in a CTA
   }
   int device() const { return device_; }
 
@@ -247,6 +248,19 @@ public:
   // convolution built from then on lose its accumulator hand-back and wait only that many rounds of 1024 polls
   // (ConvGemmParams::wait_rounds / lose_arrival), so that a launch ends with a bounded-wait error status.
   int selftest_lost_arrival = 0;
+  bool split_k = true; // set before load_module: launches with few tiles and a long K share each tile among CTAs
+  // partial-sum workspaces of the split-K plans (zero between launches; cleared again after a failed launch)
+  std::vector<std::pair<void *, size_t>> split_ws;
+  void attach_split_ws(ConvPlan &pl) {
+    if (pl.p.split_k <= 1) return;
+    const size_t bytes = (size_t)pl.ws_tiles * 128 * 128 * sizeof(int32_t), cbytes = (size_t)pl.ws_tiles * sizeof(unsigned int);
+    pl.p.ws = (int32_t *)dalloc(bytes);
+    pl.p.ws_count = (unsigned int *)dalloc(cbytes);
+    TPUCB_CUDA(cudaMemset(pl.p.ws, 0, bytes));
+    TPUCB_CUDA(cudaMemset(pl.p.ws_count, 0, cbytes));
+    split_ws.push_back({pl.p.ws, bytes});
+    split_ws.push_back({pl.p.ws_count, cbytes});
+  }
   bool fuse_activations = true; // set before load_module
   bool fuse_residual_add = false; // set before load_module: eltwise adds run in the producing convolution's epilogue
   bool fp32_tensor_cores = true; // set before load_module: fp32 convolutions as three TF32 products
@@ -464,6 +478,7 @@ public:
         encode_weight_map(&pl.tmB, d_wp, out->cp, 1, a.kp * 2, p.BK, p.dual ? 192 : p.BN);
         p.idesc = make_idesc_bf16(128, p.BN);
         pl.ops = alg_ops;
+        I.attach_split_ws(pl);
         plans_.push_back(pl);
         alg_bytes = 2.0 * ((double)in->numel() + out->numel() + filt.data.size()) + 4.0 * g.oc;
         return;
@@ -484,6 +499,7 @@ public:
       }
       p.idesc = make_idesc_bf16(128, p.BN);
       pl.ops = alg_ops;
+      I.attach_split_ws(pl);
       plans_.push_back(pl);
       alg_bytes = 2.0 * ((double)in->numel() + out->numel() + filt.data.size()) + 4.0 * g.oc;
       return;
@@ -537,6 +553,7 @@ public:
         encode_weight_map(&pl.tmB2, d_pl, out->cp, 1, kb, p.BK, p.BN);
         p.idesc = make_idesc_tf32(128, p.BN);
         pl.ops = alg_ops;
+        I.attach_split_ws(pl);
         plans_.push_back(pl);
         alg_bytes = 4.0 * ((double)in->numel() + out->numel() + filt.data.size() + g.oc);
         return;
@@ -590,6 +607,7 @@ public:
         encode_weight_map(&pl.tmB2, d_wl, out->cp, taps, k_bytes, p.BK, p.BN);
         p.idesc = make_idesc_tf32(128, p.BN);
         pl.ops = alg_ops;
+        I.attach_split_ws(pl);
         plans_.push_back(pl);
         alg_bytes = 4.0 * ((double)in->numel() + out->numel() + filt.data.size() + g.oc);
         return;
@@ -759,6 +777,7 @@ public:
         pl.p.wait_rounds = I.selftest_lost_arrival;
         pl.p.lose_arrival = 1;
       }
+      I.attach_split_ws(pl);
       plans_.push_back(pl);
     }
   }
@@ -777,7 +796,9 @@ public:
   }
   // Fused eltwise add (tensor-core INT8 plans without an activation of their own): the epilogue also forms
   // sat8(relu?((conv * ms + residual * mr + 2^(r-1)) >> r)) into `sum_out`; this op's own tensor is still written.
-  bool can_fuse_add() const { return can_fuse_leaky() && plans_.size() == 1 && in_->dtype == DT_I8; }
+  bool can_fuse_add() const {
+    return can_fuse_leaky() && plans_.size() == 1 && in_->dtype == DT_I8 && plans_[0].p.split_k <= 1;
+  }
   void set_residual_add(const int8_t *residual, int8_t *sum_out, int ms, int mr, int rshift, int relu) {
     for (auto &pl : plans_) {
       pl.p.act = 3;
@@ -920,6 +941,7 @@ public:
       encode_matrix_map(&pl.tmA, (const int8_t *)in->dev, m_, kdev_ * 2, kdev_ * 2, p.BK, a_tile_rows(p));
       encode_weight_map(&pl.tmB, d_w, n_pad, 1, kdev_ * 2, p.BK, p.dual ? 192 : p.BN);
       p.idesc = make_idesc_bf16(128, p.BN);
+      I.attach_split_ws(pl);
       plan_ = pl;
       alg_bytes = 2.0 * ((double)m_ * k_ + (double)n_ * k_ + (double)m_ * n_) + 4.0 * n_;
       return;
@@ -972,6 +994,7 @@ public:
     finish_plan(pl, m_, 1, kdev_, n_pad, I.sm_count);
     encode_matrix_map(&pl.tmA, (const int8_t *)in->dev, m_, kdev_, kdev_, p.BK, a_tile_rows(p));
     encode_weight_map(&pl.tmB, d_w, n_pad, 1, kdev_, p.BK, p.dual ? 192 : p.BN);
+    I.attach_split_ws(pl);
     plan_ = pl;
     alg_bytes = (double)m_ * k_ + (double)n_ * k_ + (double)m_ * n_ + 4.0 * n_ + 8;
   }
@@ -2425,6 +2448,7 @@ inline void Interpreter::sync_and_check() {
   TPUCB_CUDA(cudaMemcpy(&err, d_err, sizeof(int), cudaMemcpyDeviceToHost));
   if (err != 0) {
     TPUCB_CUDA(cudaMemset(d_err, 0, sizeof(int)));
+    for (auto &w : split_ws) TPUCB_CUDA(cudaMemset(w.first, 0, w.second)); // a failed launch may leave partial sums
     throw Error(strfmt("a convolution kernel gave up on a bounded wait (code %d: 1 = tile load never arrived, "
                        "2 = stage never freed, 3 = accumulator never completed or never handed back); the launch's "
                        "results are incomplete, the interpreter stays usable", err));

@@ -372,6 +372,8 @@ int tpucb_interp_set_option(tpucb_interp *it, const char *key, int value) {
   } else if (k == "selftest_lost_arrival") {
     TPUCB_CHECK(value >= 0 && value <= 1024, "selftest_lost_arrival: rounds must be in [0, 1024]");
     it->impl.selftest_lost_arrival = value; // takes effect at the next load_module
+  } else if (k == "split_k") {
+    it->impl.split_k = value != 0; // takes effect at the next load_module
   } else if (k == "fuse_activations") {
     it->impl.fuse_activations = value != 0; // takes effect at the next load_module
   } else if (k == "fuse_residual_add") {

@@ -463,7 +463,7 @@ __device__ __forceinline__ uint32_t transpose4x4(uint32_t w, const TransposeSel 
 //   out4       output address of (pixel m0, this lane's 4-channel group)
 //   ch4_ok     the 4-channel group lies inside the valid channels
 //   ncols      pixel columns of the accumulator buffer (128; 256 for the two-SM tile)
-template <int ACT, bool FAST, bool R1 = false>
+template <int ACT, bool FAST, bool R1 = false, bool FROM_WS = false>
 __device__ __forceinline__ void epilogue_channels_impl(const ConvGemmParams &p, uint32_t lane_addr, int8_t *out4,
                                                        bool ch4_ok, int m0, int half, int halves, int lane,
                                                        const ChanConst &cc, const TransposeSel &ts, int ncols,
@@ -490,7 +490,7 @@ __device__ __forceinline__ void epilogue_channels_impl(const ConvGemmParams &p, 
       }
     }
     uint32_t acc0[16], acc1[16];
-    if (ws_lane) {
+    if (FROM_WS) {
       // split K: the summed accumulators of all the tile's CTAs, [pixel column][128 channel lanes] in global memory;
       // read past L1 (other SMs wrote them) and left zero for the next launch
       int32_t *src = ws_lane + (size_t)colg * 128;
@@ -644,7 +644,7 @@ __device__ __forceinline__ void epilogue_channels_f32(const ConvGemmParams &p, u
 // terms come first: the tensor core truncates every partial sum at the accumulator's own precision, so each MMA
 // step costs up to an ulp of what has been accumulated so far, and only the steps of the last term see the
 // full magnitude (measured: the error against a double-accumulated convolution drops by the expected factor 3).
-template <bool BF16, bool FAST = true, bool TF32 = false>
+template <bool BF16, bool FAST = true, bool TF32 = false, bool SPLIT = false>
 __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUtensorMap &tmB, const ConvGemmParams &p,
                                                const CUtensorMap &tmA2, const CUtensorMap &tmB2) {
   constexpr int KIND = TF32 ? 2 : (BF16 ? 1 : 0);
@@ -691,7 +691,7 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
   const int walk_dm = (int)gridDim.x / n_tiles, walk_dn = (int)gridDim.x % n_tiles;
   const int wait_rounds = p.wait_rounds > 0 ? p.wait_rounds : 1024;
   // split K: a work item is (tile, K range); item = tile * split_k + range, one loop over items in every role
-  const int split_k = (BF16 || TF32 || p.split_k < 1) ? 1 : p.split_k;
+  const int split_k = (!SPLIT || p.split_k < 1) ? 1 : p.split_k; // SPLIT is a compile-time switch: the ordinary kernels carry none of it
 
   // Programmatic dependent launch: the next kernel of the stream may start its own set-up as soon as every CTA
   // of this launch has got here; this kernel in turn sets up its barriers and tensor memory while the
@@ -985,7 +985,7 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
       }
       // the wait result may differ between lanes only on the error path; make it uniform
       ok = __all_sync(0xffffffffu, ok);
-      const bool split_item = !BF16 && !TF32 && split_k > 1;
+      const bool split_item = SPLIT && split_k > 1;
       if (!ok && !split_item) break; // (a split item still passes its two barriers, see below)
       ptx::tcgen05_fence_after();
       const int ch4 = n0 + ch_base + (lane >> 2) * 4;
@@ -1055,14 +1055,14 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
           uint8_t *out_pair = reinterpret_cast<uint8_t *>(p.out) + (size_t)m0 * p.ldc + (size_t)(p.c_off + (ch & ~1)) * 2;
           if (p.act == 1) epilogue_channels_bf16<true>(p, lane_addr, out_pair, ch < p.n_valid, m0, half, kEpilogueWarps / 4, lane, bias_f);
           else epilogue_channels_bf16<false>(p, lane_addr, out_pair, ch < p.n_valid, m0, half, kEpilogueWarps / 4, lane, bias_f);
-        } else if (p.act == 1) epilogue_channels_impl<1, FAST>(p, lane_addr, out4, ch4_ok, m0, half, kEpilogueWarps / 4, lane, cc, ts, 128, ws_lane);
-        else if (p.act == 2) epilogue_channels_impl<2, FAST>(p, lane_addr, out4, ch4_ok, m0, half, kEpilogueWarps / 4, lane, cc, ts, 128, ws_lane);
+        } else if (p.act == 1) epilogue_channels_impl<1, FAST, false, SPLIT>(p, lane_addr, out4, ch4_ok, m0, half, kEpilogueWarps / 4, lane, cc, ts, 128, ws_lane);
+        else if (p.act == 2) epilogue_channels_impl<2, FAST, false, SPLIT>(p, lane_addr, out4, ch4_ok, m0, half, kEpilogueWarps / 4, lane, cc, ts, 128, ws_lane);
         else if (p.act == 3 && FAST && (p.fastq & 2)) epilogue_channels_impl<3, FAST, true>(p, lane_addr, out4, ch4_ok, m0, half, kEpilogueWarps / 4, lane, cc, ts, 128);
         else if (p.act == 3) epilogue_channels_impl<3, FAST>(p, lane_addr, out4, ch4_ok, m0, half, kEpilogueWarps / 4, lane, cc, ts, 128);
-        else if (FAST && (p.fastq & 2)) epilogue_channels_impl<0, FAST, true>(p, lane_addr, out4, ch4_ok, m0, half, kEpilogueWarps / 4, lane, cc, ts, 128, ws_lane);
-        else epilogue_channels_impl<0, FAST>(p, lane_addr, out4, ch4_ok, m0, half, kEpilogueWarps / 4, lane, cc, ts, 128, ws_lane);
+        else if (FAST && (p.fastq & 2)) epilogue_channels_impl<0, FAST, true, SPLIT>(p, lane_addr, out4, ch4_ok, m0, half, kEpilogueWarps / 4, lane, cc, ts, 128, ws_lane);
+        else epilogue_channels_impl<0, FAST, false, SPLIT>(p, lane_addr, out4, ch4_ok, m0, half, kEpilogueWarps / 4, lane, cc, ts, 128, ws_lane);
       }
-      if (ws_lane) continue; // split K: the accumulator buffer was handed back above
+      if (SPLIT && ws_lane) continue; // split K: the accumulator buffer was handed back above
       // hand the accumulator buffer back to the MMA issuer
       ptx::tcgen05_fence_before();
       __syncwarp();
@@ -1084,6 +1084,14 @@ __global__ void __launch_bounds__(kConvThreads, 2)
 conv_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const ConvGemmParams p) {
   conv_gemm_body<false, true>(tmA, tmB, p, tmA, tmB);
+}
+// The split-K form of both (ConvGemmParams::split_k > 1): a kernel of its own, so that the ordinary ones carry none of
+// its code (with the switch at run time the epilogue-bound layers were 14% slower).
+template <bool FAST>
+__global__ void __launch_bounds__(kConvThreads, 2)
+conv_gemm_i8_split_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                          const ConvGemmParams p) {
+  conv_gemm_body<false, FAST, false, true>(tmA, tmB, p, tmA, tmB);
 }
 // the same with the 64-bit multiply-add requantisation (requant_one), for layers outside requant_fast's domain
 __global__ void __launch_bounds__(kConvThreads, 2)

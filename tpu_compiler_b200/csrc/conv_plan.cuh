@@ -477,6 +477,8 @@ inline void launch_conv_plan(const ConvPlan &pl, cudaStream_t stream, int sm_cou
         reinterpret_cast<float4 *>(pl.split_lo), pl.split_nvec);
     launch_k(conv_gemm_tf32x3_kernel, pl.grid, threads, pl.smem, stream, pl.tmA, pl.tmB, pl.tmA2, pl.tmB2, pl.p);
   } else if (pl.bf16) launch_k(conv_gemm_bf16_kernel, pl.grid, threads, pl.smem, stream, pl.tmA, pl.tmB, pl.p);
+  else if (pl.p.split_k > 1 && (pl.p.fastq & 1)) launch_k(conv_gemm_i8_split_kernel<true>, pl.grid, threads, pl.smem, stream, pl.tmA, pl.tmB, pl.p);
+  else if (pl.p.split_k > 1) launch_k(conv_gemm_i8_split_kernel<false>, pl.grid, threads, pl.smem, stream, pl.tmA, pl.tmB, pl.p);
   else if (!(pl.p.fastq & 1)) launch_k(conv_gemm_i8_wide_kernel, pl.grid, threads, pl.smem, stream, pl.tmA, pl.tmB, pl.p);
   else launch_k(conv_gemm_i8_kernel, pl.grid, threads, pl.smem, stream, pl.tmA, pl.tmB, pl.p);
 }
@@ -484,6 +486,10 @@ inline void launch_conv_plan(const ConvPlan &pl, cudaStream_t stream, int sm_cou
 inline void conv_kernel_setup_once() {
   static bool done = [] {
     TPUCB_CUDA(cudaFuncSetAttribute(conv_gemm_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    227 * 1024));
+    TPUCB_CUDA(cudaFuncSetAttribute(conv_gemm_i8_split_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    227 * 1024));
+    TPUCB_CUDA(cudaFuncSetAttribute(conv_gemm_i8_split_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     227 * 1024));
     TPUCB_CUDA(cudaFuncSetAttribute(conv_gemm_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     227 * 1024));

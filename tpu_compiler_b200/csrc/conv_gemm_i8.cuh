@@ -644,7 +644,7 @@ __device__ __forceinline__ void epilogue_channels_f32(const ConvGemmParams &p, u
 // terms come first: the tensor core truncates every partial sum at the accumulator's own precision, so each MMA
 // step costs up to an ulp of what has been accumulated so far, and only the steps of the last term see the
 // full magnitude (measured: the error against a double-accumulated convolution drops by the expected factor 3).
-template <bool BF16, bool FAST = true, bool TF32 = false, bool SPLIT = false>
+template <bool BF16, bool FAST = true, bool TF32 = false, bool SPLIT = false, int ACTSEL = -1>
 __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUtensorMap &tmB, const ConvGemmParams &p,
                                                const CUtensorMap &tmA2, const CUtensorMap &tmB2) {
   constexpr int KIND = TF32 ? 2 : (BF16 ? 1 : 0);
@@ -1055,6 +1055,10 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
           uint8_t *out_pair = reinterpret_cast<uint8_t *>(p.out) + (size_t)m0 * p.ldc + (size_t)(p.c_off + (ch & ~1)) * 2;
           if (p.act == 1) epilogue_channels_bf16<true>(p, lane_addr, out_pair, ch < p.n_valid, m0, half, kEpilogueWarps / 4, lane, bias_f);
           else epilogue_channels_bf16<false>(p, lane_addr, out_pair, ch < p.n_valid, m0, half, kEpilogueWarps / 4, lane, bias_f);
+        } else if (ACTSEL == 1) { // kernels specialised for one epilogue (ACTSEL: 1 = ReLU, 10 = none with every rshift >= 1)
+          epilogue_channels_impl<1, FAST, false, SPLIT>(p, lane_addr, out4, ch4_ok, m0, half, kEpilogueWarps / 4, lane, cc, ts, 128, ws_lane);
+        } else if (ACTSEL == 10) {
+          epilogue_channels_impl<0, FAST, true, SPLIT>(p, lane_addr, out4, ch4_ok, m0, half, kEpilogueWarps / 4, lane, cc, ts, 128, ws_lane);
         } else if (p.act == 1) epilogue_channels_impl<1, FAST, false, SPLIT>(p, lane_addr, out4, ch4_ok, m0, half, kEpilogueWarps / 4, lane, cc, ts, 128, ws_lane);
         else if (p.act == 2) epilogue_channels_impl<2, FAST, false, SPLIT>(p, lane_addr, out4, ch4_ok, m0, half, kEpilogueWarps / 4, lane, cc, ts, 128, ws_lane);
         else if (p.act == 3 && FAST && (p.fastq & 2)) epilogue_channels_impl<3, FAST, true>(p, lane_addr, out4, ch4_ok, m0, half, kEpilogueWarps / 4, lane, cc, ts, 128);
@@ -1084,6 +1088,14 @@ __global__ void __launch_bounds__(kConvThreads, 2)
 conv_gemm_i8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const ConvGemmParams p) {
   conv_gemm_body<false, true>(tmA, tmB, p, tmA, tmB);
+}
+// The two epilogues that carry most launches as kernels of their own (ReLU; no activation with every rshift >= 1):
+// the compiler allocates registers and schedules for that one epilogue instead of for all of them.
+template <int ACTSEL>
+__global__ void __launch_bounds__(kConvThreads, 2)
+conv_gemm_i8_act_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                        const ConvGemmParams p) {
+  conv_gemm_body<false, true, false, false, ACTSEL>(tmA, tmB, p, tmA, tmB);
 }
 // The split-K form of both (ConvGemmParams::split_k > 1): a kernel of its own, so that the ordinary ones carry none of
 // its code (with the switch at run time the epilogue-bound layers were 14% slower).

@@ -314,6 +314,7 @@ struct StemPlan {
 inline void stem_kernel_setup_once() {
   static bool done = [] {
     TPUCB_CUDA(cudaFuncSetAttribute(conv_stem_i8_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+    TPUCB_CUDA(cudaFuncSetAttribute(conv_stem_i8_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
     TPUCB_CUDA(cudaFuncSetAttribute(conv_stem_i8_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
     return true;
   }();
@@ -479,6 +480,8 @@ inline void launch_conv_plan(const ConvPlan &pl, cudaStream_t stream, int sm_cou
   } else if (pl.bf16) launch_k(conv_gemm_bf16_kernel, pl.grid, threads, pl.smem, stream, pl.tmA, pl.tmB, pl.p);
   else if (pl.p.split_k > 1 && (pl.p.fastq & 1)) launch_k(conv_gemm_i8_split_kernel<true>, pl.grid, threads, pl.smem, stream, pl.tmA, pl.tmB, pl.p);
   else if (pl.p.split_k > 1) launch_k(conv_gemm_i8_split_kernel<false>, pl.grid, threads, pl.smem, stream, pl.tmA, pl.tmB, pl.p);
+  else if ((pl.p.fastq & 1) && pl.p.act == 1) launch_k(conv_gemm_i8_act_kernel<1>, pl.grid, threads, pl.smem, stream, pl.tmA, pl.tmB, pl.p);
+  else if ((pl.p.fastq & 3) == 3 && pl.p.act == 0) launch_k(conv_gemm_i8_act_kernel<10>, pl.grid, threads, pl.smem, stream, pl.tmA, pl.tmB, pl.p);
   else if (!(pl.p.fastq & 1)) launch_k(conv_gemm_i8_wide_kernel, pl.grid, threads, pl.smem, stream, pl.tmA, pl.tmB, pl.p);
   else launch_k(conv_gemm_i8_kernel, pl.grid, threads, pl.smem, stream, pl.tmA, pl.tmB, pl.p);
 }
@@ -487,6 +490,8 @@ inline void conv_kernel_setup_once() {
   static bool done = [] {
     TPUCB_CUDA(cudaFuncSetAttribute(conv_gemm_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     227 * 1024));
+    TPUCB_CUDA(cudaFuncSetAttribute(conv_gemm_i8_act_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    TPUCB_CUDA(cudaFuncSetAttribute(conv_gemm_i8_act_kernel<10>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     TPUCB_CUDA(cudaFuncSetAttribute(conv_gemm_i8_split_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     227 * 1024));
     TPUCB_CUDA(cudaFuncSetAttribute(conv_gemm_i8_split_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,

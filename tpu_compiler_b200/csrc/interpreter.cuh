@@ -857,7 +857,9 @@ public:
                                                                           (int8_t *)out_->dev, dwargs_);
     } else {
       for (auto &sp : stem_plans_)
-        if (sp.p.fastq & 1) launch_k(conv_stem_i8_kernel<true>, sp.grid, kStemThreads, sp.smem, s, sp.tmB, sp.p);
+        if ((sp.p.fastq & 1) && sp.p.act == 1) // the ReLU epilogue alone: most stems
+          launch_k(conv_stem_i8_kernel<true, true>, sp.grid, kStemThreads, sp.smem, s, sp.tmB, sp.p);
+        else if (sp.p.fastq & 1) launch_k(conv_stem_i8_kernel<true>, sp.grid, kStemThreads, sp.smem, s, sp.tmB, sp.p);
         else launch_k(conv_stem_i8_kernel<false>, sp.grid, kStemThreads, sp.smem, s, sp.tmB, sp.p);
       for (auto &pl : plans_) launch_conv_plan(pl, s, I_.sm_count);
     }

@@ -734,7 +734,8 @@ def main():
                                         "batch / 64, plus the algorithmic output bytes (ncu attributes no write-back to "
                                         "the kernel); not captured in this run. Algorithmic bytes per launch: %.1f MB"
                                         % (conv_bytes / max(n_conv, 1) / 1e6),
-                        "kernel": "conv_gemm_i8_kernel (tcgen05 kind::i8 implicit GEMM, %d launches per step)" % n_conv,
+                        "kernel": "conv_gemm_i8_act_kernel<1> / <10> and conv_stem_i8_kernel: the tcgen05 kind::i8 implicit GEMM of "
+                                  "conv_gemm_i8.cuh in its ReLU and plain instantiations, %d launches per step" % n_conv,
                         "peak_source": "2 x bf16_tflops_sustained of %s peaks (no INT8 figure is measured; the 8-bit "
                                        "rate of the same tensor pipe is twice the 16-bit rate)" % peaks["source"],
                         "avg_launch_us": conv_ms * 1e3 / max(n_conv, 1),

@@ -99,6 +99,20 @@ def deconv2d_i8(x, w, bias, rshift, multiplier, out_hw, stride=(1, 1), pad=(0, 0
     return out
 
 
+def deconv2d_f(x, w, bias, out_hw, stride=(1, 1), pad=(0, 0), dilation=(1, 1), groups=1, do_relu=False, to_bf16=False):
+    """core/deconv.cpp DeConv2DOpKernel::invoke, fp32 and BF16 graphs. x [n,ic,ih,iw], w [oc,ic/g,kh,kw]."""
+    x, w = _f32(x), _f32(w)
+    n, ic, ih, iw = x.shape
+    oc, _, kh, kw = w.shape
+    oh, ow = out_hw
+    out = np.empty((n, oc, oh, ow), np.float32)
+    bias = _f32(bias) if bias is not None else None
+    lib().orc_deconv2d_f(_p(x), _p(w), _p(bias) if bias is not None else None, _p(out), n, ic, ih, iw, oc, oh, ow, groups,
+                         kh, kw, stride[0], stride[1], pad[0], pad[1], dilation[0], dilation[1], int(do_relu),
+                         int(to_bf16))
+    return out
+
+
 def fc(x, w, bias, rshift, multiplier, do_relu=False, mode="INT8"):
     """core/fullyconnected.cpp. x [batch?, m, k] or [m,k]; w [n,k]."""
     x, w = _f32(x), _f32(w)

@@ -66,6 +66,11 @@ def run(text, weights, inputs, upto=None):
                            stride=(_i(a, "sh", 1), _i(a, "sw", 1)), pad=(_i(a, "pt"), _i(a, "pl")),
                            dilation=(_i(a, "dh", 1), _i(a, "dw", 1)), groups=_i(a, "g", 1),
                            ins=(_i(a, "ins_h"), _i(a, "ins_w")), do_relu=bool(_i(a, "do_relu")), mode=mode)
+        elif t == "deconv_2d" and op["dtype"] != "INT8":
+            out = O.deconv2d_f(X(0), W(1), W(2),
+                               (op["shape"][2], op["shape"][3]), stride=(_i(a, "sh", 1), _i(a, "sw", 1)),
+                               pad=(_i(a, "pt"), _i(a, "pl")), dilation=(_i(a, "dh", 1), _i(a, "dw", 1)),
+                               groups=_i(a, "g", 1), do_relu=bool(_i(a, "do_relu")), to_bf16=(op["dtype"] == "BF16"))
         elif t == "deconv_2d":
             out = O.deconv2d_i8(X(0), W(1), W(2), W(5), W(6), (op["shape"][2], op["shape"][3]),
                                 stride=(_i(a, "sh", 1), _i(a, "sw", 1)), pad=(_i(a, "pt"), _i(a, "pl")),

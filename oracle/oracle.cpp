@@ -843,6 +843,41 @@ void orc_deconv2d_i8(const float *in, const float *filter, const float *bias, co
       }
 }
 
+// The same scatter for fp32 and BF16 graphs (core/deconv.cpp:56-68: MKL-DNN deconvolution with the fp32 bias, ReLU,
+// and for BF16 one rounding of the result). Sums in double: the order of MKL-DNN's own sum is not known.
+void orc_deconv2d_f(const float *in, const float *filter, const float *bias, float *out, int n, int ic, int ih, int iw,
+                    int oc, int oh, int ow, int g, int kh, int kw, int sh, int sw, int pt, int pl, int dh, int dw,
+                    int do_relu, int to_bf16) {
+  const int icg = ic / g, ocg = oc / g;
+  std::vector<double> acc((size_t)n * oc * oh * ow, 0.0);
+  for (int b = 0; b < n; ++b)
+    for (int o = 0; o < oc; ++o) {
+      const int grp = o / ocg;
+      for (int c = 0; c < icg; ++c)
+        for (int y = 0; y < ih; ++y)
+          for (int x = 0; x < iw; ++x) {
+            const double a = in[(((size_t)b * ic + grp * icg + c) * ih + y) * iw + x];
+            for (int r = 0; r < kh; ++r) {
+              const int oy = y * sh + r * dh - pt;
+              if (oy < 0 || oy >= oh) continue;
+              for (int q = 0; q < kw; ++q) {
+                const int ox = x * sw + q * dw - pl;
+                if (ox < 0 || ox >= ow) continue;
+                acc[(((size_t)b * oc + o) * oh + oy) * ow + ox] += a * (double)filter[(((size_t)o * icg + c) * kh + r) * kw + q];
+              }
+            }
+          }
+    }
+  for (int b = 0; b < n; ++b)
+    for (int o = 0; o < oc; ++o)
+      for (int i = 0; i < oh * ow; ++i) {
+        const size_t oi = ((size_t)b * oc + o) * oh * ow + i;
+        float v = (float)(acc[oi] + (bias ? (double)bias[o] : 0.0));
+        if (do_relu && v < 0) v = 0;
+        out[oi] = to_bf16 ? orc_bf16(v, 1) : v;
+      }
+}
+
 // MatMul of two activations (core/matmul.cpp:33-97; dimensions per TPUOperationSupport.cpp:615-655).
 // The transposes only change where element (batch, row, col) is stored: [bh, rows, bl, cols] instead of
 // [bh, bl, rows, cols]. mode 0 INT8 (QDM requant unless multiplier and rshift are both 0), 1 fp32, 2 BF16.

@@ -166,6 +166,25 @@ def test_conv_bf16_grouped_and_depthwise(cfg):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("cfg", [dict(ic=16, oc=32, g=1, hw=7, k=2, s=2, p=0, relu=0), dict(ic=24, oc=16, g=1, hw=6, k=4, s=2, p=1, relu=1),
+                                 dict(ic=32, oc=32, g=32, hw=5, k=3, s=2, p=1, relu=0), dict(ic=8, oc=24, g=2, hw=9, k=3, s=1, p=1, relu=1)])
+def test_deconv_bf16(cfg):
+    """BF16 deconvolution (the direct kernel over the zero-inserted input with the flipped filter) against the scatter
+    form of the oracle."""
+    rng = np.random.default_rng(23)
+    ic, oc, g, hw, k, s, p = (cfg[x] for x in ("ic", "oc", "g", "hw", "k", "s", "p"))
+    oh = (hw - 1) * s + k - 2 * p
+    b = graphs.GraphBuilder(23, simulate=False)
+    b.op("input", "x", [], (2, ic, hw, hw), "BF16")
+    b.weight("w", _bf16(rng.normal(0, (2.0 / (ic // g * k * k)) ** 0.5, (oc, ic // g, k, k))))
+    b.weight("bias", rng.normal(0, 0.1, oc).astype(np.float32))
+    b.op("deconv_2d", "y", ["x", "w", "bias"], (2, oc, oh, oh), "BF16", kh=k, kw=k, sh=s, sw=s, pt=p, pb=p, pl=p, pr=p,
+         dh=1, dw=1, g=g, do_relu=cfg["relu"], with_bias=1)
+    x = _bf16(rng.normal(0, 1, (2, ic, hw, hw)))
+    assert_bf16_ulp(run_both(b.text(), b.weights, {"x": x}, ["y"]))
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("cfg", [dict(m=4, c=512, hw=1, n=1000, relu=0), dict(m=2, c=64, hw=7, n=40, relu=1)])
 def test_fc_bf16(cfg):
     """BF16 inner product on the tensor cores against the fp32-loop oracle (result rounded to BF16)."""

@@ -229,11 +229,12 @@ __device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w 
 __device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
 
 // Grouped and depthwise BF16 convolution (core/conv.cpp:90-98 with g > 1: the fp32 convolution of BF16-valued operands,
-// fp32 bias, ReLU, one BF16 rounding). One thread per output value, fp32 accumulation over (filter row, filter column,
-// input channel of the group); consecutive threads take consecutive output channels, so the stores and, for depthwise
-// layers, the loads are coalesced. Weights as fp32 [oc][kh][kw][ic / g].
+// fp32 bias, ReLU, one BF16 rounding) and, through input insertion (ins_h / ins_w zeros between the input pixels), the
+// BF16 deconvolution (core/deconv.cpp:56-68). One thread per output value, fp32 accumulation over (filter row, filter
+// column, input channel of the group); consecutive threads take consecutive output channels, so the stores and, for
+// depthwise layers, the loads are coalesced. Weights as fp32 [oc][kh][kw][ic / g].
 struct ConvBf16GroupArgs {
-  int n, ic, icp, ih, iw, oc, ocp, oh, ow, kh, kw, sh, sw, pt, pl, dh, dw, g, do_relu;
+  int n, ic, icp, ih, iw, oc, ocp, oh, ow, kh, kw, sh, sw, pt, pl, dh, dw, g, do_relu, ins_h, ins_w;
 };
 __global__ void conv_bf16_grouped_kernel(const uint16_t *__restrict__ in, const float *__restrict__ w,
                                          const float *__restrict__ bias, uint16_t *__restrict__ out, ConvBf16GroupArgs a) {
@@ -253,11 +254,15 @@ __global__ void conv_bf16_grouped_kernel(const uint16_t *__restrict__ in, const 
       const float *wo = w + (size_t)o * a.kh * a.kw * icg;
       float acc = 0.0f;
       for (int kr = 0; kr < a.kh; ++kr) {
-        const int yy = y * a.sh - a.pt + kr * a.dh;
-        if (yy < 0 || yy >= a.ih) continue;
+        int yy = y * a.sh - a.pt + kr * a.dh; // row of the zero-inserted input
+        if (yy < 0 || yy % (a.ins_h + 1) != 0) continue;
+        yy /= a.ins_h + 1;
+        if (yy >= a.ih) continue;
         for (int ks = 0; ks < a.kw; ++ks) {
-          const int xx = x * a.sw - a.pl + ks * a.dw;
-          if (xx < 0 || xx >= a.iw) continue;
+          int xx = x * a.sw - a.pl + ks * a.dw;
+          if (xx < 0 || xx % (a.ins_w + 1) != 0) continue;
+          xx /= a.ins_w + 1;
+          if (xx >= a.iw) continue;
           const uint16_t *src = in + (((size_t)b * a.ih + yy) * a.iw + xx) * a.icp + c0;
           const float *wt = wo + (size_t)(kr * a.kw + ks) * icg;
           for (int c = 0; c < icg; ++c) acc = fmaf(bf16_bits_to_f32(src[c]), wt[c], acc);

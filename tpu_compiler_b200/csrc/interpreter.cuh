@@ -422,8 +422,9 @@ public:
       // BF16 graphs (core/conv.cpp:90-98: fp32 convolution of BF16-valued operands, fp32 bias, ReLU, BF16 rounding):
       // the tensor-core pipeline with BF16 operands and fp32 accumulators; every K size and pitch is in bytes.
       TPUCB_CHECK(in->dtype == DT_BF16, "conv %s: a BF16 convolution needs a BF16 input", op.name.c_str());
-      if (g.g > 1 && !g.ins_h && !g.ins_w && !in->padded_rows()) {
-        // grouped / depthwise: the direct kernel (conv_bf16_grouped_kernel); weights as fp32 [oc][kh][kw][ic / g]
+      if ((g.g > 1 || g.ins_h || g.ins_w) && !in->padded_rows()) {
+        // grouped / depthwise layers and deconvolutions (input insertion): the direct kernel
+        // (conv_bf16_grouped_kernel); weights as fp32 [oc][kh][kw][ic / g]
         std::vector<float> wt((size_t)g.oc * g.kh * g.kw * icg);
         for (int o = 0; o < g.oc; ++o)
           for (int c = 0; c < icg; ++c)
@@ -823,7 +824,7 @@ public:
   void invoke(cudaStream_t s) override {
     if (bf16g_) {
       ConvBf16GroupArgs a{g_.n, g_.ic, in_->cp, g_.ih, g_.iw, g_.oc, out_->cp, g_.oh, g_.ow, g_.kh, g_.kw, g_.sh, g_.sw,
-                          g_.pt, g_.pl, g_.dh, g_.dw, g_.g, do_relu_};
+                          g_.pt, g_.pl, g_.dh, g_.dw, g_.g, do_relu_, g_.ins_h, g_.ins_w};
       const size_t total = (size_t)g_.n * g_.oh * g_.ow * out_->cp;
       launch_k(conv_bf16_grouped_kernel, grid_for(total, 256, I_.sm_count), 256, 0, s, (const uint16_t *)in_->dev, bf16g_w_,
                bf16g_b_, (uint16_t *)out_->dev, a);
@@ -2014,7 +2015,7 @@ inline int Interpreter::add_op(const ParsedOp &op_in) {
       //   dst[oh = ih*sh + kh*dh - pt] += src[ih] * w[kh]
       // equals a stride-1 convolution of the zero-inserted input (sh-1 zeros between pixels) with the
       // spatially flipped filter and padding dh*(kh-1) - pt, which is what the convolution op runs.
-      TPUCB_CHECK(dt == DT_I8, "deconv_2d %s: only INT8 is implemented", op.name.c_str());
+      TPUCB_CHECK(dt == DT_I8 || dt == DT_BF16, "deconv_2d %s: INT8 and BF16 are implemented", op.name.c_str());
       TPUCB_CHECK(op.in.size() >= 2 && has_weight(op.in[1]), "deconv_2d %s: filter operand missing", op.name.c_str());
       const int kh = op.geti("kh", 1), kw = op.geti("kw", 1), sh = op.geti("sh", 1), sw = op.geti("sw", 1);
       const int dh = op.geti("dh", 1), dw = op.geti("dw", 1);

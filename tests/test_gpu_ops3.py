@@ -166,6 +166,22 @@ def test_conv_bf16_grouped_and_depthwise(cfg):
 
 
 @pytest.mark.gpu
+def test_concat_upsample_pixelshuffle_bf16():
+    """The data-movement ops of BF16 graphs: plain copies of two-byte values (vector path and byte path of the concat)."""
+    rng = np.random.default_rng(24)
+    b = graphs.GraphBuilder(24, simulate=False)
+    b.op("input", "a", [], (2, 24, 6, 6), "BF16")
+    b.op("input", "b", [], (2, 255, 6, 6), "BF16")
+    b.op("input", "c", [], (2, 16, 6, 6), "BF16")
+    b.op("concat", "cat", ["a", "b", "c"], (2, 295, 6, 6), "BF16", axis=1, do_relu=0)
+    b.op("concat", "cat_vec", ["a", "c"], (2, 40, 6, 6), "BF16", axis=1, do_relu=0)
+    b.op("upsample", "up", ["a"], (2, 24, 12, 18), "BF16", scale_h=2, scale_w=3)
+    b.op("pixelshuffle", "ps", ["c"], (2, 4, 12, 12), "BF16", upscale_factor=2, mode="CRD")
+    ins = {k: _bf16(rng.normal(0, 1, shp)) for k, shp in (("a", (2, 24, 6, 6)), ("b", (2, 255, 6, 6)), ("c", (2, 16, 6, 6)))}
+    assert_exact(run_both(b.text(), b.weights, ins, ["cat", "cat_vec", "up", "ps"]))
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("cfg", [dict(ic=16, oc=32, g=1, hw=7, k=2, s=2, p=0, relu=0), dict(ic=24, oc=16, g=1, hw=6, k=4, s=2, p=1, relu=1),
                                  dict(ic=32, oc=32, g=32, hw=5, k=3, s=2, p=1, relu=0), dict(ic=8, oc=24, g=2, hw=9, k=3, s=1, p=1, relu=1)])
 def test_deconv_bf16(cfg):

@@ -1210,17 +1210,21 @@ private:
 };
 
 // --------------------------------------------------------------------------- Concat
-// ConcatOpKernel (core/concat.cpp:7-90), channel axis, INT8 with per-input rescale.
+// ConcatOpKernel (core/concat.cpp:7-90), channel axis: INT8 with per-input rescale; BF16 as a plain copy (the byte
+// kernels with two bytes per channel).
 class ConcatOp : public OpKernel {
 public:
   ConcatOp(Interpreter &I, const ParsedOp &op, std::vector<TensorPtr> ins, TensorPtr out) : I_(I), ins_(ins), out_(out) {
     TPUCB_CHECK(op.geti("axis", 1) == 1, "concat %s: only the channel axis is supported", op.name.c_str());
-    TPUCB_CHECK(out->dtype == DT_I8, "concat %s: only INT8 is implemented", op.name.c_str());
+    TPUCB_CHECK(out->dtype == DT_I8 || out->dtype == DT_BF16, "concat %s: INT8 and BF16 are implemented", op.name.c_str());
     const int nin = (int)ins.size();
     do_relu_ = op.geti("do_relu", 0);
+    es_ = (int)out->elsize();
+    TPUCB_CHECK(es_ == 1 || !do_relu_, "concat %s: BF16 concat with do_relu is not implemented", op.name.c_str());
+    for (auto &t : ins) TPUCB_CHECK(t->dtype == out->dtype, "concat %s: input and output types differ", op.name.c_str());
     mult_.assign(nin, 1);
     rsh_.assign(nin, 0);
-    if ((int)op.in.size() >= nin + 4 && I.has_weight(op.in[nin + 2]) && I.has_weight(op.in[nin + 3])) {
+    if (es_ == 1 && (int)op.in.size() >= nin + 4 && I.has_weight(op.in[nin + 2]) && I.has_weight(op.in[nin + 3])) {
       need_quant_ = true;
       const auto &rs = I.weight(op.in[nin + 2]).data;
       const auto &mu = I.weight(op.in[nin + 3]).data;
@@ -1232,26 +1236,28 @@ public:
     int c = 0;
     for (auto &t : ins) c += t->c;
     TPUCB_CHECK(c == out->c, "concat %s: channel counts do not add up", op.name.c_str());
-    alg_bytes = 2.0 * out->numel();
+    alg_bytes = 2.0 * out->numel() * es_;
   }
   void invoke(cudaStream_t s) override {
-    int off = 0;
+    int off = 0; // in bytes of a pixel row of the output
+    const int ocp = out_->cp * es_;
     for (size_t i = 0; i < ins_.size(); ++i) {
       auto &t = ins_[i];
-      size_t total = t->pixels() * t->c;
+      const int cb = t->c * es_, cpb = t->cp * es_; // channel bytes: BF16 moves as two bytes per channel
+      size_t total = t->pixels() * cb;
       int requant = need_quant_ && !(mult_[i] == 1 && rsh_[i] == 0);
-      if (t->c % 16 == 0 && off % 16 == 0 && t->cp % 16 == 0 && out_->cp % 16 == 0) {
-        size_t nvec = t->pixels() * (t->c / 16);
+      if (cb % 16 == 0 && off % 16 == 0 && cpb % 16 == 0 && ocp % 16 == 0) {
+        size_t nvec = t->pixels() * (cb / 16);
         launch_k(concat_slice_i8_vec_kernel, grid_for(nvec, 256, I_.sm_count), 256, 0, s, 
-            (const uint4 *)t->dev, (uint4 *)out_->dev, t->pixels(), t->c / 16, t->cp / 16, out_->cp / 16, off / 16,
+            (const uint4 *)t->dev, (uint4 *)out_->dev, t->pixels(), cb / 16, cpb / 16, ocp / 16, off / 16,
             mult_[i], rsh_[i], requant, do_relu_);
-        off += t->c;
+        off += cb;
         continue;
       }
       launch_k(concat_slice_i8_kernel, grid_for(total, 256, I_.sm_count), 256, 0, s, 
-          (const int8_t *)t->dev, (int8_t *)out_->dev, t->pixels(), t->c, t->cp, out_->cp, off, mult_[i], rsh_[i],
+          (const int8_t *)t->dev, (int8_t *)out_->dev, t->pixels(), cb, cpb, ocp, off, mult_[i], rsh_[i],
           requant, do_relu_);
-      off += t->c;
+      off += cb;
     }
   }
   int kernel_launches() const override { return (int)ins_.size(); }
@@ -1263,6 +1269,7 @@ private:
   std::vector<int> mult_, rsh_;
   bool need_quant_ = false;
   int do_relu_ = 0;
+  int es_ = 1; // bytes per channel value
 };
 
 // ------------------------------------------------------------ Upsample / PixelShuffle

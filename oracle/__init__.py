@@ -330,6 +330,14 @@ def relu(x):
     return out
 
 
+def leaky_relu_f(x, negative_slope, to_bf16=False):
+    """LeakyReluOpKernel::invoke, fp32 and BF16 (core/activation.cpp:129-131, 150-152; core/internal.cpp:20-25):
+    x > 0 ? x : x * slope in fp32, then for BF16 one rounding."""
+    x = _f32(x)
+    out = np.where(x > 0, x, (x * np.float32(negative_slope)).astype(np.float32)).astype(np.float32)
+    return bf16_round(out) if to_bf16 else out
+
+
 LUT_KINDS = {"sigmoid": 0, "mish": 1, "exp": 2, "tanh": 3}
 
 

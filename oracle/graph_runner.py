@@ -147,6 +147,8 @@ def run(text, weights, inputs, upto=None):
             out = O.pixelshuffle(X(0), _i(a, "upscale_factor", 1), a.get("mode", "CRD") == "DCR")
         elif t == "relu":
             out = O.relu(X(0))
+        elif t == "leaky_relu" and op["dtype"] != "INT8":
+            out = O.leaky_relu_f(X(0), float(a.get("negative_slope", 0.0)), to_bf16=(op["dtype"] == "BF16"))
         elif t == "leaky_relu":
             out = O.leaky_relu_i8(X(0), float(W(5)[0]), float(W(6)[0]), float(W(7)[0]), float(W(8)[0]))
         elif t in ("sigmoid", "mish", "exp", "tanh"):

@@ -166,6 +166,28 @@ def test_conv_bf16_grouped_and_depthwise(cfg):
 
 
 @pytest.mark.gpu
+def test_relu_and_leaky_relu_bf16():
+    """BF16 ReLU and leaky ReLU (x > 0 ? x : x * slope in fp32, one BF16 rounding), also right behind a BF16 convolution
+    (which must not take the INT8 fusion path)."""
+    rng = np.random.default_rng(25)
+    b = graphs.GraphBuilder(25, simulate=False)
+    b.op("input", "x", [], (2, 40, 8, 8), "BF16")
+    b.op("relu", "r", ["x"], (2, 40, 8, 8), "BF16")
+    b.op("leaky_relu", "l", ["x"], (2, 40, 8, 8), "BF16", negative_slope=0.1)
+    b.weight("w", _bf16(rng.normal(0, 0.2, (16, 40, 1, 1))))
+    b.weight("bias", rng.normal(0, 0.1, 16).astype(np.float32))
+    b.op("conv_2d", "c", ["x", "w", "bias"], (2, 16, 8, 8), "BF16", kh=1, kw=1, sh=1, sw=1, pt=0, pb=0, pl=0, pr=0,
+         dh=1, dw=1, g=1, do_relu=0, with_bias=1)
+    b.op("leaky_relu", "cl", ["c"], (2, 16, 8, 8), "BF16", negative_slope=0.125)
+    x = rng.normal(0, 1, (2, 40, 8, 8)).astype(np.float32)
+    x.reshape(-1)[:4] = [0.0, -0.0, 1e-30, -1e-30]
+    x = _bf16(x)
+    out = run_both(b.text(), b.weights, {"x": x}, ["r", "l", "c", "cl"])
+    assert_exact({k: out[k] for k in ("r", "l")})
+    assert_bf16_ulp({k: out[k] for k in ("c", "cl")})
+
+
+@pytest.mark.gpu
 def test_concat_upsample_pixelshuffle_bf16():
     """The data-movement ops of BF16 graphs: plain copies of two-byte values (vector path and byte path of the concat)."""
     rng = np.random.default_rng(24)

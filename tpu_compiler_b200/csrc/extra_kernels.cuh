@@ -228,6 +228,34 @@ __global__ void reduce_kernel(const void *__restrict__ in, void *__restrict__ ou
 __device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
 __device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
 
+// ReLU and leaky ReLU of BF16 tensors (core/activation.cpp:150-152, 168-180): x > 0 ? x : x * slope in fp32 and one
+// BF16 rounding; slope 0 is the plain ReLU (the product rounds to a signed zero, which the reference's relu() writes as
+// +0: handled apart). Eight values per thread.
+__global__ void leaky_relu_bf16_kernel(const uint4 *__restrict__ in, uint4 *__restrict__ out, size_t nvec, float slope,
+                                       int plain_relu) {
+  pdl_prologue();
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nvec; i += (size_t)gridDim.x * blockDim.x) {
+    const uint4 v = __ldg(in + i);
+    uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      uint32_t r = 0;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const uint16_t bits = (uint16_t)(w[q] >> (16 * h));
+        const float x = bf16_bits_to_f32(bits);
+        uint16_t y;
+        if (x > 0.0f) y = bits;
+        else if (plain_relu) y = 0;
+        else y = f32_to_bf16_bits(__fmul_rn(x, slope));
+        r |= (uint32_t)y << (16 * h);
+      }
+      w[q] = r;
+    }
+    out[i] = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
 // Grouped and depthwise BF16 convolution (core/conv.cpp:90-98 with g > 1: the fp32 convolution of BF16-valued operands,
 // fp32 bias, ReLU, one BF16 rounding) and, through input insertion (ins_h / ins_w zeros between the input pixels), the
 // BF16 deconvolution (core/deconv.cpp:56-68). One thread per output value, fp32 accumulation over (filter row, filter

@@ -785,7 +785,7 @@ public:
   // Fused leaky ReLU (tensor-core plans only): the epilogue writes the plain result to this op's tensor
   // and the activation result to `act_out`.
   bool can_fuse_leaky() const {
-    return !(f32_ || dw_ || !stem_plans_.empty() || act_ != 0 || plans_.empty());
+    return !(f32_ || dw_ || bf16g_ || !stem_plans_.empty() || act_ != 0 || plans_.empty()) && in_->dtype == DT_I8;
   }
   void set_leaky(int mp, int rp, int mn, int rn, int8_t *act_out) {
     for (auto &pl : plans_) {
@@ -1304,7 +1304,12 @@ private:
 class LeakyReluOp : public OpKernel {
 public:
   LeakyReluOp(Interpreter &I, const ParsedOp &op, TensorPtr in, TensorPtr out, bool plain) : I_(I), in_(in), out_(out), plain_(plain) {
-    TPUCB_CHECK(in->dtype == DT_I8 && out->dtype == DT_I8, "%s: only INT8 is implemented", op.name.c_str());
+    TPUCB_CHECK(in->dtype == out->dtype && (in->dtype == DT_I8 || in->dtype == DT_BF16), "%s: INT8 and BF16 are implemented",
+                op.name.c_str());
+    bf16_ = in->dtype == DT_BF16;
+    slope_ = (float)op.getf("negative_slope", 0.0);
+    alg_bytes = 2.0 * out->numel() * (bf16_ ? 2 : 1);
+    if (bf16_) return;
     if (!plain) {
       // operands 5..8: rshift_pos, multiplier_pos, rshift_neg, multiplier_neg (activation.cpp:113-124)
       TPUCB_CHECK(op.in.size() >= 9, "leaky_relu %s: INT8 needs 4 rescale operands", op.name.c_str());
@@ -1317,6 +1322,11 @@ public:
   }
   void invoke(cudaStream_t s) override {
     size_t nvec = out_->bytes() / 16;
+    if (bf16_) {
+      launch_k(leaky_relu_bf16_kernel, grid_for(nvec, 256, I_.sm_count), 256, 0, s, (const uint4 *)in_->dev, (uint4 *)out_->dev,
+               nvec, slope_, plain_ ? 1 : 0);
+      return;
+    }
     launch_k(leaky_relu_i8_kernel, grid_for(nvec, 256, I_.sm_count), 256, 0, s, (const int8_t *)in_->dev, (int8_t *)out_->dev,
                                                                           nvec, mp, rp, mn, rn, plain_ ? 1 : 0);
   }
@@ -1329,6 +1339,8 @@ private:
   Interpreter &I_;
   TensorPtr in_, out_;
   bool plain_;
+  bool bf16_ = false;
+  float slope_ = 0.0f;
 };
 
 // ---------------------------------------------------------------------- LUT activations
@@ -1849,7 +1861,7 @@ inline void Interpreter::fuse_activation_chains(const std::map<std::string, int>
   // epilogue applies it and writes both tensors; the leaky op becomes a placeholder.
   for (size_t j = 0; j < n; ++j) {
     auto *lk = dynamic_cast<LeakyReluOp *>(kernels[j].get());
-    if (!lk || lk->plain()) continue;
+    if (!lk || lk->plain() || lk->in()->dtype != DT_I8) continue;
     for (size_t i = 0; i < j; ++i) {
       auto *cv = dynamic_cast<Conv2DOp *>(kernels[i].get());
       if (!cv || cv->out() != lk->in()) continue;

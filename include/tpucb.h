@@ -137,12 +137,11 @@ int tpucb_interp_get_details(tpucb_interp *it, int outputs, char *out, size_t ca
 int tpucb_interp_get_op_info(tpucb_interp *it, char *out, size_t cap, size_t *needed);
 
 /* Options: "cuda_graph" (0/1, default 1): replay the op list as one CUDA graph.
- *          "pdl" (1 on, 0 off, -1 automatic = default): programmatic dependent launch between the op kernels; each
- *          kernel's launch and set-up (barriers, tensor memory) overlap the tail of the kernel before it, and it
- *          waits for that kernel's results before its first global access. Automatic: the third graph launch of a
- *          module captures the op list both ways, replays each ten times and keeps the faster graph (the extra
- *          replays recompute the same results); earlier launches, launches outside the graph and modules that move
- *          48 MB or more per kernel follow a rule (on for modules that move less than 10 MB per kernel on average).
+ *          "pdl" (0 off, 1 = default, 2 every kernel): programmatic dependent launch. A kernel launched with the
+ *          attribute may be scheduled while its predecessor in the stream is still running: its launch and set-up
+ *          (barriers, tensor memory) overlap that kernel's tail, and it waits for that kernel's results before its first
+ *          global access. 1 gives the attribute to the tensor-core convolution kernels only, which measured faster than
+ *          none and than all on every graph and batch tried (on the memory-bound kernels alone it costs 1-5%).
  *          "split_k" (0/1, default 1; read by the next load_module): INT8 convolutions and inner products with few
  *          tiles and 24 K blocks or more share each tile among several CTAs (exact: int32 partial sums).
  *          "fuse_activations" (0/1, default 1; read by the next load_module): run each

@@ -139,16 +139,17 @@ def test_resnet50_with_residual_adds_in_the_convolution_epilogue(model_b1):
 
 
 def test_programmatic_dependent_launch_on_and_off(model_b1):
-    """Option pdl: every kernel of the op list is launched so that it may start while its predecessor finishes and
-    orders itself behind it on the device. Forced on and forced off must give the same tensors, launch after launch
-    (a kernel that read its input too early would show as a difference between replays)."""
+    """Option pdl: kernels (1: the convolution kernels, 2: every kernel of the op list) are launched so that they may
+    start while their predecessor finishes and order themselves behind it on the device. Off and both on forms must
+    give the same tensors, launch after launch (a kernel that read its input too early would show as a difference
+    between replays)."""
     from tpu_compiler_b200 import module
     B = 2
     imgs = np.random.default_rng(7).uniform(-1, 1, (B, 3, 224, 224)).astype(np.float32)
     mb = graphs.resnet50_int8(batch=B, seed=1001)
     names = ["conv1", "pool1", "res2a", "res3d", "res4f", "res5c", "pool5", "fc1000_dequant"]
     got = {}
-    for pdl in (0, 1):
+    for pdl in (0, 1, 2):
         m = module(0)
         m.set_option("pdl", pdl)
         m.load_text(mb.text, mb.weights)
@@ -163,7 +164,8 @@ def test_programmatic_dependent_launch_on_and_off(model_b1):
                 got[(pdl, rep)] = cur
         m.close()
     for n in names:
-        assert np.array_equal(got[(0, 0)][n], got[(1, 0)][n]) and np.array_equal(got[(0, 1)][n], got[(1, 1)][n]), n
+        for pdl in (1, 2):
+            assert np.array_equal(got[(0, 0)][n], got[(pdl, 0)][n]) and np.array_equal(got[(0, 1)][n], got[(pdl, 1)][n]), n
         assert np.array_equal(got[(0, 0)][n][0], got[(0, 1)][n][1]), n
 
 

@@ -471,6 +471,7 @@ inline void launch_conv_plan(const ConvPlan &pl, cudaStream_t stream, int sm_cou
       launch_k(patch_expand_i8_kernel, grid_for(total, 256, sm_count), 256, 0, stream, pl.in, pl.patch_buf, pl.patch);
   }
   const int threads = kConvThreads;
+  PdlConvScope conv_class; // the tensor-core kernel and its helper passes may start while the predecessor finishes
   if (pl.tf32) {
     if (pl.split_src)
       launch_k(tf32_split_kernel, grid_for(pl.split_nvec, 256, sm_count), 256, 0, stream, 

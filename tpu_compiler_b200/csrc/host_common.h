@@ -73,8 +73,9 @@ struct HostWeight {
   std::vector<int64_t> shape;
 };
 
-// Whether launch_k marks its launches for programmatic dependent launch (option "pdl" of the interpreter whose call
-// is running; set by Interpreter::bind).
+// Whether launch_k marks its launches for programmatic dependent launch. Set per launch: the interpreter's option
+// "pdl" says which class of kernels gets the mark (pdl_mode: 0 none, 1 the tensor-core convolution kernels, 2 all), and
+// the code that launches a kernel of the convolution class says so with PdlConvScope.
 inline bool &launch_pdl_flag() {
   static thread_local bool on = true;
   return on;
@@ -85,6 +86,17 @@ inline bool &conv_split_k_enabled() {
   static thread_local bool on = true;
   return on;
 }
+
+inline int &pdl_mode() {
+  static thread_local int v = 1;
+  return v;
+}
+// While one lives, launch_k marks launches when the mode includes the convolution class; afterwards as before.
+struct PdlConvScope {
+  bool before;
+  PdlConvScope() : before(launch_pdl_flag()) { launch_pdl_flag() = pdl_mode() >= 1; }
+  ~PdlConvScope() { launch_pdl_flag() = before; }
+};
 
 #ifdef __CUDACC__
 // Launch of an op kernel. With the flag above the launch carries the programmatic stream serialisation

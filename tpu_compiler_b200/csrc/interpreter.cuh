@@ -120,7 +120,8 @@ public:
 
   void bind() {
     TPUCB_CUDA(cudaSetDevice(device_));
-    launch_pdl_flag() = use_pdl < 0 ? pdl_auto : use_pdl != 0;
+    pdl_mode() = use_pdl;
+    launch_pdl_flag() = use_pdl >= 2;
     conv_split_k_enabled() = split_k && selftest_lost_arrival == 0; // the self-test needs tiles that follow one another in a CTA
   }
   int device() const { return device_; }
@@ -229,21 +230,15 @@ public:
   cudaStream_t stream = nullptr;
   int *d_err = nullptr;
   bool use_graph = true;
-  // Programmatic dependent launch between the kernels of the op list: 1 on, 0 off, -1 decided per module at load.
-  // It hides each kernel's launch and set-up behind its predecessor's tail, which pays while kernels are short
-  // (INT8 ResNet-50: 10% fewer ms per launch at batch 1 to 16, 2% at 64) and costs once they are long (3% more at
-  // batch 256, 4 to 6% more on the YOLOv4-style graph at every batch). No property of the op list predicts the sign,
-  // so in automatic mode the third graph launch of a module captures the op list both ways, replays each a few
-  // times and keeps the faster graph (measure_pdl; the replays recompute the same results from the same inputs).
-  // Until then, for launches outside the graph and for modules of 48 MB or more per kernel a rule holds: on when
-  // the module moves less than 10 MB per kernel on average.
-  int use_pdl = -1;
-  bool pdl_auto = false;     // the choice in effect while use_pdl < 0
-  bool pdl_measured = false; // ... and whether it comes from the measurement below or from the load-time rule
-  bool pdl_worth_measuring = false; // modules that move 48 MB or more per kernel keep the rule's "off" (3% at most)
-  int graph_launches = 0;
+  // Programmatic dependent launch (option "pdl"): a kernel launched with the attribute may be scheduled while its
+  // predecessor in the stream is still running; it sets up its barriers and tensor memory and then waits for that
+  // kernel's results (pdl_wait). 1 (default): the tensor-core convolution kernels carry the attribute; 0: none; 2: every
+  // kernel. Measured per class (ms per graph launch, off / all / convolutions only): INT8 ResNet-50 batch 1 0.379 / 0.348 /
+  // 0.334, batch 32 0.697 / 0.668 / 0.657, batch 256 3.074 / 3.193 / 3.063; YOLOv4-style batch 8 2.361 / 2.412 / 2.265;
+  // MobileNet-v2 batch 32 0.526 / 0.504 / 0.485. On the memory-bound kernels alone the attribute costs 1-5%: their blocks
+  // then take their SMs in the order the predecessor's CTAs leave instead of evenly.
+  int use_pdl = 1;
   cudaGraphExec_t capture_graph();
-  void measure_pdl();
   // Self-test (option "selftest_lost_arrival", read by the next load_module): > 0 makes every INT8 tensor-core
   // convolution built from then on lose its accumulator hand-back and wait only that many rounds of 1024 polls
   // (ConvGemmParams::wait_rounds / lose_arrival), so that a launch ends with a bounded-wait error status.
@@ -857,11 +852,13 @@ public:
       launch_k(dwconv_i8_kernel, grid_for(total, 128, I_.sm_count), 128, 0, s, (const int8_t *)in_->dev,
                                                                           (int8_t *)out_->dev, dwargs_);
     } else {
-      for (auto &sp : stem_plans_)
+      for (auto &sp : stem_plans_) {
+        PdlConvScope conv_class;
         if ((sp.p.fastq & 1) && sp.p.act == 1) // the ReLU epilogue alone: most stems
           launch_k(conv_stem_i8_kernel<true, true>, sp.grid, kStemThreads, sp.smem, s, sp.tmB, sp.p);
         else if (sp.p.fastq & 1) launch_k(conv_stem_i8_kernel<true>, sp.grid, kStemThreads, sp.smem, s, sp.tmB, sp.p);
         else launch_k(conv_stem_i8_kernel<false>, sp.grid, kStemThreads, sp.smem, s, sp.tmB, sp.p);
+      }
       for (auto &pl : plans_) launch_conv_plan(pl, s, I_.sm_count);
     }
   }
@@ -1946,8 +1943,6 @@ inline void Interpreter::fuse_activation_chains(const std::map<std::string, int>
 inline void Interpreter::reset_module() {
   bind();
   invalidate_graph();
-  pdl_measured = false;
-  graph_launches = 0;
   kernels.clear();
   for (auto &kv : tensors)
     if (kv.second->owns && kv.second->dev) cudaFree(kv.second->dev);
@@ -2123,16 +2118,6 @@ inline int Interpreter::add_op(const ParsedOp &op_in) {
 inline void Interpreter::finish_module() {
   if (fuse_activations) fuse_activation_chains(uses);
   link_tf32_remainders();
-  {
-    double bytes = 0;
-    int launches = 0;
-    for (auto &k : kernels) {
-      bytes += k->alg_bytes;
-      launches += k->kernel_launches();
-    }
-    pdl_auto = launches > 0 && bytes / launches < 10e6;
-    pdl_worth_measuring = launches > 1 && bytes / launches < 48e6;
-  }
   output_details.clear();
   for (auto &k : kernels)
     if (!uses.count(k->name) && k->op_type != "input") output_details.push_back({k->name, k->result->numel() / (size_t)max_batch});
@@ -2374,59 +2359,10 @@ inline cudaGraphExec_t Interpreter::capture_graph() {
   return exec;
 }
 
-// Automatic mode: programmatic dependent launch on or off, by the replay time of the two graphs (best of three
-// rounds of three replays after one warm-up replay each; "on" has to win by 1%). Leaves the chosen graph in
-// graph_exec. The self-test mode of the bounded waits keeps the rule: its launches end in an error status.
-inline void Interpreter::measure_pdl() {
-  cudaGraphExec_t ex[2] = {nullptr, nullptr};
-  cudaEvent_t a = nullptr, b = nullptr;
-  float best[2] = {1e30f, 1e30f};
-  try {
-    for (int mode = 0; mode < 2; ++mode) {
-      launch_pdl_flag() = mode != 0;
-      ex[mode] = capture_graph();
-      TPUCB_CUDA(cudaGraphLaunch(ex[mode], stream));
-    }
-    TPUCB_CUDA(cudaEventCreate(&a));
-    TPUCB_CUDA(cudaEventCreate(&b));
-    for (int round = 0; round < 3; ++round)
-      for (int mode = 0; mode < 2; ++mode) {
-        TPUCB_CUDA(cudaEventRecord(a, stream));
-        for (int i = 0; i < 3; ++i) TPUCB_CUDA(cudaGraphLaunch(ex[mode], stream));
-        TPUCB_CUDA(cudaEventRecord(b, stream));
-        TPUCB_CUDA(cudaEventSynchronize(b));
-        float ms = 0;
-        TPUCB_CUDA(cudaEventElapsedTime(&ms, a, b));
-        if (ms < best[mode]) best[mode] = ms;
-      }
-  } catch (...) {
-    for (auto e : ex)
-      if (e) cudaGraphExecDestroy(e);
-    if (a) cudaEventDestroy(a);
-    if (b) cudaEventDestroy(b);
-    launch_pdl_flag() = pdl_auto;
-    throw;
-  }
-  cudaEventDestroy(a);
-  cudaEventDestroy(b);
-  const int pick = best[1] < 0.99f * best[0] ? 1 : 0;
-  cudaGraphExecDestroy(ex[1 - pick]);
-  graph_exec = ex[pick];
-  pdl_auto = pick != 0;
-  pdl_measured = true;
-  launch_pdl_flag() = pdl_auto;
-}
-
 // invoke (MlirModuleInterpreter.cpp:371-381): the op loop; replayed as one CUDA graph.
 inline void Interpreter::launch_all() {
   bind();
   if (use_graph) {
-    // automatic mode: measured at the module's third graph launch (a module that is launched once or twice, like the
-    // tuner's per-candidate modules, never pays for it) and only where the answer is open (pdl_worth_measuring)
-    if (use_pdl < 0 && !pdl_measured && pdl_worth_measuring && selftest_lost_arrival == 0 && ++graph_launches == 3) {
-      invalidate_graph();
-      measure_pdl();
-    }
     if (!graph_exec) graph_exec = capture_graph();
     TPUCB_CUDA(cudaGraphLaunch(graph_exec, stream));
   } else {

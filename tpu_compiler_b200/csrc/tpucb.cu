@@ -367,7 +367,8 @@ int tpucb_interp_set_option(tpucb_interp *it, const char *key, int value) {
     it->impl.use_graph = value != 0;
     it->impl.invalidate_graph();
   } else if (k == "pdl") {
-    it->impl.use_pdl = value < 0 ? -1 : (value != 0);
+    TPUCB_CHECK(value >= -1 && value <= 2, "pdl: 0 (off), 1 (convolution kernels, the default) or 2 (every kernel)");
+    it->impl.use_pdl = value < 0 ? 1 : value;
     it->impl.invalidate_graph();
   } else if (k == "selftest_lost_arrival") {
     TPUCB_CHECK(value >= 0 && value <= 1024, "selftest_lost_arrival: rounds must be in [0, 1024]");

@@ -722,10 +722,23 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
   __syncthreads();
   ptx::tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  // From here on the kernel touches global memory: the previous kernel's writes must be complete and visible.
-  pdl_wait();
   if (*abort_flag != 0) total_tiles = 0;
   const int total_items = total_tiles * split_k;
+  // What does not depend on the previous kernel is started before the wait for it: the tensor maps are fetched and a
+  // CTA that keeps its weights resident starts their copies (weights are written at load time only).
+  if (warp == 0 && lane == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tmA) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tmB) : "memory");
+    if (p.w_resident && (int)blockIdx.x < total_tiles) {
+      const int n0w = ((int)blockIdx.x % n_tiles) * p.BN - (p.dual ? 64 : 0);
+      ptx::mbar_expect_tx(bar_w, (uint32_t)k_iters * b_bytes);
+      for (int kit = 0; kit < k_iters; ++kit)
+        ptx::tma_load_3d(w_base + (uint32_t)kit * b_bytes, &tmB, bar_w, (kit % p.c_chunks) * p.BK, kit / p.c_chunks,
+                         n0w);
+    }
+  }
+  // From here on the kernel touches the activations: the previous kernel's writes must be complete and visible.
+  pdl_wait();
 
   if (warp == 0) {
     // ---------------------------------------------------------------- producer
@@ -734,14 +747,7 @@ __device__ __forceinline__ void conv_gemm_body(const CUtensorMap &tmA, const CUt
       int ps = 0;        // ring stage of iteration `it`
       uint32_t pph = 0;  // its phase bit
       bool ok = true;
-      if (p.w_resident && (int)blockIdx.x < total_tiles) {
-        const int n0w = ((int)blockIdx.x % n_tiles) * p.BN - (p.dual ? 64 : 0);
-        ptx::mbar_expect_tx(bar_w, (uint32_t)k_iters * b_bytes);
-        for (int kit = 0; kit < k_iters; ++kit)
-          ptx::tma_load_3d(w_base + (uint32_t)kit * b_bytes, &tmB, bar_w, (kit % p.c_chunks) * p.BK,
-                           kit / p.c_chunks, n0w);
-      }
-      int tm = walk_m0, tn = walk_n0;
+      int tm = walk_m0, tn = walk_n0; // (resident weights: their copies were started before the wait above)
       for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
         int k_begin = 0, k_end = kTerms * k_iters;
         if (split_k > 1) { // few items per CTA: the divisions do not matter here

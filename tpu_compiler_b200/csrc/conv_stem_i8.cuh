@@ -87,14 +87,18 @@ conv_stem_i8_kernel(const __grid_constant__ CUtensorMap tmB, const ConvStemParam
   __syncthreads();
   ptx::tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  pdl_wait(); // global memory from here on
   if (*abort_flag != 0) total_tiles = 0;
+  // the weights do not depend on the previous kernel: their copy starts before the wait for it
+  if (warp == 0 && lane == 0 && (int)blockIdx.x < total_tiles) {
+    const uint32_t b_bytes = (uint32_t)p.kh * w_rows * 32u;
+    asm volatile("prefetch.tensormap [%0];" ::"l"(&tmB) : "memory");
+    ptx::mbar_expect_tx(bar_b, b_bytes);
+    ptx::tma_load_3d(b_tiles, &tmB, bar_b, 0, n0 - (p.dual ? 64 : 0), 0);
+  }
+  pdl_wait(); // the activations from here on
 
   if (warp == 0) {
     if (lane == 0 && (int)blockIdx.x < total_tiles) {
-      const uint32_t b_bytes = (uint32_t)p.kh * w_rows * 32u;
-      ptx::mbar_expect_tx(bar_b, b_bytes);
-      ptx::tma_load_3d(b_tiles, &tmB, bar_b, 0, n0 - (p.dual ? 64 : 0), 0);
       bool ok = ptx::mbar_wait_bounded(bar_b, 0u, abort_flag);
       if (!ok) {
         // the copy is still owed: wait for it (bounded) before the CTA may release shared memory

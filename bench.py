@@ -38,6 +38,18 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 
+PDL_OPTION = None  # --pdl: the interpreter's "pdl" option for every module of the run (None: the library's default)
+
+
+def new_module(device):
+    """A module on `device`, with the options given on the command line."""
+    from tpu_compiler_b200 import module
+    m = module(device)
+    if PDL_OPTION is not None:
+        m.set_option("pdl", PDL_OPTION)
+    return m
+
+
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -164,7 +176,7 @@ def calibration_record(rank, world, local_rank, dist, images_per_gpu, bs, check_
     from tpu_compiler_b200.calibration import ActivationCalibrator
     n_batches = max(images_per_gpu // bs, 1)
     model = graphs.resnet50_fp32(batch=bs)
-    m = module(local_rank)
+    m = new_module(local_rank)
     m.load_text(model.text, model.weights)
     rng = np.random.default_rng(7000 + rank)
     # the input batches lie in pinned host memory, as a loader with pin_memory=True delivers them: the calibrator sends
@@ -226,7 +238,7 @@ def calibration_record(rank, world, local_rank, dist, images_per_gpu, bs, check_
     # ---- untimed: N ranks together against rank 0 alone on the same images
     cb = 8
     small = graphs.resnet50_fp32(batch=cb)
-    ms = module(local_rank)
+    ms = new_module(local_rank)
     ms.load_text(small.text, small.weights)
     crng = np.random.default_rng(7777)
     cdata = [np.clip(crng.standard_normal((cb, 3, 224, 224), dtype=np.float32), -3, 3) for _ in range(check_images // cb)]
@@ -301,7 +313,7 @@ def run_tuner(args, local_rank):
     model = graphs.resnet50_fp32(batch=n)
     rng = np.random.default_rng(7100)
     images = np.clip(rng.standard_normal((n, 3, 224, 224), dtype=np.float32), -3, 3)
-    m = module(local_rank)
+    m = new_module(local_rank)
     m.load_text(model.text, model.weights)
     # the candidate tables: one min / max pass, the cached activations serve all three histogram sizes
     cal = ActivationCalibrator(m, lambda: iter([images]))
@@ -371,7 +383,7 @@ def run_conv_sweep(args, local_rank):
     for c, hw, n, k, co, relu in cases:
         model = graphs.single_conv_i8(n=n, c_in=c, c_out=co, hw=hw, k=k, stride=1, pad=k // 2, relu=bool(relu),
                                       seed=2000 + c + n)
-        m = module(local_rank)
+        m = new_module(local_rank)
         m.load_text(model.text, model.weights)
         m.set_tensor("x", model.meta["x"])
         for _ in range(max(args.warmup, 3)):
@@ -423,7 +435,7 @@ def h2d_ceiling(nbytes, local_rank, barrier, max_over_ranks, world, reps=10):
 def graph_replay_rate(model, local_rank, inputs, steps, warmup=5):
     """(ms per launch, kernels per launch) of a module under CUDA-graph replay, inputs resident."""
     from tpu_compiler_b200 import module
-    m = module(local_rank)
+    m = new_module(local_rank)
     m.load_text(model.text, model.weights)
     for k, v in inputs.items():
         m.set_tensor(k, v)
@@ -441,7 +453,7 @@ def batch1_record(local_rank, steps=200):
     from tpu_compiler_b200 import graphs, module
     model = graphs.resnet50_int8(batch=1, seed=1001)
     x = np.random.default_rng(4243).uniform(-1, 1, (1, 3, 224, 224)).astype(np.float32)
-    m = module(local_rank)
+    m = new_module(local_rank)
     m.load_text(model.text, model.weights)
     m.set_tensor("data", x)
     for _ in range(10):
@@ -496,6 +508,8 @@ def main():
     ap.add_argument("--cpu-threads", type=int, default=0, help="--impl reference: host threads (default: all)")
     ap.add_argument("--no-extras", action="store_true", help="headline only: skip the batch-1 configuration, the "
                     "secondary graphs, the link ceiling and the calibration sub-record")
+    ap.add_argument("--pdl", type=int, default=None, choices=(0, 1, 2),
+                    help="programmatic dependent launch: 0 off, 1 the convolution kernels (the library's default), 2 every kernel")
     ap.add_argument("--case", default=None, help="conv_sweep only: one case as c,hw,n[,k[,c_out[,relu]]]")
     ap.add_argument("--cal-images", type=int, default=512, help="calibration workload: images per GPU")
     ap.add_argument("--cal-batch", type=int, default=64, help="calibration workload: images per batch (64 in the "
@@ -505,6 +519,8 @@ def main():
                     help="resnet50 is the headline configuration; the others are the secondary graphs "
                          "(their lines carry no cpu_baseline)")
     args = ap.parse_args()
+    global PDL_OPTION
+    PDL_OPTION = args.pdl
     if args.cpu_threads:
         os.environ["OMP_NUM_THREADS"] = str(args.cpu_threads)   # before any OpenMP runtime loads
     if args.workload == "conv_sweep":
@@ -553,7 +569,7 @@ def main():
         model = graphs.resnet50_int8(batch=B, seed=1001)
     else:
         model = getattr(graphs, wl["builder"])(batch=B, simulate=False)
-    m = module(local_rank)
+    m = new_module(local_rank)
     m.load_text(model.text, model.weights)
 
     # pinned host buffers: this rank's image shard and its results (every module output)
